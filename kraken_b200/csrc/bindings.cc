@@ -1,0 +1,925 @@
+// Python bindings (`kraken_b200._C`).  Thin: every function converts torch
+// tensors to raw pointers and forwards to the host core (core/, cpu/) or to
+// the kernel launchers (cuda/kernels.h) on the current CUDA stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <cstring>
+
+#include "core/checkpoint.h"
+#include "core/hash.h"
+#include "core/router.h"
+#include "core/serialize.h"
+#include "core/task_queue.h"
+#include "cpu/cpu_ops.h"
+#include "cpu/cpu_shard.h"
+#include "cuda/kernels.h"
+
+namespace py = pybind11;
+using namespace kb;
+
+namespace {
+
+#define CUDA_OK(expr)                                                                                   \
+  do {                                                                                                  \
+    cudaError_t e__ = (expr);                                                                           \
+    if (e__ != cudaSuccess) throw std::runtime_error(std::string(#expr) + ": " + cudaGetErrorString(e__)); \
+  } while (0)
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+template <typename T>
+T* ptr(const torch::Tensor& t) {
+  return t.defined() && t.numel() > 0 ? reinterpret_cast<T*>(t.data_ptr()) : nullptr;
+}
+template <typename T>
+T* optr(const c10::optional<torch::Tensor>& t) {
+  return t.has_value() ? ptr<T>(*t) : nullptr;
+}
+
+void need_cuda(const torch::Tensor& t, const char* name, c10::ScalarType st) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  TORCH_CHECK(t.scalar_type() == st, name, " has the wrong dtype");
+}
+void need_cpu(const torch::Tensor& t, const char* name, c10::ScalarType st) {
+  TORCH_CHECK(!t.is_cuda(), name, " must be a CPU tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  TORCH_CHECK(t.scalar_type() == st, name, " has the wrong dtype");
+}
+
+// ------------------------------------------------------------------ tensors <-> HostTensor
+DType dtype_of(const torch::Tensor& t) {
+  switch (t.scalar_type()) {
+    case torch::kBool: return DType::kBool;
+    case torch::kUInt8: return DType::kUint8;
+    case torch::kInt8: return DType::kInt8;
+    case torch::kInt16: return DType::kInt16;
+    case torch::kInt32: return DType::kInt32;
+    case torch::kInt64: return DType::kInt64;
+    case torch::kFloat16: return DType::kFloat16;
+    case torch::kFloat32: return DType::kFloat32;
+    case torch::kFloat64: return DType::kFloat64;
+    default: throw KrakenError(err::kBadArgument, "unsupported torch dtype");
+  }
+}
+
+c10::ScalarType scalar_of(DType d) {
+  switch (d) {
+    case DType::kBool: return torch::kBool;
+    case DType::kUint8: return torch::kUInt8;
+    case DType::kInt8: return torch::kInt8;
+    case DType::kInt16: return torch::kInt16;
+    case DType::kUint16: return torch::kInt16;
+    case DType::kInt32: return torch::kInt32;
+    case DType::kUint32: return torch::kInt32;
+    case DType::kInt64: return torch::kInt64;
+    case DType::kUint64: return torch::kInt64;
+    case DType::kFloat16: return torch::kFloat16;
+    case DType::kFloat32: return torch::kFloat32;
+    case DType::kFloat64: return torch::kFloat64;
+    default: throw KrakenError(err::kBadArgument, "unsupported element type");
+  }
+}
+
+HostTensor to_host(const torch::Tensor& t_in) {
+  torch::Tensor t = t_in.detach().cpu().contiguous();
+  HostTensor h;
+  h.dtype = dtype_of(t);
+  h.dims.assign(t.sizes().begin(), t.sizes().end());
+  h.data.resize(static_cast<size_t>(t.numel()) * t.element_size());
+  if (!h.data.empty()) std::memcpy(h.data.data(), t.data_ptr(), h.data.size());
+  return h;
+}
+
+torch::Tensor from_host(const HostTensor& h) {
+  if (h.layout == Layout::kCoo) {
+    // densify: zeros then add at the flat indices
+    torch::Tensor idx = from_host(*h.indices).to(torch::kInt64).reshape({-1});
+    torch::Tensor val = from_host(*h.values).reshape({-1});
+    int64_t n = 1;
+    for (auto d : h.dims) n *= d;
+    torch::Tensor out = torch::zeros({n}, val.options());
+    out.index_add_(0, idx, val);
+    return out.reshape(h.dims);
+  }
+  torch::Tensor t = torch::empty(h.dims, torch::TensorOptions().dtype(scalar_of(h.dtype)));
+  if (t.numel() > 0) std::memcpy(t.data_ptr(), h.data.data(), std::min<size_t>(h.data.size(), t.nbytes()));
+  return t;
+}
+
+py::dict value_to_py(const Value& v) {
+  py::dict d, st, sti;
+  d["val"] = from_host(v.val);
+  for (auto& kv : v.states) st[py::int_(kv.first)] = from_host(kv.second);
+  for (auto& kv : v.states_i) sti[py::int_(kv.first)] = kv.second;
+  d["states"] = st;
+  d["states_i"] = sti;
+  return d;
+}
+
+Value value_from_py(const py::dict& d) {
+  Value v;
+  v.val = to_host(d["val"].cast<torch::Tensor>());
+  if (d.contains("states"))
+    for (auto kv : d["states"].cast<py::dict>()) v.states[kv.first.cast<uint32_t>()] = to_host(kv.second.cast<torch::Tensor>());
+  if (d.contains("states_i"))
+    for (auto kv : d["states_i"].cast<py::dict>()) v.states_i[kv.first.cast<uint32_t>()] = kv.second.cast<int64_t>();
+  return v;
+}
+
+py::dict columns_to_py(const ckpt::SparseColumns& c) {
+  py::dict d, st, sti;
+  const int64_t n = static_cast<int64_t>(c.ids.size());
+  torch::Tensor ids = torch::empty({n}, torch::kInt64);
+  if (n) std::memcpy(ids.data_ptr(), c.ids.data(), n * 8);
+  torch::Tensor vals = torch::empty({n, c.dim}, torch::kFloat32);
+  if (n) std::memcpy(vals.data_ptr(), c.vals.data(), c.vals.size() * 4);
+  for (auto& kv : c.states) {
+    torch::Tensor s = torch::zeros({n, c.dim}, torch::kFloat32);
+    if (!kv.second.empty()) std::memcpy(s.data_ptr(), kv.second.data(), std::min<size_t>(kv.second.size() * 4, s.nbytes()));
+    st[py::int_(kv.first)] = s;
+  }
+  for (auto& kv : c.states_i) {
+    torch::Tensor s = torch::zeros({n}, torch::kInt64);
+    if (!kv.second.empty()) std::memcpy(s.data_ptr(), kv.second.data(), std::min<size_t>(kv.second.size() * 8, s.nbytes()));
+    sti[py::int_(kv.first)] = s;
+  }
+  d["dim"] = c.dim;
+  d["ids"] = ids;
+  d["vals"] = vals;
+  d["states"] = st;
+  d["states_i"] = sti;
+  return d;
+}
+
+ckpt::SparseColumns columns_from_py(int64_t dim, const torch::Tensor& ids, const torch::Tensor& vals,
+                                    const py::dict& states, const py::dict& states_i) {
+  ckpt::SparseColumns c;
+  c.dim = dim;
+  torch::Tensor i = ids.detach().cpu().contiguous();
+  need_cpu(i, "ids", torch::kInt64);
+  const int64_t n = i.numel();
+  c.ids.resize(n);
+  if (n) std::memcpy(c.ids.data(), i.data_ptr(), n * 8);
+  torch::Tensor v = vals.detach().cpu().contiguous().to(torch::kFloat32);
+  TORCH_CHECK(v.numel() == n * dim, "vals must be [n, dim]");
+  c.vals.resize(n * dim);
+  if (n) std::memcpy(c.vals.data(), v.data_ptr(), n * dim * 4);
+  for (auto kv : states) {
+    torch::Tensor s = kv.second.cast<torch::Tensor>().detach().cpu().contiguous().to(torch::kFloat32);
+    TORCH_CHECK(s.numel() == n * dim, "state must be [n, dim]");
+    auto& col = c.states[kv.first.cast<uint32_t>()];
+    col.resize(n * dim);
+    if (n) std::memcpy(col.data(), s.data_ptr(), n * dim * 4);
+  }
+  for (auto kv : states_i) {
+    torch::Tensor s = kv.second.cast<torch::Tensor>().detach().cpu().contiguous().to(torch::kInt64);
+    TORCH_CHECK(s.numel() == n, "state_i must be [n]");
+    auto& col = c.states_i[kv.first.cast<uint32_t>()];
+    col.resize(n);
+    if (n) std::memcpy(col.data(), s.data_ptr(), n * 8);
+  }
+  return c;
+}
+
+ckpt::RowFilter make_filter(int mode, uint64_t salt, uint32_t world, uint32_t rank, const Router* ring, uint64_t table_id,
+                            uint64_t node) {
+  ckpt::RowFilter f;
+  f.mode = static_cast<ckpt::RowFilter::Mode>(mode);
+  f.table_salt = salt;
+  f.world = world;
+  f.rank = rank;
+  f.ring = ring;
+  f.table_id = table_id;
+  f.node = node;
+  return f;
+}
+
+// ------------------------------------------------------------------ symmetric heap
+// One cudaMalloc'd arena per rank, exported with a CUDA IPC handle and mapped by
+// every peer of the same box.
+struct SymHeap {
+  void* local = nullptr;
+  size_t bytes = 0;
+  int rank = 0, world = 1;
+  std::vector<void*> bases;
+  std::vector<bool> opened;
+
+  SymHeap(size_t nbytes, int r, int w) : bytes(nbytes), rank(r), world(w) {
+    TORCH_CHECK(w >= 1 && w <= cu::kMaxWorldHost, "world size must be 1..16");
+    CUDA_OK(cudaMalloc(&local, nbytes));
+    CUDA_OK(cudaMemset(local, 0, nbytes));
+    bases.assign(w, nullptr);
+    opened.assign(w, false);
+    bases[r] = local;
+  }
+  ~SymHeap() { Close(); }
+  py::bytes Handle() const {
+    cudaIpcMemHandle_t h;
+    CUDA_OK(cudaIpcGetMemHandle(&h, local));
+    return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+  }
+  void Open(const std::vector<std::string>& handles) {
+    TORCH_CHECK(static_cast<int>(handles.size()) == world, "need one handle per rank");
+    for (int p = 0; p < world; ++p) {
+      if (p == rank) continue;
+      TORCH_CHECK(handles[p].size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle size");
+      cudaIpcMemHandle_t h;
+      std::memcpy(&h, handles[p].data(), sizeof(h));
+      CUDA_OK(cudaIpcOpenMemHandle(&bases[p], h, cudaIpcMemLazyEnablePeerAccess));
+      opened[p] = true;
+    }
+  }
+  void Close() {
+    for (int p = 0; p < static_cast<int>(bases.size()); ++p)
+      if (opened[p]) {
+        cudaIpcCloseMemHandle(bases[p]);
+        opened[p] = false;
+      }
+    if (local) {
+      cudaFree(local);
+      local = nullptr;
+    }
+  }
+  cu::SymHost View() const {
+    cu::SymHost s{};
+    for (int p = 0; p < world; ++p) s.base[p] = bases[p];
+    s.rank = rank;
+    s.world = world;
+    return s;
+  }
+  // Typed window into the local arena (no ownership: the heap must outlive it).
+  torch::Tensor Window(size_t off, std::vector<int64_t> shape, py::object dtype) const {
+    auto st = torch::python::detail::py_object_to_dtype(dtype);
+    int64_t n = 1;
+    for (auto d : shape) n *= d;
+    TORCH_CHECK(off + static_cast<size_t>(n) * c10::elementSize(st) <= bytes, "window exceeds the heap");
+    int dev;
+    CUDA_OK(cudaGetDevice(&dev));
+    return torch::from_blob(static_cast<char*>(local) + off, shape,
+                            torch::TensorOptions().dtype(st).device(torch::kCUDA, dev));
+  }
+};
+
+cu::TableHost make_table(const torch::Tensor& keys, const torch::Tensor& val, const c10::optional<torch::Tensor>& s0,
+                         const c10::optional<torch::Tensor>& s1, const c10::optional<torch::Tensor>& s2,
+                         const c10::optional<torch::Tensor>& steps, const c10::optional<torch::Tensor>& lead,
+                         const torch::Tensor& size, const torch::Tensor& status, uint32_t bits, int dim, int init_type,
+                         float init_a, float init_b, uint64_t seed_key) {
+  need_cuda(keys, "keys", torch::kInt64);
+  need_cuda(val, "val", torch::kFloat32);
+  TORCH_CHECK(keys.numel() == (1ll << bits), "keys must have 1 << bits elements");
+  TORCH_CHECK(val.numel() == keys.numel() * dim, "val must be [cap, dim]");
+  cu::TableHost t{};
+  t.keys = keys.data_ptr();
+  t.val = ptr<float>(val);
+  t.s[0] = optr<float>(s0);
+  t.s[1] = optr<float>(s1);
+  t.s[2] = optr<float>(s2);
+  t.steps = optr<int>(steps);
+  t.lead = lead.has_value() ? lead->data_ptr() : nullptr;
+  t.size = ptr<int>(size);
+  t.status = ptr<int>(status);
+  t.bits = bits;
+  t.dim = dim;
+  t.init.type = static_cast<uint8_t>(init_type);
+  t.init.a = init_a;
+  t.init.b = init_b;
+  t.seed_key = seed_key;
+  return t;
+}
+
+}  // namespace
+
+void bind_dense(py::module_& m);  // bindings_dense.cc
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  py::register_exception<KrakenError>(m, "KrakenError");
+
+  py::enum_<OptimType>(m, "OptimType")
+      .value("kAdagrad", OptimType::kAdagrad)
+      .value("kAdam", OptimType::kAdam)
+      .value("kRMSprop", OptimType::kRMSprop)
+      .value("kSGD", OptimType::kSGD);
+  py::enum_<InitializerType>(m, "InitializerType")
+      .value("kConstant", InitializerType::kConstant)
+      .value("kUniform", InitializerType::kUniform)
+      .value("kNormal", InitializerType::kNormal)
+      .value("kXavierUniform", InitializerType::kXavierUniform)
+      .value("kXavierNormal", InitializerType::kXavierNormal);
+  py::enum_<EmitterType>(m, "EmitterType").value("kDefault", EmitterType::kDefault).value("kDCT", EmitterType::kDCT);
+  py::enum_<TableType>(m, "TableType").value("kDense", TableType::kDense).value("kSparse", TableType::kSparse);
+
+  m.def("mix64", [](uint64_t v) { return Mix64(v); });
+  m.def("mix64_pair", [](uint64_t a, uint64_t b) { return Mix64(a, b); });
+  m.def("owner_of", [](uint64_t salt, uint64_t id, uint32_t world) { return OwnerOf(salt, id, world); });
+  m.def("table_salt", [](uint64_t table_id) { return TableSalt(table_id); });
+  m.def("seed_key", [](uint64_t seed, uint64_t table_id) { return SeedKey(seed, table_id); });
+  m.def("error_message", [](int32_t c) { return std::string(err::Msg(c)); });
+  m.def("init_row", [](int init_type, float a, float b, uint64_t seed_key, uint64_t id, int dim) {
+    InitPOD ip;
+    ip.type = static_cast<uint8_t>(init_type);
+    ip.a = a;
+    ip.b = b;
+    torch::Tensor t = torch::empty({dim}, torch::kFloat32);
+    InitRow(ip, seed_key, id, dim, t.data_ptr<float>());
+    return t;
+  });
+
+  // ---------------- router
+  py::class_<Router>(m, "Router")
+      .def(py::init<>())
+      .def("add", &Router::Add)
+      .def("remove", &Router::Remove)
+      .def("empty", &Router::Empty)
+      .def("contains", &Router::Contains)
+      .def("version", &Router::version)
+      .def("hit", &Router::Hit)
+      .def("node_ids",
+           [](const Router& r) {
+             std::vector<uint64_t> v;
+             for (auto& n : r.nodes()) v.push_back(n.id);
+             return v;
+           })
+      .def("node_name",
+           [](const Router& r, uint64_t id) {
+             for (auto& n : r.nodes())
+               if (n.id == id) return n.name;
+             throw KrakenError(err::kBadArgument, "no such node");
+           })
+      .def("vnodes",
+           [](const Router& r) {
+             std::vector<std::tuple<uint64_t, uint64_t, std::string>> v;
+             for (auto& x : r.ring()) v.emplace_back(x.hash_v, x.node_id, x.name);
+             return v;
+           })
+      .def("node_hash_ranges",
+           [](const Router& r, uint64_t id) {
+             std::vector<std::pair<uint64_t, uint64_t>> v;
+             for (auto& x : r.NodeHashRanges(id)) v.emplace_back(x.start, x.end);
+             return v;
+           })
+      .def("intersect_nodes",
+           [](const Router& r, uint64_t start, uint64_t end) {
+             auto s = r.IntersectNodes({start, end});
+             return std::vector<uint64_t>(s.begin(), s.end());
+           })
+      .def("__eq__", [](const Router& a, const Router& b) { return a == b; })
+      .def("__str__", &Router::Str)
+      .def("to_bytes",
+           [](const Router& r) {
+             MemSink s;
+             Writer w(&s);
+             r.Save(&w);
+             return py::bytes(s.str());
+           })
+      .def_static("from_bytes",
+                  [](const std::string& b) {
+                    MemSource s(b.data(), b.size());
+                    Reader r(&s);
+                    return Router::Load(&r);
+                  })
+      .def_static("for_ranks", &Router::ForRanks);
+
+  // ---------------- metadata
+  py::class_<TableMeta>(m, "TableMeta")
+      .def(py::init<>())
+      .def_readwrite("id", &TableMeta::id)
+      .def_readwrite("name", &TableMeta::name)
+      .def_readwrite("table_type", &TableMeta::table_type)
+      .def_readwrite("shape", &TableMeta::shape)
+      .def_readwrite("dimension", &TableMeta::dimension)
+      .def_readwrite("init_type", &TableMeta::init_type)
+      .def_readwrite("init_conf", &TableMeta::init_conf);
+  py::class_<ModelMeta>(m, "ModelMeta")
+      .def(py::init<>())
+      .def_readwrite("name", &ModelMeta::name)
+      .def_readwrite("optim_type", &ModelMeta::optim_type)
+      .def_readwrite("optim_conf", &ModelMeta::optim_conf)
+      .def_readwrite("tables", &ModelMeta::tables)
+      .def("to_bytes",
+           [](const ModelMeta& mm) {
+             MemSink s;
+             Writer w(&s);
+             w.Model(mm);
+             return py::bytes(s.str());
+           })
+      .def_static("from_bytes", [](const std::string& b) {
+        MemSource s(b.data(), b.size());
+        Reader r(&s);
+        return r.Model();
+      });
+
+  // ---------------- serializer (tests, socket transport)
+  m.def("serialize_tensor", [](const torch::Tensor& t) {
+    MemSink s;
+    Writer w(&s);
+    w.Tensor(to_host(t));
+    return py::bytes(s.str());
+  });
+  m.def("serialize_coo", [](const torch::Tensor& indices, const torch::Tensor& values, std::vector<int64_t> shape) {
+    HostTensor t;
+    t.layout = Layout::kCoo;
+    t.indices = std::make_shared<HostTensor>(to_host(indices));
+    t.values = std::make_shared<HostTensor>(to_host(values));
+    t.dims = shape;
+    MemSink s;
+    Writer w(&s);
+    w.Tensor(t);
+    return py::bytes(s.str());
+  });
+  m.def("deserialize_tensor", [](const std::string& b) {
+    MemSource s(b.data(), b.size());
+    Reader r(&s);
+    return from_host(r.Tensor());
+  });
+  m.def("serialize_value", [](const py::dict& d) {
+    MemSink s;
+    Writer w(&s);
+    w.Val(value_from_py(d));
+    return py::bytes(s.str());
+  });
+  m.def("deserialize_value", [](const std::string& b) {
+    MemSource s(b.data(), b.size());
+    Reader r(&s);
+    return value_to_py(r.Val());
+  });
+  m.def("serialize_string", [](const std::string& v) {
+    MemSink s;
+    Writer w(&s);
+    w.Str(v);
+    return py::bytes(s.str());
+  });
+  m.def("serialize_conf", [](const Conf& c) {
+    MemSink s;
+    Writer w(&s);
+    w.ConfMap(c);
+    return py::bytes(s.str());
+  });
+
+  // ---------------- checkpoint
+  m.def("ckpt_timestamp_dir_name", &ckpt::TimestampDirName);
+  m.def("ckpt_parse_timestamp", [](const std::string& n) {
+    int64_t k = -1;
+    bool ok = ckpt::ParseTimestampDir(n, &k);
+    return std::make_pair(ok, k);
+  });
+  m.def("ckpt_prepare_save_dir", &ckpt::PrepareSaveDir);
+  m.def("ckpt_latest_shard_dirs", &ckpt::LatestShardDirs);
+  m.def("ckpt_save_router", &ckpt::SaveRouter);
+  m.def("ckpt_load_router", &ckpt::LoadRouter);
+  m.def("ckpt_save_model", &ckpt::SaveModel);
+  m.def("ckpt_load_model", &ckpt::LoadModel);
+  m.def("ckpt_save_dense", [](const std::string& dir, uint64_t id, const std::string& name, const py::dict& v) {
+    ckpt::SaveDense(dir, id, name, value_from_py(v));
+  });
+  m.def("ckpt_load_dense", [](const std::string& dir, const std::string& name) -> py::object {
+    uint64_t id;
+    Value v;
+    if (!ckpt::LoadDense(dir, name, &id, &v)) return py::none();
+    py::dict d = value_to_py(v);
+    d["id"] = id;
+    return d;
+  });
+  m.def("ckpt_save_sparse",
+        [](const std::string& dir, uint64_t id, const std::string& name, int64_t dim, InitializerType init_type,
+           const Conf& init_conf, const torch::Tensor& ids, const torch::Tensor& vals, const py::dict& states,
+           const py::dict& states_i) {
+          ckpt::SparseHeader h;
+          h.id = id;
+          h.name = name;
+          h.dim = dim;
+          h.init_type = init_type;
+          h.init_conf = init_conf;
+          ckpt::SparseColumns c = columns_from_py(dim, ids, vals, states, states_i);
+          py::gil_scoped_release nogil;
+          ckpt::SaveSparse(dir, h, c);
+        });
+  m.def(
+      "ckpt_load_sparse",
+      [](const std::string& dir, const std::string& name, int filter_mode, uint64_t salt, uint32_t world, uint32_t rank,
+         const Router* ring, uint64_t table_id, uint64_t node) -> py::object {
+        ckpt::SparseHeader h;
+        ckpt::SparseColumns c;
+        bool ok;
+        {
+          py::gil_scoped_release nogil;
+          ok = ckpt::LoadSparse(dir, name, make_filter(filter_mode, salt, world, rank, ring, table_id, node), &h, &c);
+        }
+        if (!ok) return py::none();
+        py::dict d = columns_to_py(c);
+        d["id"] = h.id;
+        d["name"] = h.name;
+        d["init_type"] = h.init_type;
+        d["init_conf"] = h.init_conf;
+        return d;
+      },
+      py::arg("dir"), py::arg("name"), py::arg("filter_mode") = 0, py::arg("salt") = 0, py::arg("world") = 1,
+      py::arg("rank") = 0, py::arg("ring") = nullptr, py::arg("table_id") = 0, py::arg("node") = 0);
+
+  // ---------------- CPU shard
+  py::class_<CpuShard>(m, "CpuShard")
+      .def(py::init<uint64_t>(), py::arg("seed") = 0)
+      .def("init_model", &CpuShard::InitModel)
+      .def("model_initialized", &CpuShard::model_initialized)
+      .def("meta", &CpuShard::meta)
+      .def("has_table", &CpuShard::HasTable)
+      .def("create_dense_table",
+           [](CpuShard& s, uint64_t id, const std::string& name, const torch::Tensor& val) {
+             torch::Tensor v = val.detach().cpu().contiguous().to(torch::kFloat32);
+             s.CreateDenseTable(id, name, std::vector<int64_t>(v.sizes().begin(), v.sizes().end()), v.data_ptr<float>());
+           })
+      .def("create_sparse_table", &CpuShard::CreateSparseTable)
+      .def("pull_dense",
+           [](CpuShard& s, uint64_t id) {
+             torch::Tensor out = torch::empty({s.DenseNumel(id)}, torch::kFloat32);
+             s.PullDense(id, out.data_ptr<float>());
+             return out;
+           })
+      .def("push_dense",
+           [](CpuShard& s, uint64_t id, const torch::Tensor& grad, float lr) {
+             torch::Tensor g = grad.detach().cpu().contiguous().to(torch::kFloat32);
+             s.PushDense(id, g.data_ptr<float>(), g.numel(), lr);
+           })
+      .def("push_dense_coo",
+           [](CpuShard& s, uint64_t id, const torch::Tensor& idx, const torch::Tensor& vals, float lr) {
+             torch::Tensor i = idx.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
+             torch::Tensor v = vals.detach().cpu().contiguous().to(torch::kFloat32).reshape({-1});
+             TORCH_CHECK(i.numel() == v.numel(), "COO indices and values differ in length");
+             s.PushDenseCoo(id, i.data_ptr<int64_t>(), v.data_ptr<float>(), i.numel(), lr);
+           })
+      .def("sparse_dim", &CpuShard::SparseDim)
+      .def("sparse_size", &CpuShard::SparseSize)
+      .def("pull_sparse",
+           [](CpuShard& s, uint64_t id, const torch::Tensor& ids) {
+             torch::Tensor i = ids.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
+             torch::Tensor out = torch::empty({i.numel(), s.SparseDim(id)}, torch::kFloat32);
+             s.PullSparse(id, reinterpret_cast<const uint64_t*>(i.data_ptr<int64_t>()), i.numel(), out.data_ptr<float>());
+             return out;
+           })
+      .def("push_sparse",
+           [](CpuShard& s, uint64_t id, const torch::Tensor& ids, const torch::Tensor& grads, float lr) {
+             torch::Tensor i = ids.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
+             torch::Tensor g = grads.detach().cpu().contiguous().to(torch::kFloat32);
+             TORCH_CHECK(g.numel() == i.numel() * s.SparseDim(id), "grads must be [n, dim]");
+             return s.PushSparse(id, reinterpret_cast<const uint64_t*>(i.data_ptr<int64_t>()), i.numel(),
+                                 g.data_ptr<float>(), lr);
+           })
+      .def("export_dense", [](CpuShard& s, uint64_t id) { return value_to_py(s.ExportDense(id)); })
+      .def("import_dense", [](CpuShard& s, uint64_t id, const std::string& name,
+                              const py::dict& v) { s.ImportDense(id, name, value_from_py(v)); })
+      .def("export_sparse", [](CpuShard& s, uint64_t id) { return columns_to_py(s.ExportSparse(id)); })
+      .def("import_sparse",
+           [](CpuShard& s, uint64_t id, const torch::Tensor& ids, const torch::Tensor& vals, const py::dict& states,
+              const py::dict& states_i) {
+             s.ImportSparse(id, columns_from_py(s.SparseDim(id), ids, vals, states, states_i));
+           })
+      .def("filter_sparse", [](CpuShard& s, uint64_t id, int mode, uint64_t salt, uint32_t world, uint32_t rank,
+                               const Router* ring, uint64_t node) {
+        return s.FilterSparse(id, make_filter(mode, salt, world, rank, ring, id, node));
+      });
+
+  m.def("parse_optim", [](OptimType t, const Conf& c) {
+    OptimPOD o = ParseOptim(t, c);
+    py::dict d;
+    d["type"] = o.type;
+    d["has_weight_decay"] = o.has_weight_decay;
+    d["weight_decay"] = o.weight_decay;
+    d["has_momentum"] = o.has_momentum;
+    d["momentum"] = o.momentum;
+    d["has_dampening"] = o.has_dampening;
+    d["dampening"] = o.dampening;
+    d["nesterov"] = o.nesterov;
+    d["amsgrad"] = o.amsgrad;
+    d["centered"] = o.centered;
+    d["beta1"] = o.beta1;
+    d["beta2"] = o.beta2;
+    d["alpha"] = o.alpha;
+    d["eps"] = o.eps;
+    d["initial_accumulator_value"] = o.initial_accumulator_value;
+    d["slabs"] = std::vector<bool>{o.SlabUsed(0), o.SlabUsed(1), o.SlabUsed(2)};
+    d["needs_steps"] = o.NeedsSteps();
+    d["slab_state_types"] = std::vector<uint32_t>{SlabStateType(o, 0), SlabStateType(o, 1), SlabStateType(o, 2)};
+    return d;
+  });
+  m.def("parse_init", [](InitializerType t, const Conf& c) {
+    InitPOD p = ParseInit(t, c);
+    return std::make_tuple(static_cast<int>(p.type), p.a, p.b);
+  });
+
+  // ---------------- CPU client-side ops
+  m.def("cpu_dedup", [](const torch::Tensor& ids) {
+    torch::Tensor i = ids.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
+    std::vector<uint64_t> uniq;
+    std::vector<int64_t> inv;
+    cpu::Dedup(reinterpret_cast<const uint64_t*>(i.data_ptr<int64_t>()), i.numel(), &uniq, &inv);
+    torch::Tensor u = torch::empty({static_cast<int64_t>(uniq.size())}, torch::kInt64);
+    if (!uniq.empty()) std::memcpy(u.data_ptr(), uniq.data(), uniq.size() * 8);
+    torch::Tensor v = torch::empty({i.numel()}, torch::kInt64);
+    if (!inv.empty()) std::memcpy(v.data_ptr(), inv.data(), inv.size() * 8);
+    return std::make_pair(u, v);
+  });
+  m.def("cpu_segment_sum", [](const torch::Tensor& grads, const torch::Tensor& inverse, int64_t num_uniq) {
+    torch::Tensor g = grads.detach().cpu().contiguous().to(torch::kFloat32);
+    torch::Tensor inv = inverse.detach().cpu().contiguous().to(torch::kInt64);
+    const int64_t n = inv.numel();
+    const int64_t dim = n ? g.numel() / n : 0;
+    torch::Tensor out = torch::zeros({num_uniq, dim}, torch::kFloat32);
+    cpu::SegmentSum(g.data_ptr<float>(), inv.data_ptr<int64_t>(), n, dim, num_uniq, out.data_ptr<float>());
+    return out;
+  });
+  m.def("kth_largest_abs", [](const torch::Tensor& x, int64_t k) {
+    torch::Tensor v = x.detach().cpu().contiguous().to(torch::kFloat32).reshape({-1});
+    return cpu::KthLargestAbs(v.data_ptr<float>(), v.numel(), k);
+  });
+  py::class_<cpu::DctState>(m, "DctState")
+      .def(py::init<>())
+      .def_readwrite("tau", &cpu::DctState::tau)
+      .def_readwrite("step", &cpu::DctState::step)
+      .def("residual", [](const cpu::DctState& s) {
+        torch::Tensor t = torch::empty({static_cast<int64_t>(s.e.size())}, torch::kFloat32);
+        if (!s.e.empty()) std::memcpy(t.data_ptr(), s.e.data(), s.e.size() * 4);
+        return t;
+      });
+  m.def("cpu_dct_compress",
+        [](const torch::Tensor& grad, int64_t life_span, float eta, cpu::DctState& st) -> py::object {
+          torch::Tensor g = grad.detach().cpu().contiguous().to(torch::kFloat32).reshape({-1});
+          std::vector<int64_t> idx;
+          std::vector<float> vals;
+          if (!cpu::DctCompress(g.data_ptr<float>(), g.numel(), life_span, eta, &st, &idx, &vals)) return py::none();
+          torch::Tensor i = torch::empty({static_cast<int64_t>(idx.size())}, torch::kInt64);
+          torch::Tensor v = torch::empty({static_cast<int64_t>(vals.size())}, torch::kFloat32);
+          if (!idx.empty()) {
+            std::memcpy(i.data_ptr(), idx.data(), idx.size() * 8);
+            std::memcpy(v.data_ptr(), vals.data(), vals.size() * 4);
+          }
+          return py::make_tuple(i, v);
+        });
+
+  // ---------------- jagged ops (CPU and CUDA), API of the reference's kraken_native
+  auto jagged_fwd = [](const torch::Tensor& values, const torch::Tensor& offsets, float patch_value,
+                       const c10::optional<torch::Tensor>& weights, bool mean) {
+    TORCH_CHECK(values.dim() >= 1, "values must have at least one dimension");
+    torch::Tensor v = values.contiguous().to(torch::kFloat32);
+    torch::Tensor o = offsets.contiguous().to(torch::kInt64);
+    const int64_t k = o.numel() - 1;
+    TORCH_CHECK(k >= 0, "offsets must have at least one element");
+    const int64_t R = v.size(0);
+    const int64_t dim = R ? v.numel() / R : (v.dim() > 1 ? v.numel() : 1);
+    std::vector<int64_t> shape(v.sizes().begin(), v.sizes().end());
+    shape[0] = k;
+    torch::Tensor out = torch::empty(shape, v.options());
+    c10::optional<torch::Tensor> w;
+    if (weights.has_value()) w = weights->contiguous().to(torch::kFloat32);
+    int64_t d = 1;
+    for (size_t i = 1; i < shape.size(); ++i) d *= shape[i];
+    (void)dim;
+    if (v.is_cuda()) {
+      c10::cuda::CUDAGuard guard(v.device());
+      TORCH_CHECK(o.is_cuda(), "offsets must live on the same device as values");
+      cu::jagged_forward(ptr<float>(v), optr<float>(w), ptr<int64_t>(o), k, d, mean, patch_value, ptr<float>(out),
+                         cur_stream());
+      check_launch("jagged_forward");
+    } else {
+      cpu::JaggedForward(ptr<float>(v), optr<float>(w), ptr<int64_t>(o), k, d, mean, patch_value, ptr<float>(out));
+    }
+    return out;
+  };
+  auto jagged_bwd = [](const torch::Tensor& offsets, const torch::Tensor& grads,
+                       const c10::optional<torch::Tensor>& weights, bool mean) {
+    torch::Tensor g = grads.contiguous().to(torch::kFloat32);
+    torch::Tensor o = offsets.contiguous().to(torch::kInt64);
+    const int64_t k = o.numel() - 1;
+    TORCH_CHECK(k >= 0 && g.size(0) == k, "grads must have one row per bag");
+    const int64_t R = k > 0 ? o.cpu()[k].item<int64_t>() : 0;
+    std::vector<int64_t> shape(g.sizes().begin(), g.sizes().end());
+    shape[0] = R;
+    torch::Tensor out = torch::zeros(shape, g.options());
+    int64_t d = 1;
+    for (size_t i = 1; i < shape.size(); ++i) d *= shape[i];
+    c10::optional<torch::Tensor> w;
+    if (weights.has_value()) w = weights->contiguous().to(torch::kFloat32);
+    if (g.is_cuda()) {
+      c10::cuda::CUDAGuard guard(g.device());
+      TORCH_CHECK(o.is_cuda(), "offsets must live on the same device as grads");
+      cu::jagged_backward(ptr<float>(g), optr<float>(w), ptr<int64_t>(o), k, d, mean, ptr<float>(out), cur_stream());
+      check_launch("jagged_backward");
+    } else {
+      cpu::JaggedBackward(ptr<float>(g), optr<float>(w), ptr<int64_t>(o), k, d, mean, ptr<float>(out));
+    }
+    return out;
+  };
+  m.def(
+      "jagged_sum_forward",
+      [jagged_fwd](const torch::Tensor& v, const torch::Tensor& o, float p, const c10::optional<torch::Tensor>& w) {
+        return jagged_fwd(v, o, p, w, false);
+      },
+      py::arg("values"), py::arg("offsets"), py::arg("patch_value"), py::arg("weights") = py::none());
+  m.def(
+      "jagged_mean_forward",
+      [jagged_fwd](const torch::Tensor& v, const torch::Tensor& o, float p, const c10::optional<torch::Tensor>& w) {
+        return jagged_fwd(v, o, p, w, true);
+      },
+      py::arg("values"), py::arg("offsets"), py::arg("patch_value"), py::arg("weights") = py::none());
+  m.def(
+      "jagged_sum_backward",
+      [jagged_bwd](const torch::Tensor& o, const torch::Tensor& g, const c10::optional<torch::Tensor>& w) {
+        return jagged_bwd(o, g, w, false);
+      },
+      py::arg("offsets"), py::arg("grads"), py::arg("weights") = py::none());
+  m.def(
+      "jagged_mean_backward",
+      [jagged_bwd](const torch::Tensor& o, const torch::Tensor& g, const c10::optional<torch::Tensor>& w) {
+        return jagged_bwd(o, g, w, true);
+      },
+      py::arg("offsets"), py::arg("grads"), py::arg("weights") = py::none());
+
+  // ---------------- symmetric heap + device structs
+  py::class_<SymHeap>(m, "SymHeap")
+      .def(py::init<size_t, int, int>(), py::arg("bytes"), py::arg("rank"), py::arg("world"))
+      .def("handle", &SymHeap::Handle)
+      .def("open", &SymHeap::Open)
+      .def("close", &SymHeap::Close)
+      .def("window", &SymHeap::Window)
+      .def_readonly("bytes", &SymHeap::bytes)
+      .def_readonly("rank", &SymHeap::rank)
+      .def_readonly("world", &SymHeap::world)
+      .def("local_ptr", [](const SymHeap& h) { return reinterpret_cast<uintptr_t>(h.local); })
+      .def("peer_ptr", [](const SymHeap& h, int p) { return reinterpret_cast<uintptr_t>(h.bases.at(p)); });
+
+  py::class_<cu::ChanLayout>(m, "ChanLayout")
+      .def(py::init<>())
+      .def_readwrite("inbox_ids", &cu::ChanLayout::inbox_ids)
+      .def_readwrite("inbox_meta", &cu::ChanLayout::inbox_meta)
+      .def_readwrite("rows_recv", &cu::ChanLayout::rows_recv)
+      .def_readwrite("inbox_grad", &cu::ChanLayout::inbox_grad)
+      .def_readwrite("flag_req", &cu::ChanLayout::flag_req)
+      .def_readwrite("flag_rsp", &cu::ChanLayout::flag_rsp)
+      .def_readwrite("flag_push", &cu::ChanLayout::flag_push)
+      .def_readwrite("capS", &cu::ChanLayout::capS)
+      .def_readwrite("capU", &cu::ChanLayout::capU);
+
+  py::class_<cu::TableHost>(m, "TableHost");
+  m.def("make_table", &make_table, py::arg("keys"), py::arg("val"), py::arg("s0"), py::arg("s1"), py::arg("s2"),
+        py::arg("steps"), py::arg("lead"), py::arg("size"), py::arg("status"), py::arg("bits"), py::arg("dim"),
+        py::arg("init_type"), py::arg("init_a"), py::arg("init_b"), py::arg("seed_key"));
+
+  py::class_<OptimPOD>(m, "OptimPOD");
+  m.def("make_optim", [](OptimType t, const Conf& c) { return ParseOptim(t, c); });
+
+  // ---------------- sparse kernels
+  m.def("dedup_bucketize", [](const torch::Tensor& ids, int world, uint64_t salt, const torch::Tensor& hkeys,
+                              const torch::Tensor& hpos, const torch::Tensor& hwin, const torch::Tensor& slot_of,
+                              uint32_t hbits, const torch::Tensor& cnt, const torch::Tensor& off,
+                              const torch::Tensor& uniq, const torch::Tensor& inv, const torch::Tensor& status) {
+    need_cuda(ids, "ids", torch::kInt64);
+    need_cuda(hkeys, "hkeys", torch::kInt64);
+    const int n = static_cast<int>(ids.numel());
+    TORCH_CHECK(hkeys.numel() == (1ll << hbits) && (1ll << hbits) >= 2ll * n, "dedup scratch too small");
+    TORCH_CHECK(slot_of.numel() >= n && uniq.numel() >= n && inv.numel() >= n, "dedup outputs too small");
+    TORCH_CHECK(cnt.numel() >= world && off.numel() >= world + 1, "cnt/off too small");
+    c10::cuda::CUDAGuard guard(ids.device());
+    cu::DedupScratch sc{hkeys.data_ptr(), ptr<int>(hpos), ptr<int>(hwin), ptr<int>(slot_of), hbits};
+    cu::dedup_bucketize(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),
+                        ptr<int>(inv), ptr<int>(status), cur_stream());
+    check_launch("dedup_bucketize");
+  });
+  m.def("pull_dispatch", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                            const torch::Tensor& uniq, const torch::Tensor& off, int max_n) {
+    cu::pull_dispatch(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), ptr<int64_t>(uniq), ptr<int>(off),
+                      max_n, cur_stream());
+    check_launch("pull_dispatch");
+  });
+  m.def("pull_probe", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                         const cu::TableHost& table, const torch::Tensor& slot_cache, bool insert, uint32_t spin) {
+    cu::pull_probe(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), table, ptr<int>(slot_cache), insert,
+                   spin, cur_stream());
+    check_launch("pull_probe");
+  });
+  m.def("pull_gather", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                          const cu::TableHost& table, const torch::Tensor& slot_cache) {
+    cu::pull_gather(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), table, ptr<int>(slot_cache),
+                    cur_stream());
+    check_launch("pull_gather");
+  });
+  m.def("pull_combine",
+        [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl, const torch::Tensor& inv, int n,
+           int dim, const c10::optional<torch::Tensor>& bag_offsets, const c10::optional<torch::Tensor>& weights,
+           bool mean, const c10::optional<torch::Tensor>& bag_mean, float patch_value, const torch::Tensor& out,
+           uint32_t spin) {
+          const int k = bag_offsets.has_value() ? static_cast<int>(bag_offsets->numel()) - 1 : 0;
+          need_cuda(out, "out", torch::kFloat32);
+          TORCH_CHECK(out.numel() == static_cast<int64_t>(bag_offsets.has_value() ? k : n) * dim, "out has the wrong size");
+          cu::pull_combine(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), ptr<int>(inv), n, dim,
+                           optr<int64_t>(bag_offsets), k, optr<float>(weights), mean, optr<uint8_t>(bag_mean),
+                           patch_value, ptr<float>(out), spin, cur_stream());
+          check_launch("pull_combine");
+        });
+  m.def("push_scatter",
+        [](const torch::Tensor& grads, const torch::Tensor& inv, int n, int dim,
+           const c10::optional<torch::Tensor>& bag_offsets, const c10::optional<torch::Tensor>& weights, bool mean,
+           const c10::optional<torch::Tensor>& bag_mean, const torch::Tensor& ugrad) {
+          need_cuda(grads, "grads", torch::kFloat32);
+          const int k = bag_offsets.has_value() ? static_cast<int>(bag_offsets->numel()) - 1 : 0;
+          TORCH_CHECK(grads.numel() == static_cast<int64_t>(bag_offsets.has_value() ? k : n) * dim,
+                      "grads has the wrong size");
+          cu::push_scatter(ptr<float>(grads), ptr<int>(inv), n, dim, optr<int64_t>(bag_offsets), k, optr<float>(weights),
+                           mean, optr<uint8_t>(bag_mean), ptr<float>(ugrad), cur_stream());
+          check_launch("push_scatter");
+        });
+  m.def("push_dispatch", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                            const torch::Tensor& ugrad, const torch::Tensor& off, int max_n, int dim) {
+    cu::push_dispatch(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), ptr<float>(ugrad), ptr<int>(off),
+                      max_n, dim, cur_stream());
+    check_launch("push_dispatch");
+  });
+  m.def("push_apply", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                         const cu::TableHost& table, const torch::Tensor& slot_cache, const OptimPOD& optim,
+                         const torch::Tensor& lr, uint32_t spin) {
+    need_cuda(lr, "lr", torch::kFloat32);
+    cu::push_apply(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), table, ptr<int>(slot_cache), optim,
+                   ptr<float>(lr), spin, cur_stream());
+    check_launch("push_apply");
+  });
+
+  // ---------------- table maintenance
+  m.def("table_clear", [](const cu::TableHost& t) {
+    cu::table_clear(t, cur_stream());
+    check_launch("table_clear");
+  });
+  m.def("table_import", [](const cu::TableHost& t, const torch::Tensor& ids, const torch::Tensor& vals,
+                           const c10::optional<torch::Tensor>& s0, const c10::optional<torch::Tensor>& s1,
+                           const c10::optional<torch::Tensor>& s2, const c10::optional<torch::Tensor>& steps) {
+    need_cuda(ids, "ids", torch::kInt64);
+    need_cuda(vals, "vals", torch::kFloat32);
+    TORCH_CHECK(vals.numel() == ids.numel() * t.dim, "vals must be [n, dim]");
+    cu::table_import(t, ptr<int64_t>(ids), ptr<float>(vals), optr<float>(s0), optr<float>(s1), optr<float>(s2),
+                     optr<int>(steps), static_cast<int>(ids.numel()), cur_stream());
+    check_launch("table_import");
+  });
+  m.def("table_lookup", [](const cu::TableHost& t, const torch::Tensor& ids) {
+    need_cuda(ids, "ids", torch::kInt64);
+    torch::Tensor rows = torch::empty({ids.numel(), t.dim}, ids.options().dtype(torch::kFloat32));
+    torch::Tensor found = torch::empty({ids.numel()}, ids.options().dtype(torch::kUInt8));
+    cu::table_lookup(t, ptr<int64_t>(ids), static_cast<int>(ids.numel()), ptr<float>(rows), ptr<uint8_t>(found),
+                     cur_stream());
+    check_launch("table_lookup");
+    return std::make_pair(rows, found);
+  });
+  m.def("table_export",
+        [](const cu::TableHost& t, int filter_mode, uint64_t salt, int world, int rank, int min_steps,
+           const c10::optional<torch::Tensor>& out_ids, const c10::optional<torch::Tensor>& out_vals,
+           const c10::optional<torch::Tensor>& s0, const c10::optional<torch::Tensor>& s1,
+           const c10::optional<torch::Tensor>& s2, const c10::optional<torch::Tensor>& steps,
+           const torch::Tensor& out_count) {
+          const int cap = out_ids.has_value() ? static_cast<int>(out_ids->numel()) : 0;
+          cu::table_export(t, filter_mode, salt, world, rank, min_steps, optr<int64_t>(out_ids), optr<float>(out_vals),
+                           optr<float>(s0), optr<float>(s1), optr<float>(s2), optr<int>(steps), ptr<int>(out_count), cap,
+                           cur_stream());
+          check_launch("table_export");
+        });
+
+  // ---------------- model kernels
+  m.def("fm_forward", [](const torch::Tensor& emb) {
+    need_cuda(emb, "emb", torch::kFloat32);
+    TORCH_CHECK(emb.dim() == 3, "emb must be [B, F, D]");
+    c10::cuda::CUDAGuard guard(emb.device());
+    torch::Tensor out = torch::empty({emb.size(0)}, emb.options());
+    cu::fm_forward(ptr<float>(emb), emb.size(0), emb.size(1), emb.size(2), ptr<float>(out), cur_stream());
+    check_launch("fm_forward");
+    return out;
+  });
+  m.def("fm_backward", [](const torch::Tensor& emb, const torch::Tensor& gout) {
+    need_cuda(emb, "emb", torch::kFloat32);
+    need_cuda(gout, "gout", torch::kFloat32);
+    c10::cuda::CUDAGuard guard(emb.device());
+    torch::Tensor g = torch::empty_like(emb);
+    cu::fm_backward(ptr<float>(emb), ptr<float>(gout), emb.size(0), emb.size(1), emb.size(2), ptr<float>(g), cur_stream());
+    check_launch("fm_backward");
+    return g;
+  });
+  m.def("bce_with_logits", [](const torch::Tensor& logits, const torch::Tensor& labels, bool want_grad) {
+    need_cuda(logits, "logits", torch::kFloat32);
+    need_cuda(labels, "labels", torch::kFloat32);
+    TORCH_CHECK(logits.numel() == labels.numel(), "logits and labels differ in size");
+    c10::cuda::CUDAGuard guard(logits.device());
+    torch::Tensor loss = torch::zeros({}, logits.options());
+    torch::Tensor grad = want_grad ? torch::empty_like(logits) : torch::Tensor();
+    cu::bce_forward_backward(ptr<float>(logits), ptr<float>(labels), static_cast<int>(logits.numel()), ptr<float>(loss),
+                             want_grad ? ptr<float>(grad) : nullptr, cur_stream());
+    check_launch("bce_with_logits");
+    return std::make_pair(loss, grad);
+  });
+
+  bind_dense(m);
+}

@@ -1,0 +1,91 @@
+// Bindings of the dense-parameter path (fused dense step, DCT compression).
+#include <c10/cuda/CUDAStream.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "cuda/dense_kernels.h"
+
+namespace py = pybind11;
+using namespace kb;
+
+namespace {
+
+cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+template <typename T>
+T* optr(const c10::optional<torch::Tensor>& t) {
+  return (t.has_value() && t->defined() && t->numel() > 0) ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+cu::SymHost sym_from(const std::vector<uintptr_t>& bases, int rank) {
+  cu::SymHost s{};
+  TORCH_CHECK(bases.size() <= static_cast<size_t>(cu::kMaxWorldHost), "too many ranks");
+  for (size_t i = 0; i < bases.size(); ++i) s.base[i] = reinterpret_cast<void*>(bases[i]);
+  s.rank = rank;
+  s.world = static_cast<int>(bases.size());
+  return s;
+}
+
+}  // namespace
+
+void bind_dense(py::module_& m) {
+  py::class_<cu::DenseLayout>(m, "DenseLayout")
+      .def(py::init<>())
+      .def_readwrite("grad", &cu::DenseLayout::grad)
+      .def_readwrite("param", &cu::DenseLayout::param)
+      .def_readwrite("flag_grad", &cu::DenseLayout::flag_grad)
+      .def_readwrite("flag_done", &cu::DenseLayout::flag_done)
+      .def_readwrite("coo_cnt", &cu::DenseLayout::coo_cnt)
+      .def_readwrite("coo_idx", &cu::DenseLayout::coo_idx)
+      .def_readwrite("coo_val", &cu::DenseLayout::coo_val);
+  m.attr("DENSE_CHUNK") = cu::kDenseChunk;
+
+  m.def("dense_step",
+        [](const std::vector<uintptr_t>& bases, int rank, const cu::DenseLayout& lay, const torch::Tensor& ctrl,
+           int64_t n_pad, const c10::optional<torch::Tensor>& s0, const c10::optional<torch::Tensor>& s1,
+           const c10::optional<torch::Tensor>& s2, const c10::optional<torch::Tensor>& acc,
+           const torch::Tensor& chunk_table, const torch::Tensor& table_steps, const torch::Tensor& table_active,
+           const OptimPOD& optim, const torch::Tensor& lr, float grad_scale, bool use_coo, uint32_t spin) {
+          TORCH_CHECK(n_pad % (static_cast<int64_t>(bases.size()) * cu::kDenseChunk) == 0,
+                      "n_pad must be a multiple of world * 256");
+          TORCH_CHECK(chunk_table.numel() == n_pad / cu::kDenseChunk, "chunk_table has the wrong size");
+          TORCH_CHECK(!use_coo || optr<float>(acc) != nullptr, "COO mode needs the accumulator");
+          cu::dense_step(sym_from(bases, rank), lay, reinterpret_cast<cu::DenseCtrl*>(ctrl.data_ptr()), n_pad,
+                         optr<float>(s0), optr<float>(s1), optr<float>(s2), optr<float>(acc),
+                         chunk_table.data_ptr<int>(), table_steps.data_ptr<int>(), table_active.data_ptr<uint8_t>(),
+                         static_cast<int>(table_steps.numel()), optim, lr.data_ptr<float>(), grad_scale,
+                         use_coo ? 1 : 0, spin, cur_stream());
+          check_launch("dense_step");
+        });
+  m.def("dct_accumulate", [](const torch::Tensor& grad, const torch::Tensor& residual) {
+    TORCH_CHECK(grad.numel() == residual.numel(), "grad and residual differ in size");
+    cu::dct_accumulate(grad.data_ptr<float>(), residual.data_ptr<float>(), grad.numel(), cur_stream());
+    check_launch("dct_accumulate");
+  });
+  m.def("dct_select_tau", [](const torch::Tensor& x, int64_t k, const torch::Tensor& hist,
+                             const torch::Tensor& prefix_state, const torch::Tensor& tau) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && x.is_contiguous(), "x must be CUDA f32");
+    TORCH_CHECK(k >= 1 && k <= x.numel(), "k out of range");
+    TORCH_CHECK(hist.numel() >= 1024 && prefix_state.numel() >= 2, "radix scratch too small");
+    cu::dct_select_tau(x.data_ptr<float>(), x.numel(), k, reinterpret_cast<uint32_t*>(hist.data_ptr()),
+                       reinterpret_cast<uint32_t*>(prefix_state.data_ptr()), tau.data_ptr<float>(), cur_stream());
+    check_launch("dct_select_tau");
+  });
+  m.def("dct_compact", [](const std::vector<uintptr_t>& bases, int rank, const cu::DenseLayout& lay, int64_t n_pad,
+                          const torch::Tensor& residual, const torch::Tensor& tau, const torch::Tensor& chunk_table) {
+    cu::dct_compact(sym_from(bases, rank), lay, n_pad, residual.data_ptr<float>(), tau.data_ptr<float>(),
+                    chunk_table.data_ptr<int>(), cur_stream());
+    check_launch("dct_compact");
+  });
+  m.def("dct_threshold_dense", [](const torch::Tensor& grad, const torch::Tensor& residual, const torch::Tensor& tau,
+                                  const torch::Tensor& chunk_table) {
+    cu::dct_threshold_dense(grad.data_ptr<float>(), residual.data_ptr<float>(), grad.numel(), tau.data_ptr<float>(),
+                            chunk_table.data_ptr<int>(), cur_stream());
+    check_launch("dct_threshold_dense");
+  });
+}

@@ -1,0 +1,376 @@
+#include "checkpoint.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <ctime>
+#include <filesystem>
+#include <fstream>
+#include <numeric>
+#include <sstream>
+
+#include "hash.h"
+
+namespace fs = std::filesystem;
+
+namespace kb {
+namespace ckpt {
+
+namespace {
+
+const char* kRouterJson = "router.json";
+const char* kRouterBin = "router.binary";
+const char* kModelJson = "model.json";
+const char* kModelBin = "model.binary";
+const char* kDenseSuffix = ".dense";
+const char* kSparseSuffix = ".sparse";
+const char* kShardPrefix = "shard_";
+
+const char* OptimName(OptimType t) {
+  switch (t) {
+    case OptimType::kAdagrad: return "Adagrad";
+    case OptimType::kAdam: return "Adam";
+    case OptimType::kRMSprop: return "RMSprop";
+    case OptimType::kSGD: return "SGD";
+  }
+  return "UnKnow";
+}
+
+const char* InitName(InitializerType t) {
+  switch (t) {
+    case InitializerType::kConstant: return "Constant";
+    case InitializerType::kUniform: return "Uniform";
+    case InitializerType::kNormal: return "Normal";
+    case InitializerType::kXavierUniform: return "XavierUniform";
+    case InitializerType::kXavierNormal: return "XavierNormal";
+  }
+  return "UnKnow";
+}
+
+std::string JsonStr(const std::string& s) {
+  std::string o = "\"";
+  for (char c : s) {
+    switch (c) {
+      case '"': o += "\\\""; break;
+      case '\\': o += "\\\\"; break;
+      case '\n': o += "\\n"; break;
+      case '\t': o += "\\t"; break;
+      default:
+        if (static_cast<unsigned char>(c) < 0x20) {
+          char b[8];
+          std::snprintf(b, sizeof(b), "\\u%04x", c);
+          o += b;
+        } else {
+          o += c;
+        }
+    }
+  }
+  return o + "\"";
+}
+
+std::string JsonConf(const Conf& c, const std::string& ind) {
+  if (c.empty()) return "{}";
+  std::string o = "{\n";
+  size_t i = 0;
+  for (auto& kv : c) {
+    o += ind + "    " + JsonStr(kv.first) + ": " + JsonStr(kv.second);
+    o += (++i < c.size()) ? ",\n" : "\n";
+  }
+  return o + ind + "}";
+}
+
+void WriteText(const std::string& path, const std::string& text) {
+  std::ofstream f(path);
+  KB_CHECK(f.is_open(), err::kCheckpointIO, "cannot open " + path);
+  f << text << std::endl;
+}
+
+}  // namespace
+
+bool RowFilter::Keep(uint64_t id) const {
+  switch (mode) {
+    case kAll: return true;
+    case kModulo: return OwnerOf(table_salt, id, world) == rank;
+    case kRing: return ring->Hit(Mix64(table_id, id)) == node;
+  }
+  return true;
+}
+
+std::string TimestampDirName() {
+  std::time_t tt = std::time(nullptr);
+  std::tm local{};
+  localtime_r(&tt, &local);
+  char buf[80];
+  std::strftime(buf, sizeof(buf), "%Y-%m-%d-%H-%M-%S", &local);
+  return buf;
+}
+
+bool ParseTimestampDir(const std::string& name, int64_t* key) {
+  int v[6];
+  char tail;
+  if (std::sscanf(name.c_str(), "%d-%d-%d-%d-%d-%d%c", &v[0], &v[1], &v[2], &v[3], &v[4], &v[5], &tail) != 6)
+    return false;
+  if (v[1] < 1 || v[1] > 12 || v[2] < 1 || v[2] > 31 || v[3] > 23 || v[4] > 59 || v[5] > 60) return false;
+  for (int x : v)
+    if (x < 0) return false;
+  *key = ((((static_cast<int64_t>(v[0]) * 13 + v[1]) * 32 + v[2]) * 24 + v[3]) * 60 + v[4]) * 61 + v[5];
+  return true;
+}
+
+std::string PrepareSaveDir(const std::string& saved_dir, uint64_t shard, size_t max_save_count) {
+  fs::path shard_dir = fs::path(saved_dir) / (kShardPrefix + std::to_string(shard));
+  std::error_code ec;
+  fs::create_directories(shard_dir, ec);
+  KB_CHECK(!ec, err::kCheckpointIO, "cannot create " + shard_dir.string());
+
+  std::vector<std::pair<int64_t, fs::path>> stamped;
+  for (auto& e : fs::directory_iterator(shard_dir)) {
+    int64_t key;
+    if (e.is_directory() && ParseTimestampDir(e.path().filename().string(), &key)) stamped.push_back({key, e.path()});
+  }
+  std::sort(stamped.begin(), stamped.end());
+  size_t first = 0;
+  if (max_save_count > 0) {
+    while (stamped.size() - first >= max_save_count) fs::remove_all(stamped[first++].second);
+  }
+
+  // Two saves inside one second would collide: wait for the next tick.
+  std::string name = TimestampDirName();
+  fs::path dir = shard_dir / name;
+  for (int tries = 0; fs::exists(dir) && tries < 50; ++tries) {
+    struct timespec ts{0, 100 * 1000 * 1000};
+    nanosleep(&ts, nullptr);
+    name = TimestampDirName();
+    dir = shard_dir / name;
+  }
+  fs::create_directories(dir, ec);
+  KB_CHECK(!ec, err::kCheckpointIO, "cannot create " + dir.string());
+  return dir.string();
+}
+
+std::map<uint64_t, std::string> LatestShardDirs(const std::string& load_dir) {
+  std::map<uint64_t, std::string> out;
+  if (!fs::is_directory(load_dir)) return out;
+  for (auto& e : fs::directory_iterator(load_dir)) {
+    std::string fname = e.path().filename().string();
+    if (!e.is_directory() || fname.rfind(kShardPrefix, 0) != 0) continue;
+    uint64_t shard;
+    try {
+      size_t used = 0;
+      shard = std::stoull(fname.substr(std::string(kShardPrefix).size()), &used);
+      if (used != fname.size() - std::string(kShardPrefix).size()) continue;
+    } catch (...) {
+      continue;
+    }
+    int64_t best_key = -1;
+    std::string best;
+    for (auto& t : fs::directory_iterator(e.path())) {
+      int64_t key;
+      if (t.is_directory() && ParseTimestampDir(t.path().filename().string(), &key) && key > best_key) {
+        best_key = key;
+        best = t.path().string();
+      }
+    }
+    if (best_key >= 0) out[shard] = best;
+  }
+  return out;
+}
+
+void SaveRouter(const std::string& dir, const Router& r) {
+  std::ostringstream j;
+  j << "[";
+  for (size_t i = 0; i < r.nodes().size(); ++i) {
+    const auto& n = r.nodes()[i];
+    j << (i ? ",\n" : "\n") << "    {\n        \"id\": " << n.id << ",\n        \"name\": " << JsonStr(n.name)
+      << ",\n        \"virtual_nodes\": [";
+    for (size_t k = 0; k < n.vnodes.size(); ++k) {
+      std::string vname;
+      for (const auto& v : r.ring())
+        if (v.hash_v == n.vnodes[k]) vname = v.name;
+      j << (k ? ",\n" : "\n") << "            {\n                \"hash_v\": " << n.vnodes[k]
+        << ",\n                \"name\": " << JsonStr(vname) << "\n            }";
+    }
+    j << "\n        ]\n    }";
+  }
+  j << "\n]";
+  WriteText((fs::path(dir) / kRouterJson).string(), j.str());
+
+  FileSink sink((fs::path(dir) / kRouterBin).string());
+  KB_CHECK(sink.IsOpen(), err::kCheckpointIO, "cannot open router.binary in " + dir);
+  Writer w(&sink);
+  r.Save(&w);
+}
+
+Router LoadRouter(const std::string& dir) {
+  FileSource src((fs::path(dir) / kRouterBin).string());
+  KB_CHECK(src.IsOpen(), err::kCheckpointIO, "cannot open router.binary in " + dir);
+  Reader r(&src);
+  return Router::Load(&r);
+}
+
+void SaveModel(const std::string& dir, const ModelMeta& m) {
+  std::ostringstream j;
+  j << "{\n    \"name\": " << JsonStr(m.name) << ",\n    \"optim_type\": " << JsonStr(OptimName(m.optim_type))
+    << ",\n    \"optim_conf\": " << JsonConf(m.optim_conf, "    ") << ",\n    \"tables\": [";
+  size_t i = 0;
+  for (auto& kv : m.tables) {
+    const TableMeta& t = kv.second;
+    j << (i++ ? ",\n" : "\n") << "        {\n            \"id\": " << t.id << ",\n            \"name\": "
+      << JsonStr(t.name) << ",\n            \"table_type\": "
+      << (t.table_type == TableType::kDense ? "\"Dense\"" : "\"Sparse\"") << ",\n            \"element_type\": "
+      << JsonStr(DTypeName(t.element_type));
+    if (t.table_type == TableType::kDense) {
+      j << ",\n            \"shape\": [";
+      for (size_t k = 0; k < t.shape.size(); ++k) j << (k ? ", " : "") << t.shape[k];
+      j << "]";
+    } else {
+      j << ",\n            \"dimension\": " << t.dimension << ",\n            \"init_type\": "
+        << JsonStr(InitName(t.init_type)) << ",\n            \"init_conf\": " << JsonConf(t.init_conf, "            ");
+    }
+    j << "\n        }";
+  }
+  j << "\n    ]\n}";
+  WriteText((fs::path(dir) / kModelJson).string(), j.str());
+
+  FileSink sink((fs::path(dir) / kModelBin).string());
+  KB_CHECK(sink.IsOpen(), err::kCheckpointIO, "cannot open model.binary in " + dir);
+  Writer w(&sink);
+  w.Model(m);
+}
+
+ModelMeta LoadModel(const std::string& dir) {
+  FileSource src((fs::path(dir) / kModelBin).string());
+  KB_CHECK(src.IsOpen(), err::kCheckpointIO, "cannot open model.binary in " + dir);
+  Reader r(&src);
+  return r.Model();
+}
+
+void SaveDense(const std::string& dir, uint64_t id, const std::string& name, const Value& v) {
+  FileSink sink((fs::path(dir) / (name + kDenseSuffix)).string());
+  KB_CHECK(sink.IsOpen(), err::kCheckpointIO, "cannot open dense file for " + name);
+  Writer w(&sink);
+  w.Pod<uint8_t>(static_cast<uint8_t>(TableType::kDense));
+  w.Pod<uint64_t>(id);
+  w.Str(name);
+  w.Val(v);
+}
+
+bool LoadDense(const std::string& dir, const std::string& name, uint64_t* id, Value* v) {
+  fs::path p = fs::path(dir) / (name + kDenseSuffix);
+  if (!fs::exists(p)) return false;
+  FileSource src(p.string());
+  KB_CHECK(src.IsOpen(), err::kCheckpointIO, "cannot open " + p.string());
+  Reader r(&src);
+  KB_CHECK(r.Pod<uint8_t>() == static_cast<uint8_t>(TableType::kDense), err::kTableTypeUnCompatible,
+           p.string() + " is not a dense table file");
+  *id = r.Pod<uint64_t>();
+  std::string stored = r.Str();
+  (void)stored;
+  *v = r.Val();
+  return true;
+}
+
+void SaveSparse(const std::string& dir, const SparseHeader& h, const SparseColumns& c) {
+  const size_t n = c.ids.size();
+  const int64_t d = h.dim;
+  KB_CHECK(c.vals.size() == n * static_cast<size_t>(d), err::kBadArgument, "vals size does not match ids");
+  for (auto& kv : c.states)
+    KB_CHECK(kv.second.size() == n * static_cast<size_t>(d), err::kBadArgument, "state size does not match ids");
+  for (auto& kv : c.states_i) KB_CHECK(kv.second.size() == n, err::kBadArgument, "state_i size does not match ids");
+
+  std::vector<uint64_t> order(n);
+  std::iota(order.begin(), order.end(), 0);
+  std::sort(order.begin(), order.end(), [&](uint64_t a, uint64_t b) {
+    uint64_t sa = c.ids[a] % kSlotCount, sb = c.ids[b] % kSlotCount;
+    return sa != sb ? sa < sb : c.ids[a] < c.ids[b];
+  });
+  uint64_t per_slot[kSlotCount] = {0};
+  for (uint64_t id : c.ids) per_slot[id % kSlotCount]++;
+
+  FileSink sink((fs::path(dir) / (h.name + kSparseSuffix)).string());
+  KB_CHECK(sink.IsOpen(), err::kCheckpointIO, "cannot open sparse file for " + h.name);
+  Writer w(&sink);
+  w.Pod<uint8_t>(static_cast<uint8_t>(TableType::kSparse));
+  w.Pod<uint64_t>(h.id);
+  w.Str(h.name);
+  w.Pod<int64_t>(h.dim);
+  w.Pod<uint8_t>(static_cast<uint8_t>(h.dtype));
+  w.Pod<uint8_t>(static_cast<uint8_t>(h.init_type));
+  w.ConfMap(h.init_conf);
+  w.Pod<uint64_t>(kSlotCount);
+
+  size_t pos = 0;
+  for (uint64_t s = 0; s < kSlotCount; ++s) {
+    w.Pod<uint64_t>(per_slot[s]);
+    for (uint64_t k = 0; k < per_slot[s]; ++k, ++pos) {
+      const uint64_t r = order[pos];
+      w.Pod<uint64_t>(c.ids[r]);
+      w.RowF32(c.vals.data() + r * d, d);
+      w.Pod<uint64_t>(c.states.size());
+      for (auto& kv : c.states) {
+        w.Pod<uint32_t>(kv.first);
+        w.RowF32(kv.second.data() + r * d, d);
+      }
+      w.Pod<uint64_t>(c.states_i.size());
+      for (auto& kv : c.states_i) {
+        w.Pod<uint32_t>(kv.first);
+        w.Pod<int64_t>(kv.second[r]);
+      }
+    }
+  }
+}
+
+bool LoadSparse(const std::string& dir, const std::string& name, const RowFilter& filter, SparseHeader* h,
+                SparseColumns* c) {
+  fs::path p = fs::path(dir) / (name + kSparseSuffix);
+  if (!fs::exists(p)) return false;
+  FileSource src(p.string());
+  KB_CHECK(src.IsOpen(), err::kCheckpointIO, "cannot open " + p.string());
+  Reader r(&src);
+  KB_CHECK(r.Pod<uint8_t>() == static_cast<uint8_t>(TableType::kSparse), err::kTableTypeUnCompatible,
+           p.string() + " is not a sparse table file");
+  h->id = r.Pod<uint64_t>();
+  h->name = r.Str();
+  h->dim = r.Pod<int64_t>();
+  h->dtype = static_cast<DType>(r.Pod<uint8_t>());
+  h->init_type = static_cast<InitializerType>(r.Pod<uint8_t>());
+  h->init_conf = r.ConfMap();
+  KB_CHECK(h->dtype == DType::kFloat32, err::kSparseTableUnCompatible, "only Float32 sparse tables are supported");
+  KB_CHECK(h->dim > 0 && h->dim < (1 << 20), err::kSparseDimensionUnCompatible, "implausible dimension");
+  if (c->dim == 0) c->dim = h->dim;
+  KB_CHECK(c->dim == h->dim, err::kSparseDimensionUnCompatible, "dimension differs between shard files");
+  const size_t d = static_cast<size_t>(h->dim);
+
+  const uint64_t slots = r.Pod<uint64_t>();
+  KB_CHECK(slots < (1u << 16), err::kDeserializeReply, "implausible slot count");
+  for (uint64_t s = 0; s < slots; ++s) {
+    const uint64_t n = r.Pod<uint64_t>();
+    for (uint64_t k = 0; k < n; ++k) {
+      const uint64_t id = r.Pod<uint64_t>();
+      Value v = r.Val();
+      if (!filter.Keep(id)) continue;
+      KB_CHECK(static_cast<size_t>(v.val.Numel()) == d && v.val.dtype == DType::kFloat32,
+               err::kSparseDimensionUnCompatible, "row shape differs from table dimension");
+      const size_t row = c->ids.size();
+      c->ids.push_back(id);
+      c->vals.insert(c->vals.end(), v.val.f32(), v.val.f32() + d);
+      // A state the row does not carry means "never updated": zeros / step 0.
+      for (auto& kv : v.states) {
+        auto& col = c->states[kv.first];
+        col.resize(row * d, 0.f);
+        if (static_cast<size_t>(kv.second.Numel()) == d && kv.second.dtype == DType::kFloat32)
+          col.insert(col.end(), kv.second.f32(), kv.second.f32() + d);
+      }
+      for (auto& kv : c->states) kv.second.resize((row + 1) * d, 0.f);
+      for (auto& kv : v.states_i) {
+        auto& col = c->states_i[kv.first];
+        col.resize(row, 0);
+        col.push_back(kv.second);
+      }
+      for (auto& kv : c->states_i) kv.second.resize(row + 1, 0);
+    }
+  }
+  return true;
+}
+
+}  // namespace ckpt
+}  // namespace kb

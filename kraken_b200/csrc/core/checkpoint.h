@@ -1,0 +1,89 @@
+// Checkpoint files in the reference's layout, readable and writable by both.
+//
+//   <saved_dir>/shard_<node_id>/<YYYY-MM-DD-HH-MM-SS>/
+//       router.json  router.binary  model.json  model.binary
+//       <table>.dense    u8 0, u64 id, string name, Value
+//       <table>.sparse   u8 1, u64 id, string name, i64 dim, u8 dtype, u8 init_type, conf,
+//                        u64 slot_count(=8), per slot: u64 n, n x {u64 id, Value}
+//                        (slot = id % 8, ids ascending inside a slot)
+//
+// Format source: kraken/checkpoint/checkpoint.cc:17-23,55-63,288-510 and
+// kraken/checkpoint/checkpoint_exec.cc:246-377 (save, retention) / :379-521 (load).
+// Differences on purpose: maps are written in ascending key order, unused
+// metadata fields are zero instead of uninitialised, and every row carries its
+// optimizer-state entries.  The reader accepts the reference's variants (any
+// map order, rows without state entries, garbage in unused fields).
+#pragma once
+
+#include <cstdint>
+#include <map>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "router.h"
+#include "serialize.h"
+
+namespace kb {
+namespace ckpt {
+
+constexpr uint64_t kSlotCount = 8;
+
+// Columnar image of one shard's part of a sparse table (what device export
+// produces and device import consumes).
+struct SparseColumns {
+  int64_t dim = 0;
+  std::vector<uint64_t> ids;                       // [n]
+  std::vector<float> vals;                         // [n, dim]
+  std::map<uint32_t, std::vector<float>> states;   // StateType -> [n, dim]
+  std::map<uint32_t, std::vector<int64_t>> states_i;  // StateType -> [n]
+};
+
+struct SparseHeader {
+  uint64_t id = 0;
+  std::string name;
+  int64_t dim = 0;
+  DType dtype = DType::kFloat32;
+  InitializerType init_type = InitializerType::kConstant;
+  Conf init_conf;
+};
+
+// Row filter applied while loading a sparse file.
+struct RowFilter {
+  enum Mode { kAll = 0, kModulo = 1, kRing = 2 } mode = kAll;
+  uint64_t table_salt = 0;  // kModulo: OwnerOf(table_salt, id, world) == rank
+  uint32_t world = 1;
+  uint32_t rank = 0;
+  const Router* ring = nullptr;  // kRing: ring->Hit(Mix64(table_id) ^ Mix64(id)) == node
+  uint64_t table_id = 0;
+  uint64_t node = 0;
+  bool Keep(uint64_t id) const;
+};
+
+std::string TimestampDirName();                       // local time, %Y-%m-%d-%H-%M-%S
+bool ParseTimestampDir(const std::string& name, int64_t* key);  // sortable key, false if not a timestamp
+
+// Creates <saved_dir>/shard_<shard>/<timestamp>/ after deleting the oldest
+// timestamp dirs while their count >= max_save_count; returns the new dir.
+std::string PrepareSaveDir(const std::string& saved_dir, uint64_t shard, size_t max_save_count);
+// shard id -> newest timestamp dir below load_dir/shard_<id>/.
+std::map<uint64_t, std::string> LatestShardDirs(const std::string& load_dir);
+
+void SaveRouter(const std::string& dir, const Router& r);  // router.json + router.binary
+Router LoadRouter(const std::string& dir);
+void SaveModel(const std::string& dir, const ModelMeta& m);  // model.json + model.binary
+ModelMeta LoadModel(const std::string& dir);
+
+void SaveDense(const std::string& dir, uint64_t id, const std::string& name, const Value& v);
+// Returns false if the file does not exist.
+bool LoadDense(const std::string& dir, const std::string& name, uint64_t* id, Value* v);
+
+// Rows may be passed in any order; they are written slot by slot, ascending.
+// `order` (optional) receives the permutation used, for callers that cache it.
+void SaveSparse(const std::string& dir, const SparseHeader& h, const SparseColumns& cols);
+// Appends the kept rows of <dir>/<name>.sparse to *cols; false if the file does not exist.
+bool LoadSparse(const std::string& dir, const std::string& name, const RowFilter& filter, SparseHeader* h,
+                SparseColumns* cols);
+
+}  // namespace ckpt
+}  // namespace kb

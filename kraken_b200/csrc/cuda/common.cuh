@@ -1,0 +1,133 @@
+// Device-side building blocks shared by the sm_100a kernels: system-scope
+// signalling between GPUs, bounded waits, vector reductions, and the views of
+// the symmetric (peer-mapped) heap and of a hash-table shard.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../core/hash.h"
+#include "../core/optim_math.h"
+#include "../core/types.h"
+
+namespace kb {
+namespace cu {
+
+constexpr int kMaxWorld = 16;
+
+// Every rank allocates a heap with the same layout and maps all peers' heaps;
+// a buffer is named by its byte offset, so `base[p] + off` is rank p's copy.
+struct Sym {
+  char* base[kMaxWorld];
+  int rank;
+  int world;
+  template <typename T>
+  __device__ __forceinline__ T* at(int peer, size_t off) const {
+    return reinterpret_cast<T*>(base[peer] + off);
+  }
+};
+
+// One hash-table shard (open addressing, linear probing, no tombstones: rows
+// are never deleted on the training path; eviction rebuilds the table).
+struct TableView {
+  unsigned long long* keys;  // [cap], kEmptyKey = free
+  float* val;                // [cap, dim]
+  float* s[3];               // optimizer state slabs [cap, dim] or nullptr
+  int* steps;                // [cap] or nullptr
+  unsigned long long* lead;  // [cap] (push epoch << 32 | entry) or nullptr when world == 1
+  int* size;                 // number of occupied slots
+  int* status;               // first error code wins
+  uint32_t bits;             // cap = 1 << bits
+  int dim;
+  InitPOD init;
+  uint64_t seed_key;
+};
+
+__device__ __forceinline__ void set_status(int* status, int code) { atomicCAS(status, 0, code); }
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Spins until *flag >= want or `limit` polls have passed; false on give-up.
+// Never an unbounded wait: a peer that does not show up costs `limit` polls,
+// after which the caller records kTimeout and returns.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - want) >= 0) return true;
+    __nanosleep(it < 64 ? 32 : 256);
+  }
+  return false;
+}
+
+// Vector float reduction into global memory (sm_90+): one 16-byte L2 atomic.
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+// Marks the calling block as finished; returns true in exactly one block: the
+// last one of the grid to arrive.  All of the grid's earlier global / peer
+// stores are then visible system-wide to whoever observes a later release store.
+__device__ __forceinline__ bool last_block_done(uint32_t* counter) {
+  __shared__ bool is_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(counter, 1u);
+    is_last = (prev == gridDim.x - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (is_last) __threadfence_system();
+  return is_last;
+}
+
+// Finds `id`; with insert=true claims a free slot and initialises the value
+// row.  Returns the slot or -1 (absent / table full).
+__device__ __forceinline__ int table_find_or_insert(const TableView& t, uint64_t id, bool insert, bool* created) {
+  const uint64_t mask = (1ull << t.bits) - 1;
+  uint64_t slot = SlotHash(id, t.bits);
+  const uint32_t max_probe = t.bits >= 13 ? 8192u : (1u << t.bits);
+  *created = false;
+  for (uint32_t probe = 0; probe < max_probe; ++probe) {
+    unsigned long long k = __ldcg(&t.keys[slot]);
+    if (k == id) return static_cast<int>(slot);
+    if (k == kEmptyKey) {
+      if (!insert) return -1;
+      const unsigned long long old = atomicCAS(&t.keys[slot], kEmptyKey, static_cast<unsigned long long>(id));
+      if (old == kEmptyKey) {
+        *created = true;
+        float* row = t.val + slot * static_cast<uint64_t>(t.dim);
+        InitRow(t.init, t.seed_key, id, t.dim, row);
+        return static_cast<int>(slot);
+      }
+      if (old == id) return static_cast<int>(slot);
+    }
+    slot = (slot + 1) & mask;
+  }
+  set_status(t.status, err::kTableFull);
+  return -1;
+}
+
+// Adds `created` flags of the warp into the size counter with one atomic.
+__device__ __forceinline__ void count_created(const TableView& t, bool created) {
+  const unsigned m = __ballot_sync(__activemask(), created);
+  if (created && (__ffs(m) - 1) == static_cast<int>(threadIdx.x & 31)) atomicAdd(t.size, __popc(m));
+}
+
+}  // namespace cu
+}  // namespace kb

@@ -1,0 +1,287 @@
+// Dense-parameter step fused with its collective, and the DCT kernels.
+//
+// dense_step is ONE kernel per rank that does what the reference does with a
+// push RPC per table, a server-side optimizer and a pull RPC per step
+// (kraken/worker/emitter.cc:377-447, kraken/ps/dense_table.cc:31-43,
+// kraken/pytorch/optimizer.py:151-173):
+//
+//   1. raise "my gradient is complete" on every peer (release store);
+//   2. wait (bounded) for the same flag from every rank;
+//   3. for the slice this rank owns: sum the slice of every rank's gradient
+//      buffer directly out of peer memory (reduce-scatter by loads), run the
+//      optimizer on value + slice-local state, store the new values into every
+//      rank's parameter copy (all-gather by stores);
+//   4. raise "slice done" on every peer, wait for all owners, then zero the
+//      local gradient buffer for the next backward.
+//
+// With DCT the gradients do not travel dense: dct_compact turns the local
+// f = g + e into per-owner (index, value) lists and the owner scatter-adds the
+// lists of all ranks (dense_gather_coo) before step 3 reads its accumulator.
+// DCT here is Dynamic Communication Thresholding, kraken/worker/dct_emitter.cc:16-43.
+#include "common.cuh"
+#include "dense_kernels.h"
+
+namespace kb {
+namespace cu {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+Sym to_sym(const SymHost& h) {
+  Sym s;
+  for (int i = 0; i < kMaxWorld; ++i) s.base[i] = static_cast<char*>(h.base[i]);
+  s.rank = h.rank;
+  s.world = h.world;
+  return s;
+}
+
+__device__ __forceinline__ bool wait_all(const uint32_t* flags, int world, uint32_t want, uint32_t limit) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world && !wait_flag(flags + threadIdx.x, want, limit)) ok = 0;
+  __syncthreads();
+  return ok != 0;
+}
+
+// Owner side of the DCT exchange: scatter-add every rank's list into acc[slice].
+__global__ void __launch_bounds__(kThreads)
+dense_gather_coo_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long slice, float* acc, uint32_t spin_limit) {
+  const uint32_t epoch = ctrl->epoch + 1;
+  if (blockIdx.x == 0 && threadIdx.x < sym.world)
+    st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_grad) + sym.rank, epoch);
+  if (sym.world > 1 && !wait_all(sym.at<uint32_t>(sym.rank, lay.flag_grad), sym.world, epoch, spin_limit)) {
+    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
+    return;
+  }
+  const long long gtid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long gsize = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int k = 0; k < sym.world; ++k) {
+    const int p = (sym.rank + k) % sym.world;
+    const int cnt = __ldcg(sym.at<int>(p, lay.coo_cnt) + sym.rank);
+    const int* idx = sym.at<int>(p, lay.coo_idx) + static_cast<size_t>(sym.rank) * slice;
+    const float* val = sym.at<float>(p, lay.coo_val) + static_cast<size_t>(sym.rank) * slice;
+    for (long long j = gtid; j < cnt; j += gsize) {
+      const int i = __ldcg(idx + j);
+      if (i >= 0 && i < slice) atomicAdd(acc + i, __ldcg(val + j));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dense_step_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, float* __restrict__ s0,
+                  float* __restrict__ s1, float* __restrict__ s2, float* acc, const int* __restrict__ chunk_table,
+                  int* table_steps, const uint8_t* __restrict__ table_active, int n_tables, OptimPOD optim,
+                  const float* __restrict__ lr_ptr, float grad_scale, int use_coo, uint32_t spin_limit) {
+  const uint32_t epoch = ctrl->epoch + 1;
+  const long long slice = n_pad / sym.world;
+  const long long base = slice * sym.rank;
+  const float lr = *lr_ptr;
+
+  if (!use_coo) {
+    if (blockIdx.x == 0 && threadIdx.x < sym.world)
+      st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_grad) + sym.rank, epoch);
+    if (sym.world > 1 && !wait_all(sym.at<uint32_t>(sym.rank, lay.flag_grad), sym.world, epoch, spin_limit)) {
+      if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
+      return;
+    }
+  }
+
+  const long long gtid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long gsize = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long q = gtid; q * 4 < slice; q += gsize) {
+    const long long li = q * 4;      // offset inside the slice
+    const long long gi = base + li;  // offset inside the flat buffer
+    const int t = chunk_table[gi / kDenseChunk];
+    if (t < 0 || !table_active[t]) {
+      if (use_coo) *reinterpret_cast<float4*>(acc + li) = make_float4(0.f, 0.f, 0.f, 0.f);
+      continue;
+    }
+    float g[4] = {0.f, 0.f, 0.f, 0.f};
+    if (use_coo) {
+      const float4 a = *reinterpret_cast<const float4*>(acc + li);
+      g[0] = a.x, g[1] = a.y, g[2] = a.z, g[3] = a.w;
+      *reinterpret_cast<float4*>(acc + li) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      for (int k = 0; k < sym.world; ++k) {
+        const int p = (sym.rank + k) % sym.world;
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(sym.at<float>(p, lay.grad) + gi));
+        g[0] += v.x, g[1] += v.y, g[2] += v.z, g[3] += v.w;
+      }
+    }
+    const int64_t step = static_cast<int64_t>(table_steps[t]) + 1;
+    const AdamBias ab = optim.type == 1 ? AdamBiasAt(optim, step) : AdamBias{1.f, 1.f};
+    float* wptr = sym.at<float>(sym.rank, lay.param) + gi;
+    float w[4], a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0}, a2[4] = {0, 0, 0, 0};
+    *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(wptr);
+    if (s0) *reinterpret_cast<float4*>(a0) = *reinterpret_cast<const float4*>(s0 + li);
+    if (s1) *reinterpret_cast<float4*>(a1) = *reinterpret_cast<const float4*>(s1 + li);
+    if (s2) *reinterpret_cast<float4*>(a2) = *reinterpret_cast<const float4*>(s2 + li);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) UpdateElem(optim, lr, g[e] * grad_scale, step, ab, w[e], a0[e], a1[e], a2[e]);
+    if (s0) *reinterpret_cast<float4*>(s0 + li) = *reinterpret_cast<float4*>(a0);
+    if (s1) *reinterpret_cast<float4*>(s1 + li) = *reinterpret_cast<float4*>(a1);
+    if (s2) *reinterpret_cast<float4*>(s2 + li) = *reinterpret_cast<float4*>(a2);
+    const float4 wn = *reinterpret_cast<float4*>(w);
+    for (int k = 0; k < sym.world; ++k) {
+      const int p = (sym.rank + k) % sym.world;
+      *reinterpret_cast<float4*>(sym.at<float>(p, lay.param) + gi) = wn;
+    }
+  }
+
+  if (last_block_done(&ctrl->done[0])) {
+    if (threadIdx.x < sym.world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_done) + sym.rank, epoch);
+    for (int t = threadIdx.x; t < n_tables; t += blockDim.x)
+      if (table_active[t]) table_steps[t] += 1;
+    if (threadIdx.x == 0) ctrl->epoch = epoch;
+  }
+  // Every owner has finished reading this rank's gradient once its flag_done is up.
+  if (sym.world > 1 && !wait_all(sym.at<uint32_t>(sym.rank, lay.flag_done), sym.world, epoch, spin_limit)) {
+    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
+    return;
+  }
+  float4* gz = reinterpret_cast<float4*>(sym.at<float>(sym.rank, lay.grad));
+  for (long long q = gtid; q * 4 < n_pad; q += gsize) gz[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (use_coo && gtid < sym.world) sym.at<int>(sym.rank, lay.coo_cnt)[gtid] = 0;
+}
+
+// ------------------------------------------------------------------ DCT
+__global__ void dct_accumulate_kernel(float* __restrict__ grad, const float* __restrict__ residual, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    grad[i] += residual[i];
+}
+
+// prefix_state[0] = bits fixed so far, prefix_state[1] = k still to skip from the top.
+__global__ void __launch_bounds__(kThreads)
+radix_hist_kernel(const float* __restrict__ x, long long n, int pass, const uint32_t* __restrict__ prefix_state,
+                  uint32_t* hist) {
+  __shared__ uint32_t sh[256];
+  sh[threadIdx.x] = 0;
+  __syncthreads();
+  const int shift = 24 - 8 * pass;
+  const uint32_t prefix = prefix_state[0];
+  const uint32_t hi_mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t b = __float_as_uint(x[i]) & 0x7FFFFFFFu;
+    if ((b & hi_mask) == prefix) atomicAdd(&sh[(b >> shift) & 0xFFu], 1u);
+  }
+  __syncthreads();
+  if (sh[threadIdx.x]) atomicAdd(&hist[pass * 256 + threadIdx.x], sh[threadIdx.x]);
+}
+
+__global__ void radix_pick_kernel(int pass, uint32_t* prefix_state, const uint32_t* __restrict__ hist, float* tau) {
+  if (threadIdx.x != 0) return;
+  const int shift = 24 - 8 * pass;
+  uint32_t k = prefix_state[1];
+  int d = 255;
+  for (; d > 0; --d) {
+    const uint32_t c = hist[pass * 256 + d];
+    if (c >= k) break;
+    k -= c;
+  }
+  prefix_state[0] |= static_cast<uint32_t>(d) << shift;
+  prefix_state[1] = k;
+  if (pass == 3) *tau = __uint_as_float(prefix_state[0]);
+}
+
+__global__ void radix_init_kernel(uint32_t* prefix_state, uint32_t* hist, uint32_t k) {
+  for (int i = threadIdx.x; i < 4 * 256; i += blockDim.x) hist[i] = 0;
+  if (threadIdx.x == 0) {
+    prefix_state[0] = 0;
+    prefix_state[1] = k;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dct_compact_kernel(Sym sym, DenseLayout lay, long long n_pad, float* __restrict__ residual,
+                   const float* __restrict__ tau_table, const int* __restrict__ chunk_table) {
+  const long long slice = n_pad / sym.world;
+  float* grad = sym.at<float>(sym.rank, lay.grad);
+  int* cnt = sym.at<int>(sym.rank, lay.coo_cnt);
+  int* idx = sym.at<int>(sym.rank, lay.coo_idx);
+  float* val = sym.at<float>(sym.rank, lay.coo_val);
+  const int lane = threadIdx.x & 31;
+  for (long long base = blockIdx.x * static_cast<long long>(blockDim.x); base < n_pad;
+       base += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long i = base + threadIdx.x;  // n_pad is a multiple of 256: always in range
+    const float f = grad[i];
+    const int t = chunk_table[i / kDenseChunk];
+    const bool keep = t >= 0 && fabsf(f) >= tau_table[t];
+    // a warp's 32 elements share an owner: slices are multiples of 256 elements
+    const int owner = static_cast<int>(i / slice);
+    const unsigned m = __ballot_sync(0xffffffffu, keep);
+    int wbase = 0;
+    if (m != 0 && lane == __ffs(m) - 1) wbase = atomicAdd(&cnt[owner], __popc(m));
+    wbase = __shfl_sync(0xffffffffu, wbase, m ? __ffs(m) - 1 : 0);
+    if (keep) {
+      const long long pos = static_cast<long long>(owner) * slice + wbase + __popc(m & ((1u << lane) - 1));
+      idx[pos] = static_cast<int>(i - static_cast<long long>(owner) * slice);
+      val[pos] = f;
+    }
+    residual[i] = keep ? 0.f : f;
+    grad[i] = 0.f;
+  }
+}
+
+__global__ void dct_threshold_dense_kernel(float* __restrict__ grad, float* __restrict__ residual, long long n,
+                                           const float* __restrict__ tau_table, const int* __restrict__ chunk_table) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float f = grad[i];
+    const int t = chunk_table[i / kDenseChunk];
+    const bool keep = t >= 0 && fabsf(f) >= tau_table[t];
+    grad[i] = keep ? f : 0.f;
+    residual[i] = keep ? 0.f : f;
+  }
+}
+
+int grid_for(long long items, int cap = 148 * 4) {
+  long long g = (items + kThreads - 1) / kThreads;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, float* s0, float* s1, float* s2,
+                float* acc, const int* chunk_table, int* table_steps, const uint8_t* table_active, int n_tables,
+                OptimPOD optim, const float* lr, float grad_scale, int use_coo, uint32_t spin_limit,
+                cudaStream_t stream) {
+  const long long slice = n_pad / sym.world;
+  const int grid = grid_for(slice / 4, 148 * 2);
+  const Sym s = to_sym(sym);
+  if (use_coo) dense_gather_coo_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, slice, acc, spin_limit);
+  dense_step_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps,
+                                                   table_active, n_tables, optim, lr, grad_scale, use_coo, spin_limit);
+}
+
+void dct_accumulate(float* grad, const float* residual, long long n, cudaStream_t stream) {
+  dct_accumulate_kernel<<<grid_for(n), kThreads, 0, stream>>>(grad, residual, n);
+}
+
+void dct_select_tau(const float* x, long long n, long long k, uint32_t* hist, uint32_t* prefix_state, float* tau,
+                    cudaStream_t stream) {
+  radix_init_kernel<<<1, kThreads, 0, stream>>>(prefix_state, hist, static_cast<uint32_t>(k));
+  for (int pass = 0; pass < 4; ++pass) {
+    radix_hist_kernel<<<grid_for(n), kThreads, 0, stream>>>(x, n, pass, prefix_state, hist);
+    radix_pick_kernel<<<1, 32, 0, stream>>>(pass, prefix_state, hist, tau);
+  }
+}
+
+void dct_compact(SymHost sym, DenseLayout lay, long long n_pad, float* residual, const float* tau_table,
+                 const int* chunk_table, cudaStream_t stream) {
+  dct_compact_kernel<<<grid_for(n_pad), kThreads, 0, stream>>>(to_sym(sym), lay, n_pad, residual, tau_table,
+                                                               chunk_table);
+}
+
+void dct_threshold_dense(float* grad, float* residual, long long n, const float* tau_table, const int* chunk_table,
+                         cudaStream_t stream) {
+  dct_threshold_dense_kernel<<<grid_for(n), kThreads, 0, stream>>>(grad, residual, n, tau_table, chunk_table);
+}
+
+}  // namespace cu
+}  // namespace kb

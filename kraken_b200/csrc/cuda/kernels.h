@@ -1,0 +1,125 @@
+// Host-callable launchers of the sm_100a kernels.  Plain pointers and a
+// stream: nothing here depends on torch, so the kernels can be driven from
+// C, C++ or ctypes.  Every launcher is asynchronous on `stream`, allocates
+// nothing and never synchronises; errors are reported through the `status`
+// words the kernels write (codes of core/types.h).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../core/optim_math.h"
+
+namespace kb {
+namespace cu {
+
+constexpr int kMaxWorldHost = 16;
+
+struct SymHost {
+  void* base[kMaxWorldHost];
+  int rank;
+  int world;
+};
+
+// Byte offsets of one exchange channel inside every rank's symmetric heap.
+struct ChanLayout {
+  size_t inbox_ids;   // u64  [world][capS]   ids sent by each source
+  size_t inbox_meta;  // int2 [world]         {count, base offset in the source's receive buffer}
+  size_t rows_recv;   // f32  [capU][dim]     rows returned for this rank's unique ids
+  size_t inbox_grad;  // f32  [world][capS][dim]
+  size_t flag_req;    // u32  [world]
+  size_t flag_rsp;    // u32  [world]
+  size_t flag_push;   // u32  [world]
+  int capS;           // ids one source may send to one owner
+  int capU;           // unique ids one rank may request
+};
+
+// Per-channel device control block (local memory, not peer-mapped).
+struct Ctrl {
+  uint32_t pull_epoch;
+  uint32_t push_epoch;
+  uint32_t done[2];
+  int status;
+  int pad[3];
+};
+
+struct TableHost {
+  void* keys;
+  float* val;
+  float* s[3];
+  int* steps;
+  void* lead;
+  int* size;
+  int* status;
+  uint32_t bits;
+  int dim;
+  InitPOD init;
+  uint64_t seed_key;
+};
+
+// Scratch of the dedup kernels: an open-addressing set of 1 << hbits slots
+// (hbits chosen so that it holds at least 2 n ids), all keys kEmptyKey between calls.
+struct DedupScratch {
+  void* hkeys;   // u64 [1 << hbits]
+  int* hpos;     // int [1 << hbits]  rank of the unique id inside its owner group
+  int* hwin;     // int [1 << hbits]  index of the occurrence that inserted the id
+  int* slot_of;  // int [n]
+  uint32_t hbits;
+};
+
+// ---- dedup + bucketise by owner (unique ids grouped by owner rank) ----
+// cnt[world] is scratch (zeroed here).  Outputs: off[world + 1] (exclusive scan of
+// the per-owner unique counts), uniq[off[world]], inv[n] (occurrence -> unique).
+void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
+                     int64_t* uniq, int* inv, int* status, cudaStream_t stream);
+
+// ---- sparse pull ----
+void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,
+                   cudaStream_t stream);
+void pull_probe(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, int* slot_cache, bool insert,
+                uint32_t spin_limit, cudaStream_t stream);
+void pull_gather(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache, cudaStream_t stream);
+// out[n, dim] (bag_offsets == nullptr) or pooled out[k, dim].
+void pull_combine(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int* inv, int n, int dim, const int64_t* bag_offsets,
+                  int k, const float* weights, bool mean, const uint8_t* bag_mean, float patch_value, float* out,
+                  uint32_t spin_limit, cudaStream_t stream);
+
+// ---- sparse push ----
+// ugrad[capU, dim] must be zero on entry (push_dispatch re-zeroes what it sends).
+void push_scatter(const float* grads, const int* inv, int n, int dim, const int64_t* bag_offsets, int k,
+                  const float* weights, bool mean, const uint8_t* bag_mean, float* ugrad, cudaStream_t stream);
+void push_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const int* off, int max_n, int dim,
+                   cudaStream_t stream);
+void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache, OptimPOD optim,
+                const float* lr, uint32_t spin_limit, cudaStream_t stream);
+
+// ---- table maintenance ----
+void table_clear(TableHost table, cudaStream_t stream);
+// Inserts rows with given values and states (any of s0..s2 / steps may be null).
+void table_import(TableHost table, const int64_t* ids, const float* vals, const float* s0, const float* s1,
+                  const float* s2, const int* steps, int n, cudaStream_t stream);
+// Finds ids (no insert); rows[n, dim] gets the values, found[n] 1/0.
+void table_lookup(TableHost table, const int64_t* ids, int n, float* rows, uint8_t* found, cudaStream_t stream);
+// Compacts the occupied slots that pass the filter into the out_* arrays; *out_count receives how many.
+// filter_mode 0: all; 1: OwnerOf(salt, id, world) == rank; 2: OwnerOf(...) != rank; 3: steps >= min_steps.
+void table_export(TableHost table, int filter_mode, uint64_t salt, int world, int rank, int min_steps,
+                  int64_t* out_ids, float* out_vals, float* out_s0, float* out_s1, float* out_s2, int* out_steps,
+                  int* out_count, int out_cap, cudaStream_t stream);
+
+// ---- model kernels ----
+void jagged_forward(const float* values, const float* weights, const int64_t* offsets, int k, int dim, bool mean,
+                    float patch_value, float* out, cudaStream_t stream);
+void jagged_backward(const float* grads, const float* weights, const int64_t* offsets, int k, int dim, bool mean,
+                     float* out, cudaStream_t stream);
+// FM second-order interaction over emb[B, F, D]: out[b] = 0.5 * sum_k((sum_f e)^2 - sum_f e^2).
+void fm_forward(const float* emb, int B, int F, int D, float* out, cudaStream_t stream);
+void fm_backward(const float* emb, const float* gout, int B, int F, int D, float* gemb, cudaStream_t stream);
+// Binary cross entropy with logits, mean reduction: loss[0] += sum / n (loss must be zero on entry);
+// grad (optional) = (sigmoid(x) - y) / n.
+void bce_forward_backward(const float* logits, const float* labels, int n, float* loss, float* grad,
+                          cudaStream_t stream);
+
+}  // namespace cu
+}  // namespace kb

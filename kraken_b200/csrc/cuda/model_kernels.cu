@@ -1,0 +1,179 @@
+// Memory-bound model kernels: jagged (bag) pooling, FM second-order
+// interaction and binary cross entropy with logits.  Each makes one pass over
+// its input at HBM speed with the reduction done in registers / shuffles.
+//
+// Counterparts in the reference: kraken/pytorch/py/jagged_ops.cc:14-420 (CPU,
+// OpenMP), examples/DeepFM/model/DeepFM.py:96-107 (FM as torch expressions)
+// and :140 (BCEWithLogits).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace kb {
+namespace cu {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+int lanes_for(int dim) {
+  int l = 1;
+  while (l < dim && l < 32) l <<= 1;
+  return l;
+}
+
+int grid_rows(long long rows, int lpr, int cap = 148 * 16) {
+  long long g = (rows * lpr + kThreads - 1) / kThreads;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return static_cast<int>(g);
+}
+
+__global__ void __launch_bounds__(kThreads)
+jagged_forward_kernel(const float* __restrict__ values, const float* __restrict__ weights,
+                      const int64_t* __restrict__ offsets, int k, int dim, int lpr, int mean, float patch_value,
+                      float* __restrict__ out) {
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int stride = (gridDim.x * blockDim.x) / lpr;
+  for (int b = gtid / lpr; b < k; b += stride) {
+    const int64_t lo = offsets[b], hi = offsets[b + 1];
+    for (int j = lane; j < dim; j += lpr) {
+      float acc = 0.f;
+      for (int64_t r = lo; r < hi; ++r) acc += (weights ? weights[r] : 1.f) * values[r * dim + j];
+      if (hi <= lo)
+        acc = patch_value;
+      else if (mean)
+        acc /= static_cast<float>(hi - lo);
+      out[static_cast<size_t>(b) * dim + j] = acc;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+jagged_backward_kernel(const float* __restrict__ grads, const float* __restrict__ weights,
+                       const int64_t* __restrict__ offsets, int k, int dim, int lpr, int mean,
+                       float* __restrict__ out) {
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int stride = (gridDim.x * blockDim.x) / lpr;
+  for (int b = gtid / lpr; b < k; b += stride) {
+    const int64_t lo = offsets[b], hi = offsets[b + 1];
+    if (hi <= lo) continue;
+    const float scale = mean ? 1.f / static_cast<float>(hi - lo) : 1.f;
+    for (int j = lane; j < dim; j += lpr) {
+      const float g = grads[static_cast<size_t>(b) * dim + j] * scale;
+      for (int64_t r = lo; r < hi; ++r) out[r * dim + j] = weights ? g * weights[r] : g;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fm_forward_kernel(const float* __restrict__ emb, int B, int F, int D, int lpr, float* __restrict__ out) {
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int stride = (gridDim.x * blockDim.x) / lpr;
+  const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
+  const int rounds = (B + stride - 1) / stride;
+  for (int it = 0; it < rounds; ++it) {
+    const int b = gtid / lpr + it * stride;
+    float part = 0.f;
+    if (b < B) {
+      const float* e = emb + static_cast<size_t>(b) * F * D;
+      for (int j = lane; j < D; j += lpr) {
+        float s = 0.f, q = 0.f;
+        for (int f = 0; f < F; ++f) {
+          const float v = e[f * D + j];
+          s += v;
+          q += v * v;
+        }
+        part += 0.5f * (s * s - q);
+      }
+    }
+    for (int o = lpr >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(group_mask, part, o);
+    if (b < B && lane == 0) out[b] = part;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fm_backward_kernel(const float* __restrict__ emb, const float* __restrict__ gout, int B, int F, int D, int lpr,
+                   float* __restrict__ gemb) {
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int stride = (gridDim.x * blockDim.x) / lpr;
+  for (int b = gtid / lpr; b < B; b += stride) {
+    const float* e = emb + static_cast<size_t>(b) * F * D;
+    float* g = gemb + static_cast<size_t>(b) * F * D;
+    const float go = gout[b];
+    for (int j = lane; j < D; j += lpr) {
+      float s = 0.f;
+      for (int f = 0; f < F; ++f) s += e[f * D + j];
+      for (int f = 0; f < F; ++f) g[f * D + j] = go * (s - e[f * D + j]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+bce_kernel(const float* __restrict__ logits, const float* __restrict__ labels, int n, float inv_n, float* loss,
+           float* __restrict__ grad) {
+  float acc = 0.f;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const float x = logits[i], y = labels[i];
+    const float ax = fabsf(x);
+    const float t = expf(-ax);
+    acc += fmaxf(x, 0.f) - x * y + log1pf(t);
+    if (grad) {
+      const float sig = x >= 0.f ? 1.f / (1.f + t) : t / (1.f + t);
+      grad[i] = (sig - y) * inv_n;
+    }
+  }
+  __shared__ float warp_sum[kThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < kThreads / 32 ? warp_sum[threadIdx.x] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) atomicAdd(loss, v * inv_n);
+  }
+}
+
+}  // namespace
+
+void jagged_forward(const float* values, const float* weights, const int64_t* offsets, int k, int dim, bool mean,
+                    float patch_value, float* out, cudaStream_t stream) {
+  if (k <= 0) return;
+  const int lpr = lanes_for(dim);
+  jagged_forward_kernel<<<grid_rows(k, lpr), kThreads, 0, stream>>>(values, weights, offsets, k, dim, lpr, mean ? 1 : 0,
+                                                                    patch_value, out);
+}
+
+void jagged_backward(const float* grads, const float* weights, const int64_t* offsets, int k, int dim, bool mean,
+                     float* out, cudaStream_t stream) {
+  if (k <= 0) return;
+  const int lpr = lanes_for(dim);
+  jagged_backward_kernel<<<grid_rows(k, lpr), kThreads, 0, stream>>>(grads, weights, offsets, k, dim, lpr, mean ? 1 : 0,
+                                                                     out);
+}
+
+void fm_forward(const float* emb, int B, int F, int D, float* out, cudaStream_t stream) {
+  if (B <= 0) return;
+  const int lpr = lanes_for(D);
+  fm_forward_kernel<<<grid_rows(B, lpr), kThreads, 0, stream>>>(emb, B, F, D, lpr, out);
+}
+
+void fm_backward(const float* emb, const float* gout, int B, int F, int D, float* gemb, cudaStream_t stream) {
+  if (B <= 0) return;
+  const int lpr = lanes_for(D);
+  fm_backward_kernel<<<grid_rows(B, lpr), kThreads, 0, stream>>>(emb, gout, B, F, D, lpr, gemb);
+}
+
+void bce_forward_backward(const float* logits, const float* labels, int n, float* loss, float* grad,
+                          cudaStream_t stream) {
+  if (n <= 0) return;
+  int grid = (n + kThreads - 1) / kThreads;
+  if (grid > 148 * 4) grid = 148 * 4;
+  bce_kernel<<<grid, kThreads, 0, stream>>>(logits, labels, n, 1.f / static_cast<float>(n), loss, grad);
+}
+
+}  // namespace cu
+}  // namespace kb

@@ -1,0 +1,618 @@
+// Sparse pull / push for GPU-resident hash-table shards, exchanged over peer
+// memory (NVLink / NVSwitch) from inside the kernels.
+//
+// One step of a table ("channel") on every rank, all ranks running the same
+// sequence (the calls are collective):
+//
+//   dedup_bucketize   unique ids of the local batch, grouped by owner rank
+//   pull_dispatch     store each owner's id list into that owner's inbox (peer st), raise flag_req
+//   pull_probe        owner: wait for a source's flag, find-or-insert its ids, remember the slots
+//   pull_gather       owner: copy the rows straight into the requester's receive buffer (peer st),
+//                     raise flag_rsp
+//   pull_combine      requester: wait for the owners, expand unique rows to occurrences or pool bags
+//   ... model forward / backward ...
+//   push_scatter      segment-sum of occurrence (or bag) gradients per unique id (vector red)
+//   push_dispatch     store summed gradient rows into the owners' gradient inboxes, raise flag_push
+//   push_apply        owner: merge rows that several sources sent for one slot, then run the
+//                     optimizer in place on value + state slabs (slots remembered from the pull)
+//
+// This replaces the reference's client-side dedup / routing / scatter-gather
+// RPC (kraken/worker/emitter.cc:123-183, :491-550) and the server's per-slot
+// locked skip-list loops (kraken/ps/sparse_table.cc:33-108).  Flags carry a
+// per-channel epoch; every wait is bounded (common.cuh: wait_flag) and ends in
+// a status code instead of a hang.  Peer memory is only touched with plain
+// loads / stores / release stores, never with TMA.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace kb {
+namespace cu {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr uint64_t kDedupSalt = 0x5bd1e9955bd1e995ull;
+
+Sym to_sym(const SymHost& h) {
+  Sym s;
+  for (int i = 0; i < kMaxWorld; ++i) s.base[i] = static_cast<char*>(h.base[i]);
+  s.rank = h.rank;
+  s.world = h.world;
+  return s;
+}
+
+TableView to_view(const TableHost& h) {
+  TableView t;
+  t.keys = static_cast<unsigned long long*>(h.keys);
+  t.val = h.val;
+  for (int i = 0; i < 3; ++i) t.s[i] = h.s[i];
+  t.steps = h.steps;
+  t.lead = static_cast<unsigned long long*>(h.lead);
+  t.size = h.size;
+  t.status = h.status;
+  t.bits = h.bits;
+  t.dim = h.dim;
+  t.init = h.init;
+  t.seed_key = h.seed_key;
+  return t;
+}
+
+int grid_for(long long work_items, int per_block = kThreads, int cap = 148 * 8) {
+  long long g = (work_items + per_block - 1) / per_block;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return static_cast<int>(g);
+}
+
+// Row-parallel geometry: a row of `dim` floats is handled by `lpr` adjacent
+// lanes (a power of two <= 32), each moving VEC floats per chunk.
+struct RowGeom {
+  int vec;     // 4 or 1
+  int chunks;  // dim / vec
+  int lpr;     // lanes per row
+};
+
+RowGeom row_geom(int dim) {
+  RowGeom g;
+  g.vec = (dim % 4 == 0) ? 4 : 1;
+  g.chunks = dim / g.vec;
+  int l = 1;
+  while (l < g.chunks && l < 32) l <<= 1;
+  g.lpr = l;
+  return g;
+}
+
+template <int VEC>
+struct Vec;
+template <>
+struct Vec<4> {
+  using T = float4;
+  static __device__ __forceinline__ T ldcg(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+  static __device__ __forceinline__ T ld(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void st(float* p, T v) { *reinterpret_cast<float4*>(p) = v; }
+  static __device__ __forceinline__ void red(float* p, T v) { red_add_v4(p, v); }
+  static __device__ __forceinline__ T zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  static __device__ __forceinline__ T fill(float x) { return make_float4(x, x, x, x); }
+  static __device__ __forceinline__ void fma(T& a, float w, T b) {
+    a.x += w * b.x;
+    a.y += w * b.y;
+    a.z += w * b.z;
+    a.w += w * b.w;
+  }
+  static __device__ __forceinline__ T scale(T a, float w) { return make_float4(a.x * w, a.y * w, a.z * w, a.w * w); }
+};
+template <>
+struct Vec<1> {
+  using T = float;
+  static __device__ __forceinline__ T ldcg(const float* p) { return __ldcg(p); }
+  static __device__ __forceinline__ T ld(const float* p) { return *p; }
+  static __device__ __forceinline__ void st(float* p, T v) { *p = v; }
+  static __device__ __forceinline__ void red(float* p, T v) { atomicAdd(p, v); }
+  static __device__ __forceinline__ T zero() { return 0.f; }
+  static __device__ __forceinline__ T fill(float x) { return x; }
+  static __device__ __forceinline__ void fma(T& a, float w, T b) { a += w * b; }
+  static __device__ __forceinline__ T scale(T a, float w) { return a * w; }
+};
+
+// One thread of the block polls each of the `world` flags; the block learns
+// whether all arrived.
+__device__ __forceinline__ bool block_wait_all(const uint32_t* flags, int world, uint32_t want, uint32_t limit) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world && !wait_flag(flags + threadIdx.x, want, limit)) ok = 0;
+  __syncthreads();
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool block_wait_one(const uint32_t* flag, uint32_t want, uint32_t limit) {
+  __shared__ int ok1;
+  if (threadIdx.x == 0) ok1 = wait_flag(flag, want, limit) ? 1 : 0;
+  __syncthreads();
+  const bool r = ok1 != 0;
+  __syncthreads();
+  return r;
+}
+
+// ------------------------------------------------------------------ dedup
+__global__ void __launch_bounds__(kThreads)
+dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, unsigned long long* hkeys,
+                    uint32_t hbits, int* hpos, int* hwin, int* slot_of, int* cnt, int* status) {
+  __shared__ int s_cnt[kMaxWorld];
+  __shared__ int s_base[kMaxWorld];
+  if (threadIdx.x < kMaxWorld) s_cnt[threadIdx.x] = 0;
+  __syncthreads();
+
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  bool won = false;
+  int owner = 0, lpos = 0;
+  uint64_t slot = 0;
+  if (i < n) {
+    uint64_t id = static_cast<uint64_t>(ids[i]);
+    if (id == kEmptyKey) {  // reserved value: reported, then treated as its neighbour
+      set_status(status, err::kBadArgument);
+      id = kEmptyKey - 1;
+    }
+    const uint64_t mask = (1ull << hbits) - 1;
+    slot = SlotHash(id ^ kDedupSalt, hbits);
+    for (uint64_t probe = 0; probe <= mask; ++probe) {
+      const unsigned long long k = __ldcg(&hkeys[slot]);
+      if (k == id) break;
+      if (k == kEmptyKey) {
+        const unsigned long long old = atomicCAS(&hkeys[slot], kEmptyKey, static_cast<unsigned long long>(id));
+        if (old == kEmptyKey) {
+          won = true;
+          break;
+        }
+        if (old == id) break;
+      }
+      slot = (slot + 1) & mask;
+    }
+    slot_of[i] = static_cast<int>(slot);
+    if (won) {
+      owner = static_cast<int>(OwnerOf(salt, id, world));
+      lpos = atomicAdd(&s_cnt[owner], 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < world && s_cnt[threadIdx.x] > 0) s_base[threadIdx.x] = atomicAdd(&cnt[threadIdx.x], s_cnt[threadIdx.x]);
+  __syncthreads();
+  if (won) {
+    hpos[slot] = s_base[owner] + lpos;
+    hwin[slot] = i;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, unsigned long long* hkeys,
+                      const int* __restrict__ hpos, const int* __restrict__ hwin, const int* __restrict__ slot_of,
+                      const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv) {
+  __shared__ int s_off[kMaxWorld + 1];
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int o = 0; o < world; ++o) {
+      s_off[o] = acc;
+      acc += cnt[o];
+    }
+    s_off[world] = acc;
+    if (blockIdx.x == 0)
+      for (int o = 0; o <= world; ++o) off[o] = s_off[o];
+  }
+  __syncthreads();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint64_t id = static_cast<uint64_t>(ids[i]);
+  if (id == kEmptyKey) id = kEmptyKey - 1;
+  const int slot = slot_of[i];
+  const int u = s_off[OwnerOf(salt, id, world)] + hpos[slot];
+  inv[i] = u;
+  if (hwin[slot] == i) {
+    uniq[u] = static_cast<int64_t>(id);
+    hkeys[slot] = kEmptyKey;  // leave the set empty for the next call
+  }
+}
+
+// ------------------------------------------------------------------ pull
+__device__ __forceinline__ int owner_of_index(const int* s_off, int world, int u) {
+  int o = 0;
+  while (o + 1 < world && u >= s_off[o + 1]) ++o;
+  return o;
+}
+
+__global__ void __launch_bounds__(kThreads)
+pull_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int64_t* __restrict__ uniq,
+                     const int* __restrict__ off) {
+  __shared__ int s_off[kMaxWorld + 1];
+  if (threadIdx.x <= sym.world) s_off[threadIdx.x] = off[threadIdx.x];
+  __syncthreads();
+  const int U = s_off[sym.world];
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int gsize = gridDim.x * blockDim.x;
+  for (int u = gtid; u < U; u += gsize) {
+    const int o = owner_of_index(s_off, sym.world, u);
+    const int j = u - s_off[o];
+    if (j < lay.capS) {
+      sym.at<unsigned long long>(o, lay.inbox_ids)[static_cast<size_t>(sym.rank) * lay.capS + j] =
+          static_cast<unsigned long long>(uniq[u]);
+    } else {
+      set_status(&ctrl->status, err::kInboxOverflow);
+    }
+  }
+  if (U > lay.capU && gtid == 0) set_status(&ctrl->status, err::kInboxOverflow);
+  if (gtid < sym.world) {
+    const int o = gtid;
+    int c = s_off[o + 1] - s_off[o];
+    if (c > lay.capS) c = lay.capS;
+    sym.at<int2>(o, lay.inbox_meta)[sym.rank] = make_int2(c, s_off[o]);
+  }
+  if (last_block_done(&ctrl->done[0])) {
+    const uint32_t e = ctrl->pull_epoch + 1;
+    __syncthreads();
+    if (threadIdx.x < sym.world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_req) + sym.rank, e);
+    if (threadIdx.x == 0) ctrl->pull_epoch = e;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+pull_probe_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, int* slot_cache, int insert, uint32_t spin_limit) {
+  const uint32_t epoch = ctrl->pull_epoch;
+  const unsigned long long* inbox = sym.at<unsigned long long>(sym.rank, lay.inbox_ids);
+  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  const uint32_t* flags = sym.at<uint32_t>(sym.rank, lay.flag_req);
+  for (int k = 0; k < sym.world; ++k) {
+    const int s = (sym.rank + k) % sym.world;  // own ids first: they are already here
+    if (sym.world > 1 && !block_wait_one(flags + s, epoch, spin_limit)) {
+      if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
+      return;
+    }
+    const int cnt = __ldcg(&meta[s]).x;
+    for (int base = blockIdx.x * blockDim.x; base < cnt; base += gridDim.x * blockDim.x) {
+      const int j = base + threadIdx.x;
+      bool created = false;
+      if (j < cnt) {
+        const size_t e = static_cast<size_t>(s) * lay.capS + j;
+        const int slot = table_find_or_insert(t, __ldcg(&inbox[e]), insert != 0, &created);
+        if (slot < 0 && !insert) set_status(&ctrl->status, err::kSparseIdNotExist);
+        slot_cache[e] = slot;
+      }
+      count_created(t, created);
+    }
+  }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+pull_gather_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache, int chunks,
+                   int lpr) {
+  using V = Vec<VEC>;
+  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int row0 = gtid / lpr;
+  const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  for (int k = 0; k < sym.world; ++k) {
+    const int s = (sym.rank + k) % sym.world;
+    const int2 m = __ldcg(&meta[s]);
+    float* dst_base = sym.at<float>(s, lay.rows_recv) + static_cast<size_t>(m.y) * t.dim;
+    for (int r = row0; r < m.x; r += row_stride) {
+      const int slot = slot_cache[static_cast<size_t>(s) * lay.capS + r];
+      const float* src = t.val + static_cast<size_t>(slot < 0 ? 0 : slot) * t.dim;
+      float* dst = dst_base + static_cast<size_t>(r) * t.dim;
+      for (int c = lane; c < chunks; c += lpr)
+        V::st(dst + c * VEC, slot < 0 ? V::zero() : V::ld(src + c * VEC));
+    }
+  }
+  if (last_block_done(&ctrl->done[0])) {
+    if (threadIdx.x < sym.world)
+      st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_rsp) + sym.rank, ctrl->pull_epoch);
+  }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+pull_combine_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int* __restrict__ inv, int n, int dim, int chunks,
+                    int lpr, const int64_t* __restrict__ bag_offsets, int nbags, const float* __restrict__ weights,
+                    int mean, const uint8_t* __restrict__ bag_mean, float patch_value, float* __restrict__ out,
+                    uint32_t spin_limit) {
+  using V = Vec<VEC>;
+  if (sym.world > 1 &&
+      !block_wait_all(sym.at<uint32_t>(sym.rank, lay.flag_rsp), sym.world, ctrl->pull_epoch, spin_limit)) {
+    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
+    return;
+  }
+  const float* rows = sym.at<float>(sym.rank, lay.rows_recv);
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int row0 = gtid / lpr;
+  const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  if (bag_offsets == nullptr) {
+    for (int i = row0; i < n; i += row_stride) {
+      const float* src = rows + static_cast<size_t>(inv[i]) * dim;
+      float* dst = out + static_cast<size_t>(i) * dim;
+      for (int c = lane; c < chunks; c += lpr) V::st(dst + c * VEC, V::ldcg(src + c * VEC));
+    }
+  } else {
+    for (int b = row0; b < nbags; b += row_stride) {
+      const int64_t lo = bag_offsets[b], hi = bag_offsets[b + 1];
+      float* dst = out + static_cast<size_t>(b) * dim;
+      const bool is_mean = bag_mean ? bag_mean[b] != 0 : mean != 0;
+      for (int c = lane; c < chunks; c += lpr) {
+        typename V::T acc = V::zero();
+        for (int64_t r = lo; r < hi; ++r)
+          V::fma(acc, weights ? weights[r] : 1.f, V::ldcg(rows + static_cast<size_t>(inv[r]) * dim + c * VEC));
+        if (hi <= lo)
+          acc = V::fill(patch_value);
+        else if (is_mean)
+          acc = V::scale(acc, 1.f / static_cast<float>(hi - lo));
+        V::st(dst + c * VEC, acc);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ push
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+push_scatter_kernel(const float* __restrict__ grads, const int* __restrict__ inv, int n, int dim, int chunks, int lpr,
+                    const int64_t* __restrict__ bag_offsets, int nbags, const float* __restrict__ weights, int mean,
+                    const uint8_t* __restrict__ bag_mean, float* ugrad) {
+  using V = Vec<VEC>;
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int row0 = gtid / lpr;
+  const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  if (bag_offsets == nullptr) {
+    for (int i = row0; i < n; i += row_stride) {
+      const float* src = grads + static_cast<size_t>(i) * dim;
+      float* dst = ugrad + static_cast<size_t>(inv[i]) * dim;
+      for (int c = lane; c < chunks; c += lpr) V::red(dst + c * VEC, V::ld(src + c * VEC));
+    }
+  } else {
+    for (int b = row0; b < nbags; b += row_stride) {
+      const int64_t lo = bag_offsets[b], hi = bag_offsets[b + 1];
+      if (hi <= lo) continue;
+      const bool is_mean = bag_mean ? bag_mean[b] != 0 : mean != 0;
+      const float scale = is_mean ? 1.f / static_cast<float>(hi - lo) : 1.f;
+      const float* src = grads + static_cast<size_t>(b) * dim;
+      for (int c = lane; c < chunks; c += lpr) {
+        const typename V::T g = V::scale(V::ld(src + c * VEC), scale);
+        for (int64_t r = lo; r < hi; ++r)
+          V::red(ugrad + static_cast<size_t>(inv[r]) * dim + c * VEC, weights ? V::scale(g, weights[r]) : g);
+      }
+    }
+  }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+push_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const int* __restrict__ off, int dim,
+                     int chunks, int lpr) {
+  using V = Vec<VEC>;
+  __shared__ int s_off[kMaxWorld + 1];
+  if (threadIdx.x <= sym.world) s_off[threadIdx.x] = off[threadIdx.x];
+  __syncthreads();
+  const int U = s_off[sym.world];
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  for (int u = gtid / lpr; u < U; u += row_stride) {
+    const int o = owner_of_index(s_off, sym.world, u);
+    const int j = u - s_off[o];
+    float* src = ugrad + static_cast<size_t>(u) * dim;
+    float* dst = sym.at<float>(o, lay.inbox_grad) + (static_cast<size_t>(sym.rank) * lay.capS + j) * dim;
+    for (int c = lane; c < chunks; c += lpr) {
+      if (j < lay.capS) V::st(dst + c * VEC, V::ld(src + c * VEC));
+      V::st(src + c * VEC, V::zero());  // ready for the next step's segment-sum
+    }
+  }
+  if (last_block_done(&ctrl->done[1])) {
+    const uint32_t e = ctrl->push_epoch + 1;
+    __syncthreads();
+    if (threadIdx.x < sym.world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_push) + sym.rank, e);
+    if (threadIdx.x == 0) ctrl->push_epoch = e;
+  }
+}
+
+// Owner side, world > 1: several sources may have sent a row for the same
+// slot.  The first entry to claim the slot this epoch becomes its leader and
+// the others add their row into the leader's inbox row.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+push_merge_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache, int chunks,
+                  int lpr, uint32_t spin_limit) {
+  using V = Vec<VEC>;
+  const uint32_t epoch = ctrl->push_epoch;
+  if (!block_wait_all(sym.at<uint32_t>(sym.rank, lay.flag_push), sym.world, epoch, spin_limit)) {
+    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
+    return;
+  }
+  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  float* inbox = sym.at<float>(sym.rank, lay.inbox_grad);
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
+  for (int s = 0; s < sym.world; ++s) {
+    const int cnt = __ldcg(&meta[s]).x;
+    const int rounds = (cnt + row_stride - 1) / row_stride;
+    for (int it = 0; it < rounds; ++it) {
+      const int r = gtid / lpr + it * row_stride;
+      unsigned leader = 0xffffffffu;
+      unsigned entry = 0;
+      if (r < cnt) {
+        entry = static_cast<unsigned>(s) * lay.capS + r;
+        const int slot = slot_cache[entry];
+        if (lane == 0 && slot >= 0) {
+          const unsigned long long mine = (static_cast<unsigned long long>(epoch) << 32) | entry;
+          unsigned long long old = t.lead[slot];
+          while (static_cast<uint32_t>(old >> 32) != epoch) {
+            const unsigned long long prev = atomicCAS(&t.lead[slot], old, mine);
+            if (prev == old) {
+              old = mine;
+              break;
+            }
+            old = prev;
+          }
+          leader = static_cast<unsigned>(old);
+        }
+      }
+      leader = __shfl_sync(group_mask, leader, (threadIdx.x & 31) / lpr * lpr);
+      if (r < cnt && leader != 0xffffffffu && leader != entry) {
+        const float* src = inbox + static_cast<size_t>(entry) * t.dim;
+        float* dst = inbox + static_cast<size_t>(leader) * t.dim;
+        for (int c = lane; c < chunks; c += lpr) V::red(dst + c * VEC, V::ldcg(src + c * VEC));
+      }
+    }
+  }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+push_update_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache,
+                   OptimPOD optim, const float* __restrict__ lr_ptr, int chunks, int lpr) {
+  using V = Vec<VEC>;
+  const uint32_t epoch = ctrl->push_epoch;
+  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  const float* inbox = sym.at<float>(sym.rank, lay.inbox_grad);
+  const float lr = *lr_ptr;
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
+  for (int s = 0; s < sym.world; ++s) {
+    const int cnt = __ldcg(&meta[s]).x;
+    for (int r = gtid / lpr; r < cnt; r += row_stride) {
+      const unsigned entry = static_cast<unsigned>(s) * lay.capS + r;
+      const int slot = slot_cache[entry];
+      if (slot < 0) continue;
+      if (sym.world > 1 && t.lead[slot] != ((static_cast<unsigned long long>(epoch) << 32) | entry)) continue;
+      // Lane 0 of the row owns the step counter: it reads, bumps and shares it.
+      int step_i = 1;
+      if (t.steps) {
+        if (lane == 0) {
+          step_i = t.steps[slot] + 1;
+          t.steps[slot] = step_i;
+        }
+        step_i = __shfl_sync(group_mask, step_i, (threadIdx.x & 31) / lpr * lpr);
+      }
+      const int64_t step = step_i;
+      const AdamBias ab = optim.type == 1 ? AdamBiasAt(optim, step) : AdamBias{1.f, 1.f};
+      const size_t row = static_cast<size_t>(slot) * t.dim;
+      for (int c = lane; c < chunks; c += lpr) {
+        float g[VEC], w[VEC], a0[VEC], a1[VEC], a2[VEC];
+        *reinterpret_cast<typename V::T*>(g) = V::ldcg(inbox + static_cast<size_t>(entry) * t.dim + c * VEC);
+        *reinterpret_cast<typename V::T*>(w) = V::ld(t.val + row + c * VEC);
+        *reinterpret_cast<typename V::T*>(a0) = t.s[0] ? V::ld(t.s[0] + row + c * VEC) : V::zero();
+        *reinterpret_cast<typename V::T*>(a1) = t.s[1] ? V::ld(t.s[1] + row + c * VEC) : V::zero();
+        *reinterpret_cast<typename V::T*>(a2) = t.s[2] ? V::ld(t.s[2] + row + c * VEC) : V::zero();
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) UpdateElem(optim, lr, g[e], step, ab, w[e], a0[e], a1[e], a2[e]);
+        V::st(t.val + row + c * VEC, *reinterpret_cast<typename V::T*>(w));
+        if (t.s[0]) V::st(t.s[0] + row + c * VEC, *reinterpret_cast<typename V::T*>(a0));
+        if (t.s[1]) V::st(t.s[1] + row + c * VEC, *reinterpret_cast<typename V::T*>(a1));
+        if (t.s[2]) V::st(t.s[2] + row + c * VEC, *reinterpret_cast<typename V::T*>(a2));
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ launchers
+void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
+                     int64_t* uniq, int* inv, int* status, cudaStream_t stream) {
+  const int blocks = (n + kThreads - 1) / kThreads;
+  cudaMemsetAsync(cnt, 0, sizeof(int) * world, stream);
+  if (n <= 0) {
+    cudaMemsetAsync(off, 0, sizeof(int) * (world + 1), stream);
+    return;
+  }
+  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys),
+                                                       sc.hbits, sc.hpos, sc.hwin, sc.slot_of, cnt, status);
+  dedup_finalize_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt,
+                                                         static_cast<unsigned long long*>(sc.hkeys), sc.hpos, sc.hwin,
+                                                         sc.slot_of, cnt, off, uniq, inv);
+}
+
+void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,
+                   cudaStream_t stream) {
+  pull_dispatch_kernel<<<grid_for(max_n), kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, uniq, off);
+}
+
+void pull_probe(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, int* slot_cache, bool insert,
+                uint32_t spin_limit, cudaStream_t stream) {
+  pull_probe_kernel<<<grid_for(static_cast<long long>(lay.capS)), kThreads, 0, stream>>>(
+      to_sym(sym), lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0, spin_limit);
+}
+
+void pull_gather(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache,
+                 cudaStream_t stream) {
+  const RowGeom g = row_geom(table.dim);
+  const int grid = grid_for(static_cast<long long>(lay.capS) * g.lpr);
+  if (g.vec == 4)
+    pull_gather_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, to_view(table), slot_cache, g.chunks,
+                                                         g.lpr);
+  else
+    pull_gather_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, to_view(table), slot_cache, g.chunks,
+                                                         g.lpr);
+}
+
+void pull_combine(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int* inv, int n, int dim, const int64_t* bag_offsets,
+                  int k, const float* weights, bool mean, const uint8_t* bag_mean, float patch_value, float* out,
+                  uint32_t spin_limit, cudaStream_t stream) {
+  const RowGeom g = row_geom(dim);
+  const long long rows = bag_offsets ? k : n;
+  const int grid = grid_for(rows * g.lpr);
+  if (g.vec == 4)
+    pull_combine_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
+                                                          bag_offsets, k, weights, mean ? 1 : 0, bag_mean, patch_value,
+                                                          out, spin_limit);
+  else
+    pull_combine_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
+                                                          bag_offsets, k, weights, mean ? 1 : 0, bag_mean, patch_value,
+                                                          out, spin_limit);
+}
+
+void push_scatter(const float* grads, const int* inv, int n, int dim, const int64_t* bag_offsets, int k,
+                  const float* weights, bool mean, const uint8_t* bag_mean, float* ugrad, cudaStream_t stream) {
+  const RowGeom g = row_geom(dim);
+  const long long rows = bag_offsets ? k : n;
+  if (rows <= 0) return;
+  const int grid = grid_for(rows * g.lpr, kThreads, 148 * 16);
+  if (g.vec == 4)
+    push_scatter_kernel<4><<<grid, kThreads, 0, stream>>>(grads, inv, n, dim, g.chunks, g.lpr, bag_offsets, k, weights,
+                                                          mean ? 1 : 0, bag_mean, ugrad);
+  else
+    push_scatter_kernel<1><<<grid, kThreads, 0, stream>>>(grads, inv, n, dim, g.chunks, g.lpr, bag_offsets, k, weights,
+                                                          mean ? 1 : 0, bag_mean, ugrad);
+}
+
+void push_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const int* off, int max_n, int dim,
+                   cudaStream_t stream) {
+  const RowGeom g = row_geom(dim);
+  const int grid = grid_for(static_cast<long long>(max_n) * g.lpr);
+  if (g.vec == 4)
+    push_dispatch_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, ugrad, off, dim, g.chunks, g.lpr);
+  else
+    push_dispatch_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, ugrad, off, dim, g.chunks, g.lpr);
+}
+
+void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache, OptimPOD optim,
+                const float* lr, uint32_t spin_limit, cudaStream_t stream) {
+  const RowGeom g = row_geom(table.dim);
+  const int grid = grid_for(static_cast<long long>(lay.capS) * g.lpr);
+  const Sym s = to_sym(sym);
+  const TableView t = to_view(table);
+  if (g.vec == 4) {
+    if (sym.world > 1)
+      push_merge_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr, spin_limit);
+    push_update_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
+  } else {
+    if (sym.world > 1)
+      push_merge_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr, spin_limit);
+    push_update_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
+  }
+}
+
+}  // namespace cu
+}  // namespace kb

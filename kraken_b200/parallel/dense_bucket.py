@@ -1,0 +1,188 @@
+"""Dense parameter tables on the GPUs: one flat, bucketed buffer.
+
+All dense tables of a model are packed back to back (each starting on a
+256-element boundary) into one fp32 parameter buffer and one gradient buffer
+that live in symmetric memory.  Rank r owns slice r of the flat range together
+with the optimizer state of that slice (ZeRO-1 style); ``step()`` launches the
+fused reduce-scatter + optimizer + all-gather kernel (csrc/cuda/dense.cu).
+
+``param_view`` / ``grad_view`` hand out the tensors that a model's
+``nn.Parameter.data`` / ``.grad`` alias, so the backward pass accumulates
+straight into the exchange buffer and the updated values appear in place: the
+reference's per-table push RPC, server update and per-step pull
+(kraken/pytorch/optimizer.py:141-173) cost no copy here.
+
+With ``emitter_type == kDCT`` the gradient is sparsified per table before it
+crosses NVLink (top ``1 - eta`` by magnitude, threshold refreshed every
+``life_span`` steps, the rest kept as error feedback), as in
+kraken/worker/dct_emitter.cc:16-43.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .._native import C
+from .symm import Layout, SymmetricArena
+from .sparse_shard import DEFAULT_SPIN
+
+CHUNK = 256
+DCT_MIN_SIZE = 256  # tables smaller than this always travel whole (dct_emitter.cc:18-20)
+
+
+class DenseBucket:
+    def __init__(self, tables: Sequence[Tuple[int, int]], optim_type, optim_conf: Dict[str, str], rank: int,
+                 world: int, device: torch.device, group=None, dct: bool = False, life_span: int = 1000,
+                 eta: float = 0.75, spin_limit: int = DEFAULT_SPIN) -> None:
+        """tables: (table_id, numel) in registration order."""
+        self.rank, self.world, self.device, self.group = rank, world, device, group
+        self.optim_info = C.parse_optim(optim_type, optim_conf)
+        self.optim = C.make_optim(optim_type, optim_conf)
+        self.spin = int(spin_limit)
+        self.dct = bool(dct)
+        self.life_span = int(life_span)
+        self.eta = float(eta)
+
+        self.table_ids: List[int] = []
+        self.offsets: Dict[int, Tuple[int, int]] = {}
+        pos = 0
+        chunk_table: List[int] = []
+        for idx, (tid, numel) in enumerate(tables):
+            self.table_ids.append(tid)
+            self.offsets[tid] = (pos, int(numel))
+            nchunks = (int(numel) + CHUNK - 1) // CHUNK
+            chunk_table += [idx] * nchunks
+            pos += nchunks * CHUNK
+        unit = world * CHUNK
+        self.n_pad = max(unit, (pos + unit - 1) // unit * unit)
+        chunk_table += [-1] * (self.n_pad // CHUNK - len(chunk_table))
+        self.slice = self.n_pad // world
+
+        lay = Layout()
+        lay.add("grad", (self.n_pad,), torch.float32)
+        lay.add("param", (self.n_pad,), torch.float32)
+        lay.add("flag_grad", (world,), torch.int32)
+        lay.add("flag_done", (world,), torch.int32)
+        lay.add("coo_cnt", (world,), torch.int32)
+        if self.dct:
+            lay.add("coo_idx", (self.n_pad,), torch.int32)
+            lay.add("coo_val", (self.n_pad,), torch.float32)
+        self.arena = SymmetricArena(lay, rank, world, group)
+        self.lay = C.DenseLayout()
+        for name in lay.entries:
+            setattr(self.lay, name, lay.offset(name))
+        self.bases = [self.arena.heap.peer_ptr(p) for p in range(world)]
+
+        self.grad = self.arena.window("grad")
+        self.param = self.arena.window("param")
+        self.ctrl = torch.zeros(4, dtype=torch.int32, device=device)
+        self.chunk_table = torch.tensor(chunk_table, dtype=torch.int32, device=device)
+        n_tables = max(1, len(self.table_ids))
+        self.table_steps = torch.zeros(n_tables, dtype=torch.int32, device=device)
+        self.table_active = torch.ones(n_tables, dtype=torch.uint8, device=device)
+        self._active_host = [True] * n_tables
+        info = self.optim_info
+        self.state: List[Optional[torch.Tensor]] = []
+        for k in range(3):
+            if info["slabs"][k]:
+                fill = info["initial_accumulator_value"] if (info["type"] == 0 and k == 0) else 0.0
+                self.state.append(torch.full((self.slice,), fill, dtype=torch.float32, device=device))
+            else:
+                self.state.append(None)
+        self.acc = torch.zeros(self.slice, dtype=torch.float32, device=device) if self.dct else None
+        if self.dct:
+            self.residual = torch.zeros(self.n_pad, dtype=torch.float32, device=device)
+            self.tau = torch.zeros(n_tables, dtype=torch.float32, device=device)
+            self.hist = torch.zeros(1024, dtype=torch.int32, device=device)
+            self.prefix = torch.zeros(2, dtype=torch.int32, device=device)
+            self.dct_step = 0
+        self.launches = 0
+
+    # ------------------------------------------------------------------ views
+    def param_view(self, table_id: int, shape: Sequence[int]) -> torch.Tensor:
+        off, numel = self.offsets[table_id]
+        return self.param[off:off + numel].view(*shape)
+
+    def grad_view(self, table_id: int, shape: Sequence[int]) -> torch.Tensor:
+        off, numel = self.offsets[table_id]
+        return self.grad[off:off + numel].view(*shape)
+
+    def set_active(self, active: Sequence[bool]) -> None:
+        active = list(active)
+        if active != self._active_host:
+            self._active_host = active
+            self.table_active.copy_(torch.tensor(active, dtype=torch.uint8))
+
+    # ------------------------------------------------------------------ step
+    def step(self, lr: torch.Tensor, grad_scale: float = 1.0) -> None:
+        """Collective.  Consumes the gradient buffer (zero afterwards) and leaves
+        the updated parameters in every rank's ``param`` buffer."""
+        if self.dct:
+            C.dct_accumulate(self.grad, self.residual)
+            if self.dct_step % self.life_span == 0:
+                for idx, tid in enumerate(self.table_ids):
+                    off, numel = self.offsets[tid]
+                    if numel < DCT_MIN_SIZE:
+                        continue  # tau stays 0: the table travels whole
+                    k = int(numel * (1.0 - self.eta))
+                    if k < 1:
+                        raise C.KrakenError("DCT keeps no element: eta too close to 1")
+                    C.dct_select_tau(self.grad[off:off + numel], k, self.hist, self.prefix, self.tau[idx:idx + 1])
+                    self.launches += 9
+            C.dct_compact(self.bases, self.rank, self.lay, self.n_pad, self.residual, self.tau, self.chunk_table)
+            self.dct_step += 1
+            self.launches += 3
+        C.dense_step(self.bases, self.rank, self.lay, self.ctrl, self.n_pad, self.state[0], self.state[1],
+                     self.state[2], self.acc, self.chunk_table, self.table_steps, self.table_active, self.optim, lr,
+                     float(grad_scale), self.dct, self.spin)
+        self.launches += 1
+
+    def check(self) -> None:
+        code = int(self.ctrl[3].item())
+        if code != 0:
+            self.ctrl[3].zero_()
+            raise C.KrakenError(f"dense step: {C.error_message(code)} (code {code})")
+
+    # ------------------------------------------------------------------ checkpoint
+    def export_table(self, table_id: int, shape: Sequence[int]) -> dict:
+        """Value + optimizer state of one table, gathered from the owning slices (collective)."""
+        off, numel = self.offsets[table_id]
+        out = {"val": self.param[off:off + numel].detach().clone().view(*shape).cpu(), "states": {}, "states_i": {}}
+        idx = self.table_ids.index(table_id)
+        steps = int(self.table_steps[idx].item())
+        if steps > 0:
+            for k in range(3):
+                if self.state[k] is None:
+                    continue
+                full = self._gather_state(k)
+                out["states"][int(self.optim_info["slab_state_types"][k])] = full[off:off + numel].view(*shape).cpu()
+            if self.optim_info["needs_steps"]:
+                out["states_i"][0] = steps
+        return out
+
+    def _gather_state(self, k: int) -> torch.Tensor:
+        if self.world == 1:
+            return self.state[k]
+        import torch.distributed as dist
+
+        parts = [torch.empty_like(self.state[k]) for _ in range(self.world)]
+        dist.all_gather(parts, self.state[k], group=self.group)
+        return torch.cat(parts)
+
+    def import_table(self, table_id: int, value: dict) -> None:
+        off, numel = self.offsets[table_id]
+        self.param[off:off + numel].copy_(value["val"].reshape(-1).to(self.device, torch.float32))
+        lo, hi = self.rank * self.slice, (self.rank + 1) * self.slice
+        a, b = max(off, lo), min(off + numel, hi)
+        for k in range(3):
+            st = int(self.optim_info["slab_state_types"][k])
+            if self.state[k] is None or st not in value.get("states", {}) or a >= b:
+                continue
+            src = value["states"][st].reshape(-1).to(self.device, torch.float32)
+            self.state[k][a - lo:b - lo].copy_(src[a - off:b - off])
+        if 0 in value.get("states_i", {}):
+            self.table_steps[self.table_ids.index(table_id)] = int(value["states_i"][0])
+
+    def close(self) -> None:
+        self.arena.close()

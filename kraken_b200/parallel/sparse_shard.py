@@ -1,0 +1,331 @@
+"""GPU-resident sparse-table shard and its exchange channel.
+
+``GpuSparseTable`` is this rank's part of one sparse table: an open-addressing
+hash table over int64 ids whose slots index structure-of-arrays slabs (values,
+optimizer state, step counters) in HBM.  It replaces the reference server's
+lock-striped skip lists (kraken/ps/sparse_table.h:28,
+kraken/common/parallel_skip_list.h:19-21).
+
+``SparseChannel`` owns the symmetric buffers through which the ranks exchange
+ids, rows and gradients for that table, and drives the fused pull / push kernel
+sequence (csrc/cuda/sparse.cu).  It replaces the client data plane of
+kraken/worker/emitter.cc:123-183 (pull) and :491-550 (push).
+
+Pull and push are collective: every rank of the group must call them in the
+same order, with its own local ids.  Nothing here synchronises the host.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from .._native import C
+from .symm import Layout, SymmetricArena
+
+_EMPTY = -1  # 0xFFFF_FFFF_FFFF_FFFF as int64: the reserved "free slot" key
+DEFAULT_SPIN = 1 << 22
+
+
+def _next_pow2_bits(n: int) -> int:
+    return max(4, int(math.ceil(math.log2(max(2, n)))))
+
+
+class GpuSparseTable:
+    """One rank's shard of a sparse table."""
+
+    def __init__(self, table_id: int, name: str, dim: int, init_type, init_conf: Dict[str, str], optim_type,
+                 optim_conf: Dict[str, str], seed: int, capacity: int, world: int, device: torch.device) -> None:
+        self.table_id = table_id
+        self.name = name
+        self.dim = int(dim)
+        self.init_type = init_type
+        self.init_conf = dict(init_conf)
+        self.optim_type = optim_type
+        self.optim_conf = dict(optim_conf)
+        self.optim_info = C.parse_optim(optim_type, optim_conf)
+        self.optim = C.make_optim(optim_type, optim_conf)
+        self.init = C.parse_init(init_type, init_conf)
+        self.seed_key = C.seed_key(seed, table_id)
+        self.world = world
+        self.device = device
+        self.bits = _next_pow2_bits(capacity)
+        self.size = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._size_host = torch.zeros(1, dtype=torch.int32).pin_memory() if device.type == "cuda" else None
+        self._size_event: Optional[torch.cuda.Event] = None
+        self._alloc(self.bits)
+
+    # ------------------------------------------------------------------ storage
+    def _alloc(self, bits: int) -> None:
+        cap = 1 << bits
+        dev = self.device
+        info = self.optim_info
+        self.bits = bits
+        self.keys = torch.full((cap,), _EMPTY, dtype=torch.int64, device=dev)
+        self.val = torch.zeros((cap, self.dim), dtype=torch.float32, device=dev)
+        self.slabs = []
+        for k in range(3):
+            if info["slabs"][k]:
+                fill = info["initial_accumulator_value"] if (info["type"] == 0 and k == 0) else 0.0
+                self.slabs.append(torch.full((cap, self.dim), fill, dtype=torch.float32, device=dev))
+            else:
+                self.slabs.append(None)
+        self.steps = torch.zeros(cap, dtype=torch.int32, device=dev) if info["needs_steps"] else None
+        self.lead = torch.zeros(cap, dtype=torch.int64, device=dev) if self.world > 1 else None
+        self._host = C.make_table(self.keys, self.val, self.slabs[0], self.slabs[1], self.slabs[2], self.steps,
+                                  self.lead, self.size, self.status, bits, self.dim, self.init[0], self.init[1],
+                                  self.init[2], self.seed_key)
+
+    @property
+    def capacity(self) -> int:
+        return 1 << self.bits
+
+    def host(self):
+        return self._host
+
+    # ------------------------------------------------------------------ maintenance
+    def num_rows(self) -> int:
+        """Occupied slots (synchronises)."""
+        return int(self.size.item())
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise C.KrakenError(f"table {self.name!r}: {C.error_message(code)} (code {code})")
+
+    def export(self, filter_mode: int = 0, salt: int = 0, world: int = 1, rank: int = 0, min_steps: int = 0):
+        """Copies the rows that pass the filter out of the table.
+
+        filter_mode 0 = all rows, 1 = rows owned by ``rank`` under a modulo-``world``
+        placement, 2 = rows NOT owned by it, 3 = rows updated at least ``min_steps`` times.
+        Returns a dict of device tensors: ids [n], vals [n, dim], states {StateType: [n, dim]},
+        states_i {0: steps [n]}.
+        """
+        count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        C.table_export(self._host, filter_mode, salt, world, rank, min_steps, None, None, None, None, None, None, count)
+        n = int(count.item())
+        dev = self.device
+        ids = torch.empty(n, dtype=torch.int64, device=dev)
+        vals = torch.empty((n, self.dim), dtype=torch.float32, device=dev)
+        souts = [torch.empty((n, self.dim), dtype=torch.float32, device=dev) if s is not None else None
+                 for s in self.slabs]
+        steps = torch.empty(n, dtype=torch.int32, device=dev) if self.steps is not None else None
+        if n > 0:
+            C.table_export(self._host, filter_mode, salt, world, rank, min_steps, ids, vals, souts[0], souts[1],
+                           souts[2], steps, count)
+        states = {}
+        for k in range(3):
+            if souts[k] is not None:
+                states[int(self.optim_info["slab_state_types"][k])] = souts[k]
+        states_i = {0: steps.to(torch.int64)} if steps is not None else {}
+        return {"dim": self.dim, "ids": ids, "vals": vals, "states": states, "states_i": states_i}
+
+    def import_rows(self, ids: torch.Tensor, vals: torch.Tensor, states: Optional[dict] = None,
+                    states_i: Optional[dict] = None) -> None:
+        """Inserts (or overwrites) rows with the given values and optimizer state."""
+        n = int(ids.numel())
+        if n == 0:
+            return
+        self.reserve(self.num_rows() + n)
+        dev = self.device
+        ids = ids.to(dev, torch.int64).contiguous()
+        vals = vals.to(dev, torch.float32).contiguous()
+        sl = [None, None, None]
+        for k in range(3):
+            st = int(self.optim_info["slab_state_types"][k])
+            if self.slabs[k] is not None and states and st in states:
+                sl[k] = states[st].to(dev, torch.float32).contiguous()
+        steps = None
+        if self.steps is not None and states_i and 0 in states_i:
+            steps = states_i[0].to(dev, torch.int32).contiguous()
+        C.table_import(self._host, ids, vals, sl[0], sl[1], sl[2], steps)
+
+    def reserve(self, rows: int, max_load: float = 0.6) -> bool:
+        """Grows (rehashes) so that ``rows`` rows stay below ``max_load``; True if it grew."""
+        need_bits = _next_pow2_bits(int(rows / max_load) + 1)
+        if need_bits <= self.bits:
+            return False
+        old = self.export()
+        self.size.zero_()
+        self._alloc(need_bits)
+        C.table_import(self._host, old["ids"], old["vals"],
+                       *[old["states"].get(int(self.optim_info["slab_state_types"][k])) if self.slabs[k] is not None
+                         else None for k in range(3)],
+                       old["states_i"][0].to(torch.int32) if self.steps is not None else None)
+        return True
+
+    def poll_growth(self, max_load: float = 0.6) -> bool:
+        """Non-blocking load-factor check: looks at the size counter copied out
+        during the previous call and starts the next copy.  Call between steps."""
+        grew = False
+        if self._size_host is not None:
+            if self._size_event is not None and self._size_event.query():
+                rows = int(self._size_host[0])
+                if rows > max_load * self.capacity:
+                    grew = self.reserve(int(rows * 2))
+                self._size_event = None
+            if self._size_event is None:
+                self._size_host.copy_(self.size, non_blocking=True)
+                self._size_event = torch.cuda.Event()
+                self._size_event.record()
+        return grew
+
+    def evict(self, min_steps: int) -> int:
+        """Drops the rows updated fewer than ``min_steps`` times by rebuilding the
+        table from the survivors; returns how many rows were dropped."""
+        before = self.num_rows()
+        keep = self.export(filter_mode=3, min_steps=min_steps)
+        C.table_clear(self._host)
+        self.val.zero_()
+        for k, s in enumerate(self.slabs):
+            if s is not None:
+                s.fill_(self.optim_info["initial_accumulator_value"] if (self.optim_info["type"] == 0 and k == 0)
+                        else 0.0)
+        self.import_rows(keep["ids"], keep["vals"], keep["states"], keep["states_i"])
+        return before - int(keep["ids"].numel())
+
+    def lookup(self, ids: torch.Tensor):
+        """(rows [n, dim], found [n]) for ids on this shard, without inserting."""
+        return C.table_lookup(self._host, ids.to(self.device, torch.int64).contiguous())
+
+
+class Ticket:
+    """Identifies one pull so that the matching push can reuse its dedup result
+    and the slots the owners resolved."""
+
+    __slots__ = ("channel", "serial", "n", "bag_offsets", "weights", "mean", "bag_mean")
+
+    def __init__(self, channel, serial, n, bag_offsets, weights, mean, bag_mean):
+        self.channel = channel
+        self.serial = serial
+        self.n = n
+        self.bag_offsets = bag_offsets
+        self.weights = weights
+        self.mean = mean
+        self.bag_mean = bag_mean
+
+
+class SparseChannel:
+    """Exchange buffers + kernel sequence of one table."""
+
+    def __init__(self, table: GpuSparseTable, rank: int, world: int, max_ids: int, group=None,
+                 spin_limit: int = DEFAULT_SPIN, owner_salt: int = 0) -> None:
+        self.table = table
+        self.rank = rank
+        self.world = world
+        self.group = group
+        self.spin = int(spin_limit)
+        self.salt = int(owner_salt)
+        self.cap = int(max_ids)
+        dim = table.dim
+        dev = table.device
+
+        lay = Layout()
+        lay.add("inbox_ids", (world, self.cap), torch.int64)
+        lay.add("inbox_meta", (world, 2), torch.int32)
+        lay.add("rows_recv", (self.cap, dim), torch.float32)
+        lay.add("inbox_grad", (world, self.cap, dim), torch.float32)
+        lay.add("flag_req", (world,), torch.int32)
+        lay.add("flag_rsp", (world,), torch.int32)
+        lay.add("flag_push", (world,), torch.int32)
+        self.arena = SymmetricArena(lay, rank, world, group)
+        self.lay = C.ChanLayout()
+        for name in ("inbox_ids", "inbox_meta", "rows_recv", "inbox_grad", "flag_req", "flag_rsp", "flag_push"):
+            setattr(self.lay, name, lay.offset(name))
+        self.lay.capS = self.cap
+        self.lay.capU = self.cap
+
+        self.ctrl = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.hbits = _next_pow2_bits(2 * self.cap)
+        self.hkeys = torch.full((1 << self.hbits,), _EMPTY, dtype=torch.int64, device=dev)
+        self.hpos = torch.zeros(1 << self.hbits, dtype=torch.int32, device=dev)
+        self.hwin = torch.zeros(1 << self.hbits, dtype=torch.int32, device=dev)
+        self.slot_of = torch.zeros(self.cap, dtype=torch.int32, device=dev)
+        self.cnt = torch.zeros(world, dtype=torch.int32, device=dev)
+        self.off = torch.zeros(world + 1, dtype=torch.int32, device=dev)
+        self.uniq = torch.zeros(self.cap, dtype=torch.int64, device=dev)
+        self.inv = torch.zeros(self.cap, dtype=torch.int32, device=dev)
+        self.slot_cache = torch.full((world * self.cap,), -1, dtype=torch.int32, device=dev)
+        self.ugrad = torch.zeros((self.cap, dim), dtype=torch.float32, device=dev)
+        self.serial = 0
+        self.launches = 0  # kernels launched through this channel (for accounting)
+
+    # ------------------------------------------------------------------ helpers
+    def _lookup_phase(self, ids: torch.Tensor, insert: bool) -> int:
+        n = int(ids.numel())
+        if n > self.cap:
+            raise C.KrakenError(f"table {self.table.name!r}: {n} ids in one call exceed the channel capacity "
+                                f"{self.cap}; raise max_ids_per_call")
+        h, lay, ctrl, tbl = self.arena.heap, self.lay, self.ctrl, self.table.host()
+        C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.hpos, self.hwin, self.slot_of, self.hbits,
+                          self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5])
+        C.pull_dispatch(h, lay, ctrl, self.uniq, self.off, n)
+        C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)
+        self.launches += 4 if n > 0 else 2
+        self.serial += 1
+        return n
+
+    # ------------------------------------------------------------------ pull
+    def pull(self, ids: torch.Tensor, bag_offsets: Optional[torch.Tensor] = None,
+             weights: Optional[torch.Tensor] = None, mean: bool = False, bag_mean: Optional[torch.Tensor] = None,
+             patch_value: float = 0.0, out: Optional[torch.Tensor] = None):
+        """Looks up (inserting unseen ids) and returns (rows, ticket).
+
+        Without ``bag_offsets`` rows is [n, dim], one per id.  With ``bag_offsets``
+        ([k + 1], int64) rows is [k, dim]: each bag's rows pooled by sum, or mean
+        where ``mean`` / ``bag_mean[b]`` says so; empty bags give ``patch_value``.
+        """
+        ids = ids.reshape(-1)
+        n = self._lookup_phase(ids, insert=True)
+        h, lay, ctrl, tbl = self.arena.heap, self.lay, self.ctrl, self.table.host()
+        dim = self.table.dim
+        C.pull_gather(h, lay, ctrl, tbl, self.slot_cache)
+        rows = (int(bag_offsets.numel()) - 1) if bag_offsets is not None else n
+        if out is None:
+            out = torch.empty((rows, dim), dtype=torch.float32, device=self.table.device)
+        C.pull_combine(h, lay, ctrl, self.inv, n, dim, bag_offsets, weights, mean, bag_mean, patch_value, out,
+                       self.spin)
+        self.launches += 2
+        return out, Ticket(self, self.serial, n, bag_offsets, weights, mean, bag_mean)
+
+    # ------------------------------------------------------------------ push
+    def push(self, grads: torch.Tensor, lr: torch.Tensor, ticket: Optional[Ticket] = None,
+             ids: Optional[torch.Tensor] = None, bag_offsets: Optional[torch.Tensor] = None,
+             weights: Optional[torch.Tensor] = None, mean: bool = False,
+             bag_mean: Optional[torch.Tensor] = None) -> None:
+        """Sums the gradients of duplicate ids, sends them to the owners and runs
+        the optimizer there.  With the ticket of the latest pull of this channel
+        the dedup result and the owners' slots are reused; otherwise ``ids`` are
+        looked up again (an id the table does not hold is kSparseIdNotExist)."""
+        if ticket is not None and ticket.channel is self and ticket.serial == self.serial:
+            n = ticket.n
+            bag_offsets, weights, mean, bag_mean = ticket.bag_offsets, ticket.weights, ticket.mean, ticket.bag_mean
+        else:
+            if ids is None:
+                raise C.KrakenError("push without a current ticket needs the ids")
+            n = self._lookup_phase(ids.reshape(-1), insert=False)
+        h, lay, ctrl, tbl = self.arena.heap, self.lay, self.ctrl, self.table.host()
+        dim = self.table.dim
+        grads = grads.reshape(-1, dim)
+        if grads.dtype != torch.float32 or not grads.is_contiguous():
+            grads = grads.to(torch.float32).contiguous()
+        C.push_scatter(grads, self.inv, n, dim, bag_offsets, weights, mean, bag_mean, self.ugrad)
+        C.push_dispatch(h, lay, ctrl, self.ugrad, self.off, n, dim)
+        C.push_apply(h, lay, ctrl, tbl, self.slot_cache, self.table.optim, lr, self.spin)
+        self.launches += 3 + (1 if self.world > 1 else 0)
+        # A push consumes the pull's bookkeeping: a second push needs a new lookup.
+        self.serial += 1
+
+    # ------------------------------------------------------------------ status
+    def check(self) -> None:
+        code = int(self.ctrl[4].item())
+        if code != 0:
+            self.ctrl[4].zero_()
+            raise C.KrakenError(f"channel of table {self.table.name!r}: {C.error_message(code)} (code {code})")
+        self.table.check()
+
+    def close(self) -> None:
+        self.arena.close()
