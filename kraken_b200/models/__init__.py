@@ -1,0 +1,3 @@
+from .deepfm import DeepFM
+from .mlp import MLP
+from .synthetic import ClickDataset

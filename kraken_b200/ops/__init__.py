@@ -1,0 +1,1 @@
+from .functional import bce_with_logits, fm_interaction

@@ -1,0 +1,262 @@
+"""GPU engine: every rank is a worker and a shard on its own B200.
+
+Sparse tables are ``GpuSparseTable`` shards exchanged through ``SparseChannel``
+(fused pull / push kernels over peer memory); dense tables live in one
+``DenseBucket`` whose fused step replaces push + server update + pull.  No call
+here synchronises the host: errors are collected from device status words by
+``check()`` / ``end_step()``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .._native import C
+from ..parallel.dense_bucket import DenseBucket
+from ..parallel.sparse_shard import GpuSparseTable, SparseChannel, Ticket
+from .engine import Engine, EngineConfig, TableInfo
+
+
+class GpuEngine(Engine):
+    def __init__(self, cfg: EngineConfig, rank: int = 0, world: int = 1, group=None,
+                 device: Optional[torch.device] = None) -> None:
+        super().__init__(cfg, rank, world, group)
+        if not torch.cuda.is_available():
+            raise RuntimeError("the GPU engine needs a CUDA device")
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        torch.cuda.set_device(self.device)
+        self.lr_dev = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._lr_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+        self.sparse: Dict[int, GpuSparseTable] = {}
+        self.channels: Dict[int, SparseChannel] = {}
+        self.tickets: Dict[int, Tuple[Ticket, int, int, int]] = {}
+        self.dense_init: Dict[int, torch.Tensor] = {}
+        self.bucket: Optional[DenseBucket] = None
+        self._dense_pending = False
+        self._pushed: set = set()
+        self._bound = False
+        self._steps = 0
+
+    # ------------------------------------------------------------------ registry hooks
+    def _on_update_lr(self) -> None:
+        if float(self._lr_host[0]) != self.lr or self._steps == 0:
+            self._lr_host[0] = self.lr
+            self.lr_dev.copy_(self._lr_host, non_blocking=True)
+
+    def _on_register_dense(self, info: TableInfo, val: torch.Tensor) -> None:
+        v = val.detach().to(self.device, torch.float32).contiguous().clone()
+        if self.world > 1:
+            dist.broadcast(v, src=0, group=self.group)
+        self.dense_init[info.id] = v
+        if self.bucket is not None:
+            self._rebuild_bucket()
+
+    def _on_register_sparse(self, info: TableInfo) -> None:
+        self.sparse[info.id] = GpuSparseTable(info.id, info.name, info.dimension, info.init_type, info.init_conf,
+                                              self.optim_type, self.optim_conf, self.cfg.seed,
+                                              self.cfg.table_capacity, self.world, self.device)
+
+    def _salt(self, table_id: int) -> int:
+        return C.table_salt(table_id) if self.cfg.owner_salt_per_table else 0
+
+    # ------------------------------------------------------------------ dense
+    def _dense_ids(self) -> List[int]:
+        return [tid for tid, t in self.tables.items() if t.kind == "dense"]
+
+    def _build_bucket(self) -> None:
+        ids = self._dense_ids()
+        tables = [(tid, int(self.dense_init[tid].numel())) for tid in ids]
+        self.bucket = DenseBucket(tables, self.optim_type, self.optim_conf, self.rank, self.world, self.device,
+                                  self.group, dct=self.cfg.emitter_type == C.EmitterType.kDCT,
+                                  life_span=self.cfg.life_span, eta=self.cfg.eta, spin_limit=self.cfg.spin_limit)
+        for tid in ids:
+            self.bucket.param_view(tid, self.tables[tid].shape).copy_(self.dense_init[tid].view(*self.tables[tid].shape))
+        if self.world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+
+    def _rebuild_bucket(self) -> None:
+        old = self.bucket
+        for tid in old.table_ids:
+            self.dense_init[tid] = old.param_view(tid, self.tables[tid].shape).detach().clone().reshape(-1)
+        # optimizer state of the old bucket is dropped: tables are registered before training starts
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        old.close()
+        self.bucket = None
+        self._build_bucket()
+
+    def _ensure_bucket(self) -> DenseBucket:
+        if self.bucket is None:
+            self._build_bucket()
+        return self.bucket
+
+    def pull_dense_table(self, table_id: int) -> torch.Tensor:
+        info = self._table(table_id, "dense")
+        b = self._ensure_bucket()
+        self._flush_dense()
+        return b.param_view(table_id, info.shape)
+
+    def combine_pull_dense_table(self, table_ids: Sequence[int]) -> List[torch.Tensor]:
+        if not table_ids:
+            return []
+        b = self._ensure_bucket()
+        self._flush_dense()
+        return [b.param_view(t, self._table(t, "dense").shape) for t in table_ids]
+
+    def push_dense_table(self, table_id: int, grad: torch.Tensor) -> None:
+        info = self._table(table_id, "dense")
+        b = self._ensure_bucket()
+        view = b.grad_view(table_id, info.shape)
+        if grad.data_ptr() != view.data_ptr():
+            view.add_(grad.detach().to(self.device, torch.float32).view(*info.shape))
+        self._pushed.add(table_id)
+        self._dense_pending = True
+
+    def bind_dense_params(self, pairs: Sequence[Tuple[int, torch.nn.Parameter]]) -> None:
+        """Makes each parameter alias the bucket: ``.data`` is the parameter view and
+        ``.grad`` the gradient view, so backward accumulates into the exchange buffer."""
+        b = self._ensure_bucket()
+        for tid, p in pairs:
+            shape = self._table(tid, "dense").shape
+            p.data = b.param_view(tid, shape)
+            p.grad = b.grad_view(tid, shape)
+        self._bound = True
+
+    def dense_step(self) -> None:
+        """One fused optimizer step over every dense table (bound-parameter path)."""
+        b = self._ensure_bucket()
+        b.set_active([True] * len(b.table_ids))
+        b.step(self.lr_dev)
+        self._dense_pending = False
+        self._pushed.clear()
+
+    def _flush_dense(self) -> None:
+        if not self._dense_pending:
+            return
+        b = self.bucket
+        b.set_active([tid in self._pushed for tid in b.table_ids])
+        b.step(self.lr_dev)
+        self._dense_pending = False
+        self._pushed.clear()
+
+    # ------------------------------------------------------------------ sparse
+    def _channel(self, table_id: int, n: int) -> SparseChannel:
+        ch = self.channels.get(table_id)
+        if ch is not None:
+            return ch
+        cap = self.cfg.max_ids_per_call
+        if cap <= 0:
+            cap = max(1024, 2 * n)
+            if self.world > 1:
+                t = torch.tensor([cap], dtype=torch.int64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+                cap = int(t.item())
+        ch = SparseChannel(self.sparse[table_id], self.rank, self.world, cap, self.group, self.cfg.spin_limit,
+                           self._salt(table_id))
+        self.channels[table_id] = ch
+        return ch
+
+    def _prep_ids(self, indices: torch.Tensor) -> torch.Tensor:
+        idx = indices.detach()
+        if idx.device != self.device or idx.dtype != torch.int64:
+            idx = idx.to(self.device, torch.int64, non_blocking=True)
+        return idx.contiguous()
+
+    @staticmethod
+    def _sig(indices: torch.Tensor) -> Tuple[int, int, int]:
+        return (indices.data_ptr(), indices.numel(), indices._version)
+
+    def pull_sparse_table(self, table_id: int, indices: torch.Tensor) -> torch.Tensor:
+        info = self._table(table_id, "sparse")
+        idx = self._prep_ids(indices)
+        ch = self._channel(table_id, idx.numel())
+        rows, ticket = ch.pull(idx)
+        self.tickets[table_id] = (ticket, *self._sig(indices))
+        return rows.view(*indices.shape, info.dimension)
+
+    def pull_sparse_pooled(self, table_id: int, values: torch.Tensor, offsets: torch.Tensor,
+                           weights: Optional[torch.Tensor] = None, mean: bool = False,
+                           bag_mean: Optional[torch.Tensor] = None, patch_value: float = 0.0):
+        """EmbeddingBag in one fused pull: returns (pooled [k, dim], ticket)."""
+        self._table(table_id, "sparse")
+        idx = self._prep_ids(values)
+        off = offsets.detach().to(self.device, torch.int64).contiguous()
+        w = weights.detach().to(self.device, torch.float32).contiguous() if weights is not None else None
+        bm = bag_mean.detach().to(self.device, torch.uint8).contiguous() if bag_mean is not None else None
+        ch = self._channel(table_id, idx.numel())
+        return ch.pull(idx, bag_offsets=off, weights=w, mean=mean, bag_mean=bm, patch_value=patch_value)
+
+    def push_sparse_pooled(self, table_id: int, ticket: Ticket, grads: torch.Tensor,
+                           values: Optional[torch.Tensor] = None) -> None:
+        ch = self.channels[table_id]
+        ids = self._prep_ids(values) if values is not None else None
+        ch.push(grads, self.lr_dev, ticket=ticket, ids=ids, bag_offsets=ticket.bag_offsets, weights=ticket.weights,
+                mean=ticket.mean, bag_mean=ticket.bag_mean)
+
+    def push_sparse_table(self, table_id: int, indices: torch.Tensor, grad: torch.Tensor) -> None:
+        info = self._table(table_id, "sparse")
+        if grad.numel() != indices.numel() * info.dimension:
+            raise C.KrakenError("gradient shape must be indices.shape + [dimension]")
+        saved = self.tickets.pop(table_id, None)
+        ticket = saved[0] if saved is not None and saved[1:] == self._sig(indices) else None
+        idx = None if ticket is not None else self._prep_ids(indices)
+        ch = self._channel(table_id, indices.numel())
+        g = grad.detach()
+        if g.device != self.device:
+            g = g.to(self.device)
+        ch.push(g, self.lr_dev, ticket=ticket, ids=idx)
+
+    # ------------------------------------------------------------------ housekeeping
+    def end_step(self) -> None:
+        self._steps += 1
+        for t in self.sparse.values():
+            t.poll_growth()
+
+    def check(self) -> None:
+        """Raises if any kernel recorded an error (synchronises)."""
+        for ch in self.channels.values():
+            ch.check()
+        for t in self.sparse.values():
+            t.check()
+        if self.bucket is not None:
+            self.bucket.check()
+
+    def kernel_launches(self) -> int:
+        n = sum(ch.launches for ch in self.channels.values())
+        if self.bucket is not None:
+            n += self.bucket.launches
+        return n
+
+    # ------------------------------------------------------------------ checkpoint glue
+    def export_dense(self, table_id: int) -> dict:
+        return self._ensure_bucket().export_table(table_id, self._table(table_id, "dense").shape)
+
+    def import_dense(self, table_id: int, name: str, value: dict) -> None:
+        self._ensure_bucket().import_table(table_id, value)
+
+    def dense_owner(self, table_id: int) -> int:
+        return table_id % self.world
+
+    def export_sparse(self, table_id: int) -> dict:
+        return self.sparse[table_id].export()
+
+    def import_sparse(self, table_id: int, cols: dict) -> None:
+        self.sparse[table_id].import_rows(cols["ids"], cols["vals"], cols["states"], cols["states_i"])
+
+    def stop(self) -> None:
+        if self.stopped:
+            return
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for ch in self.channels.values():
+            ch.close()
+        if self.bucket is not None:
+            self.bucket.close()
+        self.channels.clear()
+        self.bucket = None
+        super().stop()

