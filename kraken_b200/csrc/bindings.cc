@@ -215,11 +215,13 @@ struct SymHeap {
   std::vector<void*> bases;
   std::vector<bool> opened;
 
-  SymHeap(size_t nbytes, int r, int w) : bytes(nbytes), rank(r), world(w) {
+  // alias_peers: every peer pointer is the local arena.  Lets one GPU run the multi-rank kernels
+  // against itself (peers that never answer), which is how the bounded waits are tested.
+  SymHeap(size_t nbytes, int r, int w, bool alias_peers) : bytes(nbytes), rank(r), world(w) {
     TORCH_CHECK(w >= 1 && w <= cu::kMaxWorldHost, "world size must be 1..16");
     CUDA_OK(cudaMalloc(&local, nbytes));
     CUDA_OK(cudaMemset(local, 0, nbytes));
-    bases.assign(w, nullptr);
+    bases.assign(w, alias_peers ? local : nullptr);
     opened.assign(w, false);
     bases[r] = local;
   }
@@ -746,7 +748,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   // ---------------- symmetric heap + device structs
   py::class_<SymHeap>(m, "SymHeap")
-      .def(py::init<size_t, int, int>(), py::arg("bytes"), py::arg("rank"), py::arg("world"))
+      .def(py::init<size_t, int, int, bool>(), py::arg("bytes"), py::arg("rank"), py::arg("world"),
+           py::arg("alias_peers") = false)
       .def("handle", &SymHeap::Handle)
       .def("open", &SymHeap::Open)
       .def("close", &SymHeap::Close)

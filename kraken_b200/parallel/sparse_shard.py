@@ -212,7 +212,7 @@ class SparseChannel:
     """Exchange buffers + kernel sequence of one table."""
 
     def __init__(self, table: GpuSparseTable, rank: int, world: int, max_ids: int, group=None,
-                 spin_limit: int = DEFAULT_SPIN, owner_salt: int = 0) -> None:
+                 spin_limit: int = DEFAULT_SPIN, owner_salt: int = 0, alias_peers: bool = False) -> None:
         self.table = table
         self.rank = rank
         self.world = world
@@ -231,7 +231,7 @@ class SparseChannel:
         lay.add("flag_req", (world,), torch.int32)
         lay.add("flag_rsp", (world,), torch.int32)
         lay.add("flag_push", (world,), torch.int32)
-        self.arena = SymmetricArena(lay, rank, world, group)
+        self.arena = SymmetricArena(lay, rank, world, group, alias_peers)
         self.lay = C.ChanLayout()
         for name in ("inbox_ids", "inbox_meta", "rows_recv", "inbox_grad", "flag_req", "flag_rsp", "flag_push"):
             setattr(self.lay, name, lay.offset(name))

@@ -45,12 +45,15 @@ class Layout:
 class SymmetricArena:
     """One arena per rank, mapped into every rank of ``group``."""
 
-    def __init__(self, layout: Layout, rank: int, world: int, group=None) -> None:
+    def __init__(self, layout: Layout, rank: int, world: int, group=None, alias_peers: bool = False) -> None:
+        """alias_peers=True maps every "peer" to the local arena instead of exchanging
+        handles: one GPU then runs the multi-rank kernels against peers that never
+        answer (used to test the bounded device-side waits)."""
         self.layout = layout
         self.rank = rank
         self.world = world
-        self.heap = C.SymHeap(max(layout.size, _ALIGN), rank, world)
-        if world > 1:
+        self.heap = C.SymHeap(max(layout.size, _ALIGN), rank, world, alias_peers)
+        if world > 1 and not alias_peers:
             handles: List[bytes] = [b""] * world
             dist.all_gather_object(handles, self.heap.handle(), group=group)
             self.heap.open(handles)
