@@ -4,6 +4,7 @@
 #include <torch/extension.h>
 
 #include "cuda/dense_kernels.h"
+#include "cuda/mlp_gemm.h"
 
 namespace py = pybind11;
 using namespace kb;
@@ -87,5 +88,64 @@ void bind_dense(py::module_& m) {
     cu::dct_threshold_dense(grad.data_ptr<float>(), residual.data_ptr<float>(), grad.numel(), tau.data_ptr<float>(),
                             chunk_table.data_ptr<int>(), cur_stream());
     check_launch("dct_threshold_dense");
+  });
+
+  // ---------------- tcgen05 Linear layers (bf16 in, fp32 accumulate)
+  auto bf = [](const torch::Tensor& t) { return reinterpret_cast<const __nv_bfloat16*>(t.data_ptr()); };
+  auto need_bf16 = [](const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.stride(1) == 1, name,
+                " must be a 2-D CUDA bf16 tensor with unit inner stride");
+  };
+  m.def("linear_forward", [bf, need_bf16](const torch::Tensor& x, const torch::Tensor& w,
+                                          const c10::optional<torch::Tensor>& bias, bool relu, const torch::Tensor& y,
+                                          const torch::Tensor& status) {
+    need_bf16(x, "x");
+    need_bf16(w, "w");
+    need_bf16(y, "y");
+    const int M = x.size(0), K = x.size(1), N = w.size(0);
+    TORCH_CHECK(w.size(1) == K && y.size(0) == M && y.size(1) == N, "linear_forward: shape mismatch");
+    const int rc = cu::linear_forward(bf(x), x.stride(0), bf(w), w.stride(0), optr<float>(bias),
+                                      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), y.stride(0), M, N, K, relu,
+                                      status.data_ptr<int>(), cur_stream());
+    TORCH_CHECK(rc == 0, "linear_forward: cannot encode the TMA descriptors (pitches must be multiples of 8)");
+  });
+  m.def("linear_dgrad", [bf, need_bf16](const torch::Tensor& dy, const torch::Tensor& wt,
+                                        const c10::optional<torch::Tensor>& h, const torch::Tensor& dx,
+                                        const torch::Tensor& status) {
+    need_bf16(dy, "dy");
+    need_bf16(wt, "wt");
+    need_bf16(dx, "dx");
+    const int M = dy.size(0), N = dy.size(1), K = wt.size(0);
+    TORCH_CHECK(wt.size(1) == N && dx.size(0) == M && dx.size(1) == K, "linear_dgrad: shape mismatch");
+    const __nv_bfloat16* hp = nullptr;
+    int ldh = 0;
+    if (h.has_value()) {
+      need_bf16(*h, "h");
+      TORCH_CHECK(h->size(0) == M && h->size(1) == K, "linear_dgrad: mask shape mismatch");
+      hp = bf(*h);
+      ldh = h->stride(0);
+    }
+    const int rc = cu::linear_dgrad(bf(dy), dy.stride(0), bf(wt), wt.stride(0), hp, ldh,
+                                    reinterpret_cast<__nv_bfloat16*>(dx.data_ptr()), dx.stride(0), M, N, K,
+                                    status.data_ptr<int>(), cur_stream());
+    TORCH_CHECK(rc == 0, "linear_dgrad: cannot encode the TMA descriptors (pitches must be multiples of 8)");
+  });
+  m.def("linear_wgrad", [bf, need_bf16](const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& dw,
+                                        const torch::Tensor& status) {
+    need_bf16(dy, "dy");
+    need_bf16(x, "x");
+    TORCH_CHECK(dw.is_cuda() && dw.scalar_type() == torch::kFloat32 && dw.dim() == 2 && dw.stride(1) == 1,
+                "dw must be a 2-D CUDA f32 tensor");
+    const int M = dy.size(0), N = dy.size(1), K = x.size(1);
+    TORCH_CHECK(x.size(0) == M && dw.size(0) == N && dw.size(1) == K, "linear_wgrad: shape mismatch");
+    const int rc = cu::linear_wgrad(bf(dy), dy.stride(0), bf(x), x.stride(0), dw.data_ptr<float>(), dw.stride(0), M,
+                                    N, K, status.data_ptr<int>(), cur_stream());
+    TORCH_CHECK(rc == 0, "linear_wgrad: cannot encode the TMA descriptors (pitches must be multiples of 8)");
+  });
+  m.def("colsum_bf16", [bf, need_bf16](const torch::Tensor& dy, const torch::Tensor& db) {
+    need_bf16(dy, "dy");
+    TORCH_CHECK(db.is_cuda() && db.scalar_type() == torch::kFloat32 && db.numel() >= dy.size(1), "db too small");
+    cu::colsum_bf16(bf(dy), dy.stride(0), dy.size(0), dy.size(1), db.data_ptr<float>(), cur_stream());
+    check_launch("colsum_bf16");
   });
 }

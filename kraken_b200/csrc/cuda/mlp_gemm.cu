@@ -1,0 +1,387 @@
+// tcgen05 GEMM kernel behind linear_forward / linear_dgrad / linear_wgrad.
+//
+// One CTA computes one 128 x BN output tile:
+//   warp 0 (one lane)  TMA producer: fills a ring of shared-memory stages with 128-byte-swizzled
+//                      A and B tiles of 64 k-elements, one mbarrier per stage counting bytes;
+//   warp 1 (one lane)  MMA issuer: four tcgen05.mma (K = 16 each) per stage into a TMEM
+//                      accumulator, tcgen05.commit frees the stage and finally signals the epilogue;
+//   warps 2-5          epilogue: tcgen05.ld the accumulator (one row per thread) and fuse
+//                      bias + ReLU (forward), the ReLU mask (input gradient) or a split-K
+//                      vector red.add into the fp32 gradient buffer (weight gradient).
+// Operands are K-major except in the weight gradient, which contracts over the batch and
+// therefore reads both activations MN-major, as they sit in memory.
+// Every mbarrier wait is bounded; on a give-up the CTA records kTimeout, lets its outstanding
+// TMA copies land, frees its tensor memory and returns.
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "../core/types.h"
+#include "mlp_gemm.h"
+#include "tcgen05.cuh"
+
+namespace kb {
+namespace cu {
+
+namespace {
+
+constexpr int kBM = 128;         // rows of the output tile = TMEM lanes
+constexpr int kBK = 64;          // k-elements per stage = one 128-byte swizzle atom of bf16
+constexpr int kThreads = 192;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int kMaxStages = 4;
+
+enum { EPI_BIAS_ACT = 0, EPI_RELU_MASK = 1, EPI_RED_F32 = 2 };
+
+struct GemmArgs {
+  int M, N, K;            // output is M x N, contraction length K
+  int BN;                 // tile width (multiple of 16; of 64 when B is MN-major)
+  int stages;
+  int kb_per_split;       // k-blocks per blockIdx.z
+  int relu;
+  const float* bias;      // [N]            (EPI_BIAS_ACT)
+  const __nv_bfloat16* H; // [M, ldh]       (EPI_RELU_MASK)
+  int ldh;
+  __nv_bfloat16* out;     // [M, ldo] bf16  (EPI_BIAS_ACT, EPI_RELU_MASK)
+  int ldo;
+  float* out32;           // [M, ldo32] f32 (EPI_RED_F32)
+  int ldo32;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(kThreads)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t a_bytes = kBM * 128;
+  const uint32_t b_bytes = static_cast<uint32_t>(g.BN) * 128;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+
+  __shared__ uint64_t full_bar[kMaxStages];
+  __shared__ uint64_t empty_bar[kMaxStages];
+  __shared__ uint64_t acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * kBM;
+  const int n0 = blockIdx.y * g.BN;
+  const int total_kb = (g.K + kBK - 1) / kBK;
+  const int kb_begin = blockIdx.z * g.kb_per_split;
+  const int kb_end = min(total_kb, kb_begin + g.kb_per_split);
+  const int num_kb = max(0, kb_end - kb_begin);
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < static_cast<uint32_t>(g.BN)) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < g.stages; ++s) {
+      tc::mbar_init(&full_bar[s], 1);
+      tc::mbar_init(&empty_bar[s], 1);
+    }
+    tc::mbar_init(&acc_bar, 1);
+    abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tmap(&tmA);
+    tc::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tc::tmem_alloc(&tmem_slot, tmem_cols);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; ++i) {
+      const int s = i % g.stages;
+      const uint32_t round = static_cast<uint32_t>(i / g.stages);
+      if (round > 0) ok = tc::mbar_wait(&empty_bar[s], (round - 1) & 1, kWaitLimit);
+      if (!ok) break;
+      uint8_t* a_dst = smem + static_cast<size_t>(s) * stage_bytes;
+      uint8_t* b_dst = a_dst + a_bytes;
+      const int k0 = (kb_begin + i) * kBK;
+      tc::mbar_expect_tx(&full_bar[s], stage_bytes);
+      if (A_MN) {
+        for (int j = 0; j < kBM / 64; ++j) tc::tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + 64 * j, k0);
+      } else {
+        tc::tma_load_2d(a_dst, &tmA, &full_bar[s], k0, m0);
+      }
+      if (B_MN) {
+        for (int j = 0; j < g.BN / 64; ++j) tc::tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + 64 * j, k0);
+      } else {
+        tc::tma_load_2d(b_dst, &tmB, &full_bar[s], k0, n0);
+      }
+    }
+    if (!ok) {
+      atomicCAS(g.status, 0, err::kTimeout);
+      abort_flag = 1;
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    const uint32_t idesc = tc::instr_desc_bf16(kBM, g.BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; ++i) {
+      const int s = i % g.stages;
+      ok = tc::mbar_wait(&full_bar[s], static_cast<uint32_t>(i / g.stages) & 1, kWaitLimit);
+      if (!ok) break;
+      tc::fence_after_sync();
+      const uint32_t a_addr = tc::smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+      const uint32_t b_addr = a_addr + a_bytes;
+#pragma unroll
+      for (int k = 0; k < kBK / 16; ++k) {
+        const uint64_t ad = A_MN ? tc::smem_desc(a_addr + k * 2048, 8192, 1024) : tc::smem_desc(a_addr + k * 32, 16, 1024);
+        const uint64_t bd = B_MN ? tc::smem_desc(b_addr + k * 2048, 8192, 1024) : tc::smem_desc(b_addr + k * 32, 16, 1024);
+        tc::mma_bf16(tmem_base, ad, bd, idesc, (i > 0 || k > 0) ? 1u : 0u);
+      }
+      tc::mma_commit(&empty_bar[s]);  // the stage is free again once these MMAs have read it
+    }
+    if (ok) {
+      tc::mma_commit(&acc_bar);
+    } else {
+      atomicCAS(g.status, 0, err::kTimeout);
+      abort_flag = 1;
+      tc::mbar_arrive(&acc_bar);  // release the epilogue warps; they see abort_flag and skip
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue: thread = one accumulator row
+    const bool ok = tc::mbar_wait(&acc_bar, 0, kWaitLimit);
+    tc::fence_after_sync();
+    if (!ok && lane == 0) atomicCAS(g.status, 0, err::kTimeout);
+    const int quarter = warp & 3;  // a warp may only read TMEM lanes [32 * (warp % 4), +32)
+    const int row = m0 + quarter * 32 + lane;
+    const bool live = ok && abort_flag == 0 && num_kb > 0;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    for (int c = 0; c < g.BN && live; c += 16) {
+      const int col = n0 + c;
+      if (col >= g.N) break;  // warp-uniform
+      uint32_t r[16];
+      tc::tmem_ld16(t_row + c, r);
+      tc::tmem_ld_wait();
+      if (row >= g.M) continue;
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+      const bool full = col + 16 <= g.N;
+      if (EPI == EPI_BIAS_ACT) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (full || col + j < g.N) {
+            v[j] += g.bias ? g.bias[col + j] : 0.f;
+            if (g.relu) v[j] = fmaxf(v[j], 0.f);
+          }
+        }
+      }
+      if (EPI == EPI_RELU_MASK && g.H != nullptr) {
+        const __nv_bfloat16* h = g.H + static_cast<size_t>(row) * g.ldh + col;
+        if (full) {
+          uint4 hv[2];
+          hv[0] = *reinterpret_cast<const uint4*>(h);
+          hv[1] = *reinterpret_cast<const uint4*>(h + 8);
+          const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(hv);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(hb[j]) > 0.f ? v[j] : 0.f;
+        } else {
+          for (int j = 0; j < 16 && col + j < g.N; ++j) v[j] = __bfloat162float(h[j]) > 0.f ? v[j] : 0.f;
+        }
+      }
+      if (EPI == EPI_RED_F32) {
+        float* o = g.out32 + static_cast<size_t>(row) * g.ldo32 + col;
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          if (col + j + 4 <= g.N) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(v[j]), "f"(v[j + 1]),
+                         "f"(v[j + 2]), "f"(v[j + 3])
+                         : "memory");
+          } else {
+            for (int e = j; e < j + 4 && col + e < g.N; ++e) atomicAdd(o + e, v[e]);
+          }
+        }
+      } else {
+        __nv_bfloat16* o = g.out + static_cast<size_t>(row) * g.ldo + col;
+        if (full) {
+          uint4 w0, w1;
+          w0.x = pack_bf16(v[0], v[1]);   w0.y = pack_bf16(v[2], v[3]);
+          w0.z = pack_bf16(v[4], v[5]);   w0.w = pack_bf16(v[6], v[7]);
+          w1.x = pack_bf16(v[8], v[9]);   w1.y = pack_bf16(v[10], v[11]);
+          w1.z = pack_bf16(v[12], v[13]); w1.w = pack_bf16(v[14], v[15]);
+          *reinterpret_cast<uint4*>(o) = w0;
+          *reinterpret_cast<uint4*>(o + 8) = w1;
+        } else {
+          for (int j = 0; j < 16 && col + j < g.N; ++j) o[j] = __float2bfloat16(v[j]);
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown: let the copies that were issued land, then free tensor memory
+  if (warp == 0 && lane == 0) {
+    const int first = max(0, num_kb - g.stages);
+    for (int i = first; i < num_kb; ++i)
+      tc::mbar_wait(&full_bar[i % g.stages], static_cast<uint32_t>(i / g.stages) & 1, kWaitLimit);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// ------------------------------------------------------------------ column sums
+__global__ void __launch_bounds__(256)
+colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ld, int M, int N, int rows_per_block, float* out) {
+  // block = 256 threads: 32 column pairs x 8 row lanes over a 64-column strip
+  const int cpair = threadIdx.x & 31;
+  const int rlane = threadIdx.x >> 5;
+  const int col = blockIdx.x * 64 + cpair * 2;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(M, r0 + rows_per_block);
+  float s0 = 0.f, s1 = 0.f;
+  if (col < N) {
+    for (int r = r0 + rlane; r < r1; r += 8) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + static_cast<size_t>(r) * ld + col);
+      s0 += __bfloat162float(v.x);
+      s1 += __bfloat162float(v.y);
+    }
+  }
+  __shared__ float sh[8][64];
+  sh[rlane][cpair * 2] = s0;
+  sh[rlane][cpair * 2 + 1] = s1;
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float t = 0.f;
+    for (int k = 0; k < 8; ++k) t += sh[k][threadIdx.x];
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    if (c < N) atomicAdd(out + c, t);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 row-major tensor [rows, cols] with pitch ld (elements); box = box_cols x box_rows,
+// 128-byte swizzle, out-of-range elements read as zero.
+bool make_tmap(CUtensorMap* m, const __nv_bfloat16* base, int rows, int cols, int ld, int box_cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld % 8) != 0 || box_cols != 64 || box_rows > 256) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int pick_bn(int n, int granule) {
+  // fewest tiles first, then the narrowest tile that still covers n with that many tiles
+  const int tiles = (n + 255) / 256;
+  int bn = (n + tiles - 1) / tiles;
+  bn = (bn + granule - 1) / granule * granule;
+  return bn < granule ? granule : bn;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int splits, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(g.stages) * (kBM + g.BN) * 128 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_kernel<A_MN, B_MN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr_set = true;
+  }
+  dim3 grid((g.M + kBM - 1) / kBM, (g.N + g.BN - 1) / g.BN, splits);
+  gemm_kernel<A_MN, B_MN, EPI><<<grid, kThreads, smem, stream>>>(ta, tb, g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace
+
+int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int ldw, const float* bias,
+                   __nv_bfloat16* Y, int ldy, int M, int N, int K, bool relu, int* status, cudaStream_t stream) {
+  GemmArgs g{};
+  g.M = M, g.N = N, g.K = K;
+  g.BN = pick_bn(N, 16);
+  g.stages = 2;
+  g.kb_per_split = (K + kBK - 1) / kBK;
+  g.relu = relu ? 1 : 0;
+  g.bias = bias;
+  g.out = Y, g.ldo = ldy;
+  g.status = status;
+  CUtensorMap ta, tb;
+  if ((ldy % 8) != 0 || !make_tmap(&ta, X, M, K, ldx, 64, kBM) || !make_tmap(&tb, W, N, K, ldw, 64, g.BN)) return -1;
+  return launch<false, false, EPI_BIAS_ACT>(ta, tb, g, 1, stream);
+}
+
+int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int ldwt, const __nv_bfloat16* H,
+                 int ldh, __nv_bfloat16* dX, int lddx, int M, int N, int K, int* status, cudaStream_t stream) {
+  // out dX is [M, K]; the contraction runs over the layer's N outputs
+  GemmArgs g{};
+  g.M = M, g.N = K, g.K = N;
+  g.BN = pick_bn(K, 16);
+  g.stages = 2;
+  g.kb_per_split = (N + kBK - 1) / kBK;
+  g.H = H, g.ldh = ldh;
+  g.out = dX, g.ldo = lddx;
+  g.status = status;
+  CUtensorMap ta, tb;
+  if ((lddx % 8) != 0 || (H && (ldh % 8) != 0) || !make_tmap(&ta, dY, M, N, lddy, 64, kBM) ||
+      !make_tmap(&tb, Wt, K, N, ldwt, 64, g.BN))
+    return -1;
+  return launch<false, false, EPI_RELU_MASK>(ta, tb, g, 1, stream);
+}
+
+int linear_wgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* X, int ldx, float* dW, int lddw, int M,
+                 int N, int K, int* status, cudaStream_t stream) {
+  // out dW is [N, K]; the contraction runs over the M batch rows, split across blockIdx.z
+  GemmArgs g{};
+  g.M = N, g.N = K, g.K = M;
+  g.BN = pick_bn(K, 64);
+  g.stages = 4;
+  const int total_kb = (M + kBK - 1) / kBK;
+  const int tiles = ((N + kBM - 1) / kBM) * ((K + g.BN - 1) / g.BN);
+  int splits = 148 / (tiles > 0 ? tiles : 1);
+  if (splits < 1) splits = 1;
+  if (splits > total_kb) splits = total_kb;
+  g.kb_per_split = (total_kb + splits - 1) / splits;
+  splits = (total_kb + g.kb_per_split - 1) / g.kb_per_split;  // no empty split
+  g.out32 = dW, g.ldo32 = lddw;
+  g.status = status;
+  CUtensorMap ta, tb;
+  if ((lddw % 4) != 0 || (reinterpret_cast<uintptr_t>(dW) & 15) != 0 || !make_tmap(&ta, dY, M, N, lddy, 64, 64) ||
+      !make_tmap(&tb, X, M, K, ldx, 64, 64))
+    return -1;
+  return launch<true, true, EPI_RED_F32>(ta, tb, g, splits, stream);
+}
+
+void colsum_bf16(const __nv_bfloat16* dY, int lddy, int M, int N, float* db, cudaStream_t stream) {
+  const int strips = (N + 63) / 64;
+  int row_blocks = (148 * 4 + strips - 1) / strips;
+  int rows_per_block = (M + row_blocks - 1) / row_blocks;
+  if (rows_per_block < 64) rows_per_block = 64;
+  row_blocks = (M + rows_per_block - 1) / rows_per_block;
+  colsum_bf16_kernel<<<dim3(strips, row_blocks), 256, 0, stream>>>(dY, lddy, M, N, rows_per_block, db);
+}
+
+}  // namespace cu
+}  // namespace kb

@@ -1,0 +1,93 @@
+"""tcgen05 Linear kernels against fp32 matmuls of the same bf16-rounded operands (B200 only)."""
+import pytest
+import torch
+
+from kraken_b200._native import C
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def close(got, want, tol=2e-2):
+    err = (got.float() - want.float()).abs().max().item()
+    ref = want.float().abs().max().item() + 1e-6
+    return err <= tol * ref, (err, ref)
+
+
+SHAPES = [(300, 400, 432), (128, 16, 64), (4096, 256, 512), (1000, 208, 72), (257, 400, 400)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("relu", [False, True])
+def test_linear_forward(M, N, K, relu):
+    torch.manual_seed(0)
+    x, w, b = rnd(M, K), rnd(N, K, scale=0.1), torch.randn(N, device=DEV)
+    y = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    C.linear_forward(x, w, b, relu, y, status)
+    want = x.float() @ w.float().t() + b
+    if relu:
+        want = want.relu()
+    assert status.item() == 0
+    ok, info = close(y, want)
+    assert ok, info
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_linear_dgrad_with_relu_mask(M, N, K):
+    torch.manual_seed(1)
+    dy, w = rnd(M, N), rnd(N, K, scale=0.1)
+    h = rnd(M, K).relu()
+    wt = w.t().contiguous()
+    dx = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    C.linear_dgrad(dy, wt, h, dx, status)
+    want = (dy.float() @ w.float()) * (h.float() > 0)
+    assert status.item() == 0
+    ok, info = close(dx, want)
+    assert ok, info
+    C.linear_dgrad(dy, wt, None, dx, status)
+    ok, info = close(dx, dy.float() @ w.float())
+    assert ok and status.item() == 0, info
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES + [(65536, 400, 432)])
+def test_linear_wgrad_accumulates(M, N, K):
+    torch.manual_seed(2)
+    dy, x = rnd(M, N, scale=0.1), rnd(M, K)
+    dw = torch.zeros(N, K, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    C.linear_wgrad(dy, x, dw, status)
+    want = dy.float().t() @ x.float()
+    assert status.item() == 0
+    ok, info = close(dw, want, tol=5e-3)
+    assert ok, info
+    C.linear_wgrad(dy, x, dw, status)  # red-add: a second call doubles the buffer
+    ok, info = close(dw, 2 * want, tol=5e-3)
+    assert ok, info
+
+
+def test_colsum_bf16():
+    torch.manual_seed(3)
+    dy = rnd(5000, 400)
+    db = torch.ones(400, device=DEV)
+    C.colsum_bf16(dy, db)
+    assert torch.allclose(db, 1 + dy.float().sum(0), atol=1e-2, rtol=1e-3)
+
+
+def test_strided_views_are_accepted():
+    """Operands may be column slices of wider buffers (pitch > width)."""
+    torch.manual_seed(4)
+    big = rnd(512, 448)
+    x = big[:, :432]
+    w = rnd(400, 432, scale=0.1)
+    ybuf = torch.zeros(512, 408, device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    C.linear_forward(x, w, None, False, ybuf[:, :400], status)
+    ok, info = close(ybuf[:, :400], x.float() @ w.float().t())
+    assert ok and status.item() == 0, info
+    assert (ybuf[:, 400:] == 0).all()
