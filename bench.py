@@ -166,7 +166,7 @@ def run_ours(args):
         out = {
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "tf32", "data": "synthetic", "impl": "ours",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": "DeepFM 26x1e7 dim16 + MLP 400-400-400-1, Adam lr 1e-3", "global_batch": args.global_batch,
                        "seq_len": NUM_FIELDS, "parallelism": f"dp{world}+row-sharded-tables{world}",
                        "l2": "working set (hash-table rows touched per step + slabs) exceeds the 126 MB L2; "

@@ -4,6 +4,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <pybind11/stl.h>
 #include <torch/extension.h>
@@ -854,6 +855,53 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                    ptr<float>(lr), spin, cur_stream());
     check_launch("push_apply");
   });
+
+  // ---------------- fused DeepFM front end
+  m.def("pull_wait", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl, uint32_t spin) {
+    cu::pull_wait(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), spin, cur_stream());
+    check_launch("pull_wait");
+  });
+  m.def("deepfm_pack_forward",
+        [](const torch::Tensor& rows2, const torch::Tensor& inv2, const torch::Tensor& rows1, const torch::Tensor& inv1,
+           const torch::Tensor& dense, int B, int F, const torch::Tensor& x, const torch::Tensor& fm_logit) {
+          need_cuda(rows2, "rows2", torch::kFloat32);
+          need_cuda(rows1, "rows1", torch::kFloat32);
+          need_cuda(dense, "dense", torch::kFloat32);
+          need_cuda(x, "x", torch::kBFloat16);
+          need_cuda(fm_logit, "fm_logit", torch::kFloat32);
+          const int D = rows2.size(1), ND = dense.size(1), ldx = x.size(1);
+          TORCH_CHECK(D % 4 == 0 && rows1.size(1) == 1, "second-order dim must be a multiple of 4, first-order dim 1");
+          TORCH_CHECK(inv2.numel() >= static_cast<int64_t>(B) * F && inv1.numel() >= static_cast<int64_t>(B) * F,
+                      "occurrence maps too small");
+          TORCH_CHECK(x.size(0) == B && ldx >= F * D + ND && ldx % 4 == 0 && dense.size(0) == B && fm_logit.numel() == B,
+                      "deepfm_pack_forward: shape mismatch");
+          cu::deepfm_pack_forward(ptr<float>(rows2), ptr<int>(inv2), ptr<float>(rows1), ptr<int>(inv1),
+                                  ptr<float>(dense), B, F, D, ND, reinterpret_cast<__nv_bfloat16*>(x.data_ptr()), ldx,
+                                  ptr<float>(fm_logit), cur_stream());
+          check_launch("deepfm_pack_forward");
+        });
+  m.def("deepfm_pack_backward",
+        [](const torch::Tensor& rows2, const torch::Tensor& inv2, const torch::Tensor& inv1,
+           const c10::optional<torch::Tensor>& dx, const torch::Tensor& dlogit, int B, int F, const torch::Tensor& ugrad2,
+           const torch::Tensor& ugrad1) {
+          need_cuda(rows2, "rows2", torch::kFloat32);
+          need_cuda(dlogit, "dlogit", torch::kFloat32);
+          need_cuda(ugrad2, "ugrad2", torch::kFloat32);
+          need_cuda(ugrad1, "ugrad1", torch::kFloat32);
+          const int D = rows2.size(1);
+          const __nv_bfloat16* dxp = nullptr;
+          int lddx = 0;
+          if (dx.has_value()) {
+            need_cuda(*dx, "dx", torch::kBFloat16);
+            TORCH_CHECK(dx->size(0) == B && dx->size(1) >= F * D && dx->size(1) % 4 == 0, "dx has the wrong shape");
+            dxp = reinterpret_cast<const __nv_bfloat16*>(dx->data_ptr());
+            lddx = dx->size(1);
+          }
+          TORCH_CHECK(dlogit.numel() == B && D % 4 == 0, "deepfm_pack_backward: shape mismatch");
+          cu::deepfm_pack_backward(ptr<float>(rows2), ptr<int>(inv2), ptr<int>(inv1), dxp, lddx, ptr<float>(dlogit), B, F,
+                                   D, ptr<float>(ugrad2), ptr<float>(ugrad1), cur_stream());
+          check_launch("deepfm_pack_backward");
+        });
 
   // ---------------- table maintenance
   m.def("table_clear", [](const cu::TableHost& t) {

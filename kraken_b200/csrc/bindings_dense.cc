@@ -148,4 +148,33 @@ void bind_dense(py::module_& m) {
     cu::colsum_bf16(bf(dy), dy.stride(0), dy.size(0), dy.size(1), db.data_ptr<float>(), cur_stream());
     check_launch("colsum_bf16");
   });
+  m.def("rowdot_forward", [bf, need_bf16](const torch::Tensor& x, const torch::Tensor& w,
+                                          const c10::optional<torch::Tensor>& bias, const torch::Tensor& y) {
+    need_bf16(x, "x");
+    TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kFloat32 && w.is_contiguous() && w.numel() == x.size(1),
+                "w must be a contiguous CUDA f32 vector of K elements");
+    TORCH_CHECK(y.scalar_type() == torch::kFloat32 && y.numel() == x.size(0) && (x.stride(0) % 2) == 0, "bad y / pitch");
+    cu::rowdot_forward(bf(x), x.stride(0), w.data_ptr<float>(), optr<float>(bias), x.size(0), x.size(1),
+                       y.data_ptr<float>(), cur_stream());
+    check_launch("rowdot_forward");
+  });
+  m.def("rowdot_backward", [bf, need_bf16](const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& dy,
+                                           bool relu_mask, const c10::optional<torch::Tensor>& dx,
+                                           const torch::Tensor& dw, const c10::optional<torch::Tensor>& db) {
+    need_bf16(x, "x");
+    TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == torch::kFloat32 && dy.is_contiguous() && dy.numel() == x.size(0),
+                "dy must be a contiguous CUDA f32 vector of M elements");
+    TORCH_CHECK(dw.scalar_type() == torch::kFloat32 && dw.is_contiguous() && dw.numel() == x.size(1), "bad dw");
+    __nv_bfloat16* dxp = nullptr;
+    int lddx = 0;
+    if (dx.has_value()) {
+      need_bf16(*dx, "dx");
+      TORCH_CHECK(dx->size(0) == x.size(0) && dx->size(1) == x.size(1) && (dx->stride(0) % 2) == 0, "bad dx");
+      dxp = reinterpret_cast<__nv_bfloat16*>(dx->data_ptr());
+      lddx = dx->stride(0);
+    }
+    cu::rowdot_backward(bf(x), x.stride(0), w.data_ptr<float>(), dy.data_ptr<float>(), x.size(0), x.size(1), relu_mask,
+                        dxp, lddx, dw.data_ptr<float>(), optr<float>(db), cur_stream());
+    check_launch("rowdot_backward");
+  });
 }

@@ -5,6 +5,7 @@
 // words the kernels write (codes of core/types.h).
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -120,6 +121,25 @@ void fm_backward(const float* emb, const float* gout, int B, int F, int D, float
 // grad (optional) = (sigmoid(x) - y) / n.
 void bce_forward_backward(const float* logits, const float* labels, int n, float* loss, float* grad,
                           cudaStream_t stream);
+
+// ---- DeepFM front end fused around the sparse exchange (deepfm_fused.cu) ----
+// Waits (bounded) until every owner has answered the channel's current pull.
+void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cudaStream_t stream);
+// x[B, ldx] bf16 = [emb rows of F fields x D | ND dense features | zeros], fm_logit[B] fp32.
+// rows2 [*, D] / rows1 [*, 1] are unique rows, inv2 / inv1 [B * F] map occurrences to them.  D % 4 == 0.
+void deepfm_pack_forward(const float* rows2, const int* inv2, const float* rows1, const int* inv1, const float* dense,
+                         int B, int F, int D, int ND, __nv_bfloat16* x, int ldx, float* fm_logit, cudaStream_t stream);
+// Adds each occurrence's gradient into ugrad2 [*, D] / ugrad1 [*, 1] (per unique id).  dx may be null.
+void deepfm_pack_backward(const float* rows2, const int* inv2, const int* inv1, const __nv_bfloat16* dx, int lddx,
+                          const float* dlogit, int B, int F, int D, float* ugrad2, float* ugrad1,
+                          cudaStream_t stream);
+
+// Linear layer with one output over bf16 rows x[M, K] (pitch ldx): y[m] = x[m, :] . w + bias[0].
+void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float* bias, int M, int K, float* y,
+                    cudaStream_t stream);
+// Its backward: dx (optional, bf16, optionally masked by x > 0), dw[K] += ..., db[0] += sum(dy).
+void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const float* dy, int M, int K, bool relu_mask,
+                     __nv_bfloat16* dx, int lddx, float* dw, float* db, cudaStream_t stream);
 
 }  // namespace cu
 }  // namespace kb

@@ -5,6 +5,8 @@
 // Counterparts in the reference: kraken/pytorch/py/jagged_ops.cc:14-420 (CPU,
 // OpenMP), examples/DeepFM/model/DeepFM.py:96-107 (FM as torch expressions)
 // and :140 (BCEWithLogits).
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -137,6 +139,58 @@ bce_kernel(const float* __restrict__ logits, const float* __restrict__ labels, i
   }
 }
 
+// ---- Linear layer with a single output (the MLP's logit head): y[m] = x[m, :] . w + b
+__global__ void __launch_bounds__(kThreads)
+rowdot_forward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ w,
+                      const float* __restrict__ bias, int M, int K, float* __restrict__ y) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int m = warp; m < M; m += nwarps) {
+    const __nv_bfloat16* row = x + static_cast<size_t>(m) * ldx;
+    float acc = 0.f;
+    for (int k = lane * 2; k < K; k += 64) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(row + k);
+      acc += __bfloat162float(v.x) * w[k];
+      if (k + 1 < K) acc += __bfloat162float(v.y) * w[k + 1];
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[m] = acc + (bias ? bias[0] : 0.f);
+  }
+}
+
+// dx[m, k] = dy[m] * w[k] * (x[m, k] > 0 if relu_mask), dw[k] += sum_m dy[m] x[m, k], db += sum_m dy[m]
+__global__ void __launch_bounds__(kThreads)
+rowdot_backward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ w,
+                       const float* __restrict__ dy, int M, int K, int rows_per_block, int relu_mask,
+                       __nv_bfloat16* __restrict__ dx, int lddx, float* dw, float* db) {
+  const int r0 = blockIdx.x * rows_per_block;
+  const int r1 = min(M, r0 + rows_per_block);
+  for (int k = threadIdx.x * 2; k < K; k += 2 * blockDim.x) {
+    const float w0 = w[k], w1 = (k + 1 < K) ? w[k + 1] : 0.f;
+    float a0 = 0.f, a1 = 0.f;
+    for (int m = r0; m < r1; ++m) {
+      const float g = dy[m];
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + static_cast<size_t>(m) * ldx + k);
+      const float x0 = __bfloat162float(v.x), x1 = __bfloat162float(v.y);
+      a0 += g * x0;
+      a1 += g * x1;
+      if (dx) {
+        const float d0 = (!relu_mask || x0 > 0.f) ? g * w0 : 0.f;
+        const float d1 = (!relu_mask || x1 > 0.f) ? g * w1 : 0.f;
+        *reinterpret_cast<__nv_bfloat162*>(dx + static_cast<size_t>(m) * lddx + k) = __floats2bfloat162_rn(d0, d1);
+      }
+    }
+    atomicAdd(dw + k, a0);
+    if (k + 1 < K) atomicAdd(dw + k + 1, a1);
+  }
+  if (db && threadIdx.x == 0) {
+    float s = 0.f;
+    for (int m = r0; m < r1; ++m) s += dy[m];
+    atomicAdd(db, s);
+  }
+}
+
 }  // namespace
 
 void jagged_forward(const float* values, const float* weights, const int64_t* offsets, int k, int dim, bool mean,
@@ -173,6 +227,25 @@ void bce_forward_backward(const float* logits, const float* labels, int n, float
   int grid = (n + kThreads - 1) / kThreads;
   if (grid > 148 * 4) grid = 148 * 4;
   bce_kernel<<<grid, kThreads, 0, stream>>>(logits, labels, n, 1.f / static_cast<float>(n), loss, grad);
+}
+
+void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float* bias, int M, int K, float* y,
+                    cudaStream_t stream) {
+  if (M <= 0) return;
+  int grid = (M * 32 + kThreads - 1) / kThreads;
+  if (grid > 148 * 8) grid = 148 * 8;
+  rowdot_forward_kernel<<<grid, kThreads, 0, stream>>>(x, ldx, w, bias, M, K, y);
+}
+
+void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const float* dy, int M, int K, bool relu_mask,
+                     __nv_bfloat16* dx, int lddx, float* dw, float* db, cudaStream_t stream) {
+  if (M <= 0) return;
+  int blocks = 148 * 4;
+  int rows_per_block = (M + blocks - 1) / blocks;
+  if (rows_per_block < 16) rows_per_block = 16;
+  blocks = (M + rows_per_block - 1) / rows_per_block;
+  rowdot_backward_kernel<<<blocks, kThreads, 0, stream>>>(x, ldx, w, dy, M, K, rows_per_block, relu_mask ? 1 : 0, dx,
+                                                          lddx, dw, db);
 }
 
 }  // namespace cu

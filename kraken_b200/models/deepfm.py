@@ -5,6 +5,11 @@ and one dim-1 table the first-order weights; ids are global (field offset
 already added).  logit = sum_f w_f + FM2(e) + MLP([e, dense]) + bias.  The
 reference's example builds the same model from 39 + 39 small tables and torch
 CPU ops (examples/DeepFM/model/DeepFM.py:64-140).
+
+On the GPU engine the front end is fused around the exchange: both tables are
+pulled with one shared dedup, a single kernel turns the unique rows into the
+bf16 MLP input and the FM logit, and the backward kernel adds every
+occurrence's gradient straight into the buffers the push sends.
 """
 from __future__ import annotations
 
@@ -13,24 +18,71 @@ from typing import Sequence
 import torch
 
 from .. import pytorch as kk
-from ..ops import fm_interaction
+from .._native import C
+from ..ops import counters, fm_interaction
+from ..pytorch import native
 from .mlp import MLP
+
+
+class _DeepFMFront(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, first_table, second_table, dense, ids, width):
+        eng = native.engine()
+        id1, id2 = first_table.table_id(), second_table.table_id()
+        B, F = ids.shape
+        rows2, inv2, t2 = eng.pull_sparse_unique(id2, ids)
+        rows1, inv1, t1 = eng.pull_sparse_unique(id1, ids, share_with=id2)
+        x = torch.empty((B, width), dtype=torch.bfloat16, device=rows2.device)
+        fm = torch.empty(B, dtype=torch.float32, device=rows2.device)
+        dense = dense.to(rows2.device, torch.float32).contiguous()
+        counters.add()
+        C.deepfm_pack_forward(rows2, inv2, rows1, inv1, dense, B, F, x, fm)
+        ctx.state = (eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F)
+        return x, fm
+
+    @staticmethod
+    def backward(ctx, dx, dfm):
+        eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F = ctx.state
+        if dfm is None:
+            dfm = torch.zeros(B, dtype=torch.float32, device=rows2.device)
+        counters.add()
+        C.deepfm_pack_backward(rows2, inv2, inv1, dx.contiguous() if dx is not None else None,
+                               dfm.float().contiguous(), B, F, eng.grad_accumulator(id2), eng.grad_accumulator(id1))
+        eng.push_sparse_accumulated(id1, t1)
+        eng.push_sparse_accumulated(id2, t2)
+        return None, None, None, None, None
 
 
 class DeepFM(torch.nn.Module):
     def __init__(self, num_fields: int = 26, num_dense: int = 13, dim: int = 16,
-                 hidden: Sequence[int] = (400, 400, 400), init_std: float = 0.01, name: str = "deepfm"):
+                 hidden: Sequence[int] = (400, 400, 400), init_std: float = 0.01, name: str = "deepfm",
+                 fused: bool = True):
         super().__init__()
         self.num_fields, self.num_dense, self.dim = num_fields, num_dense, dim
         self.first_order = kk.Embedding(1, initializer=kk.ConstantInitializer(0.0), name=f"{name}.first_order")
         self.second_order = kk.Embedding(dim, initializer=kk.NormalInitializer(0.0, init_std),
                                          name=f"{name}.second_order")
-        self.mlp = MLP(num_fields * dim + num_dense, list(hidden) + [1])
+        width = num_fields * dim + num_dense
+        self.mlp_in = (width + 7) // 8 * 8  # padded: the tensor-core path wants pitches in multiples of 8
+        self.pad = self.mlp_in - width
+        self.mlp = MLP(self.mlp_in, list(hidden) + [1])
         self.bias = torch.nn.Parameter(torch.zeros(1))
+        self.fused = fused
+
+    def _fused_ok(self, ids: torch.Tensor) -> bool:
+        return (self.fused and self.dim % 4 == 0 and ids.dim() == 2 and native.is_initialized()
+                and hasattr(native.engine(), "pull_sparse_unique") and self.mlp.use_tensor_cores)
 
     def forward(self, dense: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        if self._fused_ok(ids):
+            x, fm = _DeepFMFront.apply(self.first_order.sparse_table, self.second_order.sparse_table, dense, ids,
+                                       self.mlp_in)
+            return fm + self.mlp(x).squeeze(-1) + self.bias
         w = self.first_order(ids)       # [B, F, 1]
         e = self.second_order(ids)      # [B, F, dim]
         dense = dense.to(e.device)
-        deep = self.mlp(torch.cat([e.flatten(1), dense], dim=1)).squeeze(-1)
+        parts = [e.flatten(1), dense]
+        if self.pad:
+            parts.append(torch.zeros(dense.shape[0], self.pad, dtype=e.dtype, device=e.device))
+        deep = self.mlp(torch.cat(parts, dim=1)).squeeze(-1)
         return w.sum(dim=(1, 2)) + fm_interaction(e) + deep + self.bias

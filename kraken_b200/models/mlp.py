@@ -1,13 +1,20 @@
-"""Multi-layer perceptron head (Linear + ReLU, no activation after the last layer)."""
+"""Multi-layer perceptron head (Linear + ReLU, no activation after the last layer).
+
+On CUDA, when every layer width is a multiple of 8, the layers run on the
+hand-written tcgen05 kernels in bf16 with fp32 accumulation
+(``kraken_b200.ops.mlp``); otherwise, and on CPU, plain torch ops are used.
+"""
 from __future__ import annotations
 
 from typing import Sequence
 
 import torch
 
+from ..ops import mlp as fused
+
 
 class MLP(torch.nn.Module):
-    def __init__(self, in_features: int, sizes: Sequence[int]):
+    def __init__(self, in_features: int, sizes: Sequence[int], use_tensor_cores: bool = True):
         super().__init__()
         layers = []
         prev = in_features
@@ -15,8 +22,14 @@ class MLP(torch.nn.Module):
             layers.append(torch.nn.Linear(prev, n))
             prev = n
         self.layers = torch.nn.ModuleList(layers)
+        self.in_features = in_features
+        self.sizes = list(sizes)
+        self.use_tensor_cores = use_tensor_cores and fused.supported(in_features, sizes)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and self.use_tensor_cores:
+            return fused.fused_mlp(x, [l.weight for l in self.layers], [l.bias for l in self.layers])
+        x = x.float()
         last = len(self.layers) - 1
         for i, layer in enumerate(self.layers):
             x = layer(x)

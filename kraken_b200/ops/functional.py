@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from .._native import C
+from . import counters
 
 
 class _FMInteraction(torch.autograd.Function):
@@ -16,11 +17,13 @@ class _FMInteraction(torch.autograd.Function):
     def forward(ctx, emb):
         emb = emb.contiguous()
         ctx.save_for_backward(emb)
+        counters.add()
         return C.fm_forward(emb)
 
     @staticmethod
     def backward(ctx, gout):
         (emb,) = ctx.saved_tensors
+        counters.add()
         return C.fm_backward(emb, gout.contiguous())
 
 
@@ -36,6 +39,7 @@ def fm_interaction(emb: torch.Tensor) -> torch.Tensor:
 class _BCEWithLogits(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, labels):
+        counters.add()
         loss, grad = C.bce_with_logits(logits.contiguous().view(-1), labels.contiguous().view(-1).float(), True)
         ctx.save_for_backward(grad)
         ctx.shape = logits.shape

@@ -1,0 +1,136 @@
+"""MLP head on the tcgen05 Linear kernels (csrc/cuda/mlp_gemm.cu).
+
+``fused_mlp(x, weights, biases)`` runs Linear+ReLU layers on bf16 activations
+with fp32 parameters and fp32 accumulation; the last layer has no activation
+and, when it has a single output, runs as a row-dot kernel that keeps the
+logit in fp32.  The backward pass is hand-scheduled: per layer one split-K
+weight-gradient GEMM that red-adds straight into the parameter's gradient
+buffer, one column-sum for the bias and one input-gradient GEMM with the ReLU
+mask of the previous layer fused into its epilogue.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from .._native import C
+from . import counters
+
+_status = {}
+
+
+def gemm_status(device: torch.device) -> torch.Tensor:
+    """Device word in which the GEMM kernels record a pipeline wait that gave up."""
+    key = (device.type, device.index)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_gemm_status(device: torch.device) -> None:
+    st = gemm_status(device)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise C.KrakenError(f"tcgen05 GEMM: {C.error_message(code)} (code {code})")
+
+
+def supported(in_features: int, sizes: Sequence[int]) -> bool:
+    """Whether every layer meets the TMA pitch rule (multiples of 8 elements)."""
+    dims = [in_features] + list(sizes)
+    if any(d % 8 != 0 for d in dims[:-1]):
+        return False
+    return dims[-1] == 1 or dims[-1] % 8 == 0
+
+
+def _grad_target(p: torch.Tensor) -> torch.Tensor:
+    """The buffer a parameter's gradient is accumulated into (created zeroed if absent)."""
+    if p.grad is None:
+        p.grad = torch.zeros_like(p)
+    return p.grad
+
+
+class _FusedMLP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, n_layers, *params):
+        ws, bs = params[:n_layers], params[n_layers:]
+        dev = x.device
+        st = gemm_status(dev)
+        h = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        acts = [h]
+        M = h.shape[0]
+        for i in range(n_layers - 1):
+            w16 = ws[i].detach().to(torch.bfloat16)
+            y = torch.empty((M, w16.shape[0]), dtype=torch.bfloat16, device=dev)
+            counters.add()
+            C.linear_forward(h, w16, bs[i].detach(), True, y, st)
+            acts.append(y)
+            h = y
+        wl, bl = ws[-1].detach(), bs[-1].detach()
+        if wl.shape[0] == 1:
+            out = torch.empty(M, dtype=torch.float32, device=dev)
+            counters.add()
+            C.rowdot_forward(h, wl.reshape(-1).contiguous(), bl, out)
+            out = out.view(M, 1)
+        else:
+            y = torch.empty((M, wl.shape[0]), dtype=torch.bfloat16, device=dev)
+            counters.add()
+            C.linear_forward(h, wl.to(torch.bfloat16), bl, False, y, st)
+            out = y.float()
+        ctx.acts, ctx.ws, ctx.bs, ctx.n_layers = acts, ws, bs, n_layers
+        ctx.x_needs_grad = x.requires_grad
+        ctx.x_dtype = x.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, gout):
+        acts, ws, bs, L = ctx.acts, ctx.ws, ctx.bs, ctx.n_layers
+        dev = gout.device
+        st = gemm_status(dev)
+        M = acts[0].shape[0]
+        wl = ws[-1]
+        h_last = acts[-1]
+        need_dx_last = L > 1 or ctx.x_needs_grad
+        if wl.shape[0] == 1:
+            dy = gout.reshape(-1).float().contiguous()
+            dh = torch.empty_like(h_last) if need_dx_last else None
+            counters.add()
+            C.rowdot_backward(h_last, wl.detach().reshape(-1).contiguous(), dy, L > 1, dh,
+                              _grad_target(wl).view(-1), _grad_target(bs[-1]))
+        else:
+            dy16 = gout.to(torch.bfloat16).contiguous()
+            counters.add()
+            C.linear_wgrad(dy16, h_last, _grad_target(wl), st)
+            counters.add()
+            C.colsum_bf16(dy16, _grad_target(bs[-1]))
+            dh = None
+            if need_dx_last:
+                dh = torch.empty_like(h_last)
+                counters.add()
+                C.linear_dgrad(dy16, wl.detach().t().contiguous().to(torch.bfloat16), h_last if L > 1 else None, dh, st)
+        for i in range(L - 2, -1, -1):
+            # dh is d(loss)/d(acts[i + 1]) with layer i's ReLU mask already applied
+            counters.add()
+            C.linear_wgrad(dh, acts[i], _grad_target(ws[i]), st)
+            counters.add()
+            C.colsum_bf16(dh, _grad_target(bs[i]))
+            if i > 0 or ctx.x_needs_grad:
+                dprev = torch.empty_like(acts[i])
+                wt16 = ws[i].detach().t().contiguous().to(torch.bfloat16)
+                counters.add()
+                C.linear_dgrad(dh, wt16, acts[i] if i > 0 else None, dprev, st)
+                dh = dprev
+            else:
+                dh = None
+        dx = None
+        if ctx.x_needs_grad and dh is not None:
+            dx = dh if ctx.x_dtype == torch.bfloat16 else dh.to(ctx.x_dtype)
+        # parameter gradients were accumulated in place
+        return (dx, None) + (None,) * (2 * L)
+
+
+def fused_mlp(x: torch.Tensor, weights: List[torch.Tensor], biases: List[torch.Tensor]) -> torch.Tensor:
+    """x [M, K] (bf16 or fp32, CUDA) -> [M, out_features] fp32.  Parameter gradients are
+    accumulated into ``param.grad`` in place by the backward kernels."""
+    return _FusedMLP.apply(x, len(weights), *weights, *biases)

@@ -245,28 +245,60 @@ class SparseChannel:
         self.hwin = torch.zeros(1 << self.hbits, dtype=torch.int32, device=dev)
         self.slot_of = torch.zeros(self.cap, dtype=torch.int32, device=dev)
         self.cnt = torch.zeros(world, dtype=torch.int32, device=dev)
-        self.off = torch.zeros(world + 1, dtype=torch.int32, device=dev)
-        self.uniq = torch.zeros(self.cap, dtype=torch.int64, device=dev)
-        self.inv = torch.zeros(self.cap, dtype=torch.int32, device=dev)
+        self._own_off = torch.zeros(world + 1, dtype=torch.int32, device=dev)
+        self._own_uniq = torch.zeros(self.cap, dtype=torch.int64, device=dev)
+        self._own_inv = torch.zeros(self.cap, dtype=torch.int32, device=dev)
+        self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
+        self.rows_recv = self.arena.window("rows_recv")
         self.slot_cache = torch.full((world * self.cap,), -1, dtype=torch.int32, device=dev)
         self.ugrad = torch.zeros((self.cap, dim), dtype=torch.float32, device=dev)
         self.serial = 0
         self.launches = 0  # kernels launched through this channel (for accounting)
 
     # ------------------------------------------------------------------ helpers
-    def _lookup_phase(self, ids: torch.Tensor, insert: bool) -> int:
+    def _lookup_phase(self, ids: torch.Tensor, insert: bool, share_from: Optional["SparseChannel"] = None) -> int:
+        """Dedup + dispatch + owner-side probe.  ``share_from``: another channel that has just
+        deduplicated the SAME ids with the same owner salt; its unique list and occurrence map
+        are used instead of computing them again."""
         n = int(ids.numel())
         if n > self.cap:
             raise C.KrakenError(f"table {self.table.name!r}: {n} ids in one call exceed the channel capacity "
                                 f"{self.cap}; raise max_ids_per_call")
         h, lay, ctrl, tbl = self.arena.heap, self.lay, self.ctrl, self.table.host()
-        C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.hpos, self.hwin, self.slot_of, self.hbits,
-                          self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5])
+        if share_from is not None and share_from.salt == self.salt and share_from.world == self.world:
+            self.off, self.uniq, self.inv = share_from.off, share_from.uniq, share_from.inv
+        else:
+            self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
+            C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.hpos, self.hwin, self.slot_of, self.hbits,
+                              self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5])
+            self.launches += 2 if n > 0 else 0
         C.pull_dispatch(h, lay, ctrl, self.uniq, self.off, n)
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)
-        self.launches += 4 if n > 0 else 2
+        self.launches += 2
         self.serial += 1
         return n
+
+    def pull_unique(self, ids: torch.Tensor, share_from: Optional["SparseChannel"] = None):
+        """Pull that stops before the expansion: returns (unique rows buffer [cap, dim],
+        occurrence -> unique map [n], ticket).  The rows belong to the channel and are
+        overwritten by its next pull; a consumer kernel reads them through the map."""
+        ids = ids.reshape(-1)
+        n = self._lookup_phase(ids, insert=True, share_from=share_from)
+        C.pull_gather(self.arena.heap, self.lay, self.ctrl, self.table.host(), self.slot_cache)
+        C.pull_wait(self.arena.heap, self.lay, self.ctrl, self.spin)
+        self.launches += 2
+        return self.rows_recv, self.inv, Ticket(self, self.serial, n, None, None, False, None)
+
+    def push_accumulated(self, lr: torch.Tensor, ticket: Ticket) -> None:
+        """Push for gradients that a fused kernel has already summed per unique id into
+        ``self.ugrad`` (the pull's ticket must still be current)."""
+        if ticket.channel is not self or ticket.serial != self.serial:
+            raise C.KrakenError("push_accumulated needs the ticket of this channel's latest pull")
+        h, lay, ctrl, tbl = self.arena.heap, self.lay, self.ctrl, self.table.host()
+        C.push_dispatch(h, lay, ctrl, self.ugrad, self.off, ticket.n, self.table.dim)
+        C.push_apply(h, lay, ctrl, tbl, self.slot_cache, self.table.optim, lr, self.spin)
+        self.launches += 2 + (1 if self.world > 1 else 0)
+        self.serial += 1
 
     # ------------------------------------------------------------------ pull
     def pull(self, ids: torch.Tensor, bag_offsets: Optional[torch.Tensor] = None,

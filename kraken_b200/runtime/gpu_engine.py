@@ -197,6 +197,23 @@ class GpuEngine(Engine):
         ch.push(grads, self.lr_dev, ticket=ticket, ids=ids, bag_offsets=ticket.bag_offsets, weights=ticket.weights,
                 mean=ticket.mean, bag_mean=ticket.bag_mean)
 
+    def pull_sparse_unique(self, table_id: int, indices: torch.Tensor, share_with: Optional[int] = None):
+        """Pull for fused consumers: (unique rows buffer, occurrence -> unique map, ticket).
+        ``share_with`` names a table whose channel has just pulled the same ids: its
+        dedup result is reused."""
+        self._table(table_id, "sparse")
+        idx = self._prep_ids(indices)
+        ch = self._channel(table_id, idx.numel())
+        share = self.channels.get(share_with) if share_with is not None else None
+        return ch.pull_unique(idx, share_from=share)
+
+    def grad_accumulator(self, table_id: int) -> torch.Tensor:
+        """Per-unique-id gradient buffer [cap, dim] of the table's channel (zero between steps)."""
+        return self.channels[table_id].ugrad
+
+    def push_sparse_accumulated(self, table_id: int, ticket: Ticket) -> None:
+        self.channels[table_id].push_accumulated(self.lr_dev, ticket)
+
     def push_sparse_table(self, table_id: int, indices: torch.Tensor, grad: torch.Tensor) -> None:
         info = self._table(table_id, "sparse")
         if grad.numel() != indices.numel() * info.dimension:
@@ -226,7 +243,8 @@ class GpuEngine(Engine):
             self.bucket.check()
 
     def kernel_launches(self) -> int:
-        n = sum(ch.launches for ch in self.channels.values())
+        from ..ops import counters
+        n = sum(ch.launches for ch in self.channels.values()) + counters.launches()
         if self.bucket is not None:
             n += self.bucket.launches
         return n

@@ -91,3 +91,36 @@ def test_strided_views_are_accepted():
     ok, info = close(ybuf[:, :400], x.float() @ w.float().t())
     assert ok and status.item() == 0, info
     assert (ybuf[:, 400:] == 0).all()
+
+
+@pytest.mark.parametrize("sizes", [[400, 400, 400, 1], [64, 16], [256, 8]])
+def test_fused_mlp_matches_torch_fp32(sizes):
+    from kraken_b200.models.mlp import MLP
+    from kraken_b200.ops.mlp import check_gemm_status
+    torch.manual_seed(5)
+    K, M = 432, 1000
+    mlp = MLP(K, sizes).to(DEV)
+    ref = MLP(K, sizes, use_tensor_cores=False).to(DEV)
+    ref.load_state_dict(mlp.state_dict())
+    assert mlp.use_tensor_cores
+    x = torch.randn(M, K, device=DEV)
+    x1 = x.clone().requires_grad_(True)
+    x2 = x.clone().requires_grad_(True)
+    out, want = mlp(x1), ref(x2)
+    assert out.dtype == torch.float32 and out.shape == want.shape
+    assert (out - want).abs().max().item() < 3e-2 * (want.abs().max().item() + 1)
+    g = torch.randn_like(want)
+    out.backward(g)
+    want.backward(g)
+    check_gemm_status(torch.device(DEV, torch.cuda.current_device()))
+    for a, b in zip(mlp.parameters(), ref.parameters()):
+        ok, info = close(a.grad, b.grad, tol=3e-2)
+        assert ok, info
+    ok, info = close(x1.grad, x2.grad, tol=3e-2)
+    assert ok, info
+    # a second backward accumulates into the same gradient buffers
+    mlp(x).backward(g)
+    ref(x).backward(g)
+    for a, b in zip(mlp.parameters(), ref.parameters()):
+        ok, info = close(a.grad, b.grad, tol=3e-2)
+        assert ok, info

@@ -249,3 +249,38 @@ def test_device_wait_times_out_cleanly():
     x = torch.ones(4, device=dev) * 2
     assert float(x.sum().item()) == 8.0  # the context still works
     ch.close()
+
+
+def test_fused_deepfm_matches_unfused_path():
+    """Same seed, same data: the fused front end + tensor-core MLP must track the
+    unfused fp32 path (loss and table contents) within bf16 tolerance."""
+    from kraken_b200.models import ClickDataset, DeepFM
+    from kraken_b200.ops import bce_with_logits
+
+    def run(fused):
+        kk.initialize("gpu", seed=21, table_capacity=1 << 14)
+        torch.manual_seed(0)
+        model = DeepFM(num_fields=6, num_dense=13, dim=16, hidden=(64, 32), init_std=0.1, fused=fused).to(DEV)
+        model.mlp.use_tensor_cores = fused
+        opt = kk.Optimizer("m", model.named_parameters(), 1e-2, kk.Adam())
+        data = ClickDataset(num_fields=6, vocab=500, seed=9)
+        losses = []
+        for _ in range(5):
+            dense, ids, labels = (t.to(DEV) for t in data.batch(700))
+            loss = bce_with_logits(model(dense, ids), labels)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        kk.native.engine().check()
+        probe = torch.arange(0, 3000, 7, device=DEV)
+        rows = kk.pull_sparse_table(model.second_order.sparse_table.table_id(), probe).cpu()
+        first = kk.pull_sparse_table(model.first_order.sparse_table.table_id(), probe).cpu()
+        w = model.mlp.layers[0].weight.detach().cpu().clone()
+        kk.stop()
+        return losses, rows, first, w
+
+    l1, r1, f1, w1 = run(True)
+    l0, r0, f0, w0 = run(False)
+    assert all(abs(a - b) < 5e-3 for a, b in zip(l1, l0)), (l1, l0)
+    assert (r1 - r0).abs().max().item() < 2e-2 and (f1 - f0).abs().max().item() < 2e-2
+    assert (w1 - w0).abs().max().item() < 2e-2
