@@ -63,11 +63,18 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def mark(self):
+        """Start of the timed region: earlier samples are dropped unless nothing else arrives."""
+        self.before = len(self.rows)
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)  # at least one sample period inside / right after the region
         self.proc.terminate()
         time.sleep(0.05)
+        if len(self.rows) > getattr(self, "before", 0):
+            self.rows = self.rows[getattr(self, "before", 0):]
         sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
         mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -128,13 +135,14 @@ def run_ours(args):
 
     # ---------------- device-timed region: inputs staged on the device beforehand
     staged = [tuple(t.to(dev, non_blocking=True) for t in b) for b in host]
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()  # nvidia-smi needs a moment to start reporting: launch it ahead of the warm-up
     for i in range(args.warmup):
         step(*staged[i])
     eng.check()
     launches0 = eng.kernel_launches()
-    sampler = ClockSampler(torch.cuda.current_device())
     sync_all()
-    sampler.start()
+    sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.warmup, total):

@@ -93,34 +93,71 @@ def test_strided_views_are_accepted():
     assert (ybuf[:, 400:] == 0).all()
 
 
+def emulate(x, ws, bs, g):
+    """fp32 restatement of the fused MLP with its rounding points: bf16 inputs, weights and
+    hidden activations / activation gradients, fp32 accumulation.  Returns (out, dWs, dbs, dx)."""
+    r = lambda t: t.to(torch.bfloat16).float()
+    L = len(ws)
+    h = [r(x)]
+    for i in range(L - 1):
+        h.append(r((h[-1] @ r(ws[i]).t() + bs[i]).relu()))
+    single = ws[-1].shape[0] == 1
+    wl = ws[-1] if single else r(ws[-1])
+    out = h[-1] @ wl.t() + bs[-1]
+    if not single:
+        out = r(out)
+    dy = g if single else r(g)
+    dws, dbs = [None] * L, [None] * L
+    dws[-1], dbs[-1] = dy.t() @ h[-1], dy.sum(0)
+    dh = dy @ wl
+    if L > 1:
+        dh = dh * (h[-1] > 0)
+    dh = r(dh)
+    for i in range(L - 2, -1, -1):
+        dws[i], dbs[i] = dh.t() @ h[i], dh.sum(0)
+        dh = dh @ r(ws[i])
+        if i > 0:
+            dh = dh * (h[i] > 0)
+        dh = r(dh)
+    return out, dws, dbs, dh
+
+
 @pytest.mark.parametrize("sizes", [[400, 400, 400, 1], [64, 16], [256, 8]])
-def test_fused_mlp_matches_torch_fp32(sizes):
+def test_fused_mlp_matches_fp32_restatement(sizes):
     from kraken_b200.models.mlp import MLP
     from kraken_b200.ops.mlp import check_gemm_status
     torch.manual_seed(5)
     K, M = 432, 1000
     mlp = MLP(K, sizes).to(DEV)
-    ref = MLP(K, sizes, use_tensor_cores=False).to(DEV)
-    ref.load_state_dict(mlp.state_dict())
     assert mlp.use_tensor_cores
+    ws = [l.weight.detach().clone() for l in mlp.layers]
+    bs = [l.bias.detach().clone() for l in mlp.layers]
     x = torch.randn(M, K, device=DEV)
     x1 = x.clone().requires_grad_(True)
-    x2 = x.clone().requires_grad_(True)
-    out, want = mlp(x1), ref(x2)
+    out = mlp(x1)
+    g = torch.randn_like(out)
+    want, dws, dbs, dx = emulate(x, ws, bs, g)
     assert out.dtype == torch.float32 and out.shape == want.shape
-    assert (out - want).abs().max().item() < 3e-2 * (want.abs().max().item() + 1)
-    g = torch.randn_like(want)
-    out.backward(g)
-    want.backward(g)
-    check_gemm_status(torch.device(DEV, torch.cuda.current_device()))
-    for a, b in zip(mlp.parameters(), ref.parameters()):
-        ok, info = close(a.grad, b.grad, tol=3e-2)
-        assert ok, info
-    ok, info = close(x1.grad, x2.grad, tol=3e-2)
+    ok, info = close(out, want, tol=3e-2)
     assert ok, info
-    # a second backward accumulates into the same gradient buffers
-    mlp(x).backward(g)
+    out.backward(g)
+    check_gemm_status(torch.device(DEV, torch.cuda.current_device()))
+    for layer, dw, db in zip(mlp.layers, dws, dbs):
+        ok, info = close(layer.weight.grad, dw, tol=3e-2)
+        assert ok, info
+        ok, info = close(layer.bias.grad, db, tol=3e-2)
+        assert ok, info
+    ok, info = close(x1.grad, dx, tol=3e-2)
+    assert ok, info
+    # against plain fp32 torch the only extra differences are ReLU gates that flip for
+    # pre-activations within bf16 rounding of zero: compare in the Frobenius norm
+    ref = MLP(K, sizes, use_tensor_cores=False).to(DEV)
+    ref.load_state_dict(mlp.state_dict())
     ref(x).backward(g)
     for a, b in zip(mlp.parameters(), ref.parameters()):
-        ok, info = close(a.grad, b.grad, tol=3e-2)
+        assert (a.grad - b.grad).norm().item() <= 5e-2 * b.grad.norm().item()
+    # a second backward accumulates into the same gradient buffers
+    mlp(x).backward(g)
+    for layer, dw in zip(mlp.layers, dws):
+        ok, info = close(layer.weight.grad, 2 * dw, tol=3e-2)
         assert ok, info

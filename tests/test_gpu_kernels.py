@@ -262,7 +262,7 @@ def test_fused_deepfm_matches_unfused_path():
         torch.manual_seed(0)
         model = DeepFM(num_fields=6, num_dense=13, dim=16, hidden=(64, 32), init_std=0.1, fused=fused).to(DEV)
         model.mlp.use_tensor_cores = fused
-        opt = kk.Optimizer("m", model.named_parameters(), 1e-2, kk.Adam())
+        opt = kk.Optimizer("m", model.named_parameters(), 5e-2, kk.SGD())  # SGD: Adam would amplify sign noise of tiny gradients
         data = ClickDataset(num_fields=6, vocab=500, seed=9)
         losses = []
         for _ in range(5):
