@@ -1,0 +1,29 @@
+"""Multi-GPU runs of the fused exchange kernels (need >= 2 GPUs in one box)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def run_ranks(script, world, *args, timeout=600):
+    port = 29800 + (os.getpid() % 150)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "tests", script), *args]
+    env = dict(os.environ, PYTHONPATH=REPO, NCCL_NVLS_ENABLE="0", KRAKEN_B200_NO_BUILD="1")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-5000:]
+    return res.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gpu_ranks_match_one_shard(world, tmp_path):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = run_ranks("mp_gpu_worker.py", world, str(tmp_path))
+    for tag in ("MULTI_GPU_MATCHES_SINGLE ok", "MULTI_GPU_BAGS ok", "MULTI_GPU_CHECKPOINT_RESHARD ok"):
+        assert tag in out, out[-2000:]
