@@ -88,6 +88,8 @@ eng.check()
 if rank == 0:
     print("MULTI_GPU_BAGS ok")
 
+got = kk.pull_sparse_table(ts, probe.to(dev)).cpu()  # the zero-gradient Adam step above still moved rows
+w_saved = w.cpu()  # parameter views die with the engine's arenas
 assert kk.try_save_model()
 kk.stop()
 
@@ -100,5 +102,5 @@ if rank == 0:
     assert load_model(cpu, out_dir)
     assert torch.allclose(cpu.pull_sparse_table(0, probe), got, atol=1e-6)
     assert cpu.shard.sparse_size(0) == 200
-    assert torch.allclose(cpu.pull_dense_table(2), w.cpu(), atol=1e-6)
+    assert torch.allclose(cpu.pull_dense_table(2), w_saved, atol=1e-6)
     print("MULTI_GPU_CHECKPOINT_RESHARD ok")
