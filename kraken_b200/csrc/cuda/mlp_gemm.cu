@@ -27,7 +27,8 @@ namespace {
 
 constexpr int kBM = 128;         // rows of the output tile = TMEM lanes
 constexpr int kBK = 64;          // k-elements per stage = one 128-byte swizzle atom of bf16
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each taking half of the tile's columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr int kMaxStages = 4;
 
@@ -54,6 +55,145 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+
+// ------------------------------------------------------------------ epilogue
+// Slow path for a 16-column chunk that straddles N: the whole warp calls it (the decision depends
+// on the column only); it reads the chunk from tensor memory itself and writes element-wise with
+// bounds checks, so the fast path never needs its registers in addressable memory.
+template <int EPI>
+__device__ __noinline__ void epilogue_tail(const GemmArgs& g, const float* s_bias, uint32_t taddr, int row, int col,
+                                           int c) {
+  uint32_t r[16];
+  tc::tmem_ld16(taddr, r);
+  tc::tmem_ld_wait();
+  if (row >= g.M) return;
+  for (int j = 0; j < 16 && col + j < g.N; ++j) {
+    float v = __uint_as_float(r[j]);
+    if (EPI == EPI_BIAS_ACT) {
+      v += s_bias[c + j];
+      if (g.relu) v = fmaxf(v, 0.f);
+    }
+    if (EPI == EPI_RELU_MASK && g.H != nullptr &&
+        !(__bfloat162float(g.H[static_cast<size_t>(row) * g.ldh + col + j]) > 0.f))
+      v = 0.f;
+    if (EPI == EPI_RED_F32)
+      atomicAdd(g.out32 + static_cast<size_t>(row) * g.ldo32 + col + j, v);
+    else
+      g.out[static_cast<size_t>(row) * g.ldo + col + j] = __float2bfloat16(v);
+  }
+}
+
+// Fast path: all 16 columns valid.  Everything is unrolled with constant indices so the
+// accumulator chunk stays in registers.
+template <int EPI>
+__device__ __forceinline__ void epilogue_full(const GemmArgs& g, const float* s_bias, int row, int col, int c,
+                                              const uint32_t (&r)[16], const uint4& h0, const uint4& h1) {
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+  if (EPI == EPI_BIAS_ACT) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      v[j] += s_bias[c + j];
+      if (g.relu) v[j] = fmaxf(v[j], 0.f);
+    }
+  }
+  if (EPI == EPI_RELU_MASK) {
+    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      // bf16 > 0  <=>  sign bit clear and not zero
+      const uint32_t lo = hw[j] & 0xFFFFu, hi = hw[j] >> 16;
+      if (lo == 0u || (lo & 0x8000u)) v[2 * j] = 0.f;
+      if (hi == 0u || (hi & 0x8000u)) v[2 * j + 1] = 0.f;
+    }
+  }
+  if (EPI == EPI_RED_F32) {
+    float* o = g.out32 + static_cast<size_t>(row) * g.ldo32 + col;
+#pragma unroll
+    for (int j = 0; j < 16; j += 4)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(v[j]), "f"(v[j + 1]),
+                   "f"(v[j + 2]), "f"(v[j + 3])
+                   : "memory");
+  } else {
+    __nv_bfloat16* o = g.out + static_cast<size_t>(row) * g.ldo + col;
+    uint4 w0, w1;
+    w0.x = pack_bf16(v[0], v[1]);   w0.y = pack_bf16(v[2], v[3]);
+    w0.z = pack_bf16(v[4], v[5]);   w0.w = pack_bf16(v[6], v[7]);
+    w1.x = pack_bf16(v[8], v[9]);   w1.y = pack_bf16(v[10], v[11]);
+    w1.z = pack_bf16(v[12], v[13]); w1.w = pack_bf16(v[14], v[15]);
+    *reinterpret_cast<uint4*>(o) = w0;
+    *reinterpret_cast<uint4*>(o + 8) = w1;
+  }
+}
+
+// One epilogue warp's share of a 128 x BN accumulator: TMEM lanes of its quarter (one row per
+// thread) and the column range [c_begin, c_end).  Two 16-column chunks are in flight per wait.
+template <int EPI>
+__device__ __forceinline__ void epilogue_rows(const GemmArgs& g, const float* s_bias, uint32_t t_row, int row, int n0,
+                                              int c_begin, int c_end) {
+  const bool in_rows = row < g.M;
+  const bool masked = EPI == EPI_RELU_MASK && g.H != nullptr;
+  int c = c_begin;
+  // pairs of full chunks: both loads are issued before the single wait
+  for (; c + 32 <= c_end && n0 + c + 32 <= g.N; c += 32) {
+    const int col = n0 + c;
+    uint32_t r0[16], r1[16];
+    tc::tmem_ld16(t_row + c, r0);
+    tc::tmem_ld16(t_row + c + 16, r1);
+    uint4 h00 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), h01 = h00, h10 = h00, h11 = h00;
+    if (masked && in_rows) {
+      const __nv_bfloat16* h = g.H + static_cast<size_t>(row) * g.ldh + col;
+      h00 = *reinterpret_cast<const uint4*>(h);
+      h01 = *reinterpret_cast<const uint4*>(h + 8);
+      h10 = *reinterpret_cast<const uint4*>(h + 16);
+      h11 = *reinterpret_cast<const uint4*>(h + 24);
+    }
+    tc::tmem_ld_wait();
+    if (in_rows) {
+      epilogue_full<EPI>(g, s_bias, row, col, c, r0, h00, h01);
+      epilogue_full<EPI>(g, s_bias, row, col + 16, c + 16, r1, h10, h11);
+    }
+  }
+  // what is left: single chunks, full or straddling N (all conditions are warp-uniform)
+  for (; c < c_end && n0 + c < g.N; c += 16) {
+    const int col = n0 + c;
+    if (col + 16 <= g.N) {
+      uint32_t r0[16];
+      tc::tmem_ld16(t_row + c, r0);
+      uint4 h00 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), h01 = h00;
+      if (masked && in_rows) {
+        const __nv_bfloat16* h = g.H + static_cast<size_t>(row) * g.ldh + col;
+        h00 = *reinterpret_cast<const uint4*>(h);
+        h01 = *reinterpret_cast<const uint4*>(h + 8);
+      }
+      tc::tmem_ld_wait();
+      if (in_rows) epilogue_full<EPI>(g, s_bias, row, col, c, r0, h00, h01);
+    } else {
+      epilogue_tail<EPI>(g, s_bias, t_row + c, row, col, c);
+    }
+  }
+}
+
+// Column range of epilogue warp `ew` (0 .. kEpiWarps - 1): the tile's 16-column chunks are split
+// between the two warps that share a TMEM lane quarter.
+__device__ __forceinline__ void epi_cols(int bn, int ew, int* c_begin, int* c_end) {
+  const int chunks = bn / 16;
+  const int first = (chunks + 1) / 2;
+  if (ew < 4) {
+    *c_begin = 0;
+    *c_end = first * 16;
+  } else {
+    *c_begin = first * 16;
+    *c_end = bn;
+  }
+}
+
+// Bias of the tile's columns into shared memory (zeros where there is none).
+__device__ __forceinline__ void stage_bias(const GemmArgs& g, float* s_bias, int n0, int tid, int nthreads) {
+  for (int j = tid; j < 256; j += nthreads) s_bias[j] = (g.bias && j < g.BN && n0 + j < g.N) ? g.bias[n0 + j] : 0.f;
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(kThreads)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
@@ -68,6 +208,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __shared__ uint64_t acc_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ float s_bias[256];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -92,6 +233,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc::prefetch_tmap(&tmB);
   }
   if (warp == 1) tc::tmem_alloc(&tmem_slot, tmem_cols);
+  if (EPI == EPI_BIAS_ACT) stage_bias(g, s_bias, n0, threadIdx.x, blockDim.x);
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -151,73 +293,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc::mbar_arrive(&acc_bar);  // release the epilogue warps; they see abort_flag and skip
     }
   } else if (warp >= 2) {
-    // ---------------- epilogue: thread = one accumulator row
+    // ---------------- epilogue: thread = one accumulator row, warp = one column half
     const bool ok = tc::mbar_wait(&acc_bar, 0, kWaitLimit);
     tc::fence_after_sync();
     if (!ok && lane == 0) atomicCAS(g.status, 0, err::kTimeout);
     const int quarter = warp & 3;  // a warp may only read TMEM lanes [32 * (warp % 4), +32)
     const int row = m0 + quarter * 32 + lane;
-    const bool live = ok && abort_flag == 0 && num_kb > 0;
-    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    for (int c = 0; c < g.BN && live; c += 16) {
-      const int col = n0 + c;
-      if (col >= g.N) break;  // warp-uniform
-      uint32_t r[16];
-      tc::tmem_ld16(t_row + c, r);
-      tc::tmem_ld_wait();
-      if (row >= g.M) continue;
-      float v[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-      const bool full = col + 16 <= g.N;
-      if (EPI == EPI_BIAS_ACT) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (full || col + j < g.N) {
-            v[j] += g.bias ? g.bias[col + j] : 0.f;
-            if (g.relu) v[j] = fmaxf(v[j], 0.f);
-          }
-        }
-      }
-      if (EPI == EPI_RELU_MASK && g.H != nullptr) {
-        const __nv_bfloat16* h = g.H + static_cast<size_t>(row) * g.ldh + col;
-        if (full) {
-          uint4 hv[2];
-          hv[0] = *reinterpret_cast<const uint4*>(h);
-          hv[1] = *reinterpret_cast<const uint4*>(h + 8);
-          const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(hv);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(hb[j]) > 0.f ? v[j] : 0.f;
-        } else {
-          for (int j = 0; j < 16 && col + j < g.N; ++j) v[j] = __bfloat162float(h[j]) > 0.f ? v[j] : 0.f;
-        }
-      }
-      if (EPI == EPI_RED_F32) {
-        float* o = g.out32 + static_cast<size_t>(row) * g.ldo32 + col;
-#pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-          if (col + j + 4 <= g.N) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + j), "f"(v[j]), "f"(v[j + 1]),
-                         "f"(v[j + 2]), "f"(v[j + 3])
-                         : "memory");
-          } else {
-            for (int e = j; e < j + 4 && col + e < g.N; ++e) atomicAdd(o + e, v[e]);
-          }
-        }
-      } else {
-        __nv_bfloat16* o = g.out + static_cast<size_t>(row) * g.ldo + col;
-        if (full) {
-          uint4 w0, w1;
-          w0.x = pack_bf16(v[0], v[1]);   w0.y = pack_bf16(v[2], v[3]);
-          w0.z = pack_bf16(v[4], v[5]);   w0.w = pack_bf16(v[6], v[7]);
-          w1.x = pack_bf16(v[8], v[9]);   w1.y = pack_bf16(v[10], v[11]);
-          w1.z = pack_bf16(v[12], v[13]); w1.w = pack_bf16(v[14], v[15]);
-          *reinterpret_cast<uint4*>(o) = w0;
-          *reinterpret_cast<uint4*>(o + 8) = w1;
-        } else {
-          for (int j = 0; j < 16 && col + j < g.N; ++j) o[j] = __float2bfloat16(v[j]);
-        }
-      }
+    if (ok && abort_flag == 0 && num_kb > 0) {
+      int c_begin, c_end;
+      epi_cols(g.BN, warp - 2, &c_begin, &c_end);
+      epilogue_rows<EPI>(g, s_bias, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), row, n0, c_begin, c_end);
     }
   }
 
@@ -230,6 +315,154 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 1) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// ------------------------------------------------------------------ weight-resident persistent variant
+// Forward and input-gradient GEMMs of an MLP are tall and skinny: M = batch (tens of thousands),
+// N and K a few hundred.  With one output tile per CTA every CTA re-reads its 128 x K slice of the
+// weights from L2, and that traffic, not the tensor cores, sets the time.  Here a CTA (one per SM)
+// loads its BN x K slice of the weight matrix ONCE, keeps it in shared memory, and then streams
+// activation tiles for many 128-row tiles through a small ring, with two TMEM accumulators so the
+// epilogue of tile j overlaps the MMAs of tile j + 1.
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bres_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int total_kb = (g.K + kBK - 1) / kBK;
+  const uint32_t a_bytes = kBM * 128;
+  const uint32_t b_bytes = static_cast<uint32_t>(g.BN) * 128;  // one k-block of the resident weights
+  uint8_t* b_res = smem;
+  uint8_t* a_ring = smem + static_cast<size_t>(total_kb) * b_bytes;
+
+  __shared__ uint64_t b_full, a_full[kMaxStages], a_empty[kMaxStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ float s_bias[256];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.y * g.BN;
+  const int m_tiles = (g.M + kBM - 1) / kBM;
+  const int my_tiles = (m_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  constexpr uint32_t kAccCols = 256;  // column stride between the two accumulators
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&b_full, 1);
+    for (int s = 0; s < g.stages; ++s) {
+      tc::mbar_init(&a_full[s], 1);
+      tc::mbar_init(&a_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&acc_full[b], 1);
+      tc::mbar_init(&acc_empty[b], kEpiWarps);  // one arrival per epilogue warp
+    }
+    abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tmap(&tmA);
+    tc::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tc::tmem_alloc(&tmem_slot, 512);
+  if (EPI == EPI_BIAS_ACT) stage_bias(g, s_bias, n0, threadIdx.x, blockDim.x);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  const int total_it = my_tiles * total_kb;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- producer: the weights once, then the activation stream
+    tc::mbar_expect_tx(&b_full, static_cast<uint32_t>(total_kb) * b_bytes);
+    for (int kb = 0; kb < total_kb; ++kb)
+      tc::tma_load_2d(b_res + static_cast<size_t>(kb) * b_bytes, &tmB, &b_full, kb * kBK, n0);
+    bool ok = true;
+    for (int it = 0; it < total_it && ok; ++it) {
+      const int s = it % g.stages;
+      const uint32_t round = static_cast<uint32_t>(it / g.stages);
+      if (round > 0) ok = tc::mbar_wait(&a_empty[s], (round - 1) & 1, kWaitLimit);
+      if (!ok) break;
+      const int tile = blockIdx.x + (it / total_kb) * gridDim.x;
+      const int kb = it % total_kb;
+      tc::mbar_expect_tx(&a_full[s], a_bytes);
+      tc::tma_load_2d(a_ring + static_cast<size_t>(s) * a_bytes, &tmA, &a_full[s], kb * kBK, tile * kBM);
+    }
+    if (!ok) {
+      atomicCAS(g.status, 0, err::kTimeout);
+      abort_flag = 1;
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    const uint32_t idesc = tc::instr_desc_bf16(kBM, g.BN, 0, 0);
+    bool ok = tc::mbar_wait(&b_full, 0, kWaitLimit);
+    tc::fence_after_sync();
+    const uint32_t b_addr0 = tc::smem_u32(b_res);
+    const uint32_t a_addr0 = tc::smem_u32(a_ring);
+    int it = 0;
+    for (int j = 0; j < my_tiles && ok; ++j) {
+      const int buf = j & 1;
+      const uint32_t use = static_cast<uint32_t>(j >> 1);
+      if (use > 0) {
+        ok = tc::mbar_wait(&acc_empty[buf], (use - 1) & 1, kWaitLimit);  // epilogue has drained this buffer
+        if (!ok) break;
+        tc::fence_after_sync();
+      }
+      const uint32_t d_tmem = tmem_base + buf * kAccCols;
+      for (int kb = 0; kb < total_kb && ok; ++kb, ++it) {
+        const int s = it % g.stages;
+        ok = tc::mbar_wait(&a_full[s], static_cast<uint32_t>(it / g.stages) & 1, kWaitLimit);
+        if (!ok) break;
+        tc::fence_after_sync();
+        const uint32_t a_addr = a_addr0 + s * a_bytes;
+        const uint32_t b_addr = b_addr0 + kb * b_bytes;
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k)
+          tc::mma_bf16(d_tmem, tc::smem_desc(a_addr + k * 32, 16, 1024), tc::smem_desc(b_addr + k * 32, 16, 1024), idesc,
+                       (kb > 0 || k > 0) ? 1u : 0u);
+        tc::mma_commit(&a_empty[s]);
+      }
+      if (ok) tc::mma_commit(&acc_full[buf]);
+    }
+    if (!ok) {
+      atomicCAS(g.status, 0, err::kTimeout);
+      abort_flag = 1;
+      tc::mbar_arrive(&acc_full[0]);
+      tc::mbar_arrive(&acc_full[1]);
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue
+    const int quarter = warp & 3;
+    bool ok = true;
+    for (int j = 0; j < my_tiles && ok; ++j) {
+      const int buf = j & 1;
+      ok = tc::mbar_wait(&acc_full[buf], static_cast<uint32_t>(j >> 1) & 1, kWaitLimit);
+      tc::fence_after_sync();
+      if (!ok || abort_flag != 0) {
+        if (!ok && lane == 0) atomicCAS(g.status, 0, err::kTimeout);
+        ok = false;
+        break;
+      }
+      const int tile = blockIdx.x + j * gridDim.x;
+      const int row = tile * kBM + quarter * 32 + lane;
+      int c_begin, c_end;
+      epi_cols(g.BN, warp - 2, &c_begin, &c_end);
+      epilogue_rows<EPI>(g, s_bias, tmem_base + buf * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16), row, n0,
+                         c_begin, c_end);
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // ---------------- teardown
+  if (warp == 0 && lane == 0) {
+    tc::mbar_wait(&b_full, 0, kWaitLimit);
+    const int first = max(0, total_it - g.stages);
+    for (int it = first; it < total_it; ++it)
+      tc::mbar_wait(&a_full[it % g.stages], static_cast<uint32_t>(it / g.stages) & 1, kWaitLimit);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc::tmem_dealloc(tmem_base, 512);
 }
 
 // ------------------------------------------------------------------ column sums
@@ -315,6 +548,32 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int splits,
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// Resident-weight launch when the weight slice and a 2-stage activation ring fit in shared memory
+// and there are enough row tiles to amortise loading it; returns false if not applicable.
+template <int EPI>
+bool launch_resident(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaStream_t stream, int* rc) {
+  const int total_kb = (g.K + kBK - 1) / kBK;
+  const int n_tiles = (g.N + g.BN - 1) / g.BN;
+  const int m_tiles = (g.M + kBM - 1) / kBM;
+  g.stages = 2;
+  const size_t smem = static_cast<size_t>(total_kb) * g.BN * 128 + static_cast<size_t>(g.stages) * kBM * 128 + 1024;
+  if (smem > 225 * 1024 || n_tiles > 148 || m_tiles * n_tiles < 2 * 148) return false;
+  static size_t attr_smem = 0;  // static + dynamic shared memory share the 227 KB limit: ask for what is needed
+  if (smem > attr_smem) {
+    if (cudaFuncSetAttribute(gemm_bres_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    attr_smem = smem;
+  }
+  int per_n = 148 / n_tiles;
+  if (per_n > m_tiles) per_n = m_tiles;
+  gemm_bres_kernel<EPI><<<dim3(per_n, n_tiles), kThreads, smem, stream>>>(ta, tb, g);
+  *rc = cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return true;
+}
+
 }  // namespace
 
 int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int ldw, const float* bias,
@@ -330,6 +589,8 @@ int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int 
   g.status = status;
   CUtensorMap ta, tb;
   if ((ldy % 8) != 0 || !make_tmap(&ta, X, M, K, ldx, 64, kBM) || !make_tmap(&tb, W, N, K, ldw, 64, g.BN)) return -1;
+  int rc = 0;
+  if (launch_resident<EPI_BIAS_ACT>(ta, tb, g, stream, &rc)) return rc;
   return launch<false, false, EPI_BIAS_ACT>(ta, tb, g, 1, stream);
 }
 
@@ -348,6 +609,8 @@ int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int
   if ((lddx % 8) != 0 || (H && (ldh % 8) != 0) || !make_tmap(&ta, dY, M, N, lddy, 64, kBM) ||
       !make_tmap(&tb, Wt, K, N, ldwt, 64, g.BN))
     return -1;
+  int rc = 0;
+  if (launch_resident<EPI_RELU_MASK>(ta, tb, g, stream, &rc)) return rc;
   return launch<false, false, EPI_RELU_MASK>(ta, tb, g, 1, stream);
 }
 

@@ -77,7 +77,7 @@ class DeepFM(torch.nn.Module):
         if self._fused_ok(ids):
             x, fm = _DeepFMFront.apply(self.first_order.sparse_table, self.second_order.sparse_table, dense, ids,
                                        self.mlp_in)
-            return fm + self.mlp(x).squeeze(-1) + self.bias
+            return fm + self.mlp(x, input_grad_cols=self.num_fields * self.dim).squeeze(-1) + self.bias
         w = self.first_order(ids)       # [B, F, 1]
         e = self.second_order(ids)      # [B, F, dim]
         dense = dense.to(e.device)

@@ -53,7 +53,7 @@ def _grad_target(p: torch.Tensor) -> torch.Tensor:
 
 class _FusedMLP(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, n_layers, *params):
+    def forward(ctx, x, n_layers, input_grad_cols, *params):
         ws, bs = params[:n_layers], params[n_layers:]
         dev = x.device
         st = gemm_status(dev)
@@ -80,6 +80,7 @@ class _FusedMLP(torch.autograd.Function):
             out = y.float()
         ctx.acts, ctx.ws, ctx.bs, ctx.n_layers = acts, ws, bs, n_layers
         ctx.x_needs_grad = x.requires_grad
+        ctx.input_grad_cols = input_grad_cols
         ctx.x_dtype = x.dtype
         return out
 
@@ -119,7 +120,13 @@ class _FusedMLP(torch.autograd.Function):
                 dprev = torch.empty_like(acts[i])
                 wt16 = ws[i].detach().t().contiguous().to(torch.bfloat16)
                 counters.add()
-                C.linear_dgrad(dh, wt16, acts[i] if i > 0 else None, dprev, st)
+                cols = ctx.input_grad_cols if (i == 0 and ctx.input_grad_cols) else dprev.shape[1]
+                if cols < dprev.shape[1]:
+                    # only the leading columns of the input need a gradient (the rest are constants)
+                    dprev[:, cols:].zero_()
+                    C.linear_dgrad(dh, wt16[:cols], None, dprev[:, :cols], st)
+                else:
+                    C.linear_dgrad(dh, wt16, acts[i] if i > 0 else None, dprev, st)
                 dh = dprev
             else:
                 dh = None
@@ -127,10 +134,12 @@ class _FusedMLP(torch.autograd.Function):
         if ctx.x_needs_grad and dh is not None:
             dx = dh if ctx.x_dtype == torch.bfloat16 else dh.to(ctx.x_dtype)
         # parameter gradients were accumulated in place
-        return (dx, None) + (None,) * (2 * L)
+        return (dx, None, None) + (None,) * (2 * L)
 
 
-def fused_mlp(x: torch.Tensor, weights: List[torch.Tensor], biases: List[torch.Tensor]) -> torch.Tensor:
+def fused_mlp(x: torch.Tensor, weights: List[torch.Tensor], biases: List[torch.Tensor],
+              input_grad_cols: int = 0) -> torch.Tensor:
     """x [M, K] (bf16 or fp32, CUDA) -> [M, out_features] fp32.  Parameter gradients are
-    accumulated into ``param.grad`` in place by the backward kernels."""
-    return _FusedMLP.apply(x, len(weights), *weights, *biases)
+    accumulated into ``param.grad`` in place by the backward kernels.  ``input_grad_cols``
+    (a multiple of 8, 0 = all) limits the input gradient to the leading columns of x."""
+    return _FusedMLP.apply(x, len(weights), int(input_grad_cols), *weights, *biases)

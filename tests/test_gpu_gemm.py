@@ -18,7 +18,8 @@ def close(got, want, tol=2e-2):
     return err <= tol * ref, (err, ref)
 
 
-SHAPES = [(300, 400, 432), (128, 16, 64), (4096, 256, 512), (1000, 208, 72), (257, 400, 400)]
+SHAPES = [(300, 400, 432), (128, 16, 64), (4096, 256, 512), (1000, 208, 72), (257, 400, 400), (40001, 400, 432),
+          (30000, 416, 400)]  # the last two take the weight-resident persistent kernel
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
