@@ -229,6 +229,8 @@ class GpuEngine(Engine):
 
     # ------------------------------------------------------------------ housekeeping
     def end_step(self) -> None:
+        if torch.cuda.is_current_stream_capturing():
+            return  # growth checks use events and may reallocate: not inside a graph capture
         self._steps += 1
         for t in self.sparse.values():
             t.poll_growth()
