@@ -1,0 +1,60 @@
+"""Dense-table path: MLP 784-4096-4096-4096-10 (ReLU, cross entropy) on synthetic 28x28 images,
+batch 1024 per GPU, server-side SGD momentum 0.9 lr 0.05, with or without DCT gradient
+compression (keeps the top 25 % by magnitude, threshold refreshed every 1000 steps).
+
+    torchrun --nproc-per-node N -m kraken_b200.benchmarks.dense_dct [--dct] [--steps 30]
+"""
+import argparse
+
+import numpy as np
+import torch
+
+import kraken_b200.pytorch as kk
+from kraken_b200.benchmarks.common import DeviceTimer, emit, world_rank
+from kraken_b200.models import MLP, mnist_like
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("--steps", type=int, default=30)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--batch", type=int, default=1024)
+    p.add_argument("--dct", action="store_true")
+    a = p.parse_args()
+    world, rank = world_rank()
+    kk.initialize("gpu", emitter_type=kk.EmitterType.kDCT if a.dct else kk.EmitterType.kDefault, life_span=1000,
+                  eta=0.75)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(0)
+    model = MLP(784, [4096, 4096, 4096, 10]).to(dev)
+    opt = kk.Optimizer("mnist_mlp", model.named_parameters(), 0.05, kk.SGD(momentum=0.9))
+    rng = np.random.default_rng(100 + rank)
+    means = np.random.default_rng(7).normal(0, 1, (10, 784)).astype(np.float32)
+    total = a.warmup + a.steps
+    batches = [tuple(t.to(dev) for t in mnist_like(rng, means, a.batch)) for _ in range(total)]
+    scale = 1.0 / world
+
+    def step(x, y):
+        loss = torch.nn.functional.cross_entropy(model(x), y) * scale
+        loss.backward()
+        opt.step()
+        return loss
+
+    for i in range(a.warmup):
+        step(*batches[i])
+    kk.native.engine().check()
+    timer = DeviceTimer()
+    timer.start()
+    for i in range(a.warmup, total):
+        loss = step(*batches[i])
+    ms = timer.stop_ms()
+    kk.native.engine().check()
+    n_params = sum(p.numel() for p in model.parameters())
+    emit({"benchmark": "dense_mlp" + ("_dct" if a.dct else ""), "n_gpus": world, "batch_per_gpu": a.batch,
+          "params": n_params, "samples_per_sec": a.batch * world * a.steps / (ms / 1e3), "ms_per_step": ms / a.steps,
+          "final_loss": loss.item() * world})
+    kk.stop()
+
+
+if __name__ == "__main__":
+    main()

@@ -72,9 +72,11 @@ struct DedupScratch {
 
 // ---- dedup + bucketise by owner (unique ids grouped by owner rank) ----
 // cnt[world] is scratch (zeroed here).  Outputs: off[world + 1] (exclusive scan of
-// the per-owner unique counts), uniq[off[world]], inv[n] (occurrence -> unique).
+// the per-owner unique counts), uniq[off[world]], inv[n] (occurrence -> unique).  cap_u is the
+// capacity of uniq and of the buffers later indexed by inv: beyond it the call reports
+// kInboxOverflow and clamps its outputs into range.
 void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
-                     int64_t* uniq, int* inv, int* status, cudaStream_t stream);
+                     int64_t* uniq, int* inv, int cap_u, int* status, cudaStream_t stream);
 
 // ---- sparse pull ----
 void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,

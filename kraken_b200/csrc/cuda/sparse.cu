@@ -186,7 +186,7 @@ dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t 
 __global__ void __launch_bounds__(kThreads)
 dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, unsigned long long* hkeys,
                       const int* __restrict__ hpos, const int* __restrict__ hwin, const int* __restrict__ slot_of,
-                      const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv) {
+                      const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv, int cap_u, int* status) {
   __shared__ int s_off[kMaxWorld + 1];
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -195,8 +195,12 @@ dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_
       acc += cnt[o];
     }
     s_off[world] = acc;
-    if (blockIdx.x == 0)
-      for (int o = 0; o <= world; ++o) off[o] = s_off[o];
+    if (blockIdx.x == 0) {
+      // more unique ids than the exchange buffers hold: report it and clamp, so that no
+      // later kernel indexes past a buffer (the step's result is then invalid, not its memory)
+      if (acc > cap_u) set_status(status, err::kInboxOverflow);
+      for (int o = 0; o <= world; ++o) off[o] = min(s_off[o], cap_u);
+    }
   }
   __syncthreads();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -205,9 +209,9 @@ dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_
   if (id == kEmptyKey) id = kEmptyKey - 1;
   const int slot = slot_of[i];
   const int u = s_off[OwnerOf(salt, id, world)] + hpos[slot];
-  inv[i] = u;
+  inv[i] = u < cap_u ? u : 0;
   if (hwin[slot] == i) {
-    uniq[u] = static_cast<int64_t>(id);
+    if (u < cap_u) uniq[u] = static_cast<int64_t>(id);
     hkeys[slot] = kEmptyKey;  // leave the set empty for the next call
   }
 }
@@ -520,7 +524,7 @@ push_update_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* 
 
 // ------------------------------------------------------------------ launchers
 void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
-                     int64_t* uniq, int* inv, int* status, cudaStream_t stream) {
+                     int64_t* uniq, int* inv, int cap_u, int* status, cudaStream_t stream) {
   const int blocks = (n + kThreads - 1) / kThreads;
   cudaMemsetAsync(cnt, 0, sizeof(int) * world, stream);
   if (n <= 0) {
@@ -531,7 +535,7 @@ void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupS
                                                        sc.hbits, sc.hpos, sc.hwin, sc.slot_of, cnt, status);
   dedup_finalize_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt,
                                                          static_cast<unsigned long long*>(sc.hkeys), sc.hpos, sc.hwin,
-                                                         sc.slot_of, cnt, off, uniq, inv);
+                                                         sc.slot_of, cnt, off, uniq, inv, cap_u, status);
 }
 
 void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,

@@ -51,6 +51,32 @@ class ClickDataset:
         return tuple(t.pin_memory() for t in out) if pin else out
 
 
+class MultiHotDataset:
+    """Batches for the multi-hot model: dense [B, num_dense], one JaggedTensor of B * F bags
+    (sample-major, field-minor) over a 2^40 hashed id space, labels [B]."""
+
+    def __init__(self, num_fields: int = 100, num_dense: int = 13, vocab: int = 1_000_000, zipf_s: float = 1.1,
+                 mean_len: float = 20.0, max_len: int = 100, id_bits: int = 40, seed: int = 0):
+        self.F, self.D, self.vocab, self.s = num_fields, num_dense, int(vocab), float(zipf_s)
+        self.mean_len, self.max_len, self.id_bits = mean_len, max_len, id_bits
+        self.rng = np.random.default_rng(seed)
+        self.w_dense = np.random.default_rng(54321).normal(0.0, 0.1, num_dense).astype(np.float32)
+
+    def batch(self, batch_size: int, pin: bool = False):
+        B, F = batch_size, self.F
+        dense = np.log1p(self.rng.lognormal(0.0, 1.0, (B, self.D))).astype(np.float32)
+        lens = np.clip(self.rng.poisson(self.mean_len, B * F), 1, self.max_len).astype(np.int64)
+        offsets = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        total = int(offsets[-1])
+        field = np.repeat(np.tile(np.arange(F, dtype=np.int64), B), lens)
+        local = zipf_ids(self.rng, total, self.vocab, self.s)
+        ids = (mix64((local + field * self.vocab).view(np.uint64)) & np.uint64((1 << self.id_bits) - 1)).astype(np.int64)
+        logit = dense @ self.w_dense
+        labels = (self.rng.random(B) < 1.0 / (1.0 + np.exp(-logit))).astype(np.float32)
+        out = [torch.from_numpy(dense), torch.from_numpy(ids), torch.from_numpy(offsets), torch.from_numpy(labels)]
+        return [t.pin_memory() for t in out] if pin else out
+
+
 def mnist_like(rng: np.random.Generator, means: np.ndarray, batch_size: int):
     """Images = class mean + N(0, 1) noise over 784 pixels, labels uniform over the classes."""
     y = rng.integers(0, means.shape[0], batch_size)

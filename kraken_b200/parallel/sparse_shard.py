@@ -212,7 +212,10 @@ class SparseChannel:
     """Exchange buffers + kernel sequence of one table."""
 
     def __init__(self, table: GpuSparseTable, rank: int, world: int, max_ids: int, group=None,
-                 spin_limit: int = DEFAULT_SPIN, owner_salt: int = 0, alias_peers: bool = False) -> None:
+                 spin_limit: int = DEFAULT_SPIN, owner_salt: int = 0, alias_peers: bool = False,
+                 max_unique: int = 0) -> None:
+        """max_ids bounds the occurrences of one call, max_unique (default: max_ids) the unique ids
+        among them; the peer inboxes and the gradient buffers are sized by the latter."""
         self.table = table
         self.rank = rank
         self.world = world
@@ -220,14 +223,15 @@ class SparseChannel:
         self.spin = int(spin_limit)
         self.salt = int(owner_salt)
         self.cap = int(max_ids)
+        self.cap_u = int(max_unique) if max_unique and max_unique < max_ids else int(max_ids)
         dim = table.dim
         dev = table.device
 
         lay = Layout()
-        lay.add("inbox_ids", (world, self.cap), torch.int64)
+        lay.add("inbox_ids", (world, self.cap_u), torch.int64)
         lay.add("inbox_meta", (world, 2), torch.int32)
-        lay.add("rows_recv", (self.cap, dim), torch.float32)
-        lay.add("inbox_grad", (world, self.cap, dim), torch.float32)
+        lay.add("rows_recv", (self.cap_u, dim), torch.float32)
+        lay.add("inbox_grad", (world, self.cap_u, dim), torch.float32)
         lay.add("flag_req", (world,), torch.int32)
         lay.add("flag_rsp", (world,), torch.int32)
         lay.add("flag_push", (world,), torch.int32)
@@ -235,8 +239,8 @@ class SparseChannel:
         self.lay = C.ChanLayout()
         for name in ("inbox_ids", "inbox_meta", "rows_recv", "inbox_grad", "flag_req", "flag_rsp", "flag_push"):
             setattr(self.lay, name, lay.offset(name))
-        self.lay.capS = self.cap
-        self.lay.capU = self.cap
+        self.lay.capS = self.cap_u
+        self.lay.capU = self.cap_u
 
         self.ctrl = torch.zeros(8, dtype=torch.int32, device=dev)
         self.hbits = _next_pow2_bits(2 * self.cap)
@@ -246,12 +250,12 @@ class SparseChannel:
         self.slot_of = torch.zeros(self.cap, dtype=torch.int32, device=dev)
         self.cnt = torch.zeros(world, dtype=torch.int32, device=dev)
         self._own_off = torch.zeros(world + 1, dtype=torch.int32, device=dev)
-        self._own_uniq = torch.zeros(self.cap, dtype=torch.int64, device=dev)
+        self._own_uniq = torch.zeros(self.cap_u, dtype=torch.int64, device=dev)
         self._own_inv = torch.zeros(self.cap, dtype=torch.int32, device=dev)
         self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
         self.rows_recv = self.arena.window("rows_recv")
-        self.slot_cache = torch.full((world * self.cap,), -1, dtype=torch.int32, device=dev)
-        self.ugrad = torch.zeros((self.cap, dim), dtype=torch.float32, device=dev)
+        self.slot_cache = torch.full((world * self.cap_u,), -1, dtype=torch.int32, device=dev)
+        self.ugrad = torch.zeros((self.cap_u, dim), dtype=torch.float32, device=dev)
         self.serial = 0
         self.launches = 0  # kernels launched through this channel (for accounting)
 
@@ -270,7 +274,7 @@ class SparseChannel:
         else:
             self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
             C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.hpos, self.hwin, self.slot_of, self.hbits,
-                              self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5])
+                              self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5], self.cap_u)
             self.launches += 2 if n > 0 else 0
         C.pull_dispatch(h, lay, ctrl, self.uniq, self.off, n)
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)

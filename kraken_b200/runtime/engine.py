@@ -33,6 +33,7 @@ class EngineConfig:
     seed: int = 0
     table_capacity: int = 1 << 20    # initial slots per GPU shard (tables grow)
     max_ids_per_call: int = 0        # 0: sized from the first call (2x headroom)
+    max_unique_per_call: int = 0     # 0: same as max_ids_per_call; smaller saves exchange-buffer memory
     spin_limit: int = 1 << 22        # polls before a device-side wait gives up
     saved_dir: str = ""
     max_save_count: int = 3

@@ -156,7 +156,7 @@ class GpuEngine(Engine):
                 dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
                 cap = int(t.item())
         ch = SparseChannel(self.sparse[table_id], self.rank, self.world, cap, self.group, self.cfg.spin_limit,
-                           self._salt(table_id))
+                           self._salt(table_id), max_unique=self.cfg.max_unique_per_call)
         self.channels[table_id] = ch
         return ch
 
