@@ -24,7 +24,7 @@ def main():
     a = p.parse_args()
     world, rank = world_rank()
     max_ids = int(a.batch * a.fields * 21.5)
-    kk.initialize("gpu", table_capacity=1 << 25, max_ids_per_call=max_ids, max_unique_per_call=max(1 << 20, max_ids // 8))
+    kk.initialize("gpu", table_capacity=1 << 25, max_ids_per_call=max_ids, max_unique_per_call=max(1 << 20, max_ids // 3))
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(0)
     model = MultiHotWideAndDeep(a.fields, 13, 64, (1024, 512, 256), mean_fields=range(0, a.fields, 2)).to(dev)

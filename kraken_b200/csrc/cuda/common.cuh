@@ -96,8 +96,8 @@ __device__ __forceinline__ bool last_block_done(uint32_t* counter) {
   return is_last;
 }
 
-// Finds `id`; with insert=true claims a free slot and initialises the value
-// row.  Returns the slot or -1 (absent / table full).
+// Finds `id`; with insert=true claims a free slot (created = true: the caller must have
+// the value row initialised before anyone reads it).  Returns the slot or -1 (absent / table full).
 __device__ __forceinline__ int table_find_or_insert(const TableView& t, uint64_t id, bool insert, bool* created) {
   const uint64_t mask = (1ull << t.bits) - 1;
   uint64_t slot = SlotHash(id, t.bits);
@@ -111,8 +111,6 @@ __device__ __forceinline__ int table_find_or_insert(const TableView& t, uint64_t
       const unsigned long long old = atomicCAS(&t.keys[slot], kEmptyKey, static_cast<unsigned long long>(id));
       if (old == kEmptyKey) {
         *created = true;
-        float* row = t.val + slot * static_cast<uint64_t>(t.dim);
-        InitRow(t.init, t.seed_key, id, t.dim, row);
         return static_cast<int>(slot);
       }
       if (old == id) return static_cast<int>(slot);

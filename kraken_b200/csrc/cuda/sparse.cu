@@ -277,9 +277,48 @@ pull_probe_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, int* slot_ca
         const size_t e = static_cast<size_t>(s) * lay.capS + j;
         const int slot = table_find_or_insert(t, __ldcg(&inbox[e]), insert != 0, &created);
         if (slot < 0 && !insert) set_status(&ctrl->status, err::kSparseIdNotExist);
-        slot_cache[e] = slot;
+        // a row created here is initialised by pull_init_kernel, which finds it by this encoding
+        slot_cache[e] = created ? -(slot + 2) : slot;
       }
       count_created(t, created);
+    }
+  }
+}
+
+// Initialises the rows that pull_probe has just created, `lpr` lanes per row so that the
+// Philox draws and the stores of one row are spread over lanes, and rewrites the entry to the
+// plain slot.  A separate launch: every later reader, including entries of other sources that
+// found the same (new) id, runs after it.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+pull_init_kernel(Sym sym, ChanLayout lay, TableView t, int* slot_cache, int chunks, int lpr) {
+  const unsigned long long* inbox = sym.at<unsigned long long>(sym.rank, lay.inbox_ids);
+  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = gtid % lpr;
+  const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
+  for (int s = 0; s < sym.world; ++s) {
+    const int cnt = __ldcg(&meta[s]).x;
+    for (int r = gtid / lpr; r < cnt; r += row_stride) {
+      const size_t e = static_cast<size_t>(s) * lay.capS + r;
+      const int v = slot_cache[e];
+      if (v >= -1) continue;
+      const int slot = -(v + 2);
+      const uint64_t id = __ldcg(&inbox[e]);
+      float* row = t.val + static_cast<size_t>(slot) * t.dim;
+      for (int c = lane; c < chunks; c += lpr) {
+        float q[4];
+        if (VEC == 4) {
+          InitQuad(t.init, t.seed_key, id, c, t.dim, q);
+          *reinterpret_cast<float4*>(row + c * 4) = make_float4(q[0], q[1], q[2], q[3]);
+        } else {
+          InitQuad(t.init, t.seed_key, id, c >> 2, t.dim, q);
+          row[c] = q[c & 3];
+        }
+      }
+      __syncwarp(group_mask);  // every lane of the row has read the entry before it is rewritten
+      if (lane == 0) slot_cache[e] = slot;
     }
   }
 }
@@ -547,6 +586,13 @@ void pull_probe(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, int* s
                 uint32_t spin_limit, cudaStream_t stream) {
   pull_probe_kernel<<<grid_for(static_cast<long long>(lay.capS)), kThreads, 0, stream>>>(
       to_sym(sym), lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0, spin_limit);
+  if (!insert) return;
+  const RowGeom g = row_geom(table.dim);
+  const int grid = grid_for(static_cast<long long>(lay.capS) * g.lpr);
+  if (g.vec == 4)
+    pull_init_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, to_view(table), slot_cache, g.chunks, g.lpr);
+  else
+    pull_init_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, to_view(table), slot_cache, g.chunks, g.lpr);
 }
 
 void pull_gather(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache,

@@ -278,7 +278,7 @@ class SparseChannel:
             self.launches += 2 if n > 0 else 0
         C.pull_dispatch(h, lay, ctrl, self.uniq, self.off, n)
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)
-        self.launches += 2
+        self.launches += 3 if insert else 2
         self.serial += 1
         return n
 
