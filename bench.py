@@ -39,6 +39,8 @@ def parse():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    p.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                   help="nccl: the NCCL-only baseline path (implies --no-graph)")
     p.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     return p.parse_args()
 
@@ -98,7 +100,9 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
     local_batch = args.global_batch // world
     n_ids = local_batch * NUM_FIELDS
-    kk.initialize("gpu", table_capacity=(1 << 26) // world, max_ids_per_call=n_ids, seed=0)
+    if args.exchange == "nccl":
+        args.no_graph = True
+    kk.initialize("gpu", table_capacity=(1 << 26) // world, max_ids_per_call=n_ids, seed=0, exchange=args.exchange)
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.backends.cuda.matmul.allow_tf32 = True
     torch.backends.cudnn.allow_tf32 = True
@@ -192,7 +196,7 @@ def run_ours(args):
         out = {
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours" if args.exchange == "fused" else "ours-nccl-baseline",
             "config": {"model": "DeepFM 26x1e7 dim16 + MLP 400-400-400-1, Adam lr 1e-3", "global_batch": args.global_batch,
                        "seq_len": NUM_FIELDS, "parallelism": f"dp{world}+row-sharded-tables{world}",
                        "launch": "eager" if args.no_graph else "cuda-graph replay of the whole step",

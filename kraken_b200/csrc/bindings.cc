@@ -907,6 +907,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           check_launch("deepfm_pack_backward");
         });
 
+  m.def("owner_of_cuda", [](const torch::Tensor& ids, uint64_t salt, int world) {
+    need_cuda(ids, "ids", torch::kInt64);
+    torch::Tensor out = torch::empty({ids.numel()}, ids.options().dtype(torch::kInt32));
+    cu::owner_of(ptr<int64_t>(ids), static_cast<int>(ids.numel()), salt, world, ptr<int>(out), cur_stream());
+    check_launch("owner_of");
+    return out;
+  });
+
   // ---------------- table maintenance
   m.def("table_clear", [](const cu::TableHost& t) {
     cu::table_clear(t, cur_stream());

@@ -98,6 +98,9 @@ void push_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const 
 void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache, OptimPOD optim,
                 const float* lr, uint32_t spin_limit, cudaStream_t stream);
 
+// Owner rank of every id under the modulo placement (OwnerOf of core/hash.h).
+void owner_of(const int64_t* ids, int n, uint64_t salt, int world, int* owners, cudaStream_t stream);
+
 // ---- table maintenance ----
 void table_clear(TableHost table, cudaStream_t stream);
 // Inserts rows with given values and states (any of s0..s2 / steps may be null).

@@ -140,7 +140,17 @@ __global__ void table_export_kernel(TableView t, int filter_mode, uint64_t salt,
   }
 }
 
+__global__ void owner_of_kernel(const int64_t* __restrict__ ids, int n, uint64_t salt, int world, int* owners) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) owners[i] = static_cast<int>(OwnerOf(salt, static_cast<uint64_t>(ids[i]), world));
+}
+
 }  // namespace
+
+void owner_of(const int64_t* ids, int n, uint64_t salt, int world, int* owners, cudaStream_t stream) {
+  if (n <= 0) return;
+  owner_of_kernel<<<(n + kThreads - 1) / kThreads, kThreads, 0, stream>>>(ids, n, salt, world, owners);
+}
 
 void table_clear(TableHost table, cudaStream_t stream) {
   table_clear_kernel<<<148 * 4, kThreads, 0, stream>>>(to_view(table));

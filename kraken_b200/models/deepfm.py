@@ -71,7 +71,8 @@ class DeepFM(torch.nn.Module):
 
     def _fused_ok(self, ids: torch.Tensor) -> bool:
         return (self.fused and self.dim % 4 == 0 and ids.dim() == 2 and native.is_initialized()
-                and hasattr(native.engine(), "pull_sparse_unique") and self.mlp.use_tensor_cores)
+                and hasattr(native.engine(), "pull_sparse_unique") and not getattr(native.engine(), "nccl", False)
+                and self.mlp.use_tensor_cores)
 
     def forward(self, dense: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         if self._fused_ok(ids):

@@ -37,11 +37,11 @@ def check_gemm_status(device: torch.device) -> None:
 
 
 def supported(in_features: int, sizes: Sequence[int]) -> bool:
-    """Whether every layer meets the TMA pitch rule (multiples of 8 elements)."""
+    """Whether the hidden layers meet the TMA pitch rule (widths in multiples of 8 elements).
+    The last layer may have any width: 1 runs as a row-dot kernel, a multiple of 8 on the
+    tensor cores, anything else (a 10-class head, say) as a small fp32 matmul."""
     dims = [in_features] + list(sizes)
-    if any(d % 8 != 0 for d in dims[:-1]):
-        return False
-    return dims[-1] == 1 or dims[-1] % 8 == 0
+    return len(sizes) >= 1 and all(d % 8 == 0 for d in dims[:-1])
 
 
 def _grad_target(p: torch.Tensor) -> torch.Tensor:
@@ -73,11 +73,13 @@ class _FusedMLP(torch.autograd.Function):
             counters.add()
             C.rowdot_forward(h, wl.reshape(-1).contiguous(), bl, out)
             out = out.view(M, 1)
-        else:
+        elif wl.shape[0] % 8 == 0:
             y = torch.empty((M, wl.shape[0]), dtype=torch.bfloat16, device=dev)
             counters.add()
             C.linear_forward(h, wl.to(torch.bfloat16), bl, False, y, st)
             out = y.float()
+        else:
+            out = torch.addmm(bl, h.float(), wl.t())  # narrow odd-width head: library fp32 matmul
         ctx.acts, ctx.ws, ctx.bs, ctx.n_layers = acts, ws, bs, n_layers
         ctx.x_needs_grad = x.requires_grad
         ctx.input_grad_cols = input_grad_cols
@@ -99,6 +101,17 @@ class _FusedMLP(torch.autograd.Function):
             counters.add()
             C.rowdot_backward(h_last, wl.detach().reshape(-1).contiguous(), dy, L > 1, dh,
                               _grad_target(wl).view(-1), _grad_target(bs[-1]))
+        elif wl.shape[0] % 8 != 0:
+            g32 = gout.float()
+            h32 = h_last.float()
+            _grad_target(wl).addmm_(g32.t(), h32)
+            _grad_target(bs[-1]).add_(g32.sum(0))
+            dh = None
+            if need_dx_last:
+                d = g32 @ wl.detach()
+                if L > 1:
+                    d = d * (h32 > 0)
+                dh = d.to(torch.bfloat16)
         else:
             dy16 = gout.to(torch.bfloat16).contiguous()
             counters.add()

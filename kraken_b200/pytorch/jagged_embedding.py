@@ -24,7 +24,8 @@ def _pool(embeddings, offsets, weights, mode, patch_value):
 
 
 def _fused_available() -> bool:
-    return native.is_initialized() and hasattr(native.engine(), "pull_sparse_pooled")
+    return (native.is_initialized() and hasattr(native.engine(), "pull_sparse_pooled")
+            and not getattr(native.engine(), "nccl", False))
 
 
 class JaggedEmbedding(torch.nn.Module):

@@ -38,6 +38,7 @@ class EngineConfig:
     saved_dir: str = ""
     max_save_count: int = 3
     owner_salt_per_table: bool = False
+    exchange: str = "fused"          # "fused": peer-memory kernels; "nccl": torch.distributed collectives (baseline)
 
 
 @dataclass

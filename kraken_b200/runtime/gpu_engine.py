@@ -15,6 +15,7 @@ import torch.distributed as dist
 
 from .._native import C
 from ..parallel.dense_bucket import DenseBucket
+from ..parallel.nccl_baseline import NcclSparseChannel
 from ..parallel.sparse_shard import GpuSparseTable, SparseChannel, Ticket
 from .engine import Engine, EngineConfig, TableInfo
 
@@ -38,6 +39,8 @@ class GpuEngine(Engine):
         self._pushed: set = set()
         self._bound = False
         self._steps = 0
+        self.nccl = cfg.exchange == "nccl" and world > 1
+        self.nccl_channels: Dict[int, NcclSparseChannel] = {}
 
     # ------------------------------------------------------------------ registry hooks
     def _on_update_lr(self) -> None:
@@ -68,7 +71,8 @@ class GpuEngine(Engine):
     def _build_bucket(self) -> None:
         ids = self._dense_ids()
         tables = [(tid, int(self.dense_init[tid].numel())) for tid in ids]
-        self.bucket = DenseBucket(tables, self.optim_type, self.optim_conf, self.rank, self.world, self.device,
+        b_rank, b_world = (0, 1) if self.nccl else (self.rank, self.world)
+        self.bucket = DenseBucket(tables, self.optim_type, self.optim_conf, b_rank, b_world, self.device,
                                   self.group, dct=self.cfg.emitter_type == C.EmitterType.kDCT,
                                   life_span=self.cfg.life_span, eta=self.cfg.eta, spin_limit=self.cfg.spin_limit)
         for tid in ids:
@@ -130,6 +134,8 @@ class GpuEngine(Engine):
         """One fused optimizer step over every dense table (bound-parameter path)."""
         b = self._ensure_bucket()
         b.set_active([True] * len(b.table_ids))
+        if self.nccl:
+            dist.all_reduce(b.grad, group=self.group)
         b.step(self.lr_dev)
         self._dense_pending = False
         self._pushed.clear()
@@ -139,6 +145,8 @@ class GpuEngine(Engine):
             return
         b = self.bucket
         b.set_active([tid in self._pushed for tid in b.table_ids])
+        if self.nccl:
+            dist.all_reduce(b.grad, group=self.group)
         b.step(self.lr_dev)
         self._dense_pending = False
         self._pushed.clear()
@@ -170,9 +178,24 @@ class GpuEngine(Engine):
     def _sig(indices: torch.Tensor) -> Tuple[int, int, int]:
         return (indices.data_ptr(), indices.numel(), indices._version)
 
+    def _nccl_channel(self, table_id: int, n: int) -> NcclSparseChannel:
+        ch = self.nccl_channels.get(table_id)
+        if ch is None:
+            cap = self.cfg.max_ids_per_call or max(1024, 2 * n)
+            t = torch.tensor([cap], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            ch = NcclSparseChannel(self.sparse[table_id], self.rank, self.world, int(t.item()), self.group,
+                                   self._salt(table_id), self.cfg.spin_limit)
+            self.nccl_channels[table_id] = ch
+        return ch
+
     def pull_sparse_table(self, table_id: int, indices: torch.Tensor) -> torch.Tensor:
         info = self._table(table_id, "sparse")
         idx = self._prep_ids(indices)
+        if self.nccl:
+            rows = self._nccl_channel(table_id, idx.numel()).pull(idx)
+            self._nccl_ids = {**getattr(self, "_nccl_ids", {}), table_id: (indices.data_ptr(), idx)}
+            return rows.view(*indices.shape, info.dimension)
         ch = self._channel(table_id, idx.numel())
         rows, ticket = ch.pull(idx)
         self.tickets[table_id] = (ticket, *self._sig(indices))
@@ -218,6 +241,11 @@ class GpuEngine(Engine):
         info = self._table(table_id, "sparse")
         if grad.numel() != indices.numel() * info.dimension:
             raise C.KrakenError("gradient shape must be indices.shape + [dimension]")
+        if self.nccl:
+            kept = getattr(self, "_nccl_ids", {}).get(table_id)
+            idx = kept[1] if kept is not None and kept[0] == indices.data_ptr() else self._prep_ids(indices)
+            self._nccl_channel(table_id, idx.numel()).push(idx, grad.detach().to(self.device), self.lr_dev)
+            return
         saved = self.tickets.pop(table_id, None)
         ticket = saved[0] if saved is not None and saved[1:] == self._sig(indices) else None
         idx = None if ticket is not None else self._prep_ids(indices)
@@ -237,7 +265,7 @@ class GpuEngine(Engine):
 
     def check(self) -> None:
         """Raises if any kernel recorded an error (synchronises)."""
-        for ch in self.channels.values():
+        for ch in list(self.channels.values()) + list(self.nccl_channels.values()):
             ch.check()
         for t in self.sparse.values():
             t.check()
@@ -247,6 +275,7 @@ class GpuEngine(Engine):
     def kernel_launches(self) -> int:
         from ..ops import counters
         n = sum(ch.launches for ch in self.channels.values()) + counters.launches()
+        n += sum(ch.local.launches for ch in self.nccl_channels.values())
         if self.bucket is not None:
             n += self.bucket.launches
         return n
@@ -273,8 +302,9 @@ class GpuEngine(Engine):
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier(group=self.group)
-        for ch in self.channels.values():
+        for ch in list(self.channels.values()) + list(self.nccl_channels.values()):
             ch.close()
+        self.nccl_channels.clear()
         if self.bucket is not None:
             self.bucket.close()
         self.channels.clear()

@@ -11,7 +11,8 @@ import kraken_b200.pytorch as kk
 from kraken_b200._native import C
 
 out_dir = sys.argv[1]
-kk.initialize("gpu", seed=3, table_capacity=1 << 12, saved_dir=out_dir)
+EXCHANGE = sys.argv[2] if len(sys.argv) > 2 else "fused"
+kk.initialize("gpu", seed=3, table_capacity=1 << 12, saved_dir=out_dir, exchange=EXCHANGE)
 rank, world = dist.get_rank(), dist.get_world_size()
 dev = torch.device("cuda", torch.cuda.current_device())
 eng = kk.native.engine()
@@ -75,6 +76,10 @@ dist.all_reduce(cnt)
 assert int(cnt.item()) == 200
 if rank == 0:
     print("MULTI_GPU_MATCHES_SINGLE ok")
+
+if EXCHANGE != "fused":
+    kk.stop()
+    sys.exit(0)
 
 # fused bag lookup across ranks
 lens = torch.randint(0, 4, (40,), generator=torch.Generator().manual_seed(rank))

@@ -162,3 +162,29 @@ def test_fused_mlp_matches_fp32_restatement(sizes):
     for layer, dw in zip(mlp.layers, dws):
         ok, info = close(layer.weight.grad, 2 * dw, tol=3e-2)
         assert ok, info
+
+
+def test_fused_mlp_with_odd_width_head():
+    """A 10-class head: hidden layers on the tensor cores, the head as a small fp32 matmul."""
+    from kraken_b200.models.mlp import MLP
+    torch.manual_seed(6)
+    mlp = MLP(784, [256, 128, 10]).to(DEV)
+    assert mlp.use_tensor_cores
+    ws = [l.weight.detach().clone() for l in mlp.layers]
+    bs = [l.bias.detach().clone() for l in mlp.layers]
+    x = torch.randn(500, 784, device=DEV)
+    out = mlp(x)
+    g = torch.randn_like(out)
+    r = lambda t: t.to(torch.bfloat16).float()
+    h0 = r(x)
+    h1 = r((h0 @ r(ws[0]).t() + bs[0]).relu())
+    h2 = r((h1 @ r(ws[1]).t() + bs[1]).relu())
+    want = h2 @ ws[2].t() + bs[2]
+    ok, info = close(out, want, tol=1e-2)
+    assert ok, info
+    out.backward(g)
+    ok, info = close(mlp.layers[2].weight.grad, g.t() @ h2, tol=1e-2)
+    assert ok, info
+    dh2 = r((g @ ws[2]) * (h2 > 0))
+    ok, info = close(mlp.layers[1].weight.grad, dh2.t() @ h1, tol=2e-2)
+    assert ok, info

@@ -27,3 +27,11 @@ def test_gpu_ranks_match_one_shard(world, tmp_path):
     out = run_ranks("mp_gpu_worker.py", world, str(tmp_path))
     for tag in ("MULTI_GPU_MATCHES_SINGLE ok", "MULTI_GPU_BAGS ok", "MULTI_GPU_CHECKPOINT_RESHARD ok"):
         assert tag in out, out[-2000:]
+
+
+def test_nccl_baseline_exchange_matches_one_shard(tmp_path):
+    """The NCCL-only path must give the same tables as the fused path's oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = run_ranks("mp_gpu_worker.py", 2, str(tmp_path), "nccl")
+    assert "MULTI_GPU_MATCHES_SINGLE ok" in out, out[-2000:]
