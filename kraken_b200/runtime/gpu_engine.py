@@ -17,6 +17,7 @@ from .._native import C
 from ..parallel.dense_bucket import DenseBucket
 from ..parallel.nccl_baseline import NcclSparseChannel
 from ..parallel.sparse_shard import GpuSparseTable, SparseChannel, Ticket
+from ..utils import profiler as _profiler
 from .engine import Engine, EngineConfig, TableInfo
 
 
@@ -39,6 +40,7 @@ class GpuEngine(Engine):
         self._pushed: set = set()
         self._bound = False
         self._steps = 0
+        self.profiler = _profiler.from_env(rank)
         self.nccl = cfg.exchange == "nccl" and world > 1
         self.nccl_channels: Dict[int, NcclSparseChannel] = {}
 
@@ -134,11 +136,24 @@ class GpuEngine(Engine):
         """One fused optimizer step over every dense table (bound-parameter path)."""
         b = self._ensure_bucket()
         b.set_active([True] * len(b.table_ids))
-        if self.nccl:
-            dist.all_reduce(b.grad, group=self.group)
-        b.step(self.lr_dev)
+        with self._region("dense_step"):
+            if self.nccl:
+                dist.all_reduce(b.grad, group=self.group)
+            b.step(self.lr_dev)
         self._dense_pending = False
         self._pushed.clear()
+
+    def _region(self, name: str):
+        import contextlib
+        return self.profiler.region(name) if self.profiler is not None else contextlib.nullcontext()
+
+    def metrics(self) -> dict:
+        """Counters of the shards (synchronises): rows and load factor per sparse table."""
+        out = {}
+        for tid, t in self.sparse.items():
+            rows = t.num_rows()
+            out[self.tables[tid].name] = {"rows": rows, "capacity": t.capacity, "load_factor": rows / t.capacity}
+        return out
 
     def _flush_dense(self) -> None:
         if not self._dense_pending:
@@ -197,7 +212,8 @@ class GpuEngine(Engine):
             self._nccl_ids = {**getattr(self, "_nccl_ids", {}), table_id: (indices.data_ptr(), idx)}
             return rows.view(*indices.shape, info.dimension)
         ch = self._channel(table_id, idx.numel())
-        rows, ticket = ch.pull(idx)
+        with self._region("pull"):
+            rows, ticket = ch.pull(idx)
         self.tickets[table_id] = (ticket, *self._sig(indices))
         return rows.view(*indices.shape, info.dimension)
 
@@ -253,13 +269,16 @@ class GpuEngine(Engine):
         g = grad.detach()
         if g.device != self.device:
             g = g.to(self.device)
-        ch.push(g, self.lr_dev, ticket=ticket, ids=idx)
+        with self._region("push"):
+            ch.push(g, self.lr_dev, ticket=ticket, ids=idx)
 
     # ------------------------------------------------------------------ housekeeping
     def end_step(self) -> None:
         if torch.cuda.is_current_stream_capturing():
             return  # growth checks use events and may reallocate: not inside a graph capture
         self._steps += 1
+        if self.profiler is not None:
+            self.profiler.end_step()
         for t in self.sparse.values():
             t.poll_growth()
 
@@ -299,6 +318,8 @@ class GpuEngine(Engine):
     def stop(self) -> None:
         if self.stopped:
             return
+        if self.profiler is not None:
+            self.profiler.close()
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier(group=self.group)

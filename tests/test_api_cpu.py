@@ -166,3 +166,21 @@ def run_ranks(script: str, world: int, *args: str, timeout: int = 300) -> str:
 def test_two_cpu_ranks_match_one_rank(tmp_path):
     out = run_ranks("mp_cpu_worker.py", 2, str(tmp_path))
     assert "RANKS_MATCH_SINGLE ok" in out and "RESHARD ok" in out
+
+
+def test_step_profiler_records_regions(tmp_path):
+    from kraken_b200.utils.profiler import StepProfiler
+    path = tmp_path / "prof.jsonl"
+    prof = StepProfiler(str(path), rank=0, lag=1)
+    for step in range(3):
+        with prof.region("pull"):
+            sum(range(1000))
+        with prof.region("pull"):
+            pass
+        prof.count("unique_ids", 5)
+        prof.end_step()
+    prof.close()
+    import json
+    recs = [json.loads(l) for l in open(path)]
+    assert [r["step"] for r in recs] == [0, 1, 2] and all(r["pull_ms"] >= 0 and r["unique_ids"] == 5 for r in recs)
+    assert "pull_ms" in prof.summary()
