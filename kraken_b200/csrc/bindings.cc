@@ -866,33 +866,45 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     check_launch("pull_wait");
   });
   m.def("deepfm_pack_forward",
-        [](const torch::Tensor& rows2, const torch::Tensor& inv2, const torch::Tensor& rows1, const torch::Tensor& inv1,
-           const torch::Tensor& dense, int B, int F, const torch::Tensor& x, const torch::Tensor& fm_logit) {
+        [](const torch::Tensor& rows2, const torch::Tensor& inv2, const c10::optional<torch::Tensor>& rows1,
+           const c10::optional<torch::Tensor>& inv1, const torch::Tensor& dense, int B, int F, int D,
+           const torch::Tensor& x, const torch::Tensor& fm_logit) {
           need_cuda(rows2, "rows2", torch::kFloat32);
-          need_cuda(rows1, "rows1", torch::kFloat32);
           need_cuda(dense, "dense", torch::kFloat32);
           need_cuda(x, "x", torch::kBFloat16);
           need_cuda(fm_logit, "fm_logit", torch::kFloat32);
-          const int D = rows2.size(1), ND = dense.size(1), ldx = x.size(1);
-          TORCH_CHECK(D % 4 == 0 && rows1.size(1) == 1, "second-order dim must be a multiple of 4, first-order dim 1");
-          TORCH_CHECK(inv2.numel() >= static_cast<int64_t>(B) * F && inv1.numel() >= static_cast<int64_t>(B) * F,
-                      "occurrence maps too small");
+          const int RD = rows2.size(1), ND = dense.size(1), ldx = x.size(1);
+          TORCH_CHECK(D % 4 == 0 && RD % 4 == 0 && RD >= D, "row widths must be multiples of 4");
+          if (rows1.has_value()) {
+            need_cuda(*rows1, "rows1", torch::kFloat32);
+            TORCH_CHECK(rows1->size(1) == 1 && inv1.has_value() && inv1->numel() >= static_cast<int64_t>(B) * F,
+                        "first-order table must have dim 1 and its own occurrence map");
+          } else {
+            TORCH_CHECK(RD >= D + 1, "folded layout needs a column for the first-order weight");
+          }
+          TORCH_CHECK(inv2.numel() >= static_cast<int64_t>(B) * F, "occurrence map too small");
           TORCH_CHECK(x.size(0) == B && ldx >= F * D + ND && ldx % 4 == 0 && dense.size(0) == B && fm_logit.numel() == B,
                       "deepfm_pack_forward: shape mismatch");
-          cu::deepfm_pack_forward(ptr<float>(rows2), ptr<int>(inv2), ptr<float>(rows1), ptr<int>(inv1),
-                                  ptr<float>(dense), B, F, D, ND, reinterpret_cast<__nv_bfloat16*>(x.data_ptr()), ldx,
+          cu::deepfm_pack_forward(ptr<float>(rows2), ptr<int>(inv2), optr<float>(rows1), optr<int>(inv1),
+                                  ptr<float>(dense), B, F, D, RD, ND, reinterpret_cast<__nv_bfloat16*>(x.data_ptr()), ldx,
                                   ptr<float>(fm_logit), cur_stream());
           check_launch("deepfm_pack_forward");
         });
   m.def("deepfm_pack_backward",
-        [](const torch::Tensor& rows2, const torch::Tensor& inv2, const torch::Tensor& inv1,
-           const c10::optional<torch::Tensor>& dx, const torch::Tensor& dlogit, int B, int F, const torch::Tensor& ugrad2,
-           const torch::Tensor& ugrad1) {
+        [](const torch::Tensor& rows2, const torch::Tensor& inv2, const c10::optional<torch::Tensor>& inv1,
+           const c10::optional<torch::Tensor>& dx, const torch::Tensor& dlogit, int B, int F, int D,
+           const torch::Tensor& ugrad2, const c10::optional<torch::Tensor>& ugrad1) {
           need_cuda(rows2, "rows2", torch::kFloat32);
           need_cuda(dlogit, "dlogit", torch::kFloat32);
           need_cuda(ugrad2, "ugrad2", torch::kFloat32);
-          need_cuda(ugrad1, "ugrad1", torch::kFloat32);
-          const int D = rows2.size(1);
+          const int RD = rows2.size(1);
+          TORCH_CHECK(ugrad2.size(1) == RD && D % 4 == 0 && RD % 4 == 0, "gradient buffer must match the row width");
+          if (ugrad1.has_value()) {
+            need_cuda(*ugrad1, "ugrad1", torch::kFloat32);
+            TORCH_CHECK(inv1.has_value(), "separate first-order table needs its occurrence map");
+          } else {
+            TORCH_CHECK(RD >= D + 1, "folded layout needs a column for the first-order weight");
+          }
           const __nv_bfloat16* dxp = nullptr;
           int lddx = 0;
           if (dx.has_value()) {
@@ -901,19 +913,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
             dxp = reinterpret_cast<const __nv_bfloat16*>(dx->data_ptr());
             lddx = dx->size(1);
           }
-          TORCH_CHECK(dlogit.numel() == B && D % 4 == 0, "deepfm_pack_backward: shape mismatch");
-          cu::deepfm_pack_backward(ptr<float>(rows2), ptr<int>(inv2), ptr<int>(inv1), dxp, lddx, ptr<float>(dlogit), B, F,
-                                   D, ptr<float>(ugrad2), ptr<float>(ugrad1), cur_stream());
+          TORCH_CHECK(dlogit.numel() == B, "deepfm_pack_backward: shape mismatch");
+          cu::deepfm_pack_backward(ptr<float>(rows2), ptr<int>(inv2), optr<int>(inv1), dxp, lddx, ptr<float>(dlogit), B, F,
+                                   D, RD, ptr<float>(ugrad2), optr<float>(ugrad1), cur_stream());
           check_launch("deepfm_pack_backward");
         });
-
-  m.def("owner_of_cuda", [](const torch::Tensor& ids, uint64_t salt, int world) {
-    need_cuda(ids, "ids", torch::kInt64);
-    torch::Tensor out = torch::empty({ids.numel()}, ids.options().dtype(torch::kInt32));
-    cu::owner_of(ptr<int64_t>(ids), static_cast<int>(ids.numel()), salt, world, ptr<int>(out), cur_stream());
-    check_launch("owner_of");
-    return out;
-  });
 
   // ---------------- table maintenance
   m.def("table_clear", [](const cu::TableHost& t) {

@@ -1,5 +1,9 @@
 // DeepFM front end fused around the sparse exchange.
 //
+// Two table layouts are accepted: a dim-D embedding table plus a separate dim-1 first-order
+// table, or ONE table whose rows are RD >= D + 1 floats wide with the first-order weight in
+// column D (rows1 / ugrad1 null): the second costs one exchange per step instead of two.
+//
 // Forward: reads the UNIQUE rows that the pull left in the receive buffers (second-order
 // table [U2, D] and first-order table [U1, 1]) through the occurrence -> unique maps and, in
 // one pass per sample, writes the bf16 MLP input [emb | dense | 0-pad] and the fp32 FM logit
@@ -33,7 +37,7 @@ __global__ void pull_wait_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, uint32_t s
 __global__ void __launch_bounds__(kThreads)
 deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restrict__ inv2,
                            const float* __restrict__ rows1, const int* __restrict__ inv1,
-                           const float* __restrict__ dense, int B, int F, int D, int ND, int lpr,
+                           const float* __restrict__ dense, int B, int F, int D, int RD, int ND, int lpr,
                            __nv_bfloat16* __restrict__ x, int ldx, float* __restrict__ fm_logit) {
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
@@ -50,7 +54,7 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
       for (int c = lane; c < chunks; c += lpr) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = s;
         for (int f = 0; f < F; ++f) {
-          const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * D) + c);
+          const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
           s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
           q.x += e.x * e.x, q.y += e.y * e.y, q.z += e.z * e.z, q.w += e.w * e.w;
           __nv_bfloat162 lo = __floats2bfloat162_rn(e.x, e.y), hi = __floats2bfloat162_rn(e.z, e.w);
@@ -62,8 +66,13 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
         part += 0.5f * (s.x * s.x - q.x + s.y * s.y - q.y + s.z * s.z - q.z + s.w * s.w - q.w);
       }
       // first-order weights, dense features and the zero pad, spread over the sample's lanes
-      const int* i1 = inv1 + static_cast<size_t>(b) * F;
-      for (int f = lane; f < F; f += lpr) part += __ldcg(rows1 + i1[f]);
+      if (rows1 != nullptr) {
+        const int* i1 = inv1 + static_cast<size_t>(b) * F;
+        for (int f = lane; f < F; f += lpr) part += __ldcg(rows1 + i1[f]);
+      } else {
+        // folded layout: column D of the same row is the field's first-order weight
+        for (int f = lane; f < F; f += lpr) part += __ldcg(rows2 + static_cast<size_t>(i2[f]) * RD + D);
+      }
       const int base = F * D;
       for (int j = lane; base + j < ldx; j += lpr)
         xr[base + j] = __float2bfloat16(j < ND ? dense[static_cast<size_t>(b) * ND + j] : 0.f);
@@ -76,7 +85,7 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
 __global__ void __launch_bounds__(kThreads)
 deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restrict__ inv2,
                             const int* __restrict__ inv1, const __nv_bfloat16* __restrict__ dx, int lddx,
-                            const float* __restrict__ dlogit, int B, int F, int D, int lpr, float* ugrad2,
+                            const float* __restrict__ dlogit, int B, int F, int D, int RD, int lpr, float* ugrad2,
                             float* ugrad1) {
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
@@ -89,11 +98,11 @@ deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restri
     for (int c = lane; c < chunks; c += lpr) {
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int f = 0; f < F; ++f) {
-        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * D) + c);
+        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
         s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
       }
       for (int f = 0; f < F; ++f) {
-        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * D) + c);
+        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
         float4 d = make_float4(g * (s.x - e.x), g * (s.y - e.y), g * (s.z - e.z), g * (s.w - e.w));
         if (dxr) {
           const uint2 p = *reinterpret_cast<const uint2*>(dxr + f * D + c * 4);
@@ -102,11 +111,15 @@ deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restri
           d.x += __bfloat162float(lo.x), d.y += __bfloat162float(lo.y);
           d.z += __bfloat162float(hi.x), d.w += __bfloat162float(hi.y);
         }
-        red_add_v4(ugrad2 + static_cast<size_t>(i2[f]) * D + c * 4, d);
+        red_add_v4(ugrad2 + static_cast<size_t>(i2[f]) * RD + c * 4, d);
       }
     }
-    const int* i1 = inv1 + static_cast<size_t>(b) * F;
-    for (int f = lane; f < F; f += lpr) atomicAdd(ugrad1 + i1[f], g);
+    if (ugrad1 != nullptr) {
+      const int* i1 = inv1 + static_cast<size_t>(b) * F;
+      for (int f = lane; f < F; f += lpr) atomicAdd(ugrad1 + i1[f], g);
+    } else {
+      for (int f = lane; f < F; f += lpr) atomicAdd(ugrad2 + static_cast<size_t>(i2[f]) * RD + D, g);
+    }
   }
 }
 
@@ -138,21 +151,21 @@ void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cud
 }
 
 void deepfm_pack_forward(const float* rows2, const int* inv2, const float* rows1, const int* inv1, const float* dense,
-                         int B, int F, int D, int ND, __nv_bfloat16* x, int ldx, float* fm_logit,
+                         int B, int F, int D, int RD, int ND, __nv_bfloat16* x, int ldx, float* fm_logit,
                          cudaStream_t stream) {
   if (B <= 0) return;
   const int lpr = lanes_for_chunks(D / 4);
-  deepfm_pack_forward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, rows1, inv1, dense, B, F, D, ND,
-                                                                        lpr, x, ldx, fm_logit);
+  deepfm_pack_forward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, rows1, inv1, dense, B, F, D, RD,
+                                                                        ND, lpr, x, ldx, fm_logit);
 }
 
 void deepfm_pack_backward(const float* rows2, const int* inv2, const int* inv1, const __nv_bfloat16* dx, int lddx,
-                          const float* dlogit, int B, int F, int D, float* ugrad2, float* ugrad1,
+                          const float* dlogit, int B, int F, int D, int RD, float* ugrad2, float* ugrad1,
                           cudaStream_t stream) {
   if (B <= 0) return;
   const int lpr = lanes_for_chunks(D / 4);
   deepfm_pack_backward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, inv1, dx, lddx, dlogit, B, F, D,
-                                                                         lpr, ugrad2, ugrad1);
+                                                                         RD, lpr, ugrad2, ugrad1);
 }
 
 }  // namespace cu

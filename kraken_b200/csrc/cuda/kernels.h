@@ -131,12 +131,15 @@ void bce_forward_backward(const float* logits, const float* labels, int n, float
 // Waits (bounded) until every owner has answered the channel's current pull.
 void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cudaStream_t stream);
 // x[B, ldx] bf16 = [emb rows of F fields x D | ND dense features | zeros], fm_logit[B] fp32.
-// rows2 [*, D] / rows1 [*, 1] are unique rows, inv2 / inv1 [B * F] map occurrences to them.  D % 4 == 0.
+// rows2 [*, RD] / rows1 [*, 1] are unique rows, inv2 / inv1 [B * F] map occurrences to them.  D % 4 == 0,
+// RD % 4 == 0.  rows1 == nullptr: the first-order weight is column D of rows2 (RD >= D + 1).
 void deepfm_pack_forward(const float* rows2, const int* inv2, const float* rows1, const int* inv1, const float* dense,
-                         int B, int F, int D, int ND, __nv_bfloat16* x, int ldx, float* fm_logit, cudaStream_t stream);
-// Adds each occurrence's gradient into ugrad2 [*, D] / ugrad1 [*, 1] (per unique id).  dx may be null.
+                         int B, int F, int D, int RD, int ND, __nv_bfloat16* x, int ldx, float* fm_logit,
+                         cudaStream_t stream);
+// Adds each occurrence's gradient into ugrad2 [*, RD] / ugrad1 [*, 1] (per unique id).  dx may be null;
+// ugrad1 == nullptr: the first-order gradient goes to column D of ugrad2.
 void deepfm_pack_backward(const float* rows2, const int* inv2, const int* inv1, const __nv_bfloat16* dx, int lddx,
-                          const float* dlogit, int B, int F, int D, float* ugrad2, float* ugrad1,
+                          const float* dlogit, int B, int F, int D, int RD, float* ugrad2, float* ugrad1,
                           cudaStream_t stream);
 
 // Linear layer with one output over bf16 rows x[M, K] (pitch ldx): y[m] = x[m, :] . w + bias[0].

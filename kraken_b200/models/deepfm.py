@@ -21,47 +21,70 @@ from .. import pytorch as kk
 from .._native import C
 from ..ops import counters, fm_interaction
 from ..pytorch import native
+from ..utils.profiler import engine_region
 from .mlp import MLP
 
 
 class _DeepFMFront(torch.autograd.Function):
+    """Pull (one shared dedup) -> pack kernel -> (bf16 MLP input, fp32 FM logit); the backward
+    kernel adds every occurrence's gradient into the push buffers.  ``first_table`` is None in
+    the folded layout (first-order weight in column ``dim`` of the embedding rows)."""
+
     @staticmethod
-    def forward(ctx, first_table, second_table, dense, ids, width):
+    def forward(ctx, second_table, first_table, dense, ids, width, dim):
         eng = native.engine()
-        id1, id2 = first_table.table_id(), second_table.table_id()
+        id2 = second_table.table_id()
+        id1 = first_table.table_id() if first_table is not None else None
         B, F = ids.shape
         rows2, inv2, t2 = eng.pull_sparse_unique(id2, ids)
-        rows1, inv1, t1 = eng.pull_sparse_unique(id1, ids, share_with=id2)
+        rows1 = inv1 = t1 = None
+        if id1 is not None:
+            rows1, inv1, t1 = eng.pull_sparse_unique(id1, ids, share_with=id2)
         x = torch.empty((B, width), dtype=torch.bfloat16, device=rows2.device)
         fm = torch.empty(B, dtype=torch.float32, device=rows2.device)
         dense = dense.to(rows2.device, torch.float32).contiguous()
         counters.add()
-        C.deepfm_pack_forward(rows2, inv2, rows1, inv1, dense, B, F, x, fm)
-        ctx.state = (eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F)
+        with engine_region("pack_fwd"):
+            C.deepfm_pack_forward(rows2, inv2, rows1, inv1, dense, B, F, dim, x, fm)
+        ctx.state = (eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F, dim)
         return x, fm
 
     @staticmethod
     def backward(ctx, dx, dfm):
-        eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F = ctx.state
+        eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F, dim = ctx.state
         if dfm is None:
             dfm = torch.zeros(B, dtype=torch.float32, device=rows2.device)
         counters.add()
-        C.deepfm_pack_backward(rows2, inv2, inv1, dx.contiguous() if dx is not None else None,
-                               dfm.float().contiguous(), B, F, eng.grad_accumulator(id2), eng.grad_accumulator(id1))
-        eng.push_sparse_accumulated(id1, t1)
+        with engine_region("pack_bwd"):
+            C.deepfm_pack_backward(rows2, inv2, inv1, dx.contiguous() if dx is not None else None,
+                                   dfm.float().contiguous(), B, F, dim, eng.grad_accumulator(id2),
+                                   eng.grad_accumulator(id1) if id1 is not None else None)
+        if id1 is not None:
+            eng.push_sparse_accumulated(id1, t1)
         eng.push_sparse_accumulated(id2, t2)
-        return None, None, None, None, None
+        return None, None, None, None, None, None
 
 
 class DeepFM(torch.nn.Module):
     def __init__(self, num_fields: int = 26, num_dense: int = 13, dim: int = 16,
                  hidden: Sequence[int] = (400, 400, 400), init_std: float = 0.01, name: str = "deepfm",
-                 fused: bool = True):
+                 fused: bool = True, fold_first_order: bool = False):
+        """fold_first_order: keep each id's first-order weight in the same table row as its
+        embedding (row = dim embedding floats + 1 weight, padded to a multiple of 4), so a step
+        needs one sparse exchange instead of two.  Only the fused GPU path reads that layout."""
         super().__init__()
         self.num_fields, self.num_dense, self.dim = num_fields, num_dense, dim
-        self.first_order = kk.Embedding(1, initializer=kk.ConstantInitializer(0.0), name=f"{name}.first_order")
-        self.second_order = kk.Embedding(dim, initializer=kk.NormalInitializer(0.0, init_std),
-                                         name=f"{name}.second_order")
+        self.fold = bool(fold_first_order)
+        if self.fold:
+            self.row_dim = (dim + 1 + 3) // 4 * 4
+            self.first_order = None
+            self.second_order = kk.Embedding(self.row_dim, initializer=kk.NormalInitializer(0.0, init_std),
+                                             name=f"{name}.embedding_and_first_order")
+        else:
+            self.row_dim = dim
+            self.first_order = kk.Embedding(1, initializer=kk.ConstantInitializer(0.0), name=f"{name}.first_order")
+            self.second_order = kk.Embedding(dim, initializer=kk.NormalInitializer(0.0, init_std),
+                                             name=f"{name}.second_order")
         width = num_fields * dim + num_dense
         self.mlp_in = (width + 7) // 8 * 8  # padded: the tensor-core path wants pitches in multiples of 8
         self.pad = self.mlp_in - width
@@ -76,14 +99,18 @@ class DeepFM(torch.nn.Module):
 
     def forward(self, dense: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         if self._fused_ok(ids):
-            x, fm = _DeepFMFront.apply(self.first_order.sparse_table, self.second_order.sparse_table, dense, ids,
-                                       self.mlp_in)
+            first = self.first_order.sparse_table if self.first_order is not None else None
+            x, fm = _DeepFMFront.apply(self.second_order.sparse_table, first, dense, ids, self.mlp_in, self.dim)
             return fm + self.mlp(x, input_grad_cols=self.num_fields * self.dim).squeeze(-1) + self.bias
-        w = self.first_order(ids)       # [B, F, 1]
-        e = self.second_order(ids)      # [B, F, dim]
+        if self.fold:
+            rows = self.second_order(ids)                    # [B, F, row_dim]
+            e, w = rows[..., :self.dim], rows[..., self.dim:self.dim + 1]
+        else:
+            w = self.first_order(ids)   # [B, F, 1]
+            e = self.second_order(ids)  # [B, F, dim]
         dense = dense.to(e.device)
         parts = [e.flatten(1), dense]
         if self.pad:
             parts.append(torch.zeros(dense.shape[0], self.pad, dtype=e.dtype, device=e.device))
         deep = self.mlp(torch.cat(parts, dim=1)).squeeze(-1)
-        return w.sum(dim=(1, 2)) + fm_interaction(e) + deep + self.bias
+        return w.sum(dim=(1, 2)) + fm_interaction(e.contiguous()) + deep + self.bias

@@ -88,6 +88,12 @@ class _FusedMLP(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gout):
+        from ..utils.profiler import engine_region
+        with engine_region("mlp_bwd"):
+            return _FusedMLP._backward(ctx, gout)
+
+    @staticmethod
+    def _backward(ctx, gout):
         acts, ws, bs, L = ctx.acts, ctx.ws, ctx.bs, ctx.n_layers
         dev = gout.device
         st = gemm_status(dev)
@@ -155,4 +161,6 @@ def fused_mlp(x: torch.Tensor, weights: List[torch.Tensor], biases: List[torch.T
     """x [M, K] (bf16 or fp32, CUDA) -> [M, out_features] fp32.  Parameter gradients are
     accumulated into ``param.grad`` in place by the backward kernels.  ``input_grad_cols``
     (a multiple of 8, 0 = all) limits the input gradient to the leading columns of x."""
-    return _FusedMLP.apply(x, len(weights), int(input_grad_cols), *weights, *biases)
+    from ..utils.profiler import engine_region
+    with engine_region("mlp_fwd"):
+        return _FusedMLP.apply(x, len(weights), int(input_grad_cols), *weights, *biases)

@@ -244,14 +244,16 @@ class GpuEngine(Engine):
         idx = self._prep_ids(indices)
         ch = self._channel(table_id, idx.numel())
         share = self.channels.get(share_with) if share_with is not None else None
-        return ch.pull_unique(idx, share_from=share)
+        with self._region("pull"):
+            return ch.pull_unique(idx, share_from=share)
 
     def grad_accumulator(self, table_id: int) -> torch.Tensor:
         """Per-unique-id gradient buffer [cap, dim] of the table's channel (zero between steps)."""
         return self.channels[table_id].ugrad
 
     def push_sparse_accumulated(self, table_id: int, ticket: Ticket) -> None:
-        self.channels[table_id].push_accumulated(self.lr_dev, ticket)
+        with self._region("push"):
+            self.channels[table_id].push_accumulated(self.lr_dev, ticket)
 
     def push_sparse_table(self, table_id: int, indices: torch.Tensor, grad: torch.Tensor) -> None:
         info = self._table(table_id, "sparse")

@@ -106,3 +106,13 @@ def from_env(rank: int = 0) -> Optional[StepProfiler]:
         root, ext = os.path.splitext(path)
         path = f"{root}.rank{rank}{ext}"
     return StepProfiler(path, rank)
+
+
+def engine_region(name: str):
+    """Region of the process-global engine's profiler, or a no-op when profiling is off."""
+    from ..pytorch import native
+    if native.is_initialized():
+        prof = getattr(native.engine(), "profiler", None)
+        if prof is not None:
+            return prof.region(name)
+    return contextlib.nullcontext()

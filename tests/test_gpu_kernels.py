@@ -257,10 +257,11 @@ def test_fused_deepfm_matches_unfused_path():
     from kraken_b200.models import ClickDataset, DeepFM
     from kraken_b200.ops import bce_with_logits
 
-    def run(fused):
+    def run(fused, fold=False):
         kk.initialize("gpu", seed=21, table_capacity=1 << 14)
         torch.manual_seed(0)
-        model = DeepFM(num_fields=6, num_dense=13, dim=16, hidden=(64, 32), init_std=0.1, fused=fused).to(DEV)
+        model = DeepFM(num_fields=6, num_dense=13, dim=16, hidden=(64, 32), init_std=0.1, fused=fused,
+                       fold_first_order=fold).to(DEV)
         model.mlp.use_tensor_cores = fused
         opt = kk.Optimizer("m", model.named_parameters(), 5e-2, kk.SGD())  # SGD: Adam would amplify sign noise of tiny gradients
         data = ClickDataset(num_fields=6, vocab=500, seed=9)
@@ -274,7 +275,9 @@ def test_fused_deepfm_matches_unfused_path():
         kk.native.engine().check()
         probe = torch.arange(0, 3000, 7, device=DEV)
         rows = kk.pull_sparse_table(model.second_order.sparse_table.table_id(), probe).cpu()
-        first = kk.pull_sparse_table(model.first_order.sparse_table.table_id(), probe).cpu()
+        first = (kk.pull_sparse_table(model.first_order.sparse_table.table_id(), probe).cpu() if not fold
+                 else rows[:, 16:17].clone())
+        rows = rows[:, :16]
         w = model.mlp.layers[0].weight.detach().cpu().clone()
         kk.stop()
         return losses, rows, first, w
@@ -284,3 +287,8 @@ def test_fused_deepfm_matches_unfused_path():
     assert all(abs(a - b) < 5e-3 for a, b in zip(l1, l0)), (l1, l0)
     assert (r1 - r0).abs().max().item() < 2e-2 and (f1 - f0).abs().max().item() < 2e-2
     assert (w1 - w0).abs().max().item() < 2e-2
+    # folded layout (first-order weight inside the embedding row): fused and unfused agree too
+    l3, r3, f3, w3 = run(True, fold=True)
+    l2, r2, f2, w2 = run(False, fold=True)
+    assert all(abs(a - b) < 5e-3 for a, b in zip(l3, l2)), (l3, l2)
+    assert (r3 - r2).abs().max().item() < 2e-2 and (f3 - f2).abs().max().item() < 2e-2
