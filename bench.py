@@ -122,7 +122,9 @@ def run_ours(args):
 
     def eager_step(dense, ids, labels):
         logits = model(dense, ids)
-        loss = bce_with_logits(logits, labels) * inv_world
+        loss = bce_with_logits(logits, labels)
+        if world > 1:
+            loss = loss * inv_world
         loss.backward()
         opt.step()
         return loss

@@ -149,15 +149,19 @@ void bind_dense(py::module_& m) {
     check_launch("colsum_bf16");
   });
   m.def("rowdot_forward", [bf, need_bf16](const torch::Tensor& x, const torch::Tensor& w,
-                                          const c10::optional<torch::Tensor>& bias, const torch::Tensor& y) {
+                                          const c10::optional<torch::Tensor>& bias, const torch::Tensor& y,
+                                          const c10::optional<torch::Tensor>& addend) {
     need_bf16(x, "x");
     TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kFloat32 && w.is_contiguous() && w.numel() == x.size(1),
                 "w must be a contiguous CUDA f32 vector of K elements");
     TORCH_CHECK(y.scalar_type() == torch::kFloat32 && y.numel() == x.size(0) && (x.stride(0) % 2) == 0, "bad y / pitch");
-    cu::rowdot_forward(bf(x), x.stride(0), w.data_ptr<float>(), optr<float>(bias), x.size(0), x.size(1),
-                       y.data_ptr<float>(), cur_stream());
+    TORCH_CHECK(!addend.has_value() || (addend->is_cuda() && addend->scalar_type() == torch::kFloat32 &&
+                                        addend->is_contiguous() && addend->numel() == x.size(0)),
+                "addend must be a contiguous CUDA f32 vector of M elements");
+    cu::rowdot_forward(bf(x), x.stride(0), w.data_ptr<float>(), optr<float>(bias), optr<float>(addend), x.size(0),
+                       x.size(1), y.data_ptr<float>(), cur_stream());
     check_launch("rowdot_forward");
-  });
+  }, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("y"), py::arg("addend") = py::none());
   m.def("rowdot_backward", [bf, need_bf16](const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& dy,
                                            bool relu_mask, const c10::optional<torch::Tensor>& dx,
                                            const torch::Tensor& dw, const c10::optional<torch::Tensor>& db) {
@@ -176,5 +180,16 @@ void bind_dense(py::module_& m) {
     cu::rowdot_backward(bf(x), x.stride(0), w.data_ptr<float>(), dy.data_ptr<float>(), x.size(0), x.size(1), relu_mask,
                         dxp, lddx, dw.data_ptr<float>(), optr<float>(db), cur_stream());
     check_launch("rowdot_backward");
+  });
+  m.def("cast_w_wt", [](const torch::Tensor& w) {
+    TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kFloat32 && w.dim() == 2 && w.is_contiguous(),
+                "w must be a contiguous 2-D CUDA f32 tensor");
+    const int N = w.size(0), K = w.size(1);
+    torch::Tensor w16 = torch::empty({N, K}, w.options().dtype(torch::kBFloat16));
+    torch::Tensor wt16 = torch::empty({K, N}, w.options().dtype(torch::kBFloat16));
+    cu::cast_w_wt(w.data_ptr<float>(), N, K, reinterpret_cast<__nv_bfloat16*>(w16.data_ptr()),
+                  reinterpret_cast<__nv_bfloat16*>(wt16.data_ptr()), cur_stream());
+    check_launch("cast_w_wt");
+    return std::make_pair(w16, wt16);
   });
 }

@@ -82,17 +82,21 @@ __device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
 // Marks the calling block as finished; returns true in exactly one block: the
 // last one of the grid to arrive.  All of the grid's earlier global / peer
 // stores are then visible system-wide to whoever observes a later release store.
+// One thread per block fences, after the block barrier: the barrier orders the
+// block's stores before that thread, and its fence is cumulative over them.
 __device__ __forceinline__ bool last_block_done(uint32_t* counter) {
   __shared__ bool is_last;
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const uint32_t prev = atomicAdd(counter, 1u);
     is_last = (prev == gridDim.x - 1);
-    if (is_last) *counter = 0;
+    if (is_last) {
+      *counter = 0;
+      __threadfence_system();
+    }
   }
   __syncthreads();
-  if (is_last) __threadfence_system();
   return is_last;
 }
 

@@ -142,9 +142,13 @@ void deepfm_pack_backward(const float* rows2, const int* inv2, const int* inv1, 
                           const float* dlogit, int B, int F, int D, int RD, float* ugrad2, float* ugrad1,
                           cudaStream_t stream);
 
-// Linear layer with one output over bf16 rows x[M, K] (pitch ldx): y[m] = x[m, :] . w + bias[0].
-void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float* bias, int M, int K, float* y,
-                    cudaStream_t stream);
+// bf16 copy [N, K] and bf16 transpose [K, N] of an fp32 weight matrix [N, K], one pass.
+void cast_w_wt(const float* w, int N, int K, __nv_bfloat16* w16, __nv_bfloat16* wt16, cudaStream_t stream);
+
+// Linear layer with one output over bf16 rows x[M, K] (pitch ldx):
+// y[m] = x[m, :] . w + bias[0] + addend[m]   (bias and addend optional).
+void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float* bias, const float* addend, int M,
+                    int K, float* y, cudaStream_t stream);
 // Its backward: dx (optional, bf16, optionally masked by x > 0), dw[K] += ..., db[0] += sum(dy).
 void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const float* dy, int M, int K, bool relu_mask,
                      __nv_bfloat16* dx, int lddx, float* dw, float* db, cudaStream_t stream);

@@ -535,6 +535,13 @@ int pick_bn(int n, int granule) {
   return bn < granule ? granule : bn;
 }
 
+// With at most one CTA per SM there is no second CTA to hide a short pipeline behind: go to 4
+// stages when the whole grid fits in one wave, else 2 stages and two CTAs per SM.
+int one_wave_stages(int m, int n, int bn) {
+  const int tiles = ((m + kBM - 1) / kBM) * ((n + bn - 1) / bn);
+  return tiles <= 148 ? 4 : 2;
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int splits, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(g.stages) * (kBM + g.BN) * 128 + 1024;
@@ -591,6 +598,7 @@ int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int 
   if ((ldy % 8) != 0 || !make_tmap(&ta, X, M, K, ldx, 64, kBM) || !make_tmap(&tb, W, N, K, ldw, 64, g.BN)) return -1;
   int rc = 0;
   if (launch_resident<EPI_BIAS_ACT>(ta, tb, g, stream, &rc)) return rc;
+  g.stages = one_wave_stages(M, N, g.BN);
   return launch<false, false, EPI_BIAS_ACT>(ta, tb, g, 1, stream);
 }
 
@@ -611,6 +619,7 @@ int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int
     return -1;
   int rc = 0;
   if (launch_resident<EPI_RELU_MASK>(ta, tb, g, stream, &rc)) return rc;
+  g.stages = one_wave_stages(M, K, g.BN);
   return launch<false, false, EPI_RELU_MASK>(ta, tb, g, 1, stream);
 }
 

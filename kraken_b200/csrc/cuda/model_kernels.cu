@@ -142,7 +142,8 @@ bce_kernel(const float* __restrict__ logits, const float* __restrict__ labels, i
 // ---- Linear layer with a single output (the MLP's logit head): y[m] = x[m, :] . w + b
 __global__ void __launch_bounds__(kThreads)
 rowdot_forward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ w,
-                      const float* __restrict__ bias, int M, int K, float* __restrict__ y) {
+                      const float* __restrict__ bias, const float* __restrict__ addend, int M, int K,
+                      float* __restrict__ y) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -155,7 +156,7 @@ rowdot_forward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float*
       if (k + 1 < K) acc += __bfloat162float(v.y) * w[k + 1];
     }
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) y[m] = acc + (bias ? bias[0] : 0.f);
+    if (lane == 0) y[m] = acc + (bias ? bias[0] : 0.f) + (addend ? addend[m] : 0.f);
   }
 }
 
@@ -188,6 +189,27 @@ rowdot_backward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float
     float s = 0.f;
     for (int m = r0; m < r1; ++m) s += dy[m];
     atomicAdd(db, s);
+  }
+}
+
+// fp32 weight [N, K] -> bf16 copy [N, K] and bf16 transpose [K, N] in one pass (the forward and
+// the input-gradient GEMMs want the two layouts).
+__global__ void __launch_bounds__(256)
+cast_w_wt_kernel(const float* __restrict__ w, int N, int K, __nv_bfloat16* __restrict__ w16,
+                 __nv_bfloat16* __restrict__ wt16) {
+  __shared__ float tile[32][33];
+  const int n0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int r = ty; r < 32; r += 8) {
+    const int n = n0 + r, k = k0 + tx;
+    const float v = (n < N && k < K) ? w[static_cast<size_t>(n) * K + k] : 0.f;
+    tile[r][tx] = v;
+    if (n < N && k < K) w16[static_cast<size_t>(n) * K + k] = __float2bfloat16(v);
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int k = k0 + r, n = n0 + tx;
+    if (k < K && n < N) wt16[static_cast<size_t>(k) * N + n] = __float2bfloat16(tile[tx][r]);
   }
 }
 
@@ -229,12 +251,12 @@ void bce_forward_backward(const float* logits, const float* labels, int n, float
   bce_kernel<<<grid, kThreads, 0, stream>>>(logits, labels, n, 1.f / static_cast<float>(n), loss, grad);
 }
 
-void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float* bias, int M, int K, float* y,
-                    cudaStream_t stream) {
+void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float* bias, const float* addend, int M,
+                    int K, float* y, cudaStream_t stream) {
   if (M <= 0) return;
   int grid = (M * 32 + kThreads - 1) / kThreads;
   if (grid > 148 * 8) grid = 148 * 8;
-  rowdot_forward_kernel<<<grid, kThreads, 0, stream>>>(x, ldx, w, bias, M, K, y);
+  rowdot_forward_kernel<<<grid, kThreads, 0, stream>>>(x, ldx, w, bias, addend, M, K, y);
 }
 
 void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const float* dy, int M, int K, bool relu_mask,
@@ -246,6 +268,11 @@ void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const floa
   blocks = (M + rows_per_block - 1) / rows_per_block;
   rowdot_backward_kernel<<<blocks, kThreads, 0, stream>>>(x, ldx, w, dy, M, K, rows_per_block, relu_mask ? 1 : 0, dx,
                                                           lddx, dw, db);
+}
+
+void cast_w_wt(const float* w, int N, int K, __nv_bfloat16* w16, __nv_bfloat16* wt16, cudaStream_t stream) {
+  if (N <= 0 || K <= 0) return;
+  cast_w_wt_kernel<<<dim3((K + 31) / 32, (N + 31) / 32), 256, 0, stream>>>(w, N, K, w16, wt16);
 }
 
 }  // namespace cu

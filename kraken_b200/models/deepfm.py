@@ -2,7 +2,7 @@
 
 One dim-``dim`` table holds the second-order / deep embeddings of all fields
 and one dim-1 table the first-order weights; ids are global (field offset
-already added).  logit = sum_f w_f + FM2(e) + MLP([e, dense]) + bias.  The
+already added).  logit = sum_f w_f + FM2(e) + MLP([e, dense]) (the MLP's last layer carries the bias).  The
 reference's example builds the same model from 39 + 39 small tables and torch
 CPU ops (examples/DeepFM/model/DeepFM.py:64-140).
 
@@ -89,7 +89,6 @@ class DeepFM(torch.nn.Module):
         self.mlp_in = (width + 7) // 8 * 8  # padded: the tensor-core path wants pitches in multiples of 8
         self.pad = self.mlp_in - width
         self.mlp = MLP(self.mlp_in, list(hidden) + [1])
-        self.bias = torch.nn.Parameter(torch.zeros(1))
         self.fused = fused
 
     def _fused_ok(self, ids: torch.Tensor) -> bool:
@@ -101,7 +100,7 @@ class DeepFM(torch.nn.Module):
         if self._fused_ok(ids):
             first = self.first_order.sparse_table if self.first_order is not None else None
             x, fm = _DeepFMFront.apply(self.second_order.sparse_table, first, dense, ids, self.mlp_in, self.dim)
-            return fm + self.mlp(x, input_grad_cols=self.num_fields * self.dim).squeeze(-1) + self.bias
+            return self.mlp(x, input_grad_cols=self.num_fields * self.dim, addend=fm).squeeze(-1)
         if self.fold:
             rows = self.second_order(ids)                    # [B, F, row_dim]
             e, w = rows[..., :self.dim], rows[..., self.dim:self.dim + 1]
@@ -113,4 +112,4 @@ class DeepFM(torch.nn.Module):
         if self.pad:
             parts.append(torch.zeros(dense.shape[0], self.pad, dtype=e.dtype, device=e.device))
         deep = self.mlp(torch.cat(parts, dim=1)).squeeze(-1)
-        return w.sum(dim=(1, 2)) + fm_interaction(e.contiguous()) + deep + self.bias
+        return w.sum(dim=(1, 2)) + fm_interaction(e.contiguous()) + deep

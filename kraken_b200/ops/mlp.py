@@ -53,15 +53,18 @@ def _grad_target(p: torch.Tensor) -> torch.Tensor:
 
 class _FusedMLP(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, n_layers, input_grad_cols, *params):
+    def forward(ctx, x, addend, n_layers, input_grad_cols, *params):
         ws, bs = params[:n_layers], params[n_layers:]
         dev = x.device
         st = gemm_status(dev)
         h = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
         acts = [h]
         M = h.shape[0]
+        wts = []
         for i in range(n_layers - 1):
-            w16 = ws[i].detach().to(torch.bfloat16)
+            counters.add()
+            w16, wt16 = C.cast_w_wt(ws[i].detach().contiguous())  # both layouts in one pass; wt16 is for backward
+            wts.append(wt16)
             y = torch.empty((M, w16.shape[0]), dtype=torch.bfloat16, device=dev)
             counters.add()
             C.linear_forward(h, w16, bs[i].detach(), True, y, st)
@@ -71,8 +74,10 @@ class _FusedMLP(torch.autograd.Function):
         if wl.shape[0] == 1:
             out = torch.empty(M, dtype=torch.float32, device=dev)
             counters.add()
-            C.rowdot_forward(h, wl.reshape(-1).contiguous(), bl, out)
+            C.rowdot_forward(h, wl.reshape(-1).contiguous(), bl, out,
+                             addend.detach().float().contiguous() if addend is not None else None)
             out = out.view(M, 1)
+            addend = None
         elif wl.shape[0] % 8 == 0:
             y = torch.empty((M, wl.shape[0]), dtype=torch.bfloat16, device=dev)
             counters.add()
@@ -80,7 +85,9 @@ class _FusedMLP(torch.autograd.Function):
             out = y.float()
         else:
             out = torch.addmm(bl, h.float(), wl.t())  # narrow odd-width head: library fp32 matmul
-        ctx.acts, ctx.ws, ctx.bs, ctx.n_layers = acts, ws, bs, n_layers
+        if addend is not None:
+            out = out + addend.reshape(M, 1).to(out.dtype)
+        ctx.acts, ctx.ws, ctx.bs, ctx.n_layers, ctx.wts = acts, ws, bs, n_layers, wts
         ctx.x_needs_grad = x.requires_grad
         ctx.input_grad_cols = input_grad_cols
         ctx.x_dtype = x.dtype
@@ -137,7 +144,7 @@ class _FusedMLP(torch.autograd.Function):
             C.colsum_bf16(dh, _grad_target(bs[i]))
             if i > 0 or ctx.x_needs_grad:
                 dprev = torch.empty_like(acts[i])
-                wt16 = ws[i].detach().t().contiguous().to(torch.bfloat16)
+                wt16 = ctx.wts[i]
                 counters.add()
                 cols = ctx.input_grad_cols if (i == 0 and ctx.input_grad_cols) else dprev.shape[1]
                 if cols < dprev.shape[1]:
@@ -153,14 +160,17 @@ class _FusedMLP(torch.autograd.Function):
         if ctx.x_needs_grad and dh is not None:
             dx = dh if ctx.x_dtype == torch.bfloat16 else dh.to(ctx.x_dtype)
         # parameter gradients were accumulated in place
-        return (dx, None, None) + (None,) * (2 * L)
+        return (dx, gout.reshape(-1) if ctx.needs_input_grad[1] else None, None, None) + (None,) * (2 * L)
 
 
 def fused_mlp(x: torch.Tensor, weights: List[torch.Tensor], biases: List[torch.Tensor],
-              input_grad_cols: int = 0) -> torch.Tensor:
+              input_grad_cols: int = 0, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] (bf16 or fp32, CUDA) -> [M, out_features] fp32.  Parameter gradients are
     accumulated into ``param.grad`` in place by the backward kernels.  ``input_grad_cols``
-    (a multiple of 8, 0 = all) limits the input gradient to the leading columns of x."""
+    (a multiple of 8, 0 = all) limits the input gradient to the leading columns of x.
+    ``addend`` [M] (single-output heads) is added to the output inside the head kernel."""
     from ..utils.profiler import engine_region
     with engine_region("mlp_fwd"):
-        return _FusedMLP.apply(x, len(weights), int(input_grad_cols), *weights, *biases)
+        if addend is not None and weights[-1].shape[0] != 1:
+            raise ValueError("addend needs a single-output head")
+        return _FusedMLP.apply(x, addend, len(weights), int(input_grad_cols), *weights, *biases)
