@@ -5,7 +5,9 @@ engine instead of a ZeroMQ worker.
 ``initialize`` keeps the reference signature ``(s_addr, emitter_type, life_span,
 eta)``.  ``s_addr`` selects the backend: ``"gpu"`` / ``"cpu"`` (optionally with
 ``://`` and anything after it), while any other address - such as the
-``host:port`` a reference script passes - means "auto": GPUs if present.  When
+``host:port`` a reference script passes - means "auto": GPUs if present;
+``tcp://host:port`` connects to a running ``scheduler_server`` (multi-process CPU
+deployment, ``kraken_b200.launch``).  When
 the process runs under ``torchrun`` (RANK / WORLD_SIZE set) the ranks form one
 job: NCCL for the GPU engine, gloo for the CPU engine.
 """
@@ -61,7 +63,7 @@ def initialize(s_addr: str = "auto", emitter_type=EmitterType.kDefault, life_spa
     backend = options.pop("backend", None)
     if backend is None:
         head = (s_addr or "auto").split("://")[0].lower()
-        backend = head if head in ("cpu", "gpu") else "auto"
+        backend = head if head in ("cpu", "gpu") else ("remote" if head == "tcp" else "auto")
     if backend == "auto":
         backend = "gpu" if torch.cuda.is_available() else "cpu"
     cfg = EngineConfig(backend=backend, emitter_type=emitter_type, life_span=int(life_span), eta=float(eta))
@@ -71,6 +73,11 @@ def initialize(s_addr: str = "auto", emitter_type=EmitterType.kDefault, life_spa
             raise KrakenError(f"unknown initialize option {k!r}")
         setattr(cfg, k, v)
 
+    if backend == "remote":
+        # multi-process CPU deployment: s_addr = "tcp://host:port" of a running scheduler_server
+        from ..runtime.remote import RemoteEngine
+        _engine = RemoteEngine(cfg, s_addr.split("://", 1)[-1])
+        return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if backend == "gpu":
@@ -151,13 +158,19 @@ def combine_push_sparse_table(table_ids: Sequence[int], indices: Sequence[torch.
 
 
 def try_save_model() -> bool:
+    eng = engine()
+    if hasattr(eng, "try_save_model"):
+        return eng.try_save_model()
     from ..checkpoint.manager import save_model
-    return save_model(engine())
+    return save_model(eng)
 
 
 def try_load_model_blocked(load_dir: str) -> bool:
+    eng = engine()
+    if hasattr(eng, "try_load_model_blocked"):
+        return eng.try_load_model_blocked(load_dir)
     from ..checkpoint.manager import load_model
-    return load_model(engine(), load_dir)
+    return load_model(eng, load_dir)
 
 
 def jagged_sum_forward(values, offsets, patch_value, weights=None):

@@ -1,0 +1,193 @@
+"""Request / reply transport of the multi-process CPU deployment.
+
+The reference's processes talk ZeroMQ with a 13-byte header and a hand-rolled
+binary body (kraken/rpc/protocol.h:12-41, kraken/rpc/station.cc,
+kraken/rpc/indep_connecter.cc).  This is the same idea on plain TCP sockets:
+
+    frame   = u32 body_len | header | body
+    header  = u64 timestamp (correlation id) | u32 type (request) or i32 error_code (reply) | u8 compress
+    body    = u32 json_len | json metadata | tensors, each in the framework's binary tensor encoding
+
+RPC type numbers are the reference's (kraken/protocol/rpc_func_type.h:8-38).
+A ``Station`` serves registered handlers on a thread pool; a ``Connecter`` is a
+client with a send lock, a timeout (5 s default, as in
+kraken/rpc/indep_connecter.h:83-84) and synchronous ``call``.
+"""
+from __future__ import annotations
+
+import json
+import socket
+import socketserver
+import struct
+import threading
+import time
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .._native import C
+
+HEADER = struct.Struct("<QiB")  # timestamp, type | error code, compress
+
+
+class Rpc:
+    HEARTBEAT = 0
+    TRY_JOIN = 1
+    INIT_MODEL = 3
+    REGISTER_DENSE = 4
+    REGISTER_SPARSE = 5
+    CREATE_MODEL = 6
+    CREATE_DENSE = 7
+    CREATE_SPARSE = 8
+    FETCH_ROUTER = 11
+    PULL_DENSE = 19
+    COMBINE_PULL_DENSE = 20
+    PUSH_DENSE = 21
+    PULL_SPARSE = 22
+    PUSH_SPARSE = 24
+    TRY_SAVE = 26
+    TRY_LOAD = 27
+    NOTIFY_SAVE = 28
+    NOTIFY_LOAD = 29
+    IS_ALL_PS_WORKING = 30
+
+
+class RpcError(RuntimeError):
+    def __init__(self, code: int, what: str = ""):
+        super().__init__(f"rpc error {code}: {C.error_message(code)} {what}".strip())
+        self.code = code
+
+
+def pack_body(meta: dict, tensors: Sequence[torch.Tensor] = ()) -> bytes:
+    j = json.dumps(meta).encode()
+    parts = [struct.pack("<I", len(j)), j, struct.pack("<I", len(tensors))]
+    for t in tensors:
+        b = C.serialize_tensor(t)
+        parts += [struct.pack("<Q", len(b)), b]
+    return b"".join(parts)
+
+
+def unpack_body(body: bytes) -> Tuple[dict, List[torch.Tensor]]:
+    (jl,) = struct.unpack_from("<I", body, 0)
+    meta = json.loads(body[4:4 + jl].decode())
+    pos = 4 + jl
+    (n,) = struct.unpack_from("<I", body, pos)
+    pos += 4
+    tensors = []
+    for _ in range(n):
+        (bl,) = struct.unpack_from("<Q", body, pos)
+        pos += 8
+        tensors.append(C.deserialize_tensor(body[pos:pos + bl]))
+        pos += bl
+    return meta, tensors
+
+
+def _recv_exact(sock: socket.socket, n: int) -> bytes:
+    buf = bytearray()
+    while len(buf) < n:
+        chunk = sock.recv(n - len(buf))
+        if not chunk:
+            raise ConnectionError("peer closed the connection")
+        buf += chunk
+    return bytes(buf)
+
+
+def send_frame(sock: socket.socket, stamp: int, code: int, body: bytes) -> None:
+    sock.sendall(struct.pack("<I", len(body)) + HEADER.pack(stamp, code, 0) + body)
+
+
+def recv_frame(sock: socket.socket) -> Tuple[int, int, bytes]:
+    (n,) = struct.unpack("<I", _recv_exact(sock, 4))
+    stamp, code, _ = HEADER.unpack(_recv_exact(sock, HEADER.size))
+    return stamp, code, _recv_exact(sock, n)
+
+
+Handler = Callable[[dict, List[torch.Tensor]], Tuple[dict, Sequence[torch.Tensor]]]
+
+
+class Station:
+    """Threaded TCP server dispatching frames to registered handlers."""
+
+    def __init__(self, port: int, host: str = "0.0.0.0") -> None:
+        self.handlers: Dict[int, Handler] = {}
+        station = self
+
+        class _H(socketserver.BaseRequestHandler):
+            def handle(self):
+                self.request.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+                while True:
+                    try:
+                        stamp, rpc_type, body = recv_frame(self.request)
+                    except (ConnectionError, OSError, struct.error):
+                        return
+                    fn = station.handlers.get(rpc_type)
+                    try:
+                        if fn is None:
+                            raise RpcError(1, f"type {rpc_type}")
+                        meta, tensors = unpack_body(body)
+                        out_meta, out_tensors = fn(meta, tensors)
+                        send_frame(self.request, stamp, 0, pack_body(out_meta, out_tensors))
+                    except RpcError as e:
+                        send_frame(self.request, stamp, e.code, pack_body({"what": str(e)}))
+                    except C.KrakenError as e:
+                        send_frame(self.request, stamp, -1, pack_body({"what": str(e)}))
+                    except Exception as e:  # a failing handler must not take the server down
+                        send_frame(self.request, stamp, -1, pack_body({"what": repr(e)}))
+
+        class _S(socketserver.ThreadingTCPServer):
+            allow_reuse_address = True
+            daemon_threads = True
+
+        self.server = _S((host, port), _H)
+        self.port = self.server.server_address[1]
+        self.thread: Optional[threading.Thread] = None
+
+    def register(self, rpc_type: int, fn: Handler) -> None:
+        self.handlers[rpc_type] = fn
+
+    def start(self) -> None:
+        self.thread = threading.Thread(target=self.server.serve_forever, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> None:
+        self.server.shutdown()
+        self.server.server_close()
+
+
+class Connecter:
+    """Client for one peer.  ``call`` is synchronous; a reply that does not arrive within
+    ``timeout_ms`` raises kTimeout (17), an error reply raises with the server's code."""
+
+    def __init__(self, addr: str, timeout_ms: int = 5000) -> None:
+        host, port = addr.rsplit(":", 1)
+        self.addr = addr
+        self.timeout = timeout_ms / 1000.0
+        self.sock = socket.create_connection((host, int(port)), timeout=self.timeout)
+        self.sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+        self.lock = threading.Lock()
+        self.stamp = int(time.time() * 1e6)
+
+    def call(self, rpc_type: int, meta: Optional[dict] = None, tensors: Sequence[torch.Tensor] = (),
+             timeout_ms: Optional[int] = None) -> Tuple[dict, List[torch.Tensor]]:
+        with self.lock:
+            self.stamp += 1
+            stamp = self.stamp
+            self.sock.settimeout(self.timeout if timeout_ms is None else timeout_ms / 1000.0)
+            try:
+                send_frame(self.sock, stamp, rpc_type, pack_body(meta or {}, tensors))
+                while True:
+                    got, code, body = recv_frame(self.sock)
+                    if got == stamp:
+                        break  # stale replies of timed-out calls are dropped
+            except socket.timeout:
+                raise RpcError(17, f"{self.addr} type {rpc_type}")
+        out_meta, out_tensors = unpack_body(body)
+        if code != 0:
+            raise RpcError(code, out_meta.get("what", ""))
+        return out_meta, out_tensors
+
+    def close(self) -> None:
+        try:
+            self.sock.close()
+        except OSError:
+            pass
