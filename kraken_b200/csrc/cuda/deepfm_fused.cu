@@ -53,7 +53,9 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
       __nv_bfloat16* xr = x + static_cast<size_t>(b) * ldx;
       for (int c = lane; c < chunks; c += lpr) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = s;
-        for (int f = 0; f < F; ++f) {
+#pragma unroll 4
+  #pragma unroll 4
+      for (int f = 0; f < F; ++f) {
           const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
           s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
           q.x += e.x * e.x, q.y += e.y * e.y, q.z += e.z * e.z, q.w += e.w * e.w;
@@ -97,10 +99,12 @@ deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restri
     const __nv_bfloat16* dxr = dx ? dx + static_cast<size_t>(b) * lddx : nullptr;
     for (int c = lane; c < chunks; c += lpr) {
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
       for (int f = 0; f < F; ++f) {
         const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
         s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
       }
+#pragma unroll 4
       for (int f = 0; f < F; ++f) {
         const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
         float4 d = make_float4(g * (s.x - e.x), g * (s.y - e.y), g * (s.z - e.z), g * (s.w - e.w));

@@ -18,6 +18,16 @@ from .._native import C
 from . import counters
 
 _status = {}
+_side_streams = {}
+
+
+def _side_stream(device: torch.device) -> torch.cuda.Stream:
+    """Second stream on which weight and bias gradients run beside the input-gradient chain."""
+    key = (device.type, device.index)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
+
 
 
 def gemm_status(device: torch.device) -> torch.Tensor:
@@ -136,12 +146,19 @@ class _FusedMLP(torch.autograd.Function):
                 dh = torch.empty_like(h_last)
                 counters.add()
                 C.linear_dgrad(dy16, wl.detach().t().contiguous().to(torch.bfloat16), h_last if L > 1 else None, dh, st)
+        # The chain dh_L -> dh_{L-1} -> ... is serial; each layer's weight and bias gradients only
+        # need that layer's dh, so they run on a second stream beside the chain and are joined at
+        # the end (in a CUDA-graph capture this becomes a parallel branch).
+        main = torch.cuda.current_stream(dev)
+        side = _side_stream(dev)
         for i in range(L - 2, -1, -1):
             # dh is d(loss)/d(acts[i + 1]) with layer i's ReLU mask already applied
-            counters.add()
-            C.linear_wgrad(dh, acts[i], _grad_target(ws[i]), st)
-            counters.add()
-            C.colsum_bf16(dh, _grad_target(bs[i]))
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                counters.add(2)
+                C.linear_wgrad(dh, acts[i], _grad_target(ws[i]), st)
+                C.colsum_bf16(dh, _grad_target(bs[i]))
+                dh.record_stream(side)
             if i > 0 or ctx.x_needs_grad:
                 dprev = torch.empty_like(acts[i])
                 wt16 = ctx.wts[i]
@@ -156,6 +173,7 @@ class _FusedMLP(torch.autograd.Function):
                 dh = dprev
             else:
                 dh = None
+        main.wait_stream(side)
         dx = None
         if ctx.x_needs_grad and dh is not None:
             dx = dh if ctx.x_dtype == torch.bfloat16 else dh.to(ctx.x_dtype)
