@@ -142,6 +142,7 @@ void bind_dense(py::module_& m) {
                                     N, K, status.data_ptr<int>(), cur_stream());
     TORCH_CHECK(rc == 0, "linear_wgrad: cannot encode the TMA descriptors (pitches must be multiples of 8)");
   });
+  m.def("gemm_set_tuning", &cu::gemm_set_tuning, py::arg("variant") = 0, py::arg("n_tiles") = 0);
   m.def("colsum_bf16", [bf, need_bf16](const torch::Tensor& dy, const torch::Tensor& db) {
     need_bf16(dy, "dy");
     TORCH_CHECK(db.is_cuda() && db.scalar_type() == torch::kFloat32 && db.numel() >= dy.size(1), "db too small");

@@ -30,7 +30,7 @@ constexpr int kBK = 64;          // k-elements per stage = one 128-byte swizzle 
 constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each taking half of the tile's columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 8;
 
 enum { EPI_BIAS_ACT = 0, EPI_RELU_MASK = 1, EPI_RED_F32 = 2 };
 
@@ -465,6 +465,169 @@ gemm_bres_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) tc::tmem_dealloc(tmem_base, 512);
 }
 
+// ------------------------------------------------------------------ weight-resident CTA-pair variant
+// The single-CTA resident kernel above is bound by what one SM can take in: every MMA reads
+// (128 + BN) x 32 bytes of operands from shared memory, which keeps the shared-memory port busy
+// for most of the MMA's duration and stalls the TMA stream that shares it, and a column tile
+// narrow enough to leave room for a deep activation ring makes every activation tile cross the
+// L2-to-SM fabric once per column tile.  A pair of CTAs on one TPC running tcgen05.mma with
+// cta_group::2 fixes both: each CTA keeps only half of the column tile's weights (so the same
+// shared memory holds a wider tile AND a deeper ring) and reads only half of the B bytes per MMA.
+//
+//   cluster = 2 CTAs; pair tile = 256 rows x BN columns; CTA r loads rows [r * 128, +128) of A and
+//   weight rows [n0 + r * BN / 2, +BN / 2); the even CTA's warp 1 issues every MMA; the byte
+//   counts of both CTAs' loads complete on the even CTA's barriers; tcgen05.commit with a CTA
+//   mask frees ring stages and publishes accumulators in both CTAs; epilogue warps of both CTAs
+//   release an accumulator buffer by arriving on the even CTA's barrier.
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int total_kb = (g.K + kBK - 1) / kBK;
+  const int half_bn = g.BN / 2;
+  const uint32_t a_bytes = kBM * 128;
+  const uint32_t b_bytes = static_cast<uint32_t>(half_bn) * 128;  // one k-block of this CTA's half of the weights
+  uint8_t* b_res = smem;
+  uint8_t* a_ring = smem + static_cast<size_t>(total_kb) * b_bytes;
+
+  __shared__ uint64_t b_full, a_full[kMaxStages], a_empty[kMaxStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ float s_bias[256];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_ctarank();  // 0 = the CTA that issues the MMAs
+  const int pair = blockIdx.x >> 1;
+  const int pairs = gridDim.x >> 1;
+  const int n0 = blockIdx.y * g.BN;
+  const int m_tiles = (g.M + 2 * kBM - 1) / (2 * kBM);  // pair tiles of 256 rows
+  const int my_tiles = (m_tiles - pair + pairs - 1) / pairs;
+  constexpr uint32_t kAccCols = 256;
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&b_full, 1);
+    for (int s = 0; s < g.stages; ++s) {
+      tc::mbar_init(&a_full[s], 1);
+      tc::mbar_init(&a_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&acc_full[b], 1);
+      tc::mbar_init(&acc_empty[b], 2 * kEpiWarps);  // every epilogue warp of both CTAs
+    }
+    abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::prefetch_tmap(&tmA);
+    tc::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tc::tmem_alloc_pair(&tmem_slot, 512);
+  if (EPI == EPI_BIAS_ACT) stage_bias(g, s_bias, n0, threadIdx.x, blockDim.x);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync_all();  // the other CTA's barriers exist before anything arrives on them
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  const int total_it = my_tiles * total_kb;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- producer (both CTAs): own half of the weights once, then own rows of the stream
+    const uint32_t lead_b_full = tc::map_to_cta(tc::smem_u32(&b_full), 0);
+    if (rank == 0) tc::mbar_expect_tx(&b_full, 2u * static_cast<uint32_t>(total_kb) * b_bytes);
+    for (int kb = 0; kb < total_kb; ++kb)
+      tc::tma_load_2d_pair(b_res + static_cast<size_t>(kb) * b_bytes, &tmB, lead_b_full, kb * kBK,
+                           n0 + static_cast<int>(rank) * half_bn);
+    bool ok = true;
+    for (int it = 0; it < total_it && ok; ++it) {
+      const int s = it % g.stages;
+      const uint32_t round = static_cast<uint32_t>(it / g.stages);
+      if (round > 0) ok = tc::mbar_wait(&a_empty[s], (round - 1) & 1, kWaitLimit);
+      if (!ok) break;
+      const int tile = pair + (it / total_kb) * pairs;
+      const int kb = it % total_kb;
+      if (rank == 0) tc::mbar_expect_tx(&a_full[s], 2u * a_bytes);
+      tc::tma_load_2d_pair(a_ring + static_cast<size_t>(s) * a_bytes, &tmA, tc::map_to_cta(tc::smem_u32(&a_full[s]), 0),
+                           kb * kBK, tile * 2 * kBM + static_cast<int>(rank) * kBM);
+    }
+    if (!ok) {
+      atomicCAS(g.status, 0, err::kTimeout);
+      abort_flag = 1;
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---------------- MMA issuer (even CTA only)
+    const uint32_t idesc = tc::instr_desc_bf16(2 * kBM, g.BN, 0, 0);
+    bool ok = tc::mbar_wait(&b_full, 0, kWaitLimit);
+    tc::fence_after_sync();
+    const uint32_t b_addr0 = tc::smem_u32(b_res);
+    const uint32_t a_addr0 = tc::smem_u32(a_ring);
+    int it = 0;
+    for (int j = 0; j < my_tiles && ok; ++j) {
+      const int buf = j & 1;
+      const uint32_t use = static_cast<uint32_t>(j >> 1);
+      if (use > 0) {
+        ok = tc::mbar_wait(&acc_empty[buf], (use - 1) & 1, kWaitLimit);
+        if (!ok) break;
+        tc::fence_after_sync();
+      }
+      const uint32_t d_tmem = tmem_base + buf * kAccCols;
+      for (int kb = 0; kb < total_kb && ok; ++kb, ++it) {
+        const int s = it % g.stages;
+        ok = tc::mbar_wait(&a_full[s], static_cast<uint32_t>(it / g.stages) & 1, kWaitLimit);
+        if (!ok) break;
+        tc::fence_after_sync();
+        const uint32_t a_addr = a_addr0 + s * a_bytes;
+        const uint32_t b_addr = b_addr0 + kb * b_bytes;
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k)
+          tc::mma_bf16_pair(d_tmem, tc::smem_desc(a_addr + k * 32, 16, 1024), tc::smem_desc(b_addr + k * 32, 16, 1024),
+                            idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        tc::mma_commit_pair(&a_empty[s], 3);  // the stage is free in both CTAs
+      }
+      if (ok) tc::mma_commit_pair(&acc_full[buf], 3);
+    }
+    if (!ok) {
+      atomicCAS(g.status, 0, err::kTimeout);
+      abort_flag = 1;
+    }
+  } else if (warp >= 2) {
+    // ---------------- epilogue (both CTAs, each on its own 128 rows)
+    const int quarter = warp & 3;
+    const uint32_t lead_acc_empty[2] = {tc::map_to_cta(tc::smem_u32(&acc_empty[0]), 0),
+                                        tc::map_to_cta(tc::smem_u32(&acc_empty[1]), 0)};
+    bool ok = true;
+    for (int j = 0; j < my_tiles && ok; ++j) {
+      const int buf = j & 1;
+      ok = tc::mbar_wait(&acc_full[buf], static_cast<uint32_t>(j >> 1) & 1, kWaitLimit);
+      tc::fence_after_sync();
+      if (!ok) {
+        if (lane == 0) atomicCAS(g.status, 0, err::kTimeout);
+        break;
+      }
+      const int tile = pair + j * pairs;
+      const int row = tile * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
+      int c_begin, c_end;
+      epi_cols(g.BN, warp - 2, &c_begin, &c_end);
+      epilogue_rows<EPI>(g, s_bias, tmem_base + buf * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16), row, n0,
+                         c_begin, c_end);
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive_cluster(lead_acc_empty[buf]);
+    }
+  }
+
+  // ---------------- teardown: the even CTA's barriers count both CTAs' copies
+  if (warp == 0 && lane == 0 && rank == 0) {
+    tc::mbar_wait(&b_full, 0, kWaitLimit);
+    const int first = max(0, total_it - g.stages);
+    for (int it = first; it < total_it; ++it)
+      tc::mbar_wait(&a_full[it % g.stages], static_cast<uint32_t>(it / g.stages) & 1, kWaitLimit);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::cluster_sync_all();  // neither CTA leaves while the other may still touch its memory or barriers
+  if (warp == 1) tc::tmem_dealloc_pair(tmem_base, 512);
+}
+
 // ------------------------------------------------------------------ column sums
 __global__ void __launch_bounds__(256)
 colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ld, int M, int N, int rows_per_block, float* out) {
@@ -555,30 +718,102 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int splits,
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-// Resident-weight launch when the weight slice and a 2-stage activation ring fit in shared memory
-// and there are enough row tiles to amortise loading it; returns false if not applicable.
+int g_variant = 0;           // 0 = choose; 1 = CTA pair; 2 = single-CTA resident; 3 = one tile per CTA
+int g_resident_n_tiles = 0;  // 0 = choose; otherwise the number of column tiles of the resident variant
+
+// Plan of the resident-weight variant for an M x N output contracting over K: tile width and depth
+// of the activation ring.  The ring's depth decides how many bytes a CTA keeps in flight from L2,
+// and that, not the tensor cores, bounds these tall-and-skinny products; so the plan takes the
+// fewest column tiles whose weight slice leaves room for at least four 16 KB activation stages
+// (more column tiles re-read the activations from L2 once more each, which costs less than a
+// starved ring).  Returns false when the variant does not apply.
+bool plan_resident(int M, int N, int K, int* bn_out, int* stages_out) {
+  const int total_kb = (K + kBK - 1) / kBK;
+  const int m_tiles = (M + kBM - 1) / kBM;
+  const size_t budget = 225 * 1024 - 1024;
+  int best_bn = 0, best_stages = 0;
+  for (int n_tiles = (N + 255) / 256; n_tiles <= 8; ++n_tiles) {
+    if (g_resident_n_tiles > 0 && n_tiles != g_resident_n_tiles) continue;
+    int bn = (N + n_tiles - 1) / n_tiles;
+    bn = (bn + 15) / 16 * 16;
+    if (bn < 16) bn = 16;
+    const size_t weights = static_cast<size_t>(total_kb) * bn * 128;
+    if (weights + 2 * kBM * 128 > budget) continue;
+    int stages = static_cast<int>((budget - weights) / (kBM * 128));
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages > best_stages) best_bn = bn, best_stages = stages;
+    if (stages >= 4) break;
+  }
+  if (best_bn == 0) return false;
+  const int n_tiles = (N + best_bn - 1) / best_bn;
+  if (n_tiles > 148 || m_tiles * n_tiles < 2 * 148) return false;
+  *bn_out = best_bn;
+  *stages_out = best_stages;
+  return true;
+}
+
+// Plan of the CTA-pair variant: the widest column tile (fewest activation re-reads) whose half
+// slice of the weights leaves at least four ring stages.
+bool plan_pair(int M, int N, int K, int* bn_out, int* stages_out) {
+  const int total_kb = (K + kBK - 1) / kBK;
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  const size_t budget = 225 * 1024 - 1024;
+  for (int n_tiles = (N + 255) / 256; n_tiles <= 4; ++n_tiles) {
+    if (g_resident_n_tiles > 0 && n_tiles != g_resident_n_tiles) continue;
+    int bn = (N + n_tiles - 1) / n_tiles;
+    bn = (bn + 15) / 16 * 16;  // the MMA's N is a multiple of 16; each half is then whole 8-row swizzle groups
+    const size_t weights = static_cast<size_t>(total_kb) * (bn / 2) * 128;
+    if (weights + 4 * kBM * 128 > budget) continue;
+    int stages = static_cast<int>((budget - weights) / (kBM * 128));
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (m_tiles * n_tiles < 2 * 74) return false;  // too few tiles to amortise loading the weights
+    *bn_out = bn;
+    *stages_out = stages;
+    return true;
+  }
+  return false;
+}
+
 template <int EPI>
-bool launch_resident(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaStream_t stream, int* rc) {
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaStream_t stream) {
+  const int total_kb = (g.K + kBK - 1) / kBK;
+  const int n_tiles = (g.N + g.BN - 1) / g.BN;
+  const int m_tiles = (g.M + 2 * kBM - 1) / (2 * kBM);
+  const size_t smem = static_cast<size_t>(total_kb) * (g.BN / 2) * 128 + static_cast<size_t>(g.stages) * kBM * 128 + 1024;
+  static size_t attr_smem = 0;
+  if (smem > attr_smem) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess) {
+      cudaGetLastError();
+      return -2;
+    }
+    attr_smem = smem;
+  }
+  int pairs = 74 / n_tiles;
+  if (pairs > m_tiles) pairs = m_tiles;
+  gemm_pair_kernel<EPI><<<dim3(2 * pairs, n_tiles), kThreads, smem, stream>>>(ta, tb, g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+template <int EPI>
+int launch_resident(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaStream_t stream) {
   const int total_kb = (g.K + kBK - 1) / kBK;
   const int n_tiles = (g.N + g.BN - 1) / g.BN;
   const int m_tiles = (g.M + kBM - 1) / kBM;
-  g.stages = 2;
   const size_t smem = static_cast<size_t>(total_kb) * g.BN * 128 + static_cast<size_t>(g.stages) * kBM * 128 + 1024;
-  if (smem > 225 * 1024 || n_tiles > 148 || m_tiles * n_tiles < 2 * 148) return false;
   static size_t attr_smem = 0;  // static + dynamic shared memory share the 227 KB limit: ask for what is needed
   if (smem > attr_smem) {
     if (cudaFuncSetAttribute(gemm_bres_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess) {
       cudaGetLastError();
-      return false;
+      return -2;
     }
     attr_smem = smem;
   }
   int per_n = 148 / n_tiles;
   if (per_n > m_tiles) per_n = m_tiles;
   gemm_bres_kernel<EPI><<<dim3(per_n, n_tiles), kThreads, smem, stream>>>(ta, tb, g);
-  *rc = cudaGetLastError() == cudaSuccess ? 0 : -2;
-  return true;
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 }  // namespace
@@ -595,9 +830,13 @@ int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int 
   g.out = Y, g.ldo = ldy;
   g.status = status;
   CUtensorMap ta, tb;
-  if ((ldy % 8) != 0 || !make_tmap(&ta, X, M, K, ldx, 64, kBM) || !make_tmap(&tb, W, N, K, ldw, 64, g.BN)) return -1;
-  int rc = 0;
-  if (launch_resident<EPI_BIAS_ACT>(ta, tb, g, stream, &rc)) return rc;
+  const bool pair = (g_variant == 0 || g_variant == 1) && plan_pair(M, N, K, &g.BN, &g.stages);
+  const bool resident = !pair && (g_variant == 0 || g_variant == 2) && plan_resident(M, N, K, &g.BN, &g.stages);
+  if ((ldy % 8) != 0 || !make_tmap(&ta, X, M, K, ldx, 64, kBM) ||
+      !make_tmap(&tb, W, N, K, ldw, 64, pair ? g.BN / 2 : g.BN))
+    return -1;
+  if (pair) return launch_pair<EPI_BIAS_ACT>(ta, tb, g, stream);
+  if (resident) return launch_resident<EPI_BIAS_ACT>(ta, tb, g, stream);
   g.stages = one_wave_stages(M, N, g.BN);
   return launch<false, false, EPI_BIAS_ACT>(ta, tb, g, 1, stream);
 }
@@ -614,11 +853,13 @@ int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int
   g.out = dX, g.ldo = lddx;
   g.status = status;
   CUtensorMap ta, tb;
+  const bool pair = (g_variant == 0 || g_variant == 1) && plan_pair(M, K, N, &g.BN, &g.stages);
+  const bool resident = !pair && (g_variant == 0 || g_variant == 2) && plan_resident(M, K, N, &g.BN, &g.stages);
   if ((lddx % 8) != 0 || (H && (ldh % 8) != 0) || !make_tmap(&ta, dY, M, N, lddy, 64, kBM) ||
-      !make_tmap(&tb, Wt, K, N, ldwt, 64, g.BN))
+      !make_tmap(&tb, Wt, K, N, ldwt, 64, pair ? g.BN / 2 : g.BN))
     return -1;
-  int rc = 0;
-  if (launch_resident<EPI_RELU_MASK>(ta, tb, g, stream, &rc)) return rc;
+  if (pair) return launch_pair<EPI_RELU_MASK>(ta, tb, g, stream);
+  if (resident) return launch_resident<EPI_RELU_MASK>(ta, tb, g, stream);
   g.stages = one_wave_stages(M, K, g.BN);
   return launch<false, false, EPI_RELU_MASK>(ta, tb, g, 1, stream);
 }
@@ -644,6 +885,11 @@ int linear_wgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* X, int 
       !make_tmap(&tb, X, M, K, ldx, 64, 64))
     return -1;
   return launch<true, true, EPI_RED_F32>(ta, tb, g, splits, stream);
+}
+
+void gemm_set_tuning(int variant, int n_tiles) {
+  g_variant = variant;
+  g_resident_n_tiles = n_tiles;
 }
 
 void colsum_bf16(const __nv_bfloat16* dY, int lddy, int M, int N, float* db, cudaStream_t stream) {

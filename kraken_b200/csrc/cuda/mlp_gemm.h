@@ -33,6 +33,11 @@ int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int
 int linear_wgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* X, int ldx, float* dW, int lddw, int M,
                  int N, int K, int* status, cudaStream_t stream);
 
+// Knobs for measurements.  variant: 0 = chosen from the shape, 1 = weight-resident CTA pair
+// (cta_group::2), 2 = weight-resident single CTA, 3 = one output tile per CTA.  n_tiles: column
+// tiles of the resident variants (0 = chosen from the shape).
+void gemm_set_tuning(int variant, int n_tiles);
+
 // Column sums of a bf16 matrix added into an fp32 vector: db[n] += sum_m dY[m, n].
 void colsum_bf16(const __nv_bfloat16* dY, int lddy, int M, int N, float* db, cudaStream_t stream);
 

@@ -1,0 +1,76 @@
+"""One-batch-ahead host-to-device input pipeline.
+
+The reference's workers read their batches with a torch ``DataLoader`` on the
+host and hand them to the model synchronously (examples/deepfm/main.py of the
+reference); on a B200 the 17 MB of ids of a 65,536-sample DeepFM batch take
+longer to cross PCIe than a fifth of the step, so the copy of batch ``i+1``
+runs on its own stream while batch ``i`` trains.
+
+    for dense, ids, labels in DevicePrefetcher(loader, device):
+        loss = step(dense, ids, labels)
+
+``loader`` yields tuples of pinned host tensors of fixed shapes.  Two sets of
+device buffers are used in turn; a buffer is refilled only after the step that
+read it has been enqueued behind an event, so no batch is overwritten early.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+
+
+class DevicePrefetcher:
+    def __init__(self, loader: Iterable[Sequence[torch.Tensor]], device: torch.device, depth: int = 2) -> None:
+        self.it: Iterator[Sequence[torch.Tensor]] = iter(loader)
+        self.device = device
+        self.depth = max(2, depth)
+        self.copy_stream = torch.cuda.Stream(device=device)
+        self.bufs: List[Optional[Tuple[torch.Tensor, ...]]] = [None] * self.depth
+        self.ready = [torch.cuda.Event() for _ in range(self.depth)]     # copy into slot finished
+        self.released = [torch.cuda.Event() for _ in range(self.depth)]  # consumer of slot enqueued its work
+        self.used = [False] * self.depth
+        self.head = 0  # next slot to fill
+        self.tail = 0  # next slot to hand out
+        self.pending = 0
+        self.bytes_copied = 0
+        self._fill()
+
+    def _fill(self) -> bool:
+        try:
+            host = next(self.it)
+        except StopIteration:
+            return False
+        slot = self.head
+        if self.bufs[slot] is None:
+            self.bufs[slot] = tuple(torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host)
+        with torch.cuda.stream(self.copy_stream):
+            if self.used[slot]:
+                self.copy_stream.wait_event(self.released[slot])
+            for d, h in zip(self.bufs[slot], host):
+                d.copy_(h, non_blocking=True)
+                self.bytes_copied += h.numel() * h.element_size()
+            self.ready[slot].record(self.copy_stream)
+        self.head = (slot + 1) % self.depth
+        self.pending += 1
+        return True
+
+    def __iter__(self) -> "DevicePrefetcher":
+        return self
+
+    def __next__(self) -> Tuple[torch.Tensor, ...]:
+        if self.pending == 0:
+            raise StopIteration
+        main = torch.cuda.current_stream(self.device)
+        # the slot handed out before this one is free again once the work enqueued so far has run
+        prev = (self.tail - 1) % self.depth
+        if self.used[prev]:
+            self.released[prev].record(main)
+        slot = self.tail
+        main.wait_event(self.ready[slot])
+        self.used[slot] = True
+        self.tail = (slot + 1) % self.depth
+        self.pending -= 1
+        while self.pending < self.depth - 1 and self._fill():
+            pass
+        return self.bufs[slot]  # type: ignore[return-value]

@@ -72,6 +72,29 @@ def test_linear_wgrad_accumulates(M, N, K):
     assert ok, info
 
 
+@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("M,N,K", [(40001, 400, 448), (65536, 448, 400), (20000, 256, 192)])
+def test_every_gemm_variant_agrees(variant, M, N, K):
+    """CTA-pair (cta_group::2), single-CTA weight-resident and tile-per-CTA kernels on one shape."""
+    torch.manual_seed(2)
+    x, w, b = rnd(M, K), rnd(N, K, scale=0.1), torch.randn(N, device=DEV)
+    dy, h = rnd(M, N), rnd(M, K).relu()
+    y = torch.full((M, N), 7.0, device=DEV, dtype=torch.bfloat16)
+    dx = torch.full((M, K), 7.0, device=DEV, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    C.gemm_set_tuning(variant, 0)
+    try:
+        C.linear_forward(x, w, b, True, y, status)
+        C.linear_dgrad(dy, w.t().contiguous(), h, dx, status)
+    finally:
+        C.gemm_set_tuning(0, 0)
+    assert status.item() == 0
+    ok, info = close(y, (x.float() @ w.float().t() + b).relu())
+    assert ok, info
+    ok, info = close(dx, (dy.float() @ w.float()) * (h.float() > 0))
+    assert ok, info
+
+
 def test_colsum_bf16():
     torch.manual_seed(3)
     dy = rnd(5000, 400)

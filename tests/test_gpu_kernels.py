@@ -292,3 +292,19 @@ def test_fused_deepfm_matches_unfused_path():
     l2, r2, f2, w2 = run(False, fold=True)
     assert all(abs(a - b) < 5e-3 for a, b in zip(l3, l2)), (l3, l2)
     assert (r3 - r2).abs().max().item() < 2e-2 and (f3 - f2).abs().max().item() < 2e-2
+
+
+@pytest.mark.gpu
+def test_device_prefetcher_order_and_reuse():
+    from kraken_b200.utils.prefetch import DevicePrefetcher
+
+    dev = torch.device("cuda", 0)
+    host = [(torch.full((1 << 16,), float(i)).pin_memory(), torch.arange(i, i + 64).pin_memory()) for i in range(7)]
+    seen = []
+    for a, b in DevicePrefetcher(iter(host), dev):
+        # enqueue work that reads the buffers, then move on: buffers must not be overwritten early
+        seen.append((a.sum(), b.clone()))
+    assert len(seen) == 7
+    for i, (s, b) in enumerate(seen):
+        assert float(s) == float(i) * (1 << 16)
+        assert torch.equal(b.cpu(), torch.arange(i, i + 64))
