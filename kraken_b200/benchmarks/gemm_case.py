@@ -14,6 +14,7 @@ def main():
     p.add_argument("--k", type=int, default=432)
     p.add_argument("--op", default="forward", choices=["forward", "dgrad", "wgrad"])
     p.add_argument("--reps", type=int, default=3)
+    p.add_argument("--bits", action="store_true", help="dgrad: ReLU mask as one bit per element instead of the activations")
     p.add_argument("--rotate", type=int, default=1, help="number of operand sets to rotate over")
     p.add_argument("--n-tiles", type=int, default=0, help="column tiles of the weight-resident variants (0 = auto)")
     p.add_argument("--variant", type=int, default=0, help="0 auto, 1 CTA pair, 2 single-CTA resident, 3 tile per CTA")
@@ -38,12 +39,17 @@ def main():
     dys = [dy] + [dy.clone() for _ in range(sets - 1)]
     dxs = [dx] + [torch.empty_like(dx) for _ in range(sets - 1)]
 
+    masks = [torch.randint(-32768, 32767, ((a.k + 15) // 16, (a.m + 63) // 64 * 64), dtype=torch.int16, device=dev) for _ in range(sets)]
+
     def run(i):
         j = i % sets
         if a.op == "forward":
             C.linear_forward(xs[j], w, b, True, ys[j], st)
         elif a.op == "dgrad":
-            C.linear_dgrad(dys[j], wt, xs[j], dxs[j], st)
+            if a.bits:
+                C.linear_dgrad(dys[j], wt, None, dxs[j], st, masks[j])
+            else:
+                C.linear_dgrad(dys[j], wt, xs[j], dxs[j], st)
         else:
             C.linear_wgrad(dys[j], xs[j], dw, st)
 

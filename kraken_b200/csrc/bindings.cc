@@ -868,7 +868,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("deepfm_pack_forward",
         [](const torch::Tensor& rows2, const torch::Tensor& inv2, const c10::optional<torch::Tensor>& rows1,
            const c10::optional<torch::Tensor>& inv1, const torch::Tensor& dense, int B, int F, int D,
-           const torch::Tensor& x, const torch::Tensor& fm_logit) {
+           const torch::Tensor& x, const torch::Tensor& fm_logit, const c10::optional<torch::Tensor>& slots2,
+           const c10::optional<torch::Tensor>& slots1) {
           need_cuda(rows2, "rows2", torch::kFloat32);
           need_cuda(dense, "dense", torch::kFloat32);
           need_cuda(x, "x", torch::kBFloat16);
@@ -885,15 +886,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           TORCH_CHECK(inv2.numel() >= static_cast<int64_t>(B) * F, "occurrence map too small");
           TORCH_CHECK(x.size(0) == B && ldx >= F * D + ND && ldx % 4 == 0 && dense.size(0) == B && fm_logit.numel() == B,
                       "deepfm_pack_forward: shape mismatch");
-          cu::deepfm_pack_forward(ptr<float>(rows2), ptr<int>(inv2), optr<float>(rows1), optr<int>(inv1),
-                                  ptr<float>(dense), B, F, D, RD, ND, reinterpret_cast<__nv_bfloat16*>(x.data_ptr()), ldx,
+          cu::deepfm_pack_forward(ptr<float>(rows2), ptr<int>(inv2), optr<int>(slots2), optr<float>(rows1), optr<int>(inv1),
+                                  optr<int>(slots1), ptr<float>(dense), B, F, D, RD, ND, reinterpret_cast<__nv_bfloat16*>(x.data_ptr()), ldx,
                                   ptr<float>(fm_logit), cur_stream());
           check_launch("deepfm_pack_forward");
-        });
+        },
+        py::arg("rows2"), py::arg("inv2"), py::arg("rows1"), py::arg("inv1"), py::arg("dense"), py::arg("B"), py::arg("F"),
+        py::arg("D"), py::arg("x"), py::arg("fm_logit"), py::arg("slots2") = py::none(), py::arg("slots1") = py::none());
   m.def("deepfm_pack_backward",
         [](const torch::Tensor& rows2, const torch::Tensor& inv2, const c10::optional<torch::Tensor>& inv1,
            const c10::optional<torch::Tensor>& dx, const torch::Tensor& dlogit, int B, int F, int D,
-           const torch::Tensor& ugrad2, const c10::optional<torch::Tensor>& ugrad1) {
+           const torch::Tensor& ugrad2, const c10::optional<torch::Tensor>& ugrad1,
+           const c10::optional<torch::Tensor>& slots2) {
           need_cuda(rows2, "rows2", torch::kFloat32);
           need_cuda(dlogit, "dlogit", torch::kFloat32);
           need_cuda(ugrad2, "ugrad2", torch::kFloat32);
@@ -914,10 +918,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
             lddx = dx->size(1);
           }
           TORCH_CHECK(dlogit.numel() == B, "deepfm_pack_backward: shape mismatch");
-          cu::deepfm_pack_backward(ptr<float>(rows2), ptr<int>(inv2), optr<int>(inv1), dxp, lddx, ptr<float>(dlogit), B, F,
+          cu::deepfm_pack_backward(ptr<float>(rows2), ptr<int>(inv2), optr<int>(slots2), optr<int>(inv1), dxp, lddx, ptr<float>(dlogit), B, F,
                                    D, RD, ptr<float>(ugrad2), optr<float>(ugrad1), cur_stream());
           check_launch("deepfm_pack_backward");
-        });
+        },
+        py::arg("rows2"), py::arg("inv2"), py::arg("inv1"), py::arg("dx"), py::arg("dlogit"), py::arg("B"), py::arg("F"),
+        py::arg("D"), py::arg("ugrad2"), py::arg("ugrad1"), py::arg("slots2") = py::none());
 
   // ---------------- table maintenance
   m.def("table_clear", [](const cu::TableHost& t) {

@@ -98,20 +98,30 @@ void bind_dense(py::module_& m) {
   };
   m.def("linear_forward", [bf, need_bf16](const torch::Tensor& x, const torch::Tensor& w,
                                           const c10::optional<torch::Tensor>& bias, bool relu, const torch::Tensor& y,
-                                          const torch::Tensor& status) {
+                                          const torch::Tensor& status, const c10::optional<torch::Tensor>& mask_out) {
     need_bf16(x, "x");
     need_bf16(w, "w");
     need_bf16(y, "y");
     const int M = x.size(0), K = x.size(1), N = w.size(0);
     TORCH_CHECK(w.size(1) == K && y.size(0) == M && y.size(1) == N, "linear_forward: shape mismatch");
+    uint16_t* mp = nullptr;
+    int ldm = 0;
+    if (mask_out.has_value()) {
+      TORCH_CHECK(mask_out->is_cuda() && mask_out->scalar_type() == torch::kInt16 && mask_out->dim() == 2 &&
+                      mask_out->stride(1) == 1 && mask_out->size(0) * 16 >= N && mask_out->size(1) >= M,
+                  "mask_out must be a CUDA int16 tensor [ceil(N / 16), >= M]");
+      mp = reinterpret_cast<uint16_t*>(mask_out->data_ptr());
+      ldm = mask_out->stride(0);
+    }
     const int rc = cu::linear_forward(bf(x), x.stride(0), bf(w), w.stride(0), optr<float>(bias),
-                                      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), y.stride(0), M, N, K, relu,
+                                      reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), y.stride(0), M, N, K, relu, mp, ldm,
                                       status.data_ptr<int>(), cur_stream());
     TORCH_CHECK(rc == 0, "linear_forward: cannot encode the TMA descriptors (pitches must be multiples of 8)");
-  });
+  }, py::arg("x"), py::arg("w"), py::arg("bias"), py::arg("relu"), py::arg("y"), py::arg("status"),
+     py::arg("mask_out") = py::none());
   m.def("linear_dgrad", [bf, need_bf16](const torch::Tensor& dy, const torch::Tensor& wt,
                                         const c10::optional<torch::Tensor>& h, const torch::Tensor& dx,
-                                        const torch::Tensor& status) {
+                                        const torch::Tensor& status, const c10::optional<torch::Tensor>& mask) {
     need_bf16(dy, "dy");
     need_bf16(wt, "wt");
     need_bf16(dx, "dx");
@@ -125,11 +135,20 @@ void bind_dense(py::module_& m) {
       hp = bf(*h);
       ldh = h->stride(0);
     }
-    const int rc = cu::linear_dgrad(bf(dy), dy.stride(0), bf(wt), wt.stride(0), hp, ldh,
+    const uint16_t* mp = nullptr;
+    int ldm = 0;
+    if (mask.has_value()) {
+      TORCH_CHECK(mask->is_cuda() && mask->scalar_type() == torch::kInt16 && mask->dim() == 2 && mask->stride(1) == 1 &&
+                      mask->size(0) * 16 >= K && mask->size(1) >= M,
+                  "mask must be a CUDA int16 tensor [ceil(K / 16), >= M]");
+      mp = reinterpret_cast<const uint16_t*>(mask->data_ptr());
+      ldm = mask->stride(0);
+    }
+    const int rc = cu::linear_dgrad(bf(dy), dy.stride(0), bf(wt), wt.stride(0), hp, ldh, mp, ldm,
                                     reinterpret_cast<__nv_bfloat16*>(dx.data_ptr()), dx.stride(0), M, N, K,
                                     status.data_ptr<int>(), cur_stream());
     TORCH_CHECK(rc == 0, "linear_dgrad: cannot encode the TMA descriptors (pitches must be multiples of 8)");
-  });
+  }, py::arg("dy"), py::arg("wt"), py::arg("h"), py::arg("dx"), py::arg("status"), py::arg("mask") = py::none());
   m.def("linear_wgrad", [bf, need_bf16](const torch::Tensor& dy, const torch::Tensor& x, const torch::Tensor& dw,
                                         const torch::Tensor& status) {
     need_bf16(dy, "dy");

@@ -33,10 +33,21 @@ __global__ void pull_wait_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, uint32_t s
     set_status(&ctrl->status, err::kTimeout);
 }
 
+// Row index of unique entry `u`: the entry itself when the rows were gathered into a receive
+// buffer, or the table slot the owner resolved for it when the kernel reads the table in place
+// (single-GPU jobs: no copy of the rows is made).  A failed lookup (slot < 0) reads row 0; the
+// status word already carries the error.
+__device__ __forceinline__ size_t row_of(const int* __restrict__ slots, int u) {
+  if (slots == nullptr) return static_cast<size_t>(u);
+  const int s = __ldg(slots + u);
+  return static_cast<size_t>(s < 0 ? 0 : s);
+}
+
 // lanes per sample = D / 4; lane l owns dims [4l, 4l + 4) of every field.
 __global__ void __launch_bounds__(kThreads)
 deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restrict__ inv2,
-                           const float* __restrict__ rows1, const int* __restrict__ inv1,
+                           const int* __restrict__ slots2, const float* __restrict__ rows1,
+                           const int* __restrict__ inv1, const int* __restrict__ slots1,
                            const float* __restrict__ dense, int B, int F, int D, int RD, int ND, int lpr,
                            __nv_bfloat16* __restrict__ x, int ldx, float* __restrict__ fm_logit) {
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -54,9 +65,8 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
       for (int c = lane; c < chunks; c += lpr) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = s;
 #pragma unroll 4
-  #pragma unroll 4
-      for (int f = 0; f < F; ++f) {
-          const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
+        for (int f = 0; f < F; ++f) {
+          const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, i2[f]) * RD) + c);
           s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
           q.x += e.x * e.x, q.y += e.y * e.y, q.z += e.z * e.z, q.w += e.w * e.w;
           __nv_bfloat162 lo = __floats2bfloat162_rn(e.x, e.y), hi = __floats2bfloat162_rn(e.z, e.w);
@@ -70,10 +80,10 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
       // first-order weights, dense features and the zero pad, spread over the sample's lanes
       if (rows1 != nullptr) {
         const int* i1 = inv1 + static_cast<size_t>(b) * F;
-        for (int f = lane; f < F; f += lpr) part += __ldcg(rows1 + i1[f]);
+        for (int f = lane; f < F; f += lpr) part += __ldcg(rows1 + row_of(slots1, i1[f]));
       } else {
         // folded layout: column D of the same row is the field's first-order weight
-        for (int f = lane; f < F; f += lpr) part += __ldcg(rows2 + static_cast<size_t>(i2[f]) * RD + D);
+        for (int f = lane; f < F; f += lpr) part += __ldcg(rows2 + row_of(slots2, i2[f]) * RD + D);
       }
       const int base = F * D;
       for (int j = lane; base + j < ldx; j += lpr)
@@ -86,7 +96,7 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
 
 __global__ void __launch_bounds__(kThreads)
 deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restrict__ inv2,
-                            const int* __restrict__ inv1, const __nv_bfloat16* __restrict__ dx, int lddx,
+                            const int* __restrict__ slots2, const int* __restrict__ inv1, const __nv_bfloat16* __restrict__ dx, int lddx,
                             const float* __restrict__ dlogit, int B, int F, int D, int RD, int lpr, float* ugrad2,
                             float* ugrad1) {
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -101,12 +111,12 @@ deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restri
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
       for (int f = 0; f < F; ++f) {
-        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
+        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, i2[f]) * RD) + c);
         s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
       }
 #pragma unroll 4
       for (int f = 0; f < F; ++f) {
-        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + static_cast<size_t>(i2[f]) * RD) + c);
+        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, i2[f]) * RD) + c);
         float4 d = make_float4(g * (s.x - e.x), g * (s.y - e.y), g * (s.z - e.z), g * (s.w - e.w));
         if (dxr) {
           const uint2 p = *reinterpret_cast<const uint2*>(dxr + f * D + c * 4);
@@ -154,22 +164,23 @@ void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cud
   pull_wait_kernel<<<1, 32, 0, stream>>>(to_sym(sym), lay, ctrl, spin_limit);
 }
 
-void deepfm_pack_forward(const float* rows2, const int* inv2, const float* rows1, const int* inv1, const float* dense,
-                         int B, int F, int D, int RD, int ND, __nv_bfloat16* x, int ldx, float* fm_logit,
-                         cudaStream_t stream) {
+void deepfm_pack_forward(const float* rows2, const int* inv2, const int* slots2, const float* rows1, const int* inv1,
+                         const int* slots1, const float* dense, int B, int F, int D, int RD, int ND, __nv_bfloat16* x,
+                         int ldx, float* fm_logit, cudaStream_t stream) {
   if (B <= 0) return;
   const int lpr = lanes_for_chunks(D / 4);
-  deepfm_pack_forward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, rows1, inv1, dense, B, F, D, RD,
-                                                                        ND, lpr, x, ldx, fm_logit);
+  deepfm_pack_forward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, slots2, rows1, inv1, slots1, dense,
+                                                                        B, F, D, RD, ND, lpr, x, ldx, fm_logit);
 }
 
-void deepfm_pack_backward(const float* rows2, const int* inv2, const int* inv1, const __nv_bfloat16* dx, int lddx,
+void deepfm_pack_backward(const float* rows2, const int* inv2, const int* slots2, const int* inv1,
+                          const __nv_bfloat16* dx, int lddx,
                           const float* dlogit, int B, int F, int D, int RD, float* ugrad2, float* ugrad1,
                           cudaStream_t stream) {
   if (B <= 0) return;
   const int lpr = lanes_for_chunks(D / 4);
-  deepfm_pack_backward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, inv1, dx, lddx, dlogit, B, F, D,
-                                                                         RD, lpr, ugrad2, ugrad1);
+  deepfm_pack_backward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, slots2, inv1, dx, lddx, dlogit, B,
+                                                                         F, D, RD, lpr, ugrad2, ugrad1);
 }
 
 }  // namespace cu

@@ -41,8 +41,13 @@ struct GemmArgs {
   int kb_per_split;       // k-blocks per blockIdx.z
   int relu;
   const float* bias;      // [N]            (EPI_BIAS_ACT)
-  const __nv_bfloat16* H; // [M, ldh]       (EPI_RELU_MASK)
+  const __nv_bfloat16* H; // [M, ldh]       (EPI_RELU_MASK, when no bit mask is given)
   int ldh;
+  const uint16_t* mask;   // [chunks, ldm] one bit per element: word (c, r) = columns [16c, 16c + 16) of row r
+  uint16_t* mask_out;     // same layout, written by EPI_BIAS_ACT with relu: bit = output > 0
+  int ldm;                // row pitch of the mask in words (>= M): a warp's 32 rows are 64 contiguous bytes
+  int mask_chunks;        // number of 16-column words per row that the mask holds
+  int out_v8;             // bf16 output rows and tile columns are 32-byte aligned: one 256-bit store per chunk
   __nv_bfloat16* out;     // [M, ldo] bf16  (EPI_BIAS_ACT, EPI_RELU_MASK)
   int ldo;
   float* out32;           // [M, ldo32] f32 (EPI_RED_F32)
@@ -67,13 +72,18 @@ __device__ __noinline__ void epilogue_tail(const GemmArgs& g, const float* s_bia
   tc::tmem_ld16(taddr, r);
   tc::tmem_ld_wait();
   if (row >= g.M) return;
+  uint32_t bits_out = 0;
+  const uint32_t bits_in =
+      (EPI == EPI_RELU_MASK && g.mask != nullptr) ? g.mask[static_cast<size_t>(col >> 4) * g.ldm + row] : 0xFFFFu;
   for (int j = 0; j < 16 && col + j < g.N; ++j) {
     float v = __uint_as_float(r[j]);
     if (EPI == EPI_BIAS_ACT) {
       v += s_bias[c + j];
       if (g.relu) v = fmaxf(v, 0.f);
+      if (v > 0.f) bits_out |= 1u << j;
     }
-    if (EPI == EPI_RELU_MASK && g.H != nullptr &&
+    if (EPI == EPI_RELU_MASK && g.mask != nullptr && !((bits_in >> j) & 1u)) v = 0.f;
+    if (EPI == EPI_RELU_MASK && g.mask == nullptr && g.H != nullptr &&
         !(__bfloat162float(g.H[static_cast<size_t>(row) * g.ldh + col + j]) > 0.f))
       v = 0.f;
     if (EPI == EPI_RED_F32)
@@ -81,32 +91,32 @@ __device__ __noinline__ void epilogue_tail(const GemmArgs& g, const float* s_bia
     else
       g.out[static_cast<size_t>(row) * g.ldo + col + j] = __float2bfloat16(v);
   }
+  if (EPI == EPI_BIAS_ACT && g.mask_out != nullptr)
+    g.mask_out[static_cast<size_t>(col >> 4) * g.ldm + row] = static_cast<uint16_t>(bits_out);
 }
 
 // Fast path: all 16 columns valid.  Everything is unrolled with constant indices so the
 // accumulator chunk stays in registers.
 template <int EPI>
 __device__ __forceinline__ void epilogue_full(const GemmArgs& g, const float* s_bias, int row, int col, int c,
-                                              const uint32_t (&r)[16], const uint4& h0, const uint4& h1) {
+                                              const uint32_t (&r)[16], uint32_t keep_bits) {
   float v[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
   if (EPI == EPI_BIAS_ACT) {
+    uint32_t bits = 0;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       v[j] += s_bias[c + j];
       if (g.relu) v[j] = fmaxf(v[j], 0.f);
+      bits |= (v[j] > 0.f ? 1u : 0u) << j;
     }
+    if (g.mask_out != nullptr) g.mask_out[static_cast<size_t>(col >> 4) * g.ldm + row] = static_cast<uint16_t>(bits);
   }
   if (EPI == EPI_RELU_MASK) {
-    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      // bf16 > 0  <=>  sign bit clear and not zero
-      const uint32_t lo = hw[j] & 0xFFFFu, hi = hw[j] >> 16;
-      if (lo == 0u || (lo & 0x8000u)) v[2 * j] = 0.f;
-      if (hi == 0u || (hi & 0x8000u)) v[2 * j + 1] = 0.f;
-    }
+    for (int j = 0; j < 16; ++j)
+      if (!((keep_bits >> j) & 1u)) v[j] = 0.f;
   }
   if (EPI == EPI_RED_F32) {
     float* o = g.out32 + static_cast<size_t>(row) * g.ldo32 + col;
@@ -122,18 +132,63 @@ __device__ __forceinline__ void epilogue_full(const GemmArgs& g, const float* s_
     w0.z = pack_bf16(v[4], v[5]);   w0.w = pack_bf16(v[6], v[7]);
     w1.x = pack_bf16(v[8], v[9]);   w1.y = pack_bf16(v[10], v[11]);
     w1.z = pack_bf16(v[12], v[13]); w1.w = pack_bf16(v[14], v[15]);
-    *reinterpret_cast<uint4*>(o) = w0;
-    *reinterpret_cast<uint4*>(o + 8) = w1;
+    if (g.out_v8) {
+      // one 32-byte sector per request: the L2 write-request rate, not bytes, bounds this epilogue
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o), "r"(w0.x), "r"(w0.y), "r"(w0.z),
+                   "r"(w0.w), "r"(w1.x), "r"(w1.y), "r"(w1.z), "r"(w1.w)
+                   : "memory");
+    } else {
+      *reinterpret_cast<uint4*>(o) = w0;
+      *reinterpret_cast<uint4*>(o + 8) = w1;
+    }
   }
+}
+
+// 16 keep-bits from 16 bf16 activations: bf16 > 0  <=>  sign bit clear and not zero.
+__device__ __forceinline__ uint32_t keep_bits_of(const uint4& h0, const uint4& h1) {
+  const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+  uint32_t bits = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t lo = hw[j] & 0xFFFFu, hi = hw[j] >> 16;
+    bits |= ((lo != 0u && !(lo & 0x8000u)) ? 1u : 0u) << (2 * j);
+    bits |= ((hi != 0u && !(hi & 0x8000u)) ? 1u : 0u) << (2 * j + 1);
+  }
+  return bits;
+}
+
+// The mask words of one row for up to eight 16-column chunks starting at chunk `cb`, packed into
+// 128 bits.  Issued before the accumulator wait, so the loads fly while the MMAs run.
+struct RowMask {
+  unsigned long long lo, hi;
+  __device__ __forceinline__ uint32_t chunk(int i) const {
+    return static_cast<uint32_t>((i < 4 ? lo >> (16 * i) : hi >> (16 * (i - 4))) & 0xFFFFull);
+  }
+};
+
+__device__ __forceinline__ RowMask load_row_mask(const GemmArgs& g, int row, int cb, int nchunks) {
+  RowMask m{~0ull, ~0ull};
+  if (g.mask == nullptr || row >= g.M) return m;
+  const uint16_t* p = g.mask + row;
+  unsigned long long lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const unsigned long long w =
+        (i < nchunks && cb + i < g.mask_chunks) ? __ldg(p + static_cast<size_t>(cb + i) * g.ldm) : 0xFFFFull;
+    if (i < 4) lo |= w << (16 * i); else hi |= w << (16 * (i - 4));
+  }
+  m.lo = lo, m.hi = hi;
+  return m;
 }
 
 // One epilogue warp's share of a 128 x BN accumulator: TMEM lanes of its quarter (one row per
 // thread) and the column range [c_begin, c_end).  Two 16-column chunks are in flight per wait.
 template <int EPI>
 __device__ __forceinline__ void epilogue_rows(const GemmArgs& g, const float* s_bias, uint32_t t_row, int row, int n0,
-                                              int c_begin, int c_end) {
+                                              int c_begin, int c_end, const RowMask& rm) {
   const bool in_rows = row < g.M;
-  const bool masked = EPI == EPI_RELU_MASK && g.H != nullptr;
+  // ReLU keep-bits come from the bit mask when there is one (already in registers), else from H
+  const bool from_h = EPI == EPI_RELU_MASK && g.mask == nullptr && g.H != nullptr;
   int c = c_begin;
   // pairs of full chunks: both loads are issued before the single wait
   for (; c + 32 <= c_end && n0 + c + 32 <= g.N; c += 32) {
@@ -141,18 +196,16 @@ __device__ __forceinline__ void epilogue_rows(const GemmArgs& g, const float* s_
     uint32_t r0[16], r1[16];
     tc::tmem_ld16(t_row + c, r0);
     tc::tmem_ld16(t_row + c + 16, r1);
-    uint4 h00 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), h01 = h00, h10 = h00, h11 = h00;
-    if (masked && in_rows) {
+    uint32_t k0 = rm.chunk((c - c_begin) >> 4), k1 = rm.chunk(((c - c_begin) >> 4) + 1);
+    if (from_h && in_rows) {
       const __nv_bfloat16* h = g.H + static_cast<size_t>(row) * g.ldh + col;
-      h00 = *reinterpret_cast<const uint4*>(h);
-      h01 = *reinterpret_cast<const uint4*>(h + 8);
-      h10 = *reinterpret_cast<const uint4*>(h + 16);
-      h11 = *reinterpret_cast<const uint4*>(h + 24);
+      k0 = keep_bits_of(*reinterpret_cast<const uint4*>(h), *reinterpret_cast<const uint4*>(h + 8));
+      k1 = keep_bits_of(*reinterpret_cast<const uint4*>(h + 16), *reinterpret_cast<const uint4*>(h + 24));
     }
     tc::tmem_ld_wait();
     if (in_rows) {
-      epilogue_full<EPI>(g, s_bias, row, col, c, r0, h00, h01);
-      epilogue_full<EPI>(g, s_bias, row, col + 16, c + 16, r1, h10, h11);
+      epilogue_full<EPI>(g, s_bias, row, col, c, r0, k0);
+      epilogue_full<EPI>(g, s_bias, row, col + 16, c + 16, r1, k1);
     }
   }
   // what is left: single chunks, full or straddling N (all conditions are warp-uniform)
@@ -161,14 +214,13 @@ __device__ __forceinline__ void epilogue_rows(const GemmArgs& g, const float* s_
     if (col + 16 <= g.N) {
       uint32_t r0[16];
       tc::tmem_ld16(t_row + c, r0);
-      uint4 h00 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u), h01 = h00;
-      if (masked && in_rows) {
+      uint32_t k0 = rm.chunk((c - c_begin) >> 4);
+      if (from_h && in_rows) {
         const __nv_bfloat16* h = g.H + static_cast<size_t>(row) * g.ldh + col;
-        h00 = *reinterpret_cast<const uint4*>(h);
-        h01 = *reinterpret_cast<const uint4*>(h + 8);
+        k0 = keep_bits_of(*reinterpret_cast<const uint4*>(h), *reinterpret_cast<const uint4*>(h + 8));
       }
       tc::tmem_ld_wait();
-      if (in_rows) epilogue_full<EPI>(g, s_bias, row, col, c, r0, h00, h01);
+      if (in_rows) epilogue_full<EPI>(g, s_bias, row, col, c, r0, k0);
     } else {
       epilogue_tail<EPI>(g, s_bias, t_row + c, row, col, c);
     }
@@ -294,16 +346,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp >= 2) {
     // ---------------- epilogue: thread = one accumulator row, warp = one column half
+    const int quarter = warp & 3;  // a warp may only read TMEM lanes [32 * (warp % 4), +32)
+    const int row = m0 + quarter * 32 + lane;
+    int c_begin, c_end;
+    epi_cols(g.BN, warp - 2, &c_begin, &c_end);
+    RowMask rm{~0ull, ~0ull};
+    if (EPI == EPI_RELU_MASK) rm = load_row_mask(g, row, (n0 + c_begin) >> 4, (c_end - c_begin + 15) >> 4);
     const bool ok = tc::mbar_wait(&acc_bar, 0, kWaitLimit);
     tc::fence_after_sync();
     if (!ok && lane == 0) atomicCAS(g.status, 0, err::kTimeout);
-    const int quarter = warp & 3;  // a warp may only read TMEM lanes [32 * (warp % 4), +32)
-    const int row = m0 + quarter * 32 + lane;
-    if (ok && abort_flag == 0 && num_kb > 0) {
-      int c_begin, c_end;
-      epi_cols(g.BN, warp - 2, &c_begin, &c_end);
-      epilogue_rows<EPI>(g, s_bias, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), row, n0, c_begin, c_end);
-    }
+    if (ok && abort_flag == 0 && num_kb > 0)
+      epilogue_rows<EPI>(g, s_bias, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), row, n0, c_begin, c_end, rm);
   }
 
   // ---------------- teardown: let the copies that were issued land, then free tensor memory
@@ -431,9 +484,15 @@ gemm_bres_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp >= 2) {
     // ---------------- epilogue
     const int quarter = warp & 3;
+    int c_begin, c_end;
+    epi_cols(g.BN, warp - 2, &c_begin, &c_end);
     bool ok = true;
     for (int j = 0; j < my_tiles && ok; ++j) {
       const int buf = j & 1;
+      const int tile = blockIdx.x + j * gridDim.x;
+      const int row = tile * kBM + quarter * 32 + lane;
+      RowMask rm{~0ull, ~0ull};
+      if (EPI == EPI_RELU_MASK) rm = load_row_mask(g, row, (n0 + c_begin) >> 4, (c_end - c_begin + 15) >> 4);
       ok = tc::mbar_wait(&acc_full[buf], static_cast<uint32_t>(j >> 1) & 1, kWaitLimit);
       tc::fence_after_sync();
       if (!ok || abort_flag != 0) {
@@ -441,12 +500,8 @@ gemm_bres_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ok = false;
         break;
       }
-      const int tile = blockIdx.x + j * gridDim.x;
-      const int row = tile * kBM + quarter * 32 + lane;
-      int c_begin, c_end;
-      epi_cols(g.BN, warp - 2, &c_begin, &c_end);
       epilogue_rows<EPI>(g, s_bias, tmem_base + buf * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16), row, n0,
-                         c_begin, c_end);
+                         c_begin, c_end, rm);
       tc::fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
@@ -594,21 +649,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quarter = warp & 3;
     const uint32_t lead_acc_empty[2] = {tc::map_to_cta(tc::smem_u32(&acc_empty[0]), 0),
                                         tc::map_to_cta(tc::smem_u32(&acc_empty[1]), 0)};
+    int c_begin, c_end;
+    epi_cols(g.BN, warp - 2, &c_begin, &c_end);
     bool ok = true;
     for (int j = 0; j < my_tiles && ok; ++j) {
       const int buf = j & 1;
+      const int tile = pair + j * pairs;
+      const int row = tile * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
+      RowMask rm{~0ull, ~0ull};
+      if (EPI == EPI_RELU_MASK) rm = load_row_mask(g, row, (n0 + c_begin) >> 4, (c_end - c_begin + 15) >> 4);
       ok = tc::mbar_wait(&acc_full[buf], static_cast<uint32_t>(j >> 1) & 1, kWaitLimit);
       tc::fence_after_sync();
       if (!ok) {
         if (lane == 0) atomicCAS(g.status, 0, err::kTimeout);
         break;
       }
-      const int tile = pair + j * pairs;
-      const int row = tile * 2 * kBM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
-      int c_begin, c_end;
-      epi_cols(g.BN, warp - 2, &c_begin, &c_end);
       epilogue_rows<EPI>(g, s_bias, tmem_base + buf * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16), row, n0,
-                         c_begin, c_end);
+                         c_begin, c_end, rm);
       tc::fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive_cluster(lead_acc_empty[buf]);
@@ -818,8 +875,14 @@ int launch_resident(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cu
 
 }  // namespace
 
+// 256-bit stores need 32-byte aligned rows; tile columns are multiples of 16 elements already.
+static int can_store_v8(const void* out, int ld) {
+  return (reinterpret_cast<uintptr_t>(out) % 32 == 0 && ld % 16 == 0) ? 1 : 0;
+}
+
 int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int ldw, const float* bias,
-                   __nv_bfloat16* Y, int ldy, int M, int N, int K, bool relu, int* status, cudaStream_t stream) {
+                   __nv_bfloat16* Y, int ldy, int M, int N, int K, bool relu, uint16_t* mask_out, int ldm, int* status,
+                   cudaStream_t stream) {
   GemmArgs g{};
   g.M = M, g.N = N, g.K = K;
   g.BN = pick_bn(N, 16);
@@ -828,6 +891,9 @@ int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int 
   g.relu = relu ? 1 : 0;
   g.bias = bias;
   g.out = Y, g.ldo = ldy;
+  g.mask_out = mask_out, g.ldm = ldm, g.mask_chunks = (N + 15) / 16;
+  g.out_v8 = can_store_v8(Y, ldy);
+  if (mask_out != nullptr && ldm < M) return -1;
   g.status = status;
   CUtensorMap ta, tb;
   const bool pair = (g_variant == 0 || g_variant == 1) && plan_pair(M, N, K, &g.BN, &g.stages);
@@ -842,7 +908,8 @@ int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int 
 }
 
 int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int ldwt, const __nv_bfloat16* H,
-                 int ldh, __nv_bfloat16* dX, int lddx, int M, int N, int K, int* status, cudaStream_t stream) {
+                 int ldh, const uint16_t* mask, int ldm, __nv_bfloat16* dX, int lddx, int M, int N, int K, int* status,
+                 cudaStream_t stream) {
   // out dX is [M, K]; the contraction runs over the layer's N outputs
   GemmArgs g{};
   g.M = M, g.N = K, g.K = N;
@@ -850,6 +917,9 @@ int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int
   g.stages = 2;
   g.kb_per_split = (N + kBK - 1) / kBK;
   g.H = H, g.ldh = ldh;
+  g.mask = mask, g.ldm = ldm, g.mask_chunks = (K + 15) / 16;
+  g.out_v8 = can_store_v8(dX, lddx);
+  if (mask != nullptr && ldm < M) return -1;
   g.out = dX, g.ldo = lddx;
   g.status = status;
   CUtensorMap ta, tb;

@@ -24,11 +24,19 @@ namespace cu {
 // Each returns 0 on success or a negative code when a tensor map cannot be encoded
 // (bad alignment / driver entry point missing).  `status` (device int) receives
 // err::kTimeout if a pipeline wait inside the kernel gives up.
+//
+// ReLU mask: the forward pass can leave one bit per output element (output > 0) in
+// mask_out[ceil(N / 16), ldm] (uint16 word (c, r) = columns [16c, 16c + 16) of row r, ldm >= M, so the
+// 32 rows of a warp write 64 contiguous bytes); the input gradient of the next layer then takes that
+// bit mask instead of re-reading the bf16 activations H, which cuts its extra read traffic
+// sixteen-fold.  Either may be null; with both null no mask is applied.
 int linear_forward(const __nv_bfloat16* X, int ldx, const __nv_bfloat16* W, int ldw, const float* bias,
-                   __nv_bfloat16* Y, int ldy, int M, int N, int K, bool relu, int* status, cudaStream_t stream);
+                   __nv_bfloat16* Y, int ldy, int M, int N, int K, bool relu, uint16_t* mask_out, int ldm, int* status,
+                   cudaStream_t stream);
 
 int linear_dgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* Wt, int ldwt, const __nv_bfloat16* H,
-                 int ldh, __nv_bfloat16* dX, int lddx, int M, int N, int K, int* status, cudaStream_t stream);
+                 int ldh, const uint16_t* mask, int ldm, __nv_bfloat16* dX, int lddx, int M, int N, int K, int* status,
+                 cudaStream_t stream);
 
 int linear_wgrad(const __nv_bfloat16* dY, int lddy, const __nv_bfloat16* X, int ldx, float* dW, int lddw, int M,
                  int N, int K, int* status, cudaStream_t stream);

@@ -1,0 +1,175 @@
+// Stand-alone exercise of the host-side C++ (router, serializer, checkpoint files, CPU shard,
+// CPU reference kernels, task queue) meant to be compiled with -fsanitize=address,undefined or
+// -fsanitize=thread and run by the test-suite.  The reference builds with plain -O3 / -O0 -g and has
+// no sanitizer job (CMakeLists.txt:54-55); its known latent races are listed next to the code
+// that replaces them.  Exit code 0 = every check passed and the sanitizer stayed silent.
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <filesystem>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../core/checkpoint.h"
+#include "../core/hash.h"
+#include "../core/router.h"
+#include "../core/serialize.h"
+#include "../core/task_queue.h"
+#include "../cpu/cpu_ops.h"
+#include "../cpu/cpu_shard.h"
+
+using namespace kb;
+
+#define CHECK(cond)                                                        \
+  do {                                                                     \
+    if (!(cond)) {                                                         \
+      std::fprintf(stderr, "%s:%d: check failed: %s\n", __FILE__, __LINE__, #cond); \
+      std::exit(1);                                                        \
+    }                                                                      \
+  } while (0)
+
+static void router_and_serializer() {
+  Router r = Router::ForRanks(4);
+  CHECK(r.nodes().size() == 4);
+  std::vector<int> hits(4, 0);
+  for (uint64_t i = 0; i < 4000; ++i) hits[r.Hit(Mix64(i))]++;
+  for (int h : hits) CHECK(h > 0);
+  MemSink sink;
+  Writer w(&sink);
+  r.Save(&w);
+  MemSource src(sink.data(), sink.size());
+  Reader rd(&src);
+  Router back = Router::Load(&rd);
+  CHECK(back == r);
+  CHECK(r.Remove(3) && !r.Contains(3) && r.version() != back.version());
+}
+
+static void shard_checkpoint_round_trip(const std::string& dir) {
+  CpuShard shard(7);
+  Conf oc;
+  oc["beta1"] = "0.9";
+  oc["beta2"] = "0.999";
+  shard.InitModel("m", OptimType::kAdam, oc);
+  std::vector<float> dense(300, 0.5f);
+  shard.CreateDenseTable(0, "w", {30, 10}, dense.data());
+  Conf ic;
+  ic["mean"] = "0";
+  ic["stddev"] = "0.1";
+  shard.CreateSparseTable(1, "emb", 8, InitializerType::kNormal, ic);
+
+  std::vector<uint64_t> ids;
+  for (uint64_t i = 0; i < 500; ++i) ids.push_back(i * 7919u + 3);
+  std::vector<float> rows(ids.size() * 8), grads(ids.size() * 8, 0.25f);
+  for (int step = 0; step < 3; ++step) {
+    shard.PullSparse(1, ids.data(), static_cast<int64_t>(ids.size()), rows.data());
+    CHECK(shard.PushSparse(1, ids.data(), static_cast<int64_t>(ids.size()), grads.data(), 0.01f) == 0);
+    std::vector<float> g(300, 0.1f);
+    shard.PushDense(0, g.data(), 300, 0.01f);
+  }
+  CHECK(shard.SparseSize(1) == static_cast<int64_t>(ids.size()));
+
+  // save: dense + sparse files of one shard, then load them into a fresh shard
+  std::filesystem::create_directories(dir);
+  ckpt::SaveModel(dir, shard.meta());
+  ckpt::SaveRouter(dir, Router::ForRanks(1));
+  ckpt::SaveDense(dir, 0, "w", shard.ExportDense(0));
+  ckpt::SparseHeader h;
+  h.id = 1, h.name = "emb", h.dim = 8, h.init_type = InitializerType::kNormal, h.init_conf = ic;
+  ckpt::SaveSparse(dir, h, shard.ExportSparse(1));
+
+  ModelMeta meta = ckpt::LoadModel(dir);
+  CHECK(meta.name == "m");
+  CpuShard fresh(7);
+  fresh.InitModel(meta.name, meta.optim_type, meta.optim_conf);
+  uint64_t id = 99;
+  Value v;
+  CHECK(ckpt::LoadDense(dir, "w", &id, &v) && id == 0);
+  fresh.CreateDenseTable(0, "w", {30, 10}, dense.data());
+  fresh.ImportDense(0, "w", v);
+  ckpt::SparseHeader h2;
+  ckpt::SparseColumns cols;
+  ckpt::RowFilter all;
+  CHECK(ckpt::LoadSparse(dir, "emb", all, &h2, &cols) && h2.dim == 8 && cols.ids.size() == ids.size());
+  fresh.CreateSparseTable(1, "emb", 8, h2.init_type, h2.init_conf);
+  fresh.ImportSparse(1, cols);
+  std::vector<float> a(ids.size() * 8), b(ids.size() * 8);
+  shard.PullSparse(1, ids.data(), static_cast<int64_t>(ids.size()), a.data());
+  fresh.PullSparse(1, ids.data(), static_cast<int64_t>(ids.size()), b.data());
+  for (size_t i = 0; i < a.size(); ++i) CHECK(a[i] == b[i]);
+  std::vector<float> da(300), db(300);
+  shard.PullDense(0, da.data());
+  fresh.PullDense(0, db.data());
+  for (size_t i = 0; i < 300; ++i) CHECK(da[i] == db[i]);
+
+  // half of the rows through the modulo filter of rank 1 of 2
+  ckpt::RowFilter half;
+  half.mode = ckpt::RowFilter::kModulo, half.world = 2, half.rank = 1;
+  ckpt::SparseColumns part;
+  CHECK(ckpt::LoadSparse(dir, "emb", half, &h2, &part));
+  CHECK(!part.ids.empty() && part.ids.size() < ids.size());
+  for (uint64_t k : part.ids) CHECK(OwnerOf(0, k, 2) == 1);
+}
+
+static void reference_kernels() {
+  std::vector<uint64_t> ids = {5, 9, 5, 1, 9, 9};
+  std::vector<uint64_t> uniq;
+  std::vector<int64_t> inv;
+  cpu::Dedup(ids.data(), 6, &uniq, &inv);
+  CHECK(uniq.size() == 3 && inv.size() == 6);
+  for (size_t i = 0; i < ids.size(); ++i) CHECK(uniq[inv[i]] == ids[i]);
+  std::vector<float> g(6 * 2, 1.f), out(3 * 2, 0.f);
+  cpu::SegmentSum(g.data(), inv.data(), 6, 2, 3, out.data());
+  CHECK(out[inv[1] * 2] == 3.f && out[inv[3] * 2] == 1.f);
+
+  std::vector<float> x(1000);
+  for (size_t i = 0; i < x.size(); ++i) x[i] = std::sin(0.37f * static_cast<float>(i)) * static_cast<float>(i % 17);
+  cpu::DctState st;
+  std::vector<int64_t> idx;
+  std::vector<float> vals;
+  CHECK(cpu::DctCompress(x.data(), 1000, 10, 0.75f, &st, &idx, &vals));
+  CHECK(!idx.empty() && idx.size() <= 400 && idx.size() == vals.size());
+  for (size_t i = 1; i < idx.size(); ++i) CHECK(idx[i] > idx[i - 1]);
+  std::vector<float> small(100, 1.f);
+  CHECK(!cpu::DctCompress(small.data(), 100, 10, 0.75f, &st, &idx, &vals));
+}
+
+// Four workers drive one shard through a mutex, as the parameter-server process does.
+static void threaded_queue() {
+  CpuShard shard(1);
+  shard.InitModel("t", OptimType::kSGD, Conf{});
+  shard.CreateSparseTable(0, "e", 4, InitializerType::kConstant, Conf{});
+  std::mutex mu;
+  std::atomic<int> done{0};
+  TaskQueue q(4);
+  Latch latch(64);
+  for (int t = 0; t < 64; ++t) {
+    q.Enqueue([&, t] {
+      std::vector<uint64_t> ids = {static_cast<uint64_t>(t % 8), static_cast<uint64_t>(100 + t)};
+      std::vector<float> rows(8), grads(8, 1.f);
+      {
+        std::lock_guard<std::mutex> g(mu);
+        shard.PullSparse(0, ids.data(), 2, rows.data());
+        shard.PushSparse(0, ids.data(), 2, grads.data(), 0.5f);
+      }
+      done.fetch_add(1);
+      latch.Release();
+    });
+  }
+  CHECK(latch.WaitFor(30.0));
+  q.Drain();
+  CHECK(done.load() == 64 && q.Pending() == 0);
+  CHECK(shard.SparseSize(0) == 8 + 64);
+  q.Stop();
+}
+
+int main(int argc, char** argv) {
+  const std::string dir = argc > 1 ? argv[1] : "selftest_ckpt";
+  router_and_serializer();
+  shard_checkpoint_round_trip(dir);
+  reference_kernels();
+  threaded_queue();
+  std::puts("host selftest: ok");
+  return 0;
+}

@@ -26,11 +26,19 @@ class MLP(torch.nn.Module):
         self.sizes = list(sizes)
         self.use_tensor_cores = use_tensor_cores and fused.supported(in_features, sizes)
 
-    def forward(self, x: torch.Tensor, input_grad_cols: int = 0, addend=None) -> torch.Tensor:
+    def prepare(self):
+        """Starts casting the weights for the tensor-core path on a side stream (CUDA only); pass
+        the result as ``prepared`` to ``forward``.  Returns None where there is nothing to do."""
+        w = self.layers[0].weight
+        if w.is_cuda and self.use_tensor_cores and len(self.layers) > 1:
+            return fused.prepare_weights([l.weight for l in self.layers])
+        return None
+
+    def forward(self, x: torch.Tensor, input_grad_cols: int = 0, addend=None, prepared=None) -> torch.Tensor:
         """addend [M]: added to a single-output head (fused into the head kernel on CUDA)."""
         if x.is_cuda and self.use_tensor_cores:
             return fused.fused_mlp(x, [l.weight for l in self.layers], [l.bias for l in self.layers],
-                                   input_grad_cols if input_grad_cols % 8 == 0 else 0, addend)
+                                   input_grad_cols if input_grad_cols % 8 == 0 else 0, addend, prepared)
         if addend is not None:
             return self.forward(x) + addend.reshape(-1, 1)
         x = x.float()

@@ -30,6 +30,36 @@ def _side_stream(device: torch.device) -> torch.cuda.Stream:
 
 
 
+class PreparedWeights:
+    """bf16 copies of the hidden layers' weights (both layouts), cast on the side stream."""
+
+    def __init__(self, w16s, wt16s, event):
+        self.w16s, self.wt16s, self.event = w16s, wt16s, event
+
+
+def prepare_weights(weights: Sequence[torch.Tensor]) -> PreparedWeights:
+    """Starts the fp32 -> bf16 casts of the hidden layers' weights on the side stream and returns
+    at once.  A model calls this before work that does not depend on the weights (the sparse
+    pull of a recommender), hands the result to ``fused_mlp(prepared=...)``, and the casts run
+    beside that work instead of in front of the first GEMM."""
+    dev = weights[0].device
+    main = torch.cuda.current_stream(dev)
+    side = _side_stream(dev)
+    side.wait_stream(main)
+    w16s, wt16s = [], []
+    with torch.cuda.stream(side):
+        for w in weights[:-1]:
+            counters.add()
+            w16, wt16 = C.cast_w_wt(w.detach().contiguous())
+            w16.record_stream(main)
+            wt16.record_stream(main)
+            w16s.append(w16)
+            wt16s.append(wt16)
+        event = torch.cuda.Event()
+        event.record(side)
+    return PreparedWeights(w16s, wt16s, event)
+
+
 def gemm_status(device: torch.device) -> torch.Tensor:
     """Device word in which the GEMM kernels record a pipeline wait that gave up."""
     key = (device.type, device.index)
@@ -63,22 +93,31 @@ def _grad_target(p: torch.Tensor) -> torch.Tensor:
 
 class _FusedMLP(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, addend, n_layers, input_grad_cols, *params):
+    def forward(ctx, x, addend, n_layers, input_grad_cols, prepared, *params):
         ws, bs = params[:n_layers], params[n_layers:]
         dev = x.device
+        if prepared is not None:
+            torch.cuda.current_stream(dev).wait_event(prepared.event)
         st = gemm_status(dev)
         h = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
         acts = [h]
         M = h.shape[0]
         wts = []
+        masks = [None]  # masks[i] belongs to acts[i]; the MLP input has none
         for i in range(n_layers - 1):
-            counters.add()
-            w16, wt16 = C.cast_w_wt(ws[i].detach().contiguous())  # both layouts in one pass; wt16 is for backward
+            if prepared is not None:
+                w16, wt16 = prepared.w16s[i], prepared.wt16s[i]
+            else:
+                counters.add()
+                w16, wt16 = C.cast_w_wt(ws[i].detach().contiguous())  # both layouts in one pass; wt16 is for backward
             wts.append(wt16)
             y = torch.empty((M, w16.shape[0]), dtype=torch.bfloat16, device=dev)
+            # one bit per output (> 0): the next layer's input gradient masks with it instead of re-reading y
+            mask = torch.empty(((w16.shape[0] + 15) // 16, (M + 63) // 64 * 64), dtype=torch.int16, device=dev)
             counters.add()
-            C.linear_forward(h, w16, bs[i].detach(), True, y, st)
+            C.linear_forward(h, w16, bs[i].detach(), True, y, st, mask)
             acts.append(y)
+            masks.append(mask)
             h = y
         wl, bl = ws[-1].detach(), bs[-1].detach()
         if wl.shape[0] == 1:
@@ -97,7 +136,7 @@ class _FusedMLP(torch.autograd.Function):
             out = torch.addmm(bl, h.float(), wl.t())  # narrow odd-width head: library fp32 matmul
         if addend is not None:
             out = out + addend.reshape(M, 1).to(out.dtype)
-        ctx.acts, ctx.ws, ctx.bs, ctx.n_layers, ctx.wts = acts, ws, bs, n_layers, wts
+        ctx.acts, ctx.ws, ctx.bs, ctx.n_layers, ctx.wts, ctx.masks = acts, ws, bs, n_layers, wts, masks
         ctx.x_needs_grad = x.requires_grad
         ctx.input_grad_cols = input_grad_cols
         ctx.x_dtype = x.dtype
@@ -145,7 +184,8 @@ class _FusedMLP(torch.autograd.Function):
             if need_dx_last:
                 dh = torch.empty_like(h_last)
                 counters.add()
-                C.linear_dgrad(dy16, wl.detach().t().contiguous().to(torch.bfloat16), h_last if L > 1 else None, dh, st)
+                C.linear_dgrad(dy16, wl.detach().t().contiguous().to(torch.bfloat16), None, dh, st,
+                               ctx.masks[-1] if L > 1 else None)
         # The chain dh_L -> dh_{L-1} -> ... is serial; each layer's weight and bias gradients only
         # need that layer's dh, so they run on a second stream beside the chain and are joined at
         # the end (in a CUDA-graph capture this becomes a parallel branch).
@@ -169,7 +209,7 @@ class _FusedMLP(torch.autograd.Function):
                     dprev[:, cols:].zero_()
                     C.linear_dgrad(dh, wt16[:cols], None, dprev[:, :cols], st)
                 else:
-                    C.linear_dgrad(dh, wt16, acts[i] if i > 0 else None, dprev, st)
+                    C.linear_dgrad(dh, wt16, None, dprev, st, ctx.masks[i])
                 dh = dprev
             else:
                 dh = None
@@ -178,17 +218,19 @@ class _FusedMLP(torch.autograd.Function):
         if ctx.x_needs_grad and dh is not None:
             dx = dh if ctx.x_dtype == torch.bfloat16 else dh.to(ctx.x_dtype)
         # parameter gradients were accumulated in place
-        return (dx, gout.reshape(-1) if ctx.needs_input_grad[1] else None, None, None) + (None,) * (2 * L)
+        return (dx, gout.reshape(-1) if ctx.needs_input_grad[1] else None, None, None, None) + (None,) * (2 * L)
 
 
 def fused_mlp(x: torch.Tensor, weights: List[torch.Tensor], biases: List[torch.Tensor],
-              input_grad_cols: int = 0, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+              input_grad_cols: int = 0, addend: Optional[torch.Tensor] = None,
+              prepared: Optional[PreparedWeights] = None) -> torch.Tensor:
     """x [M, K] (bf16 or fp32, CUDA) -> [M, out_features] fp32.  Parameter gradients are
     accumulated into ``param.grad`` in place by the backward kernels.  ``input_grad_cols``
     (a multiple of 8, 0 = all) limits the input gradient to the leading columns of x.
-    ``addend`` [M] (single-output heads) is added to the output inside the head kernel."""
+    ``addend`` [M] (single-output heads) is added to the output inside the head kernel.
+    ``prepared`` is the result of an earlier ``prepare_weights`` call on the same weights."""
     from ..utils.profiler import engine_region
     with engine_region("mlp_fwd"):
         if addend is not None and weights[-1].shape[0] != 1:
             raise ValueError("addend needs a single-output head")
-        return _FusedMLP.apply(x, addend, len(weights), int(input_grad_cols), *weights, *biases)
+        return _FusedMLP.apply(x, addend, len(weights), int(input_grad_cols), prepared, *weights, *biases)

@@ -196,9 +196,10 @@ class Ticket:
     """Identifies one pull so that the matching push can reuse its dedup result
     and the slots the owners resolved."""
 
-    __slots__ = ("channel", "serial", "n", "bag_offsets", "weights", "mean", "bag_mean")
+    __slots__ = ("channel", "serial", "n", "bag_offsets", "weights", "mean", "bag_mean", "slots")
 
-    def __init__(self, channel, serial, n, bag_offsets, weights, mean, bag_mean):
+    def __init__(self, channel, serial, n, bag_offsets, weights, mean, bag_mean, slots=None):
+        self.slots = slots  # in-place pulls: table slot of every unique entry (rows are the table's value slab)
         self.channel = channel
         self.serial = serial
         self.n = n
@@ -282,12 +283,19 @@ class SparseChannel:
         self.serial += 1
         return n
 
-    def pull_unique(self, ids: torch.Tensor, share_from: Optional["SparseChannel"] = None):
+    def pull_unique(self, ids: torch.Tensor, share_from: Optional["SparseChannel"] = None, in_place: bool = False):
         """Pull that stops before the expansion: returns (unique rows buffer [cap, dim],
         occurrence -> unique map [n], ticket).  The rows belong to the channel and are
-        overwritten by its next pull; a consumer kernel reads them through the map."""
+        overwritten by its next pull; a consumer kernel reads them through the map.
+
+        ``in_place`` (honoured on single-GPU jobs): no copy of the rows is made; the first result is
+        the table's value slab and ``ticket.slots[u]`` is the slab row of unique entry ``u``.  The
+        Worth it for small batches only: a consumer that visits every occurrence then reads
+        scattered table rows instead of a compact buffer that fits in L2."""
         ids = ids.reshape(-1)
         n = self._lookup_phase(ids, insert=True, share_from=share_from)
+        if in_place and self.world == 1:
+            return self.table.val, self.inv, Ticket(self, self.serial, n, None, None, False, None, self.slot_cache)
         C.pull_gather(self.arena.heap, self.lay, self.ctrl, self.table.host(), self.slot_cache)
         C.pull_wait(self.arena.heap, self.lay, self.ctrl, self.spin)
         self.launches += 2

@@ -236,16 +236,18 @@ class GpuEngine(Engine):
         ch.push(grads, self.lr_dev, ticket=ticket, ids=ids, bag_offsets=ticket.bag_offsets, weights=ticket.weights,
                 mean=ticket.mean, bag_mean=ticket.bag_mean)
 
-    def pull_sparse_unique(self, table_id: int, indices: torch.Tensor, share_with: Optional[int] = None):
+    def pull_sparse_unique(self, table_id: int, indices: torch.Tensor, share_with: Optional[int] = None,
+                           in_place: bool = False):
         """Pull for fused consumers: (unique rows buffer, occurrence -> unique map, ticket).
         ``share_with`` names a table whose channel has just pulled the same ids: its
-        dedup result is reused."""
+        dedup result is reused.  ``in_place``: on a single GPU return the table's value slab and
+        the slot of every unique entry (``ticket.slots``) instead of copying the rows."""
         self._table(table_id, "sparse")
         idx = self._prep_ids(indices)
         ch = self._channel(table_id, idx.numel())
         share = self.channels.get(share_with) if share_with is not None else None
         with self._region("pull"):
-            return ch.pull_unique(idx, share_from=share)
+            return ch.pull_unique(idx, share_from=share, in_place=in_place)
 
     def grad_accumulator(self, table_id: int) -> torch.Tensor:
         """Per-unique-id gradient buffer [cap, dim] of the table's channel (zero between steps)."""

@@ -50,3 +50,40 @@ class GraphedStep:
             s.copy_(t, non_blocking=True)
         self.graph.replay()
         return self.static_out
+
+    def launch(self, *inputs: torch.Tensor) -> "PendingScalar":
+        """Replays the step and starts copying its (scalar) result to pinned host memory without
+        waiting for it: the caller can enqueue the next step first and read this step's value
+        afterwards, so the device never idles on the host's round trip.
+
+            pending = None
+            for batch in loader:
+                h = step.launch(*batch)
+                if pending is not None:
+                    log(pending.item())
+                pending = h
+        """
+        out = self(*inputs)
+        if not hasattr(self, "_slots"):
+            self._slots = [PendingScalar(out) for _ in range(4)]
+            self._next = 0
+        slot = self._slots[self._next]
+        self._next = (self._next + 1) % len(self._slots)
+        slot.capture(out)
+        return slot
+
+
+class PendingScalar:
+    """A device scalar on its way to pinned host memory; ``item()`` waits for that copy only."""
+
+    def __init__(self, like: torch.Tensor) -> None:
+        self.host = torch.empty(like.shape, dtype=like.dtype).pin_memory()
+        self.event = torch.cuda.Event()
+
+    def capture(self, value: torch.Tensor) -> None:
+        self.host.copy_(value, non_blocking=True)
+        self.event.record()
+
+    def item(self) -> float:
+        self.event.synchronize()
+        return self.host.item()

@@ -95,6 +95,34 @@ def test_every_gemm_variant_agrees(variant, M, N, K):
     assert ok, info
 
 
+@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("M,N,K", [(40001, 400, 448), (300, 72, 64)])
+def test_relu_bit_mask_round_trip(variant, M, N, K):
+    """Forward leaves one bit per output (> 0); the input gradient masked by those bits equals the
+    one masked by the bf16 activations themselves."""
+    torch.manual_seed(3)
+    x, w, b = rnd(M, K), rnd(N, K, scale=0.1), torch.randn(N, device=DEV)
+    y = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+    mask = torch.zeros(((N + 15) // 16, (M + 63) // 64 * 64), device=DEV, dtype=torch.int16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K2 = 96
+    dy2, w2 = rnd(M, K2), rnd(K2, N, scale=0.1)     # a following layer N -> K2
+    dx_bits = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+    dx_acts = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+    C.gemm_set_tuning(variant, 0)
+    try:
+        C.linear_forward(x, w, b, True, y, status, mask)
+        C.linear_dgrad(dy2, w2.t().contiguous(), None, dx_bits, status, mask)
+        C.linear_dgrad(dy2, w2.t().contiguous(), y, dx_acts, status)
+    finally:
+        C.gemm_set_tuning(0, 0)
+    assert status.item() == 0
+    words = (mask[:, :M].t().to(torch.int32) & 0xFFFF)                # [M, chunks]
+    got = ((words.unsqueeze(-1) >> torch.arange(16, device=DEV)) & 1).reshape(M, -1)[:, :N].bool()
+    assert torch.equal(got, y.float() > 0)
+    assert torch.equal(dx_bits, dx_acts)
+
+
 def test_colsum_bf16():
     torch.manual_seed(3)
     dy = rnd(5000, 400)
