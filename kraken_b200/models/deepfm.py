@@ -13,7 +13,7 @@ occurrence's gradient straight into the buffers the push sends.
 """
 from __future__ import annotations
 
-from typing import Sequence
+from typing import Optional, Sequence
 
 import torch
 
