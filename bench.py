@@ -63,33 +63,42 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
     def mark(self):
-        """Start of the timed region: earlier samples are dropped unless nothing else arrives."""
-        self.before = len(self.rows)
+        """Start of the timed regions (device-timed, then end-to-end)."""
+        self.t0 = time.perf_counter()
 
     def stop(self):
+        """End of the timed regions.  Samples taken between mark() and now are reported; if the regions
+        were shorter than nvidia-smi's period, the samples nearest to them (warm-up steps just before, under
+        the same load) are used and ``window`` says so."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.12)  # at least one sample period inside / right after the region
+        t1 = time.perf_counter()
+        time.sleep(0.03)
         self.proc.terminate()
         time.sleep(0.05)
-        if len(self.rows) > getattr(self, "before", 0):
-            self.rows = self.rows[getattr(self, "before", 0):]
+        t0 = getattr(self, "t0", 0.0)
+        inside = [r for t, r in self.rows if t0 <= t <= t1 + 0.03]
+        window = "timed regions"
+        if not inside:
+            inside = [r for t, r in self.rows if t0 - 1.0 <= t <= t1 + 0.5]
+            window = "nearest samples (regions shorter than the sampling period)"
+        self.rows = inside
         sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
         mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for k, n in enumerate(names) if any(len(r) >= 6 and r[2 + k].lower() == "active" for r in self.rows)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 def run_ours(args):
@@ -111,6 +120,8 @@ def run_ours(args):
         args.no_graph = True
     kk.initialize("gpu", table_capacity=(1 << 26) // world, max_ids_per_call=n_ids, seed=0, exchange=args.exchange)
     dev = torch.device("cuda", torch.cuda.current_device())
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()  # nvidia-smi takes a second or two to start reporting: launch it ahead of the set-up
     torch.backends.cuda.matmul.allow_tf32 = True
     torch.backends.cudnn.allow_tf32 = True
 
@@ -165,8 +176,6 @@ def run_ours(args):
 
     # ---------------- device-timed region: inputs staged on the device beforehand
     staged = [tuple(t.to(dev, non_blocking=True) for t in b) for b in host]
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()  # nvidia-smi needs a moment to start reporting: launch it ahead of the warm-up
     for i in range(args.warmup):
         step(*staged[i])
     eng.check()
@@ -180,7 +189,6 @@ def run_ours(args):
     e1.record()
     sync_all()
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
-    clocks = sampler.stop()
     launches = eng.kernel_launches() - launches0
     if not args.no_graph:
         launches = launches_per_step * args.steps  # replayed from the graph: counted once at capture
@@ -209,6 +217,7 @@ def run_ours(args):
     e1.record()
     sync_all()
     e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 if world == 1 else 0.0))
+    clocks = sampler.stop()  # samples cover the device-timed and the end-to-end region
     eng.check()
 
     if rank == 0:

@@ -5,6 +5,8 @@ step, device time, max over ranks) and the time to save / load the table in the 
     torchrun --nproc-per-node N -m kraken_b200.benchmarks.pull_push [--rows-per-gpu 20000000]
 """
 import argparse
+import json
+import os
 import tempfile
 import time
 
@@ -14,6 +16,40 @@ import torch
 import kraken_b200.pytorch as kk
 from kraken_b200.benchmarks.common import DeviceTimer, emit, sync_all, world_rank
 from kraken_b200.models.synthetic import zipf_ids
+
+
+def measured_peaks():
+    """Copy bandwidth measured on this pool (GB/s) if the file is present beside the package, else the fallback."""
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, "fallback"
+
+
+def roofline(ex: dict, dim: int, pull_us: float, push_us: float, link_gbs: float = 770.0) -> dict:
+    """Lower bounds of one rank's pull and push from the bytes they must move: over NVLink (per direction,
+    at the measured 770 GB/s peer-copy rate) and through HBM (algorithmic bytes at the measured copy rate);
+    the bound is the slower of the two and the fraction is bound / measured time."""
+    hbm_gbs, which = measured_peaks()
+    n, u, row = ex["occurrences"], ex["unique"], dim * 4
+    # pull: read ids, write + read the occurrence map, gather owned rows (about u rows per rank: read + write),
+    # read the received rows once and write the expanded [n, dim] result
+    pull_hbm = n * 8 + 2 * n * 4 + 2 * u * row + u * row + n * row
+    # push: read [n, dim] gradients, red-add into u rows (read-modify-write), copy them to the inbox
+    # (read + write), then read them and read-modify-write value and accumulator rows
+    push_hbm = n * row + 2 * u * row + 2 * u * row + u * row + 4 * u * row
+    pull_link = max(ex["pull_bytes_in"], ex["pull_bytes_out"])
+    push_link = ex["push_bytes_out"]
+    out = {"unique_per_gpu": u, "unique_remote_per_gpu": ex["unique_remote"], "roofline_peaks": which}
+    for name, hbm, link, t in (("pull", pull_hbm, pull_link, pull_us), ("push", push_hbm, push_link, push_us)):
+        hbm_us, link_us = hbm / (hbm_gbs * 1e3), link / (link_gbs * 1e3)
+        bound = max(hbm_us, link_us)
+        out[f"{name}_hbm_bound_us"] = round(hbm_us, 1)
+        out[f"{name}_nvlink_bound_us"] = round(link_us, 1)
+        out[f"{name}_roofline_fraction"] = round(bound / t, 3) if t > 0 else None
+    return out
 
 
 def main():
@@ -27,8 +63,13 @@ def main():
     a = p.parse_args()
     world, rank = world_rank()
     n = a.global_batch // world * 26
-    out_dir = tempfile.mkdtemp(prefix="kraken_ckpt_")
-    kk.initialize("gpu", table_capacity=int(a.rows_per_gpu / 0.5), max_ids_per_call=max(n, 1 << 22), saved_dir=out_dir)
+    # one directory for all ranks: they share the launcher as parent process
+    out_dir = os.path.join(tempfile.gettempdir(), f"kraken_ckpt_{os.getppid()}_{os.environ.get('MASTER_PORT', '0')}")
+    os.makedirs(out_dir, exist_ok=True)
+    # room for the resident rows plus the rows the timed steps create (ids are drawn from a wide space, so
+    # most of every batch is new), at a load factor of 0.6
+    capacity = int((a.rows_per_gpu + (a.warmup + a.steps) * n * 0.8) / 0.6)
+    kk.initialize("gpu", table_capacity=capacity, max_ids_per_call=max(n, 1 << 22), saved_dir=out_dir)
     dev = torch.device("cuda", torch.cuda.current_device())
     eng = kk.native.engine()
     kk.init_model("stress", kk.OptimType.kAdagrad, {"initial_accumulator_value": "0.1"})
@@ -65,6 +106,7 @@ def main():
     eng.check()
     rec = {"benchmark": "pull_push", "n_gpus": world, "global_batch": a.global_batch, "ids_per_gpu": n, "dim": 64,
            "rows_per_shard": rows_local, "pull_us": pull_ms / a.steps * 1e3, "push_us": push_ms / a.steps * 1e3}
+    rec.update(roofline(eng.metrics()["big"]["last_exchange"], 64, rec["pull_us"], rec["push_us"]))
 
     if a.checkpoint_rows > 0:
         # checkpoint timing on a shard trimmed to checkpoint-rows rows (the file format costs ~580 B per row)
@@ -82,7 +124,7 @@ def main():
         sync_all()
         rec["save_s"] = time.perf_counter() - t0
         rec["checkpoint_rows_per_shard"] = k
-        kk.stop()
+        kk.stop(keep_process_group=True)
         kk.initialize("gpu", table_capacity=int(k / 0.5))
         t0 = time.perf_counter()
         assert kk.try_load_model_blocked(out_dir)

@@ -333,16 +333,32 @@ pull_gather_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* 
   const int lane = gtid % lpr;
   const int row0 = gtid / lpr;
   const int row_stride = (gridDim.x * blockDim.x) / lpr;
+  // Four rows per thread and iteration: the four slot lookups, then the four row loads, are all in
+  // flight before the first store, which is what it takes to keep HBM busy with 16-byte requests.
+  constexpr int kUnroll = 4;
   for (int k = 0; k < sym.world; ++k) {
     const int s = (sym.rank + k) % sym.world;
     const int2 m = __ldcg(&meta[s]);
     float* dst_base = sym.at<float>(s, lay.rows_recv) + static_cast<size_t>(m.y) * t.dim;
-    for (int r = row0; r < m.x; r += row_stride) {
-      const int slot = slot_cache[static_cast<size_t>(s) * lay.capS + r];
-      const float* src = t.val + static_cast<size_t>(slot < 0 ? 0 : slot) * t.dim;
-      float* dst = dst_base + static_cast<size_t>(r) * t.dim;
-      for (int c = lane; c < chunks; c += lpr)
-        V::st(dst + c * VEC, slot < 0 ? V::zero() : V::ld(src + c * VEC));
+    const int* slots = slot_cache + static_cast<size_t>(s) * lay.capS;
+    for (int r = row0; r < m.x; r += row_stride * kUnroll) {
+      int slot[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int ru = r + u * row_stride;
+        slot[u] = ru < m.x ? slots[ru] : -1;
+      }
+      for (int c = lane; c < chunks; c += lpr) {
+        typename V::T v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+          v[u] = slot[u] < 0 ? V::zero() : V::ld(t.val + static_cast<size_t>(slot[u]) * t.dim + c * VEC);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int ru = r + u * row_stride;
+          if (ru < m.x) V::st(dst_base + static_cast<size_t>(ru) * t.dim + c * VEC, v[u]);
+        }
+      }
     }
   }
   if (last_block_done(&ctrl->done[0])) {
@@ -369,10 +385,25 @@ pull_combine_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int* __restrict__
   const int row0 = gtid / lpr;
   const int row_stride = (gridDim.x * blockDim.x) / lpr;
   if (bag_offsets == nullptr) {
-    for (int i = row0; i < n; i += row_stride) {
-      const float* src = rows + static_cast<size_t>(inv[i]) * dim;
-      float* dst = out + static_cast<size_t>(i) * dim;
-      for (int c = lane; c < chunks; c += lpr) V::st(dst + c * VEC, V::ldcg(src + c * VEC));
+    constexpr int kUnroll = 4;  // four occurrences per thread in flight, as in the gather
+    for (int i = row0; i < n; i += row_stride * kUnroll) {
+      int u_of[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int iu = i + u * row_stride;
+        u_of[u] = iu < n ? inv[iu] : -1;
+      }
+      for (int c = lane; c < chunks; c += lpr) {
+        typename V::T v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+          v[u] = u_of[u] < 0 ? V::zero() : V::ldcg(rows + static_cast<size_t>(u_of[u]) * dim + c * VEC);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int iu = i + u * row_stride;
+          if (iu < n) V::st(out + static_cast<size_t>(iu) * dim + c * VEC, v[u]);
+        }
+      }
     }
   } else {
     for (int b = row0; b < nbags; b += row_stride) {
@@ -509,11 +540,15 @@ push_merge_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* _
   }
 }
 
-template <int VEC>
-__global__ void __launch_bounds__(kThreads)
+// OPT is the optimizer type as a compile-time constant: the update switch folds away, Adam's bias
+// terms exist only where they are used, and the kernel fits four blocks per SM.
+template <int VEC, int OPT>
+__global__ void __launch_bounds__(kThreads, 4)
 push_update_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache,
-                   OptimPOD optim, const float* __restrict__ lr_ptr, int chunks, int lpr) {
+                   OptimPOD optim_in, const float* __restrict__ lr_ptr, int chunks, int lpr) {
   using V = Vec<VEC>;
+  OptimPOD optim = optim_in;
+  optim.type = OPT;
   const uint32_t epoch = ctrl->push_epoch;
   const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
   const float* inbox = sym.at<float>(sym.rank, lay.inbox_grad);
@@ -647,6 +682,19 @@ void push_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const 
     push_dispatch_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, ugrad, off, dim, g.chunks, g.lpr);
 }
 
+namespace {
+template <int VEC>
+void launch_update(int grid, cudaStream_t stream, const Sym& s, const ChanLayout& lay, Ctrl* ctrl, const TableView& t,
+                   const int* slot_cache, const OptimPOD& optim, const float* lr, int chunks, int lpr) {
+  switch (optim.type) {
+    case 0: push_update_kernel<VEC, 0><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+    case 1: push_update_kernel<VEC, 1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+    case 2: push_update_kernel<VEC, 2><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+    default: push_update_kernel<VEC, 3><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+  }
+}
+}  // namespace
+
 void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache, OptimPOD optim,
                 const float* lr, uint32_t spin_limit, cudaStream_t stream) {
   const RowGeom g = row_geom(table.dim);
@@ -656,11 +704,11 @@ void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const 
   if (g.vec == 4) {
     if (sym.world > 1)
       push_merge_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr, spin_limit);
-    push_update_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
+    launch_update<4>(grid, stream, s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
   } else {
     if (sym.world > 1)
       push_merge_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr, spin_limit);
-    push_update_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
+    launch_update<1>(grid, stream, s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
   }
 }
 

@@ -281,7 +281,21 @@ class SparseChannel:
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)
         self.launches += 3 if insert else 2
         self.serial += 1
+        self.last_n = n
         return n
+
+    def last_exchange(self) -> dict:
+        """Counters of the latest lookup (synchronises): occurrences, unique ids, how many of them
+        other ranks own, and the bytes that crossed NVLink for them in each phase, per direction
+        (ids out and rows in for a pull, gradient rows out for a push)."""
+        n = getattr(self, "last_n", 0)
+        off = self.off.cpu().tolist()
+        unique = int(off[self.world])
+        own = int(off[self.rank + 1] - off[self.rank])
+        remote = unique - own
+        row_bytes = self.table.dim * 4
+        return {"occurrences": n, "unique": unique, "unique_ratio": unique / n if n else 0.0, "unique_remote": remote,
+                "pull_bytes_out": remote * 8, "pull_bytes_in": remote * row_bytes, "push_bytes_out": remote * row_bytes}
 
     def pull_unique(self, ids: torch.Tensor, share_from: Optional["SparseChannel"] = None, in_place: bool = False):
         """Pull that stops before the expansion: returns (unique rows buffer [cap, dim],
@@ -289,7 +303,7 @@ class SparseChannel:
         overwritten by its next pull; a consumer kernel reads them through the map.
 
         ``in_place`` (honoured on single-GPU jobs): no copy of the rows is made; the first result is
-        the table's value slab and ``ticket.slots[u]`` is the slab row of unique entry ``u``.  The
+        the table's value slab and ``ticket.slots[u]`` is the slab row of unique entry ``u``.
         Worth it for small batches only: a consumer that visits every occurrence then reads
         scattered table rows instead of a compact buffer that fits in L2."""
         ids = ids.reshape(-1)

@@ -101,13 +101,16 @@ def initialize(s_addr: str = "auto", emitter_type=EmitterType.kDefault, life_spa
         _engine = CpuEngine(cfg, rank, world)
 
 
-def stop() -> None:
+def stop(keep_process_group: bool = False) -> None:
+    """Shuts the engine down.  ``keep_process_group``: leave a torch.distributed group that
+    ``initialize`` created in place, so that a later ``initialize`` in the same process reuses it
+    (a second NCCL rendezvous on the launcher's store is not possible once rank 0 has left it)."""
     global _engine, _owns_process_group
     if _engine is None:
         return
     _engine.stop()
     _engine = None
-    if _owns_process_group and dist.is_initialized():
+    if _owns_process_group and dist.is_initialized() and not keep_process_group:
         dist.destroy_process_group()
         _owns_process_group = False
 

@@ -148,11 +148,16 @@ class GpuEngine(Engine):
         return self.profiler.region(name) if self.profiler is not None else contextlib.nullcontext()
 
     def metrics(self) -> dict:
-        """Counters of the shards (synchronises): rows and load factor per sparse table."""
+        """Counters of the shards (synchronises): rows and load factor per sparse table and, where
+        a table has been used, its latest exchange (occurrences, unique ids, bytes over NVLink)."""
         out = {}
         for tid, t in self.sparse.items():
             rows = t.num_rows()
-            out[self.tables[tid].name] = {"rows": rows, "capacity": t.capacity, "load_factor": rows / t.capacity}
+            rec = {"rows": rows, "capacity": t.capacity, "load_factor": rows / t.capacity}
+            ch = self.channels.get(tid)
+            if ch is not None and hasattr(ch, "last_exchange"):
+                rec["last_exchange"] = ch.last_exchange()
+            out[self.tables[tid].name] = rec
         return out
 
     def _flush_dense(self) -> None:
