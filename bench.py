@@ -44,6 +44,8 @@ def parse():
     p.add_argument("--two-tables", action="store_true",
                    help="keep first-order weights in a separate dim-1 table instead of column 16 of the embedding rows")
     p.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    p.add_argument("--no-overlap", action="store_true",
+                   help="join the MLP backward's side stream before the sparse backward instead of after the dense step (ablation)")
     p.add_argument("--in-place", action="store_true",
                    help="single GPU: read table rows in place instead of gathering the unique rows (ablation)")
     p.add_argument("--gemm-variant", type=int, default=0,
@@ -118,7 +120,8 @@ def run_ours(args):
     n_ids = local_batch * NUM_FIELDS
     if args.exchange == "nccl":
         args.no_graph = True
-    kk.initialize("gpu", table_capacity=(1 << 26) // world, max_ids_per_call=n_ids, seed=0, exchange=args.exchange)
+    kk.initialize("gpu", table_capacity=(1 << 26) // world, max_ids_per_call=n_ids, seed=0, exchange=args.exchange,
+                  overlap_dense_step=not args.no_overlap)
     dev = torch.device("cuda", torch.cuda.current_device())
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()  # nvidia-smi takes a second or two to start reporting: launch it ahead of the set-up

@@ -19,6 +19,30 @@ from . import counters
 
 _status = {}
 _side_streams = {}
+_deferred_join = False
+_pending_join = set()
+
+
+def set_deferred_join(on: bool) -> None:
+    """With deferred join the backward pass leaves its side stream (weight and bias gradients)
+    un-joined, and whoever consumes those gradients next - the engine's fused dense step - runs on
+    that stream and joins it afterwards.  The sparse backward and push that follow the MLP in a
+    recommender's backward pass then run beside the last weight gradients and the dense step
+    instead of behind them.  Only safe when nothing reads ``param.grad`` of the MLP on the main
+    stream before the dense step, which is why the engine option that turns it on is off by default."""
+    global _deferred_join
+    _deferred_join = bool(on)
+    if not on:
+        _pending_join.clear()
+
+
+def take_pending_side_stream(device: torch.device) -> Optional[torch.cuda.Stream]:
+    """The side stream with un-joined gradient work on ``device`` (and marks it as taken), or None."""
+    key = (device.type, device.index)
+    if key in _pending_join:
+        _pending_join.discard(key)
+        return _side_streams.get(key)
+    return None
 
 
 def _side_stream(device: torch.device) -> torch.cuda.Stream:
@@ -213,7 +237,10 @@ class _FusedMLP(torch.autograd.Function):
                 dh = dprev
             else:
                 dh = None
-        main.wait_stream(side)
+        if _deferred_join:
+            _pending_join.add((dev.type, dev.index))
+        else:
+            main.wait_stream(side)
         dx = None
         if ctx.x_needs_grad and dh is not None:
             dx = dh if ctx.x_dtype == torch.bfloat16 else dh.to(ctx.x_dtype)

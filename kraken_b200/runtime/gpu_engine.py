@@ -43,6 +43,8 @@ class GpuEngine(Engine):
         self.profiler = _profiler.from_env(rank)
         self.nccl = cfg.exchange == "nccl" and world > 1
         self.nccl_channels: Dict[int, NcclSparseChannel] = {}
+        from ..ops import mlp as fused_mlp
+        fused_mlp.set_deferred_join(bool(cfg.overlap_dense_step) and not self.nccl)
 
     # ------------------------------------------------------------------ registry hooks
     def _on_update_lr(self) -> None:
@@ -139,7 +141,15 @@ class GpuEngine(Engine):
         with self._region("dense_step"):
             if self.nccl:
                 dist.all_reduce(b.grad, group=self.group)
-            b.step(self.lr_dev)
+            from ..ops import mlp as fused_mlp
+            side = fused_mlp.take_pending_side_stream(self.device) if not self.nccl else None
+            if side is not None:
+                # the MLP backward left its weight gradients on this stream: step there, then join
+                with torch.cuda.stream(side):
+                    b.step(self.lr_dev)
+                torch.cuda.current_stream(self.device).wait_stream(side)
+            else:
+                b.step(self.lr_dev)
         self._dense_pending = False
         self._pushed.clear()
 
@@ -339,4 +349,6 @@ class GpuEngine(Engine):
             self.bucket.close()
         self.channels.clear()
         self.bucket = None
+        from ..ops import mlp as fused_mlp
+        fused_mlp.set_deferred_join(False)
         super().stop()

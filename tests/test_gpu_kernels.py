@@ -257,8 +257,8 @@ def test_fused_deepfm_matches_unfused_path():
     from kraken_b200.models import ClickDataset, DeepFM
     from kraken_b200.ops import bce_with_logits
 
-    def run(fused, fold=False):
-        kk.initialize("gpu", seed=21, table_capacity=1 << 14)
+    def run(fused, fold=False, overlap=False):
+        kk.initialize("gpu", seed=21, table_capacity=1 << 14, overlap_dense_step=overlap)
         torch.manual_seed(0)
         model = DeepFM(num_fields=6, num_dense=13, dim=16, hidden=(64, 32), init_std=0.1, fused=fused,
                        fold_first_order=fold).to(DEV)
@@ -292,6 +292,11 @@ def test_fused_deepfm_matches_unfused_path():
     l2, r2, f2, w2 = run(False, fold=True)
     assert all(abs(a - b) < 5e-3 for a, b in zip(l3, l2)), (l3, l2)
     assert (r3 - r2).abs().max().item() < 2e-2 and (f3 - f2).abs().max().item() < 2e-2
+    # dense step on the backward's side stream (beside the sparse push): same kernels, same numbers
+    l4, r4, f4, w4 = run(True, fold=True, overlap=True)
+    # (split-K weight gradients are summed by atomics, so the low bits are not reproducible)
+    assert all(abs(a - b) < 1e-5 for a, b in zip(l4, l3)) and (w4 - w3).abs().max().item() < 1e-5
+    assert (r4 - r3).abs().max().item() < 1e-5
 
 
 @pytest.mark.gpu
