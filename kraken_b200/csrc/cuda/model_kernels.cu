@@ -192,6 +192,68 @@ rowdot_backward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float
   }
 }
 
+// Same contract, for K % 8 == 0 and 16-byte aligned rows: a thread owns 8 columns (one 16-byte
+// load and store per row), the block's threads are split into row lanes, and every thread keeps
+// two rows in flight, so the kernel streams x and dx at memory speed instead of waiting on one
+// 4-byte load at a time.
+__global__ void __launch_bounds__(kThreads)
+rowdot_backward_wide_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ w,
+                            const float* __restrict__ dy, int M, int K, int rows_per_block, int relu_mask,
+                            __nv_bfloat16* __restrict__ dx, int lddx, float* dw, float* db) {
+  extern __shared__ float s_dw[];  // [K] partial sums of this block
+  const int groups = K / 8;                       // 16-byte column groups per row
+  const int lanes = blockDim.x / groups;          // row lanes (>= 1: the launcher guarantees groups <= blockDim.x)
+  const int cg = threadIdx.x % groups;
+  const int rl = threadIdx.x / groups;
+  const int r0 = blockIdx.x * rows_per_block;
+  const int r1 = min(M, r0 + rows_per_block);
+  for (int k = threadIdx.x; k < K; k += blockDim.x) s_dw[k] = 0.f;
+  __syncthreads();
+  if (rl < lanes) {
+    float wk[8], acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wk[j] = w[cg * 8 + j], acc[j] = 0.f;
+    for (int m = r0 + rl; m < r1; m += 2 * lanes) {
+      const int m2 = m + lanes;
+      const bool two = m2 < r1;
+      const uint4 va = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * ldx + cg * 8);
+      const uint4 vb = two ? *reinterpret_cast<const uint4*>(x + static_cast<size_t>(m2) * ldx + cg * 8) : va;
+      const float ga = dy[m], gb = two ? dy[m2] : 0.f;
+      const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+      uint32_t oa[4], ob[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 pa = *reinterpret_cast<const __nv_bfloat162*>(&wa[j]);
+        const __nv_bfloat162 pb = *reinterpret_cast<const __nv_bfloat162*>(&wb[j]);
+        const float a0 = __bfloat162float(pa.x), a1 = __bfloat162float(pa.y);
+        const float b0 = __bfloat162float(pb.x), b1 = __bfloat162float(pb.y);
+        acc[2 * j] += ga * a0 + gb * b0;
+        acc[2 * j + 1] += ga * a1 + gb * b1;
+        const __nv_bfloat162 da = __floats2bfloat162_rn((!relu_mask || a0 > 0.f) ? ga * wk[2 * j] : 0.f,
+                                                        (!relu_mask || a1 > 0.f) ? ga * wk[2 * j + 1] : 0.f);
+        const __nv_bfloat162 dbv = __floats2bfloat162_rn((!relu_mask || b0 > 0.f) ? gb * wk[2 * j] : 0.f,
+                                                         (!relu_mask || b1 > 0.f) ? gb * wk[2 * j + 1] : 0.f);
+        oa[j] = *reinterpret_cast<const uint32_t*>(&da);
+        ob[j] = *reinterpret_cast<const uint32_t*>(&dbv);
+      }
+      if (dx) {
+        *reinterpret_cast<uint4*>(dx + static_cast<size_t>(m) * lddx + cg * 8) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+        if (two)
+          *reinterpret_cast<uint4*>(dx + static_cast<size_t>(m2) * lddx + cg * 8) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&s_dw[cg * 8 + j], acc[j]);
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < K; k += blockDim.x) atomicAdd(dw + k, s_dw[k]);
+  if (db && threadIdx.x == 0) {
+    float sum = 0.f;
+    for (int m = r0; m < r1; ++m) sum += dy[m];
+    atomicAdd(db, sum);
+  }
+}
+
 // fp32 weight [N, K] -> bf16 copy [N, K] and bf16 transpose [K, N] in one pass (the forward and
 // the input-gradient GEMMs want the two layouts).
 __global__ void __launch_bounds__(256)
@@ -266,6 +328,13 @@ void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const floa
   int rows_per_block = (M + blocks - 1) / blocks;
   if (rows_per_block < 16) rows_per_block = 16;
   blocks = (M + rows_per_block - 1) / rows_per_block;
+  const bool wide = K % 8 == 0 && K / 8 <= kThreads && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                    (dx == nullptr || (lddx % 8 == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0));
+  if (wide) {
+    rowdot_backward_wide_kernel<<<blocks, kThreads, K * sizeof(float), stream>>>(x, ldx, w, dy, M, K, rows_per_block,
+                                                                                 relu_mask ? 1 : 0, dx, lddx, dw, db);
+    return;
+  }
   rowdot_backward_kernel<<<blocks, kThreads, 0, stream>>>(x, ldx, w, dy, M, K, rows_per_block, relu_mask ? 1 : 0, dx,
                                                           lddx, dw, db);
 }

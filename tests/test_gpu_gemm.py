@@ -239,3 +239,25 @@ def test_fused_mlp_with_odd_width_head():
     dh2 = r((g @ ws[2]) * (h2 > 0))
     ok, info = close(mlp.layers[1].weight.grad, dh2.t() @ h1, tol=2e-2)
     assert ok, info
+
+
+@pytest.mark.parametrize("M,K", [(5000, 400), (8192, 32), (300, 20), (65536, 400)])
+@pytest.mark.parametrize("relu", [False, True])
+def test_rowdot_backward(M, K, relu):
+    """Head layer (K -> 1) backward: wide (16-byte) kernel for K % 8 == 0, narrow kernel otherwise."""
+    torch.manual_seed(4)
+    x = rnd(M, K)
+    w = torch.randn(K, device=DEV) * 0.1
+    dy = torch.randn(M, device=DEV) * 0.01
+    dx = torch.empty_like(x)
+    dw = torch.zeros(K, device=DEV)
+    db = torch.zeros(1, device=DEV)
+    C.rowdot_backward(x, w, dy, relu, dx, dw, db)
+    want_dx = dy[:, None] * w[None, :]
+    if relu:
+        want_dx = want_dx * (x.float() > 0)
+    ok, info = close(dx, want_dx)
+    assert ok, info
+    want_dw = dy @ x.float()
+    assert (dw - want_dw).abs().max().item() <= 1e-3 * (want_dw.abs().max().item() + 1e-6) + 1e-5
+    assert abs(db.item() - dy.sum().item()) < 1e-3
