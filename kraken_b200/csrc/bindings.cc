@@ -786,7 +786,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                               const torch::Tensor& hpos, const torch::Tensor& hwin, const torch::Tensor& slot_of,
                               uint32_t hbits, const torch::Tensor& cnt, const torch::Tensor& off,
                               const torch::Tensor& uniq, const torch::Tensor& inv, const torch::Tensor& status,
-                              int cap_u) {
+                              int cap_u, const SymHeap* heap, const cu::ChanLayout* lay,
+                              const c10::optional<torch::Tensor>& ctrl) {
     need_cuda(ids, "ids", torch::kInt64);
     need_cuda(hkeys, "hkeys", torch::kInt64);
     const int n = static_cast<int>(ids.numel());
@@ -796,12 +797,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     TORCH_CHECK(cnt.numel() >= world && off.numel() >= world + 1, "cnt/off too small");
     c10::cuda::CUDAGuard guard(ids.device());
     cu::DedupScratch sc{hkeys.data_ptr(), ptr<int>(hpos), ptr<int>(hwin), ptr<int>(slot_of), hbits};
-    cu::dedup_bucketize(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),
-                        ptr<int>(inv), cap_u, ptr<int>(status), cur_stream());
+    if (heap != nullptr && lay != nullptr && ctrl.has_value()) {
+      // with a channel: the dedup's second kernel also dispatches the unique ids to their owners
+      cu::dedup_bucketize_dispatch(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off),
+                                   ptr<int64_t>(uniq), ptr<int>(inv), cap_u, ptr<int>(status), heap->View(), *lay,
+                                   reinterpret_cast<cu::Ctrl*>(ctrl->data_ptr()), cur_stream());
+    } else {
+      cu::dedup_bucketize(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),
+                          ptr<int>(inv), cap_u, ptr<int>(status), cur_stream());
+    }
     check_launch("dedup_bucketize");
   }, py::arg("ids"), py::arg("world"), py::arg("salt"), py::arg("hkeys"), py::arg("hpos"), py::arg("hwin"),
      py::arg("slot_of"), py::arg("hbits"), py::arg("cnt"), py::arg("off"), py::arg("uniq"), py::arg("inv"),
-     py::arg("status"), py::arg("cap_u") = 0);
+     py::arg("status"), py::arg("cap_u") = 0, py::arg("heap") = nullptr, py::arg("layout") = nullptr,
+     py::arg("ctrl") = py::none());
   m.def("pull_dispatch", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
                             const torch::Tensor& uniq, const torch::Tensor& off, int max_n) {
     cu::pull_dispatch(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), ptr<int64_t>(uniq), ptr<int>(off),
@@ -924,6 +933,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         },
         py::arg("rows2"), py::arg("inv2"), py::arg("inv1"), py::arg("dx"), py::arg("dlogit"), py::arg("B"), py::arg("F"),
         py::arg("D"), py::arg("ugrad2"), py::arg("ugrad1"), py::arg("slots2") = py::none());
+
+  m.def("owner_of_cuda", [](const torch::Tensor& ids, uint64_t salt, int world) {
+    need_cuda(ids, "ids", torch::kInt64);
+    torch::Tensor out = torch::empty({ids.numel()}, ids.options().dtype(torch::kInt32));
+    cu::owner_of(ptr<int64_t>(ids), static_cast<int>(ids.numel()), salt, world, ptr<int>(out), cur_stream());
+    check_launch("owner_of");
+    return out;
+  });
 
   // ---------------- table maintenance
   m.def("table_clear", [](const cu::TableHost& t) {

@@ -77,6 +77,11 @@ struct DedupScratch {
 // kInboxOverflow and clamps its outputs into range.
 void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
                      int64_t* uniq, int* inv, int cap_u, int* status, cudaStream_t stream);
+// The same, with the pull's id dispatch (pull_dispatch below) done by the second kernel of the dedup:
+// unique ids go straight into their owners' inboxes and the channel's pull epoch advances.
+void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
+                              int64_t* uniq, int* inv, int cap_u, int* status, SymHost sym, ChanLayout lay, Ctrl* ctrl,
+                              cudaStream_t stream);
 
 // ---- sparse pull ----
 void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,

@@ -183,10 +183,16 @@ dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t 
   }
 }
 
+// DISPATCH: the pull's id dispatch is done here as well - every unique id goes straight into its
+// owner's inbox (a peer store for other ranks), block 0 writes the per-owner counts, and the last
+// block to finish raises the request flags and advances the channel's pull epoch - so a lookup needs
+// no separate dispatch launch.
+template <bool DISPATCH>
 __global__ void __launch_bounds__(kThreads)
 dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, unsigned long long* hkeys,
                       const int* __restrict__ hpos, const int* __restrict__ hwin, const int* __restrict__ slot_of,
-                      const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv, int cap_u, int* status) {
+                      const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv, int cap_u, int* status,
+                      Sym sym, ChanLayout lay, Ctrl* ctrl) {
   __shared__ int s_off[kMaxWorld + 1];
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -200,19 +206,44 @@ dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_
       // later kernel indexes past a buffer (the step's result is then invalid, not its memory)
       if (acc > cap_u) set_status(status, err::kInboxOverflow);
       for (int o = 0; o <= world; ++o) off[o] = min(s_off[o], cap_u);
+      if (DISPATCH && acc > lay.capU) set_status(&ctrl->status, err::kInboxOverflow);
     }
   }
   __syncthreads();
+  if (DISPATCH && blockIdx.x == 0 && threadIdx.x < world) {
+    const int o = threadIdx.x;
+    const int lo = min(s_off[o], cap_u), hi = min(s_off[o + 1], cap_u);
+    sym.at<int2>(o, lay.inbox_meta)[sym.rank] = make_int2(min(hi - lo, lay.capS), lo);
+  }
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  uint64_t id = static_cast<uint64_t>(ids[i]);
-  if (id == kEmptyKey) id = kEmptyKey - 1;
-  const int slot = slot_of[i];
-  const int u = s_off[OwnerOf(salt, id, world)] + hpos[slot];
-  inv[i] = u < cap_u ? u : 0;
-  if (hwin[slot] == i) {
-    if (u < cap_u) uniq[u] = static_cast<int64_t>(id);
-    hkeys[slot] = kEmptyKey;  // leave the set empty for the next call
+  if (i < n) {
+    uint64_t id = static_cast<uint64_t>(ids[i]);
+    if (id == kEmptyKey) id = kEmptyKey - 1;
+    const int slot = slot_of[i];
+    const int o = static_cast<int>(OwnerOf(salt, id, world));
+    const int j = hpos[slot];  // position among the ids of owner o
+    const int u = s_off[o] + j;
+    inv[i] = u < cap_u ? u : 0;
+    if (hwin[slot] == i) {
+      if (u < cap_u) {
+        uniq[u] = static_cast<int64_t>(id);
+        if (DISPATCH) {
+          if (j < lay.capS)
+            sym.at<unsigned long long>(o, lay.inbox_ids)[static_cast<size_t>(sym.rank) * lay.capS + j] = id;
+          else
+            set_status(&ctrl->status, err::kInboxOverflow);
+        }
+      }
+      hkeys[slot] = kEmptyKey;  // leave the set empty for the next call
+    }
+  }
+  if (DISPATCH) {
+    if (last_block_done(&ctrl->done[0])) {
+      const uint32_t e = ctrl->pull_epoch + 1;
+      __syncthreads();
+      if (threadIdx.x < world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_req) + sym.rank, e);
+      if (threadIdx.x == 0) ctrl->pull_epoch = e;
+    }
   }
 }
 
@@ -607,9 +638,26 @@ void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupS
   }
   dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys),
                                                        sc.hbits, sc.hpos, sc.hwin, sc.slot_of, cnt, status);
-  dedup_finalize_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt,
-                                                         static_cast<unsigned long long*>(sc.hkeys), sc.hpos, sc.hwin,
-                                                         sc.slot_of, cnt, off, uniq, inv, cap_u, status);
+  dedup_finalize_kernel<false><<<blocks, kThreads, 0, stream>>>(
+      ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys), sc.hpos, sc.hwin, sc.slot_of, cnt, off, uniq, inv,
+      cap_u, status, Sym{}, ChanLayout{}, nullptr);
+}
+
+void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
+                              int64_t* uniq, int* inv, int cap_u, int* status, SymHost sym, ChanLayout lay, Ctrl* ctrl,
+                              cudaStream_t stream) {
+  if (n <= 0) {  // nothing to deduplicate: the plain dispatch still has to publish empty counts and the epoch
+    dedup_bucketize(ids, n, world, salt, sc, cnt, off, uniq, inv, cap_u, status, stream);
+    pull_dispatch_kernel<<<1, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, uniq, off);
+    return;
+  }
+  const int blocks = (n + kThreads - 1) / kThreads;
+  cudaMemsetAsync(cnt, 0, sizeof(int) * world, stream);
+  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys),
+                                                       sc.hbits, sc.hpos, sc.hwin, sc.slot_of, cnt, status);
+  dedup_finalize_kernel<true><<<blocks, kThreads, 0, stream>>>(
+      ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys), sc.hpos, sc.hwin, sc.slot_of, cnt, off, uniq, inv,
+      cap_u, status, to_sym(sym), lay, ctrl);
 }
 
 void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,

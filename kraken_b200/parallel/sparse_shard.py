@@ -272,14 +272,16 @@ class SparseChannel:
         h, lay, ctrl, tbl = self.arena.heap, self.lay, self.ctrl, self.table.host()
         if share_from is not None and share_from.salt == self.salt and share_from.world == self.world:
             self.off, self.uniq, self.inv = share_from.off, share_from.uniq, share_from.inv
+            C.pull_dispatch(h, lay, ctrl, self.uniq, self.off, n)
+            self.launches += 1
         else:
+            # the dedup's second kernel also sends the unique ids to their owners' inboxes
             self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
             C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.hpos, self.hwin, self.slot_of, self.hbits,
-                              self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5], self.cap_u)
-            self.launches += 2 if n > 0 else 0
-        C.pull_dispatch(h, lay, ctrl, self.uniq, self.off, n)
+                              self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5], self.cap_u, h, lay, ctrl)
+            self.launches += 2
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)
-        self.launches += 3 if insert else 2
+        self.launches += 2 if insert else 1
         self.serial += 1
         self.last_n = n
         return n
