@@ -26,11 +26,19 @@ import torch
 
 class GraphedStep:
     def __init__(self, fn: Callable, example_inputs: Sequence[torch.Tensor], warmup: int = 3,
-                 device: torch.device | None = None) -> None:
+                 device: torch.device | None = None, slots: int = 1) -> None:
+        """slots > 1 captures the step once per set of static input buffers (the graphs share one
+        memory pool, they never run at the same time).  An input pipeline can then fill the buffers
+        of slot k + 1 while slot k is being replayed (``static_inputs`` / ``replay`` /
+        ``launch_slot``), so no device-to-device copy of the inputs is needed."""
         self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.static_in = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in example_inputs]
-        for s, t in zip(self.static_in, example_inputs):
-            s.copy_(t)
+        self.slots = max(1, int(slots))
+        self.static_ins = [[torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in example_inputs]
+                           for _ in range(self.slots)]
+        for bufs in self.static_ins:
+            for s, t in zip(bufs, example_inputs):
+                s.copy_(t)
+        self.static_in = self.static_ins[0]
         # eager warm-up on a side stream: creates channels / buckets and fills the allocator pool
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
@@ -39,17 +47,43 @@ class GraphedStep:
                 fn(*self.static_in)
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            out = fn(*self.static_in)
-        self.static_out = out
-        torch.cuda.synchronize(self.device)
+        self.graphs, self.static_outs = [], []
+        for k in range(self.slots):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self.graphs[0].pool() if self.graphs else None):
+                out = fn(*self.static_ins[k])
+            self.graphs.append(g)
+            self.static_outs.append(out)
+            torch.cuda.synchronize(self.device)
+        self.graph, self.static_out = self.graphs[0], self.static_outs[0]
 
     def __call__(self, *inputs: torch.Tensor):
         for s, t in zip(self.static_in, inputs):
             s.copy_(t, non_blocking=True)
         self.graph.replay()
         return self.static_out
+
+    def static_inputs(self, slot: int):
+        """The input buffers that the graph of ``slot`` reads."""
+        return tuple(self.static_ins[slot])
+
+    def replay(self, slot: int = 0):
+        """Replays the graph of ``slot`` on whatever its input buffers hold now."""
+        self.graphs[slot].replay()
+        return self.static_outs[slot]
+
+    def launch_slot(self, slot: int) -> "PendingScalar":
+        """``replay(slot)`` plus the start of the (scalar) result's copy to pinned host memory."""
+        return self._pending(self.replay(slot))
+
+    def _pending(self, out: torch.Tensor) -> "PendingScalar":
+        if not hasattr(self, "_slots"):
+            self._slots = [PendingScalar(out) for _ in range(4)]
+            self._next = 0
+        slot = self._slots[self._next]
+        self._next = (self._next + 1) % len(self._slots)
+        slot.capture(out)
+        return slot
 
     def launch(self, *inputs: torch.Tensor) -> "PendingScalar":
         """Replays the step and starts copying its (scalar) result to pinned host memory without
@@ -63,14 +97,7 @@ class GraphedStep:
                     log(pending.item())
                 pending = h
         """
-        out = self(*inputs)
-        if not hasattr(self, "_slots"):
-            self._slots = [PendingScalar(out) for _ in range(4)]
-            self._next = 0
-        slot = self._slots[self._next]
-        self._next = (self._next + 1) % len(self._slots)
-        slot.capture(out)
-        return slot
+        return self._pending(self(*inputs))
 
 
 class PendingScalar:
