@@ -28,7 +28,7 @@ def measured_peaks():
         return 6650.0, "fallback"
 
 
-def roofline(ex: dict, dim: int, pull_us: float, push_us: float, link_gbs: float = 770.0) -> dict:
+def roofline(ex: dict, dim: int, pull_us: float, push_us: float, created: float = 0.0, link_gbs: float = 770.0) -> dict:
     """Lower bounds of one rank's pull and push from the bytes they must move: over NVLink (per direction,
     at the measured 770 GB/s peer-copy rate) and through HBM (algorithmic bytes at the measured copy rate);
     the bound is the slower of the two and the fraction is bound / measured time."""
@@ -36,7 +36,8 @@ def roofline(ex: dict, dim: int, pull_us: float, push_us: float, link_gbs: float
     n, u, row = ex["occurrences"], ex["unique"], dim * 4
     # pull: read ids, write + read the occurrence map, gather owned rows (about u rows per rank: read + write),
     # read the received rows once and write the expanded [n, dim] result
-    pull_hbm = n * 8 + 2 * n * 4 + 2 * u * row + u * row + n * row
+    # (+ value and accumulator rows written for every row the pull creates)
+    pull_hbm = n * 8 + 2 * n * 4 + 2 * u * row + u * row + n * row + 2 * created * row
     # push: read [n, dim] gradients, red-add into u rows (read-modify-write), copy them to the inbox
     # (read + write), then read them and read-modify-write value and accumulator rows
     push_hbm = n * row + 2 * u * row + 2 * u * row + u * row + 4 * u * row
@@ -59,6 +60,9 @@ def main():
     p.add_argument("--global-batch", type=int, default=131072)
     p.add_argument("--rows-per-gpu", type=int, default=20_000_000, help="rows resident per shard before timing")
     p.add_argument("--id-space", type=int, default=1_000_000_000)
+    p.add_argument("--resident-ids", action="store_true",
+                   help="draw the ids from the rows populated before timing (steady state: no row is created in the "
+                        "timed steps) instead of from the whole id space (nearly every unique id is a new row)")
     p.add_argument("--checkpoint-rows", type=int, default=2_000_000, help="rows per shard in the save/load timing (0 = skip)")
     a = p.parse_args()
     world, rank = world_rank()
@@ -89,7 +93,16 @@ def main():
 
     rng = np.random.default_rng(5 + rank)
     total = a.warmup + a.steps
-    batches = [torch.from_numpy(zipf_ids(rng, n, a.id_space, 0.9)).to(dev) for _ in range(total)]
+    if a.resident_ids:
+        # rank r populated [r * S, r * S + filled): spread Zipf ranks over those slices
+        S = a.id_space // world
+        batches = []
+        for _ in range(total):
+            k = torch.from_numpy(zipf_ids(rng, n, world * filled, 0.9))
+            batches.append(((k % world) * S + k // world).to(dev))
+    else:
+        batches = [torch.from_numpy(zipf_ids(rng, n, a.id_space, 0.9)).to(dev) for _ in range(total)]
+    rows_before = None
     grads = torch.randn(n, 64, device=dev) * 0.01
     pull_t, push_t = DeviceTimer(), DeviceTimer()
     pull_ms = push_ms = 0.0
@@ -103,10 +116,15 @@ def main():
         if i >= a.warmup:
             pull_ms += ms_pull
             push_ms += ms_push
+        elif i == a.warmup - 1:
+            rows_before = eng.sparse[t].num_rows()
     eng.check()
+    created = (eng.sparse[t].num_rows() - (rows_before or rows_local)) / max(1, a.steps)
     rec = {"benchmark": "pull_push", "n_gpus": world, "global_batch": a.global_batch, "ids_per_gpu": n, "dim": 64,
            "rows_per_shard": rows_local, "pull_us": pull_ms / a.steps * 1e3, "push_us": push_ms / a.steps * 1e3}
-    rec.update(roofline(eng.metrics()["big"]["last_exchange"], 64, rec["pull_us"], rec["push_us"]))
+    rec["ids"] = "resident rows" if a.resident_ids else "whole id space"
+    rec["rows_created_per_step"] = round(created)
+    rec.update(roofline(eng.metrics()["big"]["last_exchange"], 64, rec["pull_us"], rec["push_us"], created))
 
     if a.checkpoint_rows > 0:
         # checkpoint timing on a shard trimmed to checkpoint-rows rows (the file format costs ~580 B per row)
