@@ -878,13 +878,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         [](const torch::Tensor& rows2, const torch::Tensor& inv2, const c10::optional<torch::Tensor>& rows1,
            const c10::optional<torch::Tensor>& inv1, const torch::Tensor& dense, int B, int F, int D,
            const torch::Tensor& x, const torch::Tensor& fm_logit, const c10::optional<torch::Tensor>& slots2,
-           const c10::optional<torch::Tensor>& slots1) {
+           const c10::optional<torch::Tensor>& slots1, const c10::optional<torch::Tensor>& ssum) {
           need_cuda(rows2, "rows2", torch::kFloat32);
           need_cuda(dense, "dense", torch::kFloat32);
           need_cuda(x, "x", torch::kBFloat16);
           need_cuda(fm_logit, "fm_logit", torch::kFloat32);
           const int RD = rows2.size(1), ND = dense.size(1), ldx = x.size(1);
           TORCH_CHECK(D % 4 == 0 && RD % 4 == 0 && RD >= D, "row widths must be multiples of 4");
+          TORCH_CHECK(((D / 4) & (D / 4 - 1)) == 0 && D <= 128, "D / 4 must be a power of two, D <= 128");
+          if (ssum.has_value()) {
+            need_cuda(*ssum, "ssum", torch::kFloat32);
+            TORCH_CHECK(ssum->numel() == static_cast<int64_t>(B) * D, "ssum must be [B, D]");
+          }
           if (rows1.has_value()) {
             need_cuda(*rows1, "rows1", torch::kFloat32);
             TORCH_CHECK(rows1->size(1) == 1 && inv1.has_value() && inv1->numel() >= static_cast<int64_t>(B) * F,
@@ -897,17 +902,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                       "deepfm_pack_forward: shape mismatch");
           cu::deepfm_pack_forward(ptr<float>(rows2), ptr<int>(inv2), optr<int>(slots2), optr<float>(rows1), optr<int>(inv1),
                                   optr<int>(slots1), ptr<float>(dense), B, F, D, RD, ND, reinterpret_cast<__nv_bfloat16*>(x.data_ptr()), ldx,
-                                  ptr<float>(fm_logit), cur_stream());
+                                  ptr<float>(fm_logit), optr<float>(ssum), cur_stream());
           check_launch("deepfm_pack_forward");
         },
         py::arg("rows2"), py::arg("inv2"), py::arg("rows1"), py::arg("inv1"), py::arg("dense"), py::arg("B"), py::arg("F"),
-        py::arg("D"), py::arg("x"), py::arg("fm_logit"), py::arg("slots2") = py::none(), py::arg("slots1") = py::none());
+        py::arg("D"), py::arg("x"), py::arg("fm_logit"), py::arg("slots2") = py::none(), py::arg("slots1") = py::none(),
+        py::arg("ssum") = py::none());
   m.def("deepfm_pack_backward",
         [](const torch::Tensor& rows2, const torch::Tensor& inv2, const c10::optional<torch::Tensor>& inv1,
            const c10::optional<torch::Tensor>& dx, const torch::Tensor& dlogit, int B, int F, int D,
            const torch::Tensor& ugrad2, const c10::optional<torch::Tensor>& ugrad1,
-           const c10::optional<torch::Tensor>& slots2) {
+           const c10::optional<torch::Tensor>& slots2, const torch::Tensor& ssum) {
           need_cuda(rows2, "rows2", torch::kFloat32);
+          need_cuda(ssum, "ssum", torch::kFloat32);
+          TORCH_CHECK(ssum.numel() == static_cast<int64_t>(B) * D && ((D / 4) & (D / 4 - 1)) == 0 && D <= 128,
+                      "ssum must be [B, D] with D / 4 a power of two");
           need_cuda(dlogit, "dlogit", torch::kFloat32);
           need_cuda(ugrad2, "ugrad2", torch::kFloat32);
           const int RD = rows2.size(1);
@@ -927,12 +936,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
             lddx = dx->size(1);
           }
           TORCH_CHECK(dlogit.numel() == B, "deepfm_pack_backward: shape mismatch");
-          cu::deepfm_pack_backward(ptr<float>(rows2), ptr<int>(inv2), optr<int>(slots2), optr<int>(inv1), dxp, lddx, ptr<float>(dlogit), B, F,
-                                   D, RD, ptr<float>(ugrad2), optr<float>(ugrad1), cur_stream());
+          cu::deepfm_pack_backward(ptr<float>(rows2), ptr<int>(inv2), optr<int>(slots2), optr<int>(inv1), dxp, lddx,
+                                   ptr<float>(dlogit), ptr<float>(ssum), B, F, D, RD, ptr<float>(ugrad2),
+                                   optr<float>(ugrad1), cur_stream());
           check_launch("deepfm_pack_backward");
         },
         py::arg("rows2"), py::arg("inv2"), py::arg("inv1"), py::arg("dx"), py::arg("dlogit"), py::arg("B"), py::arg("F"),
-        py::arg("D"), py::arg("ugrad2"), py::arg("ugrad1"), py::arg("slots2") = py::none());
+        py::arg("D"), py::arg("ugrad2"), py::arg("ugrad1"), py::arg("slots2"), py::arg("ssum"));
 
   m.def("owner_of_cuda", [](const torch::Tensor& ids, uint64_t salt, int world) {
     need_cuda(ids, "ids", torch::kInt64);

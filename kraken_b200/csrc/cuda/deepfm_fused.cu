@@ -43,39 +43,42 @@ __device__ __forceinline__ size_t row_of(const int* __restrict__ slots, int u) {
   return static_cast<size_t>(s < 0 ? 0 : s);
 }
 
-// lanes per sample = D / 4; lane l owns dims [4l, 4l + 4) of every field.
+// Lanes per sample = (D / 4) x G: lane (g, c) owns dims [4c, 4c + 4) of the fields g, g + G, ...
+// Splitting the fields over G lane groups (a power of two) multiplies the number of independent
+// row loads in flight; the per-sample sums are combined with shuffles and the forward pass leaves
+// S[b, :] = sum_f e_f for the backward pass, whose lanes then need nothing from each other.
 __global__ void __launch_bounds__(kThreads)
 deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restrict__ inv2,
                            const int* __restrict__ slots2, const float* __restrict__ rows1,
                            const int* __restrict__ inv1, const int* __restrict__ slots1,
-                           const float* __restrict__ dense, int B, int F, int D, int RD, int ND, int lpr,
-                           __nv_bfloat16* __restrict__ x, int ldx, float* __restrict__ fm_logit) {
+                           const float* __restrict__ dense, int B, int F, int D, int RD, int ND, int lpr, int G,
+                           __nv_bfloat16* __restrict__ x, int ldx, float* __restrict__ fm_logit,
+                           float* __restrict__ ssum) {
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
   const int stride = (gridDim.x * blockDim.x) / lpr;
   const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
   const int chunks = D / 4;
+  const int c = lane % chunks;   // chunks * G == lpr
+  const int fg = lane / chunks;
   const int rounds = (B + stride - 1) / stride;
   for (int it = 0; it < rounds; ++it) {
     const int b = gtid / lpr + it * stride;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = s;
     float part = 0.f;
     if (b < B) {
       const int* i2 = inv2 + static_cast<size_t>(b) * F;
       __nv_bfloat16* xr = x + static_cast<size_t>(b) * ldx;
-      for (int c = lane; c < chunks; c += lpr) {
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = s;
 #pragma unroll 4
-        for (int f = 0; f < F; ++f) {
-          const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, i2[f]) * RD) + c);
-          s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
-          q.x += e.x * e.x, q.y += e.y * e.y, q.z += e.z * e.z, q.w += e.w * e.w;
-          __nv_bfloat162 lo = __floats2bfloat162_rn(e.x, e.y), hi = __floats2bfloat162_rn(e.z, e.w);
-          uint2 packed;
-          packed.x = *reinterpret_cast<uint32_t*>(&lo);
-          packed.y = *reinterpret_cast<uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(xr + f * D + c * 4) = packed;
-        }
-        part += 0.5f * (s.x * s.x - q.x + s.y * s.y - q.y + s.z * s.z - q.z + s.w * s.w - q.w);
+      for (int f = fg; f < F; f += G) {
+        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, i2[f]) * RD) + c);
+        s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
+        q.x += e.x * e.x, q.y += e.y * e.y, q.z += e.z * e.z, q.w += e.w * e.w;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(e.x, e.y), hi = __floats2bfloat162_rn(e.z, e.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(xr + f * D + c * 4) = packed;
       }
       // first-order weights, dense features and the zero pad, spread over the sample's lanes
       if (rows1 != nullptr) {
@@ -89,6 +92,17 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
       for (int j = lane; base + j < ldx; j += lpr)
         xr[base + j] = __float2bfloat16(j < ND ? dense[static_cast<size_t>(b) * ND + j] : 0.f);
     }
+    // sums over the field groups of the same chunk (lanes c, c + chunks, c + 2 chunks, ...)
+    for (int o = chunks; o < lpr; o <<= 1) {
+      s.x += __shfl_xor_sync(group_mask, s.x, o), s.y += __shfl_xor_sync(group_mask, s.y, o);
+      s.z += __shfl_xor_sync(group_mask, s.z, o), s.w += __shfl_xor_sync(group_mask, s.w, o);
+      q.x += __shfl_xor_sync(group_mask, q.x, o), q.y += __shfl_xor_sync(group_mask, q.y, o);
+      q.z += __shfl_xor_sync(group_mask, q.z, o), q.w += __shfl_xor_sync(group_mask, q.w, o);
+    }
+    if (b < B && fg == 0) {
+      part += 0.5f * (s.x * s.x - q.x + s.y * s.y - q.y + s.z * s.z - q.z + s.w * s.w - q.w);
+      if (ssum != nullptr) *reinterpret_cast<float4*>(ssum + static_cast<size_t>(b) * D + c * 4) = s;
+    }
     for (int o = lpr >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(group_mask, part, o);
     if (b < B && lane == 0) fm_logit[b] = part;
   }
@@ -96,37 +110,34 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
 
 __global__ void __launch_bounds__(kThreads)
 deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restrict__ inv2,
-                            const int* __restrict__ slots2, const int* __restrict__ inv1, const __nv_bfloat16* __restrict__ dx, int lddx,
-                            const float* __restrict__ dlogit, int B, int F, int D, int RD, int lpr, float* ugrad2,
-                            float* ugrad1) {
+                            const int* __restrict__ slots2, const int* __restrict__ inv1,
+                            const __nv_bfloat16* __restrict__ dx, int lddx, const float* __restrict__ dlogit,
+                            const float* __restrict__ ssum, int B, int F, int D, int RD, int lpr, int G,
+                            float* ugrad2, float* ugrad1) {
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
   const int stride = (gridDim.x * blockDim.x) / lpr;
   const int chunks = D / 4;
+  const int c = lane % chunks;
+  const int fg = lane / chunks;
   for (int b = gtid / lpr; b < B; b += stride) {
     const int* i2 = inv2 + static_cast<size_t>(b) * F;
     const float g = dlogit[b];
     const __nv_bfloat16* dxr = dx ? dx + static_cast<size_t>(b) * lddx : nullptr;
-    for (int c = lane; c < chunks; c += lpr) {
-      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 s = *reinterpret_cast<const float4*>(ssum + static_cast<size_t>(b) * D + c * 4);
 #pragma unroll 4
-      for (int f = 0; f < F; ++f) {
-        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, i2[f]) * RD) + c);
-        s.x += e.x, s.y += e.y, s.z += e.z, s.w += e.w;
+    for (int f = fg; f < F; f += G) {
+      const int u = i2[f];
+      const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, u) * RD) + c);
+      float4 d = make_float4(g * (s.x - e.x), g * (s.y - e.y), g * (s.z - e.z), g * (s.w - e.w));
+      if (dxr) {
+        const uint2 p = *reinterpret_cast<const uint2*>(dxr + f * D + c * 4);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&p.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&p.y);
+        d.x += __bfloat162float(lo.x), d.y += __bfloat162float(lo.y);
+        d.z += __bfloat162float(hi.x), d.w += __bfloat162float(hi.y);
       }
-#pragma unroll 4
-      for (int f = 0; f < F; ++f) {
-        const float4 e = __ldcg(reinterpret_cast<const float4*>(rows2 + row_of(slots2, i2[f]) * RD) + c);
-        float4 d = make_float4(g * (s.x - e.x), g * (s.y - e.y), g * (s.z - e.z), g * (s.w - e.w));
-        if (dxr) {
-          const uint2 p = *reinterpret_cast<const uint2*>(dxr + f * D + c * 4);
-          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&p.x);
-          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&p.y);
-          d.x += __bfloat162float(lo.x), d.y += __bfloat162float(lo.y);
-          d.z += __bfloat162float(hi.x), d.w += __bfloat162float(hi.y);
-        }
-        red_add_v4(ugrad2 + static_cast<size_t>(i2[f]) * RD + c * 4, d);
-      }
+      red_add_v4(ugrad2 + static_cast<size_t>(u) * RD + c * 4, d);
     }
     if (ugrad1 != nullptr) {
       const int* i1 = inv1 + static_cast<size_t>(b) * F;
@@ -145,10 +156,11 @@ Sym to_sym(const SymHost& h) {
   return s;
 }
 
-int lanes_for_chunks(int chunks) {
-  int l = 1;
-  while (l < chunks && l < 32) l <<= 1;
-  return l;
+// Field groups per sample: as many as keep (D / 4) x G lanes within a quarter warp.
+int field_groups(int chunks) {
+  int g = 1;
+  while (chunks * g * 2 <= 16) g <<= 1;
+  return g;
 }
 
 int grid_for(long long rows, int lpr) {
@@ -166,21 +178,25 @@ void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cud
 
 void deepfm_pack_forward(const float* rows2, const int* inv2, const int* slots2, const float* rows1, const int* inv1,
                          const int* slots1, const float* dense, int B, int F, int D, int RD, int ND, __nv_bfloat16* x,
-                         int ldx, float* fm_logit, cudaStream_t stream) {
+                         int ldx, float* fm_logit, float* ssum, cudaStream_t stream) {
   if (B <= 0) return;
-  const int lpr = lanes_for_chunks(D / 4);
+  const int chunks = D / 4;
+  const int G = field_groups(chunks);
+  const int lpr = chunks * G;
   deepfm_pack_forward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, slots2, rows1, inv1, slots1, dense,
-                                                                        B, F, D, RD, ND, lpr, x, ldx, fm_logit);
+                                                                        B, F, D, RD, ND, lpr, G, x, ldx, fm_logit, ssum);
 }
 
 void deepfm_pack_backward(const float* rows2, const int* inv2, const int* slots2, const int* inv1,
                           const __nv_bfloat16* dx, int lddx,
-                          const float* dlogit, int B, int F, int D, int RD, float* ugrad2, float* ugrad1,
-                          cudaStream_t stream) {
+                          const float* dlogit, const float* ssum, int B, int F, int D, int RD, float* ugrad2,
+                          float* ugrad1, cudaStream_t stream) {
   if (B <= 0) return;
-  const int lpr = lanes_for_chunks(D / 4);
-  deepfm_pack_backward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, slots2, inv1, dx, lddx, dlogit, B,
-                                                                         F, D, RD, lpr, ugrad2, ugrad1);
+  const int chunks = D / 4;
+  const int G = field_groups(chunks);
+  const int lpr = chunks * G;
+  deepfm_pack_backward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, slots2, inv1, dx, lddx, dlogit,
+                                                                         ssum, B, F, D, RD, lpr, G, ugrad2, ugrad1);
 }
 
 }  // namespace cu

@@ -137,18 +137,18 @@ void bce_forward_backward(const float* logits, const float* labels, int n, float
 void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cudaStream_t stream);
 // x[B, ldx] bf16 = [emb rows of F fields x D | ND dense features | zeros], fm_logit[B] fp32.
 // rows2 [*, RD] / rows1 [*, 1] are unique rows, inv2 / inv1 [B * F] map occurrences to them.  D % 4 == 0,
-// RD % 4 == 0.  rows1 == nullptr: the first-order weight is column D of rows2 (RD >= D + 1).
+// RD % 4 == 0, D / 4 a power of two <= 32.  rows1 == nullptr: the first-order weight is column D of rows2
+// (RD >= D + 1).  ssum [B, D] (nullable in the forward) receives sum_f e_f per sample; the backward reads it.
 // slots2 / slots1 (nullable): rows2 / rows1 are then the tables' value slabs and unique entry u lives in
 // row slots[u] (the in-place path of single-GPU jobs).
 void deepfm_pack_forward(const float* rows2, const int* inv2, const int* slots2, const float* rows1, const int* inv1,
                          const int* slots1, const float* dense, int B, int F, int D, int RD, int ND, __nv_bfloat16* x,
-                         int ldx, float* fm_logit, cudaStream_t stream);
+                         int ldx, float* fm_logit, float* ssum, cudaStream_t stream);
 // Adds each occurrence's gradient into ugrad2 [*, RD] / ugrad1 [*, 1] (per unique id).  dx may be null;
 // ugrad1 == nullptr: the first-order gradient goes to column D of ugrad2.
 void deepfm_pack_backward(const float* rows2, const int* inv2, const int* slots2, const int* inv1,
-                          const __nv_bfloat16* dx, int lddx,
-                          const float* dlogit, int B, int F, int D, int RD, float* ugrad2, float* ugrad1,
-                          cudaStream_t stream);
+                          const __nv_bfloat16* dx, int lddx, const float* dlogit, const float* ssum, int B, int F, int D,
+                          int RD, float* ugrad2, float* ugrad1, cudaStream_t stream);
 
 // bf16 copy [N, K] and bf16 transpose [K, N] of an fp32 weight matrix [N, K], one pass.
 void cast_w_wt(const float* w, int N, int K, __nv_bfloat16* w16, __nv_bfloat16* wt16, cudaStream_t stream);

@@ -43,24 +43,25 @@ class _DeepFMFront(torch.autograd.Function):
             rows1, inv1, t1 = eng.pull_sparse_unique(id1, ids, share_with=id2, in_place=in_place)
         x = torch.empty((B, width), dtype=torch.bfloat16, device=rows2.device)
         fm = torch.empty(B, dtype=torch.float32, device=rows2.device)
+        ssum = torch.empty((B, dim), dtype=torch.float32, device=rows2.device)  # sum_f e_f, reused by the backward
         dense = dense.to(rows2.device, torch.float32).contiguous()
         counters.add()
         with engine_region("pack_fwd"):
             C.deepfm_pack_forward(rows2, inv2, rows1, inv1, dense, B, F, dim, x, fm, t2.slots,
-                                  t1.slots if t1 is not None else None)
-        ctx.state = (eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F, dim)
+                                  t1.slots if t1 is not None else None, ssum)
+        ctx.state = (eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F, dim, ssum)
         return x, fm
 
     @staticmethod
     def backward(ctx, dx, dfm):
-        eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F, dim = ctx.state
+        eng, id1, id2, rows2, inv2, inv1, t1, t2, B, F, dim, ssum = ctx.state
         if dfm is None:
             dfm = torch.zeros(B, dtype=torch.float32, device=rows2.device)
         counters.add()
         with engine_region("pack_bwd"):
             C.deepfm_pack_backward(rows2, inv2, inv1, dx.contiguous() if dx is not None else None,
                                    dfm.float().contiguous(), B, F, dim, eng.grad_accumulator(id2),
-                                   eng.grad_accumulator(id1) if id1 is not None else None, t2.slots)
+                                   eng.grad_accumulator(id1) if id1 is not None else None, t2.slots, ssum)
         if id1 is not None:
             eng.push_sparse_accumulated(id1, t1)
         eng.push_sparse_accumulated(id2, t2)
@@ -98,7 +99,8 @@ class DeepFM(torch.nn.Module):
         self.in_place_rows = in_place_rows
 
     def _fused_ok(self, ids: torch.Tensor) -> bool:
-        return (self.fused and self.dim % 4 == 0 and ids.dim() == 2 and native.is_initialized()
+        chunks = self.dim // 4
+        return (self.fused and self.dim % 4 == 0 and chunks & (chunks - 1) == 0 and self.dim <= 128 and ids.dim() == 2 and native.is_initialized()
                 and hasattr(native.engine(), "pull_sparse_unique") and not getattr(native.engine(), "nccl", False)
                 and self.mlp.use_tensor_cores)
 
