@@ -22,12 +22,13 @@ import torch
 
 class DevicePrefetcher:
     def __init__(self, loader: Iterable[Sequence[torch.Tensor]], device: torch.device, depth: int = 2,
-                 chunk_bytes: int = 1 << 20, buffers: Optional[Sequence[Sequence[torch.Tensor]]] = None) -> None:
+                 chunk_bytes: int = 1 << 18, buffers: Optional[Sequence[Sequence[torch.Tensor]]] = None) -> None:
         """buffers: device buffer sets to fill in turn instead of allocating (for instance the static
         inputs of a multi-slot ``GraphedStep``; ``last_slot`` then tells which set a batch landed in).
         chunk_bytes: large tensors cross PCIe as a series of copies of at most this size.  One long
-        DMA transfer running beside the step's kernels was measured to slow a 1.05 ms step by 0.10 ms;
-        the same bytes in 1 MB pieces cost 0.04 ms."""
+        DMA transfer of 17 MB running beside the step's kernels was measured to slow a 1.03 ms step by
+        0.24 ms, 1 MB pieces by 0.14 ms, 256 KB pieces by 0.06 ms; at 64 KB the host cannot issue
+        the copies fast enough."""
         self.chunk_bytes = max(1 << 16, int(chunk_bytes))
         self.it: Iterator[Sequence[torch.Tensor]] = iter(loader)
         self.device = device
