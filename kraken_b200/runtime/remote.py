@@ -10,8 +10,15 @@ gradients.  Placement is the reference's: a sparse row lives on
 ``ring.hit(Mix64(table_id))``.  A worker whose ring is stale gets
 kRouterVersion (8), refetches it and retries once (kraken/worker/emitter.cc:32-62).
 
-A server that joins after rows exist receives no rows from the older servers
-(no live migration): add servers before training, or save and load to reshard.
+Elastic scale-out (kraken/ps/ps.cc:336-477,553-602, kraken/scheduler/scheduler.cc:56-146): a
+server may join while training runs.  The scheduler admits it only when every server reports
+kWork, adds it to the ring (version + 1) and tells the older servers (kNotifyNodeJoin); each of
+them moves the rows and dense tables that the new ring assigns to the newcomer (kTransfer*
+messages, 65,536 rows per message, three attempts each), drops them, adopts the new ring and
+answers; then the newcomer starts to serve.  Unlike the reference there is no proxy phase: while
+a server is transferring it refuses requests with kNodeStatus, and workers retry with a back-off
+and a refreshed ring, re-partitioning only the part of a request that was refused (so a push is
+never applied twice).
 """
 from __future__ import annotations
 
@@ -80,20 +87,32 @@ class SchedulerServer:
 
     def try_join(self, meta, tensors):
         with self.mu:
+            # admission gate: nobody may be saving, loading or transferring (scheduler.cc:63-90)
+            if self.clients and not self._all_working():
+                return {"allow": False}, ()
             node_id = (max(self.nodes) + 1) if self.nodes else 0
+            old_clients = dict(self.clients)
             self.router.add(node_id, meta["addr"])
             self.nodes[node_id] = meta["addr"]
             self.clients[node_id] = Connecter(meta["addr"])
             new = self.clients[node_id]
+            rm = self._router_meta()
+            new.call(Rpc.FETCH_ROUTER, rm)
             if self.model is not None:
                 new.call(Rpc.CREATE_MODEL, self.model)
                 for t in self.tables.values():
                     if t["kind"] == "sparse":
                         new.call(Rpc.CREATE_SPARSE, t)
-            rm = self._router_meta()
-            for nid, c in self.clients.items():
-                c.call(Rpc.FETCH_ROUTER, rm)  # tells every shard the new ring and its version
-            return {"node_id": node_id, **rm}, ()
+            # every older server ships what the new ring takes from it, then adopts the ring
+            note = {**rm, "new_node": node_id, "new_addr": meta["addr"], "tables": list(self.tables.values())}
+            moved = 0
+            for nid, c in old_clients.items():
+                out, _ = c.call(Rpc.NOTIFY_NODE_JOIN, note, timeout_ms=600_000)
+                moved += int(out.get("rows_moved", 0))
+            if old_clients:
+                new.call(Rpc.NOTIFY_FINISH_TRANSFER, {"rows_moved": moved})
+                log.info("node %d joined: %d rows moved to it", node_id, moved)
+            return {"allow": True, "node_id": node_id, **rm}, ()
 
     def fetch_router(self, meta, tensors):
         with self.mu:
@@ -197,26 +216,48 @@ class PsServer:
         self.node_id = -1
         self.router = C.Router()
         self.version = 0
+        self.mu = threading.RLock()  # handlers run on one thread per connection: one at a time touches the shard
+        self.rows_received = 0
         s = self.station
         s.register(Rpc.HEARTBEAT, lambda m, t: ({"status": self.status}, ()))
-        s.register(Rpc.FETCH_ROUTER, self.set_router)
-        s.register(Rpc.CREATE_MODEL, self.create_model)
-        s.register(Rpc.CREATE_DENSE, self.create_dense)
-        s.register(Rpc.CREATE_SPARSE, self.create_sparse)
-        s.register(Rpc.PULL_DENSE, self.pull_dense)
-        s.register(Rpc.PUSH_DENSE, self.push_dense)
-        s.register(Rpc.PULL_SPARSE, self.pull_sparse)
-        s.register(Rpc.PUSH_SPARSE, self.push_sparse)
-        s.register(Rpc.NOTIFY_SAVE, self.notify_save)
-        s.register(Rpc.NOTIFY_LOAD, self.notify_load)
+        for rpc, fn in ((Rpc.FETCH_ROUTER, self.set_router), (Rpc.CREATE_MODEL, self.create_model),
+                        (Rpc.CREATE_DENSE, self.create_dense), (Rpc.CREATE_SPARSE, self.create_sparse),
+                        (Rpc.PULL_DENSE, self.pull_dense), (Rpc.PUSH_DENSE, self.push_dense),
+                        (Rpc.PULL_SPARSE, self.pull_sparse), (Rpc.PUSH_SPARSE, self.push_sparse),
+                        (Rpc.NOTIFY_SAVE, self.notify_save), (Rpc.NOTIFY_LOAD, self.notify_load),
+                        (Rpc.NOTIFY_NODE_JOIN, self.notify_node_join), (Rpc.TRANSFER_DENSE, self.transfer_dense),
+                        (Rpc.TRANSFER_SPARSE_VALUES, self.transfer_sparse_values),
+                        (Rpc.NOTIFY_FINISH_TRANSFER, self.notify_finish_transfer)):
+            s.register(rpc, self._locked(fn))
 
-    def start(self) -> None:
+    def _locked(self, fn):
+        def run(meta, tensors):
+            with self.mu:
+                return fn(meta, tensors)
+        return run
+
+    def start(self, join_wait_s: float = 0.2, join_deadline_s: float = 120.0) -> None:
+        """Registers with the scheduler.  While another server is saving, loading or transferring the
+        scheduler answers "not now": retried with a x1.5 back-off (kraken/ps/ps.cc:396-422 sleeps 10 s)."""
+        import time
         self.station.start()
-        meta, _ = Connecter(self.s_addr).call(Rpc.TRY_JOIN, {"addr": self.addr}, timeout_ms=60_000)
-        self.node_id = meta["node_id"]
-        self.set_router(meta, ())
-        self.status = C_STATUS_WORK
-        log.info("ps %d joined at %s (ring version %d)", self.node_id, self.addr, self.version)
+        sched = Connecter(self.s_addr)
+        wait, t0 = join_wait_s, time.monotonic()
+        while True:
+            meta, _ = sched.call(Rpc.TRY_JOIN, {"addr": self.addr}, timeout_ms=600_000)
+            if meta.get("allow", True):
+                break
+            if time.monotonic() - t0 > join_deadline_s:
+                raise RpcError(7, "the scheduler did not admit this server in time")
+            time.sleep(wait)
+            wait = min(wait * 1.5, 10.0)
+        sched.close()
+        with self.mu:
+            self.node_id = meta["node_id"]
+            self.set_router(meta, ())
+            self.status = C_STATUS_WORK
+        log.info("ps %d joined at %s (ring version %d, %d rows received)", self.node_id, self.addr, self.version,
+                 self.rows_received)
 
     def stop(self) -> None:
         self.station.stop()
@@ -235,6 +276,71 @@ class PsServer:
     def create_model(self, meta, tensors):
         self.shard.init_model(meta["name"], C.OptimType(meta["optim_type"]), meta["optim_conf"])
         return {}, ()
+
+    # ---------------- elastic scale-out: rows follow the ring to a server that has just joined
+    def notify_node_join(self, meta, tensors):
+        """Older server: move what the new ring assigns to the newcomer, then adopt the ring."""
+        new_ring = _router_from_hex(meta["router"])
+        new_node = int(meta["new_node"])
+        self.status = C_STATUS_WORK | C_STATUS_TRANSFER  # requests are refused (kNodeStatus) until this returns
+        moved = 0
+        try:
+            peer = Connecter(meta["new_addr"], timeout_ms=60_000)
+            for t in meta["tables"]:
+                tid = int(t["id"])
+                if not self.shard.has_table(tid):
+                    continue
+                if t["kind"] == "dense":
+                    if self.router.hit(C.mix64(tid)) == self.node_id and new_ring.hit(C.mix64(tid)) == new_node:
+                        v = self.shard.export_dense(tid)
+                        keys = sorted(int(k) for k in v["states"])
+                        _send_with_retries(peer, Rpc.TRANSFER_DENSE,
+                                           {"table": t, "state_keys": keys,
+                                            "states_i": {str(k): int(x) for k, x in v["states_i"].items()}},
+                                           [v["val"]] + [v["states"][k] for k in keys])
+                    continue
+                cols = self.shard.export_sparse(tid)
+                ids = cols["ids"]
+                if ids.numel() == 0:
+                    continue
+                go = torch.from_numpy(np.nonzero(_ring_owners(new_ring, tid, ids) == new_node)[0])
+                skeys = sorted(int(k) for k in cols["states"])
+                ikeys = sorted(int(k) for k in cols["states_i"])
+                for a in range(0, go.numel(), TRANSFER_ROWS):
+                    sel = go[a:a + TRANSFER_ROWS]
+                    _send_with_retries(peer, Rpc.TRANSFER_SPARSE_VALUES,
+                                       {"table_id": tid, "state_keys": skeys, "state_i_keys": ikeys},
+                                       [ids[sel], cols["vals"][sel]] + [cols["states"][k][sel] for k in skeys]
+                                       + [cols["states_i"][k][sel] for k in ikeys])
+                moved += int(go.numel())
+                # what the new ring no longer assigns to this server is dropped (kraken/ps/ps.cc:29-123)
+                self.shard.filter_sparse(tid, 2, 0, 1, 0, new_ring, self.node_id)
+            peer.close()
+            self.router, self.version = new_ring, meta["version"]
+        finally:
+            self.status = C_STATUS_WORK
+        return {"rows_moved": moved}, ()
+
+    def transfer_dense(self, meta, tensors):
+        t = meta["table"]
+        if not self.shard.has_table(int(t["id"])):
+            self.shard.create_dense_table(int(t["id"]), t["name"], tensors[0].view(*t["shape"]))
+        v = {"val": tensors[0].view(*t["shape"]),
+             "states": {int(k): x for k, x in zip(meta["state_keys"], tensors[1:])},
+             "states_i": {int(k): int(x) for k, x in meta["states_i"].items()}}
+        self.shard.import_dense(int(t["id"]), t["name"], v)
+        return {}, ()
+
+    def transfer_sparse_values(self, meta, tensors):
+        ns = len(meta["state_keys"])
+        states = {int(k): x for k, x in zip(meta["state_keys"], tensors[2:2 + ns])}
+        states_i = {int(k): x for k, x in zip(meta["state_i_keys"], tensors[2 + ns:])}
+        self.shard.import_sparse(int(meta["table_id"]), tensors[0], tensors[1], states, states_i)
+        self.rows_received += int(tensors[0].numel())
+        return {}, ()
+
+    def notify_finish_transfer(self, meta, tensors):
+        return {"rows_received": self.rows_received}, ()
 
     def create_dense(self, meta, tensors):
         self.shard.create_dense_table(meta["id"], meta["name"], tensors[0])
@@ -280,6 +386,8 @@ class PsServer:
                 if not self.shard.has_table(t["id"]):
                     continue
                 if t["kind"] == "dense":
+                    if self.router.hit(C.mix64(t["id"])) != self.node_id:
+                        continue  # moved to a server that joined later: the copy here is stale
                     C.ckpt_save_dense(out, t["id"], t["name"], self.shard.export_dense(t["id"]))
                 else:
                     cols = self.shard.export_sparse(t["id"])
@@ -315,7 +423,29 @@ class PsServer:
         return {}, ()
 
 
-C_STATUS_INIT, C_STATUS_WORK, C_STATUS_SAVE, C_STATUS_LOAD = 1, 2, 16, 32
+C_STATUS_INIT, C_STATUS_WORK, C_STATUS_TRANSFER, C_STATUS_SAVE, C_STATUS_LOAD = 1, 2, 8, 16, 32
+TRANSFER_ROWS = 65536  # rows per kTransferSparseValues message (the reference sends 1024: kraken/ps/ps.cc:251)
+
+
+def _ring_owners(router, table_id: int, ids: torch.Tensor) -> np.ndarray:
+    """Node of every id on ``router``: ring.hit(Mix64(table_id) ^ Mix64(id)), vectorised."""
+    vn = router.vnodes()
+    vhash = np.array([v[0] for v in vn], dtype=np.uint64)
+    vnode = np.array([v[1] for v in vn], dtype=np.int64)
+    hv = mix64(ids.numpy().view(np.uint64)) ^ np.uint64(C.mix64(table_id))
+    idx = np.searchsorted(vhash, hv, side="left")
+    idx[idx == len(vhash)] = 0
+    return vnode[idx]
+
+
+def _send_with_retries(peer: "Connecter", rpc: int, meta: dict, tensors, attempts: int = 3):
+    """A transfer message is tried three times before the join fails (kraken/ps/transfer.cc:37-47)."""
+    for k in range(attempts):
+        try:
+            return peer.call(rpc, meta, tensors, timeout_ms=60_000)
+        except RpcError as e:
+            if k == attempts - 1 or e.code != 17:
+                raise
 
 
 def _model_meta(meta: dict):
@@ -366,15 +496,49 @@ class RemoteEngine(Engine):
         idx[idx == len(self._vhash)] = 0
         return self._vnode[idx]
 
-    def _call_ps(self, node: int, rpc: int, meta: dict, tensors=()):
-        """One retry after refetching the ring when the server says ours is stale."""
-        try:
-            return self.ps[node].call(rpc, {**meta, "router_version": self.version}, tensors)
-        except RpcError as e:
-            if e.code != 8:
-                raise
-            self._refresh_router()
-            return self.ps[node].call(rpc, {**meta, "router_version": self.version}, tensors)
+    RETRY_CODES = (7, 8)  # kNodeStatus (server busy transferring / saving), kRouterVersion (our ring is old)
+
+    def _backoff(self, attempt: int) -> None:
+        import time
+        if attempt >= 60:
+            raise RpcError(7, "the servers stayed busy")
+        time.sleep(min(0.02 * (1.5 ** attempt), 1.0))
+        self._refresh_router()
+
+    def _call_dense(self, table_id: int, rpc: int, meta: dict, tensors=()):
+        """Calls the table's owner; if the server refuses (stale ring, or busy moving rows to a server
+        that has just joined) the ring is refetched, the owner looked up again and the call repeated."""
+        attempt = 0
+        while True:
+            owner = self.router.hit(C.mix64(table_id))
+            try:
+                return self.ps[owner].call(rpc, {**meta, "router_version": self.version}, tensors)
+            except RpcError as e:
+                if e.code not in self.RETRY_CODES:
+                    raise
+                self._backoff(attempt)
+                attempt += 1
+
+    def _call_sparse(self, rpc: int, table_id: int, meta: dict, ids: torch.Tensor, payload, done, attempt: int = 0):
+        """Sends every id (with its payload row) to its owner.  A part that a server refuses is
+        partitioned again on the refreshed ring and sent again, alone: parts that were accepted are
+        never repeated, so a push is applied exactly once.  ``done(positions, reply_tensors)`` is called
+        for every accepted part with the positions (into ``ids``) it covered."""
+        owners = self._owners(table_id, ids)
+        for node in np.unique(owners):
+            sel = torch.from_numpy(np.nonzero(owners == node)[0])
+            tensors = [ids[sel]] + ([payload[sel]] if payload is not None else [])
+            try:
+                _, ts = self.ps[int(node)].call(rpc, {**meta, "table_id": table_id, "router_version": self.version},
+                                                tensors)
+            except RpcError as e:
+                if e.code not in self.RETRY_CODES:
+                    raise
+                self._backoff(attempt)
+                self._call_sparse(rpc, table_id, meta, ids[sel], payload[sel] if payload is not None else None,
+                                  lambda pos, ts, sel=sel: done(sel[pos], ts), attempt + 1)
+                continue
+            done(sel, ts)
 
     # registry: the scheduler owns it
     def init_model(self, model_name, optim_type, optim_conf=None):
@@ -406,33 +570,32 @@ class RemoteEngine(Engine):
     # dense
     def pull_dense_table(self, table_id):
         info = self._table(table_id, "dense")
-        owner = self.router.hit(C.mix64(table_id))
-        _, ts = self._call_ps(owner, Rpc.PULL_DENSE, {"table_ids": [table_id]})
+        _, ts = self._call_dense(table_id, Rpc.PULL_DENSE, {"table_ids": [table_id]})
         return ts[0].view(*info.shape)
 
     def push_dense_table(self, table_id, grad):
         self._table(table_id, "dense")
         g = grad.detach().to("cpu", torch.float32).contiguous().reshape(-1)
-        owner = self.router.hit(C.mix64(table_id))
         st = self.dct_states.get(table_id)
         if st is not None:
             packed = C.cpu_dct_compress(g, self.cfg.life_span, self.cfg.eta, st)
             if packed is not None:
-                self._call_ps(owner, Rpc.PUSH_DENSE, {"table_id": table_id, "lr": self.lr, "coo": True}, list(packed))
+                self._call_dense(table_id, Rpc.PUSH_DENSE, {"table_id": table_id, "lr": self.lr, "coo": True},
+                                 list(packed))
                 return
-        self._call_ps(owner, Rpc.PUSH_DENSE, {"table_id": table_id, "lr": self.lr}, [g])
+        self._call_dense(table_id, Rpc.PUSH_DENSE, {"table_id": table_id, "lr": self.lr}, [g])
 
     # sparse
     def pull_sparse_table(self, table_id, indices):
         info = self._table(table_id, "sparse")
         idx = indices.detach().to("cpu").to(torch.int64).contiguous()
         uniq, inv = C.cpu_dedup(idx.reshape(-1))
-        owners = self._owners(table_id, uniq)
         rows = torch.empty((uniq.numel(), info.dimension), dtype=torch.float32)
-        for node in np.unique(owners):
-            sel = torch.from_numpy(np.nonzero(owners == node)[0])
-            _, ts = self._call_ps(int(node), Rpc.PULL_SPARSE, {"table_id": table_id}, [uniq[sel]])
-            rows[sel] = ts[0]
+
+        def put(pos, ts):
+            rows[pos] = ts[0]
+
+        self._call_sparse(Rpc.PULL_SPARSE, table_id, {}, uniq, None, put)
         return rows[inv].view(*idx.shape, info.dimension)
 
     def push_sparse_table(self, table_id, indices, grad):
@@ -441,10 +604,7 @@ class RemoteEngine(Engine):
         g = grad.detach().to("cpu", torch.float32).contiguous().view(-1, info.dimension)
         uniq, inv = C.cpu_dedup(idx)
         summed = C.cpu_segment_sum(g, inv, uniq.numel())
-        owners = self._owners(table_id, uniq)
-        for node in np.unique(owners):
-            sel = torch.from_numpy(np.nonzero(owners == node)[0])
-            self._call_ps(int(node), Rpc.PUSH_SPARSE, {"table_id": table_id, "lr": self.lr}, [uniq[sel], summed[sel]])
+        self._call_sparse(Rpc.PUSH_SPARSE, table_id, {"lr": self.lr}, uniq, summed, lambda pos, ts: None)
 
     # checkpoints are written and read by the servers; the scheduler orchestrates
     def try_save_model(self) -> bool:

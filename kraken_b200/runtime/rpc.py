@@ -33,13 +33,18 @@ HEADER = struct.Struct("<QiB")  # timestamp, type | error code, compress
 class Rpc:
     HEARTBEAT = 0
     TRY_JOIN = 1
+    NOTIFY_NODE_JOIN = 2
     INIT_MODEL = 3
     REGISTER_DENSE = 4
     REGISTER_SPARSE = 5
     CREATE_MODEL = 6
     CREATE_DENSE = 7
     CREATE_SPARSE = 8
+    NOTIFY_FINISH_TRANSFER = 10
     FETCH_ROUTER = 11
+    TRANSFER_DENSE = 12
+    TRANSFER_SPARSE_META = 13
+    TRANSFER_SPARSE_VALUES = 14
     PULL_DENSE = 19
     COMBINE_PULL_DENSE = 20
     PUSH_DENSE = 21

@@ -105,3 +105,84 @@ def test_rpc_timeout_is_reported(tmp_path):
     finally:
         c.close()
         silent.close()
+
+
+def test_server_joins_while_training(tmp_path):
+    """Elastic scale-out: a second (then a third) server joins a cluster that already holds rows and
+    optimizer state.  The rows the new ring assigns to it move over, nothing is lost or applied twice,
+    and a worker that keeps training through the join only sees retries."""
+    import threading
+
+    sched, servers = boot(tmp_path, n_ps=1)
+    try:
+        kk.initialize(f"tcp://127.0.0.1:{sched.port}")
+        kk.init_model("m", kk.OptimType.kAdagrad, {"initial_accumulator_value": "0.1"})
+        kk.update_lr(0.1)
+        w0 = torch.randn(5, 3)
+        tds = [kk.register_dense_table(f"w{i}", w0 + i) for i in range(6)]
+        ts = kk.register_sparse_table("e", 4, torch.float32, kk.InitializerType.kNormal, {"stddev": "0.1"})
+        ids = torch.arange(0, 3000)
+        kk.pull_sparse_table(ts, ids)
+        torch.manual_seed(0)
+        for _ in range(3):   # rows and Adagrad accumulators now differ from their initial values
+            kk.push_sparse_table(ts, ids, torch.randn(3000, 4))
+            for td in tds:
+                kk.push_dense_table(td, torch.randn(5, 3))
+        before = kk.pull_sparse_table(ts, ids).clone()
+        dense_before = [kk.pull_dense_table(td).clone() for td in tds]
+        state_before = servers[0].shard.export_sparse(ts)
+        order = torch.argsort(state_before["ids"])
+        acc_before = {int(k): v[order].clone() for k, v in state_before["states"].items()}
+
+        # a worker thread keeps pulling and pushing zero gradients while the servers join
+        stop, errors, steps = threading.Event(), [], [0]
+
+        def train():
+            try:
+                while not stop.is_set():
+                    kk.pull_sparse_table(ts, ids[:500])
+                    kk.push_sparse_table(ts, ids[:500], torch.zeros(500, 4))
+                    steps[0] += 1
+            except Exception as e:  # noqa: BLE001 - the test reports whatever went wrong
+                errors.append(e)
+
+        th = threading.Thread(target=train)
+        th.start()
+        for _ in range(2):
+            ps = PsServer(0, "", f"127.0.0.1:{sched.port}", saved_dir=str(tmp_path), seed=5)
+            ps.addr = f"127.0.0.1:{ps.port}"
+            ps.start()
+            servers.append(ps)
+        stop.set()
+        th.join(timeout=60)
+        assert not errors, errors
+        assert steps[0] > 0
+
+        sizes = [s.shard.sparse_size(ts) for s in servers]
+        assert sum(sizes) == 3000 and all(n > 0 for n in sizes), sizes
+        for s in servers:   # every row sits where the final ring says
+            for i in s.shard.export_sparse(ts)["ids"].tolist():
+                assert sched.router.hit(C.mix64_pair(ts, i)) == s.node_id
+        assert torch.equal(kk.pull_sparse_table(ts, ids), before)   # zero gradients: values unchanged
+        for td, want in zip(tds, dense_before):
+            assert torch.equal(kk.pull_dense_table(td), want)
+        owners = {sched.router.hit(C.mix64(td)) for td in tds}
+        assert len(owners) > 1   # some dense tables moved as well
+        # optimizer state travelled with the rows
+        got_ids = torch.cat([s.shard.export_sparse(ts)["ids"] for s in servers])
+        o2 = torch.argsort(got_ids)
+        for k, want in acc_before.items():
+            got = torch.cat([s.shard.export_sparse(ts)["states"][k] for s in servers])[o2]
+            # zero-gradient Adagrad steps leave the accumulator as it was
+            assert torch.allclose(got, want)
+        # one more real step lands exactly once
+        kk.push_sparse_table(ts, ids[:10], torch.ones(10, 4))
+        after = kk.pull_sparse_table(ts, ids[:10])
+        acc = acc_before[min(acc_before)][:10]
+        assert torch.allclose(after, before[:10] - 0.1 / (acc + 1.0).sqrt(), atol=1e-5)
+        assert kk.try_save_model()
+    finally:
+        kk.stop()
+        sched.stop()
+        for s in servers:
+            s.stop()
