@@ -63,6 +63,9 @@ def main():
     p.add_argument("--resident-ids", action="store_true",
                    help="draw the ids from the rows populated before timing (steady state: no row is created in the "
                         "timed steps) instead of from the whole id space (nearly every unique id is a new row)")
+    p.add_argument("--graph", action="store_true",
+                   help="replay the pull and the push as two CUDA graphs (as inside a captured training step) "
+                        "instead of launching their kernels from Python")
     p.add_argument("--checkpoint-rows", type=int, default=2_000_000, help="rows per shard in the save/load timing (0 = skip)")
     a = p.parse_args()
     world, rank = world_rank()
@@ -106,13 +109,35 @@ def main():
     grads = torch.randn(n, 64, device=dev) * 0.01
     pull_t, push_t = DeviceTimer(), DeviceTimer()
     pull_ms = push_ms = 0.0
+    g_pull = g_push = None
+    if a.graph:
+        static_ids = batches[0].clone()
+        for _ in range(2):  # eager: creates the channel and fills the allocator pool
+            kk.pull_sparse_table(t, static_ids)
+            kk.push_sparse_table(t, static_ids, grads)
+        sync_all()
+        g_pull, g_push = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_pull):
+            rows = kk.pull_sparse_table(t, static_ids)
+        with torch.cuda.graph(g_push, pool=g_pull.pool()):
+            kk.push_sparse_table(t, static_ids, grads)
+        sync_all()
     for i in range(total):
-        pull_t.start()
-        rows = kk.pull_sparse_table(t, batches[i])
-        ms_pull = pull_t.stop_ms()
-        push_t.start()
-        kk.push_sparse_table(t, batches[i], grads)
-        ms_push = push_t.stop_ms()
+        if g_pull is not None:
+            static_ids.copy_(batches[i])
+            pull_t.start()
+            g_pull.replay()
+            ms_pull = pull_t.stop_ms()
+            push_t.start()
+            g_push.replay()
+            ms_push = push_t.stop_ms()
+        else:
+            pull_t.start()
+            rows = kk.pull_sparse_table(t, batches[i])
+            ms_pull = pull_t.stop_ms()
+            push_t.start()
+            kk.push_sparse_table(t, batches[i], grads)
+            ms_push = push_t.stop_ms()
         if i >= a.warmup:
             pull_ms += ms_pull
             push_ms += ms_push
@@ -123,6 +148,7 @@ def main():
     rec = {"benchmark": "pull_push", "n_gpus": world, "global_batch": a.global_batch, "ids_per_gpu": n, "dim": 64,
            "rows_per_shard": rows_local, "pull_us": pull_ms / a.steps * 1e3, "push_us": push_ms / a.steps * 1e3}
     rec["ids"] = "resident rows" if a.resident_ids else "whole id space"
+    rec["launch"] = "cuda-graph replay" if a.graph else "eager"
     rec["rows_created_per_step"] = round(created)
     rec.update(roofline(eng.metrics()["big"]["last_exchange"], 64, rec["pull_us"], rec["push_us"], created))
 

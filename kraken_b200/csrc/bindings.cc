@@ -783,20 +783,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   // ---------------- sparse kernels
   m.def("dedup_bucketize", [](const torch::Tensor& ids, int world, uint64_t salt, const torch::Tensor& hkeys,
-                              const torch::Tensor& hpos, const torch::Tensor& hwin, const torch::Tensor& slot_of,
-                              uint32_t hbits, const torch::Tensor& cnt, const torch::Tensor& off,
+                              const torch::Tensor& slot_of, uint32_t hbits, const torch::Tensor& cnt, const torch::Tensor& off,
                               const torch::Tensor& uniq, const torch::Tensor& inv, const torch::Tensor& status,
                               int cap_u, const SymHeap* heap, const cu::ChanLayout* lay,
                               const c10::optional<torch::Tensor>& ctrl) {
     need_cuda(ids, "ids", torch::kInt64);
     need_cuda(hkeys, "hkeys", torch::kInt64);
     const int n = static_cast<int>(ids.numel());
-    TORCH_CHECK(hkeys.numel() == (1ll << hbits) && (1ll << hbits) >= 2ll * n, "dedup scratch too small");
+    TORCH_CHECK(hkeys.dim() == 2 && hkeys.size(0) == (1ll << hbits) && hkeys.size(1) == 2 && hkeys.is_contiguous() &&
+                    (1ll << hbits) >= 2ll * n,
+                "dedup scratch must be a contiguous int64 [1 << hbits, 2] tensor with at least 2 n slots");
     if (cap_u <= 0) cap_u = static_cast<int>(uniq.numel());
     TORCH_CHECK(slot_of.numel() >= n && inv.numel() >= n && uniq.numel() >= cap_u, "dedup outputs too small");
     TORCH_CHECK(cnt.numel() >= world && off.numel() >= world + 1, "cnt/off too small");
     c10::cuda::CUDAGuard guard(ids.device());
-    cu::DedupScratch sc{hkeys.data_ptr(), ptr<int>(hpos), ptr<int>(hwin), ptr<int>(slot_of), hbits};
+    cu::DedupScratch sc{hkeys.data_ptr(), ptr<int>(slot_of), hbits};
     if (heap != nullptr && lay != nullptr && ctrl.has_value()) {
       // with a channel: the dedup's second kernel also dispatches the unique ids to their owners
       cu::dedup_bucketize_dispatch(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off),
@@ -807,8 +808,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                           ptr<int>(inv), cap_u, ptr<int>(status), cur_stream());
     }
     check_launch("dedup_bucketize");
-  }, py::arg("ids"), py::arg("world"), py::arg("salt"), py::arg("hkeys"), py::arg("hpos"), py::arg("hwin"),
-     py::arg("slot_of"), py::arg("hbits"), py::arg("cnt"), py::arg("off"), py::arg("uniq"), py::arg("inv"),
+  }, py::arg("ids"), py::arg("world"), py::arg("salt"), py::arg("hkeys"), py::arg("slot_of"), py::arg("hbits"), py::arg("cnt"), py::arg("off"), py::arg("uniq"), py::arg("inv"),
      py::arg("status"), py::arg("cap_u") = 0, py::arg("heap") = nullptr, py::arg("layout") = nullptr,
      py::arg("ctrl") = py::none());
   m.def("pull_dispatch", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,

@@ -63,9 +63,8 @@ struct TableHost {
 // Scratch of the dedup kernels: an open-addressing set of 1 << hbits slots
 // (hbits chosen so that it holds at least 2 n ids), all keys kEmptyKey between calls.
 struct DedupScratch {
-  void* hkeys;   // u64 [1 << hbits]
-  int* hpos;     // int [1 << hbits]  rank of the unique id inside its owner group
-  int* hwin;     // int [1 << hbits]  index of the occurrence that inserted the id
+  void* table;   // [1 << hbits] entries of 16 bytes: u64 key, then u32 rank of the unique id inside its owner
+                 // group and u32 index of the occurrence that inserted it (one 32-byte sector holds two entries)
   int* slot_of;  // int [n]
   uint32_t hbits;
 };

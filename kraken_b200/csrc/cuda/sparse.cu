@@ -135,9 +135,18 @@ __device__ __forceinline__ bool block_wait_one(const uint32_t* flag, uint32_t wa
 }
 
 // ------------------------------------------------------------------ dedup
+// The scratch hash set is an array of 16-byte entries {key, pos | win << 32}: the key that the probe
+// compares, and - in the same 32-byte sector - the rank of the unique id inside its owner group and
+// the index of the occurrence that inserted it.  An insert and the later finalize therefore touch one
+// random sector per id each instead of three separate arrays.
+struct DedupEntry {
+  unsigned long long key;
+  unsigned long long pos_win;
+};
+
 __global__ void __launch_bounds__(kThreads)
-dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, unsigned long long* hkeys,
-                    uint32_t hbits, int* hpos, int* hwin, int* slot_of, int* cnt, int* status) {
+dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, DedupEntry* table,
+                    uint32_t hbits, int* slot_of, int* cnt, int* status) {
   __shared__ int s_cnt[kMaxWorld];
   __shared__ int s_base[kMaxWorld];
   if (threadIdx.x < kMaxWorld) s_cnt[threadIdx.x] = 0;
@@ -156,10 +165,10 @@ dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t 
     const uint64_t mask = (1ull << hbits) - 1;
     slot = SlotHash(id ^ kDedupSalt, hbits);
     for (uint64_t probe = 0; probe <= mask; ++probe) {
-      const unsigned long long k = __ldcg(&hkeys[slot]);
+      const unsigned long long k = __ldcg(&table[slot].key);
       if (k == id) break;
       if (k == kEmptyKey) {
-        const unsigned long long old = atomicCAS(&hkeys[slot], kEmptyKey, static_cast<unsigned long long>(id));
+        const unsigned long long old = atomicCAS(&table[slot].key, kEmptyKey, static_cast<unsigned long long>(id));
         if (old == kEmptyKey) {
           won = true;
           break;
@@ -177,10 +186,9 @@ dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t 
   __syncthreads();
   if (threadIdx.x < world && s_cnt[threadIdx.x] > 0) s_base[threadIdx.x] = atomicAdd(&cnt[threadIdx.x], s_cnt[threadIdx.x]);
   __syncthreads();
-  if (won) {
-    hpos[slot] = s_base[owner] + lpos;
-    hwin[slot] = i;
-  }
+  if (won)
+    table[slot].pos_win = static_cast<unsigned long long>(static_cast<uint32_t>(s_base[owner] + lpos)) |
+                          (static_cast<unsigned long long>(static_cast<uint32_t>(i)) << 32);
 }
 
 // DISPATCH: the pull's id dispatch is done here as well - every unique id goes straight into its
@@ -189,10 +197,9 @@ dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t 
 // no separate dispatch launch.
 template <bool DISPATCH>
 __global__ void __launch_bounds__(kThreads)
-dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, unsigned long long* hkeys,
-                      const int* __restrict__ hpos, const int* __restrict__ hwin, const int* __restrict__ slot_of,
-                      const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv, int cap_u, int* status,
-                      Sym sym, ChanLayout lay, Ctrl* ctrl) {
+dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, DedupEntry* table,
+                      const int* __restrict__ slot_of, const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv,
+                      int cap_u, int* status, Sym sym, ChanLayout lay, Ctrl* ctrl) {
   __shared__ int s_off[kMaxWorld + 1];
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -221,10 +228,11 @@ dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_
     if (id == kEmptyKey) id = kEmptyKey - 1;
     const int slot = slot_of[i];
     const int o = static_cast<int>(OwnerOf(salt, id, world));
-    const int j = hpos[slot];  // position among the ids of owner o
+    const unsigned long long pw = __ldcg(&table[slot].pos_win);
+    const int j = static_cast<int>(static_cast<uint32_t>(pw));  // position among the ids of owner o
     const int u = s_off[o] + j;
     inv[i] = u < cap_u ? u : 0;
-    if (hwin[slot] == i) {
+    if (static_cast<int>(pw >> 32) == i) {
       if (u < cap_u) {
         uniq[u] = static_cast<int64_t>(id);
         if (DISPATCH) {
@@ -234,7 +242,7 @@ dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_
             set_status(&ctrl->status, err::kInboxOverflow);
         }
       }
-      hkeys[slot] = kEmptyKey;  // leave the set empty for the next call
+      table[slot].key = kEmptyKey;  // leave the set empty for the next call
     }
   }
   if (DISPATCH) {
@@ -636,11 +644,11 @@ void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupS
     cudaMemsetAsync(off, 0, sizeof(int) * (world + 1), stream);
     return;
   }
-  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys),
-                                                       sc.hbits, sc.hpos, sc.hwin, sc.slot_of, cnt, status);
-  dedup_finalize_kernel<false><<<blocks, kThreads, 0, stream>>>(
-      ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys), sc.hpos, sc.hwin, sc.slot_of, cnt, off, uniq, inv,
-      cap_u, status, Sym{}, ChanLayout{}, nullptr);
+  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table), sc.hbits,
+                                                       sc.slot_of, cnt, status);
+  dedup_finalize_kernel<false><<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table),
+                                                                sc.slot_of, cnt, off, uniq, inv, cap_u, status, Sym{},
+                                                                ChanLayout{}, nullptr);
 }
 
 void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
@@ -653,11 +661,11 @@ void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, uint64_t sal
   }
   const int blocks = (n + kThreads - 1) / kThreads;
   cudaMemsetAsync(cnt, 0, sizeof(int) * world, stream);
-  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys),
-                                                       sc.hbits, sc.hpos, sc.hwin, sc.slot_of, cnt, status);
-  dedup_finalize_kernel<true><<<blocks, kThreads, 0, stream>>>(
-      ids, n, world, salt, static_cast<unsigned long long*>(sc.hkeys), sc.hpos, sc.hwin, sc.slot_of, cnt, off, uniq, inv,
-      cap_u, status, to_sym(sym), lay, ctrl);
+  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table), sc.hbits,
+                                                       sc.slot_of, cnt, status);
+  dedup_finalize_kernel<true><<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table),
+                                                               sc.slot_of, cnt, off, uniq, inv, cap_u, status,
+                                                               to_sym(sym), lay, ctrl);
 }
 
 void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,

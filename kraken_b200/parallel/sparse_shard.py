@@ -245,9 +245,9 @@ class SparseChannel:
 
         self.ctrl = torch.zeros(8, dtype=torch.int32, device=dev)
         self.hbits = _next_pow2_bits(2 * self.cap)
-        self.hkeys = torch.full((1 << self.hbits,), _EMPTY, dtype=torch.int64, device=dev)
-        self.hpos = torch.zeros(1 << self.hbits, dtype=torch.int32, device=dev)
-        self.hwin = torch.zeros(1 << self.hbits, dtype=torch.int32, device=dev)
+        # dedup scratch set: entries of (key, position | winner << 32); every key is free between calls
+        self.hkeys = torch.zeros((1 << self.hbits, 2), dtype=torch.int64, device=dev)
+        self.hkeys[:, 0] = _EMPTY
         self.slot_of = torch.zeros(self.cap, dtype=torch.int32, device=dev)
         self.cnt = torch.zeros(world, dtype=torch.int32, device=dev)
         self._own_off = torch.zeros(world + 1, dtype=torch.int32, device=dev)
@@ -277,7 +277,7 @@ class SparseChannel:
         else:
             # the dedup's second kernel also sends the unique ids to their owners' inboxes
             self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
-            C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.hpos, self.hwin, self.slot_of, self.hbits,
+            C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.slot_of, self.hbits,
                               self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5], self.cap_u, h, lay, ctrl)
             self.launches += 2
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)

@@ -69,7 +69,7 @@ def test_dedup_bucketize_groups_by_owner():
     for world in (1, 3, 8):
         cnt = torch.zeros(world, dtype=torch.int32, device=DEV)
         off = torch.zeros(world + 1, dtype=torch.int32, device=DEV)
-        C.dedup_bucketize(ids, world, 0, ch.hkeys, ch.hpos, ch.hwin, ch.slot_of, ch.hbits, cnt, off, ch.uniq, ch.inv,
+        C.dedup_bucketize(ids, world, 0, ch.hkeys, ch.slot_of, ch.hbits, cnt, off, ch.uniq, ch.inv,
                           ch.ctrl[4:5])
         off_h = off.cpu().tolist()
         U = off_h[-1]
@@ -79,7 +79,7 @@ def test_dedup_bucketize_groups_by_owner():
         for o in range(world):
             seg = uniq[off_h[o]:off_h[o + 1]].tolist()
             assert all(C.owner_of(0, i, world) == o for i in seg)
-        assert (ch.hkeys == -1).all()  # the scratch set is empty again
+        assert (ch.hkeys[:, 0] == -1).all()  # the scratch set is empty again
 
 
 @pytest.mark.parametrize("optim,conf", [

@@ -34,16 +34,15 @@ def _regular(ids, world, salt):
     """The existing entry point, with scratch that the caller allocates."""
     dev, n = ids.device, ids.numel()
     hbits = max(4, (2 * max(n, 1) - 1).bit_length())
-    hkeys = torch.full((1 << hbits,), -1, dtype=torch.int64, device=dev)
-    hpos = torch.zeros(1 << hbits, dtype=torch.int32, device=dev)
-    hwin = torch.zeros(1 << hbits, dtype=torch.int32, device=dev)
+    hkeys = torch.zeros((1 << hbits, 2), dtype=torch.int64, device=dev)
+    hkeys[:, 0] = -1
     slot_of = torch.zeros(max(n, 1), dtype=torch.int32, device=dev)
     cnt = torch.zeros(world, dtype=torch.int32, device=dev)
     off = torch.zeros(world + 1, dtype=torch.int32, device=dev)
     uniq = torch.zeros(max(n, 1), dtype=torch.int64, device=dev)
     inv = torch.zeros(max(n, 1), dtype=torch.int32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    C.dedup_bucketize(ids, world, salt, hkeys, hpos, hwin, slot_of, hbits, cnt, off, uniq, inv, status)
+    C.dedup_bucketize(ids, world, salt, hkeys, slot_of, hbits, cnt, off, uniq, inv, status)
     return off, uniq, inv
 
 
