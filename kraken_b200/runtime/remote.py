@@ -285,7 +285,7 @@ class PsServer:
         self.status = C_STATUS_WORK | C_STATUS_TRANSFER  # requests are refused (kNodeStatus) until this returns
         moved = 0
         try:
-            peer = Connecter(meta["new_addr"], timeout_ms=60_000)
+            peer = Connecter(meta["new_addr"], timeout_ms=60_000, compress=1)  # server to server: compressed
             for t in meta["tables"]:
                 tid = int(t["id"])
                 if not self.shard.has_table(tid):
@@ -474,7 +474,8 @@ class RemoteEngine(Engine):
     def __init__(self, cfg: EngineConfig, s_addr: str) -> None:
         super().__init__(cfg, 0, 1)
         self.device = torch.device("cpu")
-        self.scheduler = Connecter(s_addr)
+        self.scheduler = Connecter(s_addr)   # control messages travel uncompressed, as in the reference
+        self.compress = 1 if (cfg.compress is not None and int(getattr(cfg.compress, "value", cfg.compress)) != 0) else 0
         self.ps: Dict[int, Connecter] = {}
         self.dct_states: Dict[int, object] = {}
         self._refresh_router()
@@ -485,7 +486,7 @@ class RemoteEngine(Engine):
         self.version = meta["version"]
         for nid, addr in meta["nodes"].items():
             if int(nid) not in self.ps:
-                self.ps[int(nid)] = Connecter(addr)
+                self.ps[int(nid)] = Connecter(addr, compress=self.compress)
         vn = self.router.vnodes()
         self._vhash = np.array([v[0] for v in vn], dtype=np.uint64)
         self._vnode = np.array([v[1] for v in vn], dtype=np.int64)

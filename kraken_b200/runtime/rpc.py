@@ -8,6 +8,12 @@ kraken/rpc/indep_connecter.cc).  This is the same idea on plain TCP sockets:
     header  = u64 timestamp (correlation id) | u32 type (request) or i32 error_code (reply) | u8 compress
     body    = u32 json_len | json metadata | tensors, each in the framework's binary tensor encoding
 
+Bodies may be compressed (header byte ``compress``: 0 = none, 1 = compressed): the reference
+compresses worker<->server and server<->server bodies with Snappy and never the header
+(kraken/common/compress.h:18-91, kraken/rpc/station.h:62-119 answers with the request's type).
+No Snappy library is available offline, so code 1 means zlib level 1 here; a server answers in
+the compression of the request.
+
 RPC type numbers are the reference's (kraken/protocol/rpc_func_type.h:8-38).
 A ``Station`` serves registered handlers on a thread pool; a ``Connecter`` is a
 client with a send lock, a timeout (5 s default, as in
@@ -21,6 +27,7 @@ import socketserver
 import struct
 import threading
 import time
+import zlib
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -97,14 +104,25 @@ def _recv_exact(sock: socket.socket, n: int) -> bytes:
     return bytes(buf)
 
 
-def send_frame(sock: socket.socket, stamp: int, code: int, body: bytes) -> None:
-    sock.sendall(struct.pack("<I", len(body)) + HEADER.pack(stamp, code, 0) + body)
+COMPRESS_NONE, COMPRESS_ZLIB = 0, 1
 
 
-def recv_frame(sock: socket.socket) -> Tuple[int, int, bytes]:
+def send_frame(sock: socket.socket, stamp: int, code: int, body: bytes, compress: int = COMPRESS_NONE) -> None:
+    if compress == COMPRESS_ZLIB:
+        body = zlib.compress(body, 1)
+    sock.sendall(struct.pack("<I", len(body)) + HEADER.pack(stamp, code, compress) + body)
+
+
+def recv_frame(sock: socket.socket) -> Tuple[int, int, bytes, int]:
+    """(correlation id, type or error code, body as sent by the application, compression used)."""
     (n,) = struct.unpack("<I", _recv_exact(sock, 4))
-    stamp, code, _ = HEADER.unpack(_recv_exact(sock, HEADER.size))
-    return stamp, code, _recv_exact(sock, n)
+    stamp, code, compress = HEADER.unpack(_recv_exact(sock, HEADER.size))
+    body = _recv_exact(sock, n)
+    if compress == COMPRESS_ZLIB:
+        body = zlib.decompress(body)
+    elif compress != COMPRESS_NONE:
+        raise ConnectionError(f"unknown body compression {compress}")
+    return stamp, code, body, compress
 
 
 Handler = Callable[[dict, List[torch.Tensor]], Tuple[dict, Sequence[torch.Tensor]]]
@@ -122,8 +140,8 @@ class Station:
                 self.request.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
                 while True:
                     try:
-                        stamp, rpc_type, body = recv_frame(self.request)
-                    except (ConnectionError, OSError, struct.error):
+                        stamp, rpc_type, body, comp = recv_frame(self.request)
+                    except (ConnectionError, OSError, struct.error, zlib.error):
                         return
                     fn = station.handlers.get(rpc_type)
                     try:
@@ -131,7 +149,7 @@ class Station:
                             raise RpcError(1, f"type {rpc_type}")
                         meta, tensors = unpack_body(body)
                         out_meta, out_tensors = fn(meta, tensors)
-                        send_frame(self.request, stamp, 0, pack_body(out_meta, out_tensors))
+                        send_frame(self.request, stamp, 0, pack_body(out_meta, out_tensors), comp)
                     except RpcError as e:
                         send_frame(self.request, stamp, e.code, pack_body({"what": str(e)}))
                     except C.KrakenError as e:
@@ -163,9 +181,10 @@ class Connecter:
     """Client for one peer.  ``call`` is synchronous; a reply that does not arrive within
     ``timeout_ms`` raises kTimeout (17), an error reply raises with the server's code."""
 
-    def __init__(self, addr: str, timeout_ms: int = 5000) -> None:
+    def __init__(self, addr: str, timeout_ms: int = 5000, compress: int = COMPRESS_NONE) -> None:
         host, port = addr.rsplit(":", 1)
         self.addr = addr
+        self.compress = compress
         self.timeout = timeout_ms / 1000.0
         self.sock = socket.create_connection((host, int(port)), timeout=self.timeout)
         self.sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
@@ -179,9 +198,9 @@ class Connecter:
             stamp = self.stamp
             self.sock.settimeout(self.timeout if timeout_ms is None else timeout_ms / 1000.0)
             try:
-                send_frame(self.sock, stamp, rpc_type, pack_body(meta or {}, tensors))
+                send_frame(self.sock, stamp, rpc_type, pack_body(meta or {}, tensors), self.compress)
                 while True:
-                    got, code, body = recv_frame(self.sock)
+                    got, code, body, _ = recv_frame(self.sock)
                     if got == stamp:
                         break  # stale replies of timed-out calls are dropped
             except socket.timeout:

@@ -186,3 +186,40 @@ def test_server_joins_while_training(tmp_path):
         sched.stop()
         for s in servers:
             s.stop()
+
+
+def test_compressed_bodies_round_trip(tmp_path):
+    """Worker<->server bodies compressed (header byte 1): same results as uncompressed, and a frame of
+    a compressible tensor is smaller on the wire."""
+    import socket as pysocket
+
+    from kraken_b200.runtime import rpc
+
+    sched, servers = boot(tmp_path, n_ps=2)
+    try:
+        kk.initialize(f"tcp://127.0.0.1:{sched.port}", compress=kk.CompressType.kDCT)  # the reference's kSnappy slot
+        assert all(c.compress == 1 for c in kk.native.engine().ps.values())
+        kk.init_model("m", kk.OptimType.kSGD, {})
+        kk.update_lr(1.0)
+        ts = kk.register_sparse_table("e", 8, torch.float32, kk.InitializerType.kConstant, {"value": "2.0"})
+        ids = torch.arange(5000)
+        assert torch.equal(kk.pull_sparse_table(ts, ids), torch.full((5000, 8), 2.0))
+        kk.push_sparse_table(ts, ids, torch.ones(5000, 8))
+        assert torch.equal(kk.pull_sparse_table(ts, ids), torch.ones(5000, 8))
+    finally:
+        kk.stop()
+        sched.stop()
+        for s in servers:
+            s.stop()
+
+    a, b = pysocket.socketpair()
+    try:
+        body = rpc.pack_body({"k": 1}, [torch.zeros(1 << 16)])
+        rpc.send_frame(a, 7, 3, body, rpc.COMPRESS_ZLIB)
+        (n,) = rpc.struct.unpack("<I", b.recv(4, pysocket.MSG_PEEK))
+        assert n < len(body) // 20
+        stamp, code, got, comp = rpc.recv_frame(b)
+        assert (stamp, code, comp) == (7, 3, 1) and got == body
+    finally:
+        a.close()
+        b.close()
