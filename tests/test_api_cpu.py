@@ -184,3 +184,36 @@ def test_step_profiler_records_regions(tmp_path):
     recs = [json.loads(l) for l in open(path)]
     assert [r["step"] for r in recs] == [0, 1, 2] and all(r["pull_ms"] >= 0 and r["unique_ids"] == 5 for r in recs)
     assert "pull_ms" in prof.summary()
+
+
+def test_same_seed_gives_bitwise_identical_tables():
+    """Determinism check of the CPU engine: two runs with the same seed, data and step order leave
+    bit-for-bit the same rows, optimizer state and dense weights.  (The GPU kernels sum duplicate and
+    split-K gradients with floating-point atomics, so there only the tolerance tests apply.)"""
+    from kraken_b200.models import ClickDataset, DeepFM
+    from kraken_b200.ops import bce_with_logits
+
+    def run():
+        start(seed=11)
+        torch.manual_seed(0)
+        model = DeepFM(num_fields=5, num_dense=13, dim=8, hidden=(16, 8), init_std=0.1)
+        opt = kk.Optimizer("det", model.named_parameters(), 1e-2, kk.Adam())
+        data = ClickDataset(num_fields=5, vocab=200, seed=3)
+        for _ in range(6):
+            dense, ids, labels = data.batch(64)
+            loss = bce_with_logits(model(dense, ids), labels)
+            loss.backward()
+            opt.step()
+        probe = torch.arange(0, 1000)
+        rows = [kk.pull_sparse_table(p.table_id(), probe).clone() for p in
+                (model.second_order.sparse_table, model.first_order.sparse_table)]
+        dense_w = [p.detach().clone() for n, p in model.named_parameters() if p.dim() > 0 and p.numel() > 0
+                   and not hasattr(p, "table_id")]
+        kk.stop()
+        return float(loss.detach()), rows, dense_w
+
+    l0, r0, w0 = run()
+    l1, r1, w1 = run()
+    assert l0 == l1
+    assert all(torch.equal(a, b) for a, b in zip(r0, r1))
+    assert len(w0) > 0 and all(torch.equal(a, b) for a, b in zip(w0, w1))
