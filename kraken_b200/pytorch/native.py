@@ -131,12 +131,19 @@ def register_sparse_table(name: str, dimension: int, dtype, init_type, init_conf
     return engine().register_sparse_table(name, dimension, dtype, init_type, init_conf)
 
 
+def _as_registered(table_id: int, t: torch.Tensor) -> torch.Tensor:
+    """Values leave the engine in the dtype the table was registered with (shards hold float32)."""
+    info = engine().tables.get(table_id)
+    want = getattr(info, "dtype", torch.float32) if info is not None else torch.float32
+    return t if t.dtype == want else t.to(want)
+
+
 def pull_dense_table(table_id: int) -> torch.Tensor:
-    return engine().pull_dense_table(table_id)
+    return _as_registered(table_id, engine().pull_dense_table(table_id))
 
 
 def combine_pull_dense_table(table_ids: Sequence[int]) -> List[torch.Tensor]:
-    return engine().combine_pull_dense_table(list(table_ids))
+    return [_as_registered(i, t) for i, t in zip(table_ids, engine().combine_pull_dense_table(list(table_ids)))]
 
 
 def push_dense_table(table_id: int, grad: torch.Tensor) -> None:
@@ -144,11 +151,12 @@ def push_dense_table(table_id: int, grad: torch.Tensor) -> None:
 
 
 def pull_sparse_table(table_id: int, indices: torch.Tensor) -> torch.Tensor:
-    return engine().pull_sparse_table(table_id, indices)
+    return _as_registered(table_id, engine().pull_sparse_table(table_id, indices))
 
 
 def combine_pull_sparse_table(table_ids: Sequence[int], indices: Sequence[torch.Tensor]) -> List[torch.Tensor]:
-    return engine().combine_pull_sparse_table(list(table_ids), list(indices))
+    outs = engine().combine_pull_sparse_table(list(table_ids), list(indices))
+    return [_as_registered(i, t) for i, t in zip(table_ids, outs)]
 
 
 def push_sparse_table(table_id: int, indices: torch.Tensor, grad: torch.Tensor) -> None:

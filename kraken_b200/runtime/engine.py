@@ -53,6 +53,7 @@ class TableInfo:
     dimension: int = 0
     init_type: object = None
     init_conf: Dict[str, str] = field(default_factory=dict)
+    dtype: object = torch.float32    # what the caller registered; shards always hold float32
 
 
 def _env_int(name: str, default: int) -> int:
@@ -116,7 +117,8 @@ class Engine:
                 raise C.KrakenError(f"dense table {name!r} is already registered with another type or shape")
             return info.id
         tid = self._new_id(table_id)
-        info = TableInfo(id=tid, name=name, kind="dense", shape=tuple(val.shape))
+        info = TableInfo(id=tid, name=name, kind="dense", shape=tuple(val.shape),
+                         dtype=val.dtype if val.is_floating_point() else torch.float32)
         self.tables[tid] = info
         self.name_to_id[name] = tid
         self._on_register_dense(info, val)
@@ -125,8 +127,10 @@ class Engine:
     def register_sparse_table(self, name: str, dimension: int, dtype, init_type, init_conf: Dict[str, str],
                               table_id: Optional[int] = None) -> int:
         self._need_model()
-        if dtype not in (torch.float32, None):
-            raise C.KrakenError("sparse tables hold float32 rows")
+        # Shards hold float32 rows and state whatever the caller asks for; float64 / float16 / bfloat16
+        # tables are converted where values leave or enter the engine (pytorch/native.py).
+        if dtype not in (torch.float32, torch.float64, torch.float16, torch.bfloat16, None):
+            raise C.KrakenError("sparse tables are float32, float64, float16 or bfloat16")
         if name in self.name_to_id:
             info = self.tables[self.name_to_id[name]]
             if info.kind != "sparse" or info.dimension != int(dimension) or info.init_type != init_type:
@@ -134,7 +138,7 @@ class Engine:
             return info.id
         tid = self._new_id(table_id)
         info = TableInfo(id=tid, name=name, kind="sparse", dimension=int(dimension), init_type=init_type,
-                         init_conf=dict(init_conf))
+                         init_conf=dict(init_conf), dtype=dtype or torch.float32)
         self.tables[tid] = info
         self.name_to_id[name] = tid
         self._on_register_sparse(info)

@@ -217,3 +217,22 @@ def test_same_seed_gives_bitwise_identical_tables():
     assert l0 == l1
     assert all(torch.equal(a, b) for a, b in zip(r0, r1))
     assert len(w0) > 0 and all(torch.equal(a, b) for a, b in zip(w0, w1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float16])
+def test_tables_of_other_float_types(dtype):
+    """The reference's tables are f32 or f64 (kraken/t/math.cc); here the shards always hold float32
+    and values are converted where they leave or enter the engine."""
+    start()
+    try:
+        ts = kk.register_sparse_table("e", 4, dtype, kk.InitializerType.kConstant, {"value": "1"})
+        rows = kk.pull_sparse_table(ts, torch.tensor([[1, 2]]))
+        assert rows.dtype == dtype and rows.shape == (1, 2, 4)
+        kk.push_sparse_table(ts, torch.tensor([1]), torch.ones(1, 4, dtype=dtype))
+        assert torch.equal(kk.pull_sparse_table(ts, torch.tensor([1])), torch.full((1, 4), 0.5, dtype=dtype))
+        td = kk.register_dense_table("w", torch.ones(3, dtype=dtype))
+        kk.push_dense_table(td, torch.ones(3, dtype=dtype))
+        got = kk.pull_dense_table(td)
+        assert got.dtype == dtype and torch.equal(got, torch.full((3,), 0.5, dtype=dtype))
+    finally:
+        kk.stop()
