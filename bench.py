@@ -139,7 +139,9 @@ def run_ours(args):
 
     data = ClickDataset(NUM_FIELDS, NUM_DENSE, VOCAB, 1.1, seed=1000 + rank)
     total = args.warmup + args.steps
-    host = [data.batch(local_batch, pin=True) for _ in range(total)]
+    # at most 64 distinct batches are generated (1.1 GB of pinned ids at batch 65536); longer runs cycle through them
+    distinct = min(total, 64)
+    host = [data.batch(local_batch, pin=True) for _ in range(distinct)]
     h2d_bytes = sum(t.numel() * t.element_size() for t in host[0])
     inv_world = 1.0 / world  # local mean * 1/world summed over ranks = global mean
 
@@ -180,7 +182,7 @@ def run_ours(args):
     # ---------------- device-timed region: inputs staged on the device beforehand
     staged = [tuple(t.to(dev, non_blocking=True) for t in b) for b in host]
     for i in range(args.warmup):
-        step(*staged[i])
+        step(*staged[i % distinct])
     eng.check()
     launches0 = eng.kernel_launches()
     sync_all()
@@ -188,7 +190,7 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.warmup, total):
-        step(*staged[i])
+        step(*staged[i % distinct])
     e1.record()
     sync_all()
     dev_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -198,7 +200,7 @@ def run_ours(args):
     eng.check()
 
     # ---------------- end-to-end region: pinned host inputs in, loss out, every step
-    for batch in DevicePrefetcher((host[i] for i in range(min(3, args.warmup))), dev):
+    for batch in DevicePrefetcher((host[i % distinct] for i in range(min(3, args.warmup))), dev):
         step(*batch).item()
     sync_all()
     t0 = time.perf_counter()
@@ -207,7 +209,7 @@ def run_ours(args):
     # batch i+1 crosses PCIe on a copy stream while batch i trains; every copy is inside the timed region
     # and the loss of step i is read back after step i+1 has been enqueued, so the device does not wait for the host
     pending = None
-    loader = (host[i] for i in range(args.warmup, total))
+    loader = (host[i % distinct] for i in range(args.warmup, total))
     if args.no_graph:
         for batch in DevicePrefetcher(loader, dev):
             last = step(*batch).item()
@@ -239,7 +241,7 @@ def run_ours(args):
                        "seq_len": NUM_FIELDS, "parallelism": f"dp{world}+row-sharded-tables{world}",
                        "launch": "eager" if args.no_graph else "cuda-graph replay of the whole step",
                        "l2": "working set (hash-table rows touched per step + slabs) exceeds the 126 MB L2; "
-                             "a fresh batch every step"},
+                             "a different batch every step (64 distinct batches, cycled)"},
             "clocks": clocks,
             "e2e": {"value": args.global_batch * args.steps / (e2e_ms / 1e3), "unit": "samples/s",
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
