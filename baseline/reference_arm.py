@@ -36,7 +36,7 @@ def run(args) -> None:
             "impl": "reference",
             "unavailable": "reference does not build offline: cmake FetchContent git-clones Eigen/libzmq/snappy/"
                            "pybind11/gflags/googletest/configor/libcuckoo/parallel_hashmap from github.com "
-                           "(pip install of /root/reference fails at the Eigen clone, no network)",
+                           "(the offline pip install of the reference source fails at the Eigen clone: no network)",
         }), flush=True)
         return
     # The reference is CPU-only (every entry point rejects CUDA tensors) and needs a scheduler and
