@@ -50,9 +50,33 @@ def main():
     ms = timer.stop_ms()
     kk.native.engine().check()
     n_params = sum(p.numel() for p in model.parameters())
-    emit({"benchmark": "dense_mlp" + ("_dct" if a.dct else ""), "n_gpus": world, "batch_per_gpu": a.batch,
-          "params": n_params, "samples_per_sec": a.batch * world * a.steps / (ms / 1e3), "ms_per_step": ms / a.steps,
-          "final_loss": loss.item() * world})
+    rec = {"benchmark": "dense_mlp" + ("_dct" if a.dct else ""), "n_gpus": world, "batch_per_gpu": a.batch,
+           "params": n_params, "samples_per_sec": a.batch * world * a.steps / (ms / 1e3), "ms_per_step": ms / a.steps,
+           "final_loss": loss.item() * world}
+
+    # the fused dense step alone (reduce-scatter + optimizer + all-gather in one kernel), on whatever the
+    # gradient buffer holds; every rank starts each step together (the timer synchronises and barriers)
+    eng = kk.native.engine()
+    if not a.dct and getattr(eng, "bucket", None) is not None:
+        for _ in range(3):
+            eng.dense_step()
+        step_ms = 0.0
+        for _ in range(10):
+            timer.start()
+            eng.dense_step()
+            step_ms += timer.stop_ms()
+        us = step_ms / 10 * 1e3
+        n_pad = int(eng.bucket.n_pad)
+        # per GPU and direction: (G - 1) / G of the bucket comes in as gradient slices and goes out as weights
+        link = (world - 1) / world * n_pad * 4
+        # HBM: G gradient slices read + zeroed bucket, owned slice of value and momentum read + written,
+        # the whole updated bucket written once by the owners
+        hbm = n_pad * 4 * (1 + 1 + 1) + (n_pad / world) * 4 * 4
+        link_us, hbm_us = link / 770e3, hbm / 6552e3
+        rec.update({"dense_step_us": round(us, 1), "dense_step_nvlink_bound_us": round(link_us, 1),
+                    "dense_step_hbm_bound_us": round(hbm_us, 1),
+                    "dense_step_roofline_fraction": round(max(link_us, hbm_us) / us, 3)})
+    emit(rec)
     kk.stop()
 
 
