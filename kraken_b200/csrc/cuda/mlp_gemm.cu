@@ -1,17 +1,21 @@
-// tcgen05 GEMM kernel behind linear_forward / linear_dgrad / linear_wgrad.
+// tcgen05 GEMM kernels behind linear_forward / linear_dgrad / linear_wgrad.
 //
-// One CTA computes one 128 x BN output tile:
+// All three kernels share one warp-specialised structure per CTA (320 threads):
 //   warp 0 (one lane)  TMA producer: fills a ring of shared-memory stages with 128-byte-swizzled
-//                      A and B tiles of 64 k-elements, one mbarrier per stage counting bytes;
+//                      tiles of 64 k-elements, one mbarrier per stage counting bytes;
 //   warp 1 (one lane)  MMA issuer: four tcgen05.mma (K = 16 each) per stage into a TMEM
 //                      accumulator, tcgen05.commit frees the stage and finally signals the epilogue;
-//   warps 2-5          epilogue: tcgen05.ld the accumulator (one row per thread) and fuse
-//                      bias + ReLU (forward), the ReLU mask (input gradient) or a split-K
-//                      vector red.add into the fp32 gradient buffer (weight gradient).
+//   warps 2-9          epilogue: two warps per TMEM lane quarter, each taking half of the tile's
+//                      columns; tcgen05.ld the accumulator (one row per thread) and fuse bias + ReLU
+//                      (+ a one-bit ReLU mask) in the forward pass, the ReLU mask in the input
+//                      gradient, or a split-K vector red.add into the fp32 gradient buffer.
+// gemm_kernel computes one 128 x BN tile per CTA; gemm_bres_kernel and gemm_pair_kernel are
+// persistent, keep their slice of the weights in shared memory and stream activation tiles past it
+// with two TMEM accumulators (the pair variant runs tcgen05.mma.cta_group::2 on two CTAs).
 // Operands are K-major except in the weight gradient, which contracts over the batch and
 // therefore reads both activations MN-major, as they sit in memory.
 // Every mbarrier wait is bounded; on a give-up the CTA records kTimeout, lets its outstanding
-// TMA copies land, frees its tensor memory and returns.
+// TMA copies land, frees its tensor memory and returns.  No TMA load uses cluster multicast.
 #include <cuda_bf16.h>
 
 #include <mutex>
