@@ -252,7 +252,10 @@ void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, 
                 OptimPOD optim, const float* lr, float grad_scale, int use_coo, uint32_t spin_limit,
                 cudaStream_t stream) {
   const long long slice = n_pad / sym.world;
-  const int grid = grid_for(slice / 4, 148 * 8);  // small models: one float4 per thread, no serial loop
+  // Every block waits (bounded) for flags that peers raise only after ALL their blocks have passed the
+  // update phase, so on more than one GPU the whole grid must be resident at once: two blocks per SM.
+  // A single GPU has no such wait and takes one float4 per thread for small models.
+  const int grid = grid_for(slice / 4, sym.world > 1 ? 148 * 2 : 148 * 8);
   const Sym s = to_sym(sym);
   if (use_coo) dense_gather_coo_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, slice, acc, spin_limit);
   dense_step_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps,
