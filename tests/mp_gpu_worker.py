@@ -25,6 +25,10 @@ ts = kk.register_sparse_table("e", DIM, torch.float32, kk.InitializerType.kNorma
 t1 = kk.register_sparse_table("e1", 1, torch.float32, kk.InitializerType.kConstant, {"value": "0.5"})
 td = kk.register_dense_table("w", torch.linspace(-1, 1, 700).view(70, 10))
 td2 = kk.register_dense_table("b", torch.ones(5))
+# large enough that the fused dense step needs more blocks than fit on the GPU at once: its grid must
+# stay resident (blocks wait for a flag raised after every block has finished), so it loops instead
+BIG = (1200, 1024)
+td3 = kk.register_dense_table("big", torch.full(BIG, 0.25))
 
 torch.manual_seed(0)
 ids_all = torch.randint(0, 200, (STEPS, world * PER))
@@ -39,6 +43,7 @@ shard.create_sparse_table(ts, "e", DIM, kk.InitializerType.kNormal, {"stddev": "
 shard.create_sparse_table(t1, "e1", 1, kk.InitializerType.kConstant, {"value": "0.5"})
 shard.create_dense_table(td, "w", torch.linspace(-1, 1, 700).view(70, 10))
 shard.create_dense_table(td2, "b", torch.ones(5))
+shard.create_dense_table(td3, "big", torch.full(BIG, 0.25))
 
 mine = slice(rank * PER, (rank + 1) * PER)
 for s in range(STEPS):
@@ -53,13 +58,17 @@ for s in range(STEPS):
     kk.push_sparse_table(ts, ids, g_all[s, mine].to(dev))
     kk.push_dense_table(td, gd_all[s, rank].to(dev))
     kk.push_dense_table(td2, gd2_all[s, rank].to(dev))
+    kk.push_dense_table(td3, torch.full(BIG, 0.01 * (rank + 1) * (s + 1), device=dev))
     w, b = kk.combine_pull_dense_table([td, td2])
     assert shard.push_sparse(ts, uniq, C.cpu_segment_sum(g_all[s], inv, uniq.numel()), LR) == 0
     assert shard.push_sparse(t1, uniq, C.cpu_segment_sum(g1_all[s], inv, uniq.numel()), LR) == 0
     shard.push_dense(td, gd_all[s].sum(0), LR)
     shard.push_dense(td2, gd2_all[s].sum(0), LR)
+    shard.push_dense(td3, torch.full(BIG, 0.01 * (s + 1) * world * (world + 1) / 2), LR)
     assert torch.allclose(w.cpu(), shard.pull_dense(td).view(70, 10), atol=1e-5), s
     assert torch.allclose(b.cpu(), shard.pull_dense(td2), atol=1e-5), s
+big = kk.pull_dense_table(td3).cpu()
+assert torch.allclose(big, shard.pull_dense(td3).view(*BIG), atol=1e-5), (big - shard.pull_dense(td3).view(*BIG)).abs().max()
 eng.check()
 probe = torch.arange(200)
 got = kk.pull_sparse_table(ts, probe.to(dev)).cpu()
@@ -108,4 +117,5 @@ if rank == 0:
     assert torch.allclose(cpu.pull_sparse_table(0, probe), got, atol=1e-6)
     assert cpu.shard.sparse_size(0) == 200
     assert torch.allclose(cpu.pull_dense_table(2), w_saved, atol=1e-6)
+    assert torch.allclose(cpu.pull_dense_table(4), big, atol=1e-6)
     print("MULTI_GPU_CHECKPOINT_RESHARD ok")
