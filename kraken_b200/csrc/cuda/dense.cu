@@ -69,7 +69,7 @@ dense_gather_coo_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long sli
   }
 }
 
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 dense_step_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, float* __restrict__ s0,
                   float* __restrict__ s1, float* __restrict__ s2, float* acc, const int* __restrict__ chunk_table,
                   int* table_steps, const uint8_t* __restrict__ table_active, int n_tables, OptimPOD optim,
@@ -253,9 +253,10 @@ void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, 
                 cudaStream_t stream) {
   const long long slice = n_pad / sym.world;
   // Every block waits (bounded) for flags that peers raise only after ALL their blocks have passed the
-  // update phase, so on more than one GPU the whole grid must be resident at once: two blocks per SM.
-  // A single GPU has no such wait and takes one float4 per thread for small models.
-  const int grid = grid_for(slice / 4, sym.world > 1 ? 148 * 2 : 148 * 8);
+  // update phase, so on more than one GPU the whole grid must be resident at once: three blocks per SM,
+  // which the kernel's launch bounds guarantee to fit.  A single GPU has no such wait and takes one
+  // float4 per thread for small models.
+  const int grid = grid_for(slice / 4, sym.world > 1 ? 148 * 3 : 148 * 8);
   const Sym s = to_sym(sym);
   if (use_coo) dense_gather_coo_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, slice, acc, spin_limit);
   dense_step_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps,
