@@ -194,6 +194,45 @@ void CpuShard::PullDense(uint64_t id, float* out) const {
   std::memcpy(out, t.val.data(), t.val.size() * sizeof(float));
 }
 
+namespace {
+
+// One optimizer update over a contiguous span.  The optimizer type is a template constant, so the
+// per-element switch folds away and the loop vectorises; slabs the optimizer does not use point at
+// a scratch block (in pieces of kSpanBlock elements) instead of being tested per element.
+constexpr int64_t kSpanBlock = 256;
+
+template <int TYPE>
+void UpdateSpanT(OptimPOD o, float lr, const float* g, int64_t n, int64_t step, float* w, float* s0, float* s1,
+                 float* s2) {
+  o.type = TYPE;
+  const AdamBias ab = TYPE == 1 ? AdamBiasAt(o, step) : AdamBias{1.f, 1.f};
+  float scratch[3][kSpanBlock];
+  for (int64_t base = 0; base < n; base += kSpanBlock) {
+    const int64_t m = n - base < kSpanBlock ? n - base : kSpanBlock;
+    float* a0 = s0 ? s0 + base : scratch[0];
+    float* a1 = s1 ? s1 + base : scratch[1];
+    float* a2 = s2 ? s2 + base : scratch[2];
+    if (!s0) for (int64_t j = 0; j < m; ++j) a0[j] = 0.f;
+    if (!s1) for (int64_t j = 0; j < m; ++j) a1[j] = 0.f;
+    if (!s2) for (int64_t j = 0; j < m; ++j) a2[j] = 0.f;
+    const float* gg = g + base;
+    float* ww = w + base;
+    for (int64_t j = 0; j < m; ++j) UpdateElem(o, lr, gg[j], step, ab, ww[j], a0[j], a1[j], a2[j]);
+  }
+}
+
+void UpdateSpan(const OptimPOD& o, float lr, const float* g, int64_t n, int64_t step, float* w, float* s0, float* s1,
+                float* s2) {
+  switch (o.type) {
+    case 0: UpdateSpanT<0>(o, lr, g, n, step, w, s0, s1, s2); break;
+    case 1: UpdateSpanT<1>(o, lr, g, n, step, w, s0, s1, s2); break;
+    case 2: UpdateSpanT<2>(o, lr, g, n, step, w, s0, s1, s2); break;
+    default: UpdateSpanT<3>(o, lr, g, n, step, w, s0, s1, s2); break;
+  }
+}
+
+}  // namespace
+
 void CpuShard::UpdateDense(Dense& t, const float* g, float lr) {
   const size_t n = t.val.size();
   for (int k = 0; k < 3; ++k)
@@ -201,14 +240,10 @@ void CpuShard::UpdateDense(Dense& t, const float* g, float lr) {
       t.s[k].assign(n, (optim_.type == 0 && k == 0) ? optim_.initial_accumulator_value : 0.f);
   const int64_t step = ++t.steps;
   t.touched = true;
-  const AdamBias ab = optim_.type == 1 ? AdamBiasAt(optim_, step) : AdamBias{1.f, 1.f};
-  float dummy = 0.f;
   float* s0 = t.s[0].empty() ? nullptr : t.s[0].data();
   float* s1 = t.s[1].empty() ? nullptr : t.s[1].data();
   float* s2 = t.s[2].empty() ? nullptr : t.s[2].data();
-  for (size_t i = 0; i < n; ++i) {
-    UpdateElem(optim_, lr, g[i], step, ab, t.val[i], s0 ? s0[i] : dummy, s1 ? s1[i] : dummy, s2 ? s2[i] : dummy);
-  }
+  UpdateSpan(optim_, lr, g, static_cast<int64_t>(n), step, t.val.data(), s0, s1, s2);
 }
 
 void CpuShard::PushDense(uint64_t id, const float* grad, int64_t n, float lr) {
@@ -264,18 +299,14 @@ void CpuShard::PullSparse(uint64_t id, const uint64_t* ids, int64_t n, float* ou
 int32_t CpuShard::PushSparse(uint64_t id, const uint64_t* ids, int64_t n, const float* grads, float lr) {
   Sparse& t = sparse(id);
   std::lock_guard<std::mutex> g(t.mu);
-  float dummy = 0.f;
   for (int64_t i = 0; i < n; ++i) {
     auto it = t.index.find(ids[i]);
     if (it == t.index.end()) return err::kSparseIdNotExist;
     const int64_t row = it->second;
     const int64_t step = ++t.steps[row];
-    const AdamBias ab = optim_.type == 1 ? AdamBiasAt(optim_, step) : AdamBias{1.f, 1.f};
-    for (int64_t j = 0; j < t.dim; ++j) {
-      const int64_t e = row * t.dim + j;
-      UpdateElem(optim_, lr, grads[i * t.dim + j], step, ab, t.val[e], t.s[0].empty() ? dummy : t.s[0][e],
-                 t.s[1].empty() ? dummy : t.s[1][e], t.s[2].empty() ? dummy : t.s[2][e]);
-    }
+    const int64_t e = row * t.dim;
+    UpdateSpan(optim_, lr, grads + i * t.dim, t.dim, step, t.val.data() + e, t.s[0].empty() ? nullptr : t.s[0].data() + e,
+               t.s[1].empty() ? nullptr : t.s[1].data() + e, t.s[2].empty() ? nullptr : t.s[2].data() + e);
   }
   return err::kSuccess;
 }

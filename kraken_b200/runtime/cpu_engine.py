@@ -92,6 +92,9 @@ class CpuEngine(Engine):
         idx = indices.detach().to("cpu").to(torch.int64).contiguous()
         flat = idx.reshape(-1)
         uniq, inv = C.cpu_dedup(flat)
+        # the push that follows a pull of the same ids (an Embedding's backward) reuses this result
+        self._last_dedup = getattr(self, "_last_dedup", {})
+        self._last_dedup[table_id] = (flat.clone(), uniq, inv)
         if self.world == 1:
             rows = self.shard.pull_sparse(table_id, uniq)
         else:
@@ -114,7 +117,11 @@ class CpuEngine(Engine):
         g = grad.detach().to("cpu", torch.float32).contiguous()
         if g.numel() != idx.numel() * info.dimension:
             raise C.KrakenError("gradient shape must be indices.shape + [dimension]")
-        uniq, inv = C.cpu_dedup(idx)
+        kept = getattr(self, "_last_dedup", {}).pop(table_id, None)
+        if kept is not None and kept[0].numel() == idx.numel() and torch.equal(kept[0], idx):
+            uniq, inv = kept[1], kept[2]
+        else:
+            uniq, inv = C.cpu_dedup(idx)
         summed = C.cpu_segment_sum(g.view(-1, info.dimension), inv, uniq.numel())
         if self.world > 1:
             owner = owner_of(self._salt(table_id), uniq, self.world)
