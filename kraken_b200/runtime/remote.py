@@ -224,6 +224,8 @@ class PsServer:
                         (Rpc.CREATE_DENSE, self.create_dense), (Rpc.CREATE_SPARSE, self.create_sparse),
                         (Rpc.PULL_DENSE, self.pull_dense), (Rpc.PUSH_DENSE, self.push_dense),
                         (Rpc.PULL_SPARSE, self.pull_sparse), (Rpc.PUSH_SPARSE, self.push_sparse),
+                        (Rpc.COMBINE_PULL_DENSE, self.pull_dense), (Rpc.COMBINE_PULL_SPARSE, self.combine_pull_sparse),
+                        (Rpc.COMBINE_PUSH_SPARSE, self.combine_push_sparse),
                         (Rpc.NOTIFY_SAVE, self.notify_save), (Rpc.NOTIFY_LOAD, self.notify_load),
                         (Rpc.NOTIFY_NODE_JOIN, self.notify_node_join), (Rpc.TRANSFER_DENSE, self.transfer_dense),
                         (Rpc.TRANSFER_SPARSE_VALUES, self.transfer_sparse_values),
@@ -372,6 +374,20 @@ class PsServer:
         code = self.shard.push_sparse(meta["table_id"], tensors[0], tensors[1], meta["lr"])
         if code != 0:
             raise RpcError(code)
+        return {}, ()
+
+    def combine_pull_sparse(self, meta, tensors):
+        """Several tables in one round trip (kraken/ps/ps_op.cc CombinePullSparseTable): ids of table k in tensor k."""
+        self._check(meta)
+        return {}, [self.shard.pull_sparse(t, ids) for t, ids in zip(meta["table_ids"], tensors)]
+
+    def combine_push_sparse(self, meta, tensors):
+        """Tensors are (ids, summed gradients) pairs in the order of ``table_ids``."""
+        self._check(meta)
+        for k, t in enumerate(meta["table_ids"]):
+            code = self.shard.push_sparse(t, tensors[2 * k], tensors[2 * k + 1], meta["lr"])
+            if code != 0:
+                raise RpcError(code)
         return {}, ()
 
     def notify_save(self, meta, tensors):
@@ -606,6 +622,81 @@ class RemoteEngine(Engine):
         uniq, inv = C.cpu_dedup(idx)
         summed = C.cpu_segment_sum(g, inv, uniq.numel())
         self._call_sparse(Rpc.PUSH_SPARSE, table_id, {"lr": self.lr}, uniq, summed, lambda pos, ts: None)
+
+    # several tables in one round trip per server (kCombinePull* / kCombinePushSparseTable of the reference)
+    def combine_pull_dense_table(self, table_ids):
+        by_owner: Dict[int, List[int]] = {}
+        for t in table_ids:
+            self._table(t, "dense")
+            by_owner.setdefault(self.router.hit(C.mix64(t)), []).append(t)
+        out: Dict[int, torch.Tensor] = {}
+        for owner, tids in by_owner.items():
+            try:
+                _, ts = self.ps[owner].call(Rpc.COMBINE_PULL_DENSE, {"table_ids": tids, "router_version": self.version})
+                for t, v in zip(tids, ts):
+                    out[t] = v.view(*self.tables[t].shape)
+            except RpcError as e:
+                if e.code not in self.RETRY_CODES:
+                    raise
+                for t in tids:  # refused: table by table, each with its own retries on the refreshed ring
+                    out[t] = self.pull_dense_table(t)
+        return [out[t] for t in table_ids]
+
+    def _combine_sparse(self, rpc: int, meta: dict, table_ids, uniqs, payloads, done) -> None:
+        """One message per server carrying that server's part of every table.  A server that refuses
+        gets its parts again table by table through ``_call_sparse`` (which re-partitions and retries)."""
+        owners = [self._owners(t, u) for t, u in zip(table_ids, uniqs)]
+        nodes = sorted({int(n) for o in owners for n in np.unique(o)})
+        for node in nodes:
+            sels = [torch.from_numpy(np.nonzero(o == node)[0]) for o in owners]
+            ks = [k for k, sel in enumerate(sels) if sel.numel() > 0]
+            tensors = []
+            for k in ks:
+                tensors.append(uniqs[k][sels[k]])
+                if payloads is not None:
+                    tensors.append(payloads[k][sels[k]])
+            try:
+                _, ts = self.ps[node].call(rpc, {**meta, "table_ids": [table_ids[k] for k in ks],
+                                                 "router_version": self.version}, tensors)
+                for j, k in enumerate(ks):
+                    done(k, sels[k], [ts[j]] if ts else [])
+            except RpcError as e:
+                if e.code not in self.RETRY_CODES:
+                    raise
+                self._backoff(0)
+                single = Rpc.PULL_SPARSE if payloads is None else Rpc.PUSH_SPARSE
+                for k in ks:
+                    self._call_sparse(single, table_ids[k], meta, uniqs[k][sels[k]],
+                                      payloads[k][sels[k]] if payloads is not None else None,
+                                      lambda pos, ts, k=k: done(k, sels[k][pos], ts), 1)
+
+    def combine_pull_sparse_table(self, table_ids, indices):
+        if len(table_ids) != len(indices):
+            raise C.KrakenError("table_ids and indices differ in length")
+        infos = [self._table(t, "sparse") for t in table_ids]
+        idxs = [i.detach().to("cpu").to(torch.int64).contiguous() for i in indices]
+        dd = [C.cpu_dedup(i.reshape(-1)) for i in idxs]
+        rows = [torch.empty((u.numel(), info.dimension), dtype=torch.float32) for (u, _), info in zip(dd, infos)]
+
+        def put(k, pos, ts):
+            rows[k][pos] = ts[0]
+
+        self._combine_sparse(Rpc.COMBINE_PULL_SPARSE, {}, list(table_ids), [u for u, _ in dd], None, put)
+        return [r[inv].view(*i.shape, info.dimension) for r, (_, inv), i, info in zip(rows, dd, idxs, infos)]
+
+    def combine_push_sparse_table(self, table_ids, indices, grads):
+        if not (len(table_ids) == len(indices) == len(grads)):
+            raise C.KrakenError("table_ids, indices and grads differ in length")
+        uniqs, sums = [], []
+        for t, i, g in zip(table_ids, indices, grads):
+            info = self._table(t, "sparse")
+            idx = i.detach().to("cpu").to(torch.int64).contiguous().reshape(-1)
+            uniq, inv = C.cpu_dedup(idx)
+            uniqs.append(uniq)
+            sums.append(C.cpu_segment_sum(g.detach().to("cpu", torch.float32).contiguous().view(-1, info.dimension), inv,
+                                          uniq.numel()))
+        self._combine_sparse(Rpc.COMBINE_PUSH_SPARSE, {"lr": self.lr}, list(table_ids), uniqs, sums,
+                             lambda k, pos, ts: None)
 
     # checkpoints are written and read by the servers; the scheduler orchestrates
     def try_save_model(self) -> bool:

@@ -56,7 +56,9 @@ class Rpc:
     COMBINE_PULL_DENSE = 20
     PUSH_DENSE = 21
     PULL_SPARSE = 22
+    COMBINE_PULL_SPARSE = 23
     PUSH_SPARSE = 24
+    COMBINE_PUSH_SPARSE = 25
     TRY_SAVE = 26
     TRY_LOAD = 27
     NOTIFY_SAVE = 28

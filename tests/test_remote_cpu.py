@@ -223,3 +223,43 @@ def test_compressed_bodies_round_trip(tmp_path):
     finally:
         a.close()
         b.close()
+
+
+def test_combined_requests_use_one_round_per_server(tmp_path):
+    """kCombinePullDense / kCombinePullSparse / kCombinePushSparse: several tables per message, same
+    results as the per-table calls."""
+    sched, servers = boot(tmp_path, n_ps=2)
+    try:
+        kk.initialize(f"tcp://127.0.0.1:{sched.port}")
+        kk.init_model("m", kk.OptimType.kSGD, {})
+        kk.update_lr(0.5)
+        tds = [kk.register_dense_table(f"w{i}", torch.full((2, 3), float(i))) for i in range(5)]
+        t_a = kk.register_sparse_table("a", 2, torch.float32, kk.InitializerType.kConstant, {"value": "1.0"})
+        t_b = kk.register_sparse_table("b", 3, torch.float32, kk.InitializerType.kConstant, {"value": "2.0"})
+        calls = {}
+        eng = kk.native.engine()
+        for node, c in eng.ps.items():
+            orig = c.call
+
+            def counted(rpc, meta=None, tensors=(), timeout_ms=None, orig=orig):
+                calls[rpc] = calls.get(rpc, 0) + 1
+                return orig(rpc, meta, tensors, timeout_ms)
+
+            c.call = counted
+        dense = kk.combine_pull_dense_table(tds)
+        assert all(torch.equal(d, torch.full((2, 3), float(i))) for i, d in enumerate(dense))
+        ids_a, ids_b = torch.arange(0, 300).view(3, 100), torch.arange(100, 500)
+        ra, rb = kk.combine_pull_sparse_table([t_a, t_b], [ids_a, ids_b])
+        assert torch.equal(ra, torch.ones(3, 100, 2)) and torch.equal(rb, torch.full((400, 3), 2.0))
+        kk.combine_push_sparse_table([t_a, t_b], [ids_a, ids_b], [torch.ones(3, 100, 2), torch.ones(400, 3)])
+        ra, rb = kk.combine_pull_sparse_table([t_a, t_b], [ids_a, ids_b])
+        assert torch.equal(ra, torch.full((3, 100, 2), 0.5)) and torch.equal(rb, torch.full((400, 3), 1.5))
+        from kraken_b200.runtime.rpc import Rpc
+        assert calls.get(Rpc.COMBINE_PULL_DENSE, 0) <= 2            # one per server that owns a table
+        assert calls.get(Rpc.COMBINE_PULL_SPARSE, 0) <= 4 and calls.get(Rpc.COMBINE_PUSH_SPARSE, 0) <= 2
+        assert Rpc.PULL_SPARSE not in calls and Rpc.PUSH_SPARSE not in calls and Rpc.PULL_DENSE not in calls
+    finally:
+        kk.stop()
+        sched.stop()
+        for s in servers:
+            s.stop()
