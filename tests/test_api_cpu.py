@@ -236,3 +236,53 @@ def test_tables_of_other_float_types(dtype):
         assert got.dtype == dtype and torch.equal(got, torch.full((3,), 0.5, dtype=dtype))
     finally:
         kk.stop()
+
+
+def test_corrupted_or_missing_checkpoint_is_reported(tmp_path):
+    """Fault injection on the host: a truncated .sparse file, a garbage model.binary and an empty
+    directory each end in an error (or a False return), never in a crash."""
+    d = str(tmp_path / "ck")
+    kk.initialize("cpu", saved_dir=d)
+    kk.init_model("m", kk.OptimType.kSGD, {})
+    kk.update_lr(0.1)
+    ts = kk.register_sparse_table("e", 4, torch.float32, kk.InitializerType.kNormal, {})
+    kk.pull_sparse_table(ts, torch.arange(500))
+    assert kk.try_save_model()
+    kk.stop()
+    shard_dir = os.path.join(d, "shard_0")
+    snap = os.path.join(shard_dir, sorted(os.listdir(shard_dir))[-1])
+    sparse_file = os.path.join(snap, "e.sparse")
+    blob = open(sparse_file, "rb").read()
+
+    # 1. truncated rows
+    with open(sparse_file, "wb") as f:
+        f.write(blob[:len(blob) // 2])
+    kk.initialize("cpu")
+    with pytest.raises(Exception):
+        kk.try_load_model_blocked(d)
+    kk.stop()
+
+    # 2. model metadata replaced by garbage
+    with open(sparse_file, "wb") as f:
+        f.write(blob)
+    model_file = os.path.join(snap, "model.binary")
+    good = open(model_file, "rb").read()
+    with open(model_file, "wb") as f:
+        f.write(b"\\xff" * 40)
+    kk.initialize("cpu")
+    with pytest.raises(Exception):
+        kk.try_load_model_blocked(d)
+    kk.stop()
+
+    # 3. nothing there at all
+    kk.initialize("cpu")
+    assert not kk.try_load_model_blocked(str(tmp_path / "empty"))
+    kk.stop()
+
+    # the intact files still load
+    with open(model_file, "wb") as f:
+        f.write(good)
+    kk.initialize("cpu")
+    assert kk.try_load_model_blocked(d)
+    assert kk.native.engine().shard.sparse_size(0) == 500
+    kk.stop()
