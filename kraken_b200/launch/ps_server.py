@@ -6,6 +6,7 @@ the reference's ps_server binary (kraken/executable/ps_server_main.cc:5-10);
 """
 import argparse
 import logging
+import os
 import threading
 
 from ..runtime.remote import PsServer
@@ -20,7 +21,8 @@ def main(argv=None):
     p.add_argument("--saved_dir", default="")
     p.add_argument("--max_save_count", type=int, default=3)
     a = p.parse_args(argv)
-    logging.basicConfig(level=logging.INFO)
+    from kraken_b200.utils.log import configure
+    configure(os.environ.get("KRAKEN_LOG_LEVEL", "info"))
     s = PsServer(a.port, a.addr or f"127.0.0.1:{a.port}", a.s_addr, a.saved_dir, a.max_save_count)
     s.start()
     threading.Event().wait()

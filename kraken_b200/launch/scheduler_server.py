@@ -6,6 +6,7 @@ scheduler_server binary (kraken/executable/scheduler_server_main.cc:5).
 """
 import argparse
 import logging
+import os
 import threading
 
 from ..runtime.remote import SchedulerServer
@@ -15,7 +16,8 @@ def main(argv=None):
     p = argparse.ArgumentParser()
     p.add_argument("--port", type=int, default=50000)
     a = p.parse_args(argv)
-    logging.basicConfig(level=logging.INFO)
+    from kraken_b200.utils.log import configure
+    configure(os.environ.get("KRAKEN_LOG_LEVEL", "info"))
     s = SchedulerServer(a.port)
     s.start()
     logging.getLogger("kraken_b200").info("scheduler listening on port %d", s.port)

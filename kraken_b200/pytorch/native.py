@@ -60,6 +60,8 @@ def initialize(s_addr: str = "auto", emitter_type=EmitterType.kDefault, life_spa
     global _engine, _owns_process_group
     if _engine is not None:
         return
+    from ..utils.log import configure as _configure_logging
+    _configure_logging()
     backend = options.pop("backend", None)
     if backend is None:
         head = (s_addr or "auto").split("://")[0].lower()
