@@ -8,6 +8,7 @@ here synchronises the host: errors are collected from device status words by
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -41,6 +42,7 @@ class GpuEngine(Engine):
         self._bound = False
         self._steps = 0
         self.profiler = _profiler.from_env(rank)
+        self._nvtx = os.environ.get("KRAKEN_NVTX", "") == "1"
         self.nccl = cfg.exchange == "nccl" and world > 1
         self.nccl_channels: Dict[int, NcclSparseChannel] = {}
         from ..ops import mlp as fused_mlp
@@ -154,8 +156,14 @@ class GpuEngine(Engine):
         self._pushed.clear()
 
     def _region(self, name: str):
+        """Phase bracket: CUDA-event timing when KRAKEN_PROFILE is set, an NVTX range when KRAKEN_NVTX=1
+        (for timeline tools), nothing otherwise."""
         import contextlib
-        return self.profiler.region(name) if self.profiler is not None else contextlib.nullcontext()
+        if self.profiler is not None:
+            return self.profiler.region(name)
+        if self._nvtx:
+            return torch.cuda.nvtx.range(f"kraken.{name}")
+        return contextlib.nullcontext()
 
     def metrics(self) -> dict:
         """Counters of the shards (synchronises): rows and load factor per sparse table and, where
