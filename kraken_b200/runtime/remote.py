@@ -106,9 +106,26 @@ class SchedulerServer:
             # every older server ships what the new ring takes from it, then adopts the ring
             note = {**rm, "new_node": node_id, "new_addr": meta["addr"], "tables": list(self.tables.values())}
             moved = 0
-            for nid, c in old_clients.items():
-                out, _ = c.call(Rpc.NOTIFY_NODE_JOIN, note, timeout_ms=600_000)
-                moved += int(out.get("rows_moved", 0))
+            notified = []
+            try:
+                for nid, c in old_clients.items():
+                    out, _ = c.call(Rpc.NOTIFY_NODE_JOIN, note, timeout_ms=600_000)
+                    notified.append(nid)
+                    moved += int(out.get("rows_moved", 0))
+            except Exception:
+                # A transfer failed: the newcomer is taken out of the ring again.  Servers that had already
+                # moved rows keep the new ring and the scheduler's version moves on, so workers refetch; the
+                # rows they shipped stay on the newcomer, which has to be restarted to join again.
+                log.error("join of node %d failed after %d of %d servers had transferred", node_id, len(notified),
+                          len(old_clients))
+                if not notified:
+                    self.router.remove(node_id)
+                    self.nodes.pop(node_id, None)
+                    self.clients.pop(node_id).close()
+                    back = self._router_meta()
+                    for c in old_clients.values():
+                        c.call(Rpc.FETCH_ROUTER, back)
+                raise
             if old_clients:
                 new.call(Rpc.NOTIFY_FINISH_TRANSFER, {"rows_moved": moved})
                 log.info("node %d joined: %d rows moved to it", node_id, moved)

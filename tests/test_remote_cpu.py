@@ -263,3 +263,39 @@ def test_combined_requests_use_one_round_per_server(tmp_path):
         sched.stop()
         for s in servers:
             s.stop()
+
+
+def test_failed_join_is_rolled_back(tmp_path):
+    """Host-side fault injection: the only older server fails its transfer.  The newcomer is refused,
+    the ring goes back to what it was and the worker keeps training on the old server."""
+    import pytest
+
+    from kraken_b200.runtime.rpc import Rpc, RpcError
+
+    sched, servers = boot(tmp_path, n_ps=1)
+    late = None
+    try:
+        kk.initialize(f"tcp://127.0.0.1:{sched.port}")
+        kk.init_model("m", kk.OptimType.kSGD, {})
+        kk.update_lr(1.0)
+        ts = kk.register_sparse_table("e", 2, torch.float32, kk.InitializerType.kConstant, {"value": "1.0"})
+        ids = torch.arange(200)
+        kk.pull_sparse_table(ts, ids)
+
+        def broken(meta, tensors):
+            raise RpcError(-1, "injected transfer failure")
+
+        servers[0].station.handlers[Rpc.NOTIFY_NODE_JOIN] = broken
+        late = PsServer(0, "", f"127.0.0.1:{sched.port}", saved_dir=str(tmp_path), seed=5)
+        late.addr = f"127.0.0.1:{late.port}"
+        with pytest.raises(RpcError):
+            late.start()
+        assert list(sched.nodes) == [0] and not sched.router.contains(1)
+        kk.push_sparse_table(ts, ids, torch.ones(200, 2))
+        assert torch.equal(kk.pull_sparse_table(ts, ids), torch.zeros(200, 2))
+        assert servers[0].shard.sparse_size(ts) == 200
+    finally:
+        kk.stop()
+        sched.stop()
+        for s in servers + ([late] if late is not None else []):
+            s.stop()
