@@ -31,6 +31,8 @@ def _find_native() -> bool:
 
 
 def run(args) -> None:
+    if int(os.environ.get("RANK", "0")) != 0:
+        return  # launched once per GPU: one line for the whole job
     if not _find_native():
         print(json.dumps({
             "impl": "reference",
