@@ -35,7 +35,8 @@ METRIC = "deepfm_train_samples_per_sec"
 def parse():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--steps", type=int, default=None,
+                   help="timed steps (default: 200 for this framework, 20 for the CPU-bound reference arm)")
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
@@ -258,6 +259,8 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse()
+    if a.steps is None:
+        a.steps = 20 if a.impl == "reference" else 200
     if a.impl == "reference":
         run_reference(a)
     else:
