@@ -47,6 +47,13 @@ T* optr(const c10::optional<torch::Tensor>& t) {
   return t.has_value() ? ptr<T>(*t) : nullptr;
 }
 
+// The channel control block (cuda/kernels.h: Ctrl) lives in an int32 CUDA tensor of at least kCtrlInts elements.
+cu::Ctrl* ctrl_ptr(const torch::Tensor& t) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kInt32 && t.numel() >= cu::kCtrlInts,
+              "ctrl must be a contiguous int32 CUDA tensor of at least ", cu::kCtrlInts, " elements");
+  return reinterpret_cast<cu::Ctrl*>(t.data_ptr());
+}
+
 void need_cuda(const torch::Tensor& t, const char* name, c10::ScalarType st) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
@@ -308,6 +315,7 @@ void bind_dense(py::module_& m);  // bindings_dense.cc
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::register_exception<KrakenError>(m, "KrakenError");
+  m.attr("CTRL_INTS") = cu::kCtrlInts;
 
   py::enum_<OptimType>(m, "OptimType")
       .value("kAdagrad", OptimType::kAdagrad)
@@ -802,7 +810,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       // with a channel: the dedup's second kernel also dispatches the unique ids to their owners
       cu::dedup_bucketize_dispatch(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off),
                                    ptr<int64_t>(uniq), ptr<int>(inv), cap_u, ptr<int>(status), heap->View(), *lay,
-                                   reinterpret_cast<cu::Ctrl*>(ctrl->data_ptr()), cur_stream());
+                                   ctrl_ptr(*ctrl), cur_stream());
     } else {
       cu::dedup_bucketize(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),
                           ptr<int>(inv), cap_u, ptr<int>(status), cur_stream());
@@ -813,19 +821,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
      py::arg("ctrl") = py::none());
   m.def("pull_dispatch", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
                             const torch::Tensor& uniq, const torch::Tensor& off, int max_n) {
-    cu::pull_dispatch(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), ptr<int64_t>(uniq), ptr<int>(off),
+    cu::pull_dispatch(h.View(), lay, ctrl_ptr(ctrl), ptr<int64_t>(uniq), ptr<int>(off),
                       max_n, cur_stream());
     check_launch("pull_dispatch");
   });
   m.def("pull_probe", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
                          const cu::TableHost& table, const torch::Tensor& slot_cache, bool insert, uint32_t spin) {
-    cu::pull_probe(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), table, ptr<int>(slot_cache), insert,
+    cu::pull_probe(h.View(), lay, ctrl_ptr(ctrl), table, ptr<int>(slot_cache), insert,
                    spin, cur_stream());
     check_launch("pull_probe");
   });
   m.def("pull_gather", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
                           const cu::TableHost& table, const torch::Tensor& slot_cache) {
-    cu::pull_gather(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), table, ptr<int>(slot_cache),
+    cu::pull_gather(h.View(), lay, ctrl_ptr(ctrl), table, ptr<int>(slot_cache),
                     cur_stream());
     check_launch("pull_gather");
   });
@@ -837,7 +845,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           const int k = bag_offsets.has_value() ? static_cast<int>(bag_offsets->numel()) - 1 : 0;
           need_cuda(out, "out", torch::kFloat32);
           TORCH_CHECK(out.numel() == static_cast<int64_t>(bag_offsets.has_value() ? k : n) * dim, "out has the wrong size");
-          cu::pull_combine(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), ptr<int>(inv), n, dim,
+          cu::pull_combine(h.View(), lay, ctrl_ptr(ctrl), ptr<int>(inv), n, dim,
                            optr<int64_t>(bag_offsets), k, optr<float>(weights), mean, optr<uint8_t>(bag_mean),
                            patch_value, ptr<float>(out), spin, cur_stream());
           check_launch("pull_combine");
@@ -856,7 +864,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         });
   m.def("push_dispatch", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
                             const torch::Tensor& ugrad, const torch::Tensor& off, int max_n, int dim) {
-    cu::push_dispatch(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), ptr<float>(ugrad), ptr<int>(off),
+    cu::push_dispatch(h.View(), lay, ctrl_ptr(ctrl), ptr<float>(ugrad), ptr<int>(off),
                       max_n, dim, cur_stream());
     check_launch("push_dispatch");
   });
@@ -864,14 +872,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                          const cu::TableHost& table, const torch::Tensor& slot_cache, const OptimPOD& optim,
                          const torch::Tensor& lr, uint32_t spin) {
     need_cuda(lr, "lr", torch::kFloat32);
-    cu::push_apply(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), table, ptr<int>(slot_cache), optim,
+    cu::push_apply(h.View(), lay, ctrl_ptr(ctrl), table, ptr<int>(slot_cache), optim,
                    ptr<float>(lr), spin, cur_stream());
     check_launch("push_apply");
   });
 
   // ---------------- fused DeepFM front end
   m.def("pull_wait", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl, uint32_t spin) {
-    cu::pull_wait(h.View(), lay, reinterpret_cast<cu::Ctrl*>(ctrl.data_ptr()), spin, cur_stream());
+    cu::pull_wait(h.View(), lay, ctrl_ptr(ctrl), spin, cur_stream());
     check_launch("pull_wait");
   });
   m.def("deepfm_pack_forward",

@@ -45,6 +45,7 @@ void bind_dense(py::module_& m) {
       .def_readwrite("coo_idx", &cu::DenseLayout::coo_idx)
       .def_readwrite("coo_val", &cu::DenseLayout::coo_val);
   m.attr("DENSE_CHUNK") = cu::kDenseChunk;
+  m.attr("DENSE_CTRL_INTS") = cu::kDenseCtrlInts;
 
   m.def("dense_step",
         [](const std::vector<uintptr_t>& bases, int rank, const cu::DenseLayout& lay, const torch::Tensor& ctrl,
@@ -56,6 +57,8 @@ void bind_dense(py::module_& m) {
                       "n_pad must be a multiple of world * 256");
           TORCH_CHECK(chunk_table.numel() == n_pad / cu::kDenseChunk, "chunk_table has the wrong size");
           TORCH_CHECK(!use_coo || optr<float>(acc) != nullptr, "COO mode needs the accumulator");
+          TORCH_CHECK(ctrl.is_cuda() && ctrl.scalar_type() == torch::kInt32 && ctrl.numel() >= cu::kDenseCtrlInts,
+                      "ctrl must be an int32 CUDA tensor of at least ", cu::kDenseCtrlInts, " elements");
           cu::dense_step(sym_from(bases, rank), lay, reinterpret_cast<cu::DenseCtrl*>(ctrl.data_ptr()), n_pad,
                          optr<float>(s0), optr<float>(s1), optr<float>(s2), optr<float>(acc),
                          chunk_table.data_ptr<int>(), table_steps.data_ptr<int>(), table_active.data_ptr<uint8_t>(),

@@ -25,14 +25,6 @@ namespace {
 
 constexpr int kThreads = 256;
 
-// One-block kernel that only waits for the owners' answers of the current pull.
-__global__ void pull_wait_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit) {
-  if (sym.world <= 1) return;
-  if (threadIdx.x < sym.world &&
-      !wait_flag(sym.at<uint32_t>(sym.rank, lay.flag_rsp) + threadIdx.x, ctrl->pull_epoch, spin_limit))
-    set_status(&ctrl->status, err::kTimeout);
-}
-
 // Row index of unique entry `u`: the entry itself when the rows were gathered into a receive
 // buffer, or the table slot the owner resolved for it when the kernel reads the table in place
 // (single-GPU jobs: no copy of the rows is made).  A failed lookup (slot < 0) reads row 0; the
@@ -171,10 +163,6 @@ int grid_for(long long rows, int lpr) {
 }
 
 }  // namespace
-
-void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cudaStream_t stream) {
-  pull_wait_kernel<<<1, 32, 0, stream>>>(to_sym(sym), lay, ctrl, spin_limit);
-}
 
 void deepfm_pack_forward(const float* rows2, const int* inv2, const int* slots2, const float* rows1, const int* inv1,
                          const int* slots1, const float* dense, int B, int F, int D, int RD, int ND, __nv_bfloat16* x,

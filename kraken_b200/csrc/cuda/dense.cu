@@ -5,14 +5,18 @@
 // (kraken/worker/emitter.cc:377-447, kraken/ps/dense_table.cc:31-43,
 // kraken/pytorch/optimizer.py:151-173):
 //
-//   1. raise "my gradient is complete" on every peer (release store);
-//   2. wait (bounded) for the same flag from every rank;
-//   3. for the slice this rank owns: sum the slice of every rank's gradient
-//      buffer directly out of peer memory (reduce-scatter by loads), run the
-//      optimizer on value + slice-local state, store the new values into every
-//      rank's parameter copy (all-gather by stores);
-//   4. raise "slice done" on every peer, wait for all owners, then zero the
-//      local gradient buffer for the next backward.
+//   1. one warp raises "my gradient is complete" on every peer (release store) and
+//      waits (bounded) for the same flag from every rank;
+//   2. the update grid, for the slice this rank owns: sums the slice of every
+//      rank's gradient buffer directly out of peer memory (reduce-scatter by
+//      loads), runs the optimizer on value + slice-local state, stores the new
+//      values into every rank's parameter copy (all-gather by stores); its last
+//      block raises "slice done" on every peer;
+//   3. one warp waits for "slice done" of all owners, after which a grid zeroes
+//      the local gradient buffer for the next backward.
+// The waits are separate one-warp launches so that no block of a large grid
+// spins while holding registers another stream's kernels need; on a single GPU
+// the call is the update grid alone.
 //
 // With DCT the gradients do not travel dense: dct_compact turns the local
 // f = g + e into per-owner (index, value) lists and the owner scatter-adds the
@@ -36,25 +40,40 @@ Sym to_sym(const SymHost& h) {
   return s;
 }
 
-__device__ __forceinline__ bool wait_all(const uint32_t* flags, int world, uint32_t want, uint32_t limit) {
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  if (threadIdx.x < world && !wait_flag(flags + threadIdx.x, want, limit)) ok = 0;
-  __syncthreads();
-  return ok != 0;
+// phase 0: announce this rank's gradient and wait for every rank's; phase 1: wait until every owner
+// has written its slice.  One warp, lane p polls peer p.
+__global__ void dense_rendezvous_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, int phase, uint32_t spin_limit) {
+  const int p = threadIdx.x;
+  const uint32_t epoch = phase == 0 ? ctrl->epoch + 1 : ctrl->epoch;
+  bool ok = true;
+  if (p < sym.world) {
+    if (phase == 0) st_release_sys(sym.at<uint32_t>(p, lay.flag_grad) + sym.rank, epoch);
+    ok = wait_flag(sym.at<uint32_t>(sym.rank, phase == 0 ? lay.flag_grad : lay.flag_done) + p, epoch, spin_limit);
+  }
+  const bool all_ok = __all_sync(0xffffffffu, ok);
+  if (p == 0) {
+    if (!all_ok) {
+      set_status(&ctrl->status, err::kTimeout);
+      ctrl->abort = 1;
+    } else if (phase == 0) {
+      ctrl->abort = 0;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dense_zero_kernel(Sym sym, DenseLayout lay, long long n_pad, int use_coo) {
+  const long long gtid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long gsize = static_cast<long long>(gridDim.x) * blockDim.x;
+  float4* gz = reinterpret_cast<float4*>(sym.at<float>(sym.rank, lay.grad));
+  for (long long q = gtid; q * 4 < n_pad; q += gsize) gz[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (use_coo && gtid < sym.world) sym.at<int>(sym.rank, lay.coo_cnt)[gtid] = 0;
 }
 
 // Owner side of the DCT exchange: scatter-add every rank's list into acc[slice].
 __global__ void __launch_bounds__(kThreads)
-dense_gather_coo_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long slice, float* acc, uint32_t spin_limit) {
-  const uint32_t epoch = ctrl->epoch + 1;
-  if (blockIdx.x == 0 && threadIdx.x < sym.world)
-    st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_grad) + sym.rank, epoch);
-  if (sym.world > 1 && !wait_all(sym.at<uint32_t>(sym.rank, lay.flag_grad), sym.world, epoch, spin_limit)) {
-    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
-    return;
-  }
+dense_gather_coo_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long slice, float* acc) {
+  if (ctrl->abort) return;
   const long long gtid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long gsize = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int k = 0; k < sym.world; ++k) {
@@ -73,24 +92,16 @@ __global__ void __launch_bounds__(kThreads, 3)
 dense_step_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, float* __restrict__ s0,
                   float* __restrict__ s1, float* __restrict__ s2, float* acc, const int* __restrict__ chunk_table,
                   int* table_steps, const uint8_t* __restrict__ table_active, int n_tables, OptimPOD optim,
-                  const float* __restrict__ lr_ptr, float grad_scale, int use_coo, uint32_t spin_limit) {
+                  const float* __restrict__ lr_ptr, float grad_scale, int use_coo) {
   const uint32_t epoch = ctrl->epoch + 1;
   const long long slice = n_pad / sym.world;
   const long long base = slice * sym.rank;
   const float lr = *lr_ptr;
-
-  if (!use_coo) {
-    if (blockIdx.x == 0 && threadIdx.x < sym.world)
-      st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_grad) + sym.rank, epoch);
-    if (sym.world > 1 && !wait_all(sym.at<uint32_t>(sym.rank, lay.flag_grad), sym.world, epoch, spin_limit)) {
-      if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
-      return;
-    }
-  }
+  const bool aborted = ctrl->abort != 0;  // a peer's gradient never arrived: change nothing, keep the flags moving
 
   const long long gtid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const long long gsize = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long q = gtid; q * 4 < slice; q += gsize) {
+  for (long long q = gtid; q * 4 < slice && !aborted; q += gsize) {
     const long long li = q * 4;      // offset inside the slice
     const long long gi = base + li;  // offset inside the flat buffer
     const int t = chunk_table[gi / kDenseChunk];
@@ -132,15 +143,12 @@ dense_step_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, fl
 
   if (last_block_done(&ctrl->done[0])) {
     if (threadIdx.x < sym.world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_done) + sym.rank, epoch);
-    for (int t = threadIdx.x; t < n_tables; t += blockDim.x)
+    for (int t = threadIdx.x; t < n_tables && !aborted; t += blockDim.x)
       if (table_active[t]) table_steps[t] += 1;
     if (threadIdx.x == 0) ctrl->epoch = epoch;
   }
-  // Every owner has finished reading this rank's gradient once its flag_done is up.
-  if (sym.world > 1 && !wait_all(sym.at<uint32_t>(sym.rank, lay.flag_done), sym.world, epoch, spin_limit)) {
-    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
-    return;
-  }
+  if (sym.world > 1) return;  // other ranks still read this rank's gradient: zeroed by a later launch
+  // single GPU: every thread zeroes exactly the elements it has just consumed
   float4* gz = reinterpret_cast<float4*>(sym.at<float>(sym.rank, lay.grad));
   for (long long q = gtid; q * 4 < n_pad; q += gsize) gz[q] = make_float4(0.f, 0.f, 0.f, 0.f);
   if (use_coo && gtid < sym.world) sym.at<int>(sym.rank, lay.coo_cnt)[gtid] = 0;
@@ -252,15 +260,17 @@ void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, 
                 OptimPOD optim, const float* lr, float grad_scale, int use_coo, uint32_t spin_limit,
                 cudaStream_t stream) {
   const long long slice = n_pad / sym.world;
-  // Every block waits (bounded) for flags that peers raise only after ALL their blocks have passed the
-  // update phase, so on more than one GPU the whole grid must be resident at once: three blocks per SM,
-  // which the kernel's launch bounds guarantee to fit.  A single GPU has no such wait and takes one
-  // float4 per thread for small models.
-  const int grid = grid_for(slice / 4, sym.world > 1 ? 148 * 3 : 148 * 8);
+  const int grid = grid_for(slice / 4, 148 * 8);
   const Sym s = to_sym(sym);
-  if (use_coo) dense_gather_coo_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, slice, acc, spin_limit);
+  const bool multi = sym.world > 1;
+  if (multi) dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 0, spin_limit);
+  if (use_coo) dense_gather_coo_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, slice, acc);
   dense_step_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps,
-                                                   table_active, n_tables, optim, lr, grad_scale, use_coo, spin_limit);
+                                                   table_active, n_tables, optim, lr, grad_scale, use_coo);
+  if (multi) {
+    dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 1, spin_limit);
+    dense_zero_kernel<<<grid_for(n_pad / 4, 148 * 8), kThreads, 0, stream>>>(s, lay, n_pad, use_coo);
+  }
 }
 
 void dct_accumulate(float* grad, const float* residual, long long n, cudaStream_t stream) {

@@ -31,7 +31,10 @@ struct DenseCtrl {
   uint32_t epoch;
   uint32_t done[2];
   int status;
+  int abort;  // raised by a rendezvous that ran out of polls: the step then changes no parameter
+  int pad[3];
 };
+constexpr int kDenseCtrlInts = static_cast<int>(sizeof(DenseCtrl) / sizeof(int));
 
 // One optimizer step over all dense tables, all ranks together:
 //   owner(slice) sums every rank's gradient slice straight out of peer memory,
@@ -40,7 +43,10 @@ struct DenseCtrl {
 // chunk_table[n_pad / 256] maps a chunk to its table; table_active[t] == 0
 // leaves table t untouched; table_steps[t] is bumped for active tables.
 // use_coo != 0: gradients arrive as the (idx, val) lists written by dct_compact.
-// The local gradient buffer is zero again when the kernel ends.
+// The local gradient buffer is zero again when the call's last kernel ends.
+// Between GPUs the call is a short sequence in stream order - a one-warp rendezvous ("my gradient is
+// complete" to every peer, wait for theirs), the update grid, a one-warp wait for every owner's
+// "slice written", the zeroing grid - so that no block of a large grid ever spins on a peer.
 void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, float* s0, float* s1, float* s2,
                 float* acc, const int* chunk_table, int* table_steps, const uint8_t* table_active, int n_tables,
                 OptimPOD optim, const float* lr, float grad_scale, int use_coo, uint32_t spin_limit,

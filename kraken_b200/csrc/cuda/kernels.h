@@ -38,13 +38,20 @@ struct ChanLayout {
 };
 
 // Per-channel device control block (local memory, not peer-mapped).
+// `snap` is this rank's private copy of {count, base} of every source for the exchange in flight:
+// peers overwrite inbox_meta as soon as THEY start their next lookup, which can be while this rank's
+// push kernels of the previous exchange still run, so every owner-side kernel reads the copy.
+// `abort` is raised by a wait that ran out of polls; the kernels of that exchange then move no data.
 struct Ctrl {
   uint32_t pull_epoch;
   uint32_t push_epoch;
   uint32_t done[2];
   int status;
-  int pad[3];
+  int abort;
+  int pad[2];
+  int2 snap[kMaxWorldHost];
 };
+constexpr int kCtrlInts = static_cast<int>(sizeof(Ctrl) / sizeof(int));
 
 struct TableHost {
   void* keys;
@@ -83,6 +90,10 @@ void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, uint64_t sal
                               cudaStream_t stream);
 
 // ---- sparse pull ----
+// Cross-GPU waits never run inside the big grids: each is a one-warp kernel in stream order
+// (exchange_wait), so a block that spins never holds registers or shared memory that a producer on
+// another stream of the same GPU could need.  pull_probe, pull_combine / pull_wait and push_apply
+// launch the wait they depend on themselves when world > 1.
 void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq, const int* off, int max_n,
                    cudaStream_t stream);
 void pull_probe(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, int* slot_cache, bool insert,

@@ -22,6 +22,13 @@
 // per-channel epoch; every wait is bounded (common.cuh: wait_flag) and ends in
 // a status code instead of a hang.  Peer memory is only touched with plain
 // loads / stores / release stores, never with TMA.
+//
+// Waiting is done by exchange_wait_kernel, ONE warp launched in stream order ahead of the grid that
+// needs the data: the request wait (before pull_probe) also copies the peer-writable
+// {count, base} words into the channel's control block, which is what every later owner-side
+// kernel of the exchange reads - a peer may already be writing the next exchange's words while this
+// rank still applies the previous push.  No block of a large grid ever spins, so two streams of
+// one GPU cannot starve each other's producers.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -114,24 +121,34 @@ struct Vec<1> {
   static __device__ __forceinline__ T scale(T a, float w) { return a * w; }
 };
 
-// One thread of the block polls each of the `world` flags; the block learns
-// whether all arrived.
-__device__ __forceinline__ bool block_wait_all(const uint32_t* flags, int world, uint32_t want, uint32_t limit) {
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  if (threadIdx.x < world && !wait_flag(flags + threadIdx.x, want, limit)) ok = 0;
-  __syncthreads();
-  return ok != 0;
+// The channel's three rendezvous points.  One warp; lane s polls source s.
+//   kWaitRequest   owner: every source's ids of the current pull have arrived; snapshots their counts
+//   kWaitResponse  requester: every owner has written the rows of the current pull
+//   kWaitPush      owner: every source's gradient rows of the current push have arrived
+// A wait that runs out of polls records kTimeout and raises `abort`; the request wait of the next
+// exchange lowers it again.
+enum WaitKind { kWaitRequest = 0, kWaitResponse = 1, kWaitPush = 2 };
+
+__global__ void exchange_wait_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, int kind, uint32_t spin_limit) {
+  const int s = threadIdx.x;
+  const size_t flag_off = kind == kWaitRequest ? lay.flag_req : kind == kWaitResponse ? lay.flag_rsp : lay.flag_push;
+  const uint32_t want = kind == kWaitPush ? ctrl->push_epoch : ctrl->pull_epoch;
+  bool ok = true;
+  if (s < sym.world) ok = wait_flag(sym.at<uint32_t>(sym.rank, flag_off) + s, want, spin_limit);
+  const bool all_ok = __all_sync(0xffffffffu, ok);
+  if (kind == kWaitRequest && all_ok && s < sym.world) ctrl->snap[s] = __ldcg(sym.at<int2>(sym.rank, lay.inbox_meta) + s);
+  if (s == 0) {
+    if (!all_ok) {
+      set_status(&ctrl->status, err::kTimeout);
+      ctrl->abort = 1;
+    } else if (kind == kWaitRequest) {
+      ctrl->abort = 0;
+    }
+  }
 }
 
-__device__ __forceinline__ bool block_wait_one(const uint32_t* flag, uint32_t want, uint32_t limit) {
-  __shared__ int ok1;
-  if (threadIdx.x == 0) ok1 = wait_flag(flag, want, limit) ? 1 : 0;
-  __syncthreads();
-  const bool r = ok1 != 0;
-  __syncthreads();
-  return r;
+void launch_wait(const Sym& s, const ChanLayout& lay, Ctrl* ctrl, int kind, uint32_t spin_limit, cudaStream_t stream) {
+  if (s.world > 1) exchange_wait_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, kind, spin_limit);
 }
 
 // ------------------------------------------------------------------ dedup
@@ -220,7 +237,9 @@ dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_
   if (DISPATCH && blockIdx.x == 0 && threadIdx.x < world) {
     const int o = threadIdx.x;
     const int lo = min(s_off[o], cap_u), hi = min(s_off[o + 1], cap_u);
-    sym.at<int2>(o, lay.inbox_meta)[sym.rank] = make_int2(min(hi - lo, lay.capS), lo);
+    const int2 m = make_int2(min(hi - lo, lay.capS), lo);
+    sym.at<int2>(o, lay.inbox_meta)[sym.rank] = m;
+    if (o == sym.rank) ctrl->snap[o] = m;  // single-GPU jobs launch no request wait
   }
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
@@ -287,6 +306,7 @@ pull_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int64_t* __restr
     int c = s_off[o + 1] - s_off[o];
     if (c > lay.capS) c = lay.capS;
     sym.at<int2>(o, lay.inbox_meta)[sym.rank] = make_int2(c, s_off[o]);
+    if (o == sym.rank) ctrl->snap[o] = make_int2(c, s_off[o]);
   }
   if (last_block_done(&ctrl->done[0])) {
     const uint32_t e = ctrl->pull_epoch + 1;
@@ -296,68 +316,60 @@ pull_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int64_t* __restr
   }
 }
 
+// Owner side of a lookup: one thread per received id finds (or, with `insert`, claims) its slot and
+// records it in slot_cache; the rows that the warp's threads have just created are then initialised
+// by the whole warp together, `lpr` lanes per row, so that the Philox draws and the stores of a row
+// are spread over lanes.  Readers of the rows (pull_gather, a fused consumer) are later launches.
+template <int VEC>
 __global__ void __launch_bounds__(kThreads)
-pull_probe_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, int* slot_cache, int insert, uint32_t spin_limit) {
-  const uint32_t epoch = ctrl->pull_epoch;
+pull_probe_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, int* slot_cache, int insert, int chunks, int lpr) {
+  if (ctrl->abort) return;
   const unsigned long long* inbox = sym.at<unsigned long long>(sym.rank, lay.inbox_ids);
-  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
-  const uint32_t* flags = sym.at<uint32_t>(sym.rank, lay.flag_req);
+  const int lane = threadIdx.x & 31;
+  const int rows_per_pass = 32 / lpr;
   for (int k = 0; k < sym.world; ++k) {
-    const int s = (sym.rank + k) % sym.world;  // own ids first: they are already here
-    if (sym.world > 1 && !block_wait_one(flags + s, epoch, spin_limit)) {
-      if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
-      return;
-    }
-    const int cnt = __ldcg(&meta[s]).x;
+    const int s = (sym.rank + k) % sym.world;
+    const int cnt = ctrl->snap[s].x;
     for (int base = blockIdx.x * blockDim.x; base < cnt; base += gridDim.x * blockDim.x) {
       const int j = base + threadIdx.x;
       bool created = false;
+      int slot = -1;
+      uint64_t id = 0;
       if (j < cnt) {
         const size_t e = static_cast<size_t>(s) * lay.capS + j;
-        const int slot = table_find_or_insert(t, __ldcg(&inbox[e]), insert != 0, &created);
+        id = __ldcg(&inbox[e]);
+        slot = table_find_or_insert(t, id, insert != 0, &created);
         if (slot < 0 && !insert) set_status(&ctrl->status, err::kSparseIdNotExist);
-        // a row created here is initialised by pull_init_kernel, which finds it by this encoding
-        slot_cache[e] = created ? -(slot + 2) : slot;
+        slot_cache[e] = slot;
       }
       count_created(t, created);
-    }
-  }
-}
-
-// Initialises the rows that pull_probe has just created, `lpr` lanes per row so that the
-// Philox draws and the stores of one row are spread over lanes, and rewrites the entry to the
-// plain slot.  A separate launch: every later reader, including entries of other sources that
-// found the same (new) id, runs after it.
-template <int VEC>
-__global__ void __launch_bounds__(kThreads)
-pull_init_kernel(Sym sym, ChanLayout lay, TableView t, int* slot_cache, int chunks, int lpr) {
-  const unsigned long long* inbox = sym.at<unsigned long long>(sym.rank, lay.inbox_ids);
-  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
-  const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
-  const int lane = gtid % lpr;
-  const int row_stride = (gridDim.x * blockDim.x) / lpr;
-  const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
-  for (int s = 0; s < sym.world; ++s) {
-    const int cnt = __ldcg(&meta[s]).x;
-    for (int r = gtid / lpr; r < cnt; r += row_stride) {
-      const size_t e = static_cast<size_t>(s) * lay.capS + r;
-      const int v = slot_cache[e];
-      if (v >= -1) continue;
-      const int slot = -(v + 2);
-      const uint64_t id = __ldcg(&inbox[e]);
-      float* row = t.val + static_cast<size_t>(slot) * t.dim;
-      for (int c = lane; c < chunks; c += lpr) {
-        float q[4];
-        if (VEC == 4) {
-          InitQuad(t.init, t.seed_key, id, c, t.dim, q);
-          *reinterpret_cast<float4*>(row + c * 4) = make_float4(q[0], q[1], q[2], q[3]);
-        } else {
-          InitQuad(t.init, t.seed_key, id, c >> 2, t.dim, q);
-          row[c] = q[c & 3];
+      unsigned todo = __ballot_sync(0xffffffffu, created);
+      while (todo) {
+        // the next rows_per_pass creators of the warp, one per lane group
+        int src = -1;
+        unsigned rest = todo;
+        for (int g = 0; g < rows_per_pass && rest; ++g) {
+          const int l = __ffs(rest) - 1;
+          rest &= rest - 1;
+          if (g == lane / lpr) src = l;
+        }
+        todo = rest;
+        const int r_slot = __shfl_sync(0xffffffffu, slot, src < 0 ? 0 : src);
+        const uint64_t r_id = __shfl_sync(0xffffffffu, id, src < 0 ? 0 : src);
+        if (src >= 0) {
+          float* row = t.val + static_cast<size_t>(r_slot) * t.dim;
+          for (int c = lane % lpr; c < chunks; c += lpr) {
+            float q[4];
+            if (VEC == 4) {
+              InitQuad(t.init, t.seed_key, r_id, c, t.dim, q);
+              *reinterpret_cast<float4*>(row + c * 4) = make_float4(q[0], q[1], q[2], q[3]);
+            } else {
+              InitQuad(t.init, t.seed_key, r_id, c >> 2, t.dim, q);
+              row[c] = q[c & 3];
+            }
+          }
         }
       }
-      __syncwarp(group_mask);  // every lane of the row has read the entry before it is rewritten
-      if (lane == 0) slot_cache[e] = slot;
     }
   }
 }
@@ -367,7 +379,8 @@ __global__ void __launch_bounds__(kThreads)
 pull_gather_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache, int chunks,
                    int lpr) {
   using V = Vec<VEC>;
-  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  const int2* meta = ctrl->snap;
+  const bool aborted = ctrl->abort != 0;  // the answer flags still go up, so the peers do not time out in turn
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
   const int row0 = gtid / lpr;
@@ -377,7 +390,8 @@ pull_gather_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* 
   constexpr int kUnroll = 4;
   for (int k = 0; k < sym.world; ++k) {
     const int s = (sym.rank + k) % sym.world;
-    const int2 m = __ldcg(&meta[s]);
+    int2 m = meta[s];
+    if (aborted) m.x = 0;
     float* dst_base = sym.at<float>(s, lay.rows_recv) + static_cast<size_t>(m.y) * t.dim;
     const int* slots = slot_cache + static_cast<size_t>(s) * lay.capS;
     for (int r = row0; r < m.x; r += row_stride * kUnroll) {
@@ -410,14 +424,8 @@ template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 pull_combine_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int* __restrict__ inv, int n, int dim, int chunks,
                     int lpr, const int64_t* __restrict__ bag_offsets, int nbags, const float* __restrict__ weights,
-                    int mean, const uint8_t* __restrict__ bag_mean, float patch_value, float* __restrict__ out,
-                    uint32_t spin_limit) {
+                    int mean, const uint8_t* __restrict__ bag_mean, float patch_value, float* __restrict__ out) {
   using V = Vec<VEC>;
-  if (sym.world > 1 &&
-      !block_wait_all(sym.at<uint32_t>(sym.rank, lay.flag_rsp), sym.world, ctrl->pull_epoch, spin_limit)) {
-    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
-    return;
-  }
   const float* rows = sym.at<float>(sym.rank, lay.rows_recv);
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
@@ -505,6 +513,7 @@ push_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const in
   if (threadIdx.x <= sym.world) s_off[threadIdx.x] = off[threadIdx.x];
   __syncthreads();
   const int U = s_off[sym.world];
+  const bool aborted = ctrl->abort != 0;
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
   const int row_stride = (gridDim.x * blockDim.x) / lpr;
@@ -514,7 +523,8 @@ push_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const in
     float* src = ugrad + static_cast<size_t>(u) * dim;
     float* dst = sym.at<float>(o, lay.inbox_grad) + (static_cast<size_t>(sym.rank) * lay.capS + j) * dim;
     for (int c = lane; c < chunks; c += lpr) {
-      if (j < lay.capS) V::st(dst + c * VEC, V::ld(src + c * VEC));
+      // after a failed pull the rows (and so the gradients) mean nothing: zeros keep the owners' tables intact
+      if (j < lay.capS) V::st(dst + c * VEC, aborted ? V::zero() : V::ld(src + c * VEC));
       V::st(src + c * VEC, V::zero());  // ready for the next step's segment-sum
     }
   }
@@ -532,21 +542,18 @@ push_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const in
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 push_merge_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache, int chunks,
-                  int lpr, uint32_t spin_limit) {
+                  int lpr) {
   using V = Vec<VEC>;
+  if (ctrl->abort) return;
   const uint32_t epoch = ctrl->push_epoch;
-  if (!block_wait_all(sym.at<uint32_t>(sym.rank, lay.flag_push), sym.world, epoch, spin_limit)) {
-    if (threadIdx.x == 0) set_status(&ctrl->status, err::kTimeout);
-    return;
-  }
-  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  const int2* meta = ctrl->snap;
   float* inbox = sym.at<float>(sym.rank, lay.inbox_grad);
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
   const int row_stride = (gridDim.x * blockDim.x) / lpr;
   const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
   for (int s = 0; s < sym.world; ++s) {
-    const int cnt = __ldcg(&meta[s]).x;
+    const int cnt = meta[s].x;
     const int rounds = (cnt + row_stride - 1) / row_stride;
     for (int it = 0; it < rounds; ++it) {
       const int r = gtid / lpr + it * row_stride;
@@ -588,8 +595,9 @@ push_update_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* 
   using V = Vec<VEC>;
   OptimPOD optim = optim_in;
   optim.type = OPT;
+  if (ctrl->abort) return;
   const uint32_t epoch = ctrl->push_epoch;
-  const int2* meta = sym.at<int2>(sym.rank, lay.inbox_meta);
+  const int2* meta = ctrl->snap;
   const float* inbox = sym.at<float>(sym.rank, lay.inbox_grad);
   const float lr = *lr_ptr;
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -597,7 +605,7 @@ push_update_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* 
   const int row_stride = (gridDim.x * blockDim.x) / lpr;
   const unsigned group_mask = (lpr == 32 ? 0xffffffffu : ((1u << lpr) - 1u)) << ((threadIdx.x & 31) / lpr * lpr);
   for (int s = 0; s < sym.world; ++s) {
-    const int cnt = __ldcg(&meta[s]).x;
+    const int cnt = meta[s].x;
     for (int r = gtid / lpr; r < cnt; r += row_stride) {
       const unsigned entry = static_cast<unsigned>(s) * lay.capS + r;
       const int slot = slot_cache[entry];
@@ -675,15 +683,20 @@ void pull_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int64_t* uniq,
 
 void pull_probe(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, int* slot_cache, bool insert,
                 uint32_t spin_limit, cudaStream_t stream) {
-  pull_probe_kernel<<<grid_for(static_cast<long long>(lay.capS)), kThreads, 0, stream>>>(
-      to_sym(sym), lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0, spin_limit);
-  if (!insert) return;
+  const Sym s = to_sym(sym);
+  launch_wait(s, lay, ctrl, kWaitRequest, spin_limit, stream);
   const RowGeom g = row_geom(table.dim);
-  const int grid = grid_for(static_cast<long long>(lay.capS) * g.lpr);
+  const int grid = grid_for(static_cast<long long>(lay.capS));
   if (g.vec == 4)
-    pull_init_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, to_view(table), slot_cache, g.chunks, g.lpr);
+    pull_probe_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0,
+                                                        g.chunks, g.lpr);
   else
-    pull_init_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, to_view(table), slot_cache, g.chunks, g.lpr);
+    pull_probe_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0,
+                                                        g.chunks, g.lpr);
+}
+
+void pull_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, uint32_t spin_limit, cudaStream_t stream) {
+  launch_wait(to_sym(sym), lay, ctrl, kWaitResponse, spin_limit, stream);
 }
 
 void pull_gather(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache,
@@ -704,14 +717,15 @@ void pull_combine(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int* inv, int n
   const RowGeom g = row_geom(dim);
   const long long rows = bag_offsets ? k : n;
   const int grid = grid_for(rows * g.lpr);
+  launch_wait(to_sym(sym), lay, ctrl, kWaitResponse, spin_limit, stream);
   if (g.vec == 4)
     pull_combine_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
                                                           bag_offsets, k, weights, mean ? 1 : 0, bag_mean, patch_value,
-                                                          out, spin_limit);
+                                                          out);
   else
     pull_combine_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
                                                           bag_offsets, k, weights, mean ? 1 : 0, bag_mean, patch_value,
-                                                          out, spin_limit);
+                                                          out);
 }
 
 void push_scatter(const float* grads, const int* inv, int n, int dim, const int64_t* bag_offsets, int k,
@@ -757,13 +771,12 @@ void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const 
   const int grid = grid_for(static_cast<long long>(lay.capS) * g.lpr);
   const Sym s = to_sym(sym);
   const TableView t = to_view(table);
+  launch_wait(s, lay, ctrl, kWaitPush, spin_limit, stream);
   if (g.vec == 4) {
-    if (sym.world > 1)
-      push_merge_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr, spin_limit);
+    if (sym.world > 1) push_merge_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr);
     launch_update<4>(grid, stream, s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
   } else {
-    if (sym.world > 1)
-      push_merge_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr, spin_limit);
+    if (sym.world > 1) push_merge_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr);
     launch_update<1>(grid, stream, s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
   }
 }

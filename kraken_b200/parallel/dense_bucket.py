@@ -76,7 +76,7 @@ class DenseBucket:
 
         self.grad = self.arena.window("grad")
         self.param = self.arena.window("param")
-        self.ctrl = torch.zeros(4, dtype=torch.int32, device=device)
+        self.ctrl = torch.zeros(C.DENSE_CTRL_INTS, dtype=torch.int32, device=device)  # csrc/cuda/dense_kernels.h: DenseCtrl
         self.chunk_table = torch.tensor(chunk_table, dtype=torch.int32, device=device)
         n_tables = max(1, len(self.table_ids))
         self.table_steps = torch.zeros(n_tables, dtype=torch.int32, device=device)
@@ -132,11 +132,12 @@ class DenseBucket:
                     self.launches += 9
             C.dct_compact(self.bases, self.rank, self.lay, self.n_pad, self.residual, self.tau, self.chunk_table)
             self.dct_step += 1
-            self.launches += 3
+            self.launches += 2
         C.dense_step(self.bases, self.rank, self.lay, self.ctrl, self.n_pad, self.state[0], self.state[1],
                      self.state[2], self.acc, self.chunk_table, self.table_steps, self.table_active, self.optim, lr,
                      float(grad_scale), self.dct, self.spin)
-        self.launches += 1
+        # between GPUs: rendezvous, (COO gather,) update, wait for the owners, zero; one GPU: (COO gather,) update
+        self.launches += (4 if self.world > 1 else 1) + (1 if self.dct else 0)
 
     def check(self) -> None:
         code = int(self.ctrl[3].item())

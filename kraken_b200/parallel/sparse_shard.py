@@ -129,7 +129,9 @@ class GpuSparseTable:
         n = int(ids.numel())
         if n == 0:
             return
-        self.reserve(self.num_rows() + n)
+        total = self.num_rows() + n
+        self.reserve(total)
+        self.rows_hi = max(getattr(self, "rows_hi", 0), total)  # host-side upper bound used by the engine's growth check
         dev = self.device
         ids = ids.to(dev, torch.int64).contiguous()
         vals = vals.to(dev, torch.float32).contiguous()
@@ -164,8 +166,11 @@ class GpuSparseTable:
         if self._size_host is not None:
             if self._size_event is not None and self._size_event.query():
                 rows = int(self._size_host[0])
-                if rows > max_load * self.capacity:
-                    grew = self.reserve(int(rows * 2))
+                # the sample is a step or two old: leave room for what arrives at the pace seen since the last one
+                pace = max(0, rows - getattr(self, "_rows_seen", rows))
+                self._rows_seen = rows
+                if rows + 2 * pace > max_load * self.capacity:
+                    grew = self.reserve(int((rows + 2 * pace) * 2))
                 self._size_event = None
             if self._size_event is None:
                 self._size_host.copy_(self.size, non_blocking=True)
@@ -243,7 +248,7 @@ class SparseChannel:
         self.lay.capS = self.cap_u
         self.lay.capU = self.cap_u
 
-        self.ctrl = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.ctrl = torch.zeros(C.CTRL_INTS, dtype=torch.int32, device=dev)  # csrc/cuda/kernels.h: Ctrl
         self.hbits = _next_pow2_bits(2 * self.cap)
         # dedup scratch set: entries of (key, position | winner << 32); every key is free between calls
         self.hkeys = torch.zeros((1 << self.hbits, 2), dtype=torch.int64, device=dev)
@@ -259,6 +264,7 @@ class SparseChannel:
         self.ugrad = torch.zeros((self.cap_u, dim), dtype=torch.float32, device=dev)
         self.serial = 0
         self.launches = 0  # kernels launched through this channel (for accounting)
+        self._wait = 1 if world > 1 else 0  # the one-warp rendezvous kernels exist only between GPUs
 
     # ------------------------------------------------------------------ helpers
     def _lookup_phase(self, ids: torch.Tensor, insert: bool, share_from: Optional["SparseChannel"] = None) -> int:
@@ -281,7 +287,7 @@ class SparseChannel:
                               self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5], self.cap_u, h, lay, ctrl)
             self.launches += 2
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)
-        self.launches += 2 if insert else 1
+        self.launches += 1 + self._wait  # (request wait +) probe, which also initialises the rows it creates
         self.serial += 1
         self.last_n = n
         return n
@@ -313,8 +319,9 @@ class SparseChannel:
         if in_place and self.world == 1:
             return self.table.val, self.inv, Ticket(self, self.serial, n, None, None, False, None, self.slot_cache)
         C.pull_gather(self.arena.heap, self.lay, self.ctrl, self.table.host(), self.slot_cache)
-        C.pull_wait(self.arena.heap, self.lay, self.ctrl, self.spin)
-        self.launches += 2
+        if self.world > 1:
+            C.pull_wait(self.arena.heap, self.lay, self.ctrl, self.spin)
+        self.launches += 1 + self._wait
         return self.rows_recv, self.inv, Ticket(self, self.serial, n, None, None, False, None)
 
     def push_accumulated(self, lr: torch.Tensor, ticket: Ticket) -> None:
@@ -325,7 +332,7 @@ class SparseChannel:
         h, lay, ctrl, tbl = self.arena.heap, self.lay, self.ctrl, self.table.host()
         C.push_dispatch(h, lay, ctrl, self.ugrad, self.off, ticket.n, self.table.dim)
         C.push_apply(h, lay, ctrl, tbl, self.slot_cache, self.table.optim, lr, self.spin)
-        self.launches += 2 + (1 if self.world > 1 else 0)
+        self.launches += 2 + 2 * self._wait  # dispatch, (push wait, merge,) update
         self.serial += 1
 
     # ------------------------------------------------------------------ pull
@@ -348,7 +355,7 @@ class SparseChannel:
             out = torch.empty((rows, dim), dtype=torch.float32, device=self.table.device)
         C.pull_combine(h, lay, ctrl, self.inv, n, dim, bag_offsets, weights, mean, bag_mean, patch_value, out,
                        self.spin)
-        self.launches += 2
+        self.launches += 2 + self._wait  # gather, (response wait,) combine
         return out, Ticket(self, self.serial, n, bag_offsets, weights, mean, bag_mean)
 
     # ------------------------------------------------------------------ push
@@ -375,7 +382,7 @@ class SparseChannel:
         C.push_scatter(grads, self.inv, n, dim, bag_offsets, weights, mean, bag_mean, self.ugrad)
         C.push_dispatch(h, lay, ctrl, self.ugrad, self.off, n, dim)
         C.push_apply(h, lay, ctrl, tbl, self.slot_cache, self.table.optim, lr, self.spin)
-        self.launches += 3 + (1 if self.world > 1 else 0)
+        self.launches += 3 + 2 * self._wait  # scatter, dispatch, (push wait, merge,) update
         # A push consumes the pull's bookkeeping: a second push needs a new lookup.
         self.serial += 1
 

@@ -172,6 +172,8 @@ def combine_push_sparse_table(table_ids: Sequence[int], indices: Sequence[torch.
 
 def try_save_model() -> bool:
     eng = engine()
+    if hasattr(eng, "check"):
+        eng.check()  # a table that recorded an error must not be written out as if it were sound
     if hasattr(eng, "try_save_model"):
         return eng.try_save_model()
     from ..checkpoint.manager import save_model

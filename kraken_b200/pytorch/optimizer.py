@@ -100,9 +100,17 @@ class Optimizer:
             for p, _ in self._dense:
                 p.grad = None
             self._pull_dense()
+        self.host_step()
+
+    def host_step(self) -> bool:
+        """The part of ``step()`` that runs on the host: advances the learning-rate schedule (the new
+        value reaches the kernels through the engine's device-side copy) and lets the engine do its
+        between-step work (table growth, error words).  A CUDA-graph replay of a step repeats the
+        kernels only, so ``GraphedStep`` calls this after every replay; True means a table was
+        reallocated and captured graphs must be rebuilt."""
         self._lr.step()
         native.update_lr(self._lr.lr())
-        eng.end_step()
+        return bool(native.engine().end_step())
 
     def zero_grad(self):
         pass

@@ -40,6 +40,7 @@ class EngineConfig:
     owner_salt_per_table: bool = False
     exchange: str = "fused"          # "fused": peer-memory kernels; "nccl": torch.distributed collectives (baseline)
     compress: object = None          # TCP deployment: CompressType of worker<->server bodies (None / kNo = off)
+    status_poll_interval: int = 8    # GPU engine: steps between asynchronous reads of the kernels' error words
     overlap_dense_step: bool = False  # run the fused dense step on the MLP backward's side stream, beside the
                                       # sparse backward + push (needs: nothing reads the MLP's .grad before step())
 

@@ -231,10 +231,12 @@ class GpuEngine(Engine):
         info = self._table(table_id, "sparse")
         idx = self._prep_ids(indices)
         if self.nccl:
+            self._ensure_room(table_id, idx.numel())
             rows = self._nccl_channel(table_id, idx.numel()).pull(idx)
             self._nccl_ids = {**getattr(self, "_nccl_ids", {}), table_id: (indices.data_ptr(), idx)}
             return rows.view(*indices.shape, info.dimension)
         ch = self._channel(table_id, idx.numel())
+        self._ensure_room(table_id, idx.numel())
         with self._region("pull"):
             rows, ticket = ch.pull(idx)
         self.tickets[table_id] = (ticket, *self._sig(indices))
@@ -250,6 +252,7 @@ class GpuEngine(Engine):
         w = weights.detach().to(self.device, torch.float32).contiguous() if weights is not None else None
         bm = bag_mean.detach().to(self.device, torch.uint8).contiguous() if bag_mean is not None else None
         ch = self._channel(table_id, idx.numel())
+        self._ensure_room(table_id, idx.numel())
         return ch.pull(idx, bag_offsets=off, weights=w, mean=mean, bag_mean=bm, patch_value=patch_value)
 
     def push_sparse_pooled(self, table_id: int, ticket: Ticket, grads: torch.Tensor,
@@ -269,6 +272,7 @@ class GpuEngine(Engine):
         idx = self._prep_ids(indices)
         ch = self._channel(table_id, idx.numel())
         share = self.channels.get(share_with) if share_with is not None else None
+        self._ensure_room(table_id, idx.numel())
         with self._region("pull"):
             return ch.pull_unique(idx, share_from=share, in_place=in_place)
 
@@ -300,14 +304,80 @@ class GpuEngine(Engine):
             ch.push(g, self.lr_dev, ticket=ticket, ids=idx)
 
     # ------------------------------------------------------------------ housekeeping
-    def end_step(self) -> None:
+    def end_step(self) -> bool:
+        """Between steps: grows tables whose load factor passed the limit and surfaces errors that
+        kernels recorded (table full, inbox overflow, a wait that timed out, push to an unknown id) as
+        ``KrakenError`` - the reference answers every RPC with an error code, here the codes are
+        collected from device memory without stalling the step: the words are copied to pinned memory
+        every ``status_poll_interval`` steps and examined once that copy has landed.  Returns True when
+        a table was reallocated (a captured CUDA graph of the step is stale then)."""
         if torch.cuda.is_current_stream_capturing():
-            return  # growth checks use events and may reallocate: not inside a graph capture
+            return False  # growth checks use events and may reallocate: not inside a graph capture
         self._steps += 1
         if self.profiler is not None:
             self.profiler.end_step()
+        grew = False
         for t in self.sparse.values():
-            t.poll_growth()
+            grew = t.poll_growth() or grew
+        self._poll_status()
+        return grew
+
+    def _status_words(self):
+        """(label, 1-element int32 device tensor) of every status word kernels of this engine write."""
+        out = []
+        for tid, ch in self.channels.items():
+            out.append((f"exchange of table {self.tables[tid].name!r}", ch.ctrl[4:5]))
+        for tid, ch in self.nccl_channels.items():
+            out.append((f"exchange of table {self.tables[tid].name!r}", ch.local.ctrl[4:5]))
+        for tid, t in self.sparse.items():
+            out.append((f"table {t.name!r}", t.status))
+        if self.bucket is not None:
+            out.append(("dense step", self.bucket.ctrl[3:4]))
+        return out
+
+    def _poll_status(self) -> None:
+        pend = getattr(self, "_status_pending", None)
+        if pend is not None:
+            event, host, words = pend
+            if not event.query():
+                return
+            self._status_pending = None
+            codes = host.tolist()
+            bad = [(label, code, w) for (label, w), code in zip(words, codes) if code != 0]
+            if bad:
+                for _, _, w in bad:
+                    w.zero_()
+                raise C.KrakenError("; ".join(f"{label}: {C.error_message(code)} (code {code})" for label, code, _ in bad))
+        if self._steps % max(1, int(getattr(self.cfg, "status_poll_interval", 8))) != 0:
+            return
+        words = self._status_words()
+        if not words:
+            return
+        host = getattr(self, "_status_host", None)
+        if host is None or host.numel() < len(words):
+            host = self._status_host = torch.zeros(max(16, 2 * len(words)), dtype=torch.int32).pin_memory()
+        for k, (_, w) in enumerate(words):
+            host[k:k + 1].copy_(w, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._status_pending = (ev, host[:len(words)], words)
+
+    def _ensure_room(self, table_id: int, n_ids: int) -> None:
+        """Makes sure the shard can take the rows this lookup may create BEFORE the kernels run (growth
+        by ``end_step`` reacts one step late: a first batch larger than the free slots would otherwise
+        hit the probe limit and come back as kTableFull).  A host-side upper bound of the row count is
+        kept per table; only when it nears the load limit is the exact counter read (one synchronisation)."""
+        if torch.cuda.is_current_stream_capturing():
+            return
+        t = self.sparse[table_id]
+        inflow = n_ids * self.world  # worst case: every rank's ids of this call belong to this shard
+        hi = getattr(t, "rows_hi", 0) + inflow
+        if hi > 0.6 * t.capacity:
+            exact = t.num_rows()
+            hi = exact + inflow
+            if hi > 0.6 * t.capacity:
+                t.reserve(hi)
+        t.rows_hi = hi
 
     def check(self) -> None:
         """Raises if any kernel recorded an error (synchronises)."""
@@ -348,6 +418,11 @@ class GpuEngine(Engine):
         if self.profiler is not None:
             self.profiler.close()
         torch.cuda.synchronize()
+        failure = None
+        try:
+            self.check()  # an error recorded after the last poll must not disappear with the engine
+        except C.KrakenError as e:
+            failure = e
         if self.world > 1:
             dist.barrier(group=self.group)
         for ch in list(self.channels.values()) + list(self.nccl_channels.values()):
@@ -360,3 +435,5 @@ class GpuEngine(Engine):
         from ..ops import mlp as fused_mlp
         fused_mlp.set_deferred_join(False)
         super().stop()
+        if failure is not None:
+            raise failure

@@ -29,6 +29,16 @@ def test_gpu_ranks_match_one_shard(world, tmp_path):
         assert tag in out, out[-2000:]
 
 
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_back_to_back_exchanges_match_one_shard(world):
+    """50 pull/push steps on two tables with no dense step, host sync or other collective between them
+    (half eager, half CUDA-graph replays), 200 k skewed ids per rank: every row must match the CPU shard."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = run_ranks("mp_gpu_stress_worker.py", world, "200000", "50", timeout=900)
+    assert "MULTI_GPU_STRESS ok" in out, out[-2000:]
+
+
 def test_nccl_baseline_exchange_matches_one_shard(tmp_path):
     """The NCCL-only path must give the same tables as the fused path's oracle."""
     if torch.cuda.device_count() < 2:
