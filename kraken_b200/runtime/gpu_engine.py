@@ -216,6 +216,18 @@ class GpuEngine(Engine):
     def _sig(indices: torch.Tensor) -> Tuple[int, int, int]:
         return (indices.data_ptr(), indices.numel(), indices._version)
 
+    def _remember(self, table_id: int, ticket, indices: torch.Tensor) -> None:
+        """Keeps the pull's ticket for the push that follows.  The indices tensor itself is kept alive with
+        it: a ticket is matched by address + version, and memory of a freed tensor could be handed to a
+        DIFFERENT id tensor of the same size, whose push would then update the rows of the earlier pull."""
+        self.tickets[table_id] = (ticket, indices, *self._sig(indices))
+
+    def _recall(self, table_id: int, indices: torch.Tensor):
+        saved = self.tickets.pop(table_id, None)
+        if saved is None or saved[2:] != self._sig(indices):
+            return None
+        return saved[0]
+
     def _nccl_channel(self, table_id: int, n: int) -> NcclSparseChannel:
         ch = self.nccl_channels.get(table_id)
         if ch is None:
@@ -233,13 +245,13 @@ class GpuEngine(Engine):
         if self.nccl:
             self._ensure_room(table_id, idx.numel())
             rows = self._nccl_channel(table_id, idx.numel()).pull(idx)
-            self._nccl_ids = {**getattr(self, "_nccl_ids", {}), table_id: (indices.data_ptr(), idx)}
+            self._nccl_ids = {**getattr(self, "_nccl_ids", {}), table_id: (indices, *self._sig(indices), idx)}
             return rows.view(*indices.shape, info.dimension)
         ch = self._channel(table_id, idx.numel())
         self._ensure_room(table_id, idx.numel())
         with self._region("pull"):
             rows, ticket = ch.pull(idx)
-        self.tickets[table_id] = (ticket, *self._sig(indices))
+        self._remember(table_id, ticket, indices)
         return rows.view(*indices.shape, info.dimension)
 
     def pull_sparse_pooled(self, table_id: int, values: torch.Tensor, offsets: torch.Tensor,
@@ -289,12 +301,11 @@ class GpuEngine(Engine):
         if grad.numel() != indices.numel() * info.dimension:
             raise C.KrakenError("gradient shape must be indices.shape + [dimension]")
         if self.nccl:
-            kept = getattr(self, "_nccl_ids", {}).get(table_id)
-            idx = kept[1] if kept is not None and kept[0] == indices.data_ptr() else self._prep_ids(indices)
+            kept = getattr(self, "_nccl_ids", {}).pop(table_id, None)
+            idx = kept[4] if kept is not None and kept[1:4] == self._sig(indices) else self._prep_ids(indices)
             self._nccl_channel(table_id, idx.numel()).push(idx, grad.detach().to(self.device), self.lr_dev)
             return
-        saved = self.tickets.pop(table_id, None)
-        ticket = saved[0] if saved is not None and saved[1:] == self._sig(indices) else None
+        ticket = self._recall(table_id, indices)
         idx = None if ticket is not None else self._prep_ids(indices)
         ch = self._channel(table_id, indices.numel())
         g = grad.detach()

@@ -28,9 +28,26 @@ DIM_A, DIM_B = 8, 4
 LR = 0.01
 
 kk.initialize("gpu", seed=5, table_capacity=1 << 22, max_ids_per_call=PER, overlap_dense_step=True)
-rank, world = dist.get_rank(), dist.get_world_size()
-dev = torch.device("cuda", torch.cuda.current_device())
 eng = kk.native.engine()
+rank, world = eng.rank, eng.world
+dev = torch.device("cuda", torch.cuda.current_device())
+
+
+def barrier():
+    if world > 1:
+        dist.barrier()
+
+
+def broadcast(t):
+    if world > 1:
+        dist.broadcast(t, 0)
+
+
+def all_reduce(t, op=dist.ReduceOp.SUM):
+    if world > 1:
+        dist.all_reduce(t, op=op)
+
+
 kk.init_model("stress", kk.OptimType.kAdam, {})
 kk.update_lr(LR)
 ta = kk.register_sparse_table("a", DIM_A, torch.float32, kk.InitializerType.kConstant, {"value": "0.25"})
@@ -77,7 +94,7 @@ def one_step(ia: torch.Tensor, ib: torch.Tensor, ga: torch.Tensor, gb: torch.Ten
 
 
 torch.cuda.synchronize()
-dist.barrier()
+barrier()
 t0 = time.perf_counter()
 eager_steps = STEPS // 2
 for s in range(eager_steps):
@@ -112,7 +129,7 @@ for s in range(eager_steps, STEPS):
 torch.cuda.synchronize()
 elapsed = time.perf_counter() - t0
 eng.check()
-dist.barrier()
+barrier()
 
 # ------------------------------------------------------------------ oracle on rank 0, compare everywhere
 exp_a, exp_b = eng.sparse[ta].export(), eng.sparse[tb].export()
@@ -139,16 +156,16 @@ for t, exp, dim in ((ta, exp_a, DIM_A), (tb, exp_b, DIM_B)):
         meta = torch.tensor([seen.numel()], device=dev)
     else:
         meta = torch.zeros(1, dtype=torch.int64, device=dev)
-    dist.broadcast(meta, 0)
+    broadcast(meta)
     n = int(meta.item())
     all_ids = seen.to(dev) if rank == 0 else torch.empty(n, dtype=torch.int64, device=dev)
     all_val = want.to(dev) if rank == 0 else torch.empty((n, dim), dtype=torch.float32, device=dev)
-    dist.broadcast(all_ids, 0)
-    dist.broadcast(all_val, 0)
+    broadcast(all_ids)
+    broadcast(all_val)
     mine = owner_of(0, all_ids, world).to(dev) == rank
     rows, found = eng.sparse[t].lookup(all_ids[mine])
     total = torch.tensor([int(exp["ids"].numel())], device=dev)
-    dist.all_reduce(total)
+    all_reduce(total)
     bad = []
     if not bool(found.all()):
         bad.append(f"{int((~found.bool()).sum())} rows missing")
@@ -160,7 +177,7 @@ for t, exp, dim in ((ta, exp_a, DIM_A), (tb, exp_b, DIM_B)):
     if bad:
         print(f"rank {rank} table {t}: " + "; ".join(bad), flush=True)
         ok.zero_()
-dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+all_reduce(ok, dist.ReduceOp.MIN)
 eng.check()
 if rank == 0:
     rows_a = int(exp_a["ids"].numel())
