@@ -30,7 +30,7 @@ CXX_FLAGS = ["-O3", "-std=c++17", "-Wall", "-Wno-unknown-pragmas", "-Wno-unused-
 
 def sources():
     out = []
-    for pat in ("*.cc", "core/*.cc", "cpu/*.cc", "cuda/*.cu", "comm/*.cc", "comm/*.cu"):
+    for pat in ("*.cc", "core/*.cc", "cpu/*.cc", "cuda/*.cu"):
         out += sorted(glob.glob(os.path.join(_CSRC, pat)))
     return out
 

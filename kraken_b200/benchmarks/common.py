@@ -56,6 +56,51 @@ class DeviceTimer:
         return max_over_ranks(ms, dev)
 
 
+def measure_copy_gbs(device=None, mib: int = 1024, reps: int = 5) -> float:
+    """Device copy bandwidth in GB/s (read + write bytes of ``dst.copy_(src)`` over ``mib`` MiB, best of
+    ``reps``, CUDA events): the denominator of the HBM side of a roofline, measured where the benchmark runs."""
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    n = mib << 20
+    a, b = torch.empty(n, dtype=torch.uint8, device=dev), torch.empty(n, dtype=torch.uint8, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(reps + 1):
+        e0.record()
+        b.copy_(a)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        best = min(best, e0.elapsed_time(e1))
+    return 2.0 * n / (best * 1e-3) / 1e9
+
+
+def measure_peer_gbs(mib: int = 256, reps: int = 5) -> float:
+    """Per-direction bandwidth in GB/s of a copy from this rank's GPU into the next rank's (every rank
+    copies at the same time, so all links are busy as in an exchange); the minimum over ranks.  0 when there
+    is one rank.  This is the link figure the NVLink side of a roofline divides by."""
+    world, rank = world_rank()
+    if world <= 1 or torch.cuda.device_count() < world:
+        return 0.0
+    me = torch.device("cuda", torch.cuda.current_device())
+    peer = torch.device("cuda", (torch.cuda.current_device() + 1) % world)
+    n = mib << 20
+    src = torch.empty(n, dtype=torch.uint8, device=me)
+    dst = torch.empty(n, dtype=torch.uint8, device=peer)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(reps + 1):
+        sync_all()
+        e0.record()
+        dst.copy_(src, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize(me)
+        best = min(best, e0.elapsed_time(e1))
+    gbs = n / (best * 1e-3) / 1e9
+    t = torch.tensor([gbs], dtype=torch.float64, device=me)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    del src, dst
+    return float(t.item())
+
+
 def emit(record: dict) -> None:
     world, rank = world_rank()
     if rank == 0:

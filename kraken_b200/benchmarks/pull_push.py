@@ -5,7 +5,6 @@ step, device time, max over ranks) and the time to save / load the table in the 
     torchrun --nproc-per-node N -m kraken_b200.benchmarks.pull_push [--rows-per-gpu 20000000]
 """
 import argparse
-import json
 import os
 import tempfile
 import time
@@ -14,25 +13,14 @@ import numpy as np
 import torch
 
 import kraken_b200.pytorch as kk
-from kraken_b200.benchmarks.common import DeviceTimer, emit, sync_all, world_rank
+from kraken_b200.benchmarks.common import DeviceTimer, emit, measure_copy_gbs, measure_peer_gbs, sync_all, world_rank
 from kraken_b200.models.synthetic import zipf_ids
 
 
-def measured_peaks():
-    """Copy bandwidth measured on this pool (GB/s) if the file is present beside the package, else the fallback."""
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
-    try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    except (OSError, KeyError, ValueError):
-        return 6650.0, "fallback"
-
-
-def roofline(ex: dict, dim: int, pull_us: float, push_us: float, created: float = 0.0, link_gbs: float = 770.0) -> dict:
+def roofline(ex: dict, dim: int, pull_us: float, push_us: float, created: float, hbm_gbs: float, link_gbs: float) -> dict:
     """Lower bounds of one rank's pull and push from the bytes they must move: over NVLink (per direction,
-    at the measured 770 GB/s peer-copy rate) and through HBM (algorithmic bytes at the measured copy rate);
-    the bound is the slower of the two and the fraction is bound / measured time."""
-    hbm_gbs, which = measured_peaks()
+    at ``link_gbs``) and through HBM (algorithmic bytes at ``hbm_gbs``) - both rates measured by this run
+    unless given on the command line; the bound is the slower of the two and the fraction is bound / measured time."""
     n, u, row = ex["occurrences"], ex["unique"], dim * 4
     # pull: read ids, write + read the occurrence map, gather owned rows (about u rows per rank: read + write),
     # read the received rows once and write the expanded [n, dim] result
@@ -43,9 +31,10 @@ def roofline(ex: dict, dim: int, pull_us: float, push_us: float, created: float 
     push_hbm = n * row + 2 * u * row + 2 * u * row + u * row + 4 * u * row
     pull_link = max(ex["pull_bytes_in"], ex["pull_bytes_out"])
     push_link = ex["push_bytes_out"]
-    out = {"unique_per_gpu": u, "unique_remote_per_gpu": ex["unique_remote"], "roofline_peaks": which}
+    out = {"unique_per_gpu": u, "unique_remote_per_gpu": ex["unique_remote"], "hbm_copy_gbs": round(hbm_gbs, 1),
+           "peer_copy_gbs_per_direction": round(link_gbs, 1)}
     for name, hbm, link, t in (("pull", pull_hbm, pull_link, pull_us), ("push", push_hbm, push_link, push_us)):
-        hbm_us, link_us = hbm / (hbm_gbs * 1e3), link / (link_gbs * 1e3)
+        hbm_us, link_us = hbm / (hbm_gbs * 1e3), (link / (link_gbs * 1e3) if link_gbs > 0 else 0.0)
         bound = max(hbm_us, link_us)
         out[f"{name}_hbm_bound_us"] = round(hbm_us, 1)
         out[f"{name}_nvlink_bound_us"] = round(link_us, 1)
@@ -67,6 +56,9 @@ def main():
                    help="replay the pull and the push as two CUDA graphs (as inside a captured training step) "
                         "instead of launching their kernels from Python")
     p.add_argument("--checkpoint-rows", type=int, default=2_000_000, help="rows per shard in the save/load timing (0 = skip)")
+    p.add_argument("--hbm-gbs", type=float, default=0.0, help="copy bandwidth for the roofline (0 = measure it here)")
+    p.add_argument("--link-gbs", type=float, default=0.0,
+                   help="peer-copy bandwidth per direction for the roofline (0 = measure it here with rank -> rank + 1 copies)")
     a = p.parse_args()
     world, rank = world_rank()
     n = a.global_batch // world * 26
@@ -150,7 +142,10 @@ def main():
     rec["ids"] = "resident rows" if a.resident_ids else "whole id space"
     rec["launch"] = "cuda-graph replay" if a.graph else "eager"
     rec["rows_created_per_step"] = round(created)
-    rec.update(roofline(eng.metrics()["big"]["last_exchange"], 64, rec["pull_us"], rec["push_us"], created))
+    hbm_gbs = a.hbm_gbs or measure_copy_gbs(dev)
+    link_gbs = a.link_gbs or measure_peer_gbs()
+    rec.update(roofline(eng.metrics()["big"]["last_exchange"], 64, rec["pull_us"], rec["push_us"], created, hbm_gbs,
+                        link_gbs))
 
     if a.checkpoint_rows > 0:
         # checkpoint timing on a shard trimmed to checkpoint-rows rows (the file format costs ~580 B per row)

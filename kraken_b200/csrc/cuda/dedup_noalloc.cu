@@ -137,8 +137,12 @@ extern "C" int kraken_dedup_bucketize_noalloc(const int64_t* ids, int n, int wor
 
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
-    return fail(err, err_len, -4, "cannot identify the current device: ", cudaGetErrorString(e));
+  if (e != cudaSuccess) return fail(err, err_len, -4, "cannot identify the current device: ", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) {
+    char detail[64];
+    std::snprintf(detail, sizeof(detail), " (ordinal %d, supported 0..%d)", dev, kMaxDevices - 1);
+    return fail(err, err_len, -4, "device ordinal out of the supported range", detail);
+  }
   unsigned char* scratch = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_mu);
@@ -165,9 +169,16 @@ extern "C" int kraken_dedup_bucketize_noalloc(const int64_t* ids, int n, int wor
     return e == cudaSuccess ? 0 : fail(err, err_len, -4, "cudaMemsetAsync failed: ", cudaGetErrorString(e));
   }
   const int blocks = (n + kThreads - 1) / kThreads;
+  // cudaPeekAtLastError right after each launch reports that launch's configuration errors; a sticky
+  // error left by earlier, unrelated asynchronous work shows up here too, hence the wording.
   noalloc_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, scratch, hbits, status);
-  noalloc_finalize_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, scratch, off, uniq, inv);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(err, err_len, -4, "kernel launch failed: ", cudaGetErrorString(e));
+  e = cudaPeekAtLastError();
+  if (e == cudaSuccess) {
+    noalloc_finalize_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, scratch, off, uniq, inv);
+    e = cudaPeekAtLastError();
+  }
+  if (e != cudaSuccess)
+    return fail(err, err_len, -4, "CUDA reported an error at kernel launch (this launch, or earlier work on the context): ",
+                cudaGetErrorString(e));
   return 0;
 }

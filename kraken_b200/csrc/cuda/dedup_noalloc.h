@@ -16,15 +16,22 @@
 //
 // Scratch: a file-scope static __device__ array of KRAKEN_NOALLOC_SCRATCH_BYTES
 // bytes (hash set for 2 * KRAKEN_NOALLOC_MAX_IDS keys, slot bookkeeping,
-// per-owner counters).  Every GPU that loads the library holds that array until
-// the process exits, whether or not this function is ever called.
+// per-owner counters).  Every GPU that loads the library's device code holds that
+// array until the process exits.  With CUDA's default lazy module loading the
+// device code, and with it the array, is placed on a GPU at the library's first
+// use there, not at dlopen time: a caller that hands out all remaining device
+// memory afterwards must make its first call on each GPU BEFORE it commits that
+// memory, or the load itself can fail for lack of room.
 //
 // Rules for callers:
 //   * n must be <= KRAKEN_NOALLOC_MAX_IDS and 1 <= world <= 16; anything else is
 //     refused with a negative return code and a message, nothing is launched.
 //   * The FIRST call on a device resolves the array's device address
 //     (cudaGetSymbolAddress, with that device current).  Make that first call
-//     outside of any stream capture.
+//     outside of any stream capture, and before the memory budget is committed
+//     (see above).
+//   * `stream` must belong to the device that is current when the call is made:
+//     the scratch address that the kernels receive is that device's.
 //   * All calls on a device share the one array and it keeps whatever the last
 //     call left there; each call clears the parts it needs on `stream` before
 //     its kernels run.  Two calls whose work overlaps on the GPU (different

@@ -12,13 +12,13 @@
 #include <string>
 #include <vector>
 
-#include "../core/checkpoint.h"
-#include "../core/hash.h"
-#include "../core/router.h"
-#include "../core/serialize.h"
-#include "../core/task_queue.h"
-#include "../cpu/cpu_ops.h"
-#include "../cpu/cpu_shard.h"
+#include "core/checkpoint.h"
+#include "core/hash.h"
+#include "core/router.h"
+#include "core/serialize.h"
+#include "core/task_queue.h"
+#include "cpu/cpu_ops.h"
+#include "cpu/cpu_shard.h"
 
 using namespace kb;
 

@@ -13,9 +13,25 @@ def rnd(*shape, scale=1.0):
 
 
 def close(got, want, tol=2e-2):
-    err = (got.float() - want.float()).abs().max().item()
-    ref = want.float().abs().max().item() + 1e-6
-    return err <= tol * ref, (err, ref)
+    """Two checks.  Over the whole matrix: max error within ``tol`` of the largest reference value.  Per row
+    and per column: max error within ``tol`` of THAT row's / column's largest reference value (plus a small
+    share of the global one for rows that are all near zero) - a wrong or missing tile whose values happen
+    to be small passes the first check and fails this one."""
+    got, want = got.float(), want.float()
+    diff = (got - want).abs()
+    err = diff.max().item()
+    ref = want.abs().max().item() + 1e-6
+    if err > tol * ref:
+        return False, ("global", err, ref)
+    if got.dim() == 2:
+        for axis in (1, 0):
+            e = diff.amax(dim=axis)
+            r = want.abs().amax(dim=axis)
+            bad = e > tol * r + 2e-3 * ref
+            if bool(bad.any()):
+                k = int(bad.nonzero()[0])
+                return False, ("row" if axis == 1 else "column", k, e[k].item(), r[k].item())
+    return True, (err, ref)
 
 
 SHAPES = [(300, 400, 432), (128, 16, 64), (4096, 256, 512), (1000, 208, 72), (257, 400, 400), (40001, 400, 432),

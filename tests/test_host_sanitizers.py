@@ -9,7 +9,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(ROOT, "kraken_b200", "csrc")
-SOURCES = ["selftest/host_selftest.cc", "core/router.cc", "core/checkpoint.cc", "cpu/cpu_shard.cc", "cpu/cpu_ops.cc"]
+SOURCES = [os.path.join(ROOT, "tests", "host_selftest_src", "host_selftest.cc"), "core/router.cc", "core/checkpoint.cc", "cpu/cpu_shard.cc", "cpu/cpu_ops.cc"]
 
 
 @pytest.mark.parametrize("name,flags", [("asan_ubsan", "-fsanitize=address,undefined"), ("tsan", "-fsanitize=thread")])
@@ -18,7 +18,7 @@ def test_host_code_is_clean_under_sanitizers(tmp_path, name, flags):
     if cxx is None:
         pytest.skip("no g++")
     exe = tmp_path / f"host_selftest_{name}"
-    cmd = [cxx, "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-Wno-unknown-pragmas", *flags.split(),
+    cmd = [cxx, "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-Wno-unknown-pragmas", "-I", CSRC, *flags.split(),
            *SOURCES, "-o", str(exe), "-lpthread"]
     build = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True, timeout=600)
     if build.returncode != 0 and "cannot find" in build.stderr and "san" in build.stderr:

@@ -85,6 +85,22 @@ def test_no_alloc_entry_matches_regular_entry_twice():
         torch.cuda.synchronize()
         assert got[3].item() == 0
         _same_result(ids, got, _regular(ids, world, salt), world)
+    # the claim in the name: with its outputs already allocated, a call takes no device memory at all
+    # (the first call above has loaded the module and resolved the scratch address)
+    n = first.numel()
+    off = torch.zeros(9, dtype=torch.int32, device=dev)
+    uniq = torch.zeros(n, dtype=torch.int64, device=dev)
+    inv = torch.zeros(n, dtype=torch.int32, device=dev)
+    msg = ctypes.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(2):
+        assert fn(first.data_ptr(), n, 8, 0, off.data_ptr(), uniq.data_ptr(), inv.data_ptr(), None, stream, msg,
+                  len(msg)) == 0, msg.value
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
 
 
 def test_no_alloc_entry_refuses_what_it_cannot_hold():
