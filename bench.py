@@ -235,7 +235,13 @@ def run_ours(args):
         out = {
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours" if args.exchange == "fused" else "ours-nccl-baseline",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            # bf16 is the LOWEST precision of any stage; what each stage runs in:
+            "precision": {"tables_and_row_optimizer": "fp32", "fm_interaction_logit_loss": "fp32",
+                          "mlp_gemm_operands": "bf16, fp32 accumulation (TMEM), fp32 master weights",
+                          "mlp_input_gradient_dx": "bf16", "weight_gradients_and_dense_optimizer": "fp32",
+                          "parity_with_fp32": "kraken_b200/benchmarks/precision_parity.py (numbers in BASELINE.md)"},
+            "impl": "ours" if args.exchange == "fused" else "ours-nccl-baseline",
             "config": {"model": "DeepFM 26x1e7 dim16 + MLP 400-400-400-1, Adam lr 1e-3",
                        "tables": "dim-16 embedding + dim-1 first-order" if args.two_tables else
                        "one table, rows = 16 embedding floats + first-order weight (padded to 20)", "global_batch": args.global_batch,

@@ -778,6 +778,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("flag_req", &cu::ChanLayout::flag_req)
       .def_readwrite("flag_rsp", &cu::ChanLayout::flag_rsp)
       .def_readwrite("flag_push", &cu::ChanLayout::flag_push)
+      .def_readwrite("inbox_tcnt", &cu::ChanLayout::inbox_tcnt)
       .def_readwrite("capS", &cu::ChanLayout::capS)
       .def_readwrite("capU", &cu::ChanLayout::capU);
 
@@ -875,6 +876,71 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     cu::push_apply(h.View(), lay, ctrl_ptr(ctrl), table, ptr<int>(slot_cache), optim,
                    ptr<float>(lr), spin, cur_stream());
     check_launch("push_apply");
+  });
+
+  // ---------------- one exchange for several tables of one row width
+  m.def("group_table_views", [](const std::vector<cu::TableHost>& tables) {
+    // the tables' device-side descriptors as one CPU byte tensor; the caller copies it to the device
+    const int T = static_cast<int>(tables.size());
+    auto out = torch::zeros({static_cast<int64_t>(T * cu::group_table_view_bytes())}, torch::kUInt8);
+    cu::group_table_views(tables.data(), T, out.data_ptr());
+    return out;
+  });
+  m.def("group_dedup_dispatch",
+        [](const torch::Tensor& ids, const torch::Tensor& occ_start, const torch::Tensor& region_base,
+           const torch::Tensor& region_bits, const torch::Tensor& salts, int world, const torch::Tensor& hkeys,
+           const torch::Tensor& slot_of, const torch::Tensor& cnt, const torch::Tensor& off, const torch::Tensor& uniq,
+           const torch::Tensor& inv, const torch::Tensor& status, int cap_u, const SymHeap& heap,
+           const cu::ChanLayout& lay, const torch::Tensor& ctrl) {
+          need_cuda(ids, "ids", torch::kInt64);
+          need_cuda(occ_start, "occ_start", torch::kInt32);
+          need_cuda(region_base, "region_base", torch::kInt32);
+          need_cuda(region_bits, "region_bits", torch::kInt32);
+          need_cuda(salts, "salts", torch::kInt64);
+          need_cuda(hkeys, "hkeys", torch::kInt64);
+          const int T = static_cast<int>(region_base.numel());
+          const int n = static_cast<int>(ids.numel());
+          TORCH_CHECK(T >= 1 && T <= 4096 && occ_start.numel() == T + 1 && region_bits.numel() == T && salts.numel() == T,
+                      "group descriptors differ in length");
+          TORCH_CHECK(static_cast<size_t>(4) * (T + 1 + 2 * world * T + 256) <= 48 * 1024,
+                      "too many tables in one group for the kernels' shared memory");
+          TORCH_CHECK(slot_of.numel() >= n && inv.numel() >= n && cnt.numel() >= static_cast<int64_t>(world) * T &&
+                          off.numel() >= world + 1 && uniq.numel() >= cap_u,
+                      "group dedup buffers too small");
+          c10::cuda::CUDAGuard guard(ids.device());
+          cu::GroupDesc d{T, ptr<int>(occ_start), ptr<int>(region_base), ptr<int>(region_bits),
+                          reinterpret_cast<const unsigned long long*>(salts.data_ptr())};
+          cu::DedupScratch sc{hkeys.data_ptr(), ptr<int>(slot_of), 0};
+          cu::group_dedup_dispatch(ptr<int64_t>(ids), n, d, world, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),
+                                   ptr<int>(inv), cap_u, ptr<int>(status), heap.View(), lay, ctrl_ptr(ctrl), cur_stream());
+          check_launch("group_dedup_dispatch");
+        });
+  m.def("group_probe", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                          const torch::Tensor& table_views, int T, int dim, const torch::Tensor& snap_t,
+                          const torch::Tensor& slot_cache, const torch::Tensor& ttab, bool insert, uint32_t spin) {
+    need_cuda(table_views, "table_views", torch::kUInt8);
+    need_cuda(snap_t, "snap_t", torch::kInt32);
+    need_cuda(ttab, "ttab", torch::kInt16);
+    TORCH_CHECK(table_views.numel() >= static_cast<int64_t>(T * cu::group_table_view_bytes()), "table_views too small");
+    TORCH_CHECK(snap_t.numel() >= static_cast<int64_t>(h.world) * (T + 1), "snap_t too small");
+    cu::group_probe(h.View(), lay, ctrl_ptr(ctrl), table_views.data_ptr(), T, dim, ptr<int>(snap_t), ptr<int>(slot_cache),
+                    ptr<int16_t>(ttab), insert, spin, cur_stream());
+    check_launch("group_probe");
+  });
+  m.def("group_gather", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                           const torch::Tensor& table_views, int dim, const torch::Tensor& slot_cache,
+                           const torch::Tensor& ttab) {
+    cu::group_gather(h.View(), lay, ctrl_ptr(ctrl), table_views.data_ptr(), dim, ptr<int>(slot_cache), ptr<int16_t>(ttab),
+                     cur_stream());
+    check_launch("group_gather");
+  });
+  m.def("group_push_apply", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
+                               const torch::Tensor& table_views, int dim, const torch::Tensor& slot_cache,
+                               const torch::Tensor& ttab, const OptimPOD& optim, const torch::Tensor& lr, uint32_t spin) {
+    need_cuda(lr, "lr", torch::kFloat32);
+    cu::group_push_apply(h.View(), lay, ctrl_ptr(ctrl), table_views.data_ptr(), dim, ptr<int>(slot_cache),
+                         ptr<int16_t>(ttab), optim, ptr<float>(lr), spin, cur_stream());
+    check_launch("group_push_apply");
   });
 
   // ---------------- fused DeepFM front end

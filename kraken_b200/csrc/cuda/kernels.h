@@ -33,6 +33,7 @@ struct ChanLayout {
   size_t flag_req;    // u32  [world]
   size_t flag_rsp;    // u32  [world]
   size_t flag_push;   // u32  [world]
+  size_t inbox_tcnt;  // int  [world][T + 1]  multi-table channels only: per source, prefix of its ids per table
   int capS;           // ids one source may send to one owner
   int capU;           // unique ids one rank may request
 };
@@ -112,6 +113,41 @@ void push_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const 
                    cudaStream_t stream);
 void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const int* slot_cache, OptimPOD optim,
                 const float* lr, uint32_t spin_limit, cudaStream_t stream);
+
+// One of the channel's rendezvous points as a launch of its own: kind 0 = every source's request has
+// arrived (also snapshots the counts), 1 = every owner has answered the pull, 2 = every source's gradient
+// rows have arrived.  Nothing is launched when world == 1.
+void exchange_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, int kind, uint32_t spin_limit, cudaStream_t stream);
+
+// ---- one exchange for several tables of the same row width (sparse_group.cu) ----
+// The ids of the group's tables are one concatenated list; occ_start[T + 1] gives each table's part.
+// The dedup scratch set is split into one region per table (region_base / region_bits, in entries),
+// so equal ids of different tables stay distinct; unique ids come out grouped by (owner, table).
+// All arrays are device memory, rewritten by the host only when the shapes of a call change.
+struct GroupDesc {
+  int T;
+  const int* occ_start;                // [T + 1]
+  const int* region_base;              // [T]
+  const int* region_bits;              // [T]
+  const unsigned long long* salt;      // [T] owner salt of every table
+};
+// Fills out_host[T * group_table_view_bytes()] with the device-side descriptors of the tables; the caller
+// copies the block to device memory and passes that pointer as `table_views` below (again after a table
+// was reallocated).
+void group_table_views(const TableHost* tables, int T, void* out_host);
+size_t group_table_view_bytes();
+// dedup + dispatch of the whole group (cnt: scratch of world * T ints).
+void group_dedup_dispatch(const int64_t* ids, int n, const GroupDesc& d, int world, DedupScratch sc, int* cnt,
+                          int* off, int64_t* uniq, int* inv, int cap_u, int* status, SymHost sym, ChanLayout lay,
+                          Ctrl* ctrl, cudaStream_t stream);
+// Owner side: request rendezvous (always launched: it also copies the per-table prefixes into snap_t
+// [world * (T + 1)]), then find-or-insert of every received id in its table; records slot and table per entry.
+void group_probe(SymHost sym, ChanLayout lay, Ctrl* ctrl, const void* table_views, int T, int dim, int* snap_t,
+                 int* slot_cache, int16_t* ttab, bool insert, uint32_t spin_limit, cudaStream_t stream);
+void group_gather(SymHost sym, ChanLayout lay, Ctrl* ctrl, const void* table_views, int dim, const int* slot_cache,
+                  const int16_t* ttab, cudaStream_t stream);
+void group_push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, const void* table_views, int dim, const int* slot_cache,
+                      const int16_t* ttab, OptimPOD optim, const float* lr, uint32_t spin_limit, cudaStream_t stream);
 
 // Owner rank of every id under the modulo placement (OwnerOf of core/hash.h).
 void owner_of(const int64_t* ids, int n, uint64_t salt, int world, int* owners, cudaStream_t stream);

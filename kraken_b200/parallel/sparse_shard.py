@@ -59,6 +59,7 @@ class GpuSparseTable:
 
     # ------------------------------------------------------------------ storage
     def _alloc(self, bits: int) -> None:
+        self.generation = getattr(self, "generation", 0) + 1  # bumps whenever the slabs move: cached descriptors are stale
         cap = 1 << bits
         dev = self.device
         info = self.optim_info
@@ -393,6 +394,176 @@ class SparseChannel:
             self.ctrl[4].zero_()
             raise C.KrakenError(f"channel of table {self.table.name!r}: {C.error_message(code)} (code {code})")
         self.table.check()
+
+    def close(self) -> None:
+        self.arena.close()
+
+
+class GroupChannel:
+    """One exchange for several tables of the same row width (csrc/cuda/sparse_group.cu).
+
+    The ids of the tables travel as one concatenated list: one dedup keyed by (table, id), one
+    dispatch, one owner-side probe, one gather and one push sequence serve the whole group - what the
+    reference does with its combined requests (kraken/worker/emitter.cc:185-278, :552-632;
+    kraken/ps/ps_op.cc:370-387, :456-469).  ``pull`` returns one [n_total, dim] buffer holding the rows of
+    every table's ids back to back (split it per table); ``push`` takes the gradients in the same layout.
+    Collective like SparseChannel: every rank calls with the same tables in the same order.
+    """
+
+    def __init__(self, tables, rank: int, world: int, max_ids: int, group=None, spin_limit: int = DEFAULT_SPIN,
+                 salts=None, alias_peers: bool = False, max_unique: int = 0) -> None:
+        dims = {t.dim for t in tables}
+        if len(dims) != 1:
+            raise C.KrakenError("the tables of a group must have the same dimension")
+        self.tables = list(tables)
+        self.T = len(self.tables)
+        self.dim = self.tables[0].dim
+        self.rank, self.world, self.group = rank, world, group
+        self.spin = int(spin_limit)
+        self.cap = int(max_ids)
+        self.cap_u = int(max_unique) if max_unique and max_unique < max_ids else int(max_ids)
+        dev = self.tables[0].device
+        self.device = dev
+        T, dim = self.T, self.dim
+
+        lay = Layout()
+        lay.add("inbox_ids", (world, self.cap_u), torch.int64)
+        lay.add("inbox_meta", (world, 2), torch.int32)
+        lay.add("inbox_tcnt", (world, T + 1), torch.int32)
+        lay.add("rows_recv", (self.cap_u, dim), torch.float32)
+        lay.add("inbox_grad", (world, self.cap_u, dim), torch.float32)
+        lay.add("flag_req", (world,), torch.int32)
+        lay.add("flag_rsp", (world,), torch.int32)
+        lay.add("flag_push", (world,), torch.int32)
+        self.arena = SymmetricArena(lay, rank, world, group, alias_peers)
+        self.lay = C.ChanLayout()
+        for name in ("inbox_ids", "inbox_meta", "inbox_tcnt", "rows_recv", "inbox_grad", "flag_req", "flag_rsp",
+                     "flag_push"):
+            setattr(self.lay, name, lay.offset(name))
+        self.lay.capS = self.cap_u
+        self.lay.capU = self.cap_u
+
+        self.ctrl = torch.zeros(C.CTRL_INTS, dtype=torch.int32, device=dev)
+        self.salts = torch.tensor([int(x) for x in (salts or [0] * T)], dtype=torch.int64, device=dev)
+        self.snap_t = torch.zeros(world * (T + 1), dtype=torch.int32, device=dev)
+        self.slot_of = torch.zeros(self.cap, dtype=torch.int32, device=dev)
+        self.cnt = torch.zeros(world * T, dtype=torch.int32, device=dev)
+        self.off = torch.zeros(world + 1, dtype=torch.int32, device=dev)
+        self.uniq = torch.zeros(self.cap_u, dtype=torch.int64, device=dev)
+        self.inv = torch.zeros(self.cap, dtype=torch.int32, device=dev)
+        self.rows_recv = self.arena.window("rows_recv")
+        self.slot_cache = torch.full((world * self.cap_u,), -1, dtype=torch.int32, device=dev)
+        self.ttab = torch.zeros(world * self.cap_u, dtype=torch.int16, device=dev)
+        self.ugrad = torch.zeros((self.cap_u, dim), dtype=torch.float32, device=dev)
+        self.hkeys = None           # dedup scratch, one region per table, sized on first use
+        self._shape_sig = None      # ids per table of the call the descriptors were built for
+        self._views_sig = None      # generations of the tables the device-side descriptors describe
+        self.table_views = None
+        self.serial = 0
+        self.launches = 0
+
+    # ------------------------------------------------------------------ descriptors
+    def _describe(self, counts) -> None:
+        """Device-side description of a call's shape (ids per table) - rebuilt only when it changes."""
+        sig = tuple(int(c) for c in counts)
+        if sig == self._shape_sig:
+            return
+        if torch.cuda.is_current_stream_capturing():
+            raise C.KrakenError("the number of ids per table changed inside a CUDA-graph capture")
+        occ, base, bits, pos = [0], [], [], 0
+        for c in sig:
+            occ.append(occ[-1] + c)
+            b = _next_pow2_bits(2 * max(c, 1))
+            base.append(pos)
+            bits.append(b)
+            pos += 1 << b
+        dev = self.device
+        self.occ_start = torch.tensor(occ, dtype=torch.int32, device=dev)
+        self.region_base = torch.tensor(base, dtype=torch.int32, device=dev)
+        self.region_bits = torch.tensor(bits, dtype=torch.int32, device=dev)
+        if self.hkeys is None or self.hkeys.shape[0] < pos:
+            self.hkeys = torch.zeros((pos, 2), dtype=torch.int64, device=dev)
+            self.hkeys[:, 0] = _EMPTY
+        self._shape_sig = sig
+
+    def _refresh_views(self) -> None:
+        sig = tuple(t.generation for t in self.tables)
+        if sig == self._views_sig:
+            return
+        host = C.group_table_views([t.host() for t in self.tables])
+        if self.table_views is None:
+            self.table_views = host.to(self.device)
+        else:
+            self.table_views.copy_(host)   # same device buffer: launches captured in a CUDA graph stay valid
+        self._views_sig = sig
+
+    # ------------------------------------------------------------------ exchange
+    def _lookup_phase(self, ids_cat: torch.Tensor, counts, insert: bool) -> int:
+        n = int(ids_cat.numel())
+        if n > self.cap:
+            raise C.KrakenError(f"{n} ids in one combined call exceed the channel capacity {self.cap}; "
+                                "raise max_ids_per_call")
+        self._describe(counts)
+        self._refresh_views()
+        h, lay, ctrl = self.arena.heap, self.lay, self.ctrl
+        C.group_dedup_dispatch(ids_cat, self.occ_start, self.region_base, self.region_bits, self.salts, self.world,
+                               self.hkeys, self.slot_of, self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5],
+                               self.cap_u, h, lay, ctrl)
+        C.group_probe(h, lay, ctrl, self.table_views, self.T, self.dim, self.snap_t, self.slot_cache, self.ttab,
+                      insert, self.spin)
+        self.launches += 5  # memset is not counted: insert, finalize + dispatch, request wait, probe (+ init)
+        self.serial += 1
+        self.last_n = n
+        return n
+
+    def pull(self, ids_cat: torch.Tensor, counts, bag_offsets: Optional[torch.Tensor] = None,
+             weights: Optional[torch.Tensor] = None, bag_mean: Optional[torch.Tensor] = None,
+             patch_value: float = 0.0):
+        """ids_cat: the tables' ids back to back, counts[t] of them for table t.  Returns (rows, ticket):
+        rows is [n_total, dim], or [k_total, dim] pooled per bag when ``bag_offsets`` (over the concatenated
+        list) is given - ``bag_mean[b]`` selects mean pooling per bag."""
+        n = self._lookup_phase(ids_cat.reshape(-1), counts, insert=True)
+        h, lay, ctrl = self.arena.heap, self.lay, self.ctrl
+        C.group_gather(h, lay, ctrl, self.table_views, self.dim, self.slot_cache, self.ttab)
+        rows = (int(bag_offsets.numel()) - 1) if bag_offsets is not None else n
+        out = torch.empty((rows, self.dim), dtype=torch.float32, device=self.device)
+        C.pull_combine(h, lay, ctrl, self.inv, n, self.dim, bag_offsets, weights, False, bag_mean, patch_value, out,
+                       self.spin)
+        self.launches += 2 + (1 if self.world > 1 else 0)
+        return out, Ticket(self, self.serial, n, bag_offsets, weights, False, bag_mean)
+
+    def push(self, grads_cat: torch.Tensor, lr: torch.Tensor, ticket: Optional[Ticket] = None,
+             ids_cat: Optional[torch.Tensor] = None, counts=None) -> None:
+        """Gradients in the layout ``pull`` returned.  With the ticket of this channel's latest pull the
+        dedup result and the owners' slots are reused; otherwise the ids are looked up again (an id a table
+        does not hold is kSparseIdNotExist)."""
+        bag_offsets = weights = bag_mean = None
+        if ticket is not None and ticket.channel is self and ticket.serial == self.serial:
+            n = ticket.n
+            bag_offsets, weights, bag_mean = ticket.bag_offsets, ticket.weights, ticket.bag_mean
+        else:
+            if ids_cat is None or counts is None:
+                raise C.KrakenError("a combined push without a current ticket needs the ids")
+            n = self._lookup_phase(ids_cat.reshape(-1), counts, insert=False)
+        h, lay, ctrl = self.arena.heap, self.lay, self.ctrl
+        grads = grads_cat.reshape(-1, self.dim)
+        if grads.dtype != torch.float32 or not grads.is_contiguous():
+            grads = grads.to(torch.float32).contiguous()
+        C.push_scatter(grads, self.inv, n, self.dim, bag_offsets, weights, False, bag_mean, self.ugrad)
+        C.push_dispatch(h, lay, ctrl, self.ugrad, self.off, n, self.dim)
+        C.group_push_apply(h, lay, ctrl, self.table_views, self.dim, self.slot_cache, self.ttab, self.tables[0].optim,
+                           lr, self.spin)
+        self.launches += 3 + (2 if self.world > 1 else 0)
+        self.serial += 1
+
+    def check(self) -> None:
+        code = int(self.ctrl[4].item())
+        if code != 0:
+            self.ctrl[4].zero_()
+            names = ", ".join(repr(t.name) for t in self.tables[:4]) + (", ..." if self.T > 4 else "")
+            raise C.KrakenError(f"combined channel of tables {names}: {C.error_message(code)} (code {code})")
+        for t in self.tables:
+            t.check()
 
     def close(self) -> None:
         self.arena.close()

@@ -17,7 +17,7 @@ import torch.distributed as dist
 from .._native import C
 from ..parallel.dense_bucket import DenseBucket
 from ..parallel.nccl_baseline import NcclSparseChannel
-from ..parallel.sparse_shard import GpuSparseTable, SparseChannel, Ticket
+from ..parallel.sparse_shard import GpuSparseTable, GroupChannel, SparseChannel, Ticket
 from ..utils import profiler as _profiler
 from .engine import Engine, EngineConfig, TableInfo
 
@@ -35,6 +35,8 @@ class GpuEngine(Engine):
         self.sparse: Dict[int, GpuSparseTable] = {}
         self.channels: Dict[int, SparseChannel] = {}
         self.tickets: Dict[int, Tuple[Ticket, int, int, int]] = {}
+        self.group_channels: Dict[Tuple[int, ...], GroupChannel] = {}
+        self.group_tickets: Dict[Tuple[int, ...], tuple] = {}
         self.dense_init: Dict[int, torch.Tensor] = {}
         self.bucket: Optional[DenseBucket] = None
         self._dense_pending = False
@@ -254,6 +256,87 @@ class GpuEngine(Engine):
         self._remember(table_id, ticket, indices)
         return rows.view(*indices.shape, info.dimension)
 
+    # ------------------------------------------------------------------ several tables, one exchange
+    def _group_channel(self, tids: Tuple[int, ...], n_total: int) -> GroupChannel:
+        ch = self.group_channels.get(tids)
+        if ch is not None:
+            return ch
+        cap = max(1024, 2 * n_total)
+        if self.world > 1:
+            t = torch.tensor([cap], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            cap = int(t.item())
+        ch = GroupChannel([self.sparse[t] for t in tids], self.rank, self.world, cap, self.group, self.cfg.spin_limit,
+                          salts=[self._salt(t) for t in tids])
+        self.group_channels[tids] = ch
+        return ch
+
+    def _dim_classes(self, table_ids: Sequence[int]):
+        """Positions of ``table_ids`` grouped by row width, in first-appearance order; None when a table is
+        named twice (each call then goes through its own exchange)."""
+        if len(set(table_ids)) != len(table_ids):
+            return None
+        classes: Dict[int, List[int]] = {}
+        for pos, t in enumerate(table_ids):
+            classes.setdefault(self._table(t, "sparse").dimension, []).append(pos)
+        return classes
+
+    def combine_pull_sparse_table(self, table_ids: Sequence[int], indices: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+        """All tables of one row width share ONE exchange (dedup keyed by (table, id), one dispatch, one
+        gather), as the reference's combined request does in one round per server
+        (kraken/worker/emitter.cc:185-278); tables of different widths form one group per width."""
+        if len(table_ids) != len(indices):
+            raise C.KrakenError("table_ids and indices differ in length")
+        classes = None if self.nccl else self._dim_classes(table_ids)
+        if classes is None or all(len(p) == 1 for p in classes.values()):
+            return super().combine_pull_sparse_table(table_ids, indices)
+        out: List[Optional[torch.Tensor]] = [None] * len(table_ids)
+        for dim, pos in classes.items():
+            if len(pos) == 1:
+                out[pos[0]] = self.pull_sparse_table(table_ids[pos[0]], indices[pos[0]])
+                continue
+            tids = tuple(int(table_ids[p]) for p in pos)
+            flat = [self._prep_ids(indices[p]).reshape(-1) for p in pos]
+            counts = [int(f.numel()) for f in flat]
+            ch = self._group_channel(tids, sum(counts))
+            for t, c in zip(tids, counts):
+                self._ensure_room(t, c)
+            with self._region("pull"):
+                rows, ticket = ch.pull(torch.cat(flat), counts)
+            self.group_tickets[tids] = (ticket, [indices[p] for p in pos], [self._sig(indices[p]) for p in pos])
+            for p, part in zip(pos, rows.split(counts)):
+                out[p] = part.view(*indices[p].shape, dim)
+        return out
+
+    def combine_push_sparse_table(self, table_ids: Sequence[int], indices: Sequence[torch.Tensor],
+                                  grads: Sequence[torch.Tensor]) -> None:
+        if not (len(table_ids) == len(indices) == len(grads)):
+            raise C.KrakenError("table_ids, indices and grads differ in length")
+        classes = None if self.nccl else self._dim_classes(table_ids)
+        if classes is None or all(len(p) == 1 for p in classes.values()):
+            return super().combine_push_sparse_table(table_ids, indices, grads)
+        for dim, pos in reversed(list(classes.items())):
+            if len(pos) == 1:
+                self.push_sparse_table(table_ids[pos[0]], indices[pos[0]], grads[pos[0]])
+                continue
+            tids = tuple(int(table_ids[p]) for p in pos)
+            grads = list(grads)
+            for p in pos:
+                if grads[p] is None:  # an output autograd never used
+                    grads[p] = torch.zeros((int(indices[p].numel()), dim), dtype=torch.float32, device=self.device)
+                if grads[p].numel() != indices[p].numel() * dim:
+                    raise C.KrakenError("gradient shape must be indices.shape + [dimension]")
+            saved = self.group_tickets.pop(tids, None)
+            ticket = saved[0] if saved is not None and saved[2] == [self._sig(indices[p]) for p in pos] else None
+            g = torch.cat([grads[p].detach().to(self.device, torch.float32).reshape(-1, dim) for p in pos])
+            ch = self._group_channel(tids, sum(int(indices[p].numel()) for p in pos))
+            with self._region("push"):
+                if ticket is not None:
+                    ch.push(g, self.lr_dev, ticket=ticket)
+                else:
+                    flat = [self._prep_ids(indices[p]).reshape(-1) for p in pos]
+                    ch.push(g, self.lr_dev, ids_cat=torch.cat(flat), counts=[int(f.numel()) for f in flat])
+
     def pull_sparse_pooled(self, table_id: int, values: torch.Tensor, offsets: torch.Tensor,
                            weights: Optional[torch.Tensor] = None, mean: bool = False,
                            bag_mean: Optional[torch.Tensor] = None, patch_value: float = 0.0):
@@ -340,6 +423,8 @@ class GpuEngine(Engine):
             out.append((f"exchange of table {self.tables[tid].name!r}", ch.ctrl[4:5]))
         for tid, ch in self.nccl_channels.items():
             out.append((f"exchange of table {self.tables[tid].name!r}", ch.local.ctrl[4:5]))
+        for tids, ch in self.group_channels.items():
+            out.append((f"combined exchange of tables {list(tids)}", ch.ctrl[4:5]))
         for tid, t in self.sparse.items():
             out.append((f"table {t.name!r}", t.status))
         if self.bucket is not None:
@@ -392,7 +477,7 @@ class GpuEngine(Engine):
 
     def check(self) -> None:
         """Raises if any kernel recorded an error (synchronises)."""
-        for ch in list(self.channels.values()) + list(self.nccl_channels.values()):
+        for ch in list(self.channels.values()) + list(self.nccl_channels.values()) + list(self.group_channels.values()):
             ch.check()
         for t in self.sparse.values():
             t.check()
@@ -402,6 +487,7 @@ class GpuEngine(Engine):
     def kernel_launches(self) -> int:
         from ..ops import counters
         n = sum(ch.launches for ch in self.channels.values()) + counters.launches()
+        n += sum(ch.launches for ch in self.group_channels.values())
         n += sum(ch.local.launches for ch in self.nccl_channels.values())
         if self.bucket is not None:
             n += self.bucket.launches
@@ -436,9 +522,10 @@ class GpuEngine(Engine):
             failure = e
         if self.world > 1:
             dist.barrier(group=self.group)
-        for ch in list(self.channels.values()) + list(self.nccl_channels.values()):
+        for ch in list(self.channels.values()) + list(self.nccl_channels.values()) + list(self.group_channels.values()):
             ch.close()
         self.nccl_channels.clear()
+        self.group_channels.clear()
         if self.bucket is not None:
             self.bucket.close()
         self.channels.clear()

@@ -91,3 +91,91 @@ def test_graphed_step_grows_tables_and_follows_the_lr_schedule():
     # every id was pushed exactly once with gradient 1 and the learning rate of its step: all rows moved
     rows, found = eng.sparse[tid].lookup(torch.arange(512 * 40, device=DEV))
     assert bool(found.all()) and bool((rows[:512 * 2] < 0).all())
+
+
+def test_bf16_step_tracks_the_fp32_step_on_the_teacher_task():
+    """The benchmark's fused bf16 step and the all-fp32 step, same model, same batches, 300 Adam steps:
+    held-out loss and AUC must agree closely (the reference computes in fp32, kraken/t/math.cc:20-76)."""
+    from kraken_b200.benchmarks.precision_parity import main
+    rec = main(["--steps", "300", "--batch", "4096", "--vocab", "20000", "--distinct", "300", "--eval-batches", "4",
+                "--table-capacity", str(1 << 21)])
+    assert rec["fp32"]["eval_auc"] > 0.55, rec          # the task is learnable: both arms learn it
+    assert abs(rec["eval_auc_diff"]) < 0.01, rec
+    assert abs(rec["eval_loss_diff"]) < 0.01, rec
+
+
+def _combined_scenario(dev, rank=0, world=1, steps=3):
+    """Six tables (three of width 4, two of width 8, one of width 1) pulled and pushed through the combined
+    calls for a few steps, the SAME ids appearing in several tables; every table must then equal a CPU
+    shard fed the concatenated stream (scenario of kraken/test/worker/emitter_test.cc:108-158)."""
+    from kraken_b200._native import C
+    dims = [4, 8, 4, 1, 8, 4]
+    kk.init_model("m", kk.OptimType.kAdagrad, {})
+    kk.update_lr(0.1)
+    tids = [kk.register_sparse_table(f"t{k}", d, torch.float32, kk.InitializerType.kConstant, {"value": str(0.1 * (k + 1))})
+            for k, d in enumerate(dims)]
+    shard = C.CpuShard(0)
+    shard.init_model("m", kk.OptimType.kAdagrad, {})
+    for k, (t, d) in enumerate(zip(tids, dims)):
+        shard.create_sparse_table(t, f"t{k}", d, kk.InitializerType.kConstant, {"value": str(0.1 * (k + 1))})
+    eng = kk.native.engine()
+    gen = torch.Generator().manual_seed(7)
+    for s in range(steps):
+        # per rank and table: ids from a small range so that tables and ranks overlap heavily
+        all_ids = [[torch.randint(0, 300, (50 + 17 * k + 5 * r,), generator=gen) for k in range(len(dims))]
+                   for r in range(world)]
+        all_g = [[torch.randn(all_ids[r][k].numel(), d, generator=gen) for k, d in enumerate(dims)] for r in range(world)]
+        mine = [i.to(dev) for i in all_ids[rank]]
+        before = eng.kernel_launches()
+        rows = kk.combine_pull_sparse_table(tids, mine)
+        pull_launches = eng.kernel_launches() - before
+        for k, t in enumerate(tids):
+            cat = torch.cat([all_ids[r][k] for r in range(world)])
+            uniq, inv = C.cpu_dedup(cat)
+            want = shard.pull_sparse(t, uniq)[inv]
+            lo = sum(all_ids[r][k].numel() for r in range(rank))
+            got = rows[k].cpu()
+            assert got.shape == (mine[k].numel(), dims[k])
+            assert torch.allclose(got, want[lo:lo + mine[k].numel()], atol=1e-5), (s, k)
+        kk.combine_push_sparse_table(tids, mine, [g.to(dev) for g in all_g[rank]])
+        for k, t in enumerate(tids):
+            cat = torch.cat([all_ids[r][k] for r in range(world)])
+            gcat = torch.cat([all_g[r][k] for r in range(world)])
+            uniq, inv = C.cpu_dedup(cat)
+            assert shard.push_sparse(t, uniq, C.cpu_segment_sum(gcat, inv, uniq.numel()), 0.1) == 0
+        # three row widths -> two group exchanges + one single-table exchange, not six exchanges
+        assert pull_launches <= 2 * 8 + 6, pull_launches
+    eng.check()
+    probe = torch.arange(300)
+    for k, t in enumerate(tids):
+        got = kk.pull_sparse_table(t, probe.to(dev)).cpu()
+        assert torch.allclose(got, shard.pull_sparse(t, probe), atol=1e-4), k
+    # a combined push that is not preceded by its pull looks the ids up again
+    ids2 = [torch.arange(5 + k, device=dev) for k in range(len(dims))]
+    kk.combine_push_sparse_table(tids, ids2, [torch.zeros(5 + k, d, device=dev) for k, d in enumerate(dims)])
+    eng.check()
+
+
+def test_combined_tables_share_one_exchange():
+    kk.initialize("gpu", table_capacity=1 << 12, seed=0)
+    _combined_scenario(torch.device("cuda", torch.cuda.current_device()))
+
+
+def test_combine_embedding_trains_through_the_group_exchange():
+    """kk.CombineEmbedding forward + backward through autograd on the group exchange."""
+    kk.initialize("gpu", table_capacity=1 << 12, seed=0)
+    emb = kk.CombineEmbedding([4, 4, 4], initializers=[kk.ConstantInitializer(1.0)] * 3, names=["a", "b", "c"])
+    opt = kk.Optimizer("m", emb.named_parameters(), 0.5, kk.SGD())
+    ids = [torch.tensor([1, 2, 2, 3], device=DEV), torch.tensor([2, 2], device=DEV), torch.tensor([9], device=DEV)]
+    outs = emb(ids)
+    assert [tuple(o.shape) for o in outs] == [(4, 4), (2, 4), (1, 4)]
+    (outs[0].sum() + 2.0 * outs[1].sum() + 3.0 * outs[2].sum()).backward()
+    opt.step()
+    tids = emb.combine_sparse_table.table_ids()
+    a = kk.pull_sparse_table(tids[0], torch.tensor([1, 2, 3], device=DEV)).cpu()
+    b = kk.pull_sparse_table(tids[1], torch.tensor([2], device=DEV)).cpu()
+    c = kk.pull_sparse_table(tids[2], torch.tensor([9], device=DEV)).cpu()
+    assert torch.allclose(a, torch.tensor([[0.5] * 4, [0.0] * 4, [0.5] * 4]))      # id 2 occurs twice in table a
+    assert torch.allclose(b, torch.full((1, 4), 1.0 - 0.5 * 2.0 * 2))              # twice, gradient 2 each
+    assert torch.allclose(c, torch.full((1, 4), 1.0 - 0.5 * 3.0))
+    kk.native.engine().check()

@@ -39,6 +39,14 @@ def test_back_to_back_exchanges_match_one_shard(world):
     assert "MULTI_GPU_STRESS ok" in out, out[-2000:]
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_combined_tables_one_exchange_across_ranks(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = run_ranks("mp_gpu_combined_worker.py", world)
+    assert "MULTI_GPU_COMBINED ok" in out, out[-2000:]
+
+
 def test_nccl_baseline_exchange_matches_one_shard(tmp_path):
     """The NCCL-only path must give the same tables as the fused path's oracle."""
     if torch.cuda.device_count() < 2:
