@@ -592,8 +592,24 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("export_sparse", [](CpuShard& s, uint64_t id) { return columns_to_py(s.ExportSparse(id)); })
       .def("import_sparse",
            [](CpuShard& s, uint64_t id, const torch::Tensor& ids, const torch::Tensor& vals, const py::dict& states,
-              const py::dict& states_i) {
-             s.ImportSparse(id, columns_from_py(s.SparseDim(id), ids, vals, states, states_i));
+              const py::dict& states_i, bool overwrite) {
+             s.ImportSparse(id, columns_from_py(s.SparseDim(id), ids, vals, states, states_i), overwrite);
+           },
+           py::arg("id"), py::arg("ids"), py::arg("vals"), py::arg("states"), py::arg("states_i"),
+           py::arg("overwrite") = true)
+      .def("contains_sparse",
+           [](CpuShard& s, uint64_t id, const torch::Tensor& ids) {
+             need_cpu(ids, "ids", torch::kInt64);
+             auto out = torch::zeros({ids.numel()}, torch::kUInt8);
+             s.ContainsSparse(id, reinterpret_cast<const uint64_t*>(ids.data_ptr<int64_t>()), ids.numel(),
+                              out.data_ptr<uint8_t>());
+             return out;
+           })
+      .def("export_sparse_rows",
+           [](CpuShard& s, uint64_t id, const torch::Tensor& ids) {
+             need_cpu(ids, "ids", torch::kInt64);
+             return columns_to_py(s.ExportSparseRows(id, reinterpret_cast<const uint64_t*>(ids.data_ptr<int64_t>()),
+                                                     ids.numel()));
            })
       .def("filter_sparse", [](CpuShard& s, uint64_t id, int mode, uint64_t salt, uint32_t world, uint32_t rank,
                                const Router* ring, uint64_t node) {

@@ -364,13 +364,48 @@ ckpt::SparseColumns CpuShard::ExportSparse(uint64_t id) const {
   return c;
 }
 
-void CpuShard::ImportSparse(uint64_t id, const ckpt::SparseColumns& c) {
+void CpuShard::ContainsSparse(uint64_t id, const uint64_t* ids, int64_t n, uint8_t* out) const {
+  const Sparse& t = sparse(id);
+  std::lock_guard<std::mutex> g(t.mu);
+  for (int64_t i = 0; i < n; ++i) out[i] = t.index.find(ids[i]) != t.index.end() ? 1 : 0;
+}
+
+ckpt::SparseColumns CpuShard::ExportSparseRows(uint64_t id, const uint64_t* ids, int64_t n) const {
+  const Sparse& t = sparse(id);
+  std::lock_guard<std::mutex> g(t.mu);
+  ckpt::SparseColumns c;
+  c.dim = t.dim;
+  std::vector<int64_t> rows;
+  for (int64_t i = 0; i < n; ++i) {
+    auto it = t.index.find(ids[i]);
+    if (it == t.index.end()) continue;
+    c.ids.push_back(ids[i]);
+    rows.push_back(it->second);
+  }
+  c.vals.resize(rows.size() * t.dim);
+  for (size_t r = 0; r < rows.size(); ++r) std::memcpy(c.vals.data() + r * t.dim, t.val.data() + rows[r] * t.dim, t.dim * 4);
+  for (int k = 0; k < 3; ++k) {
+    if (t.s[k].empty() && !(optim_.SlabUsed(k) && rows.empty())) continue;
+    std::vector<float>& dst = c.states[SlabStateType(optim_, k)];
+    dst.resize(rows.size() * t.dim);
+    for (size_t r = 0; r < rows.size(); ++r) std::memcpy(dst.data() + r * t.dim, t.s[k].data() + rows[r] * t.dim, t.dim * 4);
+  }
+  if (optim_.NeedsSteps()) {
+    std::vector<int64_t>& st = c.states_i[static_cast<uint32_t>(StateType::kSteps)];
+    st.resize(rows.size());
+    for (size_t r = 0; r < rows.size(); ++r) st[r] = t.steps[rows[r]];
+  }
+  return c;
+}
+
+void CpuShard::ImportSparse(uint64_t id, const ckpt::SparseColumns& c, bool overwrite) {
   Sparse& t = sparse(id);
   std::lock_guard<std::mutex> g(t.mu);
   KB_CHECK(c.dim == t.dim || c.ids.empty(), err::kSparseDimensionUnCompatible, "imported rows have another dimension");
   auto steps_it = c.states_i.find(static_cast<uint32_t>(StateType::kSteps));
   for (size_t i = 0; i < c.ids.size(); ++i) {
     auto it = t.index.find(c.ids[i]);
+    if (it != t.index.end() && !overwrite) continue;
     const int64_t row = it != t.index.end() ? it->second : t.AddRow(c.ids[i], optim_);
     std::memcpy(t.val.data() + row * t.dim, c.vals.data() + i * t.dim, t.dim * 4);
     for (int k = 0; k < 3; ++k) {

@@ -62,7 +62,12 @@ class CpuShard {
   Value ExportDense(uint64_t id) const;
   void ImportDense(uint64_t id, const std::string& name, const Value& v);
   ckpt::SparseColumns ExportSparse(uint64_t id) const;
-  void ImportSparse(uint64_t id, const ckpt::SparseColumns& cols);
+  // overwrite = false keeps the rows the table already holds (a row that arrived earlier is newer).
+  void ImportSparse(uint64_t id, const ckpt::SparseColumns& cols, bool overwrite = true);
+  // out[i] = 1 if the table holds ids[i].
+  void ContainsSparse(uint64_t id, const uint64_t* ids, int64_t n, uint8_t* out) const;
+  // Value, optimizer state and step count of those of the given ids that the table holds (others are skipped).
+  ckpt::SparseColumns ExportSparseRows(uint64_t id, const uint64_t* ids, int64_t n) const;
   // Drops the rows for which keep(id) is false; returns how many were dropped.
   int64_t FilterSparse(uint64_t id, const ckpt::RowFilter& keep);
 

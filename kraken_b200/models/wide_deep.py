@@ -65,7 +65,6 @@ class MultiHotWideAndDeep(torch.nn.Module):
 
     def forward(self, dense: torch.Tensor, bags: kk.JaggedTensor) -> torch.Tensor:
         from ..pytorch import native
-        from ..pytorch.jagged_embedding_funcs import FusedJaggedLookupFunction
 
         k = bags.num_bags()
         B = k // self.num_fields

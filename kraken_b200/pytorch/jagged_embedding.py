@@ -9,8 +9,8 @@ import torch
 from . import native
 from .embedding import CombineEmbedding, Embedding
 from .initializer import Initializer
-from .jagged_embedding_funcs import (FusedJaggedLookupFunction, JaggedEmbeddingMeanFunction,
-                                     JaggedEmbeddingSumFunction)
+from .jagged_embedding_funcs import (FusedCombineJaggedLookupFunction, FusedJaggedLookupFunction,
+                                     JaggedEmbeddingMeanFunction, JaggedEmbeddingSumFunction)
 from .jagged_tensor import JaggedTensor
 
 _MODES = ("sum", "mean")
@@ -40,9 +40,8 @@ class JaggedEmbedding(torch.nn.Module):
 
     def forward(self, input: JaggedTensor):
         if _fused_available() and input.values().dim() == 1:
-            tid = self.embedding.sparse_table.table_id()
-            return FusedJaggedLookupFunction.apply(tid, input.values(), input.offsets(), input.weights(),
-                                                   self._mode == "mean", self._patch_value)
+            return FusedJaggedLookupFunction.apply(self.embedding.sparse_table, input.values(), input.offsets(),
+                                                   input.weights(), self._mode == "mean", self._patch_value)
         emb = self.embedding(input.values())
         return _pool(emb, input.offsets(), input.weights(), self._mode, self._patch_value)
 
@@ -66,11 +65,13 @@ class CombineJaggedEmbedding(torch.nn.Module):
     def forward(self, inputs: List[JaggedTensor]):
         if len(inputs) != len(self._modes):
             raise ValueError("one JaggedTensor per table is required")
-        table_ids = self.combine_embedding.combine_sparse_table.table_ids()
-        if _fused_available() and all(i.values().dim() == 1 for i in inputs):
-            return [FusedJaggedLookupFunction.apply(table_ids[k], inp.values(), inp.offsets(), inp.weights(),
-                                                    self._modes[k] == "mean", self._patch_values[k])
-                    for k, inp in enumerate(inputs)]
+        if (_fused_available() and hasattr(native.engine(), "combine_pull_sparse_pooled")
+                and all(i.values().dim() == 1 for i in inputs)):
+            outs = FusedCombineJaggedLookupFunction.apply(
+                self.combine_embedding.combine_sparse_table,
+                [(i.values(), i.offsets(), i.weights()) for i in inputs],
+                [m == "mean" for m in self._modes], list(self._patch_values))
+            return list(outs)
         embs = self.combine_embedding([i.values() for i in inputs])
         return [_pool(embs[k], inp.offsets(), inp.weights(), self._modes[k], self._patch_values[k])
                 for k, inp in enumerate(inputs)]

@@ -32,17 +32,37 @@ class JaggedEmbeddingMeanFunction(torch.autograd.Function):
 
 class FusedJaggedLookupFunction(torch.autograd.Function):
     """EmbeddingBag as one fused pull (dedup, exchange, gather and pooling in
-    the same kernel sequence) and one fused push.  GPU engine only."""
+    the same kernel sequence) and one fused push.  GPU engine only.  The first argument is the
+    table's (empty) Parameter: it is what makes autograd call ``backward``."""
 
     @staticmethod
-    def forward(ctx, sparse_table_id, values, offsets, weights, mean, patch_value):
+    def forward(ctx, sparse_table, values, offsets, weights, mean, patch_value):
         eng = native.engine()
-        out, ticket = eng.pull_sparse_pooled(sparse_table_id, values, offsets, weights=weights, mean=mean,
-                                             patch_value=patch_value)
-        ctx.table_id, ctx.ticket, ctx.values = sparse_table_id, ticket, values
+        tid = sparse_table.table_id()
+        out, ticket = eng.pull_sparse_pooled(tid, values, offsets, weights=weights, mean=mean, patch_value=patch_value)
+        ctx.table_id, ctx.ticket, ctx.values = tid, ticket, values
         return out
 
     @staticmethod
     def backward(ctx, grads):
         native.engine().push_sparse_pooled(ctx.table_id, ctx.ticket, grads.contiguous(), ctx.values)
         return None, None, None, None, None, None
+
+
+class FusedCombineJaggedLookupFunction(torch.autograd.Function):
+    """Bags of several tables pooled through the combined exchange: tables of equal row width (and equal
+    patch value) share one dedup, one dispatch, one pooled gather and one push
+    (kraken/pytorch/combine_jagged_embedding.py:11-76 over kraken/worker/emitter.cc:185-278).
+    ``inputs`` is a list of (values, offsets, weights-or-None) per table."""
+
+    @staticmethod
+    def forward(ctx, combine_sparse_table, inputs, means, patch_values):
+        eng = native.engine()
+        outs, handles = eng.combine_pull_sparse_pooled(combine_sparse_table.table_ids(), inputs, means, patch_values)
+        ctx.handles = handles
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        native.engine().combine_push_sparse_pooled(ctx.handles, list(grads))
+        return None, None, None, None

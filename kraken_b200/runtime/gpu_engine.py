@@ -337,6 +337,88 @@ class GpuEngine(Engine):
                     flat = [self._prep_ids(indices[p]).reshape(-1) for p in pos]
                     ch.push(g, self.lr_dev, ids_cat=torch.cat(flat), counts=[int(f.numel()) for f in flat])
 
+    def combine_pull_sparse_pooled(self, table_ids: Sequence[int], inputs, means: Sequence[bool],
+                                   patch_values: Sequence[float]):
+        """EmbeddingBag lookups of several tables.  ``inputs[k]`` = (values, offsets, weights or None) of table
+        k.  Tables of equal row width and patch value go through ONE combined exchange whose pooled gather
+        handles per-bag sum / mean; the others take the single-table fused path.  Returns (pooled outputs in
+        table order, handles for ``combine_push_sparse_pooled``)."""
+        n_tab = len(table_ids)
+        if not (n_tab == len(inputs) == len(means) == len(patch_values)):
+            raise C.KrakenError("table_ids, inputs, means and patch_values differ in length")
+        outs: List[Optional[torch.Tensor]] = [None] * n_tab
+        handles = []
+        classes: Dict[Tuple[int, float], List[int]] = {}
+        if len(set(table_ids)) == n_tab:
+            for pos, t in enumerate(table_ids):
+                classes.setdefault((self._table(t, "sparse").dimension, float(patch_values[pos])), []).append(pos)
+        else:
+            classes = {(-pos - 1, 0.0): [pos] for pos in range(n_tab)}  # a table named twice: one exchange each
+        for (dim, patch), pos in classes.items():
+            if len(pos) == 1:
+                p = pos[0]
+                v, o, w = inputs[p]
+                out, ticket = self.pull_sparse_pooled(table_ids[p], v, o, weights=w, mean=bool(means[p]),
+                                                      patch_value=float(patch_values[p]))
+                outs[p] = out
+                handles.append(("single", int(table_ids[p]), ticket, v, [p]))
+                continue
+            tids = tuple(int(table_ids[p]) for p in pos)
+            vals = [self._prep_ids(inputs[p][0]).reshape(-1) for p in pos]
+            counts = [int(v.numel()) for v in vals]
+            offs, bags, base = [], [], 0
+            for k, p in enumerate(pos):
+                o = inputs[p][1].detach().to(self.device, torch.int64)
+                offs.append(o + base if k == 0 else o[1:] + base)
+                bags.append(int(o.numel()) - 1)
+                base += counts[k]
+            weights = None
+            if any(inputs[p][2] is not None for p in pos):
+                weights = torch.cat([inputs[p][2].detach().to(self.device, torch.float32).reshape(-1)
+                                     if inputs[p][2] is not None else torch.ones(counts[k], device=self.device)
+                                     for k, p in enumerate(pos)])
+            bag_mean = torch.cat([torch.full((bags[k],), 1 if means[p] else 0, dtype=torch.uint8, device=self.device)
+                                  for k, p in enumerate(pos)])
+            ch = self._group_channel(tids, sum(counts))
+            for t, c in zip(tids, counts):
+                self._ensure_room(t, c)
+            with self._region("pull"):
+                rows, ticket = ch.pull(torch.cat(vals), counts, bag_offsets=torch.cat(offs).contiguous(),
+                                       weights=weights, bag_mean=bag_mean, patch_value=patch)
+            for p, part in zip(pos, rows.split(bags)):
+                outs[p] = part
+            handles.append(("group", tids, ticket, (vals, counts, bags), list(pos)))
+        return outs, handles
+
+    def combine_push_sparse_pooled(self, handles, grads: Sequence[Optional[torch.Tensor]]) -> None:
+        for kind, key, ticket, ids, pos in reversed(handles):
+            if kind == "single":
+                g = grads[pos[0]]
+                if g is None:
+                    continue
+                self.push_sparse_pooled(key, ticket, g.contiguous(), ids)
+                continue
+            ch = self.group_channels[key]
+            dim = ch.dim
+            vals, counts, bags = ids
+            parts = []
+            for k, p in enumerate(pos):
+                g = grads[p]
+                if g is None:  # an output autograd never used
+                    g = torch.zeros((bags[k], dim), dtype=torch.float32, device=self.device)
+                elif g.numel() != bags[k] * dim:
+                    raise C.KrakenError("gradient rows do not match the bags of the combined lookup")
+                parts.append(g.detach().to(self.device, torch.float32).reshape(-1, dim))
+            g_cat = torch.cat(parts)
+            with self._region("push"):
+                if ticket.channel is ch and ticket.serial == ch.serial:
+                    ch.push(g_cat, self.lr_dev, ticket=ticket)
+                else:
+                    # another lookup used the channel in between: resolve the ids again, pool shape from the ticket
+                    n = ch._lookup_phase(torch.cat(vals), counts, insert=False)
+                    t2 = Ticket(ch, ch.serial, n, ticket.bag_offsets, ticket.weights, False, ticket.bag_mean)
+                    ch.push(g_cat, self.lr_dev, ticket=t2)
+
     def pull_sparse_pooled(self, table_id: int, values: torch.Tensor, offsets: torch.Tensor,
                            weights: Optional[torch.Tensor] = None, mean: bool = False,
                            bag_mean: Optional[torch.Tensor] = None, patch_value: float = 0.0):

@@ -15,10 +15,14 @@ server may join while training runs.  The scheduler admits it only when every se
 kWork, adds it to the ring (version + 1) and tells the older servers (kNotifyNodeJoin); each of
 them moves the rows and dense tables that the new ring assigns to the newcomer (kTransfer*
 messages, 65,536 rows per message, three attempts each), drops them, adopts the new ring and
-answers; then the newcomer starts to serve.  Unlike the reference there is no proxy phase: while
-a server is transferring it refuses requests with kNodeStatus, and workers retry with a back-off
-and a refreshed ring, re-partitioning only the part of a request that was refused (so a push is
-never applied twice).
+answers.  Training never stops while rows move (the reference's proxy phase, kraken/ps/proxy.cc:29-145,
+kraken/ps/ps_op.cc:10-127,141-164,315-357): every older server adopts the new ring at once, keeps serving
+the rows it still owns and ships the others from a background thread; the newcomer serves from the first
+moment in state kWork|kProxy - a request for a table or row it does not hold yet is answered after fetching
+it on demand from the owner under the OLD ring (kTryFetch* messages, ids 15-18), and what a later transfer
+message brings for a row that is already there is ignored (the copy that arrived first has since been
+updated).  When the last older server reports kNotifyFinishTransfer the newcomer drops the proxy.  A worker
+whose ring is stale gets kRouterVersion, refetches and re-partitions only the refused part of its request.
 """
 from __future__ import annotations
 
@@ -92,43 +96,50 @@ class SchedulerServer:
                 return {"allow": False}, ()
             node_id = (max(self.nodes) + 1) if self.nodes else 0
             old_clients = dict(self.clients)
+            meta_old_ring = _router_hex(self.router)
             self.router.add(node_id, meta["addr"])
             self.nodes[node_id] = meta["addr"]
             self.clients[node_id] = Connecter(meta["addr"])
             new = self.clients[node_id]
             rm = self._router_meta()
-            new.call(Rpc.FETCH_ROUTER, rm)
+            old_ring_hex = meta_old_ring
+            setup = dict(rm)
+            if old_clients:
+                # the newcomer serves at once, fetching what it lacks from the owners under the old ring
+                setup.update({"proxy_old_router": old_ring_hex,
+                              "proxy_nodes": {str(k): self.nodes[k] for k in old_clients},
+                              "self_node": node_id})
+            new.call(Rpc.FETCH_ROUTER, setup)
             if self.model is not None:
                 new.call(Rpc.CREATE_MODEL, self.model)
                 for t in self.tables.values():
                     if t["kind"] == "sparse":
                         new.call(Rpc.CREATE_SPARSE, t)
-            # every older server ships what the new ring takes from it, then adopts the ring
+            # every older server adopts the ring and starts shipping what the new ring takes from it
             note = {**rm, "new_node": node_id, "new_addr": meta["addr"], "tables": list(self.tables.values())}
-            moved = 0
             notified = []
             try:
                 for nid, c in old_clients.items():
-                    out, _ = c.call(Rpc.NOTIFY_NODE_JOIN, note, timeout_ms=600_000)
+                    c.call(Rpc.NOTIFY_NODE_JOIN, note, timeout_ms=60_000)
                     notified.append(nid)
-                    moved += int(out.get("rows_moved", 0))
             except Exception:
-                # A transfer failed: the newcomer is taken out of the ring again.  Servers that had already
-                # moved rows keep the new ring and the scheduler's version moves on, so workers refetch; the
-                # rows they shipped stay on the newcomer, which has to be restarted to join again.
-                log.error("join of node %d failed after %d of %d servers had transferred", node_id, len(notified),
+                # An older server could not be told: the newcomer is taken out of the ring again.  Servers that
+                # had already adopted the new ring are given the old one back under a NEWER version, so workers
+                # refetch; rows they have shipped meanwhile stay on the newcomer, which must be restarted to join.
+                log.error("join of node %d failed after %d of %d servers had been notified", node_id, len(notified),
                           len(old_clients))
-                if not notified:
-                    self.router.remove(node_id)
-                    self.nodes.pop(node_id, None)
-                    self.clients.pop(node_id).close()
-                    back = self._router_meta()
-                    for c in old_clients.values():
-                        c.call(Rpc.FETCH_ROUTER, back)
+                self.router.remove(node_id)
+                self.nodes.pop(node_id, None)
+                self.clients.pop(node_id).close()
+                back = self._router_meta()
+                for c in old_clients.values():
+                    try:
+                        c.call(Rpc.FETCH_ROUTER, {**back, "cancel_transfer": True})
+                    except Exception:
+                        pass
                 raise
             if old_clients:
-                new.call(Rpc.NOTIFY_FINISH_TRANSFER, {"rows_moved": moved})
-                log.info("node %d joined: %d rows moved to it", node_id, moved)
+                log.info("node %d joined: %d servers are shipping rows to it", node_id, len(old_clients))
             return {"allow": True, "node_id": node_id, **rm}, ()
 
     def fetch_router(self, meta, tensors):
@@ -235,6 +246,11 @@ class PsServer:
         self.version = 0
         self.mu = threading.RLock()  # handlers run on one thread per connection: one at a time touches the shard
         self.rows_received = 0
+        self.rows_fetched = 0          # rows this server pulled through the proxy while it was joining
+        self.proxy: Optional[dict] = None   # while joining: {"ring", "vhash", "vnode", "peers": {node: Connecter}, "pending": set}
+        self.tables_meta: Dict[int, dict] = {}
+        self._transfer_thread: Optional[threading.Thread] = None
+        self._cancel_transfer = False
         s = self.station
         s.register(Rpc.HEARTBEAT, lambda m, t: ({"status": self.status}, ()))
         for rpc, fn in ((Rpc.FETCH_ROUTER, self.set_router), (Rpc.CREATE_MODEL, self.create_model),
@@ -246,6 +262,11 @@ class PsServer:
                         (Rpc.NOTIFY_SAVE, self.notify_save), (Rpc.NOTIFY_LOAD, self.notify_load),
                         (Rpc.NOTIFY_NODE_JOIN, self.notify_node_join), (Rpc.TRANSFER_DENSE, self.transfer_dense),
                         (Rpc.TRANSFER_SPARSE_VALUES, self.transfer_sparse_values),
+                        (Rpc.TRANSFER_SPARSE_META, self.transfer_sparse_meta),
+                        (Rpc.TRY_FETCH_DENSE, self.try_fetch_dense),
+                        (Rpc.TRY_COMBINE_FETCH_DENSE, self.try_fetch_dense),
+                        (Rpc.TRY_FETCH_SPARSE_META, self.try_fetch_sparse_meta),
+                        (Rpc.TRY_FETCH_SPARSE_VALUES, self.try_fetch_sparse_values),
                         (Rpc.NOTIFY_FINISH_TRANSFER, self.notify_finish_transfer)):
             s.register(rpc, self._locked(fn))
 
@@ -274,7 +295,8 @@ class PsServer:
         with self.mu:
             self.node_id = meta["node_id"]
             self.set_router(meta, ())
-            self.status = C_STATUS_WORK
+            if self.proxy is None:
+                self.status = C_STATUS_WORK  # first server, or every older server has already finished shipping
         log.info("ps %d joined at %s (ring version %d, %d rows received)", self.node_id, self.addr, self.version,
                  self.rows_received)
 
@@ -282,7 +304,9 @@ class PsServer:
         self.station.stop()
 
     def _check(self, meta) -> None:
-        if self.status != C_STATUS_WORK:
+        # a server that ships rows away (kTransfer) or fetches them on demand (kProxy) keeps serving; one that is
+        # saving, loading or not yet admitted does not (kraken/ps/ps_op.cc:129-139)
+        if not (self.status & C_STATUS_WORK) or (self.status & (C_STATUS_SAVE | C_STATUS_LOAD)):
             raise RpcError(7)
         if meta.get("router_version", self.version) != self.version:
             raise RpcError(8)
@@ -290,7 +314,80 @@ class PsServer:
     def set_router(self, meta, tensors):
         self.router = _router_from_hex(meta["router"])
         self.version = meta["version"]
+        if meta.get("cancel_transfer"):
+            self._cancel_transfer = True
+        if "proxy_old_router" in meta:
+            # this server has just been admitted next to older ones: serve at once, through the proxy
+            ring = _router_from_hex(meta["proxy_old_router"])
+            vn = ring.vnodes()
+            self.node_id = int(meta["self_node"])
+            self.proxy = {"ring": ring, "vhash": np.array([v[0] for v in vn], dtype=np.uint64),
+                          "vnode": np.array([v[1] for v in vn], dtype=np.int64),
+                          "peers": {int(k): Connecter(a, timeout_ms=60_000, compress=1)
+                                    for k, a in meta["proxy_nodes"].items()},
+                          "pending": {int(k) for k in meta["proxy_nodes"]}}
+            self.status = C_STATUS_WORK | C_STATUS_PROXY
         return {}, ()
+
+    # ---------------- proxy phase of a join (newcomer side): fetch on demand from the old owners
+    def _proxy_owner(self, table_id: int, ids: torch.Tensor) -> np.ndarray:
+        hv = mix64(ids.numpy().view(np.uint64)) ^ np.uint64(C.mix64(table_id))
+        idx = np.searchsorted(self.proxy["vhash"], hv, side="left")
+        idx[idx == len(self.proxy["vhash"])] = 0
+        return self.proxy["vnode"][idx]
+
+    def _proxy_sparse(self, table_id: int, ids: torch.Tensor) -> None:
+        """Before a request touches ``ids``: rows this server does not hold yet are asked of their owners
+        under the old ring and inserted if those had them (kraken/ps/ps_op.cc:315-357)."""
+        if self.proxy is None or ids.numel() == 0:
+            return
+        if not self.shard.has_table(table_id):
+            self._proxy_sparse_meta(table_id)
+        ids = ids.reshape(-1).to(torch.int64).contiguous()
+        missing = ids[self.shard.contains_sparse(table_id, ids) == 0]
+        if missing.numel() == 0:
+            return
+        missing = torch.unique(missing)
+        owners = self._proxy_owner(table_id, missing)
+        for node in np.unique(owners):
+            peer = self.proxy["peers"].get(int(node))
+            if peer is None or int(node) not in self.proxy["pending"]:
+                continue  # that owner has finished shipping: what it had for us is here already
+            part = missing[torch.from_numpy(np.nonzero(owners == node)[0])]
+            meta, ts = peer.call(Rpc.TRY_FETCH_SPARSE_VALUES, {"table_id": table_id}, [part])
+            if ts and ts[0].numel() > 0:
+                ns = len(meta["state_keys"])
+                states = {int(k): x for k, x in zip(meta["state_keys"], ts[2:2 + ns])}
+                states_i = {int(k): x for k, x in zip(meta["state_i_keys"], ts[2 + ns:])}
+                self.shard.import_sparse(table_id, ts[0], ts[1], states, states_i, False)
+                self.rows_fetched += int(ts[0].numel())
+
+    def _proxy_sparse_meta(self, table_id: int) -> None:
+        for peer in self.proxy["peers"].values():
+            meta, _ = peer.call(Rpc.TRY_FETCH_SPARSE_META, {"table_id": table_id})
+            if meta.get("exist"):
+                self.create_sparse(meta["table"], ())
+                return
+
+    def _proxy_dense(self, table_ids: Sequence[int]) -> None:
+        if self.proxy is None:
+            return
+        lacking = [int(t) for t in table_ids if not self.shard.has_table(int(t))]
+        if not lacking:
+            return
+        by_owner: Dict[int, List[int]] = {}
+        for t in lacking:
+            by_owner.setdefault(int(self.proxy["ring"].hit(C.mix64(t))), []).append(t)
+        for node, tids in by_owner.items():
+            peer = self.proxy["peers"].get(node)
+            if peer is None:
+                continue
+            meta, ts = peer.call(Rpc.TRY_COMBINE_FETCH_DENSE, {"table_ids": tids})
+            pos = 0
+            for ent in meta["exist"]:
+                n = 1 + len(ent["state_keys"])
+                self._import_dense(ent["table"], ent["state_keys"], ent["states_i"], ts[pos:pos + n])
+                pos += n
 
     def create_model(self, meta, tensors):
         self.shard.init_model(meta["name"], C.OptimType(meta["optim_type"]), meta["optim_conf"])
@@ -298,27 +395,49 @@ class PsServer:
 
     # ---------------- elastic scale-out: rows follow the ring to a server that has just joined
     def notify_node_join(self, meta, tensors):
-        """Older server: move what the new ring assigns to the newcomer, then adopt the ring."""
+        """Older server: adopt the new ring at once and ship, in the background, what it assigns to the
+        newcomer.  Requests for rows this server keeps are served throughout; the rows to ship are frozen by the
+        new ring itself (no worker on the new ring sends them here any more, one on the old ring is refused
+        with kRouterVersion) and stay available to the newcomer's proxy until the shipment is complete."""
         new_ring = _router_from_hex(meta["router"])
-        new_node = int(meta["new_node"])
-        self.status = C_STATUS_WORK | C_STATUS_TRANSFER  # requests are refused (kNodeStatus) until this returns
+        old_ring = self.router
+        self.tables_meta = {int(t["id"]): t for t in meta["tables"]}
+        self.router, self.version = new_ring, meta["version"]
+        self.status = C_STATUS_WORK | C_STATUS_TRANSFER
+        self._cancel_transfer = False
+        self._transfer_thread = threading.Thread(target=self._transfer_to, daemon=True,
+                                                 args=(meta, old_ring, new_ring, int(meta["new_node"])))
+        self._transfer_thread.start()
+        return {}, ()
+
+    def _transfer_to(self, meta, old_ring, new_ring, new_node: int) -> None:
+        """kraken/ps/ps.cc:336-372 (TransferTo): dense tables, then sparse rows in batches, then the rows that
+        moved are dropped and the newcomer is told that this server has finished.  The shard lock is held only
+        while a batch is copied out, never across a message to the newcomer."""
         moved = 0
         try:
             peer = Connecter(meta["new_addr"], timeout_ms=60_000, compress=1)  # server to server: compressed
             for t in meta["tables"]:
                 tid = int(t["id"])
-                if not self.shard.has_table(tid):
-                    continue
+                if self._cancel_transfer:
+                    return
+                with self.mu:
+                    if not self.shard.has_table(tid):
+                        continue
+                    if t["kind"] == "dense":
+                        ship = old_ring.hit(C.mix64(tid)) == self.node_id and new_ring.hit(C.mix64(tid)) == new_node
+                        v = self.shard.export_dense(tid) if ship else None
+                    else:
+                        cols = self.shard.export_sparse(tid)
                 if t["kind"] == "dense":
-                    if self.router.hit(C.mix64(tid)) == self.node_id and new_ring.hit(C.mix64(tid)) == new_node:
-                        v = self.shard.export_dense(tid)
+                    if v is not None:
                         keys = sorted(int(k) for k in v["states"])
                         _send_with_retries(peer, Rpc.TRANSFER_DENSE,
-                                           {"table": t, "state_keys": keys,
+                                           {"table": t, "state_keys": keys, "from": self.node_id,
                                             "states_i": {str(k): int(x) for k, x in v["states_i"].items()}},
                                            [v["val"]] + [v["states"][k] for k in keys])
                     continue
-                cols = self.shard.export_sparse(tid)
+                _send_with_retries(peer, Rpc.TRANSFER_SPARSE_META, {"table": t, "from": self.node_id}, ())
                 ids = cols["ids"]
                 if ids.numel() == 0:
                     continue
@@ -326,40 +445,97 @@ class PsServer:
                 skeys = sorted(int(k) for k in cols["states"])
                 ikeys = sorted(int(k) for k in cols["states_i"])
                 for a in range(0, go.numel(), TRANSFER_ROWS):
+                    if self._cancel_transfer:
+                        return
                     sel = go[a:a + TRANSFER_ROWS]
                     _send_with_retries(peer, Rpc.TRANSFER_SPARSE_VALUES,
-                                       {"table_id": tid, "state_keys": skeys, "state_i_keys": ikeys},
+                                       {"table_id": tid, "state_keys": skeys, "state_i_keys": ikeys, "from": self.node_id},
                                        [ids[sel], cols["vals"][sel]] + [cols["states"][k][sel] for k in skeys]
                                        + [cols["states_i"][k][sel] for k in ikeys])
                 moved += int(go.numel())
-                # what the new ring no longer assigns to this server is dropped (kraken/ps/ps.cc:29-123)
-                self.shard.filter_sparse(tid, 2, 0, 1, 0, new_ring, self.node_id)
+            # everything has arrived: what the new ring no longer assigns to this server is dropped
+            # (kraken/ps/ps.cc:29-123), then the newcomer may stop asking this server
+            with self.mu:
+                for t in meta["tables"]:
+                    if t["kind"] == "sparse" and self.shard.has_table(int(t["id"])):
+                        self.shard.filter_sparse(int(t["id"]), 2, 0, 1, 0, new_ring, self.node_id)
+            peer.call(Rpc.NOTIFY_FINISH_TRANSFER, {"from": self.node_id, "rows_moved": moved}, timeout_ms=60_000)
             peer.close()
-            self.router, self.version = new_ring, meta["version"]
+            log.info("ps %d shipped %d rows to node %d", self.node_id, moved, new_node)
+        except Exception as e:  # the rows stay here and stay reachable through the newcomer's proxy
+            log.error("ps %d: transfer to node %d failed: %s", self.node_id, new_node, e)
         finally:
-            self.status = C_STATUS_WORK
-        return {"rows_moved": moved}, ()
+            with self.mu:
+                self.status &= ~C_STATUS_TRANSFER
+
+    def _import_dense(self, t: dict, state_keys, states_i, tensors) -> None:
+        tid = int(t["id"])
+        if self.shard.has_table(tid):
+            return  # fetched through the proxy earlier: that copy has been updated since (ps.cc:745-750)
+        self.shard.create_dense_table(tid, t["name"], tensors[0].view(*t["shape"]))
+        v = {"val": tensors[0].view(*t["shape"]),
+             "states": {int(k): x for k, x in zip(state_keys, tensors[1:])},
+             "states_i": {int(k): int(x) for k, x in states_i.items()}}
+        self.shard.import_dense(tid, t["name"], v)
 
     def transfer_dense(self, meta, tensors):
-        t = meta["table"]
-        if not self.shard.has_table(int(t["id"])):
-            self.shard.create_dense_table(int(t["id"]), t["name"], tensors[0].view(*t["shape"]))
-        v = {"val": tensors[0].view(*t["shape"]),
-             "states": {int(k): x for k, x in zip(meta["state_keys"], tensors[1:])},
-             "states_i": {int(k): int(x) for k, x in meta["states_i"].items()}}
-        self.shard.import_dense(int(t["id"]), t["name"], v)
+        self._import_dense(meta["table"], meta["state_keys"], meta["states_i"], tensors)
+        return {}, ()
+
+    def transfer_sparse_meta(self, meta, tensors):
+        if not self.shard.has_table(int(meta["table"]["id"])):
+            self.create_sparse(meta["table"], ())
         return {}, ()
 
     def transfer_sparse_values(self, meta, tensors):
         ns = len(meta["state_keys"])
         states = {int(k): x for k, x in zip(meta["state_keys"], tensors[2:2 + ns])}
         states_i = {int(k): x for k, x in zip(meta["state_i_keys"], tensors[2 + ns:])}
-        self.shard.import_sparse(int(meta["table_id"]), tensors[0], tensors[1], states, states_i)
+        # rows already here came through the proxy and may have been updated since: they win
+        self.shard.import_sparse(int(meta["table_id"]), tensors[0], tensors[1], states, states_i, False)
         self.rows_received += int(tensors[0].numel())
         return {}, ()
 
     def notify_finish_transfer(self, meta, tensors):
+        if self.proxy is not None and "from" in meta:
+            self.proxy["pending"].discard(int(meta["from"]))
+            if not self.proxy["pending"]:
+                for c in self.proxy["peers"].values():
+                    c.close()
+                self.proxy = None
+                self.status = C_STATUS_WORK
+                log.info("ps %d: all transfers finished (%d rows received, %d fetched on demand)", self.node_id,
+                         self.rows_received, self.rows_fetched)
         return {"rows_received": self.rows_received}, ()
+
+    # ---------------- proxy phase (older server's side): hand out what the newcomer asks for
+    def try_fetch_dense(self, meta, tensors):
+        tids = meta["table_ids"] if "table_ids" in meta else [meta["table_id"]]
+        exist, out = [], []
+        for tid in tids:
+            tid = int(tid)
+            t = self.tables_meta.get(tid)
+            if t is None or not self.shard.has_table(tid):
+                continue
+            v = self.shard.export_dense(tid)
+            keys = sorted(int(k) for k in v["states"])
+            exist.append({"table": t, "state_keys": keys, "states_i": {str(k): int(x) for k, x in v["states_i"].items()}})
+            out += [v["val"]] + [v["states"][k] for k in keys]
+        return {"exist": exist}, out
+
+    def try_fetch_sparse_meta(self, meta, tensors):
+        t = self.tables_meta.get(int(meta["table_id"]))
+        return ({"exist": True, "table": t} if t is not None and t["kind"] == "sparse" else {"exist": False}), ()
+
+    def try_fetch_sparse_values(self, meta, tensors):
+        tid = int(meta["table_id"])
+        if not self.shard.has_table(tid):
+            return {"state_keys": [], "state_i_keys": []}, ()
+        cols = self.shard.export_sparse_rows(tid, tensors[0].reshape(-1).to(torch.int64).contiguous())
+        skeys = sorted(int(k) for k in cols["states"])
+        ikeys = sorted(int(k) for k in cols["states_i"])
+        return ({"state_keys": skeys, "state_i_keys": ikeys},
+                [cols["ids"], cols["vals"]] + [cols["states"][k] for k in skeys] + [cols["states_i"][k] for k in ikeys])
 
     def create_dense(self, meta, tensors):
         self.shard.create_dense_table(meta["id"], meta["name"], tensors[0])
@@ -372,10 +548,12 @@ class PsServer:
 
     def pull_dense(self, meta, tensors):
         self._check(meta)
+        self._proxy_dense(meta["table_ids"])
         return {}, [self.shard.pull_dense(t) for t in meta["table_ids"]]
 
     def push_dense(self, meta, tensors):
         self._check(meta)
+        self._proxy_dense([meta["table_id"]])
         if meta.get("coo"):
             self.shard.push_dense_coo(meta["table_id"], tensors[0], tensors[1], meta["lr"])
         else:
@@ -384,10 +562,12 @@ class PsServer:
 
     def pull_sparse(self, meta, tensors):
         self._check(meta)
+        self._proxy_sparse(meta["table_id"], tensors[0])
         return {}, [self.shard.pull_sparse(meta["table_id"], tensors[0])]
 
     def push_sparse(self, meta, tensors):
         self._check(meta)
+        self._proxy_sparse(meta["table_id"], tensors[0])
         code = self.shard.push_sparse(meta["table_id"], tensors[0], tensors[1], meta["lr"])
         if code != 0:
             raise RpcError(code)
@@ -396,12 +576,15 @@ class PsServer:
     def combine_pull_sparse(self, meta, tensors):
         """Several tables in one round trip (kraken/ps/ps_op.cc CombinePullSparseTable): ids of table k in tensor k."""
         self._check(meta)
+        for t, ids in zip(meta["table_ids"], tensors):
+            self._proxy_sparse(t, ids)
         return {}, [self.shard.pull_sparse(t, ids) for t, ids in zip(meta["table_ids"], tensors)]
 
     def combine_push_sparse(self, meta, tensors):
         """Tensors are (ids, summed gradients) pairs in the order of ``table_ids``."""
         self._check(meta)
         for k, t in enumerate(meta["table_ids"]):
+            self._proxy_sparse(t, tensors[2 * k])
             code = self.shard.push_sparse(t, tensors[2 * k], tensors[2 * k + 1], meta["lr"])
             if code != 0:
                 raise RpcError(code)
@@ -456,7 +639,8 @@ class PsServer:
         return {}, ()
 
 
-C_STATUS_INIT, C_STATUS_WORK, C_STATUS_TRANSFER, C_STATUS_SAVE, C_STATUS_LOAD = 1, 2, 8, 16, 32
+# bit flags of kraken/common/info.h:26-37
+C_STATUS_INIT, C_STATUS_WORK, C_STATUS_PROXY, C_STATUS_TRANSFER, C_STATUS_SAVE, C_STATUS_LOAD = 1, 2, 4, 8, 16, 32
 TRANSFER_ROWS = 65536  # rows per kTransferSparseValues message (the reference sends 1024: kraken/ps/ps.cc:251)
 
 
@@ -511,6 +695,7 @@ class RemoteEngine(Engine):
         self.compress = 1 if (cfg.compress is not None and int(getattr(cfg.compress, "value", cfg.compress)) != 0) else 0
         self.ps: Dict[int, Connecter] = {}
         self.dct_states: Dict[int, object] = {}
+        self.refusals: Dict[int, int] = {}   # error code -> how often a server refused a request of this worker
         self._refresh_router()
 
     def _refresh_router(self) -> None:
@@ -532,11 +717,15 @@ class RemoteEngine(Engine):
 
     RETRY_CODES = (7, 8)  # kNodeStatus (server busy transferring / saving), kRouterVersion (our ring is old)
 
-    def _backoff(self, attempt: int) -> None:
+    def _backoff(self, attempt: int, code: int = 7) -> None:
+        """After a refusal: count it (``refusals[code]``), wait if the server said it was busy, refetch the ring.
+        A stale ring (8) needs no wait the first time: the scheduler already has the new one."""
         import time
+        self.refusals[code] = self.refusals.get(code, 0) + 1
         if attempt >= 60:
             raise RpcError(7, "the servers stayed busy")
-        time.sleep(min(0.02 * (1.5 ** attempt), 1.0))
+        if code != 8 or attempt > 0:
+            time.sleep(min(0.02 * (1.5 ** attempt), 1.0))
         self._refresh_router()
 
     def _call_dense(self, table_id: int, rpc: int, meta: dict, tensors=()):
@@ -550,7 +739,7 @@ class RemoteEngine(Engine):
             except RpcError as e:
                 if e.code not in self.RETRY_CODES:
                     raise
-                self._backoff(attempt)
+                self._backoff(attempt, e.code)
                 attempt += 1
 
     def _call_sparse(self, rpc: int, table_id: int, meta: dict, ids: torch.Tensor, payload, done, attempt: int = 0):
@@ -568,7 +757,7 @@ class RemoteEngine(Engine):
             except RpcError as e:
                 if e.code not in self.RETRY_CODES:
                     raise
-                self._backoff(attempt)
+                self._backoff(attempt, e.code)
                 self._call_sparse(rpc, table_id, meta, ids[sel], payload[sel] if payload is not None else None,
                                   lambda pos, ts, sel=sel: done(sel[pos], ts), attempt + 1)
                 continue
@@ -680,7 +869,7 @@ class RemoteEngine(Engine):
             except RpcError as e:
                 if e.code not in self.RETRY_CODES:
                     raise
-                self._backoff(0)
+                self._backoff(0, e.code)
                 single = Rpc.PULL_SPARSE if payloads is None else Rpc.PUSH_SPARSE
                 for k in ks:
                     self._call_sparse(single, table_ids[k], meta, uniqs[k][sels[k]],

@@ -52,6 +52,10 @@ class Rpc:
     TRANSFER_DENSE = 12
     TRANSFER_SPARSE_META = 13
     TRANSFER_SPARSE_VALUES = 14
+    TRY_FETCH_DENSE = 15
+    TRY_COMBINE_FETCH_DENSE = 16
+    TRY_FETCH_SPARSE_META = 17
+    TRY_FETCH_SPARSE_VALUES = 18
     PULL_DENSE = 19
     COMBINE_PULL_DENSE = 20
     PUSH_DENSE = 21

@@ -179,3 +179,39 @@ def test_combine_embedding_trains_through_the_group_exchange():
     assert torch.allclose(b, torch.full((1, 4), 1.0 - 0.5 * 2.0 * 2))              # twice, gradient 2 each
     assert torch.allclose(c, torch.full((1, 4), 1.0 - 0.5 * 3.0))
     kk.native.engine().check()
+
+
+def test_jagged_embeddings_train_on_the_gpu_engine():
+    """kk.JaggedEmbedding and kk.CombineJaggedEmbedding (sum / mean bags, an empty bag, per-id weights) must
+    reach the tables through autograd: one SGD step, rows compared with the same step on the CPU engine."""
+    def run(backend):
+        kk.stop()
+        kk.initialize(backend, table_capacity=1 << 10, seed=0)
+        torch.manual_seed(0)
+        dev = "cuda" if backend == "gpu" else "cpu"
+        single = kk.JaggedEmbedding(4, initializer=kk.ConstantInitializer(0.5), name="s", mode="mean", patch_value=-1.0)
+        combo = kk.CombineJaggedEmbedding([4, 4, 2], initializers=[kk.ConstantInitializer(0.25)] * 3,
+                                          names=["c0", "c1", "c2"], modes=["sum", "mean", "sum"],
+                                          patch_values=[0.0, 0.0, 0.0])
+        mods = torch.nn.ModuleList([single, combo])
+        opt = kk.Optimizer("m", mods.named_parameters(), 0.5, kk.SGD())
+        jt = lambda vals, offs, w=None: kk.JaggedTensor(torch.tensor(vals, device=dev), torch.tensor(offs, device=dev),
+                                                        None if w is None else torch.tensor(w, device=dev))
+        a = single(jt([1, 2, 2, 7], [0, 3, 3, 4]))                      # bags: {1,2,2}, {}, {7}
+        outs = combo([jt([1, 1, 3], [0, 2, 3], [1.0, 2.0, 0.5]), jt([1, 4, 5, 6], [0, 1, 4]), jt([9], [0, 1])])
+        loss = a.sum() + outs[0].sum() * 2.0 + outs[1].sum() + outs[2].sum() * 3.0
+        empty_bag = a[1].detach().cpu().clone()
+        loss.backward()
+        opt.step()
+        tids = [single.embedding.sparse_table.table_id()] + list(combo.combine_embedding.combine_sparse_table.table_ids())
+        probes = [[1, 2, 7], [1, 3], [1, 4, 5, 6], [9]]
+        rows = [kk.pull_sparse_table(t, torch.tensor(p, device=dev)).cpu() for t, p in zip(tids, probes)]
+        kk.stop()
+        return empty_bag, rows
+
+    e_gpu, r_gpu = run("gpu")
+    e_cpu, r_cpu = run("cpu")
+    assert torch.equal(e_gpu, torch.full((4,), -1.0)) and torch.equal(e_cpu, e_gpu)
+    for g, c in zip(r_gpu, r_cpu):
+        assert torch.allclose(g, c, atol=1e-6), (g, c)
+    assert not torch.allclose(r_gpu[0], torch.full_like(r_gpu[0], 0.5))   # the rows did move
