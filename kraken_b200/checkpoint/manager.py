@@ -40,12 +40,17 @@ def save_model(engine, saved_dir: str = "") -> bool:
     out = C.ckpt_prepare_save_dir(saved_dir, engine.rank, engine.cfg.max_save_count)
     C.ckpt_save_router(out, engine.router)
     C.ckpt_save_model(out, engine.model_meta())
-    rows = 0
+    rows = nbytes = 0
     for tid, info in sorted(engine.tables.items()):
         if info.kind == "dense":
             value = engine.export_dense(tid)  # collective on the GPU engine
             if engine.dense_owner(tid) == engine.rank:
                 C.ckpt_save_dense(out, tid, info.name, value)
+        elif hasattr(engine, "save_sparse_streamed"):
+            # GPU shards: device-side ordering, chunks through pinned buffers, multi-threaded writer
+            done = engine.save_sparse_streamed(tid, out, info)
+            rows += done["rows"]
+            nbytes += done["bytes"]
         else:
             cols = engine.export_sparse(tid)
             ids = cols["ids"].cpu()
@@ -54,7 +59,10 @@ def save_model(engine, saved_dir: str = "") -> bool:
                                cols["vals"].cpu(), {k: v.cpu() for k, v in cols["states"].items()},
                                {k: v.cpu() for k, v in cols["states_i"].items()})
     _barrier(engine)
-    log.info("rank %d saved %d sparse rows to %s in %.2fs", engine.rank, rows, out, time.time() - t0)
+    dt = time.time() - t0
+    log.info("rank %d saved %d sparse rows to %s in %.2fs%s", engine.rank, rows, out, dt,
+             f" ({nbytes / dt / 1e9:.2f} GB/s)" if nbytes else "")
+    engine.last_checkpoint = {"op": "save", "rows": rows, "bytes": nbytes, "seconds": dt}
     return True
 
 
@@ -71,6 +79,7 @@ def load_model(engine, load_dir: str) -> bool:
     old_router = C.ckpt_load_router(first)
     log.info("loading model %r written by %d shard(s); saved router: %s", meta.name, len(shard_dirs), old_router)
     engine.init_model(meta.name, meta.optim_type, dict(meta.optim_conf))
+    rows_read, t_load = 0, time.time()
 
     for tid in sorted(meta.tables):
         t = meta.tables[tid]
@@ -88,9 +97,16 @@ def load_model(engine, load_dir: str) -> bool:
             new_id = engine.register_sparse_table(t.name, t.dimension, torch.float32, t.init_type, dict(t.init_conf),
                                                   table_id=tid)
             salt = engine._salt(new_id)
+            if hasattr(engine, "import_sparse_routed"):
+                # GPU shards: every rank reads 1 / world of the shard files (all their rows, multi-threaded) and
+                # the rows are forwarded to their owners under the CURRENT placement on the device
+                mine = [d for k, (_, d) in enumerate(sorted(shard_dirs.items())) if k % engine.world == engine.rank]
+                rows_read += engine.import_sparse_routed(new_id, t.name, mine)
+                continue
             for d in shard_dirs.values():
                 cols = C.ckpt_load_sparse(d, t.name, 1, salt, engine.world, engine.rank)
                 if cols is not None and cols["ids"].numel() > 0:
                     engine.import_sparse(new_id, cols)
     _barrier(engine)
+    engine.last_checkpoint = {"op": "load", "rows_read": rows_read, "seconds": time.time() - t_load}
     return True

@@ -538,6 +538,70 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       py::arg("dir"), py::arg("name"), py::arg("filter_mode") = 0, py::arg("salt") = 0, py::arg("world") = 1,
       py::arg("rank") = 0, py::arg("ring") = nullptr, py::arg("table_id") = 0, py::arg("node") = 0);
 
+  // streamed save of a large table: rows arrive in chunks, already in file order (slot by slot, ids ascending
+  // as unsigned numbers inside a slot); CPU tensors (pinned or not), float32 / int64, contiguous
+  py::class_<ckpt::SparseStreamWriter>(m, "SparseStreamWriter")
+      .def(py::init([](const std::string& dir, uint64_t id, const std::string& name, int64_t dim, InitializerType init_type,
+                       const Conf& init_conf, std::vector<uint32_t> state_types, std::vector<uint32_t> int_state_types,
+                       int threads) {
+             ckpt::SparseHeader h;
+             h.id = id;
+             h.name = name;
+             h.dim = dim;
+             h.init_type = init_type;
+             h.init_conf = init_conf;
+             return new ckpt::SparseStreamWriter(dir, h, std::move(state_types), std::move(int_state_types), threads);
+           }),
+           py::arg("dir"), py::arg("id"), py::arg("name"), py::arg("dim"), py::arg("init_type"), py::arg("init_conf"),
+           py::arg("state_types"), py::arg("int_state_types"), py::arg("threads") = 8)
+      .def("begin_slot", &ckpt::SparseStreamWriter::BeginSlot)
+      .def("append",
+           [](ckpt::SparseStreamWriter& w, const torch::Tensor& ids, const torch::Tensor& vals,
+              const std::vector<torch::Tensor>& states, const std::vector<torch::Tensor>& states_i) {
+             need_cpu(ids, "ids", torch::kInt64);
+             need_cpu(vals, "vals", torch::kFloat32);
+             const size_t n = static_cast<size_t>(ids.numel());
+             std::vector<const float*> sp;
+             std::vector<const int64_t*> ip;
+             for (auto& t : states) {
+               need_cpu(t, "state", torch::kFloat32);
+               TORCH_CHECK(t.numel() == vals.numel(), "a state column differs in size from the values");
+               sp.push_back(t.data_ptr<float>());
+             }
+             for (auto& t : states_i) {
+               need_cpu(t, "int state", torch::kInt64);
+               TORCH_CHECK(static_cast<size_t>(t.numel()) == n, "an integer state column differs in size from the ids");
+               ip.push_back(t.data_ptr<int64_t>());
+             }
+             py::gil_scoped_release nogil;
+             w.Append(reinterpret_cast<const uint64_t*>(ids.data_ptr<int64_t>()), vals.data_ptr<float>(), sp.data(),
+                      ip.data(), n);
+           })
+      .def("close", &ckpt::SparseStreamWriter::Close)
+      .def("bytes_written", &ckpt::SparseStreamWriter::bytes_written)
+      .def("row_bytes", &ckpt::SparseStreamWriter::row_bytes);
+  m.def(
+      "ckpt_load_sparse_fast",
+      [](const std::string& dir, const std::string& name, int threads) -> py::object {
+        // None: no such file; False: the file is not in the fixed layout (use ckpt_load_sparse); else all rows
+        ckpt::SparseHeader h;
+        ckpt::SparseColumns c;
+        bool ok, fast = false;
+        {
+          py::gil_scoped_release nogil;
+          ok = ckpt::LoadSparseFast(dir, name, &h, &c, &fast, threads);
+        }
+        if (!ok) return py::none();
+        if (!fast) return py::bool_(false);
+        py::dict d = columns_to_py(c);
+        d["id"] = h.id;
+        d["name"] = h.name;
+        d["init_type"] = h.init_type;
+        d["init_conf"] = h.init_conf;
+        return d;
+      },
+      py::arg("dir"), py::arg("name"), py::arg("threads") = 8);
+
   // ---------------- CPU shard
   py::class_<CpuShard>(m, "CpuShard")
       .def(py::init<uint64_t>(), py::arg("seed") = 0)

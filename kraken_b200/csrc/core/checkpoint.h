@@ -85,5 +85,42 @@ void SaveSparse(const std::string& dir, const SparseHeader& h, const SparseColum
 bool LoadSparse(const std::string& dir, const std::string& name, const RowFilter& filter, SparseHeader* h,
                 SparseColumns* cols);
 
+// ---- large tables: streamed, multi-threaded save and load of the same file format ----
+//
+// Every row of a table written by this framework has the same byte length (same dimension, same
+// state entries in ascending type order), so a row's file offset follows from its index.  The
+// stream writer formats rows that arrive in chunks, already in file order (slot by slot, ids
+// ascending as unsigned numbers inside a slot), with several threads that each pwrite() their part;
+// no sort and no whole-table copy happens on the host.  The fast reader maps a file, checks that
+// every row matches the fixed layout of its first row and extracts the columns with several threads;
+// a file that does not match (written by the reference with per-row state sets, say) is left to LoadSparse.
+class SparseStreamWriter {
+ public:
+  // state_types / int_state_types: StateType codes in ascending order, one column each in Append.
+  SparseStreamWriter(const std::string& dir, const SparseHeader& h, std::vector<uint32_t> state_types,
+                     std::vector<uint32_t> int_state_types, int threads = 8);
+  ~SparseStreamWriter();
+  void BeginSlot(uint64_t rows);  // slots 0..7 in order; `rows` rows follow through Append
+  void Append(const uint64_t* ids, const float* vals, const float* const* states, const int64_t* const* states_i,
+              size_t n);
+  void Close();  // all 8 slots must be complete
+  uint64_t bytes_written() const { return offset_; }
+  size_t row_bytes() const { return row_bytes_; }
+
+ private:
+  int fd_ = -1;
+  int64_t dim_;
+  std::vector<uint32_t> st_, sti_;
+  size_t row_bytes_;
+  uint64_t offset_ = 0, slot_left_ = 0;
+  int slots_begun_ = 0, threads_;
+  std::string path_;
+};
+
+// false: no such file.  *fast = false: the file exists but does not have the fixed layout (use LoadSparse).
+// On success the columns of ALL rows are appended to *cols (no filter) and *h is filled.
+bool LoadSparseFast(const std::string& dir, const std::string& name, SparseHeader* h, SparseColumns* cols, bool* fast,
+                    int threads = 8);
+
 }  // namespace ckpt
 }  // namespace kb

@@ -160,7 +160,8 @@ void table_import(TableHost table, const int64_t* ids, const float* vals, const 
 // Finds ids (no insert); rows[n, dim] gets the values, found[n] 1/0.
 void table_lookup(TableHost table, const int64_t* ids, int n, float* rows, uint8_t* found, cudaStream_t stream);
 // Compacts the occupied slots that pass the filter into the out_* arrays; *out_count receives how many.
-// filter_mode 0: all; 1: OwnerOf(salt, id, world) == rank; 2: OwnerOf(...) != rank; 3: steps >= min_steps.
+// filter_mode 0: all; 1: OwnerOf(salt, id, world) == rank; 2: OwnerOf(...) != rank; 3: steps >= min_steps;
+// 4: id % world == rank (a checkpoint file's slot: world = 8, rank = slot).
 void table_export(TableHost table, int filter_mode, uint64_t salt, int world, int rank, int min_steps,
                   int64_t* out_ids, float* out_vals, float* out_s0, float* out_s1, float* out_s2, int* out_steps,
                   int* out_count, int out_cap, cudaStream_t stream);

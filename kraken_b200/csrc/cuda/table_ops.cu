@@ -113,6 +113,7 @@ __global__ void table_export_kernel(TableView t, int filter_mode, uint64_t salt,
           case 1: take = static_cast<int>(OwnerOf(salt, k, world)) == rank; break;
           case 2: take = static_cast<int>(OwnerOf(salt, k, world)) != rank; break;
           case 3: take = t.steps ? t.steps[slot] >= min_steps : true; break;
+          case 4: take = static_cast<int>(k % static_cast<unsigned long long>(world)) == rank; break;  // id % world == rank
           default: take = true;
         }
       }

@@ -124,6 +124,68 @@ class GpuSparseTable:
         states_i = {0: steps.to(torch.int64)} if steps is not None else {}
         return {"dim": self.dim, "ids": ids, "vals": vals, "states": states, "states_i": states_i}
 
+    def save_streamed(self, out_dir: str, init_type, init_conf, chunk_rows: int = 1 << 21, threads: int = 8) -> dict:
+        """Writes this shard's rows as ``<name>.sparse`` in the reference's file format without a host-side copy
+        of the table: for each of the file's 8 slots (id % 8) the matching rows are compacted on the device,
+        ordered by id (as unsigned numbers) with a device sort, and streamed in chunks through two pinned
+        buffers on a copy stream to a multi-threaded writer (csrc/core/checkpoint.cc: SparseStreamWriter), so the
+        copy of chunk k + 1 overlaps the formatting and writing of chunk k.  Returns {"rows", "bytes"}."""
+        info = self.optim_info
+        cols = sorted((int(info["slab_state_types"][k]), k) for k in range(3) if self.slabs[k] is not None)
+        int_types = [0] if self.steps is not None else []
+        w = C.SparseStreamWriter(out_dir, self.table_id, self.name, self.dim, init_type, dict(init_conf),
+                                 [st for st, _ in cols], int_types, threads)
+        dev = self.device
+        copy_stream = torch.cuda.Stream(device=dev)
+        n_cols = 1 + len(cols)
+        pinned = [{"ids": torch.empty(chunk_rows, dtype=torch.int64).pin_memory(),
+                   "f": [torch.empty((chunk_rows, self.dim), dtype=torch.float32).pin_memory() for _ in range(n_cols)],
+                   "steps": torch.empty(chunk_rows, dtype=torch.int64).pin_memory(), "event": None} for _ in range(2)]
+        total = 0
+        flip = torch.tensor(-(1 << 63), dtype=torch.int64, device=dev)
+        for slot in range(8):
+            part = self.export(filter_mode=4, world=8, rank=slot)
+            n = int(part["ids"].numel())
+            w.begin_slot(n)
+            if n == 0:
+                continue
+            order = torch.argsort(part["ids"] ^ flip)   # ascending as uint64
+            fcols = [part["vals"]] + [part["states"][st] for st, _ in cols]
+            steps = part["states_i"][0] if self.steps is not None else None
+            pending = None
+            for k, a in enumerate(range(0, n, chunk_rows)):
+                sel = order[a:a + chunk_rows]
+                m = int(sel.numel())
+                buf = pinned[k % 2]
+                staged = [part["ids"].index_select(0, sel)] + [c.index_select(0, sel) for c in fcols]
+                staged_steps = steps.index_select(0, sel) if steps is not None else None
+                copy_stream.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(copy_stream):
+                    buf["ids"][:m].copy_(staged[0], non_blocking=True)
+                    for dst, src in zip(buf["f"], staged[1:]):
+                        dst[:m].copy_(src, non_blocking=True)
+                        src.record_stream(copy_stream)
+                    staged[0].record_stream(copy_stream)
+                    if staged_steps is not None:
+                        buf["steps"][:m].copy_(staged_steps, non_blocking=True)
+                        staged_steps.record_stream(copy_stream)
+                    ev = torch.cuda.Event()
+                    ev.record(copy_stream)
+                if pending is not None:        # write the previous chunk while this one crosses PCIe
+                    self._append_chunk(w, *pending)
+                pending = (buf, m, ev, steps is not None)
+            if pending is not None:
+                self._append_chunk(w, *pending)
+            total += n
+            del part, order, fcols
+        w.close()
+        return {"rows": total, "bytes": int(w.bytes_written())}
+
+    @staticmethod
+    def _append_chunk(w, buf, m, event, has_steps) -> None:
+        event.synchronize()
+        w.append(buf["ids"][:m], buf["f"][0][:m], [c[:m] for c in buf["f"][1:]], [buf["steps"][:m]] if has_steps else [])
+
     def import_rows(self, ids: torch.Tensor, vals: torch.Tensor, states: Optional[dict] = None,
                     states_i: Optional[dict] = None) -> None:
         """Inserts (or overwrites) rows with the given values and optimizer state."""

@@ -591,6 +591,81 @@ class GpuEngine(Engine):
     def import_sparse(self, table_id: int, cols: dict) -> None:
         self.sparse[table_id].import_rows(cols["ids"], cols["vals"], cols["states"], cols["states_i"])
 
+    def save_sparse_streamed(self, table_id: int, out_dir: str, info: TableInfo) -> dict:
+        return self.sparse[table_id].save_streamed(out_dir, info.init_type, info.init_conf)
+
+    def import_sparse_routed(self, table_id: int, name: str, dirs: Sequence[str], chunk_rows: int = 1 << 21) -> int:
+        """Checkpoint load for GPU shards.  This rank reads ALL rows of the shard files in ``dirs`` (its 1 / world
+        share of the checkpoint; fixed-layout files with the multi-threaded reader, anything else - a file the
+        reference wrote - with the general one), uploads them in chunks and sends every row to the rank that owns
+        it under the current placement (device-side owner computation, one all-to-all per chunk over NCCL);
+        owners insert what they receive.  Collective: ranks with fewer chunks take part with empty ones.
+        Replaces "every rank parses every file and drops (world - 1) / world of it"."""
+        t = self.sparse[table_id]
+        salt = self._salt(table_id)
+        dev = self.device
+        parts = []
+        for d in dirs:
+            cols = C.ckpt_load_sparse_fast(d, name)
+            if cols is False:
+                cols = C.ckpt_load_sparse(d, name)
+            if cols is not None and cols["ids"].numel() > 0:
+                parts.append(cols)
+        skeys = sorted({int(k) for c in parts for k in c["states"]})
+        ikeys = sorted({int(k) for c in parts for k in c["states_i"]})
+        chunks = [(c, a) for c in parts for a in range(0, int(c["ids"].numel()), chunk_rows)]
+        rounds = len(chunks)
+        if self.world > 1:
+            # every rank must know the same column set and the same number of rounds
+            meta = torch.zeros(2 + 16, dtype=torch.int64, device=dev)
+            meta[0] = rounds
+            for k in skeys:
+                meta[2 + k] = 1
+            for k in ikeys:
+                meta[2 + 8 + k] = 1
+            dist.all_reduce(meta, op=dist.ReduceOp.MAX, group=self.group)
+            rounds = int(meta[0].item())
+            flags = meta[2:].tolist()
+            skeys = [k for k in range(8) if flags[k]]
+            ikeys = [k for k in range(8) if flags[8 + k]]
+        read = 0
+        for r in range(rounds):
+            if r < len(chunks):
+                c, a = chunks[r]
+                b = min(a + chunk_rows, int(c["ids"].numel()))
+                ids = c["ids"][a:b].to(dev, non_blocking=True)
+                vals = c["vals"][a:b].to(dev, non_blocking=True)
+                states = {k: (c["states"][k][a:b].to(dev, non_blocking=True) if k in c["states"]
+                              else torch.zeros((b - a, t.dim), device=dev)) for k in skeys}
+                states_i = {k: (c["states_i"][k][a:b].to(dev, non_blocking=True) if k in c["states_i"]
+                                else torch.zeros(b - a, dtype=torch.int64, device=dev)) for k in ikeys}
+                read += b - a
+            else:
+                ids = torch.empty(0, dtype=torch.int64, device=dev)
+                vals = torch.empty((0, t.dim), device=dev)
+                states = {k: torch.empty((0, t.dim), device=dev) for k in skeys}
+                states_i = {k: torch.empty(0, dtype=torch.int64, device=dev) for k in ikeys}
+            if self.world > 1:
+                owners = C.owner_of_cuda(ids, salt, self.world).long() if ids.numel() else torch.empty(0, dtype=torch.long, device=dev)
+                order = torch.argsort(owners, stable=True)
+                send = torch.bincount(owners, minlength=self.world)
+                recv = torch.empty_like(send)
+                dist.all_to_all_single(recv, send, group=self.group)
+                sc, rc = send.tolist(), recv.tolist()
+
+                def a2a(x, width):
+                    out = torch.empty((sum(rc), width) if width else (sum(rc),), dtype=x.dtype, device=dev)
+                    dist.all_to_all_single(out, x[order].contiguous(), rc, sc, group=self.group)
+                    return out
+
+                ids = a2a(ids, 0)
+                vals = a2a(vals, t.dim)
+                states = {k: a2a(v, t.dim) for k, v in states.items()}
+                states_i = {k: a2a(v, 0) for k, v in states_i.items()}
+            if ids.numel():
+                t.import_rows(ids, vals, states, states_i)
+        return read
+
     def stop(self) -> None:
         if self.stopped:
             return

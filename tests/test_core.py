@@ -165,3 +165,58 @@ def test_dense_file_round_trip(tmp_path):
     assert back["id"] == 2 and torch.equal(back["val"], v["val"]) and torch.equal(back["states"][1], v["states"][1])
     assert back["states_i"] == {0: 12}
     assert C.ckpt_load_dense(str(tmp_path), "missing") is None
+
+
+def test_streamed_sparse_writer_and_fast_reader_match_the_plain_ones(tmp_path):
+    """The multi-threaded stream writer must produce the same bytes as the plain writer, and the fast
+    reader the same columns as the plain reader; a file whose rows differ in layout (as the reference
+    writes them: state entries appear with the first update) must be left to the plain reader."""
+    import torch
+    from kraken_b200._native import C
+
+    g = torch.Generator().manual_seed(3)
+    n, dim = 20_000, 6
+    ids = torch.randint(-(1 << 62), 1 << 62, (n,), generator=g, dtype=torch.int64).unique()
+    n = ids.numel()
+    vals = torch.randn(n, dim, generator=g)
+    states = {3: torch.randn(n, dim, generator=g), 4: torch.rand(n, dim, generator=g)}
+    steps = torch.randint(0, 50, (n,), generator=g, dtype=torch.int64)
+    a, b = tmp_path / "plain", tmp_path / "stream"
+    a.mkdir()
+    b.mkdir()
+    C.ckpt_save_sparse(str(a), 7, "emb.table", dim, C.InitializerType.kNormal, {"mean": "0", "stddev": "1"}, ids, vals,
+                       states, {0: steps})
+    w = C.SparseStreamWriter(str(b), 7, "emb.table", dim, C.InitializerType.kNormal, {"mean": "0", "stddev": "1"},
+                             [3, 4], [0], 4)
+    u = ids.numpy().view("uint64")
+    for slot in range(8):
+        sel = torch.from_numpy(((u % 8) == slot).nonzero()[0])
+        sel = sel[torch.from_numpy(u[sel.numpy()].argsort())]
+        w.begin_slot(int(sel.numel()))
+        for lo in range(0, int(sel.numel()), 3000):   # several appends per slot
+            s = sel[lo:lo + 3000]
+            w.append(ids[s].contiguous(), vals[s].contiguous(), [states[3][s].contiguous(), states[4][s].contiguous()],
+                     [steps[s].contiguous()])
+    w.close()
+    assert (a / "emb.table.sparse").read_bytes() == (b / "emb.table.sparse").read_bytes()
+    fast = C.ckpt_load_sparse_fast(str(b), "emb.table", 3)
+    plain = C.ckpt_load_sparse(str(a), "emb.table")
+    assert fast is not False and fast is not None
+    assert torch.equal(fast["ids"], plain["ids"]) and torch.equal(fast["vals"], plain["vals"])
+    assert torch.equal(fast["states"][3], plain["states"][3]) and torch.equal(fast["states"][4], plain["states"][4])
+    assert torch.equal(fast["states_i"][0], plain["states_i"][0])
+    assert C.ckpt_load_sparse_fast(str(tmp_path), "missing") is None
+    # a row without state entries in the middle of the file: not the fixed layout
+    raw = bytearray((a / "emb.table.sparse").read_bytes())
+    row = w.row_bytes()
+    first_row = len(raw) - int(w.bytes_written()) + 0  # both files are equal in length: header is what is not rows
+    head = len(raw) - (n * row + 8 * 8)
+    # rewrite the LAST row as {id, val, 0 states, 0 int states} and pad: length changes, so the layout check must fail
+    cut = raw[:len(raw) - row] + raw[len(raw) - row:len(raw) - row + 8 + 18 + dim * 4] + (0).to_bytes(8, "little") * 2
+    c = tmp_path / "mixed"
+    c.mkdir()
+    (c / "emb.table.sparse").write_bytes(bytes(cut))
+    assert C.ckpt_load_sparse_fast(str(c), "emb.table") is False
+    mixed = C.ckpt_load_sparse(str(c), "emb.table")
+    assert mixed["ids"].numel() == n and float(mixed["states"][3][-1].abs().sum()) == 0.0
+    assert head > 0 and first_row >= 0
