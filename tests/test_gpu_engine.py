@@ -97,9 +97,9 @@ def test_bf16_step_tracks_the_fp32_step_on_the_teacher_task():
     """The benchmark's fused bf16 step and the all-fp32 step, same model, same batches, 300 Adam steps:
     held-out loss and AUC must agree closely (the reference computes in fp32, kraken/t/math.cc:20-76)."""
     from kraken_b200.benchmarks.precision_parity import main
-    rec = main(["--steps", "300", "--batch", "4096", "--vocab", "20000", "--distinct", "300", "--eval-batches", "4",
+    rec = main(["--steps", "300", "--batch", "4096", "--vocab", "20000", "--eval-batches", "4",
                 "--table-capacity", str(1 << 21)])
-    assert rec["fp32"]["eval_auc"] > 0.55, rec          # the task is learnable: both arms learn it
+    assert rec["fp32"]["eval_auc"] > 0.6, rec           # the task is learnable: both arms learn it
     assert abs(rec["eval_auc_diff"]) < 0.01, rec
     assert abs(rec["eval_loss_diff"]) < 0.01, rec
 
@@ -143,8 +143,9 @@ def _combined_scenario(dev, rank=0, world=1, steps=3):
             gcat = torch.cat([all_g[r][k] for r in range(world)])
             uniq, inv = C.cpu_dedup(cat)
             assert shard.push_sparse(t, uniq, C.cpu_segment_sum(gcat, inv, uniq.numel()), 0.1) == 0
-        # three row widths -> two group exchanges + one single-table exchange, not six exchanges
-        assert pull_launches <= 2 * 8 + 6, pull_launches
+        # three row widths -> two group exchanges (8 launches each between GPUs) + one single-table exchange (7),
+        # not six exchanges
+        assert pull_launches <= 2 * 8 + 7, pull_launches
     eng.check()
     probe = torch.arange(300)
     for k, t in enumerate(tids):
