@@ -20,11 +20,16 @@ def main():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--batch", type=int, default=16384)
     p.add_argument("--fields", type=int, default=100)
-    p.add_argument("--vocab", type=int, default=1_000_000)
+    p.add_argument("--vocab", type=int, default=(1 << 40) // 100,
+                   help="Zipf ranks per field; (field, rank) is hashed into the 2^40 id space (default: the fields "
+                        "together span all of it)")
+    p.add_argument("--table-capacity", type=int, default=1 << 27, help="initial slots per GPU shard")
     a = p.parse_args()
     world, rank = world_rank()
     max_ids = int(a.batch * a.fields * 21.5)
-    kk.initialize("gpu", table_capacity=1 << 25, max_ids_per_call=max_ids, max_unique_per_call=max(1 << 20, max_ids // 3))
+    max_unique = max(1 << 20, max_ids // 2)
+    kk.initialize("gpu", table_capacity=a.table_capacity, max_ids_per_call=max_ids, max_unique_per_call=max_unique,
+                  max_per_owner_per_call=max_unique if world == 1 else int(2.5 * max_unique / world))
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(0)
     model = MultiHotWideAndDeep(a.fields, 13, 64, (1024, 512, 256), mean_fields=range(0, a.fields, 2)).to(dev)
@@ -52,7 +57,8 @@ def main():
     ids_per_step = sum(int(b[1].numel()) for b in batches[a.warmup:]) / a.steps
     emit({"benchmark": "multihot_wide_deep", "n_gpus": world, "batch_per_gpu": a.batch, "fields": a.fields,
           "ids_per_gpu_step": ids_per_step, "samples_per_sec": a.batch * world * a.steps / (ms / 1e3),
-          "ms_per_step": ms / a.steps, "final_loss": loss.item() * world})
+          "ms_per_step": ms / a.steps, "final_loss": loss.item() * world, "id_space": "2^40 (hashed Zipf ranks)",
+          "ranks_per_field": a.vocab, "rows_per_gpu_after": sum(t.num_rows() for t in kk.native.engine().sparse.values())})
     kk.stop()
 
 

@@ -23,6 +23,23 @@ _deferred_join = False
 _pending_join = set()
 
 
+_grad_ready = None
+
+
+def set_grad_ready_callback(fn) -> None:
+    """``fn(parameter, stream)`` is called by the backward pass once every kernel that writes a parameter's
+    gradient this step has been enqueued on ``stream`` (the engine uses it to launch the fused dense step of a
+    bucket while the backward pass is still running)."""
+    global _grad_ready
+    _grad_ready = fn
+
+
+def _notify(params, stream) -> None:
+    if _grad_ready is not None:
+        for p in params:
+            _grad_ready(p, stream)
+
+
 def set_deferred_join(on: bool) -> None:
     """With deferred join the backward pass leaves its side stream (weight and bias gradients)
     un-joined, and whoever consumes those gradients next - the engine's fused dense step - runs on
@@ -210,6 +227,7 @@ class _FusedMLP(torch.autograd.Function):
                 counters.add()
                 C.linear_dgrad(dy16, wl.detach().t().contiguous().to(torch.bfloat16), None, dh, st,
                                ctx.masks[-1] if L > 1 else None)
+        _notify((wl, bs[-1]), torch.cuda.current_stream(dev))
         # The chain dh_L -> dh_{L-1} -> ... is serial; each layer's weight and bias gradients only
         # need that layer's dh, so they run on a second stream beside the chain and are joined at
         # the end (in a CUDA-graph capture this becomes a parallel branch).
@@ -223,6 +241,7 @@ class _FusedMLP(torch.autograd.Function):
                 C.linear_wgrad(dh, acts[i], _grad_target(ws[i]), st)
                 C.colsum_bf16(dh, _grad_target(bs[i]))
                 dh.record_stream(side)
+            _notify((ws[i], bs[i]), side)
             if i > 0 or ctx.x_needs_grad:
                 dprev = torch.empty_like(acts[i])
                 wt16 = ctx.wts[i]

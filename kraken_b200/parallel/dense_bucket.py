@@ -187,3 +187,91 @@ class DenseBucket:
 
     def close(self) -> None:
         self.arena.close()
+
+
+class BucketSet:
+    """The dense tables of a model split into several ``DenseBucket``s, in registration order.
+
+    Each bucket has its own symmetric arena, flags and optimizer-state slices, so it can be stepped
+    (reduce-scatter + optimizer + all-gather, one fused kernel sequence) as soon as ITS gradients are
+    complete, while the backward pass still computes the gradients of the layers in front of it: the
+    reference pushes every dense gradient from a per-parameter hook during backward
+    (kraken/pytorch/optimizer.py:115-121,141-149); here the unit is a bucket of at least
+    ``bucket_elems`` elements so that small tables share one launch sequence.  The interface is that
+    of a single ``DenseBucket``; ``step`` steps whatever has not been stepped since the previous ``step``.
+    """
+
+    def __init__(self, tables: Sequence[Tuple[int, int]], optim_type, optim_conf: Dict[str, str], rank: int,
+                 world: int, device: torch.device, group=None, dct: bool = False, life_span: int = 1000,
+                 eta: float = 0.75, spin_limit: int = DEFAULT_SPIN, bucket_elems: int = 1 << 21) -> None:
+        groups: List[List[Tuple[int, int]]] = [[]]
+        size = 0
+        for tid, numel in tables:
+            groups[-1].append((tid, numel))
+            size += int(numel)
+            if size >= bucket_elems:
+                groups.append([])
+                size = 0
+        if not groups[-1] and len(groups) > 1:
+            groups.pop()
+        self.buckets = [DenseBucket(g, optim_type, optim_conf, rank, world, device, group, dct, life_span, eta,
+                                    spin_limit) for g in groups]
+        self.table_ids: List[int] = [tid for g in groups for tid, _ in g]
+        self.bucket_of: Dict[int, int] = {tid: k for k, g in enumerate(groups) for tid, _ in g}
+        self.n_pad = sum(b.n_pad for b in self.buckets)
+        self.world, self.rank, self.device = world, rank, device
+        self._stepped = [False] * len(self.buckets)
+
+    # ------------------------------------------------------------------ views
+    def param_view(self, table_id: int, shape: Sequence[int]) -> torch.Tensor:
+        return self.buckets[self.bucket_of[table_id]].param_view(table_id, shape)
+
+    def grad_view(self, table_id: int, shape: Sequence[int]) -> torch.Tensor:
+        return self.buckets[self.bucket_of[table_id]].grad_view(table_id, shape)
+
+    def grads(self) -> List[torch.Tensor]:
+        return [b.grad for b in self.buckets]
+
+    def set_active(self, active: Sequence[bool]) -> None:
+        active = list(active)
+        pos = 0
+        for b in self.buckets:
+            n = len(b.table_ids)
+            b.set_active(active[pos:pos + n])
+            pos += n
+
+    # ------------------------------------------------------------------ step
+    def step_bucket(self, k: int, lr: torch.Tensor, grad_scale: float = 1.0) -> None:
+        """Steps bucket k now, on the current stream (collective: every rank steps its buckets in the same order)."""
+        if not self._stepped[k]:
+            self.buckets[k].step(lr, grad_scale)
+            self._stepped[k] = True
+
+    def step(self, lr: torch.Tensor, grad_scale: float = 1.0) -> None:
+        """Steps every bucket that ``step_bucket`` has not stepped since the last call, last bucket first (the
+        order in which a backward pass completes them), and starts a new round."""
+        for k in range(len(self.buckets) - 1, -1, -1):
+            self.step_bucket(k, lr, grad_scale)
+        self._stepped = [False] * len(self.buckets)
+
+    @property
+    def launches(self) -> int:
+        return sum(b.launches for b in self.buckets)
+
+    def status_words(self) -> List[torch.Tensor]:
+        return [b.ctrl[3:4] for b in self.buckets]
+
+    def check(self) -> None:
+        for b in self.buckets:
+            b.check()
+
+    # ------------------------------------------------------------------ checkpoint
+    def export_table(self, table_id: int, shape: Sequence[int]) -> dict:
+        return self.buckets[self.bucket_of[table_id]].export_table(table_id, shape)
+
+    def import_table(self, table_id: int, value: dict) -> None:
+        self.buckets[self.bucket_of[table_id]].import_table(table_id, value)
+
+    def close(self) -> None:
+        for b in self.buckets:
+            b.close()

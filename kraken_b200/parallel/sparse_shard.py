@@ -282,9 +282,13 @@ class SparseChannel:
 
     def __init__(self, table: GpuSparseTable, rank: int, world: int, max_ids: int, group=None,
                  spin_limit: int = DEFAULT_SPIN, owner_salt: int = 0, alias_peers: bool = False,
-                 max_unique: int = 0) -> None:
+                 max_unique: int = 0, max_per_owner: int = 0) -> None:
         """max_ids bounds the occurrences of one call, max_unique (default: max_ids) the unique ids
-        among them; the peer inboxes and the gradient buffers are sized by the latter."""
+        among them, max_per_owner (default: max_unique) the unique ids one rank sends to ONE owner.  The
+        receive buffer is sized by max_unique; the peer inboxes and the gradient inbox hold
+        world x max_per_owner entries - with a uniform owner hash about max_unique / world per owner are
+        expected, so a bound of two or three times that saves most of the worst-case memory.  A call that
+        exceeds a bound is reported as kInboxOverflow, never written out of bounds."""
         self.table = table
         self.rank = rank
         self.world = world
@@ -293,14 +297,15 @@ class SparseChannel:
         self.salt = int(owner_salt)
         self.cap = int(max_ids)
         self.cap_u = int(max_unique) if max_unique and max_unique < max_ids else int(max_ids)
+        self.cap_s = int(max_per_owner) if max_per_owner and max_per_owner < self.cap_u else self.cap_u
         dim = table.dim
         dev = table.device
 
         lay = Layout()
-        lay.add("inbox_ids", (world, self.cap_u), torch.int64)
+        lay.add("inbox_ids", (world, self.cap_s), torch.int64)
         lay.add("inbox_meta", (world, 2), torch.int32)
         lay.add("rows_recv", (self.cap_u, dim), torch.float32)
-        lay.add("inbox_grad", (world, self.cap_u, dim), torch.float32)
+        lay.add("inbox_grad", (world, self.cap_s, dim), torch.float32)
         lay.add("flag_req", (world,), torch.int32)
         lay.add("flag_rsp", (world,), torch.int32)
         lay.add("flag_push", (world,), torch.int32)
@@ -308,7 +313,7 @@ class SparseChannel:
         self.lay = C.ChanLayout()
         for name in ("inbox_ids", "inbox_meta", "rows_recv", "inbox_grad", "flag_req", "flag_rsp", "flag_push"):
             setattr(self.lay, name, lay.offset(name))
-        self.lay.capS = self.cap_u
+        self.lay.capS = self.cap_s
         self.lay.capU = self.cap_u
 
         self.ctrl = torch.zeros(C.CTRL_INTS, dtype=torch.int32, device=dev)  # csrc/cuda/kernels.h: Ctrl
@@ -323,7 +328,7 @@ class SparseChannel:
         self._own_inv = torch.zeros(self.cap, dtype=torch.int32, device=dev)
         self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
         self.rows_recv = self.arena.window("rows_recv")
-        self.slot_cache = torch.full((world * self.cap_u,), -1, dtype=torch.int32, device=dev)
+        self.slot_cache = torch.full((world * self.cap_s,), -1, dtype=torch.int32, device=dev)
         self.ugrad = torch.zeros((self.cap_u, dim), dtype=torch.float32, device=dev)
         self.serial = 0
         self.launches = 0  # kernels launched through this channel (for accounting)

@@ -34,12 +34,15 @@ class EngineConfig:
     table_capacity: int = 1 << 20    # initial slots per GPU shard (tables grow)
     max_ids_per_call: int = 0        # 0: sized from the first call (2x headroom)
     max_unique_per_call: int = 0     # 0: same as max_ids_per_call; smaller saves exchange-buffer memory
+    max_per_owner_per_call: int = 0  # 0: same as max_unique_per_call; unique ids one rank may send to one owner
     spin_limit: int = 1 << 22        # polls before a device-side wait gives up
     saved_dir: str = ""
     max_save_count: int = 3
     owner_salt_per_table: bool = False
     exchange: str = "fused"          # "fused": peer-memory kernels; "nccl": torch.distributed collectives (baseline)
     compress: object = None          # TCP deployment: CompressType of worker<->server bodies (None / kNo = off)
+    dense_bucket_elems: int = 1 << 21  # GPU engine: dense tables are grouped into buckets of at least this many
+                                       # elements; with overlap_dense_step each is stepped as soon as its gradients exist
     status_poll_interval: int = 8    # GPU engine: steps between asynchronous reads of the kernels' error words
     overlap_dense_step: bool = False  # run the fused dense step on the MLP backward's side stream, beside the
                                       # sparse backward + push (needs: nothing reads the MLP's .grad before step())

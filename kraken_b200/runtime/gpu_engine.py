@@ -15,7 +15,7 @@ import torch
 import torch.distributed as dist
 
 from .._native import C
-from ..parallel.dense_bucket import DenseBucket
+from ..parallel.dense_bucket import BucketSet
 from ..parallel.nccl_baseline import NcclSparseChannel
 from ..parallel.sparse_shard import GpuSparseTable, GroupChannel, SparseChannel, Ticket
 from ..utils import profiler as _profiler
@@ -38,7 +38,10 @@ class GpuEngine(Engine):
         self.group_channels: Dict[Tuple[int, ...], GroupChannel] = {}
         self.group_tickets: Dict[Tuple[int, ...], tuple] = {}
         self.dense_init: Dict[int, torch.Tensor] = {}
-        self.bucket: Optional[DenseBucket] = None
+        self.bucket: Optional[BucketSet] = None
+        self._comm_stream: Optional[torch.cuda.Stream] = None
+        self._param_table: Dict[int, int] = {}     # id(parameter) -> dense table id (bound parameters)
+        self._bucket_ready: Dict[int, set] = {}     # bucket -> tables whose gradient is complete this step
         self._dense_pending = False
         self._pushed: set = set()
         self._bound = False
@@ -80,9 +83,10 @@ class GpuEngine(Engine):
         ids = self._dense_ids()
         tables = [(tid, int(self.dense_init[tid].numel())) for tid in ids]
         b_rank, b_world = (0, 1) if self.nccl else (self.rank, self.world)
-        self.bucket = DenseBucket(tables, self.optim_type, self.optim_conf, b_rank, b_world, self.device,
-                                  self.group, dct=self.cfg.emitter_type == C.EmitterType.kDCT,
-                                  life_span=self.cfg.life_span, eta=self.cfg.eta, spin_limit=self.cfg.spin_limit)
+        self.bucket = BucketSet(tables, self.optim_type, self.optim_conf, b_rank, b_world, self.device,
+                                self.group, dct=self.cfg.emitter_type == C.EmitterType.kDCT,
+                                life_span=self.cfg.life_span, eta=self.cfg.eta, spin_limit=self.cfg.spin_limit,
+                                bucket_elems=self.cfg.dense_bucket_elems)
         for tid in ids:
             self.bucket.param_view(tid, self.tables[tid].shape).copy_(self.dense_init[tid].view(*self.tables[tid].shape))
         if self.world > 1:
@@ -132,11 +136,44 @@ class GpuEngine(Engine):
         """Makes each parameter alias the bucket: ``.data`` is the parameter view and
         ``.grad`` the gradient view, so backward accumulates into the exchange buffer."""
         b = self._ensure_bucket()
+        from ..ops import mlp as fused_mlp
         for tid, p in pairs:
             shape = self._table(tid, "dense").shape
             p.data = b.param_view(tid, shape)
             p.grad = b.grad_view(tid, shape)
+            self._param_table[id(p)] = tid
+            if self.cfg.overlap_dense_step and hasattr(p, "register_post_accumulate_grad_hook"):
+                # gradients that autograd accumulates (layers outside the fused MLP) report through this hook;
+                # the fused MLP writes its gradients from its own kernels and reports them itself
+                p.register_post_accumulate_grad_hook(lambda param: self.dense_grad_ready(param))
+        if self.cfg.overlap_dense_step and not self.nccl:
+            fused_mlp.set_grad_ready_callback(self.dense_grad_ready)
         self._bound = True
+
+    def dense_grad_ready(self, param, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """The gradient of a bound dense parameter is complete for this step (all kernels that write it are
+        enqueued on ``stream``, default: the current one).  When that completes a bucket, its fused step
+        (reduce-scatter + optimizer + all-gather) is launched at once on the communication stream, behind an
+        event on ``stream``, so it overlaps the rest of the backward pass.  Only with ``overlap_dense_step``;
+        every rank sees the same parameters complete in the same order, so the launches stay collective."""
+        tid = self._param_table.get(id(param))
+        b = self.bucket
+        if tid is None or b is None or self.nccl or not self.cfg.overlap_dense_step:
+            return
+        k = b.bucket_of[tid]
+        ready = self._bucket_ready.setdefault(k, set())
+        ready.add(tid)
+        if len(ready) < len(b.buckets[k].table_ids) or len(b.buckets) == 1:
+            return  # a single bucket is stepped by dense_step(), on the stream the last gradients were written on
+        src = stream or torch.cuda.current_stream(self.device)
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=self.device)
+        ev = torch.cuda.Event()
+        ev.record(src)
+        self._comm_stream.wait_event(ev)
+        b.buckets[k].set_active([True] * len(b.buckets[k].table_ids))
+        with self._region("dense_step"), torch.cuda.stream(self._comm_stream):
+            b.step_bucket(k, self.lr_dev)
 
     def dense_step(self) -> None:
         """One fused optimizer step over every dense table (bound-parameter path)."""
@@ -144,16 +181,21 @@ class GpuEngine(Engine):
         b.set_active([True] * len(b.table_ids))
         with self._region("dense_step"):
             if self.nccl:
-                dist.all_reduce(b.grad, group=self.group)
+                for g in b.grads():
+                    dist.all_reduce(g, group=self.group)
             from ..ops import mlp as fused_mlp
             side = fused_mlp.take_pending_side_stream(self.device) if not self.nccl else None
+            main = torch.cuda.current_stream(self.device)
             if side is not None:
-                # the MLP backward left its weight gradients on this stream: step there, then join
+                # the MLP backward left its weight gradients on this stream: step (what is left) there, then join
                 with torch.cuda.stream(side):
                     b.step(self.lr_dev)
-                torch.cuda.current_stream(self.device).wait_stream(side)
+                main.wait_stream(side)
             else:
                 b.step(self.lr_dev)
+            if self._comm_stream is not None:
+                main.wait_stream(self._comm_stream)  # buckets that were stepped during the backward pass
+        self._bucket_ready.clear()
         self._dense_pending = False
         self._pushed.clear()
 
@@ -186,7 +228,8 @@ class GpuEngine(Engine):
         b = self.bucket
         b.set_active([tid in self._pushed for tid in b.table_ids])
         if self.nccl:
-            dist.all_reduce(b.grad, group=self.group)
+            for g in b.grads():
+                dist.all_reduce(g, group=self.group)
         b.step(self.lr_dev)
         self._dense_pending = False
         self._pushed.clear()
@@ -204,7 +247,8 @@ class GpuEngine(Engine):
                 dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
                 cap = int(t.item())
         ch = SparseChannel(self.sparse[table_id], self.rank, self.world, cap, self.group, self.cfg.spin_limit,
-                           self._salt(table_id), max_unique=self.cfg.max_unique_per_call)
+                           self._salt(table_id), max_unique=self.cfg.max_unique_per_call,
+                           max_per_owner=self.cfg.max_per_owner_per_call)
         self.channels[table_id] = ch
         return ch
 
@@ -510,7 +554,7 @@ class GpuEngine(Engine):
         for tid, t in self.sparse.items():
             out.append((f"table {t.name!r}", t.status))
         if self.bucket is not None:
-            out.append(("dense step", self.bucket.ctrl[3:4]))
+            out += [("dense step", w) for w in self.bucket.status_words()]
         return out
 
     def _poll_status(self) -> None:
@@ -689,6 +733,7 @@ class GpuEngine(Engine):
         self.bucket = None
         from ..ops import mlp as fused_mlp
         fused_mlp.set_deferred_join(False)
+        fused_mlp.set_grad_ready_callback(None)
         super().stop()
         if failure is not None:
             raise failure

@@ -47,6 +47,14 @@ def test_combined_tables_one_exchange_across_ranks(world):
     assert "MULTI_GPU_COMBINED ok" in out, out[-2000:]
 
 
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_bucketed_dense_step_during_backward_matches_single_bucket(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = run_ranks("mp_gpu_dense_overlap_worker.py", world)
+    assert "DENSE_OVERLAP ok" in out, out[-2000:]
+
+
 def test_nccl_baseline_exchange_matches_one_shard(tmp_path):
     """The NCCL-only path must give the same tables as the fused path's oracle."""
     if torch.cuda.device_count() < 2:
