@@ -592,6 +592,9 @@ class GpuEngine(Engine):
         if torch.cuda.is_current_stream_capturing():
             return
         t = self.sparse[table_id]
+        ch = self.channels.get(table_id)
+        if ch is not None:
+            n_ids = min(n_ids, ch.cap_u)  # no more unique ids than the exchange buffers admit
         inflow = n_ids * self.world  # worst case: every rank's ids of this call belong to this shard
         hi = getattr(t, "rows_hi", 0) + inflow
         if hi > 0.6 * t.capacity:
