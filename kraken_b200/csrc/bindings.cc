@@ -875,7 +875,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                               const torch::Tensor& slot_of, uint32_t hbits, const torch::Tensor& cnt, const torch::Tensor& off,
                               const torch::Tensor& uniq, const torch::Tensor& inv, const torch::Tensor& status,
                               int cap_u, const SymHeap* heap, const cu::ChanLayout* lay,
-                              const c10::optional<torch::Tensor>& ctrl) {
+                              const c10::optional<torch::Tensor>& ctrl, int owner_world) {
+    if (owner_world <= 0 || owner_world > world) owner_world = world;
     need_cuda(ids, "ids", torch::kInt64);
     need_cuda(hkeys, "hkeys", torch::kInt64);
     const int n = static_cast<int>(ids.numel());
@@ -889,17 +890,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     cu::DedupScratch sc{hkeys.data_ptr(), ptr<int>(slot_of), hbits};
     if (heap != nullptr && lay != nullptr && ctrl.has_value()) {
       // with a channel: the dedup's second kernel also dispatches the unique ids to their owners
-      cu::dedup_bucketize_dispatch(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off),
+      cu::dedup_bucketize_dispatch(ptr<int64_t>(ids), n, world, owner_world, salt, sc, ptr<int>(cnt), ptr<int>(off),
                                    ptr<int64_t>(uniq), ptr<int>(inv), cap_u, ptr<int>(status), heap->View(), *lay,
                                    ctrl_ptr(*ctrl), cur_stream());
     } else {
-      cu::dedup_bucketize(ptr<int64_t>(ids), n, world, salt, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),
+      cu::dedup_bucketize(ptr<int64_t>(ids), n, world, owner_world, salt, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),
                           ptr<int>(inv), cap_u, ptr<int>(status), cur_stream());
     }
     check_launch("dedup_bucketize");
   }, py::arg("ids"), py::arg("world"), py::arg("salt"), py::arg("hkeys"), py::arg("slot_of"), py::arg("hbits"), py::arg("cnt"), py::arg("off"), py::arg("uniq"), py::arg("inv"),
      py::arg("status"), py::arg("cap_u") = 0, py::arg("heap") = nullptr, py::arg("layout") = nullptr,
-     py::arg("ctrl") = py::none());
+     py::arg("ctrl") = py::none(), py::arg("owner_world") = 0);
   m.def("pull_dispatch", [](const SymHeap& h, const cu::ChanLayout& lay, const torch::Tensor& ctrl,
                             const torch::Tensor& uniq, const torch::Tensor& off, int max_n) {
     cu::pull_dispatch(h.View(), lay, ctrl_ptr(ctrl), ptr<int64_t>(uniq), ptr<int>(off),
@@ -971,7 +972,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            const torch::Tensor& region_bits, const torch::Tensor& salts, int world, const torch::Tensor& hkeys,
            const torch::Tensor& slot_of, const torch::Tensor& cnt, const torch::Tensor& off, const torch::Tensor& uniq,
            const torch::Tensor& inv, const torch::Tensor& status, int cap_u, const SymHeap& heap,
-           const cu::ChanLayout& lay, const torch::Tensor& ctrl) {
+           const cu::ChanLayout& lay, const torch::Tensor& ctrl, int owner_world) {
+          if (owner_world <= 0 || owner_world > world) owner_world = world;
           need_cuda(ids, "ids", torch::kInt64);
           need_cuda(occ_start, "occ_start", torch::kInt32);
           need_cuda(region_base, "region_base", torch::kInt32);
@@ -988,7 +990,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                           off.numel() >= world + 1 && uniq.numel() >= cap_u,
                       "group dedup buffers too small");
           c10::cuda::CUDAGuard guard(ids.device());
-          cu::GroupDesc d{T, ptr<int>(occ_start), ptr<int>(region_base), ptr<int>(region_bits),
+          cu::GroupDesc d{T, owner_world, ptr<int>(occ_start), ptr<int>(region_base), ptr<int>(region_bits),
                           reinterpret_cast<const unsigned long long*>(salts.data_ptr())};
           cu::DedupScratch sc{hkeys.data_ptr(), ptr<int>(slot_of), 0};
           cu::group_dedup_dispatch(ptr<int64_t>(ids), n, d, world, sc, ptr<int>(cnt), ptr<int>(off), ptr<int64_t>(uniq),

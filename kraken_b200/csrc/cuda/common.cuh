@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
+#include <utility>
 
 #include "../core/hash.h"
 #include "../core/optim_math.h"
@@ -73,6 +75,20 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, u
   return false;
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl() may become resident while the
+// kernel in front of it in the stream is still running: its blocks are scheduled once every block of that
+// kernel has executed pdl_trigger(), and they run their prologue (barrier set-up, tensor-memory allocation,
+// loads of data the predecessor does not write) until pdl_wait(), which returns when the predecessor has
+// completed and its writes are visible.  Rule kept by every kernel here: pdl_trigger() comes AFTER the
+// kernel's own pdl_wait(), so "predecessor complete" stays transitive along the stream.  Launched without
+// the attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+  pdl_wait();
+  pdl_trigger();
+}
+
 // Vector float reduction into global memory (sm_90+): one 16-byte L2 atomic.
 __device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
@@ -129,6 +145,31 @@ __device__ __forceinline__ int table_find_or_insert(const TableView& t, uint64_t
 __device__ __forceinline__ void count_created(const TableView& t, bool created) {
   const unsigned m = __ballot_sync(__activemask(), created);
   if (created && (__ffs(m) - 1) == static_cast<int>(threadIdx.x & 31)) atomicAdd(t.size, __popc(m));
+}
+
+// Host side: launch with the programmatic-stream-serialization attribute (see pdl_wait above).  KRAKEN_PDL=0 in
+// the environment turns it off (plain stream order), for comparison.
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("KRAKEN_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
 }
 
 }  // namespace cu

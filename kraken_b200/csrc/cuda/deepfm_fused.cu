@@ -46,6 +46,7 @@ deepfm_pack_forward_kernel(const float* __restrict__ rows2, const int* __restric
                            const float* __restrict__ dense, int B, int F, int D, int RD, int ND, int lpr, int G,
                            __nv_bfloat16* __restrict__ x, int ldx, float* __restrict__ fm_logit,
                            float* __restrict__ ssum) {
+  pdl_enter();
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
   const int stride = (gridDim.x * blockDim.x) / lpr;
@@ -106,6 +107,7 @@ deepfm_pack_backward_kernel(const float* __restrict__ rows2, const int* __restri
                             const __nv_bfloat16* __restrict__ dx, int lddx, const float* __restrict__ dlogit,
                             const float* __restrict__ ssum, int B, int F, int D, int RD, int lpr, int G,
                             float* ugrad2, float* ugrad1) {
+  pdl_enter();
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
   const int stride = (gridDim.x * blockDim.x) / lpr;
@@ -171,7 +173,7 @@ void deepfm_pack_forward(const float* rows2, const int* inv2, const int* slots2,
   const int chunks = D / 4;
   const int G = field_groups(chunks);
   const int lpr = chunks * G;
-  deepfm_pack_forward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, slots2, rows1, inv1, slots1, dense,
+  launch_pdl(deepfm_pack_forward_kernel, dim3(grid_for(B, lpr)), dim3(kThreads), 0, stream, rows2, inv2, slots2, rows1, inv1, slots1, dense,
                                                                         B, F, D, RD, ND, lpr, G, x, ldx, fm_logit, ssum);
 }
 
@@ -183,7 +185,7 @@ void deepfm_pack_backward(const float* rows2, const int* inv2, const int* slots2
   const int chunks = D / 4;
   const int G = field_groups(chunks);
   const int lpr = chunks * G;
-  deepfm_pack_backward_kernel<<<grid_for(B, lpr), kThreads, 0, stream>>>(rows2, inv2, slots2, inv1, dx, lddx, dlogit,
+  launch_pdl(deepfm_pack_backward_kernel, dim3(grid_for(B, lpr)), dim3(kThreads), 0, stream, rows2, inv2, slots2, inv1, dx, lddx, dlogit,
                                                                          ssum, B, F, D, RD, lpr, G, ugrad2, ugrad1);
 }
 

@@ -82,13 +82,15 @@ struct DedupScratch {
 // the per-owner unique counts), uniq[off[world]], inv[n] (occurrence -> unique).  cap_u is the
 // capacity of uniq and of the buffers later indexed by inv: beyond it the call reports
 // kInboxOverflow and clamps its outputs into range.
-void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
-                     int64_t* uniq, int* inv, int cap_u, int* status, cudaStream_t stream);
+// owner_world <= world: rows are owned by ranks 0 .. owner_world - 1 only (OwnerOf(salt, id, owner_world)); the other
+// ranks still look rows up and push gradients.  Normally equal to world; smaller after a live reshard.
+void dedup_bucketize(const int64_t* ids, int n, int world, int owner_world, uint64_t salt, DedupScratch sc, int* cnt,
+                     int* off, int64_t* uniq, int* inv, int cap_u, int* status, cudaStream_t stream);
 // The same, with the pull's id dispatch (pull_dispatch below) done by the second kernel of the dedup:
 // unique ids go straight into their owners' inboxes and the channel's pull epoch advances.
-void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
-                              int64_t* uniq, int* inv, int cap_u, int* status, SymHost sym, ChanLayout lay, Ctrl* ctrl,
-                              cudaStream_t stream);
+void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, int owner_world, uint64_t salt, DedupScratch sc,
+                              int* cnt, int* off, int64_t* uniq, int* inv, int cap_u, int* status, SymHost sym,
+                              ChanLayout lay, Ctrl* ctrl, cudaStream_t stream);
 
 // ---- sparse pull ----
 // Cross-GPU waits never run inside the big grids: each is a one-warp kernel in stream order
@@ -126,6 +128,7 @@ void exchange_wait(SymHost sym, ChanLayout lay, Ctrl* ctrl, int kind, uint32_t s
 // All arrays are device memory, rewritten by the host only when the shapes of a call change.
 struct GroupDesc {
   int T;
+  int owner_world;                     // rows are owned by ranks 0 .. owner_world - 1
   const int* occ_start;                // [T + 1]
   const int* region_base;              // [T]
   const int* region_bits;              // [T]

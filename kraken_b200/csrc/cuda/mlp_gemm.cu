@@ -21,6 +21,7 @@
 #include <mutex>
 
 #include "../core/types.h"
+#include "common.cuh"
 #include "mlp_gemm.h"
 #include "tcgen05.cuh"
 
@@ -293,6 +294,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
+  pdl_enter();  // everything above touches nothing the kernel in front of this one writes
   const uint32_t tmem_base = tmem_slot;
 
   if (warp == 0 && lane == 0) {
@@ -424,6 +426,7 @@ gemm_bres_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
+  pdl_enter();  // everything above touches nothing the kernel in front of this one writes
   const uint32_t tmem_base = tmem_slot;
   const int total_it = my_tiles * total_kb;
 
@@ -586,6 +589,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc::cluster_sync_all();  // the other CTA's barriers exist before anything arrives on them
   tc::fence_after_sync();
+  pdl_enter();  // everything above touches nothing the kernel in front of this one writes
   const uint32_t tmem_base = tmem_slot;
   const int total_it = my_tiles * total_kb;
 
@@ -692,6 +696,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ------------------------------------------------------------------ column sums
 __global__ void __launch_bounds__(256)
 colsum_bf16_kernel(const __nv_bfloat16* __restrict__ x, int ld, int M, int N, int rows_per_block, float* out) {
+  pdl_enter();
   // block = 256 threads: 32 column pairs x 8 row lanes over a 64-column strip
   const int cpair = threadIdx.x & 31;
   const int rlane = threadIdx.x >> 5;
@@ -775,7 +780,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, int splits,
     attr_set = true;
   }
   dim3 grid((g.M + kBM - 1) / kBM, (g.N + g.BN - 1) / g.BN, splits);
-  gemm_kernel<A_MN, B_MN, EPI><<<grid, kThreads, smem, stream>>>(ta, tb, g);
+  launch_pdl(gemm_kernel<A_MN, B_MN, EPI>, grid, dim3(kThreads), smem, stream, ta, tb, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -852,7 +857,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cudaSt
   }
   int pairs = 74 / n_tiles;
   if (pairs > m_tiles) pairs = m_tiles;
-  gemm_pair_kernel<EPI><<<dim3(2 * pairs, n_tiles), kThreads, smem, stream>>>(ta, tb, g);
+  launch_pdl(gemm_pair_kernel<EPI>, dim3(2 * pairs, n_tiles), dim3(kThreads), smem, stream, ta, tb, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -873,7 +878,7 @@ int launch_resident(const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs g, cu
   }
   int per_n = 148 / n_tiles;
   if (per_n > m_tiles) per_n = m_tiles;
-  gemm_bres_kernel<EPI><<<dim3(per_n, n_tiles), kThreads, smem, stream>>>(ta, tb, g);
+  launch_pdl(gemm_bres_kernel<EPI>, dim3(per_n, n_tiles), dim3(kThreads), smem, stream, ta, tb, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -972,7 +977,7 @@ void colsum_bf16(const __nv_bfloat16* dY, int lddy, int M, int N, float* db, cud
   int rows_per_block = (M + row_blocks - 1) / row_blocks;
   if (rows_per_block < 64) rows_per_block = 64;
   row_blocks = (M + rows_per_block - 1) / rows_per_block;
-  colsum_bf16_kernel<<<dim3(strips, row_blocks), 256, 0, stream>>>(dY, lddy, M, N, rows_per_block, db);
+  launch_pdl(colsum_bf16_kernel, dim3(strips, row_blocks), dim3(256), 0, stream, dY, lddy, M, N, rows_per_block, db);
 }
 
 }  // namespace cu

@@ -117,6 +117,7 @@ fm_backward_kernel(const float* __restrict__ emb, const float* __restrict__ gout
 __global__ void __launch_bounds__(kThreads)
 bce_kernel(const float* __restrict__ logits, const float* __restrict__ labels, int n, float inv_n, float* loss,
            float* __restrict__ grad) {
+  pdl_enter();
   float acc = 0.f;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const float x = logits[i], y = labels[i];
@@ -144,6 +145,7 @@ __global__ void __launch_bounds__(kThreads)
 rowdot_forward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ w,
                       const float* __restrict__ bias, const float* __restrict__ addend, int M, int K,
                       float* __restrict__ y) {
+  pdl_enter();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -165,6 +167,7 @@ __global__ void __launch_bounds__(kThreads)
 rowdot_backward_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ w,
                        const float* __restrict__ dy, int M, int K, int rows_per_block, int relu_mask,
                        __nv_bfloat16* __restrict__ dx, int lddx, float* dw, float* db) {
+  pdl_enter();
   const int r0 = blockIdx.x * rows_per_block;
   const int r1 = min(M, r0 + rows_per_block);
   for (int k = threadIdx.x * 2; k < K; k += 2 * blockDim.x) {
@@ -200,6 +203,7 @@ __global__ void __launch_bounds__(kThreads)
 rowdot_backward_wide_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ w,
                             const float* __restrict__ dy, int M, int K, int rows_per_block, int relu_mask,
                             __nv_bfloat16* __restrict__ dx, int lddx, float* dw, float* db) {
+  pdl_enter();
   extern __shared__ float s_dw[];  // [K] partial sums of this block
   const int groups = K / 8;                       // 16-byte column groups per row
   const int lanes = blockDim.x / groups;          // row lanes (>= 1: the launcher guarantees groups <= blockDim.x)
@@ -259,6 +263,7 @@ rowdot_backward_wide_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const 
 __global__ void __launch_bounds__(256)
 cast_w_wt_kernel(const float* __restrict__ w, int N, int K, __nv_bfloat16* __restrict__ w16,
                  __nv_bfloat16* __restrict__ wt16) {
+  pdl_enter();
   __shared__ float tile[32][33];
   const int n0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
@@ -310,7 +315,7 @@ void bce_forward_backward(const float* logits, const float* labels, int n, float
   if (n <= 0) return;
   int grid = (n + kThreads - 1) / kThreads;
   if (grid > 148 * 4) grid = 148 * 4;
-  bce_kernel<<<grid, kThreads, 0, stream>>>(logits, labels, n, 1.f / static_cast<float>(n), loss, grad);
+  launch_pdl(bce_kernel, dim3(grid), dim3(kThreads), 0, stream, logits, labels, n, 1.f / static_cast<float>(n), loss, grad);
 }
 
 void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float* bias, const float* addend, int M,
@@ -318,7 +323,7 @@ void rowdot_forward(const __nv_bfloat16* x, int ldx, const float* w, const float
   if (M <= 0) return;
   int grid = (M * 32 + kThreads - 1) / kThreads;
   if (grid > 148 * 8) grid = 148 * 8;
-  rowdot_forward_kernel<<<grid, kThreads, 0, stream>>>(x, ldx, w, bias, addend, M, K, y);
+  launch_pdl(rowdot_forward_kernel, dim3(grid), dim3(kThreads), 0, stream, x, ldx, w, bias, addend, M, K, y);
 }
 
 void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const float* dy, int M, int K, bool relu_mask,
@@ -331,17 +336,17 @@ void rowdot_backward(const __nv_bfloat16* x, int ldx, const float* w, const floa
   const bool wide = K % 8 == 0 && K / 8 <= kThreads && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                     (dx == nullptr || (lddx % 8 == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0));
   if (wide) {
-    rowdot_backward_wide_kernel<<<blocks, kThreads, K * sizeof(float), stream>>>(x, ldx, w, dy, M, K, rows_per_block,
-                                                                                 relu_mask ? 1 : 0, dx, lddx, dw, db);
+    launch_pdl(rowdot_backward_wide_kernel, dim3(blocks), dim3(kThreads), K * sizeof(float), stream, x, ldx, w, dy, M, K,
+               rows_per_block, relu_mask ? 1 : 0, dx, lddx, dw, db);
     return;
   }
-  rowdot_backward_kernel<<<blocks, kThreads, 0, stream>>>(x, ldx, w, dy, M, K, rows_per_block, relu_mask ? 1 : 0, dx,
-                                                          lddx, dw, db);
+  launch_pdl(rowdot_backward_kernel, dim3(blocks), dim3(kThreads), 0, stream, x, ldx, w, dy, M, K, rows_per_block,
+             relu_mask ? 1 : 0, dx, lddx, dw, db);
 }
 
 void cast_w_wt(const float* w, int N, int K, __nv_bfloat16* w16, __nv_bfloat16* wt16, cudaStream_t stream) {
   if (N <= 0 || K <= 0) return;
-  cast_w_wt_kernel<<<dim3((K + 31) / 32, (N + 31) / 32), 256, 0, stream>>>(w, N, K, w16, wt16);
+  launch_pdl(cast_w_wt_kernel, dim3((K + 31) / 32, (N + 31) / 32), dim3(256), 0, stream, w, N, K, w16, wt16);
 }
 
 }  // namespace cu

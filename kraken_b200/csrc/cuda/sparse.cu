@@ -47,6 +47,7 @@ namespace {
 enum WaitKind { kWaitRequest = 0, kWaitResponse = 1, kWaitPush = 2 };
 
 __global__ void exchange_wait_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, int kind, uint32_t spin_limit) {
+  pdl_enter();
   const int s = threadIdx.x;
   const size_t flag_off = kind == kWaitRequest ? lay.flag_req : kind == kWaitResponse ? lay.flag_rsp : lay.flag_push;
   const uint32_t want = kind == kWaitPush ? ctrl->push_epoch : ctrl->pull_epoch;
@@ -65,12 +66,12 @@ __global__ void exchange_wait_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, int ki
 }
 
 void launch_wait(const Sym& s, const ChanLayout& lay, Ctrl* ctrl, int kind, uint32_t spin_limit, cudaStream_t stream) {
-  if (s.world > 1) exchange_wait_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, kind, spin_limit);
+  if (s.world > 1) launch_pdl(exchange_wait_kernel, dim3(1), dim3(32), 0, stream, s, lay, ctrl, kind, spin_limit);
 }
 
 // ------------------------------------------------------------------ dedup
 __global__ void __launch_bounds__(kThreads)
-dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, DedupEntry* table,
+dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, int owner_world, uint64_t salt, DedupEntry* table,
                     uint32_t hbits, int* slot_of, int* cnt, int* status) {
   __shared__ int s_cnt[kMaxWorld];
   __shared__ int s_base[kMaxWorld];
@@ -104,7 +105,7 @@ dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t 
     }
     slot_of[i] = static_cast<int>(slot);
     if (won) {
-      owner = static_cast<int>(OwnerOf(salt, id, world));
+      owner = static_cast<int>(OwnerOf(salt, id, owner_world));
       lpos = atomicAdd(&s_cnt[owner], 1);
     }
   }
@@ -122,9 +123,10 @@ dedup_insert_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t 
 // no separate dispatch launch.
 template <bool DISPATCH>
 __global__ void __launch_bounds__(kThreads)
-dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_t salt, DedupEntry* table,
+dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, int owner_world, uint64_t salt, DedupEntry* table,
                       const int* __restrict__ slot_of, const int* __restrict__ cnt, int* off, int64_t* uniq, int* inv,
                       int cap_u, int* status, Sym sym, ChanLayout lay, Ctrl* ctrl) {
+  pdl_enter();
   __shared__ int s_off[kMaxWorld + 1];
   if (threadIdx.x == 0) {
     int acc = 0;
@@ -154,7 +156,7 @@ dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, int world, uint64_
     uint64_t id = static_cast<uint64_t>(ids[i]);
     if (id == kEmptyKey) id = kEmptyKey - 1;
     const int slot = slot_of[i];
-    const int o = static_cast<int>(OwnerOf(salt, id, world));
+    const int o = static_cast<int>(OwnerOf(salt, id, owner_world));
     const unsigned long long pw = __ldcg(&table[slot].pos_win);
     const int j = static_cast<int>(static_cast<uint32_t>(pw));  // position among the ids of owner o
     const int u = s_off[o] + j;
@@ -225,6 +227,7 @@ pull_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int64_t* __restr
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 pull_probe_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, int* slot_cache, int insert, int chunks, int lpr) {
+  pdl_enter();
   if (ctrl->abort) return;
   const unsigned long long* inbox = sym.at<unsigned long long>(sym.rank, lay.inbox_ids);
   const int lane = threadIdx.x & 31;
@@ -280,6 +283,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 pull_gather_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache, int chunks,
                    int lpr) {
+  pdl_enter();
   using V = Vec<VEC>;
   const int2* meta = ctrl->snap;
   const bool aborted = ctrl->abort != 0;  // the answer flags still go up, so the peers do not time out in turn
@@ -327,6 +331,7 @@ __global__ void __launch_bounds__(kThreads)
 pull_combine_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, const int* __restrict__ inv, int n, int dim, int chunks,
                     int lpr, const int64_t* __restrict__ bag_offsets, int nbags, const float* __restrict__ weights,
                     int mean, const uint8_t* __restrict__ bag_mean, float patch_value, float* __restrict__ out) {
+  pdl_enter();
   using V = Vec<VEC>;
   const float* rows = sym.at<float>(sym.rank, lay.rows_recv);
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -379,6 +384,7 @@ __global__ void __launch_bounds__(kThreads)
 push_scatter_kernel(const float* __restrict__ grads, const int* __restrict__ inv, int n, int dim, int chunks, int lpr,
                     const int64_t* __restrict__ bag_offsets, int nbags, const float* __restrict__ weights, int mean,
                     const uint8_t* __restrict__ bag_mean, float* ugrad) {
+  pdl_enter();
   using V = Vec<VEC>;
   const int gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = gtid % lpr;
@@ -410,6 +416,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 push_dispatch_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const int* __restrict__ off, int dim,
                      int chunks, int lpr) {
+  pdl_enter();
   using V = Vec<VEC>;
   __shared__ int s_off[kMaxWorld + 1];
   if (threadIdx.x <= sym.world) s_off[threadIdx.x] = off[threadIdx.x];
@@ -445,6 +452,7 @@ template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 push_merge_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache, int chunks,
                   int lpr) {
+  pdl_enter();
   using V = Vec<VEC>;
   if (ctrl->abort) return;
   const uint32_t epoch = ctrl->push_epoch;
@@ -494,6 +502,7 @@ template <int VEC, int OPT>
 __global__ void __launch_bounds__(kThreads, 4)
 push_update_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* __restrict__ slot_cache,
                    OptimPOD optim_in, const float* __restrict__ lr_ptr, int chunks, int lpr) {
+  pdl_enter();
   using V = Vec<VEC>;
   OptimPOD optim = optim_in;
   optim.type = OPT;
@@ -546,34 +555,34 @@ push_update_kernel(Sym sym, ChanLayout lay, Ctrl* ctrl, TableView t, const int* 
 }  // namespace
 
 // ------------------------------------------------------------------ launchers
-void dedup_bucketize(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
-                     int64_t* uniq, int* inv, int cap_u, int* status, cudaStream_t stream) {
+void dedup_bucketize(const int64_t* ids, int n, int world, int owner_world, uint64_t salt, DedupScratch sc, int* cnt,
+                     int* off, int64_t* uniq, int* inv, int cap_u, int* status, cudaStream_t stream) {
   const int blocks = (n + kThreads - 1) / kThreads;
   cudaMemsetAsync(cnt, 0, sizeof(int) * world, stream);
   if (n <= 0) {
     cudaMemsetAsync(off, 0, sizeof(int) * (world + 1), stream);
     return;
   }
-  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table), sc.hbits,
+  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, owner_world, salt, static_cast<DedupEntry*>(sc.table), sc.hbits,
                                                        sc.slot_of, cnt, status);
-  dedup_finalize_kernel<false><<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table),
+  launch_pdl(dedup_finalize_kernel<false>, dim3(blocks), dim3(kThreads), 0, stream, ids, n, world, owner_world, salt, static_cast<DedupEntry*>(sc.table),
                                                                 sc.slot_of, cnt, off, uniq, inv, cap_u, status, Sym{},
                                                                 ChanLayout{}, nullptr);
 }
 
-void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, uint64_t salt, DedupScratch sc, int* cnt, int* off,
-                              int64_t* uniq, int* inv, int cap_u, int* status, SymHost sym, ChanLayout lay, Ctrl* ctrl,
-                              cudaStream_t stream) {
+void dedup_bucketize_dispatch(const int64_t* ids, int n, int world, int owner_world, uint64_t salt, DedupScratch sc,
+                              int* cnt, int* off, int64_t* uniq, int* inv, int cap_u, int* status, SymHost sym,
+                              ChanLayout lay, Ctrl* ctrl, cudaStream_t stream) {
   if (n <= 0) {  // nothing to deduplicate: the plain dispatch still has to publish empty counts and the epoch
-    dedup_bucketize(ids, n, world, salt, sc, cnt, off, uniq, inv, cap_u, status, stream);
+    dedup_bucketize(ids, n, world, owner_world, salt, sc, cnt, off, uniq, inv, cap_u, status, stream);
     pull_dispatch_kernel<<<1, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, uniq, off);
     return;
   }
   const int blocks = (n + kThreads - 1) / kThreads;
   cudaMemsetAsync(cnt, 0, sizeof(int) * world, stream);
-  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table), sc.hbits,
+  dedup_insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, n, world, owner_world, salt, static_cast<DedupEntry*>(sc.table), sc.hbits,
                                                        sc.slot_of, cnt, status);
-  dedup_finalize_kernel<true><<<blocks, kThreads, 0, stream>>>(ids, n, world, salt, static_cast<DedupEntry*>(sc.table),
+  launch_pdl(dedup_finalize_kernel<true>, dim3(blocks), dim3(kThreads), 0, stream, ids, n, world, owner_world, salt, static_cast<DedupEntry*>(sc.table),
                                                                sc.slot_of, cnt, off, uniq, inv, cap_u, status,
                                                                to_sym(sym), lay, ctrl);
 }
@@ -590,10 +599,10 @@ void pull_probe(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, int* s
   const RowGeom g = row_geom(table.dim);
   const int grid = grid_for(static_cast<long long>(lay.capS));
   if (g.vec == 4)
-    pull_probe_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0,
+    launch_pdl(pull_probe_kernel<4>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0,
                                                         g.chunks, g.lpr);
   else
-    pull_probe_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0,
+    launch_pdl(pull_probe_kernel<1>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, to_view(table), slot_cache, insert ? 1 : 0,
                                                         g.chunks, g.lpr);
 }
 
@@ -610,10 +619,10 @@ void pull_gather(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const
   const RowGeom g = row_geom(table.dim);
   const int grid = grid_for(static_cast<long long>(lay.capS) * g.lpr);
   if (g.vec == 4)
-    pull_gather_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, to_view(table), slot_cache, g.chunks,
+    launch_pdl(pull_gather_kernel<4>, dim3(grid), dim3(kThreads), 0, stream, to_sym(sym), lay, ctrl, to_view(table), slot_cache, g.chunks,
                                                          g.lpr);
   else
-    pull_gather_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, to_view(table), slot_cache, g.chunks,
+    launch_pdl(pull_gather_kernel<1>, dim3(grid), dim3(kThreads), 0, stream, to_sym(sym), lay, ctrl, to_view(table), slot_cache, g.chunks,
                                                          g.lpr);
 }
 
@@ -625,11 +634,11 @@ void pull_combine(SymHost sym, ChanLayout lay, Ctrl* ctrl, const int* inv, int n
   const int grid = grid_for(rows * g.lpr);
   launch_wait(to_sym(sym), lay, ctrl, kWaitResponse, spin_limit, stream);
   if (g.vec == 4)
-    pull_combine_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
+    launch_pdl(pull_combine_kernel<4>, dim3(grid), dim3(kThreads), 0, stream, to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
                                                           bag_offsets, k, weights, mean ? 1 : 0, bag_mean, patch_value,
                                                           out);
   else
-    pull_combine_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
+    launch_pdl(pull_combine_kernel<1>, dim3(grid), dim3(kThreads), 0, stream, to_sym(sym), lay, ctrl, inv, n, dim, g.chunks, g.lpr,
                                                           bag_offsets, k, weights, mean ? 1 : 0, bag_mean, patch_value,
                                                           out);
 }
@@ -641,10 +650,10 @@ void push_scatter(const float* grads, const int* inv, int n, int dim, const int6
   if (rows <= 0) return;
   const int grid = grid_for(rows * g.lpr, kThreads, 148 * 16);
   if (g.vec == 4)
-    push_scatter_kernel<4><<<grid, kThreads, 0, stream>>>(grads, inv, n, dim, g.chunks, g.lpr, bag_offsets, k, weights,
+    launch_pdl(push_scatter_kernel<4>, dim3(grid), dim3(kThreads), 0, stream, grads, inv, n, dim, g.chunks, g.lpr, bag_offsets, k, weights,
                                                           mean ? 1 : 0, bag_mean, ugrad);
   else
-    push_scatter_kernel<1><<<grid, kThreads, 0, stream>>>(grads, inv, n, dim, g.chunks, g.lpr, bag_offsets, k, weights,
+    launch_pdl(push_scatter_kernel<1>, dim3(grid), dim3(kThreads), 0, stream, grads, inv, n, dim, g.chunks, g.lpr, bag_offsets, k, weights,
                                                           mean ? 1 : 0, bag_mean, ugrad);
 }
 
@@ -653,9 +662,9 @@ void push_dispatch(SymHost sym, ChanLayout lay, Ctrl* ctrl, float* ugrad, const 
   const RowGeom g = row_geom(dim);
   const int grid = grid_for(static_cast<long long>(max_n) * g.lpr);
   if (g.vec == 4)
-    push_dispatch_kernel<4><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, ugrad, off, dim, g.chunks, g.lpr);
+    launch_pdl(push_dispatch_kernel<4>, dim3(grid), dim3(kThreads), 0, stream, to_sym(sym), lay, ctrl, ugrad, off, dim, g.chunks, g.lpr);
   else
-    push_dispatch_kernel<1><<<grid, kThreads, 0, stream>>>(to_sym(sym), lay, ctrl, ugrad, off, dim, g.chunks, g.lpr);
+    launch_pdl(push_dispatch_kernel<1>, dim3(grid), dim3(kThreads), 0, stream, to_sym(sym), lay, ctrl, ugrad, off, dim, g.chunks, g.lpr);
 }
 
 namespace {
@@ -663,10 +672,10 @@ template <int VEC>
 void launch_update(int grid, cudaStream_t stream, const Sym& s, const ChanLayout& lay, Ctrl* ctrl, const TableView& t,
                    const int* slot_cache, const OptimPOD& optim, const float* lr, int chunks, int lpr) {
   switch (optim.type) {
-    case 0: push_update_kernel<VEC, 0><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
-    case 1: push_update_kernel<VEC, 1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
-    case 2: push_update_kernel<VEC, 2><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
-    default: push_update_kernel<VEC, 3><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+    case 0: launch_pdl(push_update_kernel<VEC, 0>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+    case 1: launch_pdl(push_update_kernel<VEC, 1>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+    case 2: launch_pdl(push_update_kernel<VEC, 2>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
+    default: launch_pdl(push_update_kernel<VEC, 3>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, t, slot_cache, optim, lr, chunks, lpr); break;
   }
 }
 }  // namespace
@@ -679,10 +688,10 @@ void push_apply(SymHost sym, ChanLayout lay, Ctrl* ctrl, TableHost table, const 
   const TableView t = to_view(table);
   launch_wait(s, lay, ctrl, kWaitPush, spin_limit, stream);
   if (g.vec == 4) {
-    if (sym.world > 1) push_merge_kernel<4><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr);
+    if (sym.world > 1) launch_pdl(push_merge_kernel<4>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, t, slot_cache, g.chunks, g.lpr);
     launch_update<4>(grid, stream, s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
   } else {
-    if (sym.world > 1) push_merge_kernel<1><<<grid, kThreads, 0, stream>>>(s, lay, ctrl, t, slot_cache, g.chunks, g.lpr);
+    if (sym.world > 1) launch_pdl(push_merge_kernel<1>, dim3(grid), dim3(kThreads), 0, stream, s, lay, ctrl, t, slot_cache, g.chunks, g.lpr);
     launch_update<1>(grid, stream, s, lay, ctrl, t, slot_cache, optim, lr, g.chunks, g.lpr);
   }
 }

@@ -74,7 +74,7 @@ group_dedup_insert_kernel(const int64_t* __restrict__ ids, int n, GroupDesc d, i
     slot = static_cast<uint64_t>(d.region_base[t]) + p;
     slot_of[i] = static_cast<int>(slot);
     if (won) {
-      cell = static_cast<int>(OwnerOf(d.salt[t], id, world)) * d.T + t;
+      cell = static_cast<int>(OwnerOf(d.salt[t], id, d.owner_world)) * d.T + t;
       lpos = atomicAdd(&s_cnt[cell], 1);
     }
   }
@@ -152,7 +152,7 @@ group_dedup_finalize_kernel(const int64_t* __restrict__ ids, int n, GroupDesc d,
     if (id == kEmptyKey) id = kEmptyKey - 1;
     const int t = segment_of(s_occ, d.T, i);
     const int slot = slot_of[i];
-    const int o = static_cast<int>(OwnerOf(d.salt[t], id, world));
+    const int o = static_cast<int>(OwnerOf(d.salt[t], id, d.owner_world));
     const unsigned long long pw = __ldcg(&table[slot].pos_win);
     const int u = s_off[o * d.T + t] + static_cast<int>(static_cast<uint32_t>(pw));
     inv[i] = u < cap_u ? u : 0;

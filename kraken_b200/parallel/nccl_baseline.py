@@ -29,7 +29,7 @@ class NcclSparseChannel:
 
     def _route(self, ids: torch.Tensor):
         uniq, inv = torch.unique(ids.reshape(-1), return_inverse=True)
-        owners = C.owner_of_cuda(uniq, self.salt, self.world).long()
+        owners = C.owner_of_cuda(uniq, self.salt, getattr(self, 'owner_world', self.world)).long()
         order = torch.argsort(owners, stable=True)
         send_counts = torch.bincount(owners, minlength=self.world)
         recv_counts = torch.empty_like(send_counts)

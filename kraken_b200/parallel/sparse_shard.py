@@ -333,6 +333,7 @@ class SparseChannel:
         self.serial = 0
         self.launches = 0  # kernels launched through this channel (for accounting)
         self._wait = 1 if world > 1 else 0  # the one-warp rendezvous kernels exist only between GPUs
+        self.owner_world = world            # rows live on ranks 0 .. owner_world - 1 (smaller after a live reshard)
 
     # ------------------------------------------------------------------ helpers
     def _lookup_phase(self, ids: torch.Tensor, insert: bool, share_from: Optional["SparseChannel"] = None) -> int:
@@ -352,7 +353,8 @@ class SparseChannel:
             # the dedup's second kernel also sends the unique ids to their owners' inboxes
             self.off, self.uniq, self.inv = self._own_off, self._own_uniq, self._own_inv
             C.dedup_bucketize(ids, self.world, self.salt, self.hkeys, self.slot_of, self.hbits,
-                              self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5], self.cap_u, h, lay, ctrl)
+                              self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5], self.cap_u, h, lay, ctrl,
+                              self.owner_world)
             self.launches += 2
         C.pull_probe(h, lay, ctrl, tbl, self.slot_cache, insert, self.spin)
         self.launches += 1 + self._wait  # (request wait +) probe, which also initialises the rows it creates
@@ -525,6 +527,7 @@ class GroupChannel:
         self.hkeys = None           # dedup scratch, one region per table, sized on first use
         self._shape_sig = None      # ids per table of the call the descriptors were built for
         self._views_sig = None      # generations of the tables the device-side descriptors describe
+        self.owner_world = world    # rows live on ranks 0 .. owner_world - 1 (smaller after a live reshard)
         self.table_views = None
         self.serial = 0
         self.launches = 0
@@ -575,7 +578,7 @@ class GroupChannel:
         h, lay, ctrl = self.arena.heap, self.lay, self.ctrl
         C.group_dedup_dispatch(ids_cat, self.occ_start, self.region_base, self.region_bits, self.salts, self.world,
                                self.hkeys, self.slot_of, self.cnt, self.off, self.uniq, self.inv, self.ctrl[4:5],
-                               self.cap_u, h, lay, ctrl)
+                               self.cap_u, h, lay, ctrl, self.owner_world)
         C.group_probe(h, lay, ctrl, self.table_views, self.T, self.dim, self.snap_t, self.slot_cache, self.ttab,
                       insert, self.spin)
         self.launches += 5  # memset is not counted: insert, finalize + dispatch, request wait, probe (+ init)

@@ -37,6 +37,7 @@ class GpuEngine(Engine):
         self.tickets: Dict[int, Tuple[Ticket, int, int, int]] = {}
         self.group_channels: Dict[Tuple[int, ...], GroupChannel] = {}
         self.group_tickets: Dict[Tuple[int, ...], tuple] = {}
+        self.owner_world = world   # sparse rows live on ranks 0 .. owner_world - 1; reshard() changes it
         self.dense_init: Dict[int, torch.Tensor] = {}
         self.bucket: Optional[BucketSet] = None
         self._comm_stream: Optional[torch.cuda.Stream] = None
@@ -249,6 +250,7 @@ class GpuEngine(Engine):
         ch = SparseChannel(self.sparse[table_id], self.rank, self.world, cap, self.group, self.cfg.spin_limit,
                            self._salt(table_id), max_unique=self.cfg.max_unique_per_call,
                            max_per_owner=self.cfg.max_per_owner_per_call)
+        ch.owner_world = self.owner_world
         self.channels[table_id] = ch
         return ch
 
@@ -282,6 +284,7 @@ class GpuEngine(Engine):
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
             ch = NcclSparseChannel(self.sparse[table_id], self.rank, self.world, int(t.item()), self.group,
                                    self._salt(table_id), self.cfg.spin_limit)
+            ch.owner_world = self.owner_world
             self.nccl_channels[table_id] = ch
         return ch
 
@@ -312,6 +315,7 @@ class GpuEngine(Engine):
             cap = int(t.item())
         ch = GroupChannel([self.sparse[t] for t in tids], self.rank, self.world, cap, self.group, self.cfg.spin_limit,
                           salts=[self._salt(t) for t in tids])
+        ch.owner_world = self.owner_world
         self.group_channels[tids] = ch
         return ch
 
@@ -523,6 +527,78 @@ class GpuEngine(Engine):
         with self._region("push"):
             ch.push(g, self.lr_dev, ticket=ticket, ids=idx)
 
+    # ------------------------------------------------------------------ live reshard
+    def reshard(self, owner_world: int) -> int:
+        """Changes, inside the running job, how many of the ranks hold sparse rows: afterwards row ``id`` of a
+        table lives on rank ``OwnerOf(salt, id, owner_world)`` (ranks >= owner_world hold none and act as workers
+        only).  Collective, between steps.  Every rank compacts the rows it no longer owns on the device
+        (``table_export`` with the owner filter), sends each with its optimizer state and step count to the new
+        owner (one all-to-all per table), rebuilds its own table from the rows it keeps and inserts what it
+        receives - the scale-out / scale-in of kraken/ps/ps.cc:125-372 (TransferTo, CleanTables) without files.
+        Returns how many rows this rank sent away."""
+        owner_world = int(owner_world)
+        if not 1 <= owner_world <= self.world:
+            raise C.KrakenError(f"owner_world must be between 1 and {self.world}")
+        if owner_world == self.owner_world:
+            return 0
+        torch.cuda.synchronize(self.device)
+        sent = 0
+        dev = self.device
+        for tid, t in sorted(self.sparse.items()):
+            salt = self._salt(tid)
+            away = t.export(filter_mode=2, salt=salt, world=owner_world, rank=self.rank)   # rows another rank will own
+            keep = t.export(filter_mode=1, salt=salt, world=owner_world, rank=self.rank)
+            n = int(away["ids"].numel())
+            sent += n
+            skeys = sorted(int(k) for k in away["states"])
+            has_steps = 0 in away["states_i"]
+            owners = (C.owner_of_cuda(away["ids"], salt, owner_world).long() if n
+                      else torch.empty(0, dtype=torch.long, device=dev))
+            order = torch.argsort(owners, stable=True)
+            send = torch.bincount(owners, minlength=self.world)
+            recv = torch.empty_like(send)
+            if self.world > 1:
+                dist.all_to_all_single(recv, send, group=self.group)
+            else:
+                recv.copy_(send)
+            sc, rc = send.tolist(), recv.tolist()
+
+            def a2a(x: torch.Tensor, width: int) -> torch.Tensor:
+                out = torch.empty((sum(rc), width) if width else (sum(rc),), dtype=x.dtype, device=dev)
+                if self.world > 1:
+                    dist.all_to_all_single(out, x[order].contiguous(), rc, sc, group=self.group)
+                else:
+                    out.copy_(x[order])
+                return out
+
+            in_ids = a2a(away["ids"], 0)
+            in_vals = a2a(away["vals"], t.dim)
+            in_states = {k: a2a(away["states"][k], t.dim) for k in skeys}
+            in_steps = {0: a2a(away["states_i"][0], 0)} if has_steps else {}
+            C.table_clear(t.host())
+            t.val.zero_()
+            for k, slab in enumerate(t.slabs):
+                if slab is not None:
+                    slab.fill_(t.optim_info["initial_accumulator_value"] if (t.optim_info["type"] == 0 and k == 0) else 0.0)
+            if t.steps is not None:
+                t.steps.zero_()
+            t.rows_hi = 0
+            t.import_rows(keep["ids"], keep["vals"], keep["states"], keep["states_i"])
+            t.import_rows(in_ids, in_vals, in_states, in_steps)
+        self.owner_world = owner_world
+        for ch in list(self.channels.values()) + list(self.group_channels.values()) + list(self.nccl_channels.values()):
+            ch.owner_world = owner_world
+        self.tickets.clear()         # slots resolved before the move are stale
+        self.group_tickets.clear()
+        for ch in self.channels.values():
+            ch.serial += 1
+        for ch in self.group_channels.values():
+            ch.serial += 1
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        return sent
+
     # ------------------------------------------------------------------ housekeeping
     def end_step(self) -> bool:
         """Between steps: grows tables whose load factor passed the limit and surfaces errors that
@@ -693,7 +769,7 @@ class GpuEngine(Engine):
                 states = {k: torch.empty((0, t.dim), device=dev) for k in skeys}
                 states_i = {k: torch.empty(0, dtype=torch.int64, device=dev) for k in ikeys}
             if self.world > 1:
-                owners = C.owner_of_cuda(ids, salt, self.world).long() if ids.numel() else torch.empty(0, dtype=torch.long, device=dev)
+                owners = C.owner_of_cuda(ids, salt, self.owner_world).long() if ids.numel() else torch.empty(0, dtype=torch.long, device=dev)
                 order = torch.argsort(owners, stable=True)
                 send = torch.bincount(owners, minlength=self.world)
                 recv = torch.empty_like(send)

@@ -55,6 +55,14 @@ def test_bucketed_dense_step_during_backward_matches_single_bucket(world):
     assert "DENSE_OVERLAP ok" in out, out[-2000:]
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_live_reshard_halves_and_restores_the_owners(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = run_ranks("mp_gpu_reshard_worker.py", world)
+    assert "LIVE_RESHARD ok" in out, out[-2000:]
+
+
 def test_nccl_baseline_exchange_matches_one_shard(tmp_path):
     """The NCCL-only path must give the same tables as the fused path's oracle."""
     if torch.cuda.device_count() < 2:
