@@ -11,7 +11,7 @@ import kraken_b200.pytorch as kk
 from kraken_b200._native import C
 from kraken_b200.utils.hashing import owner_of
 
-kk.initialize("gpu", seed=9, table_capacity=1 << 14)
+kk.initialize("gpu", seed=9, table_capacity=1 << 14, max_ids_per_call=20_000)
 eng = kk.native.engine()
 rank, world = eng.rank, eng.world
 dev = torch.device("cuda", torch.cuda.current_device())
