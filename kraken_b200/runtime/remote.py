@@ -748,11 +748,14 @@ class RemoteEngine(Engine):
         never repeated, so a push is applied exactly once.  ``done(positions, reply_tensors)`` is called
         for every accepted part with the positions (into ``ids``) it covered."""
         owners = self._owners(table_id, ids)
+        # every part carries the version of the ring it was partitioned on: a refetch triggered by one refused part
+        # must not let the remaining parts of the OLD partition pass a server's version check
+        version = self.version
         for node in np.unique(owners):
             sel = torch.from_numpy(np.nonzero(owners == node)[0])
             tensors = [ids[sel]] + ([payload[sel]] if payload is not None else [])
             try:
-                _, ts = self.ps[int(node)].call(rpc, {**meta, "table_id": table_id, "router_version": self.version},
+                _, ts = self.ps[int(node)].call(rpc, {**meta, "table_id": table_id, "router_version": version},
                                                 tensors)
             except RpcError as e:
                 if e.code not in self.RETRY_CODES:
@@ -836,9 +839,10 @@ class RemoteEngine(Engine):
             self._table(t, "dense")
             by_owner.setdefault(self.router.hit(C.mix64(t)), []).append(t)
         out: Dict[int, torch.Tensor] = {}
+        version = self.version  # of the ring the owners above were looked up on
         for owner, tids in by_owner.items():
             try:
-                _, ts = self.ps[owner].call(Rpc.COMBINE_PULL_DENSE, {"table_ids": tids, "router_version": self.version})
+                _, ts = self.ps[owner].call(Rpc.COMBINE_PULL_DENSE, {"table_ids": tids, "router_version": version})
                 for t, v in zip(tids, ts):
                     out[t] = v.view(*self.tables[t].shape)
             except RpcError as e:
@@ -853,6 +857,7 @@ class RemoteEngine(Engine):
         gets its parts again table by table through ``_call_sparse`` (which re-partitions and retries)."""
         owners = [self._owners(t, u) for t, u in zip(table_ids, uniqs)]
         nodes = sorted({int(n) for o in owners for n in np.unique(o)})
+        version = self.version  # of the ring this partition was made on (see _call_sparse)
         for node in nodes:
             sels = [torch.from_numpy(np.nonzero(o == node)[0]) for o in owners]
             ks = [k for k, sel in enumerate(sels) if sel.numel() > 0]
@@ -863,7 +868,7 @@ class RemoteEngine(Engine):
                     tensors.append(payloads[k][sels[k]])
             try:
                 _, ts = self.ps[node].call(rpc, {**meta, "table_ids": [table_ids[k] for k in ks],
-                                                 "router_version": self.version}, tensors)
+                                                 "router_version": version}, tensors)
                 for j, k in enumerate(ks):
                     done(k, sels[k], [ts[j]] if ts else [])
             except RpcError as e:
