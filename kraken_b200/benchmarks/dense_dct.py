@@ -20,10 +20,13 @@ def main():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--batch", type=int, default=1024)
     p.add_argument("--dct", action="store_true")
+    p.add_argument("--no-overlap", action="store_true",
+                   help="step all buckets after the backward pass instead of each as soon as its gradients exist")
+    p.add_argument("--graph", action="store_true", help="replay the training step as one CUDA graph (not with --dct)")
     a = p.parse_args()
     world, rank = world_rank()
     kk.initialize("gpu", emitter_type=kk.EmitterType.kDCT if a.dct else kk.EmitterType.kDefault, life_span=1000,
-                  eta=0.75)
+                  eta=0.75, overlap_dense_step=not a.no_overlap)
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(0)
     model = MLP(784, [4096, 4096, 4096, 10]).to(dev)
@@ -34,11 +37,16 @@ def main():
     batches = [tuple(t.to(dev) for t in mnist_like(rng, means, a.batch)) for _ in range(total)]
     scale = 1.0 / world
 
-    def step(x, y):
+    def eager_step(x, y):
         loss = torch.nn.functional.cross_entropy(model(x), y) * scale
         loss.backward()
         opt.step()
         return loss
+
+    step = eager_step
+    if a.graph and not a.dct:
+        from kraken_b200.utils.graph import GraphedStep
+        step = GraphedStep(eager_step, batches[0], warmup=2, optimizer=None)
 
     for i in range(a.warmup):
         step(*batches[i])
@@ -52,7 +60,9 @@ def main():
     n_params = sum(p.numel() for p in model.parameters())
     rec = {"benchmark": "dense_mlp" + ("_dct" if a.dct else ""), "n_gpus": world, "batch_per_gpu": a.batch,
            "params": n_params, "samples_per_sec": a.batch * world * a.steps / (ms / 1e3), "ms_per_step": ms / a.steps,
-           "final_loss": loss.item() * world}
+           "final_loss": loss.item() * world, "dense_step": "all buckets after backward" if a.no_overlap else
+           "each bucket as soon as its gradients exist", "launch": "cuda-graph replay" if (a.graph and not a.dct) else "eager",
+           "buckets": len(kk.native.engine().bucket.buckets) if getattr(kk.native.engine(), "bucket", None) else 0}
 
     # the fused dense step alone (reduce-scatter + optimizer + all-gather in one kernel), on whatever the
     # gradient buffer holds; every rank starts each step together (the timer synchronises and barriers)
