@@ -10,7 +10,7 @@ import numpy as np
 import torch
 
 import kraken_b200.pytorch as kk
-from kraken_b200.benchmarks.common import DeviceTimer, emit, world_rank
+from kraken_b200.benchmarks.common import DeviceTimer, emit, measure_copy_gbs, measure_peer_gbs, world_rank
 from kraken_b200.models import MLP, mnist_like
 
 
@@ -75,6 +75,20 @@ def main():
             timer.start()
             eng.dense_step()
             step_ms += timer.stop_ms()
+        us_eager = step_ms / 10 * 1e3
+        # the same call as one CUDA-graph replay: what it costs inside a captured training step, without the
+        # host's launch overhead between its short kernels
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            eng.dense_step()
+        for _ in range(3):
+            g.replay()
+        step_ms = 0.0
+        for _ in range(10):
+            timer.start()
+            g.replay()
+            step_ms += timer.stop_ms()
         us = step_ms / 10 * 1e3
         n_pad = int(eng.bucket.n_pad)
         # per GPU and direction: (G - 1) / G of the bucket comes in as gradient slices and goes out as weights
@@ -82,8 +96,11 @@ def main():
         # HBM: G gradient slices read + zeroed bucket, owned slice of value and momentum read + written,
         # the whole updated bucket written once by the owners
         hbm = n_pad * 4 * (1 + 1 + 1) + (n_pad / world) * 4 * 4
-        link_us, hbm_us = link / 770e3, hbm / 6552e3
-        rec.update({"dense_step_us": round(us, 1), "dense_step_nvlink_bound_us": round(link_us, 1),
+        hbm_gbs, link_gbs = measure_copy_gbs(dev), measure_peer_gbs()
+        link_us, hbm_us = (link / (link_gbs * 1e3) if link_gbs > 0 else 0.0), hbm / (hbm_gbs * 1e3)
+        rec.update({"dense_step_us": round(us, 1), "dense_step_eager_us": round(us_eager, 1),
+                    "hbm_copy_gbs": round(hbm_gbs, 1), "peer_copy_gbs_per_direction": round(link_gbs, 1),
+                    "dense_step_nvlink_bound_us": round(link_us, 1),
                     "dense_step_hbm_bound_us": round(hbm_us, 1),
                     "dense_step_roofline_fraction": round(max(link_us, hbm_us) / us, 3)})
     emit(rec)
