@@ -175,6 +175,7 @@ class GpuEngine(Engine):
         b.buckets[k].set_active([True] * len(b.buckets[k].table_ids))
         with self._region("dense_step"), torch.cuda.stream(self._comm_stream):
             b.step_bucket(k, self.lr_dev)
+        self._comm_used = True
 
     def dense_step(self) -> None:
         """One fused optimizer step over every dense table (bound-parameter path)."""
@@ -194,8 +195,9 @@ class GpuEngine(Engine):
                 main.wait_stream(side)
             else:
                 b.step(self.lr_dev)
-            if self._comm_stream is not None:
+            if getattr(self, "_comm_used", False):
                 main.wait_stream(self._comm_stream)  # buckets that were stepped during the backward pass
+                self._comm_used = False
         self._bucket_ready.clear()
         self._dense_pending = False
         self._pushed.clear()
@@ -669,9 +671,13 @@ class GpuEngine(Engine):
             return
         t = self.sparse[table_id]
         ch = self.channels.get(table_id)
-        if ch is not None:
-            n_ids = min(n_ids, ch.cap_u)  # no more unique ids than the exchange buffers admit
         inflow = n_ids * self.world  # worst case: every rank's ids of this call belong to this shard
+        if ch is not None:
+            # no more than the exchange buffers admit (world x cap_s), and with a uniform owner hash about
+            # 1 / world of every rank's unique ids - twice that is reserved; a shard that still runs full
+            # reports kTableFull and is grown by end_step()
+            n_ids = min(n_ids, ch.cap_u)
+            inflow = min(self.world * ch.cap_s, 2 * n_ids) if self.world > 1 else n_ids
         hi = getattr(t, "rows_hi", 0) + inflow
         if hi > 0.6 * t.capacity:
             exact = t.num_rows()
