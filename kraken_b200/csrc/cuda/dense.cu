@@ -22,6 +22,10 @@
 // f = g + e into per-owner (index, value) lists and the owner scatter-adds the
 // lists of all ranks (dense_gather_coo) before step 3 reads its accumulator.
 // DCT here is Dynamic Communication Thresholding, kraken/worker/dct_emitter.cc:16-43.
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+
 #include "common.cuh"
 #include "dense_kernels.h"
 
@@ -88,70 +92,121 @@ dense_gather_coo_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long sli
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 3)
+// The update grid.  OPT fixes the optimizer type at compile time (-1: read it from the descriptor) and
+// SLABS is the bit mask of state slabs that exist, so that an SGD-momentum step carries 12 registers of
+// payload per float4 group instead of 20 and the switch in UpdateElem folds away.  A block handles kIlp
+// consecutive runs of 256 float4 groups and every load of a thread is issued before the first is used:
+// HBM needs ~45 KB of reads in flight per SM all the time, and a thread alternates between a load and a
+// store phase, so the SM must hold several times that in resident threads x bytes per thread.
+template <int OPT, int SLABS, bool MULTI>
+__global__ void __launch_bounds__(kThreads)
 dense_step_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, float* __restrict__ s0,
                   float* __restrict__ s1, float* __restrict__ s2, float* acc, const int* __restrict__ chunk_table,
                   int* table_steps, const uint8_t* __restrict__ table_active, int n_tables, OptimPOD optim,
                   const float* __restrict__ lr_ptr, float grad_scale, int use_coo) {
+  constexpr int kIlp = MULTI ? 2 : 4;
+  constexpr bool kS0 = (SLABS & 1) != 0, kS1 = (SLABS & 2) != 0, kS2 = (SLABS & 4) != 0;
+  if (OPT >= 0) optim.type = static_cast<uint8_t>(OPT);
   const uint32_t epoch = ctrl->epoch + 1;
-  const long long slice = n_pad / sym.world;
-  const long long base = slice * sym.rank;
+  const int world = MULTI ? sym.world : 1;
+  const long long slice = n_pad / world;
+  const long long base = slice * (MULTI ? sym.rank : 0);
   const float lr = *lr_ptr;
   const bool aborted = ctrl->abort != 0;  // a peer's gradient never arrived: change nothing, keep the flags moving
+  float* const param = sym.at<float>(sym.rank, lay.param);
+  float* const grad = sym.at<float>(sym.rank, lay.grad);
 
-  const long long gtid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  const long long gsize = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long q = gtid; q * 4 < slice && !aborted; q += gsize) {
-    const long long li = q * 4;      // offset inside the slice
-    const long long gi = base + li;  // offset inside the flat buffer
-    const int t = chunk_table[gi / kDenseChunk];
-    if (t < 0 || !table_active[t]) {
-      if (use_coo) *reinterpret_cast<float4*>(acc + li) = make_float4(0.f, 0.f, 0.f, 0.f);
-      continue;
-    }
-    float g[4] = {0.f, 0.f, 0.f, 0.f};
-    if (use_coo) {
-      const float4 a = *reinterpret_cast<const float4*>(acc + li);
-      g[0] = a.x, g[1] = a.y, g[2] = a.z, g[3] = a.w;
-      *reinterpret_cast<float4*>(acc + li) = make_float4(0.f, 0.f, 0.f, 0.f);
-    } else {
-      for (int k = 0; k < sym.world; ++k) {
-        const int p = (sym.rank + k) % sym.world;
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(sym.at<float>(p, lay.grad) + gi));
-        g[0] += v.x, g[1] += v.y, g[2] += v.z, g[3] += v.w;
+  const long long groups = slice / 4;
+  const long long per_block = static_cast<long long>(kThreads) * kIlp;
+  for (long long b0 = blockIdx.x * per_block; b0 < groups && !aborted; b0 += gridDim.x * per_block) {
+    long long li[kIlp];
+    int tab[kIlp];
+    bool inside[kIlp];
+    float4 g[kIlp], w[kIlp], a0[kIlp], a1[kIlp], a2[kIlp];
+#pragma unroll
+    for (int u = 0; u < kIlp; ++u) {
+      const long long q = b0 + u * kThreads + threadIdx.x;
+      li[u] = q * 4;  // offset inside the slice; base + li is the offset inside the flat buffer
+      inside[u] = q < groups;
+      tab[u] = inside[u] ? chunk_table[(base + li[u]) / kDenseChunk] : -1;
+      g[u] = a0[u] = a1[u] = a2[u] = w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      // none of the loads below waits for the table lookup above: a chunk that takes no update is read all the same
+      if (!inside[u]) continue;
+      w[u] = *reinterpret_cast<const float4*>(param + base + li[u]);
+      if (kS0) a0[u] = *reinterpret_cast<const float4*>(s0 + li[u]);
+      if (kS1) a1[u] = *reinterpret_cast<const float4*>(s1 + li[u]);
+      if (kS2) a2[u] = *reinterpret_cast<const float4*>(s2 + li[u]);
+      if (use_coo) {
+        g[u] = *reinterpret_cast<const float4*>(acc + li[u]);
+      } else if (!MULTI) {
+        g[u] = __ldcs(reinterpret_cast<const float4*>(grad + li[u]));
+      } else {
+        // four peers' slices requested before the first is added (a peer load is a round trip over the switch)
+        for (int k0 = 0; k0 < world; k0 += 4) {
+          float4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + j < world) {
+              const int p = (sym.rank + k0 + j) % world;
+              v[j] = __ldcg(reinterpret_cast<const float4*>(sym.at<float>(p, lay.grad) + base + li[u]));
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[u].x += v[j].x, g[u].y += v[j].y, g[u].z += v[j].z, g[u].w += v[j].w;
+        }
       }
     }
-    const int64_t step = static_cast<int64_t>(table_steps[t]) + 1;
-    const AdamBias ab = optim.type == 1 ? AdamBiasAt(optim, step) : AdamBias{1.f, 1.f};
-    float* wptr = sym.at<float>(sym.rank, lay.param) + gi;
-    float w[4], a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0}, a2[4] = {0, 0, 0, 0};
-    *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(wptr);
-    if (s0) *reinterpret_cast<float4*>(a0) = *reinterpret_cast<const float4*>(s0 + li);
-    if (s1) *reinterpret_cast<float4*>(a1) = *reinterpret_cast<const float4*>(s1 + li);
-    if (s2) *reinterpret_cast<float4*>(a2) = *reinterpret_cast<const float4*>(s2 + li);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) UpdateElem(optim, lr, g[e] * grad_scale, step, ab, w[e], a0[e], a1[e], a2[e]);
-    if (s0) *reinterpret_cast<float4*>(s0 + li) = *reinterpret_cast<float4*>(a0);
-    if (s1) *reinterpret_cast<float4*>(s1 + li) = *reinterpret_cast<float4*>(a1);
-    if (s2) *reinterpret_cast<float4*>(s2 + li) = *reinterpret_cast<float4*>(a2);
-    const float4 wn = *reinterpret_cast<float4*>(w);
-    for (int k = 0; k < sym.world; ++k) {
-      const int p = (sym.rank + k) % sym.world;
-      *reinterpret_cast<float4*>(sym.at<float>(p, lay.param) + gi) = wn;
+    for (int u = 0; u < kIlp; ++u) {
+      if (!inside[u]) continue;
+      if (use_coo) *reinterpret_cast<float4*>(acc + li[u]) = make_float4(0.f, 0.f, 0.f, 0.f);
+      // single GPU: nobody else reads this gradient, so it is cleared for the next backward here
+      if (!MULTI) __stcs(reinterpret_cast<float4*>(grad + li[u]), make_float4(0.f, 0.f, 0.f, 0.f));
+      if (tab[u] < 0 || !table_active[tab[u]]) continue;
+      const int64_t step = static_cast<int64_t>(table_steps[tab[u]]) + 1;
+      const AdamBias ab = optim.type == 1 ? AdamBiasAt(optim, step) : AdamBias{1.f, 1.f};
+      UpdateElem(optim, lr, g[u].x * grad_scale, step, ab, w[u].x, a0[u].x, a1[u].x, a2[u].x);
+      UpdateElem(optim, lr, g[u].y * grad_scale, step, ab, w[u].y, a0[u].y, a1[u].y, a2[u].y);
+      UpdateElem(optim, lr, g[u].z * grad_scale, step, ab, w[u].z, a0[u].z, a1[u].z, a2[u].z);
+      UpdateElem(optim, lr, g[u].w * grad_scale, step, ab, w[u].w, a0[u].w, a1[u].w, a2[u].w);
+      if (kS0) *reinterpret_cast<float4*>(s0 + li[u]) = a0[u];
+      if (kS1) *reinterpret_cast<float4*>(s1 + li[u]) = a1[u];
+      if (kS2) *reinterpret_cast<float4*>(s2 + li[u]) = a2[u];
+      if (!MULTI) {
+        *reinterpret_cast<float4*>(param + li[u]) = w[u];
+      } else {
+        for (int k = 0; k < world; ++k) {
+          const int p = (sym.rank + k) % world;
+          *reinterpret_cast<float4*>(sym.at<float>(p, lay.param) + base + li[u]) = w[u];
+        }
+      }
     }
   }
 
   if (last_block_done(&ctrl->done[0])) {
-    if (threadIdx.x < sym.world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_done) + sym.rank, epoch);
+    if (threadIdx.x < world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_done) + sym.rank, epoch);
     for (int t = threadIdx.x; t < n_tables && !aborted; t += blockDim.x)
       if (table_active[t]) table_steps[t] += 1;
     if (threadIdx.x == 0) ctrl->epoch = epoch;
   }
-  if (sym.world > 1) return;  // other ranks still read this rank's gradient: zeroed by a later launch
-  // single GPU: every thread zeroes exactly the elements it has just consumed
-  float4* gz = reinterpret_cast<float4*>(sym.at<float>(sym.rank, lay.grad));
-  for (long long q = gtid; q * 4 < n_pad; q += gsize) gz[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (use_coo && gtid < sym.world) sym.at<int>(sym.rank, lay.coo_cnt)[gtid] = 0;
+  // other ranks still read this rank's gradient: with peers it is zeroed by a later launch
+  if (!MULTI && use_coo && blockIdx.x == 0 && threadIdx.x == 0) sym.at<int>(sym.rank, lay.coo_cnt)[0] = 0;
+}
+
+template <int OPT, int SLABS>
+void launch_dense_step(bool multi, int grid, cudaStream_t stream, Sym s, DenseLayout lay, DenseCtrl* ctrl,
+                       long long n_pad, float* s0, float* s1, float* s2, float* acc, const int* chunk_table,
+                       int* table_steps, const uint8_t* table_active, int n_tables, OptimPOD optim, const float* lr,
+                       float grad_scale, int use_coo) {
+  if (multi)
+    dense_step_kernel<OPT, SLABS, true><<<grid, kThreads, 0, stream>>>(
+        s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps, table_active, n_tables, optim, lr, grad_scale,
+        use_coo);
+  else
+    dense_step_kernel<OPT, SLABS, false><<<grid, kThreads, 0, stream>>>(
+        s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps, table_active, n_tables, optim, lr, grad_scale,
+        use_coo);
 }
 
 // ------------------------------------------------------------------ DCT
@@ -260,13 +315,36 @@ void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, 
                 OptimPOD optim, const float* lr, float grad_scale, int use_coo, uint32_t spin_limit,
                 cudaStream_t stream) {
   const long long slice = n_pad / sym.world;
-  const int grid = grid_for(slice / 4, 148 * 8);
   const Sym s = to_sym(sym);
   const bool multi = sym.world > 1;
+  // single GPU: one pass per block (short-lived blocks keep loads and stores of different blocks interleaved).
+  // With peers a block ends on a fence that waits for its stores into peer memory to be acknowledged over
+  // the switch, so there the grid is resident and strides: a few hundred such waits instead of thousands.
+  const int per_block = kThreads * (multi ? 2 : 4);
+  const int grid = static_cast<int>(
+      std::min<long long>((slice / 4 + per_block - 1) / per_block, multi ? 148 * 3 : 1 << 20));
   if (multi) dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 0, spin_limit);
-  if (use_coo) dense_gather_coo_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, slice, acc);
-  dense_step_kernel<<<grid, kThreads, 0, stream>>>(s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps,
-                                                   table_active, n_tables, optim, lr, grad_scale, use_coo);
+  if (use_coo) dense_gather_coo_kernel<<<grid_for(slice / 4, 148 * 8), kThreads, 0, stream>>>(s, lay, ctrl, slice, acc);
+  const int slabs = (s0 ? 1 : 0) | (s1 ? 2 : 0) | (s2 ? 4 : 0);
+#define KB_DENSE_STEP(OPT, SLABS)                                                                                    \
+  launch_dense_step<OPT, SLABS>(multi, grid, stream, s, lay, ctrl, n_pad, s0, s1, s2, acc, chunk_table, table_steps, \
+                                table_active, n_tables, optim, lr, grad_scale, use_coo)
+  const int key = optim.type * 8 + slabs;
+  switch (key) {
+    case 0 * 8 + 1: KB_DENSE_STEP(0, 1); break;  // Adagrad
+    case 1 * 8 + 3: KB_DENSE_STEP(1, 3); break;  // Adam
+    case 1 * 8 + 7: KB_DENSE_STEP(1, 7); break;  // Adam, amsgrad
+    case 2 * 8 + 1: KB_DENSE_STEP(2, 1); break;  // RMSprop
+    case 2 * 8 + 3: KB_DENSE_STEP(2, 3); break;  //   centered
+    case 2 * 8 + 5: KB_DENSE_STEP(2, 5); break;  //   momentum
+    case 2 * 8 + 7: KB_DENSE_STEP(2, 7); break;  //   centered, momentum
+    case 3 * 8 + 0: KB_DENSE_STEP(3, 0); break;  // SGD
+    case 3 * 8 + 1: KB_DENSE_STEP(3, 1); break;  // SGD, momentum
+    default:
+      throw std::invalid_argument("dense_step: optimizer type " + std::to_string(int(optim.type)) +
+                                  " does not go with state slab mask " + std::to_string(slabs));
+  }
+#undef KB_DENSE_STEP
   if (multi) {
     dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 1, spin_limit);
     dense_zero_kernel<<<grid_for(n_pad / 4, 148 * 8), kThreads, 0, stream>>>(s, lay, n_pad, use_coo);
