@@ -15,6 +15,7 @@
 #include "core/hash.h"
 #include "core/router.h"
 #include "core/serialize.h"
+#include "core/snappy_codec.h"
 #include "core/task_queue.h"
 #include "cpu/cpu_ops.h"
 #include "cpu/cpu_shard.h"
@@ -453,6 +454,25 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     MemSource s(b.data(), b.size());
     Reader r(&s);
     return from_host(r.Tensor());
+  });
+  // RPC body compression in the Snappy block format (kraken/common/compress.h:18-91)
+  m.def("snappy_compress", [](const std::string& b) {
+    std::string out;
+    {
+      py::gil_scoped_release nogil;
+      snappy_codec::Compress(b.data(), b.size(), &out);
+    }
+    return py::bytes(out);
+  });
+  m.def("snappy_uncompress", [](const std::string& b) {
+    std::string out;
+    bool ok;
+    {
+      py::gil_scoped_release nogil;
+      ok = snappy_codec::Uncompress(b.data(), b.size(), &out);
+    }
+    KB_CHECK(ok, err::kSnappyUncompress, "malformed Snappy stream");
+    return py::bytes(out);
   });
   m.def("serialize_value", [](const py::dict& d) {
     MemSink s;

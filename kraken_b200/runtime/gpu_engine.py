@@ -299,11 +299,50 @@ class GpuEngine(Engine):
             self._nccl_ids = {**getattr(self, "_nccl_ids", {}), table_id: (indices, *self._sig(indices), idx)}
             return rows.view(*indices.shape, info.dimension)
         ch = self._channel(table_id, idx.numel())
+        if self.cfg.long_id_streams:
+            rounds = self._rounds(idx.numel(), ch.cap)
+            if rounds > 1:
+                return self._pull_in_rounds(table_id, ch, idx, rounds).view(*indices.shape, info.dimension)
         self._ensure_room(table_id, idx.numel())
         with self._region("pull"):
             rows, ticket = ch.pull(idx)
         self._remember(table_id, ticket, indices)
         return rows.view(*indices.shape, info.dimension)
+
+    # ------------------------------------------------------------------ id streams longer than the buffers
+    def _rounds(self, n: int, cap: int) -> int:
+        """How many exchanges of at most ``cap`` ids a call of ``n`` ids needs - the maximum over the ranks,
+        because every exchange is collective: a rank with fewer ids joins the later rounds with none."""
+        r = max(1, -(-int(n) // int(cap)))
+        if self.world > 1:
+            t = torch.tensor([r], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            r = int(t.item())
+        return r
+
+    def _pull_in_rounds(self, table_id: int, ch: SparseChannel, idx: torch.Tensor, rounds: int) -> torch.Tensor:
+        """The chunked exchange for long id streams: round k looks up ids [k * cap, (k + 1) * cap) through the
+        same buffers (the reference's emitter has no size limit per request, kraken/worker/emitter.cc:123-183).
+        No ticket is kept: the push that follows deduplicates its own rounds."""
+        flat = idx.reshape(-1)
+        out = torch.empty((flat.numel(), ch.table.dim), dtype=torch.float32, device=self.device)
+        self.tickets.pop(table_id, None)
+        with self._region("pull"):
+            for k in range(rounds):
+                part = flat[k * ch.cap:(k + 1) * ch.cap]
+                self._ensure_room(table_id, part.numel())
+                ch.pull(part, out=out[k * ch.cap:k * ch.cap + part.numel()])
+        return out
+
+    def _push_in_rounds(self, ch: SparseChannel, idx: torch.Tensor, g: torch.Tensor, rounds: int) -> None:
+        """Push of a long id stream.  An id that occurs in several rounds is updated once per round it occurs
+        in (the reference applies one update per request too); within a round duplicates are summed first."""
+        flat, g2 = idx.reshape(-1), g.reshape(-1, ch.table.dim)
+        with self._region("push"):
+            for k in range(rounds):
+                a, b = k * ch.cap, min((k + 1) * ch.cap, flat.numel())
+                a = min(a, b)
+                ch.push(g2[a:b], self.lr_dev, ticket=None, ids=flat[a:b])
 
     # ------------------------------------------------------------------ several tables, one exchange
     def _group_channel(self, tids: Tuple[int, ...], n_total: int) -> GroupChannel:
@@ -526,6 +565,10 @@ class GpuEngine(Engine):
         g = grad.detach()
         if g.device != self.device:
             g = g.to(self.device)
+        if self.cfg.long_id_streams:
+            rounds = self._rounds(indices.numel(), ch.cap)
+            if rounds > 1:
+                return self._push_in_rounds(ch, self._prep_ids(indices), g.to(torch.float32), rounds)
         with self._region("push"):
             ch.push(g, self.lr_dev, ticket=ticket, ids=idx)
 

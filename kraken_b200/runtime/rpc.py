@@ -11,8 +11,9 @@ kraken/rpc/indep_connecter.cc).  This is the same idea on plain TCP sockets:
 Bodies may be compressed (header byte ``compress``: 0 = none, 1 = compressed): the reference
 compresses worker<->server and server<->server bodies with Snappy and never the header
 (kraken/common/compress.h:18-91, kraken/rpc/station.h:62-119 answers with the request's type).
-No Snappy library is available offline, so code 1 means zlib level 1 here; a server answers in
-the compression of the request.
+Code 1 is a Snappy stream here too, written and read by the framework's own codec
+(csrc/core/snappy_codec.h: the public block format, no library); a server answers in the
+compression of the request.
 
 RPC type numbers are the reference's (kraken/protocol/rpc_func_type.h:8-38).
 A ``Station`` serves registered handlers on a thread pool; a ``Connecter`` is a
@@ -27,7 +28,6 @@ import socketserver
 import struct
 import threading
 import time
-import zlib
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -110,12 +110,12 @@ def _recv_exact(sock: socket.socket, n: int) -> bytes:
     return bytes(buf)
 
 
-COMPRESS_NONE, COMPRESS_ZLIB = 0, 1
+COMPRESS_NONE, COMPRESS_SNAPPY = 0, 1   # CompressType::kNo / kSnappy, kraken/rpc/protocol.h:7-10
 
 
 def send_frame(sock: socket.socket, stamp: int, code: int, body: bytes, compress: int = COMPRESS_NONE) -> None:
-    if compress == COMPRESS_ZLIB:
-        body = zlib.compress(body, 1)
+    if compress == COMPRESS_SNAPPY:
+        body = C.snappy_compress(bytes(body))
     sock.sendall(struct.pack("<I", len(body)) + HEADER.pack(stamp, code, compress) + body)
 
 
@@ -124,8 +124,11 @@ def recv_frame(sock: socket.socket) -> Tuple[int, int, bytes, int]:
     (n,) = struct.unpack("<I", _recv_exact(sock, 4))
     stamp, code, compress = HEADER.unpack(_recv_exact(sock, HEADER.size))
     body = _recv_exact(sock, n)
-    if compress == COMPRESS_ZLIB:
-        body = zlib.decompress(body)
+    if compress == COMPRESS_SNAPPY:
+        try:
+            body = C.snappy_uncompress(body)
+        except C.KrakenError as e:   # kSnappyUncompress: the stream is unusable, drop the connection
+            raise ConnectionError(str(e)) from e
     elif compress != COMPRESS_NONE:
         raise ConnectionError(f"unknown body compression {compress}")
     return stamp, code, body, compress
@@ -147,7 +150,7 @@ class Station:
                 while True:
                     try:
                         stamp, rpc_type, body, comp = recv_frame(self.request)
-                    except (ConnectionError, OSError, struct.error, zlib.error):
+                    except (ConnectionError, OSError, struct.error):
                         return
                     fn = station.handlers.get(rpc_type)
                     try:

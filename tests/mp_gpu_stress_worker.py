@@ -177,6 +177,25 @@ for t, exp, dim in ((ta, exp_a, DIM_A), (tb, exp_b, DIM_B)):
     if bad:
         print(f"rank {rank} table {t}: " + "; ".join(bad), flush=True)
         ok.zero_()
+# a call longer than the exchange buffers, of a different length on every rank: the ranks agree on the
+# number of rounds and the shorter ones join the later rounds with no ids
+tc = kk.register_sparse_table("c", 4, torch.float32, kk.InitializerType.kConstant, {"value": "0.5"})
+eng.cfg.long_id_streams = True
+n_long = (rank + 1) * PER + PER // 3 + 17
+long_ids = torch.arange(n_long, device=dev) * 13 + (1 << 41)      # ranks overlap: rank r's ids contain rank r-1's
+for _ in range(2):
+    got = kk.pull_sparse_table(tc, long_ids)
+    if got.shape != (n_long, 4) or not bool((got == 0.5).all()):
+        print(f"rank {rank}: long id stream came back wrong", flush=True)
+        ok.zero_()
+    kk.push_sparse_table(tc, long_ids, torch.zeros(n_long, 4, device=dev))   # Adam with zero gradients moves nothing
+rows_c = torch.tensor([eng.sparse[tc].num_rows()], device=dev)
+all_reduce(rows_c)
+if int(rows_c.item()) != world * PER + PER // 3 + 17:
+    print(f"rank {rank}: table c holds {int(rows_c.item())} rows over all shards", flush=True)
+    ok.zero_()
+eng.cfg.long_id_streams = False
+
 all_reduce(ok, dist.ReduceOp.MIN)
 eng.check()
 if rank == 0:

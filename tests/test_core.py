@@ -220,3 +220,45 @@ def test_streamed_sparse_writer_and_fast_reader_match_the_plain_ones(tmp_path):
     mixed = C.ckpt_load_sparse(str(c), "emb.table")
     assert mixed["ids"].numel() == n and float(mixed["states"][3][-1].abs().sum()) == 0.0
     assert head > 0 and first_row >= 0
+
+
+def test_snappy_codec_reads_and_writes_the_block_format():
+    """RPC bodies travel as Snappy streams (kraken/common/compress.h:18-91).  Streams assembled by hand
+    from the format description - every element kind - must decode; what the compressor writes must
+    decode to the input and must be made of the same elements; damaged streams are kSnappyUncompress."""
+    un, co = C.snappy_uncompress, C.snappy_compress
+    assert un(b"\x00") == b"" and co(b"") == b"\x00"
+    assert co(b"abc") == b"\x03\x08abc"                                  # varint 3, literal of 3
+    assert un(b"\x0c" + b"\x0cabcd" + b"\x11\x04") == b"abcd" * 3         # copy, 11-bit offset: length 8, offset 4
+    assert un(b"\x09" + b"\x0cabcd" + b"\x12\x04\x00") == b"abcdabcda"    # copy, 16-bit offset: length 5
+    assert un(b"\x09" + b"\x0cabcd" + b"\x13\x04\x00\x00\x00") == b"abcdabcda"   # copy, 32-bit offset
+    assert un(b"\x0a" + b"\x00x" + b"\x15\x01") == b"x" * 10              # offset 1 < length 9: a run
+    long_lit = bytes(range(256)) * 2                                      # 512 bytes: literal with 2 length bytes
+    assert un(b"\x80\x04" + b"\xf4\xff\x01" + long_lit) == long_lit
+    rng = np.random.default_rng(3)
+    cases = [b"a" * 100_000, rng.integers(0, 256, 200_001, dtype=np.uint8).tobytes(),
+             np.repeat(rng.normal(size=3000).astype(np.float32), 7).tobytes(),
+             (b"0123456789abcdef" * 5000) + b"tail", bytes(70_000), b"ab" * 33, b"xyzw" * 17]
+    for raw in cases:
+        packed = co(raw)
+        assert un(packed) == raw
+    assert len(co(bytes(1 << 20))) < (1 << 20) // 20
+    assert len(co(cases[1])) <= len(cases[1]) + len(cases[1]) // 6 + 32   # incompressible input stays within the bound
+    for bad in (b"", b"\x05\x08abc", b"\x03\x08ab", b"\x04\x00a\x09\x02", b"\x04\x00a\x12\x00\x00", b"\x03\x08abcd",
+                b"\xff\xff\xff\xff\xff\xff\x01"):
+        with pytest.raises(C.KrakenError):
+            un(bad)
+
+
+def test_snappy_codec_interoperates_with_the_snappy_library():
+    """Both directions against the Snappy build inside pyarrow (skipped where that is absent): the library
+    reads what the codec writes and the codec reads what the library writes."""
+    pa = pytest.importorskip("pyarrow")
+    if not pa.Codec.is_available("snappy"):
+        pytest.skip("pyarrow was built without snappy")
+    lib = pa.Codec("snappy")
+    rng = np.random.default_rng(11)
+    for raw in (b"a" * 100_000, np.repeat(rng.normal(size=30_000).astype(np.float32), 3).tobytes(),
+                rng.integers(0, 256, 70_001, dtype=np.uint8).tobytes(), b"0123456789abcdef" * 5000 + b"tail", b"", b"q"):
+        assert C.snappy_uncompress(lib.compress(raw, asbytes=True)) == raw
+        assert lib.decompress(C.snappy_compress(raw), decompressed_size=len(raw), asbytes=True) == raw

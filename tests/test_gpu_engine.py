@@ -28,6 +28,32 @@ def test_first_pull_larger_than_the_table_grows_it_first():
     assert eng.sparse[t].num_rows() == 20_000 and eng.sparse[t].capacity >= 20_000 / 0.6
 
 
+def test_long_id_stream_runs_as_several_rounds():
+    """With ``long_id_streams`` a call longer than the exchange buffers (1000 ids here) is served in rounds
+    through the same buffers, as the reference's emitter takes a request of any length
+    (kraken/worker/emitter.cc:123-183).  3500 ids with repeats: every occurrence gets its row, and a push
+    applies one SGD update per round an id occurs in."""
+    kk.initialize("gpu", table_capacity=1 << 14, max_ids_per_call=1000, long_id_streams=True, seed=3)
+    kk.init_model("m", kk.OptimType.kSGD, {})
+    kk.update_lr(1.0)
+    t = kk.register_sparse_table("e", 4, torch.float32, kk.InitializerType.kConstant, {"value": "2.0"})
+    ids = (torch.arange(3500, device=DEV) % 1200) * 31
+    rows = kk.pull_sparse_table(t, ids)
+    assert rows.shape == (3500, 4) and torch.equal(rows, torch.full_like(rows, 2.0))
+    kk.push_sparse_table(t, ids, torch.full((3500, 4), 0.125, device=DEV))
+    eng = kk.native.engine()
+    eng.check()
+    assert eng.sparse[t].num_rows() == 1200
+    # per round (1000 ids) the occurrences of an id are summed, then one update with lr 1: row = 2 - 0.125 * occurrences
+    occ = torch.bincount(ids // 31, minlength=1200).to(torch.float32)
+    want = (2.0 - 0.125 * occ)[ids // 31]
+    got = kk.pull_sparse_table(t, ids)
+    assert torch.allclose(got, want[:, None].expand(-1, 4))
+    with pytest.raises(kk.KrakenError, match="exceed the channel capacity"):
+        kk.native.engine().cfg.long_id_streams = False
+        kk.pull_sparse_table(t, ids)
+
+
 def test_recorded_error_reaches_the_caller_at_end_step():
     """A push to ids the table has never seen is kSparseIdNotExist on the owner
     (kraken/ps/sparse_table.cc:96-98).  Nothing synchronises in the step itself; the code must come

@@ -241,9 +241,9 @@ def test_compressed_bodies_round_trip(tmp_path):
     a, b = pysocket.socketpair()
     try:
         body = rpc.pack_body({"k": 1}, [torch.zeros(1 << 16)])
-        rpc.send_frame(a, 7, 3, body, rpc.COMPRESS_ZLIB)
+        rpc.send_frame(a, 7, 3, body, rpc.COMPRESS_SNAPPY)
         (n,) = rpc.struct.unpack("<I", b.recv(4, pysocket.MSG_PEEK))
-        assert n < len(body) // 20
+        assert n < len(body) // 15   # zeros: one 3-byte copy element per 64 bytes
         stamp, code, got, comp = rpc.recv_frame(b)
         assert (stamp, code, comp) == (7, 3, 1) and got == body
     finally:
