@@ -91,8 +91,10 @@ def main():
             step_ms += timer.stop_ms()
         us = step_ms / 10 * 1e3
         n_pad = int(eng.bucket.n_pad)
-        # per GPU and direction: (G - 1) / G of the bucket comes in as gradient slices and goes out as weights
-        link = (world - 1) / world * n_pad * 4
+        # per GPU and direction, (G - 1) / G of the bucket crosses the link TWICE: inbound are the peers' gradient
+        # slices this owner loads AND the other owners' weight slices stored into this rank's copy; outbound the
+        # mirror image (this rank's gradient read by the other owners, its own slice stored to every peer)
+        link = 2 * (world - 1) / world * n_pad * 4
         # HBM: G gradient slices read + zeroed bucket, owned slice of value and momentum read + written,
         # the whole updated bucket written once by the owners
         hbm = n_pad * 4 * (1 + 1 + 1) + (n_pad / world) * 4 * 4

@@ -1,6 +1,6 @@
 // Dense-parameter step fused with its collective, and the DCT kernels.
 //
-// dense_step is ONE kernel per rank that does what the reference does with a
+// dense_step is one short launch sequence per rank that does what the reference does with a
 // push RPC per table, a server-side optimizer and a pull RPC per step
 // (kraken/worker/emitter.cc:377-447, kraken/ps/dense_table.cc:31-43,
 // kraken/pytorch/optimizer.py:151-173):
@@ -10,13 +10,14 @@
 //   2. the update grid, for the slice this rank owns: sums the slice of every
 //      rank's gradient buffer directly out of peer memory (reduce-scatter by
 //      loads), runs the optimizer on value + slice-local state, stores the new
-//      values into every rank's parameter copy (all-gather by stores); its last
-//      block raises "slice done" on every peer;
-//   3. one warp waits for "slice done" of all owners, after which a grid zeroes
-//      the local gradient buffer for the next backward.
-// The waits are separate one-warp launches so that no block of a large grid
-// spins while holding registers another stream's kernels need; on a single GPU
-// the call is the update grid alone.
+//      values into every rank's parameter copy (all-gather by stores);
+//   3. one warp raises "slice done" on every peer, counts the step, and waits for
+//      "slice done" of all owners, after which a grid zeroes the local gradient
+//      buffer for the next backward.
+// The waits and signals are separate one-warp launches so that no block of a large
+// grid spins, or ends on a fence that waits for the switch, while holding registers
+// another stream's kernels need; on a single GPU the call is the update grid alone
+// (which then also clears the gradient it has just read).
 //
 // With DCT the gradients do not travel dense: dct_compact turns the local
 // f = g + e into per-owner (index, value) lists and the owner scatter-adds the
@@ -44,17 +45,29 @@ Sym to_sym(const SymHost& h) {
   return s;
 }
 
-// phase 0: announce this rank's gradient and wait for every rank's; phase 1: wait until every owner
-// has written its slice.  One warp, lane p polls peer p.
-__global__ void dense_rendezvous_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, int phase, uint32_t spin_limit) {
+// phase 0: announce this rank's gradient and wait for every rank's.
+// phase 1 (launched behind the update grid): tell every rank that this rank's slice is written, count the
+// step of the tables that took part, then wait until every owner has written its slice.  The update grid
+// itself signals nothing: its stores into peer memory are complete when it has ended, which stream order
+// puts before this kernel, so no block of it has to end on a fence that waits for the switch.
+// One warp, lane p talks to peer p.
+__global__ void dense_rendezvous_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, int phase, uint32_t spin_limit,
+                                        int* table_steps, const uint8_t* __restrict__ table_active, int n_tables) {
   const int p = threadIdx.x;
-  const uint32_t epoch = phase == 0 ? ctrl->epoch + 1 : ctrl->epoch;
+  const uint32_t epoch = ctrl->epoch + 1;
   bool ok = true;
+  if (phase == 1) __threadfence_system();
   if (p < sym.world) {
-    if (phase == 0) st_release_sys(sym.at<uint32_t>(p, lay.flag_grad) + sym.rank, epoch);
+    st_release_sys(sym.at<uint32_t>(p, phase == 0 ? lay.flag_grad : lay.flag_done) + sym.rank, epoch);
     ok = wait_flag(sym.at<uint32_t>(sym.rank, phase == 0 ? lay.flag_grad : lay.flag_done) + p, epoch, spin_limit);
   }
   const bool all_ok = __all_sync(0xffffffffu, ok);
+  if (phase == 1) {
+    const bool aborted = ctrl->abort != 0;
+    for (int t = p; t < n_tables && !aborted; t += 32)
+      if (table_active[t]) table_steps[t] += 1;
+    __syncwarp();
+  }
   if (p == 0) {
     if (!all_ok) {
       set_status(&ctrl->status, err::kTimeout);
@@ -62,6 +75,7 @@ __global__ void dense_rendezvous_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctr
     } else if (phase == 0) {
       ctrl->abort = 0;
     }
+    if (phase == 1) ctrl->epoch = epoch;
   }
 }
 
@@ -104,7 +118,7 @@ dense_step_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, fl
                   float* __restrict__ s1, float* __restrict__ s2, float* acc, const int* __restrict__ chunk_table,
                   int* table_steps, const uint8_t* __restrict__ table_active, int n_tables, OptimPOD optim,
                   const float* __restrict__ lr_ptr, float grad_scale, int use_coo) {
-  constexpr int kIlp = MULTI ? 2 : 4;
+  constexpr int kIlp = MULTI ? 2 : 4;  // with peers every group also has world - 1 loads from peer memory in flight
   constexpr bool kS0 = (SLABS & 1) != 0, kS1 = (SLABS & 2) != 0, kS2 = (SLABS & 4) != 0;
   if (OPT >= 0) optim.type = static_cast<uint8_t>(OPT);
   const uint32_t epoch = ctrl->epoch + 1;
@@ -184,14 +198,13 @@ dense_step_kernel(Sym sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, fl
     }
   }
 
+  if (MULTI) return;  // the one-warp launch behind this grid publishes the slice and counts the step
   if (last_block_done(&ctrl->done[0])) {
-    if (threadIdx.x < world) st_release_sys(sym.at<uint32_t>(threadIdx.x, lay.flag_done) + sym.rank, epoch);
-    for (int t = threadIdx.x; t < n_tables && !aborted; t += blockDim.x)
+    for (int t = threadIdx.x; t < n_tables; t += blockDim.x)
       if (table_active[t]) table_steps[t] += 1;
     if (threadIdx.x == 0) ctrl->epoch = epoch;
   }
-  // other ranks still read this rank's gradient: with peers it is zeroed by a later launch
-  if (!MULTI && use_coo && blockIdx.x == 0 && threadIdx.x == 0) sym.at<int>(sym.rank, lay.coo_cnt)[0] = 0;
+  if (use_coo && blockIdx.x == 0 && threadIdx.x == 0) sym.at<int>(sym.rank, lay.coo_cnt)[0] = 0;
 }
 
 template <int OPT, int SLABS>
@@ -317,13 +330,12 @@ void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, 
   const long long slice = n_pad / sym.world;
   const Sym s = to_sym(sym);
   const bool multi = sym.world > 1;
-  // single GPU: one pass per block (short-lived blocks keep loads and stores of different blocks interleaved).
-  // With peers a block ends on a fence that waits for its stores into peer memory to be acknowledged over
-  // the switch, so there the grid is resident and strides: a few hundred such waits instead of thousands.
+  // one pass per block: short-lived blocks keep the loads of some blocks and the stores of others in flight
+  // at the same time; the kernel strides where the grid would exceed 2^20 blocks
   const int per_block = kThreads * (multi ? 2 : 4);
-  const int grid = static_cast<int>(
-      std::min<long long>((slice / 4 + per_block - 1) / per_block, multi ? 148 * 3 : 1 << 20));
-  if (multi) dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 0, spin_limit);
+  const int grid = static_cast<int>(std::min<long long>((slice / 4 + per_block - 1) / per_block, 1 << 20));
+  if (multi)
+    dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 0, spin_limit, table_steps, table_active, n_tables);
   if (use_coo) dense_gather_coo_kernel<<<grid_for(slice / 4, 148 * 8), kThreads, 0, stream>>>(s, lay, ctrl, slice, acc);
   const int slabs = (s0 ? 1 : 0) | (s1 ? 2 : 0) | (s2 ? 4 : 0);
 #define KB_DENSE_STEP(OPT, SLABS)                                                                                    \
@@ -346,7 +358,7 @@ void dense_step(SymHost sym, DenseLayout lay, DenseCtrl* ctrl, long long n_pad, 
   }
 #undef KB_DENSE_STEP
   if (multi) {
-    dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 1, spin_limit);
+    dense_rendezvous_kernel<<<1, 32, 0, stream>>>(s, lay, ctrl, 1, spin_limit, table_steps, table_active, n_tables);
     dense_zero_kernel<<<grid_for(n_pad / 4, 148 * 8), kThreads, 0, stream>>>(s, lay, n_pad, use_coo);
   }
 }
