@@ -169,6 +169,11 @@ def main():
         assert kk.try_load_model_blocked(out_dir)
         sync_all()
         rec["load_s"] = time.perf_counter() - t0
+        eng2 = kk.native.engine()
+        rec["rows_after_load_per_shard"] = int(next(iter(eng2.sparse.values())).num_rows())
+        rec["checkpoint_gb_per_shard"] = round(os.path.getsize(max(
+            (os.path.join(dp, f) for dp, _, fs in os.walk(out_dir) for f in fs if f.endswith(".sparse")),
+            key=os.path.getsize)) / 1e9, 2)
     emit(rec)
     kk.stop()
 

@@ -622,6 +622,49 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       },
       py::arg("dir"), py::arg("name"), py::arg("threads") = 8);
 
+  // chunked load of a large table: rows [lo, lo + n) of the file order into caller-owned CPU tensors
+  // (pinned staging buffers that are reused for every chunk)
+  py::class_<ckpt::SparseChunkReader>(m, "SparseChunkReader")
+      .def(py::init<const std::string&, const std::string&, int>(), py::arg("dir"), py::arg("name"),
+           py::arg("threads") = 8)
+      .def_property_readonly("exists", &ckpt::SparseChunkReader::exists)
+      .def_property_readonly("fast", &ckpt::SparseChunkReader::fast)
+      .def_property_readonly("rows", &ckpt::SparseChunkReader::rows)
+      .def_property_readonly("dim", [](const ckpt::SparseChunkReader& r) { return r.header().dim; })
+      .def_property_readonly("id", [](const ckpt::SparseChunkReader& r) { return r.header().id; })
+      .def_property_readonly("name", [](const ckpt::SparseChunkReader& r) { return r.header().name; })
+      .def_property_readonly("init_type", [](const ckpt::SparseChunkReader& r) { return r.header().init_type; })
+      .def_property_readonly("init_conf", [](const ckpt::SparseChunkReader& r) { return r.header().init_conf; })
+      .def_property_readonly("state_types", &ckpt::SparseChunkReader::state_types)
+      .def_property_readonly("int_state_types", &ckpt::SparseChunkReader::int_state_types)
+      .def("read_into",
+           [](ckpt::SparseChunkReader& r, uint64_t lo, uint64_t n, torch::Tensor ids, torch::Tensor vals,
+              std::vector<torch::Tensor> states, std::vector<torch::Tensor> states_i) {
+             need_cpu(ids, "ids", torch::kInt64);
+             need_cpu(vals, "vals", torch::kFloat32);
+             const int64_t d = r.header().dim;
+             TORCH_CHECK(static_cast<uint64_t>(ids.numel()) >= n && static_cast<uint64_t>(vals.numel()) >= n * d,
+                         "read_into: the destination holds fewer than n rows");
+             TORCH_CHECK(states.size() == r.state_types().size() && states_i.size() == r.int_state_types().size(),
+                         "read_into: one tensor per state column of the file is needed");
+             std::vector<float*> sp;
+             std::vector<int64_t*> ip;
+             for (auto& t : states) {
+               need_cpu(t, "state", torch::kFloat32);
+               TORCH_CHECK(static_cast<uint64_t>(t.numel()) >= n * d, "read_into: a state column is too small");
+               sp.push_back(t.data_ptr<float>());
+             }
+             for (auto& t : states_i) {
+               need_cpu(t, "int state", torch::kInt64);
+               TORCH_CHECK(static_cast<uint64_t>(t.numel()) >= n, "read_into: an integer state column is too small");
+               ip.push_back(t.data_ptr<int64_t>());
+             }
+             py::gil_scoped_release nogil;
+             return r.Read(lo, n, reinterpret_cast<uint64_t*>(ids.data_ptr<int64_t>()), vals.data_ptr<float>(), sp.data(),
+                           ip.data());
+           },
+           "False: a row deviates from the fixed layout (load the file with ckpt_load_sparse instead)");
+
   // ---------------- CPU shard
   py::class_<CpuShard>(m, "CpuShard")
       .def(py::init<uint64_t>(), py::arg("seed") = 0)

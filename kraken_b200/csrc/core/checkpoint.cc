@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cerrno>
 #include <cstdio>
 #include <ctime>
 #include <filesystem>
@@ -662,6 +663,172 @@ bool LoadSparseFast(const std::string& dir, const std::string& name, SparseHeade
   }
   *fast = true;
   return true;
+}
+
+// ------------------------------------------------------------------ chunked reader
+namespace {
+
+bool PreadAll(int fd, char* buf, size_t n, uint64_t off) {
+  while (n > 0) {
+    const ssize_t got = ::pread(fd, buf, n, static_cast<off_t>(off));
+    if (got < 0 && errno == EINTR) continue;
+    if (got <= 0) return false;
+    buf += got;
+    off += static_cast<uint64_t>(got);
+    n -= static_cast<size_t>(got);
+  }
+  return true;
+}
+
+}  // namespace
+
+SparseChunkReader::SparseChunkReader(const std::string& dir, const std::string& name, int threads)
+    : threads_(threads < 1 ? 1 : threads) {
+  fs::path p = fs::path(dir) / (name + kSparseSuffix);
+  if (!fs::exists(p)) return;
+  exists_ = true;
+  fd_ = ::open(p.string().c_str(), O_RDONLY);
+  KB_CHECK(fd_ >= 0, err::kCheckpointIO, "cannot open " + p.string());
+  const uint64_t size = static_cast<uint64_t>(fs::file_size(p));
+
+  // header: a few hundred bytes at most (name + initializer conf); 1 MiB is read to be safe
+  std::vector<char> head(static_cast<size_t>(std::min<uint64_t>(size, 1u << 20)));
+  KB_CHECK(PreadAll(fd_, head.data(), head.size(), 0), err::kCheckpointIO, "cannot read " + p.string());
+  MemSource src(head.data(), head.size());
+  Reader r(&src);
+  KB_CHECK(r.Pod<uint8_t>() == static_cast<uint8_t>(TableType::kSparse), err::kTableTypeUnCompatible,
+           p.string() + " is not a sparse table file");
+  h_.id = r.Pod<uint64_t>();
+  h_.name = r.Str();
+  h_.dim = r.Pod<int64_t>();
+  h_.dtype = static_cast<DType>(r.Pod<uint8_t>());
+  h_.init_type = static_cast<InitializerType>(r.Pod<uint8_t>());
+  h_.init_conf = r.ConfMap();
+  if (h_.dtype != DType::kFloat32 || h_.dim <= 0 || h_.dim >= (1 << 20)) return;
+  if (r.Pod<uint64_t>() != kSlotCount) return;
+  uint64_t pos = src.offset();
+
+  row_start_.assign(1, 0);
+  for (uint64_t s = 0; s < kSlotCount; ++s) {
+    uint64_t n = 0;
+    if (pos + 8 > size || !PreadAll(fd_, reinterpret_cast<char*>(&n), 8, pos)) return;
+    pos += 8;
+    if (n > 0 && row_bytes_ == 0) {
+      // the first row of the file fixes the layout: which state entries, in which order
+      // no row carries more than 8 float and 8 integer state entries (the StateType codes are 0..7)
+      std::vector<char> one(static_cast<size_t>(std::min<uint64_t>(size - pos, RowBytes(h_.dim, 8, 8))));
+      if (!PreadAll(fd_, one.data(), one.size(), pos)) return;
+      MemSource first(one.data(), one.size());
+      Reader rr(&first);
+      try {
+        rr.Pod<uint64_t>();
+        Value v = rr.Val();
+        const size_t d = static_cast<size_t>(h_.dim);
+        if (static_cast<size_t>(v.val.Numel()) != d || v.val.dtype != DType::kFloat32) return;
+        for (auto& kv : v.states) {
+          if (static_cast<size_t>(kv.second.Numel()) != d || kv.second.dtype != DType::kFloat32) return;
+          st_.push_back(kv.first);
+        }
+        for (auto& kv : v.states_i) sti_.push_back(kv.first);
+      } catch (const KrakenError&) {
+        return;
+      }
+      row_bytes_ = RowBytes(h_.dim, st_.size(), sti_.size());
+      if (first.offset() != row_bytes_) return;  // entries not in ascending type order, or another encoding
+    }
+    if (n > 0 && n > (size - pos) / row_bytes_) return;
+    segs_.emplace_back(pos, n);
+    pos += n * row_bytes_;
+    total_ += n;
+    row_start_.push_back(total_);
+  }
+  if (pos != size) return;
+
+  tmpl_.assign(row_bytes_, 0);
+  if (row_bytes_) {
+    const size_t d = static_cast<size_t>(h_.dim);
+    char* q = tmpl_.data() + 8;
+    q = PutTensorHead(q, h_.dim) + d * 4;
+    const uint64_t ns = st_.size();
+    std::memcpy(q, &ns, 8);
+    q += 8;
+    for (uint32_t k : st_) {
+      std::memcpy(q, &k, 4);
+      q = PutTensorHead(q + 4, h_.dim) + d * 4;
+    }
+    const uint64_t ni = sti_.size();
+    std::memcpy(q, &ni, 8);
+    q += 8;
+    for (uint32_t k : sti_) {
+      std::memcpy(q, &k, 4);
+      q += 12;
+    }
+  }
+  bufs_.resize(static_cast<size_t>(threads_));
+  fast_ = true;
+}
+
+SparseChunkReader::~SparseChunkReader() {
+  if (fd_ >= 0) ::close(fd_);
+}
+
+bool SparseChunkReader::Read(uint64_t lo, uint64_t n, uint64_t* ids, float* vals, float* const* states,
+                             int64_t* const* states_i) {
+  KB_CHECK(fast_, err::kBadArgument, "the file does not have the fixed layout");
+  KB_CHECK(lo + n <= total_, err::kBadArgument, "row range beyond the end of the file");
+  if (n == 0) return true;
+  const size_t d = static_cast<size_t>(h_.dim);
+  const size_t R = row_bytes_;
+  constexpr uint64_t kBatch = 8192;  // rows per pread
+  std::atomic<bool> ok{true};
+  auto work = [&](int tid, uint64_t a, uint64_t b) {  // global rows [a, b), written at index (row - lo)
+    std::vector<char>& buf = bufs_[static_cast<size_t>(tid)];
+    if (buf.size() < kBatch * R) buf.resize(kBatch * R);
+    size_t seg = 0;
+    const char* t = tmpl_.data();
+    while (a < b && ok) {
+      while (a >= row_start_[seg + 1]) ++seg;
+      const uint64_t take = std::min<uint64_t>({kBatch, b - a, row_start_[seg + 1] - a});
+      if (!PreadAll(fd_, buf.data(), take * R, segs_[seg].first + (a - row_start_[seg]) * R)) {
+        ok = false;
+        return;
+      }
+      for (uint64_t k = 0; k < take; ++k) {
+        const char* q = buf.data() + k * R;
+        const size_t out = static_cast<size_t>(a + k - lo);
+        std::memcpy(&ids[out], q, 8);
+        size_t o = 8;
+        if (std::memcmp(q + o, t + o, kTensorHead) != 0) { ok = false; return; }
+        o += kTensorHead;
+        std::memcpy(vals + out * d, q + o, d * 4);
+        o += d * 4;
+        if (std::memcmp(q + o, t + o, 8) != 0) { ok = false; return; }
+        o += 8;
+        for (size_t c = 0; c < st_.size(); ++c) {
+          if (std::memcmp(q + o, t + o, 4 + kTensorHead) != 0) { ok = false; return; }
+          o += 4 + kTensorHead;
+          std::memcpy(states[c] + out * d, q + o, d * 4);
+          o += d * 4;
+        }
+        if (std::memcmp(q + o, t + o, 8) != 0) { ok = false; return; }
+        o += 8;
+        for (size_t c = 0; c < sti_.size(); ++c) {
+          if (std::memcmp(q + o, t + o, 4) != 0) { ok = false; return; }
+          std::memcpy(&states_i[c][out], q + o + 4, 8);
+          o += 12;
+        }
+      }
+      a += take;
+    }
+  };
+  const int T = static_cast<int>(std::max<uint64_t>(1, std::min<uint64_t>(threads_, (n + kBatch - 1) / kBatch)));
+  const uint64_t per = (n + T - 1) / T;
+  std::vector<std::thread> pool;
+  for (int t = 1; t < T; ++t)
+    pool.emplace_back(work, t, lo + std::min<uint64_t>(n, t * per), lo + std::min<uint64_t>(n, (t + 1) * per));
+  work(0, lo, lo + std::min<uint64_t>(n, per));
+  for (auto& th : pool) th.join();
+  return ok;
 }
 
 }  // namespace ckpt

@@ -122,5 +122,39 @@ class SparseStreamWriter {
 bool LoadSparseFast(const std::string& dir, const std::string& name, SparseHeader* h, SparseColumns* cols, bool* fast,
                     int threads = 8);
 
+// Chunked reader of a fixed-layout sparse file, for tables larger than the host wants to hold twice: the file
+// is opened once (header, the 8 slot counts and the first row's layout are read with pread), then Read()
+// extracts any row range [lo, lo + n) of the file order straight into caller-owned column arrays - pinned
+// staging buffers that are reused for every chunk, so that neither the file (no mapping) nor the destination
+// pays a page fault per 4 KiB in steady state.  Each thread preads its rows in batches into a buffer it keeps.
+class SparseChunkReader {
+ public:
+  SparseChunkReader(const std::string& dir, const std::string& name, int threads = 8);
+  ~SparseChunkReader();
+  SparseChunkReader(const SparseChunkReader&) = delete;
+  SparseChunkReader& operator=(const SparseChunkReader&) = delete;
+  bool exists() const { return exists_; }
+  bool fast() const { return fast_; }  // false: not the fixed layout (or not float32): use LoadSparse
+  const SparseHeader& header() const { return h_; }
+  uint64_t rows() const { return total_; }
+  const std::vector<uint32_t>& state_types() const { return st_; }
+  const std::vector<uint32_t>& int_state_types() const { return sti_; }
+  // False when a row deviates from the first row's layout (nothing can be trusted then: use LoadSparse).
+  bool Read(uint64_t lo, uint64_t n, uint64_t* ids, float* vals, float* const* states, int64_t* const* states_i);
+
+ private:
+  int fd_ = -1;
+  bool exists_ = false, fast_ = false;
+  SparseHeader h_;
+  uint64_t total_ = 0;
+  size_t row_bytes_ = 0;
+  int threads_;
+  std::vector<uint32_t> st_, sti_;
+  std::vector<std::pair<uint64_t, uint64_t>> segs_;  // (file offset of the first row, rows) per slot
+  std::vector<uint64_t> row_start_;                  // first global row of each slot, plus the total
+  std::vector<char> tmpl_;                           // a row with every fixed byte in place
+  std::vector<std::vector<char>> bufs_;              // one batch buffer per thread
+};
+
 }  // namespace ckpt
 }  // namespace kb

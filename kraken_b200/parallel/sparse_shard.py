@@ -138,9 +138,9 @@ class GpuSparseTable:
         dev = self.device
         copy_stream = torch.cuda.Stream(device=dev)
         n_cols = 1 + len(cols)
-        pinned = [{"ids": torch.empty(chunk_rows, dtype=torch.int64).pin_memory(),
-                   "f": [torch.empty((chunk_rows, self.dim), dtype=torch.float32).pin_memory() for _ in range(n_cols)],
-                   "steps": torch.empty(chunk_rows, dtype=torch.int64).pin_memory(), "event": None} for _ in range(2)]
+        pinned = [{"ids": torch.empty(chunk_rows, dtype=torch.int64, pin_memory=True),
+                   "f": [torch.empty((chunk_rows, self.dim), dtype=torch.float32, pin_memory=True) for _ in range(n_cols)],
+                   "steps": torch.empty(chunk_rows, dtype=torch.int64, pin_memory=True), "event": None} for _ in range(2)]
         total = 0
         flip = torch.tensor(-(1 << 63), dtype=torch.int64, device=dev)
         for slot in range(8):

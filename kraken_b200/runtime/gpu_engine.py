@@ -768,25 +768,38 @@ class GpuEngine(Engine):
 
     def import_sparse_routed(self, table_id: int, name: str, dirs: Sequence[str], chunk_rows: int = 1 << 21) -> int:
         """Checkpoint load for GPU shards.  This rank reads ALL rows of the shard files in ``dirs`` (its 1 / world
-        share of the checkpoint; fixed-layout files with the multi-threaded reader, anything else - a file the
-        reference wrote - with the general one), uploads them in chunks and sends every row to the rank that owns
-        it under the current placement (device-side owner computation, one all-to-all per chunk over NCCL);
-        owners insert what they receive.  Collective: ranks with fewer chunks take part with empty ones.
+        share of the checkpoint) and sends every row to the rank that owns it under the current placement
+        (device-side owner computation, one all-to-all per chunk over NCCL); owners insert what they receive.
+        Fixed-layout files are read chunk by chunk with ``SparseChunkReader`` into two sets of pinned staging
+        buffers: a reader thread fills one set (preads + column extraction on 8 threads) while the other set is
+        uploaded, routed and inserted, so the host never holds more than two chunks and pays the page faults of
+        its buffers once.  Anything else - a file the reference wrote with per-row state sets - goes through the
+        general reader as a whole.  Collective: ranks with fewer chunks take part with empty ones.
         Replaces "every rank parses every file and drops (world - 1) / world of it"."""
+        import threading
         t = self.sparse[table_id]
         salt = self._salt(table_id)
         dev = self.device
-        parts = []
+        # sources: ("file", reader, a, b) rows [a, b) of a fixed-layout file; ("mem", columns, a, b) parsed columns
+        sources = []
+        skeys, ikeys = set(), set()
         for d in dirs:
-            cols = C.ckpt_load_sparse_fast(d, name)
-            if cols is False:
-                cols = C.ckpt_load_sparse(d, name)
+            rd = C.SparseChunkReader(d, name)
+            if not rd.exists:
+                continue
+            if rd.fast and rd.dim == t.dim:
+                skeys.update(int(k) for k in rd.state_types)
+                ikeys.update(int(k) for k in rd.int_state_types)
+                sources += [("file", rd, a, min(a + chunk_rows, int(rd.rows))) for a in range(0, int(rd.rows), chunk_rows)]
+                continue
+            cols = C.ckpt_load_sparse(d, name)
             if cols is not None and cols["ids"].numel() > 0:
-                parts.append(cols)
-        skeys = sorted({int(k) for c in parts for k in c["states"]})
-        ikeys = sorted({int(k) for c in parts for k in c["states_i"]})
-        chunks = [(c, a) for c in parts for a in range(0, int(c["ids"].numel()), chunk_rows)]
-        rounds = len(chunks)
+                skeys.update(int(k) for k in cols["states"])
+                ikeys.update(int(k) for k in cols["states_i"])
+                n = int(cols["ids"].numel())
+                sources += [("mem", cols, a, min(a + chunk_rows, n)) for a in range(0, n, chunk_rows)]
+        skeys, ikeys = sorted(skeys), sorted(ikeys)
+        rounds = len(sources)
         if self.world > 1:
             # every rank must know the same column set and the same number of rounds
             meta = torch.zeros(2 + 16, dtype=torch.int64, device=dev)
@@ -800,18 +813,65 @@ class GpuEngine(Engine):
             flags = meta[2:].tolist()
             skeys = [k for k in range(8) if flags[k]]
             ikeys = [k for k in range(8) if flags[8 + k]]
+
+        file_rows = max([b - a for kind, _, a, b in sources if kind == "file"], default=0)
+        stage = []
+        if file_rows:
+            stage = [{"ids": torch.empty(file_rows, dtype=torch.int64, pin_memory=True),
+                      "vals": torch.empty((file_rows, t.dim), dtype=torch.float32, pin_memory=True),
+                      "f": {k: torch.empty((file_rows, t.dim), dtype=torch.float32, pin_memory=True) for k in skeys},
+                      "i": {k: torch.empty(file_rows, dtype=torch.int64, pin_memory=True) for k in ikeys},
+                      "free": None} for _ in range(2)]
+        fill_result = {}
+
+        def fill(r: int) -> None:
+            """Reader thread: source r -> staging set r % 2 (file sources only)."""
+            kind, src, a, b = sources[r]
+            buf = stage[r % 2]
+            if buf["free"] is not None:
+                buf["free"].synchronize()      # the uploads of round r - 2 have left this set
+            ok = src.read_into(a, b - a, buf["ids"], buf["vals"], [buf["f"][int(k)] for k in src.state_types],
+                               [buf["i"][int(k)] for k in src.int_state_types])
+            fill_result[r] = bool(ok)
+
+        def start_fill(r: int):
+            if r < len(sources) and sources[r][0] == "file":
+                th = threading.Thread(target=fill, args=(r,), daemon=True)
+                th.start()
+                return th
+            return None
+
         read = 0
+        pending = start_fill(0)
         for r in range(rounds):
-            if r < len(chunks):
-                c, a = chunks[r]
-                b = min(a + chunk_rows, int(c["ids"].numel()))
-                ids = c["ids"][a:b].to(dev, non_blocking=True)
-                vals = c["vals"][a:b].to(dev, non_blocking=True)
-                states = {k: (c["states"][k][a:b].to(dev, non_blocking=True) if k in c["states"]
-                              else torch.zeros((b - a, t.dim), device=dev)) for k in skeys}
-                states_i = {k: (c["states_i"][k][a:b].to(dev, non_blocking=True) if k in c["states_i"]
-                                else torch.zeros(b - a, dtype=torch.int64, device=dev)) for k in ikeys}
-                read += b - a
+            if r < len(sources):
+                kind, src, a, b = sources[r]
+                m = b - a
+                if kind == "file":
+                    pending.join()
+                    if not fill_result.pop(r):
+                        raise C.KrakenError(f"{name}: a row of the checkpoint file deviates from the file's layout")
+                    buf = stage[r % 2]
+                    pending = start_fill(r + 1)      # the next chunk is read while this one is uploaded and inserted
+                    have_f, have_i = {int(k) for k in src.state_types}, {int(k) for k in src.int_state_types}
+                    ids = buf["ids"][:m].to(dev, non_blocking=True)
+                    vals = buf["vals"][:m].to(dev, non_blocking=True)
+                    states = {k: (buf["f"][k][:m].to(dev, non_blocking=True) if k in have_f
+                                  else torch.zeros((m, t.dim), device=dev)) for k in skeys}
+                    states_i = {k: (buf["i"][k][:m].to(dev, non_blocking=True) if k in have_i
+                                    else torch.zeros(m, dtype=torch.int64, device=dev)) for k in ikeys}
+                    buf["free"] = torch.cuda.Event()
+                    buf["free"].record()
+                else:
+                    if pending is None:
+                        pending = start_fill(r + 1)
+                    ids = src["ids"][a:b].to(dev, non_blocking=True)
+                    vals = src["vals"][a:b].to(dev, non_blocking=True)
+                    states = {k: (src["states"][k][a:b].to(dev, non_blocking=True) if k in src["states"]
+                                  else torch.zeros((m, t.dim), device=dev)) for k in skeys}
+                    states_i = {k: (src["states_i"][k][a:b].to(dev, non_blocking=True) if k in src["states_i"]
+                                    else torch.zeros(m, dtype=torch.int64, device=dev)) for k in ikeys}
+                read += m
             else:
                 ids = torch.empty(0, dtype=torch.int64, device=dev)
                 vals = torch.empty((0, t.dim), device=dev)
@@ -836,6 +896,9 @@ class GpuEngine(Engine):
                 states_i = {k: a2a(v, 0) for k, v in states_i.items()}
             if ids.numel():
                 t.import_rows(ids, vals, states, states_i)
+        if pending is not None:
+            pending.join()
+        torch.cuda.synchronize(dev)   # the staging buffers are freed below: their last uploads must have finished
         return read
 
     def stop(self) -> None:

@@ -105,6 +105,22 @@ if rank == 0:
 got = kk.pull_sparse_table(ts, probe.to(dev)).cpu()  # the zero-gradient Adam step above still moved rows
 w_saved = w.cpu()  # parameter views die with the engine's arenas
 assert kk.try_save_model()
+kk.stop(keep_process_group=True)
+
+# the same ranks load what they have just written into new engines: every rank reads its share of the shard
+# files and routes the rows to their owners
+kk.initialize("gpu", seed=17, table_capacity=1 << 10, exchange=EXCHANGE)
+assert kk.try_load_model_blocked(out_dir)
+eng2 = kk.native.engine()
+ts2 = next(tid for tid, info in eng2.tables.items() if info.name == "e")
+again = kk.pull_sparse_table(ts2, probe.to(dev)).cpu()
+assert torch.allclose(again, got, atol=1e-6), "rows differ after the multi-rank load"
+rows_now = torch.tensor([eng2.sparse[ts2].num_rows()], device=dev)
+dist.all_reduce(rows_now)
+assert int(rows_now.item()) == 200, f"{int(rows_now.item())} rows over all shards after the load"
+eng2.check()
+if rank == 0:
+    print("MULTI_GPU_CHECKPOINT_LOAD ok")
 kk.stop()
 
 if rank == 0:

@@ -206,6 +206,22 @@ def test_streamed_sparse_writer_and_fast_reader_match_the_plain_ones(tmp_path):
     assert torch.equal(fast["states"][3], plain["states"][3]) and torch.equal(fast["states"][4], plain["states"][4])
     assert torch.equal(fast["states_i"][0], plain["states_i"][0])
     assert C.ckpt_load_sparse_fast(str(tmp_path), "missing") is None
+    # the chunked reader: any row range of the file order, into caller-owned buffers that are reused
+    rd = C.SparseChunkReader(str(b), "emb.table", 3)
+    assert rd.exists and rd.fast and rd.rows == n and rd.dim == dim and rd.id == 7 and rd.name == "emb.table"
+    assert list(rd.state_types) == [3, 4] and list(rd.int_state_types) == [0] and rd.init_conf == {"mean": "0", "stddev": "1"}
+    cap = 4099
+    bi, bv = torch.empty(cap, dtype=torch.int64), torch.empty(cap, dim)
+    bs, bt = [torch.empty(cap, dim), torch.empty(cap, dim)], [torch.empty(cap, dtype=torch.int64)]
+    for lo in list(range(0, n, cap)) + [n - 1, 5]:
+        m = min(cap, n - lo)
+        assert rd.read_into(lo, m, bi, bv, bs, bt) is True
+        assert torch.equal(bi[:m], plain["ids"][lo:lo + m]) and torch.equal(bv[:m], plain["vals"][lo:lo + m])
+        assert torch.equal(bs[0][:m], plain["states"][3][lo:lo + m]) and torch.equal(bs[1][:m], plain["states"][4][lo:lo + m])
+        assert torch.equal(bt[0][:m], plain["states_i"][0][lo:lo + m])
+    with pytest.raises(Exception):
+        rd.read_into(n - 3, 10, bi, bv, bs, bt)          # beyond the end of the file
+    assert not C.SparseChunkReader(str(tmp_path), "missing").exists
     # a row without state entries in the middle of the file: not the fixed layout
     raw = bytearray((a / "emb.table.sparse").read_bytes())
     row = w.row_bytes()
@@ -217,6 +233,8 @@ def test_streamed_sparse_writer_and_fast_reader_match_the_plain_ones(tmp_path):
     c.mkdir()
     (c / "emb.table.sparse").write_bytes(bytes(cut))
     assert C.ckpt_load_sparse_fast(str(c), "emb.table") is False
+    mixed_rd = C.SparseChunkReader(str(c), "emb.table")
+    assert mixed_rd.exists and not mixed_rd.fast        # the file length does not fit rows of one size
     mixed = C.ckpt_load_sparse(str(c), "emb.table")
     assert mixed["ids"].numel() == n and float(mixed["states"][3][-1].abs().sum()) == 0.0
     assert head > 0 and first_row >= 0

@@ -242,3 +242,44 @@ def test_jagged_embeddings_train_on_the_gpu_engine():
     for g, c in zip(r_gpu, r_cpu):
         assert torch.allclose(g, c, atol=1e-6), (g, c)
     assert not torch.allclose(r_gpu[0], torch.full_like(r_gpu[0], 0.5))   # the rows did move
+
+
+def test_streamed_save_and_chunked_load_round_trip_on_the_gpu_engine(tmp_path):
+    """A table of 2.6 M rows with Adagrad state is written by the streamed writer and read back into a NEW
+    GPU engine through the chunked reader (two chunks of 2^21 rows and a remainder, so the reader thread,
+    both staging sets and their reuse are exercised): ids, values and accumulators must come back bit for bit,
+    and a further update must continue from the restored accumulator."""
+    n, dim = 2_600_000, 4
+    kk.initialize("gpu", table_capacity=1 << 23, max_ids_per_call=n, saved_dir=str(tmp_path), seed=11)
+    kk.init_model("m", kk.OptimType.kAdagrad, {"initial_accumulator_value": "0.1"})
+    kk.update_lr(0.5)
+    t = kk.register_sparse_table("e", dim, torch.float32, kk.InitializerType.kNormal, {"stddev": "0.1"})
+    ids = torch.arange(n, device=DEV) * 2654435761 - (1 << 40)          # negative ids too
+    kk.pull_sparse_table(t, ids)
+    g = torch.randn(n, dim, device=DEV)
+    kk.push_sparse_table(t, ids, g)
+    eng = kk.native.engine()
+    before = eng.sparse[t].export()
+    order = torch.argsort(before["ids"])
+    assert kk.try_save_model()
+    kk.stop()
+
+    kk.initialize("gpu", table_capacity=1 << 16, seed=99)               # grows while it loads
+    assert kk.try_load_model_blocked(str(tmp_path))
+    eng = kk.native.engine()
+    eng.check()
+    t2 = next(iter(eng.sparse))
+    after = eng.sparse[t2].export()
+    order2 = torch.argsort(after["ids"])
+    assert after["ids"].numel() == n and torch.equal(after["ids"][order2], before["ids"][order])
+    assert torch.equal(after["vals"][order2], before["vals"][order])
+    for k in before["states"]:
+        assert torch.equal(after["states"][k][order2], before["states"][k][order])
+    # the restored accumulator takes part in the next update: acc' = acc + g^2, w' = w - lr g / (sqrt(acc') + eps)
+    kk.update_lr(0.5)          # the learning rate is the worker's, not part of a checkpoint
+    some = ids[:1000]
+    w0 = kk.pull_sparse_table(t2, some)
+    kk.push_sparse_table(t2, some, torch.ones(1000, dim, device=DEV))
+    w1 = kk.pull_sparse_table(t2, some)
+    acc = 0.1 + g[:1000] ** 2 + 1.0
+    assert torch.allclose(w0 - w1, 0.5 / (acc.sqrt() + 1e-10), rtol=1e-4, atol=1e-6)

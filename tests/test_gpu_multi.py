@@ -25,7 +25,8 @@ def test_gpu_ranks_match_one_shard(world, tmp_path):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = run_ranks("mp_gpu_worker.py", world, str(tmp_path))
-    for tag in ("MULTI_GPU_MATCHES_SINGLE ok", "MULTI_GPU_BAGS ok", "MULTI_GPU_CHECKPOINT_RESHARD ok"):
+    for tag in ("MULTI_GPU_MATCHES_SINGLE ok", "MULTI_GPU_BAGS ok", "MULTI_GPU_CHECKPOINT_LOAD ok",
+                "MULTI_GPU_CHECKPOINT_RESHARD ok"):
         assert tag in out, out[-2000:]
 
 
