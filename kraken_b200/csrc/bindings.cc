@@ -603,21 +603,43 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def(
       "ckpt_load_sparse_fast",
       [](const std::string& dir, const std::string& name, int threads) -> py::object {
-        // None: no such file; False: the file is not in the fixed layout (use ckpt_load_sparse); else all rows
-        ckpt::SparseHeader h;
-        ckpt::SparseColumns c;
-        bool ok, fast = false;
+        // None: no such file; False: the file is not in the fixed layout (use ckpt_load_sparse); else all rows,
+        // extracted by `threads` threads straight into the tensors that are returned
+        ckpt::SparseChunkReader r(dir, name, threads);
+        if (!r.exists()) return py::none();
+        if (!r.fast()) return py::bool_(false);
+        const int64_t n = static_cast<int64_t>(r.rows()), dim = r.header().dim;
+        torch::Tensor ids = torch::empty({n}, torch::kInt64), vals = torch::empty({n, dim}, torch::kFloat32);
+        std::vector<torch::Tensor> st, sti;
+        std::vector<float*> sp;
+        std::vector<int64_t*> ip;
+        for (size_t k = 0; k < r.state_types().size(); ++k) {
+          st.push_back(torch::empty({n, dim}, torch::kFloat32));
+          sp.push_back(st.back().data_ptr<float>());
+        }
+        for (size_t k = 0; k < r.int_state_types().size(); ++k) {
+          sti.push_back(torch::empty({n}, torch::kInt64));
+          ip.push_back(sti.back().data_ptr<int64_t>());
+        }
+        bool ok;
         {
           py::gil_scoped_release nogil;
-          ok = ckpt::LoadSparseFast(dir, name, &h, &c, &fast, threads);
+          ok = r.Read(0, r.rows(), reinterpret_cast<uint64_t*>(ids.data_ptr<int64_t>()), vals.data_ptr<float>(), sp.data(),
+                      ip.data());
         }
-        if (!ok) return py::none();
-        if (!fast) return py::bool_(false);
-        py::dict d = columns_to_py(c);
-        d["id"] = h.id;
-        d["name"] = h.name;
-        d["init_type"] = h.init_type;
-        d["init_conf"] = h.init_conf;
+        if (!ok) return py::bool_(false);
+        py::dict d, ds, di;
+        for (size_t k = 0; k < st.size(); ++k) ds[py::int_(r.state_types()[k])] = st[k];
+        for (size_t k = 0; k < sti.size(); ++k) di[py::int_(r.int_state_types()[k])] = sti[k];
+        d["dim"] = dim;
+        d["ids"] = ids;
+        d["vals"] = vals;
+        d["states"] = ds;
+        d["states_i"] = di;
+        d["id"] = r.header().id;
+        d["name"] = r.header().name;
+        d["init_type"] = r.header().init_type;
+        d["init_conf"] = r.header().init_conf;
         return d;
       },
       py::arg("dir"), py::arg("name"), py::arg("threads") = 8);

@@ -1,7 +1,6 @@
 #include "checkpoint.h"
 
 #include <fcntl.h>
-#include <sys/mman.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -511,158 +510,6 @@ void SparseStreamWriter::Close() {
     KB_CHECK(::close(fd_) == 0, err::kCheckpointIO, "closing the checkpoint file failed");
     fd_ = -1;
   }
-}
-
-bool LoadSparseFast(const std::string& dir, const std::string& name, SparseHeader* h, SparseColumns* c, bool* fast,
-                    int threads) {
-  *fast = false;
-  fs::path p = fs::path(dir) / (name + kSparseSuffix);
-  if (!fs::exists(p)) return false;
-  const int fd = ::open(p.string().c_str(), O_RDONLY);
-  KB_CHECK(fd >= 0, err::kCheckpointIO, "cannot open " + p.string());
-  const size_t size = static_cast<size_t>(fs::file_size(p));
-  void* map = size ? ::mmap(nullptr, size, PROT_READ, MAP_PRIVATE, fd, 0) : nullptr;
-  ::close(fd);
-  KB_CHECK(size == 0 || map != MAP_FAILED, err::kCheckpointIO, "cannot map " + p.string());
-  struct Unmap {
-    void* m;
-    size_t n;
-    ~Unmap() { if (m) ::munmap(m, n); }
-  } guard{map, size};
-  const char* base = static_cast<const char*>(map);
-
-  MemSource src(base, size);
-  Reader r(&src);
-  KB_CHECK(r.Pod<uint8_t>() == static_cast<uint8_t>(TableType::kSparse), err::kTableTypeUnCompatible,
-           p.string() + " is not a sparse table file");
-  h->id = r.Pod<uint64_t>();
-  h->name = r.Str();
-  h->dim = r.Pod<int64_t>();
-  h->dtype = static_cast<DType>(r.Pod<uint8_t>());
-  h->init_type = static_cast<InitializerType>(r.Pod<uint8_t>());
-  h->init_conf = r.ConfMap();
-  if (h->dtype != DType::kFloat32 || h->dim <= 0 || h->dim >= (1 << 20)) return true;
-  if (c->dim == 0) c->dim = h->dim;
-  if (c->dim != h->dim) return true;
-  const uint64_t slots = r.Pod<uint64_t>();
-  if (slots != kSlotCount) return true;
-  size_t pos = src.offset();
-  const size_t d = static_cast<size_t>(h->dim);
-
-  // layout of the first row (if any): which state entries, in which order
-  std::vector<uint32_t> st, sti;
-  size_t R = 0;
-  std::vector<std::pair<size_t, uint64_t>> segs;  // (offset of first row, rows) per slot
-  uint64_t total = 0;
-  for (uint64_t s = 0; s < slots; ++s) {
-    if (pos + 8 > size) return true;
-    uint64_t n;
-    std::memcpy(&n, base + pos, 8);
-    pos += 8;
-    if (n > 0 && R == 0) {
-      MemSource one(base + pos, size - pos);
-      Reader rr(&one);
-      rr.Pod<uint64_t>();
-      Value v = rr.Val();
-      if (static_cast<size_t>(v.val.Numel()) != d || v.val.dtype != DType::kFloat32) return true;
-      for (auto& kv : v.states) {
-        if (static_cast<size_t>(kv.second.Numel()) != d || kv.second.dtype != DType::kFloat32) return true;
-        st.push_back(kv.first);
-      }
-      for (auto& kv : v.states_i) sti.push_back(kv.first);
-      R = RowBytes(h->dim, st.size(), sti.size());
-      if (one.offset() != R) return true;  // entries not in ascending type order, or another encoding
-    }
-    if (n > 0 && (R == 0 || n > (size - pos) / R)) return true;
-    segs.emplace_back(pos, n);
-    pos += n * R;
-    total += n;
-  }
-  if (pos != size) return true;
-
-  const size_t row0 = c->ids.size();
-  for (uint32_t k : st)
-    if (!c->states.count(k)) c->states[k].assign(row0 * d, 0.f);
-  for (uint32_t k : sti)
-    if (!c->states_i.count(k)) c->states_i[k].assign(row0, 0);
-  c->ids.resize(row0 + total);
-  c->vals.resize((row0 + total) * d);
-  for (auto& kv : c->states) kv.second.resize((row0 + total) * d, 0.f);
-  for (auto& kv : c->states_i) kv.second.resize(row0 + total, 0);
-  std::vector<float*> scol;
-  std::vector<int64_t*> icol;
-  for (uint32_t k : st) scol.push_back(c->states[k].data());
-  for (uint32_t k : sti) icol.push_back(c->states_i[k].data());
-
-  // every row is checked against the fixed layout while it is copied out
-  std::vector<char> tmpl(R, 0);
-  if (R) {
-    char* q = tmpl.data() + 8;
-    q = PutTensorHead(q, h->dim) + d * 4;
-    const uint64_t ns = st.size();
-    std::memcpy(q, &ns, 8);
-    q += 8;
-    for (uint32_t k : st) {
-      std::memcpy(q, &k, 4);
-      q = PutTensorHead(q + 4, h->dim) + d * 4;
-    }
-    const uint64_t ni = sti.size();
-    std::memcpy(q, &ni, 8);
-    q += 8;
-    for (uint32_t k : sti) {
-      std::memcpy(q, &k, 4);
-      q += 12;
-    }
-  }
-  std::atomic<bool> ok{true};
-  std::vector<std::thread> pool;
-  const int T = static_cast<int>(std::max<uint64_t>(1, std::min<uint64_t>(threads, (total + 65535) / 65536)));
-  // global row g -> (segment, index): rows of segment k start at row_start[k]
-  std::vector<uint64_t> row_start(segs.size() + 1, 0);
-  for (size_t k = 0; k < segs.size(); ++k) row_start[k + 1] = row_start[k] + segs[k].second;
-  auto work = [&](uint64_t lo, uint64_t hi) {
-    size_t seg = 0;
-    for (uint64_t g = lo; g < hi; ++g) {
-      while (g >= row_start[seg + 1]) ++seg;
-      const char* q = base + segs[seg].first + (g - row_start[seg]) * R;
-      const size_t out = row0 + g;
-      std::memcpy(&c->ids[out], q, 8);
-      const char* t = tmpl.data();
-      size_t o = 8;
-      if (std::memcmp(q + o, t + o, kTensorHead) != 0) { ok = false; return; }
-      o += kTensorHead;
-      std::memcpy(&c->vals[out * d], q + o, d * 4);
-      o += d * 4;
-      if (std::memcmp(q + o, t + o, 8) != 0) { ok = false; return; }
-      o += 8;
-      for (size_t k = 0; k < st.size(); ++k) {
-        if (std::memcmp(q + o, t + o, 4 + kTensorHead) != 0) { ok = false; return; }
-        o += 4 + kTensorHead;
-        std::memcpy(scol[k] + out * d, q + o, d * 4);
-        o += d * 4;
-      }
-      if (std::memcmp(q + o, t + o, 8) != 0) { ok = false; return; }
-      o += 8;
-      for (size_t k = 0; k < sti.size(); ++k) {
-        if (std::memcmp(q + o, t + o, 4) != 0) { ok = false; return; }
-        std::memcpy(icol[k] + out, q + o + 4, 8);
-        o += 12;
-      }
-    }
-  };
-  const uint64_t per = (total + T - 1) / T;
-  for (int t = 1; t < T; ++t) pool.emplace_back(work, std::min<uint64_t>(total, t * per), std::min<uint64_t>(total, (t + 1) * per));
-  if (total) work(0, std::min<uint64_t>(total, per));
-  for (auto& th : pool) th.join();
-  if (!ok) {  // some row deviates: undo and leave the file to the general reader
-    c->ids.resize(row0);
-    c->vals.resize(row0 * d);
-    for (auto& kv : c->states) kv.second.resize(row0 * d);
-    for (auto& kv : c->states_i) kv.second.resize(row0);
-    return true;
-  }
-  *fast = true;
-  return true;
 }
 
 // ------------------------------------------------------------------ chunked reader

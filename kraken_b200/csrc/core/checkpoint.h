@@ -91,8 +91,8 @@ bool LoadSparse(const std::string& dir, const std::string& name, const RowFilter
 // state entries in ascending type order), so a row's file offset follows from its index.  The
 // stream writer formats rows that arrive in chunks, already in file order (slot by slot, ids
 // ascending as unsigned numbers inside a slot), with several threads that each pwrite() their part;
-// no sort and no whole-table copy happens on the host.  The fast reader maps a file, checks that
-// every row matches the fixed layout of its first row and extracts the columns with several threads;
+// no sort and no whole-table copy happens on the host.  The chunked reader below checks that every row
+// matches the fixed layout of the file's first row while it extracts the columns with several threads;
 // a file that does not match (written by the reference with per-row state sets, say) is left to LoadSparse.
 class SparseStreamWriter {
  public:
@@ -116,11 +116,6 @@ class SparseStreamWriter {
   int slots_begun_ = 0, threads_;
   std::string path_;
 };
-
-// false: no such file.  *fast = false: the file exists but does not have the fixed layout (use LoadSparse).
-// On success the columns of ALL rows are appended to *cols (no filter) and *h is filled.
-bool LoadSparseFast(const std::string& dir, const std::string& name, SparseHeader* h, SparseColumns* cols, bool* fast,
-                    int threads = 8);
 
 // Chunked reader of a fixed-layout sparse file, for tables larger than the host wants to hold twice: the file
 // is opened once (header, the 8 slot counts and the first row's layout are read with pread), then Read()
