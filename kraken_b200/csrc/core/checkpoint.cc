@@ -1,6 +1,7 @@
 #include "checkpoint.h"
 
 #include <fcntl.h>
+#include <sys/mman.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -426,14 +427,23 @@ SparseStreamWriter::SparseStreamWriter(const std::string& dir, const SparseHeade
   w.Pod<uint8_t>(static_cast<uint8_t>(h.init_type));
   w.ConfMap(h.init_conf);
   w.Pod<uint64_t>(kSlotCount);
-  fd_ = ::open(path_.c_str(), O_CREAT | O_TRUNC | O_WRONLY, 0644);
+  const char* mode = std::getenv("KRAKEN_CKPT_WRITE");  // "pwrite": buffered writes instead of the shared mapping
+  map_mode_ = mode == nullptr || std::string(mode) != "pwrite";
+  fd_ = ::open(path_.c_str(), O_CREAT | O_TRUNC | (map_mode_ ? O_RDWR : O_WRONLY), 0644);
   KB_CHECK(fd_ >= 0, err::kCheckpointIO, "cannot open sparse file for " + h.name);
   PwriteAll(fd_, reinterpret_cast<const char*>(head.data()), head.size(), 0);
   offset_ = head.size();
 }
 
 SparseStreamWriter::~SparseStreamWriter() {
+  Unmap();
   if (fd_ >= 0) ::close(fd_);
+}
+
+void SparseStreamWriter::Unmap() {
+  if (map_ != nullptr) ::munmap(map_, map_len_);
+  map_ = nullptr;
+  map_len_ = 0;
 }
 
 void SparseStreamWriter::BeginSlot(uint64_t rows) {
@@ -443,6 +453,20 @@ void SparseStreamWriter::BeginSlot(uint64_t rows) {
   offset_ += 8;
   slot_left_ = rows;
   ++slots_begun_;
+  if (map_mode_ && rows > 0) {
+    // the slot's byte range is known now: extend the file and map the range, so that the formatting threads
+    // store rows straight into the page cache, each faulting its own pages, instead of queueing on the one
+    // lock that buffered writes into a single file take
+    const uint64_t end = offset_ + rows * row_bytes_;
+    const uint64_t page = static_cast<uint64_t>(::sysconf(_SC_PAGESIZE));
+    if (::ftruncate(fd_, static_cast<off_t>(end)) == 0) {
+      map_file_off_ = offset_ / page * page;
+      map_len_ = static_cast<size_t>(end - map_file_off_);
+      void* m = ::mmap(nullptr, map_len_, PROT_READ | PROT_WRITE, MAP_SHARED, fd_, static_cast<off_t>(map_file_off_));
+      map_ = m == MAP_FAILED ? nullptr : static_cast<char*>(m);  // no mapping: this slot goes through pwrite
+      if (map_ == nullptr) map_len_ = 0;
+    }
+  }
 }
 
 void SparseStreamWriter::Append(const uint64_t* ids, const float* vals, const float* const* states,
@@ -455,39 +479,45 @@ void SparseStreamWriter::Append(const uint64_t* ids, const float* vals, const fl
   const int T = static_cast<int>(std::min<size_t>(threads_, (n + 4095) / 4096));
   std::vector<std::thread> pool;
   std::atomic<bool> failed{false};
+  auto format = [&](size_t a, size_t b, char* p) {  // rows [a, b) of this call, back to back at p
+    for (size_t r = a; r < b; ++r) {
+      std::memcpy(p, &ids[r], 8);
+      p += 8;
+      p = PutTensorHead(p, dim_);
+      std::memcpy(p, vals + r * d, d * 4);
+      p += d * 4;
+      const uint64_t ns = st_.size();
+      std::memcpy(p, &ns, 8);
+      p += 8;
+      for (size_t k = 0; k < st_.size(); ++k) {
+        std::memcpy(p, &st_[k], 4);
+        p += 4;
+        p = PutTensorHead(p, dim_);
+        std::memcpy(p, states[k] + r * d, d * 4);
+        p += d * 4;
+      }
+      const uint64_t ni = sti_.size();
+      std::memcpy(p, &ni, 8);
+      p += 8;
+      for (size_t k = 0; k < sti_.size(); ++k) {
+        std::memcpy(p, &sti_[k], 4);
+        p += 4;
+        std::memcpy(p, &states_i[k][r], 8);
+        p += 8;
+      }
+    }
+  };
   auto work = [&](size_t lo, size_t hi) {
     try {
+      if (map_ != nullptr) {
+        format(lo, hi, map_ + (base - map_file_off_) + lo * R);
+        return;
+      }
       constexpr size_t kBatch = 8192;  // rows formatted per pwrite
       std::vector<char> buf(kBatch * R);
       for (size_t a = lo; a < hi; a += kBatch) {
         const size_t b = std::min(hi, a + kBatch);
-        char* p = buf.data();
-        for (size_t r = a; r < b; ++r) {
-          std::memcpy(p, &ids[r], 8);
-          p += 8;
-          p = PutTensorHead(p, dim_);
-          std::memcpy(p, vals + r * d, d * 4);
-          p += d * 4;
-          const uint64_t ns = st_.size();
-          std::memcpy(p, &ns, 8);
-          p += 8;
-          for (size_t k = 0; k < st_.size(); ++k) {
-            std::memcpy(p, &st_[k], 4);
-            p += 4;
-            p = PutTensorHead(p, dim_);
-            std::memcpy(p, states[k] + r * d, d * 4);
-            p += d * 4;
-          }
-          const uint64_t ni = sti_.size();
-          std::memcpy(p, &ni, 8);
-          p += 8;
-          for (size_t k = 0; k < sti_.size(); ++k) {
-            std::memcpy(p, &sti_[k], 4);
-            p += 4;
-            std::memcpy(p, &states_i[k][r], 8);
-            p += 8;
-          }
-        }
+        format(a, b, buf.data());
         PwriteAll(fd_, buf.data(), (b - a) * R, base + a * R);
       }
     } catch (...) {
@@ -501,11 +531,13 @@ void SparseStreamWriter::Append(const uint64_t* ids, const float* vals, const fl
   KB_CHECK(!failed, err::kCheckpointIO, "write to the checkpoint file failed");
   offset_ += n * R;
   slot_left_ -= n;
+  if (slot_left_ == 0) Unmap();
 }
 
 void SparseStreamWriter::Close() {
   KB_CHECK(slot_left_ == 0 && slots_begun_ == static_cast<int>(kSlotCount), err::kBadArgument,
            "the sparse file is incomplete: not all slots were written");
+  Unmap();
   if (fd_ >= 0) {
     KB_CHECK(::close(fd_) == 0, err::kCheckpointIO, "closing the checkpoint file failed");
     fd_ = -1;

@@ -90,7 +90,8 @@ bool LoadSparse(const std::string& dir, const std::string& name, const RowFilter
 // Every row of a table written by this framework has the same byte length (same dimension, same
 // state entries in ascending type order), so a row's file offset follows from its index.  The
 // stream writer formats rows that arrive in chunks, already in file order (slot by slot, ids
-// ascending as unsigned numbers inside a slot), with several threads that each pwrite() their part;
+// ascending as unsigned numbers inside a slot), with several threads that each store their part into a
+// shared mapping of the slot's byte range (buffered writes into one file queue on the file's lock);
 // no sort and no whole-table copy happens on the host.  The chunked reader below checks that every row
 // matches the fixed layout of the file's first row while it extracts the columns with several threads;
 // a file that does not match (written by the reference with per-row state sets, say) is left to LoadSparse.
@@ -115,6 +116,12 @@ class SparseStreamWriter {
   uint64_t offset_ = 0, slot_left_ = 0;
   int slots_begun_ = 0, threads_;
   std::string path_;
+  // rows are stored through a shared mapping of the slot's byte range (KRAKEN_CKPT_WRITE=pwrite: buffered writes)
+  bool map_mode_ = false;
+  char* map_ = nullptr;
+  size_t map_len_ = 0;
+  uint64_t map_file_off_ = 0;
+  void Unmap();
 };
 
 // Chunked reader of a fixed-layout sparse file, for tables larger than the host wants to hold twice: the file
