@@ -34,6 +34,7 @@ class EngineConfig:
     table_capacity: int = 1 << 20    # initial slots per GPU shard (tables grow)
     max_ids_per_call: int = 0        # 0: sized from the first call (2x headroom)
     max_unique_per_call: int = 0     # 0: same as max_ids_per_call; smaller saves exchange-buffer memory
+    async_push: bool = False         # TCP deployment: pushes are applied by a background thread, the caller does not wait (a pull may be one push stale)
     long_id_streams: bool = False    # GPU engine: a pull / push longer than the exchange buffers runs as several rounds (the ranks agree on the count: one small all-reduce per call)
     max_per_owner_per_call: int = 0  # 0: same as max_unique_per_call; unique ids one rank may send to one owner
     spin_limit: int = 1 << 22        # polls before a device-side wait gives up

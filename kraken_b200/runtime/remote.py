@@ -26,8 +26,10 @@ whose ring is stale gets kRouterVersion, refetches and re-partitions only the re
 """
 from __future__ import annotations
 
+import collections
 import logging
 import threading
+from concurrent.futures import ThreadPoolExecutor
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -696,24 +698,54 @@ class RemoteEngine(Engine):
         self.ps: Dict[int, Connecter] = {}
         self.dct_states: Dict[int, object] = {}
         self.refusals: Dict[int, int] = {}   # error code -> how often a server refused a request of this worker
+        self._ring_lock = threading.RLock()
         self._refresh_router()
+        # async_push: pushes are handed to one background thread (so they stay in order) and the caller goes on
+        # with the next forward pass; a pull may then see rows from before the latest push - the reference's
+        # fire-and-forget pushes (kraken/worker/emitter.cc:431-446, 539-549).  A push that failed raises at the
+        # next push, pull or stop.
+        self._pusher = ThreadPoolExecutor(max_workers=1, thread_name_prefix="kraken-push") if cfg.async_push else None
+        self._push_futs: "collections.deque" = collections.deque()
 
     def _refresh_router(self) -> None:
-        meta, _ = self.scheduler.call(Rpc.FETCH_ROUTER)
-        self.router = _router_from_hex(meta["router"])
-        self.version = meta["version"]
-        for nid, addr in meta["nodes"].items():
-            if int(nid) not in self.ps:
-                self.ps[int(nid)] = Connecter(addr, compress=self.compress)
-        vn = self.router.vnodes()
-        self._vhash = np.array([v[0] for v in vn], dtype=np.uint64)
-        self._vnode = np.array([v[1] for v in vn], dtype=np.int64)
+        """Fetches the ring and publishes it as ONE tuple (router, version, vnode hashes, vnode owners): a request
+        partitions its ids and stamps its version from the same tuple, whichever thread refreshes meanwhile
+        (with ``async_push`` the push thread and the caller's thread both do)."""
+        with self._ring_lock:
+            meta, _ = self.scheduler.call(Rpc.FETCH_ROUTER)
+            router = _router_from_hex(meta["router"])
+            for nid, addr in meta["nodes"].items():
+                if int(nid) not in self.ps:
+                    self.ps[int(nid)] = Connecter(addr, compress=self.compress)
+            vn = router.vnodes()
+            self._ring = (router, meta["version"], np.array([v[0] for v in vn], dtype=np.uint64),
+                          np.array([v[1] for v in vn], dtype=np.int64))
 
-    def _owners(self, table_id: int, ids: torch.Tensor) -> np.ndarray:
+    @property
+    def router(self):
+        return self._ring[0]
+
+    @router.setter
+    def router(self, r) -> None:   # the base class installs a placeholder ring before the first fetch
+        old = getattr(self, "_ring", (None, 0, np.zeros(0, np.uint64), np.zeros(0, np.int64)))
+        self._ring = (r, old[1], old[2], old[3])
+
+    @property
+    def version(self) -> int:
+        return self._ring[1]
+
+    @version.setter
+    def version(self, v: int) -> None:   # tests age the ring with it
+        r = self._ring
+        self._ring = (r[0], int(v), r[2], r[3])
+
+    @staticmethod
+    def _owners(ring, table_id: int, ids: torch.Tensor) -> np.ndarray:
+        _, _, vhash, vnode = ring
         hv = mix64(ids.numpy().view(np.uint64)) ^ np.uint64(C.mix64(table_id))
-        idx = np.searchsorted(self._vhash, hv, side="left")
-        idx[idx == len(self._vhash)] = 0
-        return self._vnode[idx]
+        idx = np.searchsorted(vhash, hv, side="left")
+        idx[idx == len(vhash)] = 0
+        return vnode[idx]
 
     RETRY_CODES = (7, 8)  # kNodeStatus (server busy transferring / saving), kRouterVersion (our ring is old)
 
@@ -733,9 +765,10 @@ class RemoteEngine(Engine):
         that has just joined) the ring is refetched, the owner looked up again and the call repeated."""
         attempt = 0
         while True:
-            owner = self.router.hit(C.mix64(table_id))
+            router, version = self._ring[0], self._ring[1]
+            owner = router.hit(C.mix64(table_id))
             try:
-                return self.ps[owner].call(rpc, {**meta, "router_version": self.version}, tensors)
+                return self.ps[owner].call(rpc, {**meta, "router_version": version}, tensors)
             except RpcError as e:
                 if e.code not in self.RETRY_CODES:
                     raise
@@ -747,10 +780,11 @@ class RemoteEngine(Engine):
         partitioned again on the refreshed ring and sent again, alone: parts that were accepted are
         never repeated, so a push is applied exactly once.  ``done(positions, reply_tensors)`` is called
         for every accepted part with the positions (into ``ids``) it covered."""
-        owners = self._owners(table_id, ids)
         # every part carries the version of the ring it was partitioned on: a refetch triggered by one refused part
-        # must not let the remaining parts of the OLD partition pass a server's version check
-        version = self.version
+        # (or by another thread) must not let the remaining parts of the OLD partition pass a server's version check
+        ring = self._ring
+        owners = self._owners(ring, table_id, ids)
+        version = ring[1]
         for node in np.unique(owners):
             sel = torch.from_numpy(np.nonzero(owners == node)[0])
             tensors = [ids[sel]] + ([payload[sel]] if payload is not None else [])
@@ -794,8 +828,25 @@ class RemoteEngine(Engine):
         return tid
 
     # dense
+    def _submit_push(self, fn, *args) -> None:
+        if self._pusher is None:
+            fn(*args)
+            return
+        self._reap_pushes()
+        self._push_futs.append(self._pusher.submit(fn, *args))
+
+    def _reap_pushes(self, wait: bool = False) -> None:
+        """Raises the error of a background push that has failed; ``wait``: blocks until every push is applied."""
+        while self._push_futs and (wait or self._push_futs[0].done()):
+            self._push_futs.popleft().result()
+
+    def flush_pushes(self) -> None:
+        """Returns when every push handed over so far has been applied on the servers."""
+        self._reap_pushes(wait=True)
+
     def pull_dense_table(self, table_id):
         info = self._table(table_id, "dense")
+        self._reap_pushes()
         _, ts = self._call_dense(table_id, Rpc.PULL_DENSE, {"table_ids": [table_id]})
         return ts[0].view(*info.shape)
 
@@ -806,10 +857,10 @@ class RemoteEngine(Engine):
         if st is not None:
             packed = C.cpu_dct_compress(g, self.cfg.life_span, self.cfg.eta, st)
             if packed is not None:
-                self._call_dense(table_id, Rpc.PUSH_DENSE, {"table_id": table_id, "lr": self.lr, "coo": True},
-                                 list(packed))
+                self._submit_push(self._call_dense, table_id, Rpc.PUSH_DENSE,
+                                  {"table_id": table_id, "lr": self.lr, "coo": True}, list(packed))
                 return
-        self._call_dense(table_id, Rpc.PUSH_DENSE, {"table_id": table_id, "lr": self.lr}, [g])
+        self._submit_push(self._call_dense, table_id, Rpc.PUSH_DENSE, {"table_id": table_id, "lr": self.lr}, [g])
 
     # sparse
     def pull_sparse_table(self, table_id, indices):
@@ -821,6 +872,7 @@ class RemoteEngine(Engine):
         def put(pos, ts):
             rows[pos] = ts[0]
 
+        self._reap_pushes()
         self._call_sparse(Rpc.PULL_SPARSE, table_id, {}, uniq, None, put)
         return rows[inv].view(*idx.shape, info.dimension)
 
@@ -830,16 +882,18 @@ class RemoteEngine(Engine):
         g = grad.detach().to("cpu", torch.float32).contiguous().view(-1, info.dimension)
         uniq, inv = C.cpu_dedup(idx)
         summed = C.cpu_segment_sum(g, inv, uniq.numel())
-        self._call_sparse(Rpc.PUSH_SPARSE, table_id, {"lr": self.lr}, uniq, summed, lambda pos, ts: None)
+        self._submit_push(self._call_sparse, Rpc.PUSH_SPARSE, table_id, {"lr": self.lr}, uniq, summed,
+                          lambda pos, ts: None)
 
     # several tables in one round trip per server (kCombinePull* / kCombinePushSparseTable of the reference)
     def combine_pull_dense_table(self, table_ids):
         by_owner: Dict[int, List[int]] = {}
+        ring = self._ring
         for t in table_ids:
             self._table(t, "dense")
-            by_owner.setdefault(self.router.hit(C.mix64(t)), []).append(t)
+            by_owner.setdefault(ring[0].hit(C.mix64(t)), []).append(t)
         out: Dict[int, torch.Tensor] = {}
-        version = self.version  # of the ring the owners above were looked up on
+        version = ring[1]  # of the ring the owners above were looked up on
         for owner, tids in by_owner.items():
             try:
                 _, ts = self.ps[owner].call(Rpc.COMBINE_PULL_DENSE, {"table_ids": tids, "router_version": version})
@@ -855,9 +909,10 @@ class RemoteEngine(Engine):
     def _combine_sparse(self, rpc: int, meta: dict, table_ids, uniqs, payloads, done) -> None:
         """One message per server carrying that server's part of every table.  A server that refuses
         gets its parts again table by table through ``_call_sparse`` (which re-partitions and retries)."""
-        owners = [self._owners(t, u) for t, u in zip(table_ids, uniqs)]
+        ring = self._ring
+        owners = [self._owners(ring, t, u) for t, u in zip(table_ids, uniqs)]
         nodes = sorted({int(n) for o in owners for n in np.unique(o)})
-        version = self.version  # of the ring this partition was made on (see _call_sparse)
+        version = ring[1]  # of the ring this partition was made on (see _call_sparse)
         for node in nodes:
             sels = [torch.from_numpy(np.nonzero(o == node)[0]) for o in owners]
             ks = [k for k, sel in enumerate(sels) if sel.numel() > 0]
@@ -906,11 +961,12 @@ class RemoteEngine(Engine):
             uniqs.append(uniq)
             sums.append(C.cpu_segment_sum(g.detach().to("cpu", torch.float32).contiguous().view(-1, info.dimension), inv,
                                           uniq.numel()))
-        self._combine_sparse(Rpc.COMBINE_PUSH_SPARSE, {"lr": self.lr}, list(table_ids), uniqs, sums,
-                             lambda k, pos, ts: None)
+        self._submit_push(self._combine_sparse, Rpc.COMBINE_PUSH_SPARSE, {"lr": self.lr}, list(table_ids), uniqs, sums,
+                          lambda k, pos, ts: None)
 
     # checkpoints are written and read by the servers; the scheduler orchestrates
     def try_save_model(self) -> bool:
+        self.flush_pushes()
         return bool(self.scheduler.call(Rpc.TRY_SAVE, timeout_ms=600_000)[0]["success"])
 
     def try_load_model_blocked(self, load_dir: str) -> bool:
@@ -925,6 +981,11 @@ class RemoteEngine(Engine):
         return True
 
     def stop(self):
-        for c in list(self.ps.values()) + [self.scheduler]:
-            c.close()
-        super().stop()
+        try:
+            self.flush_pushes()
+        finally:
+            if self._pusher is not None:
+                self._pusher.shutdown(wait=True)
+            for c in list(self.ps.values()) + [self.scheduler]:
+                c.close()
+            super().stop()

@@ -325,3 +325,49 @@ def test_failed_join_is_rolled_back(tmp_path):
         sched.stop()
         for s in servers + ([late] if late is not None else []):
             s.stop()
+
+
+def test_async_push_returns_at_once_and_is_applied_in_order(tmp_path):
+    """``initialize(..., async_push=True)``: a push is handed to a background thread and the call returns before
+    the servers have answered (the reference's fire-and-forget pushes, kraken/worker/emitter.cc:431-446,539-549).
+    Pushes stay in order, ``flush_pushes()`` (and a save, and stop) wait for them, and a push that a server
+    rejects raises at a later call instead of vanishing."""
+    import time
+    import pytest
+    sched, servers = boot(tmp_path)
+    try:
+        kk.initialize(f"tcp://127.0.0.1:{sched.port}", async_push=True)
+        kk.init_model("m", kk.OptimType.kSGD, {})
+        kk.update_lr(1.0)
+        ts = kk.register_sparse_table("e", 2, torch.float32, kk.InitializerType.kConstant, {"value": "0.0"})
+        td = kk.register_dense_table("w", torch.zeros(4))
+        ids = torch.arange(2000)
+        kk.pull_sparse_table(ts, ids)
+        # make every server slow to answer a push: the calls below must not wait for it
+        from kraken_b200.runtime.rpc import Rpc
+        for s in servers:
+            real = s.station.handlers[Rpc.PUSH_SPARSE]
+            s.station.handlers[Rpc.PUSH_SPARSE] = lambda meta, tensors, real=real: (time.sleep(0.15), real(meta, tensors))[1]
+        t0 = time.perf_counter()
+        for step in range(1, 4):
+            kk.update_lr(float(step))                       # each push carries the rate it was made with
+            kk.push_sparse_table(ts, ids, torch.ones(2000, 2))
+            kk.push_dense_table(td, torch.ones(4))
+        handed_over = time.perf_counter() - t0
+        eng = kk.native.engine()
+        eng.flush_pushes()
+        applied = time.perf_counter() - t0
+        assert handed_over < 0.25 < applied, (handed_over, applied)   # 3 pushes x 2 servers x 0.15 s happen behind the caller
+        assert torch.allclose(kk.pull_sparse_table(ts, ids), torch.full((2000, 2), -6.0))   # -(1 + 2 + 3)
+        assert torch.allclose(kk.pull_dense_table(td), torch.full((4,), -6.0))
+        # a push the servers reject (unknown ids) surfaces at a later call
+        kk.push_sparse_table(ts, torch.arange(10_000, 10_010), torch.ones(10, 2))
+        from kraken_b200.runtime.rpc import RpcError
+        with pytest.raises(RpcError) as err:
+            eng.flush_pushes()
+        assert err.value.code == 15          # kSparseIdNotExist, as the synchronous push reports it
+    finally:
+        kk.stop()
+        sched.stop()
+        for s in servers:
+            s.stop()
