@@ -4,6 +4,7 @@ from __future__ import annotations
 import json
 import os
 import time
+from typing import Optional
 
 import torch
 import torch.distributed as dist
@@ -99,6 +100,56 @@ def measure_peer_gbs(mib: int = 256, reps: int = 5) -> float:
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     del src, dst
     return float(t.item())
+
+
+class NvlinkCounters:
+    """NVLink bytes sent and received by this rank's GPU, read from NVML's per-device throughput counters
+    (fields NVLINK_THROUGHPUT_DATA_TX / RX; payload bytes, in KiB; asked for all links at once, else link by
+    link).  Reading only: nothing on the GPU is configured.  ``read()`` returns (tx_bytes, rx_bytes) or None
+    where the driver does not expose the counters (``why`` then says what failed); differences between two
+    reads are the traffic in between."""
+
+    def __init__(self, device: Optional[torch.device] = None) -> None:
+        self.handle, self.why, self.per_link = None, "", False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            dev = torch.cuda.current_device() if device is None else (device.index or 0)
+            uuid = getattr(torch.cuda.get_device_properties(dev), "uuid", None)
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(dev)
+        except Exception as e:   # no NVML, or no such device in this container
+            self.why = f"NVML: {type(e).__name__}: {e}"
+
+    def _fields(self, scopes):
+        nv = self.nv
+        ids = [(f, s) for s in scopes for f in (nv.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX,
+                                                nv.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX)]
+        vals = nv.nvmlDeviceGetFieldValues(self.handle, ids)
+        good = [v for v in vals if v.nvmlReturn == nv.NVML_SUCCESS]
+        if not good:
+            self.why = f"field query returned {sorted({int(v.nvmlReturn) for v in vals})}"
+            return None
+        tx = sum(int(v.value.ullVal) for v in good if v.fieldId == nv.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX)
+        rx = sum(int(v.value.ullVal) for v in good if v.fieldId == nv.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX)
+        return tx * 1024, rx * 1024
+
+    def read(self):
+        if self.handle is None:
+            return None
+        try:
+            if not self.per_link:
+                got = self._fields([0xFFFFFFFF])   # scope: all links of the device
+                if got is not None:
+                    return got
+                self.per_link = True
+            return self._fields(range(18))
+        except Exception as e:
+            self.why = f"{type(e).__name__}: {e}"
+            return None
 
 
 def emit(record: dict) -> None:

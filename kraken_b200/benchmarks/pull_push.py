@@ -13,7 +13,8 @@ import numpy as np
 import torch
 
 import kraken_b200.pytorch as kk
-from kraken_b200.benchmarks.common import DeviceTimer, emit, measure_copy_gbs, measure_peer_gbs, sync_all, world_rank
+from kraken_b200.benchmarks.common import (DeviceTimer, NvlinkCounters, emit, measure_copy_gbs, measure_peer_gbs, sync_all,
+                                            world_rank)
 from kraken_b200.models.synthetic import zipf_ids
 
 
@@ -144,8 +145,37 @@ def main():
     rec["rows_created_per_step"] = round(created)
     hbm_gbs = a.hbm_gbs or measure_copy_gbs(dev)
     link_gbs = a.link_gbs or measure_peer_gbs()
-    rec.update(roofline(eng.metrics()["big"]["last_exchange"], 64, rec["pull_us"], rec["push_us"], created, hbm_gbs,
-                        link_gbs))
+    ex = eng.metrics()["big"]["last_exchange"]
+    rec.update(roofline(ex, 64, rec["pull_us"], rec["push_us"], created, hbm_gbs, link_gbs))
+
+    if world > 1 and g_pull is not None:
+        # measured link traffic of the fused kernels: NVML's NVLink byte counters around 50 replays of the pull
+        # alone and 50 of the push alone (same ids), next to the bytes the exchange counts predict
+        nvl = NvlinkCounters(dev)
+        reps = 50
+
+        def traffic(graph):
+            sync_all()
+            time.sleep(0.2)          # the counters are sampled by the driver, not updated per packet
+            a = nvl.read()
+            for _ in range(reps):
+                graph.replay()
+            sync_all()
+            time.sleep(0.2)
+            b = nvl.read()
+            return None if a is None or b is None else ((b[0] - a[0]) / reps, (b[1] - a[1]) / reps)
+
+        t_pull, t_push = traffic(g_pull), traffic(g_push)
+        if t_pull is None or t_push is None:
+            rec["nvlink_counters"] = "not exposed by the driver here: " + nvl.why
+        else:
+            rec["nvlink_counters"] = {
+                "pull_tx_bytes": round(t_pull[0]), "pull_rx_bytes": round(t_pull[1]),
+                "pull_expected_out": ex["pull_bytes_out"], "pull_expected_in": ex["pull_bytes_in"],
+                "push_tx_bytes": round(t_push[0]), "push_rx_bytes": round(t_push[1]),
+                "push_expected_out": ex["push_bytes_out"],
+                "note": "per launch sequence and GPU; expected = remote unique rows x row bytes (+ 8 B per id sent); "
+                        "rx of a push and tx of a pull are the other ranks' rows for this shard, about the same size"}
 
     if a.checkpoint_rows > 0:
         # checkpoint timing on a shard trimmed to checkpoint-rows rows (the file format costs ~580 B per row)
