@@ -13,6 +13,7 @@
 
 #include "core/checkpoint.h"
 #include "core/hash.h"
+#include "core/net.h"
 #include "core/router.h"
 #include "core/serialize.h"
 #include "core/snappy_codec.h"
@@ -686,6 +687,77 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                            ip.data());
            },
            "False: a row deviates from the fixed layout (load the file with ckpt_load_sparse instead)");
+
+  // ---------------- TCP transport of the multi-process deployment (framing, compression, client, server)
+  m.def(
+      "net_send_frame",
+      [](int fd, uint64_t stamp, int32_t code, const std::string& body, uint8_t compress) {
+        py::gil_scoped_release nogil;
+        return net::SendFrame(fd, stamp, code, body, compress);
+      },
+      py::arg("fd"), py::arg("stamp"), py::arg("code"), py::arg("body"), py::arg("compress") = 0);
+  m.def(
+      "net_recv_frame",
+      [](int fd, int timeout_ms) -> py::object {
+        // (stamp, code, body, compress), or the reason as a string: "closed", "timeout", "bad frame"
+        net::Frame f;
+        net::RecvStatus st;
+        {
+          py::gil_scoped_release nogil;
+          st = net::RecvFrame(fd, timeout_ms, &f);
+        }
+        switch (st) {
+          case net::RecvStatus::kOk: return py::make_tuple(f.stamp, f.code, py::bytes(f.body), f.compress);
+          case net::RecvStatus::kClosed: return py::str("closed");
+          case net::RecvStatus::kTimeout: return py::str("timeout");
+          default: return py::str("bad frame");
+        }
+      },
+      py::arg("fd"), py::arg("timeout_ms") = -1);
+  py::class_<net::Connecter>(m, "NetConnecter")
+      .def(py::init<const std::string&, int, int, uint8_t>(), py::arg("host"), py::arg("port"),
+           py::arg("timeout_ms") = 5000, py::arg("compress") = 0, py::call_guard<py::gil_scoped_release>())
+      .def(
+          "call",
+          [](net::Connecter& c, uint32_t type, const std::string& body, int timeout_ms) {
+            // (0, reply code, reply body), or (kTimeout | kConnection, 0, message) when no reply was had
+            std::pair<int32_t, std::string> r;
+            int32_t transport = 0;
+            {
+              py::gil_scoped_release nogil;
+              try {
+                r = c.Call(type, body, timeout_ms);
+              } catch (const KrakenError& e) {
+                transport = e.code;
+                r = {0, e.what()};
+              }
+            }
+            return py::make_tuple(transport, r.first, py::bytes(r.second));
+          },
+          py::arg("type"), py::arg("body"), py::arg("timeout_ms") = 0)
+      .def("close", &net::Connecter::Close, py::call_guard<py::gil_scoped_release>());
+  py::class_<net::Station>(m, "NetStation")
+      .def(py::init([](const std::string& host, int port, py::function fn) {
+             // the callable is released under the GIL, whichever thread drops the last reference
+             auto held = std::shared_ptr<py::function>(new py::function(std::move(fn)), [](py::function* p) {
+               py::gil_scoped_acquire g;
+               delete p;
+             });
+             net::Handler h = [held](uint32_t type, const std::string& body) -> std::pair<int32_t, std::string> {
+               py::gil_scoped_acquire g;
+               try {
+                 py::tuple out = (*held)(type, py::bytes(body)).cast<py::tuple>();
+                 return {out[0].cast<int32_t>(), out[1].cast<std::string>()};
+               } catch (py::error_already_set& e) {
+                 return {err::kUnknown, std::string(e.what())};
+               }
+             };
+             return new net::Station(host, port, std::move(h));
+           }),
+           py::arg("host"), py::arg("port"), py::arg("handler"))
+      .def_property_readonly("port", &net::Station::port)
+      .def("start", &net::Station::Start)
+      .def("stop", &net::Station::Stop, py::call_guard<py::gil_scoped_release>());
 
   // ---------------- CPU shard
   py::class_<CpuShard>(m, "CpuShard")

@@ -125,6 +125,7 @@ constexpr int32_t kTableFull = 21;       // device hash table has no free slot w
 constexpr int32_t kInboxOverflow = 22;   // a peer sent more unique ids than the inbox holds
 constexpr int32_t kCheckpointIO = 23;
 constexpr int32_t kBadArgument = 24;
+constexpr int32_t kConnection = 25;     // the peer closed the connection or sent a broken frame
 
 inline const char* Msg(int32_t c) {
   switch (c) {
@@ -153,6 +154,7 @@ inline const char* Msg(int32_t c) {
     case kInboxOverflow: return "peer inbox overflow";
     case kCheckpointIO: return "checkpoint I/O error";
     case kBadArgument: return "bad argument";
+    case kConnection: return "connection lost";
     default: return "unknown error";
   }
 }

@@ -24,18 +24,12 @@ from __future__ import annotations
 
 import json
 import socket
-import socketserver
 import struct
-import threading
-import time
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from .._native import C
-
-HEADER = struct.Struct("<QiB")  # timestamp, type | error code, compress
-
 
 class Rpc:
     HEARTBEAT = 0
@@ -100,127 +94,93 @@ def unpack_body(body: bytes) -> Tuple[dict, List[torch.Tensor]]:
     return meta, tensors
 
 
-def _recv_exact(sock: socket.socket, n: int) -> bytes:
-    buf = bytearray()
-    while len(buf) < n:
-        chunk = sock.recv(n - len(buf))
-        if not chunk:
-            raise ConnectionError("peer closed the connection")
-        buf += chunk
-    return bytes(buf)
-
-
 COMPRESS_NONE, COMPRESS_SNAPPY = 0, 1   # CompressType::kNo / kSnappy, kraken/rpc/protocol.h:7-10
 
 
 def send_frame(sock: socket.socket, stamp: int, code: int, body: bytes, compress: int = COMPRESS_NONE) -> None:
-    if compress == COMPRESS_SNAPPY:
-        body = C.snappy_compress(bytes(body))
-    sock.sendall(struct.pack("<I", len(body)) + HEADER.pack(stamp, code, compress) + body)
+    """One frame onto a connected socket (the native framing code, csrc/core/net.cc, on the socket's descriptor)."""
+    if not C.net_send_frame(sock.fileno(), stamp, code, bytes(body), compress):
+        raise ConnectionError("peer closed the connection")
 
 
-def recv_frame(sock: socket.socket) -> Tuple[int, int, bytes, int]:
+def recv_frame(sock: socket.socket, timeout_ms: int = -1) -> Tuple[int, int, bytes, int]:
     """(correlation id, type or error code, body as sent by the application, compression used)."""
-    (n,) = struct.unpack("<I", _recv_exact(sock, 4))
-    stamp, code, compress = HEADER.unpack(_recv_exact(sock, HEADER.size))
-    body = _recv_exact(sock, n)
-    if compress == COMPRESS_SNAPPY:
-        try:
-            body = C.snappy_uncompress(body)
-        except C.KrakenError as e:   # kSnappyUncompress: the stream is unusable, drop the connection
-            raise ConnectionError(str(e)) from e
-    elif compress != COMPRESS_NONE:
-        raise ConnectionError(f"unknown body compression {compress}")
-    return stamp, code, body, compress
+    got = C.net_recv_frame(sock.fileno(), timeout_ms)
+    if isinstance(got, str):
+        if got == "timeout":
+            raise socket.timeout("no frame in time")
+        raise ConnectionError(f"peer {got}")
+    return got
 
 
 Handler = Callable[[dict, List[torch.Tensor]], Tuple[dict, Sequence[torch.Tensor]]]
 
 
 class Station:
-    """Threaded TCP server dispatching frames to registered handlers."""
+    """Threaded TCP server dispatching frames to registered handlers.  Sockets, framing, body compression
+    and the thread per connection are native (csrc/core/net.cc); a request's body is unpacked, handled and
+    the reply packed here, on the connection's thread."""
 
     def __init__(self, port: int, host: str = "0.0.0.0") -> None:
         self.handlers: Dict[int, Handler] = {}
-        station = self
+        self.native = C.NetStation(host, port, self._dispatch)
+        self.port = self.native.port
 
-        class _H(socketserver.BaseRequestHandler):
-            def handle(self):
-                self.request.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
-                while True:
-                    try:
-                        stamp, rpc_type, body, comp = recv_frame(self.request)
-                    except (ConnectionError, OSError, struct.error):
-                        return
-                    fn = station.handlers.get(rpc_type)
-                    try:
-                        if fn is None:
-                            raise RpcError(1, f"type {rpc_type}")
-                        meta, tensors = unpack_body(body)
-                        out_meta, out_tensors = fn(meta, tensors)
-                        send_frame(self.request, stamp, 0, pack_body(out_meta, out_tensors), comp)
-                    except RpcError as e:
-                        send_frame(self.request, stamp, e.code, pack_body({"what": str(e)}))
-                    except C.KrakenError as e:
-                        send_frame(self.request, stamp, -1, pack_body({"what": str(e)}))
-                    except Exception as e:  # a failing handler must not take the server down
-                        send_frame(self.request, stamp, -1, pack_body({"what": repr(e)}))
-
-        class _S(socketserver.ThreadingTCPServer):
-            allow_reuse_address = True
-            daemon_threads = True
-
-        self.server = _S((host, port), _H)
-        self.port = self.server.server_address[1]
-        self.thread: Optional[threading.Thread] = None
+    def _dispatch(self, rpc_type: int, body: bytes) -> Tuple[int, bytes]:
+        fn = self.handlers.get(rpc_type)
+        try:
+            if fn is None:
+                raise RpcError(1, f"type {rpc_type}")
+            meta, tensors = unpack_body(body)
+            out_meta, out_tensors = fn(meta, tensors)
+            return 0, pack_body(out_meta, out_tensors)
+        except RpcError as e:
+            return e.code, pack_body({"what": str(e)})
+        except C.KrakenError as e:
+            return -1, pack_body({"what": str(e)})
+        except Exception as e:  # a failing handler must not take the server down
+            return -1, pack_body({"what": repr(e)})
 
     def register(self, rpc_type: int, fn: Handler) -> None:
         self.handlers[rpc_type] = fn
 
     def start(self) -> None:
-        self.thread = threading.Thread(target=self.server.serve_forever, daemon=True)
-        self.thread.start()
+        self.native.start()
 
     def stop(self) -> None:
-        self.server.shutdown()
-        self.server.server_close()
+        self.native.stop()
 
 
 class Connecter:
-    """Client for one peer.  ``call`` is synchronous; a reply that does not arrive within
-    ``timeout_ms`` raises kTimeout (17), an error reply raises with the server's code."""
+    """Client for one peer (native socket code, csrc/core/net.cc).  ``call`` is synchronous and thread-safe; a
+    reply that does not arrive within ``timeout_ms`` raises kTimeout (17), an error reply raises with the
+    server's code, a lost connection raises ConnectionError."""
 
     def __init__(self, addr: str, timeout_ms: int = 5000, compress: int = COMPRESS_NONE) -> None:
         host, port = addr.rsplit(":", 1)
         self.addr = addr
         self.compress = compress
-        self.timeout = timeout_ms / 1000.0
-        self.sock = socket.create_connection((host, int(port)), timeout=self.timeout)
-        self.sock.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
-        self.lock = threading.Lock()
-        self.stamp = int(time.time() * 1e6)
+        try:
+            self.native = C.NetConnecter(host, int(port), int(timeout_ms), int(compress))
+        except C.KrakenError as e:
+            raise ConnectionError(str(e)) from e
 
     def call(self, rpc_type: int, meta: Optional[dict] = None, tensors: Sequence[torch.Tensor] = (),
              timeout_ms: Optional[int] = None) -> Tuple[dict, List[torch.Tensor]]:
-        with self.lock:
-            self.stamp += 1
-            stamp = self.stamp
-            self.sock.settimeout(self.timeout if timeout_ms is None else timeout_ms / 1000.0)
-            try:
-                send_frame(self.sock, stamp, rpc_type, pack_body(meta or {}, tensors), self.compress)
-                while True:
-                    got, code, body, _ = recv_frame(self.sock)
-                    if got == stamp:
-                        break  # stale replies of timed-out calls are dropped
-            except socket.timeout:
-                raise RpcError(17, f"{self.addr} type {rpc_type}")
-        out_meta, out_tensors = unpack_body(body)
+        transport, code, body = self.native.call(int(rpc_type), pack_body(meta or {}, tensors), int(timeout_ms or 0))
+        if transport == 17:
+            raise RpcError(17, f"{self.addr} type {rpc_type}")
+        if transport != 0:
+            raise ConnectionError(bytes(body).decode(errors="replace"))
+        try:
+            out_meta, out_tensors = unpack_body(body)
+        except Exception:
+            if code == 0:
+                raise
+            out_meta, out_tensors = {"what": bytes(body).decode(errors="replace")}, []   # an error raised below the handler
         if code != 0:
             raise RpcError(code, out_meta.get("what", ""))
         return out_meta, out_tensors
 
     def close(self) -> None:
-        try:
-            self.sock.close()
-        except OSError:
-            pass
+        self.native.close()

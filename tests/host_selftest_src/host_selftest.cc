@@ -1,19 +1,22 @@
 // Stand-alone exercise of the host-side C++ (router, serializer, checkpoint files, CPU shard,
-// CPU reference kernels, task queue) meant to be compiled with -fsanitize=address,undefined or
+// CPU reference kernels, task queue, TCP transport) meant to be compiled with -fsanitize=address,undefined or
 // -fsanitize=thread and run by the test-suite.  The reference builds with plain -O3 / -O0 -g and has
 // no sanitizer job (CMakeLists.txt:54-55); its known latent races are listed next to the code
 // that replaces them.  Exit code 0 = every check passed and the sanitizer stayed silent.
 #include <atomic>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <filesystem>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "core/checkpoint.h"
 #include "core/hash.h"
+#include "core/net.h"
 #include "core/router.h"
 #include "core/serialize.h"
 #include "core/task_queue.h"
@@ -164,12 +167,60 @@ static void threaded_queue() {
   q.Stop();
 }
 
+// Station + connecters: eight client threads against one server, half of them with compressed bodies, a call
+// that times out, the late reply that must be dropped, and a shutdown under open connections.
+static void transport() {
+  std::atomic<int> served{0};
+  net::Station st("127.0.0.1", 0, [&](uint32_t type, const std::string& body) -> std::pair<int32_t, std::string> {
+    served.fetch_add(1);
+    if (type == 99) std::this_thread::sleep_for(std::chrono::milliseconds(300));
+    if (type == 98) throw KrakenError(err::kTableNotExist, "no such table");
+    return {0, std::string(body.rbegin(), body.rend())};
+  });
+  st.Start();
+  std::vector<std::thread> clients;
+  std::atomic<int> bad{0};
+  for (int k = 0; k < 8; ++k)
+    clients.emplace_back([&, k] {
+      net::Connecter c("127.0.0.1", st.port(), 5000, static_cast<uint8_t>(k % 2));
+      for (int i = 0; i < 50; ++i) {
+        std::string body(static_cast<size_t>(1 + 977 * (i % 5)), static_cast<char>('a' + k));
+        body[0] = static_cast<char>('0' + i % 10);
+        auto r = c.Call(static_cast<uint32_t>(k), body, 0);
+        if (r.first != 0 || r.second != std::string(body.rbegin(), body.rend())) bad.fetch_add(1);
+      }
+    });
+  for (auto& t : clients) t.join();
+  CHECK(bad.load() == 0 && served.load() == 400);
+  net::Connecter c("127.0.0.1", st.port(), 5000, 0);
+  bool timed_out = false;
+  try {
+    c.Call(99, "slow", 50);
+  } catch (const KrakenError& e) {
+    timed_out = e.code == err::kTimeout;
+  }
+  CHECK(timed_out);
+  auto r = c.Call(1, "abc", 2000);  // the reply to the call above arrives first and is skipped
+  CHECK(r.first == 0 && r.second == "cba");
+  r = c.Call(98, "", 0);
+  CHECK(r.first == err::kTableNotExist);
+  st.Stop();
+  bool lost = false;
+  try {
+    c.Call(1, "abc", 500);
+  } catch (const KrakenError& e) {
+    lost = e.code == err::kConnection;
+  }
+  CHECK(lost);
+}
+
 int main(int argc, char** argv) {
   const std::string dir = argc > 1 ? argv[1] : "selftest_ckpt";
   router_and_serializer();
   shard_checkpoint_round_trip(dir);
   reference_kernels();
   threaded_queue();
+  transport();
   std::puts("host selftest: ok");
   return 0;
 }

@@ -1,4 +1,4 @@
-"""Host-side C++ (router, serializer, checkpoint files, CPU shard, reference kernels, task queue)
+"""Host-side C++ (router, serializer, checkpoint files, CPU shard, reference kernels, task queue, TCP transport)
 built with AddressSanitizer + UBSan and with ThreadSanitizer and run as a stand-alone program.
 The reference has no sanitizer job (its CMakeLists.txt:54-55 sets -O3 / -O0 -g only)."""
 import os
@@ -9,7 +9,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(ROOT, "kraken_b200", "csrc")
-SOURCES = [os.path.join(ROOT, "tests", "host_selftest_src", "host_selftest.cc"), "core/router.cc", "core/checkpoint.cc", "cpu/cpu_shard.cc", "cpu/cpu_ops.cc"]
+SOURCES = [os.path.join(ROOT, "tests", "host_selftest_src", "host_selftest.cc"), "core/router.cc", "core/checkpoint.cc", "core/net.cc", "cpu/cpu_shard.cc", "cpu/cpu_ops.cc"]
 
 
 @pytest.mark.parametrize("name,flags", [("asan_ubsan", "-fsanitize=address,undefined"), ("tsan", "-fsanitize=thread")])
