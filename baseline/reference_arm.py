@@ -155,3 +155,44 @@ def run(args) -> None:
                 p.kill()
         for f in logs:
             f.close()
+
+
+def run_wide_deep_cpu(steps: int = 200, batch: int = 512, torch_threads: int = 0) -> dict:
+    """The CPU Wide&Deep configuration on the reference: its scheduler, ONE ps_server and one worker process
+    (baseline/ref_wide_deep_worker.py) over localhost.  Returns the worker's record, or {"unavailable": why}."""
+    why = _installed()
+    if why:
+        return {"impl": "reference", "unavailable": why}
+    env = dict(os.environ)
+    env["LD_LIBRARY_PATH"] = os.path.join(_REF, "lib") + os.pathsep + env.get("LD_LIBRARY_PATH", "")
+    env.pop("PYTHONPATH", None)
+    ports = _free_ports(2)
+    s_addr = f"127.0.0.1:{ports[0]}"
+    procs = []
+    try:
+        procs.append(subprocess.Popen([os.path.join(_REF, "bin", "scheduler_server"), f"--port={ports[0]}"], env=env,
+                                      stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL))
+        time.sleep(1.0)
+        procs.append(subprocess.Popen([os.path.join(_REF, "bin", "ps_server"), f"--port={ports[1]}", "--thread_nums=2",
+                                       f"--addr=127.0.0.1:{ports[1]}", f"--s_addr={s_addr}"], env=env,
+                                      stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL))
+        time.sleep(2.0)
+        if any(p.poll() is not None for p in procs):
+            return {"impl": "reference", "unavailable": "a reference server process exited at start-up"}
+        w = subprocess.run([sys.executable, os.path.join(_HERE, "ref_wide_deep_worker.py"), "--ref-path", _REF,
+                            "--s-addr", s_addr, "--steps", str(steps), "--batch", str(batch),
+                            "--torch-threads", str(torch_threads)], env=env, capture_output=True, text=True, timeout=1800)
+        for ln in w.stdout.splitlines():
+            if ln.startswith("{") and "wide_deep_cpu" in ln:
+                return json.loads(ln)
+        tail = [t for t in (w.stderr or w.stdout).strip().splitlines() if "rror" in t][-2:]
+        return {"impl": "reference", "unavailable": f"reference worker exit {w.returncode}: " + " | ".join(tail)[:400]}
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.terminate()
+        for p in procs:
+            try:
+                p.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                p.kill()
