@@ -5,6 +5,7 @@ compression (keeps the top 25 % by magnitude, threshold refreshed every 1000 ste
     torchrun --nproc-per-node N -m kraken_b200.benchmarks.dense_dct [--dct] [--steps 30]
 """
 import argparse
+import re
 
 import numpy as np
 import torch
@@ -23,6 +24,9 @@ def main():
     p.add_argument("--no-overlap", action="store_true",
                    help="step all buckets after the backward pass instead of each as soon as its gradients exist")
     p.add_argument("--graph", action="store_true", help="replay the training step as one CUDA graph (not with --dct)")
+    p.add_argument("--timeline", action="store_true",
+                   help="also print rank 0's per-kernel timeline of one fused dense step (start, duration, kernel), taken "
+                        "with torch.profiler - for diagnosis, never a benchmark number")
     a = p.parse_args()
     world, rank = world_rank()
     kk.initialize("gpu", emitter_type=kk.EmitterType.kDCT if a.dct else kk.EmitterType.kDefault, life_span=1000,
@@ -105,6 +109,20 @@ def main():
                     "dense_step_nvlink_bound_us": round(link_us, 1),
                     "dense_step_hbm_bound_us": round(hbm_us, 1),
                     "dense_step_roofline_fraction": round(max(link_us, hbm_us) / us, 3)})
+    if a.timeline and not a.dct and getattr(eng, "bucket", None) is not None:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                timer.start()          # barrier + synchronize: every rank enters the step together
+                eng.dense_step()
+                torch.cuda.synchronize()
+        if rank == 0:
+            evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "dense_" in e.name),
+                         key=lambda e: e.time_range.start)
+            last = evs[-(len(evs) // 3):]
+            t0 = last[0].time_range.start
+            rec["dense_step_timeline_us"] = [[round(e.time_range.start - t0, 1), round(e.time_range.end - e.time_range.start, 1),
+                                              re.search(r"dense_\w+(<[^>]*>)?", e.name).group(0)] for e in last]
     emit(rec)
     kk.stop()
 
