@@ -73,6 +73,8 @@ def main():
     p.add_argument("--batch", type=int, default=512)
     p.add_argument("--deployment", choices=("inproc", "tcp"), default="inproc")
     p.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    p.add_argument("--async-push", action="store_true",
+                   help="tcp deployment: pushes are applied behind the worker's back (the reference's fire-and-forget mode)")
     a = p.parse_args()
     if a.impl == "reference":
         sys.path.insert(0, ROOT)
@@ -84,7 +86,7 @@ def main():
     try:
         if a.deployment == "tcp":
             s_addr, procs = _start_servers()
-            kk.initialize(f"tcp://{s_addr}", seed=0)
+            kk.initialize(f"tcp://{s_addr}", seed=0, async_push=a.async_push)
         else:
             kk.initialize("cpu", seed=0)
         model = WideAndDeep(26, 13, 8, (256, 128))
@@ -101,7 +103,7 @@ def main():
         dt = time.perf_counter() - t0
         emit({"benchmark": "wide_deep_cpu", "impl": "ours",
               "engine": "cpu, shard and worker in one process" if a.deployment == "inproc" else
-                        "scheduler_server + 1 ps_server + 1 worker as processes, localhost TCP",
+                        "scheduler_server + 1 ps_server + 1 worker as processes, localhost TCP" + (", async pushes" if a.async_push else ""),
               "steps": a.steps, "batch": a.batch, "samples_per_sec": a.steps * a.batch / dt,
               "ms_per_step": dt / a.steps * 1e3, "loss_first10": sum(losses[:10]) / 10,
               "loss_last10": sum(losses[-10:]) / 10, "torch_threads": torch.get_num_threads()})

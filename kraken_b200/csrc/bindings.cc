@@ -433,6 +433,93 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return r.Model();
       });
 
+  // ---------------- message bodies of the socket transport: u32 json_len | json | u32 n | n x (u64 len | tensor)
+  // One allocation and one copy per tensor in each direction (the per-tensor calls below copy four times).
+  m.def("rpc_pack_body", [](const std::string& json, const std::vector<torch::Tensor>& tensors) {
+    std::vector<torch::Tensor> keep;
+    keep.reserve(tensors.size());
+    size_t total = 4 + json.size() + 4;
+    for (auto& t_in : tensors) {
+      torch::Tensor t = t_in.detach();
+      KB_CHECK(!t.is_cuda(), err::kSerializeRequest, "message tensors live on the host");
+      if (t.dim() == 0) t = t.reshape({1});
+      t = t.contiguous();
+      dtype_of(t);  // throws for a dtype the wire format has no code for
+      total += 8 + 1 + 8 + 8 * static_cast<size_t>(t.dim()) + 1 + static_cast<size_t>(t.nbytes());
+      keep.push_back(std::move(t));
+    }
+    KB_CHECK(json.size() <= 0xFFFFFFFFu && keep.size() <= 0xFFFFFFFFu, err::kSerializeRequest, "message too large");
+    py::bytes out = py::reinterpret_steal<py::bytes>(PyBytes_FromStringAndSize(nullptr, static_cast<Py_ssize_t>(total)));
+    KB_CHECK(out.ptr() != nullptr, err::kSerializeRequest, "cannot allocate the message body");
+    char* p = PyBytes_AS_STRING(out.ptr());
+    auto put = [&p](const void* src, size_t n) {
+      std::memcpy(p, src, n);
+      p += n;
+    };
+    const uint32_t jl = static_cast<uint32_t>(json.size()), n = static_cast<uint32_t>(keep.size());
+    put(&jl, 4);
+    put(json.data(), json.size());
+    put(&n, 4);
+    for (auto& t : keep) {
+      const uint64_t nd = static_cast<uint64_t>(t.dim());
+      const uint64_t len = 1 + 8 + 8 * nd + 1 + static_cast<uint64_t>(t.nbytes());
+      const uint8_t layout = static_cast<uint8_t>(Layout::kStride), dt = static_cast<uint8_t>(dtype_of(t));
+      put(&len, 8);
+      put(&layout, 1);
+      put(&nd, 8);
+      for (int64_t d : t.sizes()) put(&d, 8);
+      put(&dt, 1);
+      if (t.nbytes()) put(t.data_ptr(), static_cast<size_t>(t.nbytes()));
+    }
+    return out;
+  });
+  m.def("rpc_unpack_body", [](const std::string& b) {
+    size_t pos = 0;
+    auto need = [&](size_t n) {
+      KB_CHECK(n <= b.size() - pos, err::kDeserializeRequest, "message body is truncated");
+    };
+    auto u32 = [&]() {
+      need(4);
+      uint32_t v;
+      std::memcpy(&v, b.data() + pos, 4);
+      pos += 4;
+      return v;
+    };
+    const uint32_t jl = u32();
+    need(jl);
+    py::bytes json(b.data() + pos, jl);
+    pos += jl;
+    const uint32_t n = u32();
+    py::list tensors;
+    for (uint32_t i = 0; i < n; ++i) {
+      need(8);
+      uint64_t len;
+      std::memcpy(&len, b.data() + pos, 8);
+      pos += 8;
+      need(len);
+      const char* q = b.data() + pos;
+      if (len >= 1 && static_cast<uint8_t>(q[0]) == static_cast<uint8_t>(Layout::kStride)) {
+        // dense: straight from the message into the tensor's storage
+        MemSource one(q + 1, len - 1);
+        Reader rr(&one);
+        std::vector<int64_t> dims = rr.Vec<int64_t>();
+        const DType dt = static_cast<DType>(rr.Pod<uint8_t>());
+        for (int64_t d : dims) KB_CHECK(d >= 0, err::kDeserializeRequest, "negative tensor extent");
+        torch::Tensor t = torch::empty(dims, torch::TensorOptions().dtype(scalar_of(dt)));
+        KB_CHECK(1 + one.offset() + static_cast<size_t>(t.nbytes()) == len, err::kDeserializeRequest,
+                 "tensor payload does not match its shape");
+        if (t.nbytes()) std::memcpy(t.data_ptr(), q + 1 + one.offset(), static_cast<size_t>(t.nbytes()));
+        tensors.append(t);
+      } else {
+        MemSource one(q, len);
+        Reader rr(&one);
+        tensors.append(from_host(rr.Tensor()));
+      }
+      pos += len;
+    }
+    return py::make_tuple(json, tensors);
+  });
+
   // ---------------- serializer (tests, socket transport)
   m.def("serialize_tensor", [](const torch::Tensor& t) {
     MemSink s;

@@ -71,27 +71,13 @@ class RpcError(RuntimeError):
 
 
 def pack_body(meta: dict, tensors: Sequence[torch.Tensor] = ()) -> bytes:
-    j = json.dumps(meta).encode()
-    parts = [struct.pack("<I", len(j)), j, struct.pack("<I", len(tensors))]
-    for t in tensors:
-        b = C.serialize_tensor(t)
-        parts += [struct.pack("<Q", len(b)), b]
-    return b"".join(parts)
+    """u32 json_len | json | u32 n | n x (u64 len | tensor in the framework's binary tensor encoding)."""
+    return C.rpc_pack_body(json.dumps(meta).encode(), list(tensors))
 
 
 def unpack_body(body: bytes) -> Tuple[dict, List[torch.Tensor]]:
-    (jl,) = struct.unpack_from("<I", body, 0)
-    meta = json.loads(body[4:4 + jl].decode())
-    pos = 4 + jl
-    (n,) = struct.unpack_from("<I", body, pos)
-    pos += 4
-    tensors = []
-    for _ in range(n):
-        (bl,) = struct.unpack_from("<Q", body, pos)
-        pos += 8
-        tensors.append(C.deserialize_tensor(body[pos:pos + bl]))
-        pos += bl
-    return meta, tensors
+    j, tensors = C.rpc_unpack_body(body)
+    return json.loads(j), tensors
 
 
 COMPRESS_NONE, COMPRESS_SNAPPY = 0, 1   # CompressType::kNo / kSnappy, kraken/rpc/protocol.h:7-10

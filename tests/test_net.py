@@ -128,3 +128,32 @@ def test_stop_ends_connections_and_a_lost_peer_is_reported():
     assert status == 25, (status, msg)               # kConnection, not a hang until the timeout
     with pytest.raises(C.KrakenError):
         C.NetConnecter("127.0.0.1", st.port, 500, 0)  # nobody listens there any more
+
+
+def test_message_bodies_pack_and_unpack_with_one_copy_per_tensor():
+    """Body = u32 json_len | json | u32 n | n x (u64 len | tensor encoding).  The packer must write exactly what
+    the per-tensor serializer writes (the format of kraken/common/serialize.h: layout byte, dims, dtype byte,
+    payload), take non-contiguous and empty tensors, and the unpacker must reject truncated bodies."""
+    import json
+
+    import torch
+
+    from kraken_b200.runtime import rpc
+    ts = [torch.arange(12, dtype=torch.int64).view(3, 4), torch.randn(5, 8), torch.zeros(0, 4),
+          torch.tensor([1, 2, 3], dtype=torch.int32), torch.randn(4, 6)[:, ::2], torch.randn(7).double()]
+    meta = {"table_id": 3, "ids": [1, 2], "name": "x"}
+    j = json.dumps(meta).encode()
+    want = struct.pack("<I", len(j)) + j + struct.pack("<I", len(ts))
+    for t in ts:
+        b = C.serialize_tensor(t)
+        want += struct.pack("<Q", len(b)) + b
+    body = rpc.pack_body(meta, ts)
+    assert body == want
+    got_meta, got = rpc.unpack_body(body)
+    assert got_meta == meta and len(got) == len(ts)
+    for a, b in zip(ts, got):
+        assert a.dtype == b.dtype and torch.equal(a, b)
+    assert rpc.unpack_body(rpc.pack_body({}, [])) == ({}, [])
+    for bad in (body[:-1], body[:9], b"\x09\x00\x00\x00{}", body[:len(j) + 8] + b"\xff" * 8):
+        with pytest.raises(C.KrakenError):
+            rpc.unpack_body(bad)
