@@ -14,7 +14,7 @@ toolchain file to use what is there, and the documented pip command installs the
 The reference's setup.py installs only the Python extension; the two server executables and the
 reference's own test binary are copied from its build tree into baseline/_ref/bin afterwards.
 
-Usage: python baseline/build_reference.py [--reference /root/reference] [--keep-build]
+Usage: python baseline/build_reference.py [--reference <checkout of the reference>] [--keep-build]
 """
 from __future__ import annotations
 
@@ -52,7 +52,8 @@ def tree_hash(root: str) -> str:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("KRAKEN_REFERENCE_SRC", "/root/reference"),
+                    help="checkout of the reference (read only; copied before the build)")
     ap.add_argument("--work", default="/tmp/kraken_reference_build")
     ap.add_argument("--keep-build", action="store_true")
     args = ap.parse_args()

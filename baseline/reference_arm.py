@@ -17,6 +17,7 @@ import os
 import socket
 import subprocess
 import sys
+import tempfile
 import time
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -63,7 +64,7 @@ def run(args) -> None:
     ports = _free_ports(1 + n_ps)
     s_addr = f"127.0.0.1:{ports[0]}"
     procs = []
-    logdir = os.path.join(_HERE, "..", "gpurun_out")
+    logdir = os.environ.get("KRAKEN_REF_LOG_DIR") or os.path.join(tempfile.gettempdir(), "kraken_reference_logs")
     os.makedirs(logdir, exist_ok=True)
     logs = []
 
@@ -135,7 +136,7 @@ def run(args) -> None:
                                       "processes + scheduler over localhost ZeroMQ, CPU only",
                        "why_micro_batches": "the reference's 5000 ms RPC timeout rejects a pull for a whole 65536-sample batch",
                        "device": "host CPU (the reference has no GPU code)", "torch_threads_per_worker": lines[0].get("torch_threads"),
-                       "build": "offline, dependency stand-ins listed in BASELINE.md; reference sources unmodified"},
+                       "build": "offline against the dependency stand-ins under baseline/standins; reference sources unmodified"},
             # the reference's inputs never leave the host, so the end-to-end figure is the same wall-clock measurement
             "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "ms_per_step": ms},

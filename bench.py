@@ -240,7 +240,7 @@ def run_ours(args):
             "precision": {"tables_and_row_optimizer": "fp32", "fm_interaction_logit_loss": "fp32",
                           "mlp_gemm_operands": "bf16, fp32 accumulation (TMEM), fp32 master weights",
                           "mlp_input_gradient_dx": "bf16", "weight_gradients_and_dense_optimizer": "fp32",
-                          "parity_with_fp32": "kraken_b200/benchmarks/precision_parity.py (numbers in BASELINE.md)"},
+                          "parity_with_fp32": "python -m kraken_b200.benchmarks.precision_parity prints loss and AUC of both"},
             "impl": "ours" if args.exchange == "fused" else "ours-nccl-baseline",
             "config": {"model": "DeepFM 26x1e7 dim16 + MLP 400-400-400-1, Adam lr 1e-3",
                        "tables": "dim-16 embedding + dim-1 first-order" if args.two_tables else
