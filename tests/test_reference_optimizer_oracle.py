@@ -1,0 +1,103 @@
+"""The server-side optimizers against the reference itself: the same pushes go to the UNMODIFIED reference
+(one cluster per configuration, baseline/ref_optim_worker.py) and to this framework's CPU shard, whose
+element-wise math (csrc/core/optim_math.h) is the one the CUDA kernels compile too.  Needs the offline
+reference build; skipped where that is absent.  Reference math: kraken/ps/optim/{sgd,adagrad,adam,rmsprop}.cc."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from kraken_b200._native import C
+from test_reference_checkpoint_compat import REF, ROOT, ReferenceCluster
+
+pytestmark = pytest.mark.skipif(
+    not (os.path.exists(os.path.join(REF, "bin", "ps_server")) and os.path.exists(os.path.join(REF, "kraken_native.so"))),
+    reason="the reference is not built here (python baseline/build_reference.py)")
+
+CASES = [
+    ("SGD", {}),
+    ("SGD", {"momentum": "0.9", "dampening": "0.1", "weight_decay": "0.01"}),
+    ("SGD", {"momentum": "0.9", "nesterov": "true"}),
+    ("Adagrad", {"weight_decay": "0.01", "eps": "1e-6"}),
+    ("Adam", {}),
+    ("Adam", {"amsgrad": "true", "weight_decay": "0.02", "beta1": "0.8", "beta2": "0.99"}),
+    ("RMSprop", {}),
+    ("RMSprop", {"centered": "true", "momentum": "0.9", "weight_decay": "0.01", "alpha": "0.95"}),
+]
+
+
+@pytest.mark.parametrize("optim,conf", CASES, ids=[f"{o}-{'-'.join(sorted(c)) or 'default'}" for o, c in CASES])
+def test_optimizer_follows_the_reference_step_by_step(optim, conf, tmp_path):
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import ref_optim_worker as w
+    finally:
+        sys.path.pop(0)
+    cluster = ReferenceCluster(str(tmp_path / "scratch"), n_ps=1)
+    try:
+        import subprocess
+        out = str(tmp_path / "oracle.npz")
+        run = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "ref_optim_worker.py"), "--ref-path", REF,
+                              "--s-addr", cluster.s_addr, "--optim", optim, "--conf", json.dumps(conf), "--out", out],
+                             env=cluster.env, capture_output=True, text=True, timeout=300)
+        assert run.returncode == 0, (run.stdout + run.stderr)[-2000:]
+        want = dict(np.load(out))
+    finally:
+        cluster.stop()
+
+    shard = C.CpuShard(0)
+    shard.init_model("oracle", getattr(C.OptimType, "k" + optim), conf)
+    shard.create_sparse_table(0, "e", w.DIM, C.InitializerType.kConstant, {"value": "0.5"})
+    shard.create_dense_table(1, "w", torch.linspace(-1, 1, 15).view(3, 5))
+    ids, sparse, dense, lrs = w.inputs()
+    probe = torch.arange(w.ROWS, dtype=torch.int64) * 11
+    shard.pull_sparse(0, probe)
+    for k in range(w.STEPS):
+        uniq, inv = C.cpu_dedup(ids[k])
+        shard.push_sparse(0, uniq, C.cpu_segment_sum(sparse[k], inv, uniq.numel()), lrs[k])
+        shard.push_dense(1, dense[k].reshape(-1), lrs[k])
+        got_rows = shard.pull_sparse(0, probe).numpy()
+        got_dense = shard.pull_dense(1).numpy().reshape(3, 5)
+        assert np.allclose(got_rows, want[f"rows_{k}"], rtol=2e-5, atol=2e-6), (optim, conf, k)
+        assert np.allclose(got_dense, want[f"dense_{k}"], rtol=2e-5, atol=2e-6), (optim, conf, k)
+
+
+def test_jagged_pooling_follows_the_reference(tmp_path):
+    """Bag pooling against the reference's own CPU ops (kraken/pytorch/py/jagged_ops.cc): sum and mean forward
+    with an empty bag and a patch value, mean backward.  The reference's sum backward writes only the first
+    row of every bag and leaves the rest uninitialised (jagged_ops.cc:147-200); here every row of a bag gets the
+    bag's gradient, so only those first rows are compared."""
+    import subprocess
+    out = str(tmp_path / "jagged.npz")
+    code = f"""
+import sys, numpy as np, torch
+sys.path.insert(0, {REF!r})
+import kraken_native as kn
+g = torch.Generator().manual_seed(3)
+values = torch.randn(23, 6, generator=g)
+offsets = torch.tensor([0, 4, 4, 9, 10, 23], dtype=torch.int64)
+grads = torch.randn(5, 6, generator=g)
+np.savez({out!r}, sum_f=kn.jagged_sum_forward(values, offsets, -2.5).numpy(),
+         mean_f=kn.jagged_mean_forward(values, offsets, 0.25).numpy(),
+         mean_b=kn.jagged_mean_backward(offsets, grads).numpy(),
+         sum_b=kn.jagged_sum_backward(offsets, grads).numpy())
+"""
+    env = dict(os.environ, LD_LIBRARY_PATH=os.path.join(REF, "lib") + os.pathsep + os.environ.get("LD_LIBRARY_PATH", ""))
+    env.pop("PYTHONPATH", None)
+    run = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0, (run.stdout + run.stderr)[-2000:]
+    want = dict(np.load(out))
+    g = torch.Generator().manual_seed(3)
+    values = torch.randn(23, 6, generator=g)
+    offsets = torch.tensor([0, 4, 4, 9, 10, 23], dtype=torch.int64)
+    grads = torch.randn(5, 6, generator=g)
+    assert np.allclose(C.jagged_sum_forward(values, offsets, -2.5).numpy(), want["sum_f"], atol=1e-6)
+    assert np.allclose(C.jagged_mean_forward(values, offsets, 0.25).numpy(), want["mean_f"], atol=1e-6)
+    assert np.allclose(C.jagged_mean_backward(offsets, grads).numpy(), want["mean_b"], atol=1e-6)
+    ours = C.jagged_sum_backward(offsets, grads).numpy()
+    firsts = [0, 4, 9, 10]                      # first row of every non-empty bag
+    assert np.allclose(ours[firsts], want["sum_b"][firsts], atol=1e-6)
+    assert np.allclose(ours[5], grads[2].numpy(), atol=1e-6)    # a later row of bag 2 carries the bag's gradient too
