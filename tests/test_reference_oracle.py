@@ -1,4 +1,4 @@
-"""The server-side optimizers against the reference itself: the same pushes go to the UNMODIFIED reference
+"""Optimizers, bag pooling and DCT compression against the reference itself.  Optimizers: the same pushes go to the UNMODIFIED reference
 (one cluster per configuration, baseline/ref_optim_worker.py) and to this framework's CPU shard, whose
 element-wise math (csrc/core/optim_math.h) is the one the CUDA kernels compile too.  Needs the offline
 reference build; skipped where that is absent.  Reference math: kraken/ps/optim/{sgd,adagrad,adam,rmsprop}.cc."""
@@ -101,3 +101,44 @@ np.savez({out!r}, sum_f=kn.jagged_sum_forward(values, offsets, -2.5).numpy(),
     firsts = [0, 4, 9, 10]                      # first row of every non-empty bag
     assert np.allclose(ours[firsts], want["sum_b"][firsts], atol=1e-6)
     assert np.allclose(ours[5], grads[2].numpy(), atol=1e-6)    # a later row of bag 2 carries the bag's gradient too
+
+
+def test_dct_compression_follows_the_reference(tmp_path):
+    """Dynamic communication thresholding against the reference's own emitter (kraken/worker/dct_emitter.cc:16-43):
+    the same 8 gradients through both, life span 3, eta 0.75, SGD on the server.  After every push the table
+    must hold the same values - which entries crossed, what stayed behind as error feedback, when the threshold
+    was refreshed - for a table above the 256-element limit and one below it."""
+    import subprocess
+
+    import kraken_b200.pytorch as kk
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import ref_dct_worker as w
+    finally:
+        sys.path.pop(0)
+    cluster = ReferenceCluster(str(tmp_path / "scratch"), n_ps=1)
+    try:
+        out = str(tmp_path / "dct.npz")
+        run = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "ref_dct_worker.py"), "--ref-path", REF,
+                              "--s-addr", cluster.s_addr, "--out", out], env=cluster.env, capture_output=True, text=True,
+                             timeout=300)
+        assert run.returncode == 0, (run.stdout + run.stderr)[-2000:]
+        want = dict(np.load(out))
+    finally:
+        cluster.stop()
+
+    kk.initialize("cpu", kk.EmitterType.kDCT, w.LIFE_SPAN, w.ETA)
+    try:
+        kk.init_model("dct", kk.OptimType.kSGD, {})
+        kk.update_lr(w.LR)
+        tb = kk.register_dense_table("big", torch.zeros(*w.BIG))
+        ts = kk.register_dense_table("small", torch.zeros(*w.SMALL))
+        for k, (gb, gs) in enumerate(w.inputs()):
+            kk.push_dense_table(tb, gb)
+            kk.push_dense_table(ts, gs)
+            assert np.allclose(kk.pull_dense_table(tb).numpy(), want[f"big_{k}"], atol=1e-6), k
+            assert np.allclose(kk.pull_dense_table(ts).numpy(), want[f"small_{k}"], atol=1e-6), k
+        moved = np.count_nonzero(want["big_0"])
+        assert 0 < moved < 0.3 * 1200        # the first push really was sparse: about (1 - eta) of the entries
+    finally:
+        kk.stop()
