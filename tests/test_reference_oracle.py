@@ -142,3 +142,58 @@ def test_dct_compression_follows_the_reference(tmp_path):
         assert 0 < moved < 0.3 * 1200        # the first push really was sparse: about (1 - eta) of the entries
     finally:
         kk.stop()
+
+
+def test_row_initialisers_draw_from_the_reference_distributions(tmp_path):
+    """The reference seeds its random initialisers from std::random_device (kraken/t/math.cc:455-517), so rows
+    cannot be compared one by one; 20 000 new rows of width 16 per initialiser are compared by mean, spread and
+    range instead - in particular the Xavier bounds, which depend on how fan-in and fan-out are read off a row."""
+    import subprocess
+
+    import kraken_b200.pytorch as kk
+    specs = [("constant", "kConstant", {"value": "0.75"}), ("uniform", "kUniform", {"lower": "-0.5", "upper": "1.5"}),
+             ("normal", "kNormal", {"mean": "0.3", "stddev": "0.2"}), ("xu", "kXavierUniform", {"gain": "2.0"}),
+             ("xn", "kXavierNormal", {"gain": "0.5"})]
+    out = str(tmp_path / "init.npz")
+    code = f"""
+import sys, numpy as np, torch
+sys.path.insert(0, {REF!r})
+import kraken.pytorch as kk
+kk.initialize(sys.argv[1])
+kk.init_model("init", kk.OptimType.kSGD, {{}})
+res = {{}}
+for name, kind, conf in {specs!r}:
+    t = kk.register_sparse_table(name, 16, torch.float32, getattr(kk.InitializerType, kind), conf)
+    res[name] = kk.pull_sparse_table(t, torch.arange(20000, dtype=torch.int64)).numpy()
+np.savez({out!r}, **res)
+kk.stop()
+"""
+    cluster = ReferenceCluster(str(tmp_path / "scratch"), n_ps=1)
+    try:
+        run = subprocess.run([sys.executable, "-c", code, cluster.s_addr], env=cluster.env, capture_output=True, text=True,
+                             timeout=300)
+        assert run.returncode == 0, (run.stdout + run.stderr)[-2000:]
+        want = dict(np.load(out))
+    finally:
+        cluster.stop()
+
+    kk.initialize("cpu", seed=4)
+    try:
+        kk.init_model("init", kk.OptimType.kSGD, {})
+        for name, kind, conf in specs:
+            t = kk.register_sparse_table(name, 16, torch.float32, getattr(kk.InitializerType, kind), conf)
+            got = kk.pull_sparse_table(t, torch.arange(20000)).numpy()
+            ref = want[name]
+            assert got.shape == ref.shape
+            if name == "constant":
+                assert np.array_equal(got, ref)
+                continue
+            n = got.size
+            tol = 6 * ref.std() / np.sqrt(n)                   # six standard errors of a mean of n draws
+            assert abs(got.mean() - ref.mean()) < 2 * tol, (name, got.mean(), ref.mean())
+            assert abs(got.std() / ref.std() - 1) < 0.02, (name, got.std(), ref.std())
+            if name in ("uniform", "xu"):                       # bounded: the same support
+                assert abs(got.min() - ref.min()) < 0.01 * (ref.max() - ref.min()), (name, got.min(), ref.min())
+                assert abs(got.max() - ref.max()) < 0.01 * (ref.max() - ref.min()), (name, got.max(), ref.max())
+    finally:
+        kk.stop()
