@@ -197,3 +197,31 @@ kk.stop()
                 assert abs(got.max() - ref.max()) < 0.01 * (ref.max() - ref.min()), (name, got.max(), ref.max())
     finally:
         kk.stop()
+
+
+def test_the_same_script_trains_the_same_under_both_packages(tmp_path):
+    """baseline/dropin_train.py is written against the reference's public API and run twice: once with
+    ``kraken.pytorch`` = the unmodified reference (scheduler + server processes), once with ``kraken.pytorch`` =
+    this framework behind ``install_alias()``.  Same data, same torch seed, Adam on the servers: the loss of
+    every one of the 25 steps and the final dense layers must agree."""
+    import subprocess
+    script = os.path.join(ROOT, "baseline", "dropin_train.py")
+    cluster = ReferenceCluster(str(tmp_path / "scratch"), n_ps=1)
+    try:
+        ref_out = str(tmp_path / "ref.npz")
+        run = subprocess.run([sys.executable, script, "--impl", "reference", "--ref-path", REF, "--s-addr", cluster.s_addr,
+                              "--out", ref_out], env=cluster.env, capture_output=True, text=True, timeout=300)
+        assert run.returncode == 0, (run.stdout + run.stderr)[-2000:]
+    finally:
+        cluster.stop()
+    our_out = str(tmp_path / "ours.npz")
+    env = dict(os.environ, KRAKEN_B200_NO_BUILD="1", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    run = subprocess.run([sys.executable, script, "--impl", "ours", "--s-addr", "cpu", "--out", our_out], env=env,
+                         capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, (run.stdout + run.stderr)[-2000:]
+    ref, ours = dict(np.load(ref_out)), dict(np.load(our_out))
+    assert ref["losses"].shape == ours["losses"].shape == (25,)
+    assert ref["losses"][0] > ref["losses"][-1]                  # it did train
+    assert np.allclose(ours["losses"], ref["losses"], rtol=1e-4, atol=1e-5), (ours["losses"], ref["losses"])
+    for k in range(6):
+        assert np.allclose(ours[f"param_{k}"], ref[f"param_{k}"], rtol=1e-3, atol=1e-5), k
