@@ -38,7 +38,10 @@ def _free_port() -> int:
 def _start_servers():
     """scheduler_server + one ps_server as child processes; returns (scheduler address, processes)."""
     from kraken_b200.runtime.rpc import Connecter, Rpc
-    env = dict(os.environ, KRAKEN_B200_NO_BUILD="1", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    # the servers' work per request is small: two threads each, so that they do not fight the worker's
+    # math threads for the same cores (the worker keeps two cores free for them, see main)
+    env = dict(os.environ, KRAKEN_B200_NO_BUILD="1", OMP_NUM_THREADS="2",
+               PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     sp, pp = _free_port(), _free_port()
     procs = [subprocess.Popen([sys.executable, "-m", "kraken_b200.launch.scheduler_server", "--port", str(sp)], env=env)]
 
@@ -73,6 +76,9 @@ def main():
     p.add_argument("--batch", type=int, default=512)
     p.add_argument("--deployment", choices=("inproc", "tcp"), default="inproc")
     p.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    p.add_argument("--combine", action="store_true",
+                   help="wide and deep tables through one CombineEmbedding (one request round per step and direction, as "
+                        "the reference arm's model does)")
     p.add_argument("--async-push", action="store_true",
                    help="tcp deployment: pushes are applied behind the worker's back (the reference's fire-and-forget mode)")
     a = p.parse_args()
@@ -86,10 +92,12 @@ def main():
     try:
         if a.deployment == "tcp":
             s_addr, procs = _start_servers()
+            if "OMP_NUM_THREADS" not in os.environ:
+                torch.set_num_threads(max(1, (os.cpu_count() or 4) - 2))   # worker and servers share this host
             kk.initialize(f"tcp://{s_addr}", seed=0, async_push=a.async_push)
         else:
             kk.initialize("cpu", seed=0)
-        model = WideAndDeep(26, 13, 8, (256, 128))
+        model = WideAndDeep(26, 13, 8, (256, 128), combine=a.combine)
         opt = kk.Optimizer("wide_deep", model.named_parameters(), 0.01, kk.Adagrad(initial_accumulator_value=0.1))
         data = ClickDataset(26, 13, 100_000, 1.05, seed=0)
         batches = [data.batch(a.batch) for _ in range(a.steps)]

@@ -10,6 +10,7 @@
 #include <torch/extension.h>
 
 #include <cstring>
+#include <map>
 
 #include "core/checkpoint.h"
 #include "core/hash.h"
@@ -953,6 +954,48 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
 
   // ---------------- CPU client-side ops
+  // Worker side of the TCP deployment: which ring node owns every (table, id), grouped by node.  Returns
+  // (nodes ascending, positions of the ids grouped in that node order, how many per node); with one node
+  // the positions are simply 0..n-1.  hash = Mix64(table) ^ Mix64(id), owner = first virtual node at or after
+  // it on the ring (kraken/common/router.cc:262-277, kraken/worker/emitter.cc:123-183).
+  m.def("route_partition", [](const torch::Tensor& ids, uint64_t table_id, const torch::Tensor& vhash,
+                              const torch::Tensor& vnode) {
+    need_cpu(ids, "ids", torch::kInt64);
+    TORCH_CHECK(vhash.is_contiguous() && vnode.is_contiguous() && vhash.numel() == vnode.numel() && vhash.numel() > 0 &&
+                    vhash.element_size() == 8 && vnode.scalar_type() == torch::kInt64,
+                "route_partition: the ring is two equally long arrays of 64-bit numbers");
+    const int64_t n = ids.numel(), v = vhash.numel();
+    const uint64_t* id = reinterpret_cast<const uint64_t*>(ids.data_ptr<int64_t>());
+    const uint64_t* vh = reinterpret_cast<const uint64_t*>(vhash.data_ptr());
+    const int64_t* vn = vnode.data_ptr<int64_t>();
+    const uint64_t salt = Mix64(table_id);
+    std::vector<int64_t> owner(static_cast<size_t>(n));
+    std::map<int64_t, int64_t> count;
+    for (int64_t i = 0; i < n; ++i) {
+      const uint64_t h = salt ^ Mix64(id[i]);
+      int64_t k = std::lower_bound(vh, vh + v, h) - vh;
+      if (k == v) k = 0;
+      owner[static_cast<size_t>(i)] = vn[k];
+      ++count[vn[k]];
+    }
+    std::vector<int64_t> nodes, counts;
+    std::map<int64_t, int64_t> cursor;
+    int64_t at = 0;
+    for (auto& kv : count) {
+      nodes.push_back(kv.first);
+      counts.push_back(kv.second);
+      cursor[kv.first] = at;
+      at += kv.second;
+    }
+    torch::Tensor order = torch::empty({n}, torch::kInt64);
+    int64_t* o = order.data_ptr<int64_t>();
+    if (nodes.size() == 1) {
+      for (int64_t i = 0; i < n; ++i) o[i] = i;
+    } else {
+      for (int64_t i = 0; i < n; ++i) o[cursor[owner[static_cast<size_t>(i)]]++] = i;
+    }
+    return py::make_tuple(nodes, order, counts);
+  });
   m.def("cpu_dedup", [](const torch::Tensor& ids) {
     torch::Tensor i = ids.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
     std::vector<uint64_t> uniq;

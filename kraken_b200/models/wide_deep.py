@@ -23,19 +23,31 @@ from .mlp import MLP
 
 class WideAndDeep(torch.nn.Module):
     def __init__(self, num_fields: int = 26, num_dense: int = 13, dim: int = 8, hidden: Sequence[int] = (256, 128),
-                 name: str = "wide_deep"):
+                 name: str = "wide_deep", combine: bool = False):
+        """``combine``: both tables go through one ``CombineEmbedding`` - one request round per step and direction
+        instead of two (what counts on the TCP deployment, where a round is a message to every server)."""
         super().__init__()
         self.num_fields, self.num_dense, self.dim = num_fields, num_dense, dim
-        self.wide = kk.Embedding(1, initializer=kk.ConstantInitializer(0.0), name=f"{name}.wide")
-        self.deep = kk.Embedding(dim, initializer=kk.NormalInitializer(0.0, 0.05), name=f"{name}.deep")
+        if combine:
+            self.both = kk.CombineEmbedding([1, dim], initializers=[kk.ConstantInitializer(0.0),
+                                                                    kk.NormalInitializer(0.0, 0.05)],
+                                            names=[f"{name}.wide", f"{name}.deep"])
+        else:
+            self.both = None
+            self.wide = kk.Embedding(1, initializer=kk.ConstantInitializer(0.0), name=f"{name}.wide")
+            self.deep = kk.Embedding(dim, initializer=kk.NormalInitializer(0.0, 0.05), name=f"{name}.deep")
         width = num_fields * dim + num_dense
         self.mlp_in = (width + 7) // 8 * 8
         self.mlp = MLP(self.mlp_in, list(hidden) + [1])
         self.bias = torch.nn.Parameter(torch.zeros(1))
 
     def forward(self, dense: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
-        wide = self.wide(ids).sum(dim=(1, 2))
-        e = self.deep(ids)
+        if self.both is not None:
+            w, e = self.both([ids, ids])
+            wide = w.sum(dim=(1, 2))
+        else:
+            wide = self.wide(ids).sum(dim=(1, 2))
+            e = self.deep(ids)
         dense = dense.to(e.device)
         parts = [e.flatten(1), dense]
         if self.mlp_in > e.shape[1] * e.shape[2] + dense.shape[1]:

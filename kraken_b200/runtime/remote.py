@@ -718,8 +718,10 @@ class RemoteEngine(Engine):
                 if int(nid) not in self.ps:
                     self.ps[int(nid)] = Connecter(addr, compress=self.compress)
             vn = router.vnodes()
-            self._ring = (router, meta["version"], np.array([v[0] for v in vn], dtype=np.uint64),
-                          np.array([v[1] for v in vn], dtype=np.int64))
+            vhash = np.array([v[0] for v in vn], dtype=np.uint64)
+            vnode = np.array([v[1] for v in vn], dtype=np.int64)
+            self._ring = (router, meta["version"], vhash, vnode,
+                          torch.from_numpy(vhash.view(np.int64).copy()), torch.from_numpy(vnode.copy()))
 
     @property
     def router(self):
@@ -727,8 +729,8 @@ class RemoteEngine(Engine):
 
     @router.setter
     def router(self, r) -> None:   # the base class installs a placeholder ring before the first fetch
-        old = getattr(self, "_ring", (None, 0, np.zeros(0, np.uint64), np.zeros(0, np.int64)))
-        self._ring = (r, old[1], old[2], old[3])
+        old = getattr(self, "_ring", (None, 0, np.zeros(0, np.uint64), np.zeros(0, np.int64), None, None))
+        self._ring = (r,) + tuple(old[1:])
 
     @property
     def version(self) -> int:
@@ -737,11 +739,11 @@ class RemoteEngine(Engine):
     @version.setter
     def version(self, v: int) -> None:   # tests age the ring with it
         r = self._ring
-        self._ring = (r[0], int(v), r[2], r[3])
+        self._ring = (r[0], int(v)) + tuple(r[2:])
 
     @staticmethod
     def _owners(ring, table_id: int, ids: torch.Tensor) -> np.ndarray:
-        _, _, vhash, vnode = ring
+        vhash, vnode = ring[2], ring[3]
         hv = mix64(ids.numpy().view(np.uint64)) ^ np.uint64(C.mix64(table_id))
         idx = np.searchsorted(vhash, hv, side="left")
         idx[idx == len(vhash)] = 0
@@ -783,22 +785,26 @@ class RemoteEngine(Engine):
         # every part carries the version of the ring it was partitioned on: a refetch triggered by one refused part
         # (or by another thread) must not let the remaining parts of the OLD partition pass a server's version check
         ring = self._ring
-        owners = self._owners(ring, table_id, ids)
         version = ring[1]
-        for node in np.unique(owners):
-            sel = torch.from_numpy(np.nonzero(owners == node)[0])
-            tensors = [ids[sel]] + ([payload[sel]] if payload is not None else [])
+        nodes, order, counts = C.route_partition(ids, table_id, ring[4], ring[5])
+        at = 0
+        for node, cnt in zip(nodes, counts):
+            # one server holds everything (a single-server deployment, or a small request): no index copies
+            sel = None if len(nodes) == 1 else order[at:at + cnt]
+            at += cnt
+            part_ids = ids if sel is None else ids[sel]
+            part_payload = None if payload is None else (payload if sel is None else payload[sel])
             try:
                 _, ts = self.ps[int(node)].call(rpc, {**meta, "table_id": table_id, "router_version": version},
-                                                tensors)
+                                                [part_ids] + ([part_payload] if part_payload is not None else []))
             except RpcError as e:
                 if e.code not in self.RETRY_CODES:
                     raise
                 self._backoff(attempt, e.code)
-                self._call_sparse(rpc, table_id, meta, ids[sel], payload[sel] if payload is not None else None,
-                                  lambda pos, ts, sel=sel: done(sel[pos], ts), attempt + 1)
+                self._call_sparse(rpc, table_id, meta, part_ids, part_payload,
+                                  (lambda pos, ts, sel=sel: done(pos if sel is None else sel[pos], ts)), attempt + 1)
                 continue
-            done(sel, ts)
+            done(slice(None) if sel is None else sel, ts)
 
     # registry: the scheduler owns it
     def init_model(self, model_name, optim_type, optim_conf=None):
@@ -867,13 +873,15 @@ class RemoteEngine(Engine):
         info = self._table(table_id, "sparse")
         idx = indices.detach().to("cpu").to(torch.int64).contiguous()
         uniq, inv = C.cpu_dedup(idx.reshape(-1))
-        rows = torch.empty((uniq.numel(), info.dimension), dtype=torch.float32)
-
-        def put(pos, ts):
-            rows[pos] = ts[0]
-
+        parts = []
         self._reap_pushes()
-        self._call_sparse(Rpc.PULL_SPARSE, table_id, {}, uniq, None, put)
+        self._call_sparse(Rpc.PULL_SPARSE, table_id, {}, uniq, None, lambda pos, ts: parts.append((pos, ts[0])))
+        if len(parts) == 1 and isinstance(parts[0][0], slice):
+            rows = parts[0][1]            # one server answered for every id: its reply is the result
+        else:
+            rows = torch.empty((uniq.numel(), info.dimension), dtype=torch.float32)
+            for pos, part in parts:
+                rows[pos] = part
         return rows[inv].view(*idx.shape, info.dimension)
 
     def push_sparse_table(self, table_id, indices, grad):
