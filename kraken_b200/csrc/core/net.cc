@@ -9,10 +9,13 @@
 #include <sys/uio.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cerrno>
 #include <chrono>
 #include <cstring>
+#include <new>
 #include <set>
+#include <stdexcept>
 
 #include "snappy_codec.h"
 #include "types.h"
@@ -116,16 +119,27 @@ RecvStatus RecvFrame(int fd, int timeout_ms, Frame* out) {
   out->stamp = GetLE(head + 4, 8);
   out->code = static_cast<int32_t>(static_cast<uint32_t>(GetLE(head + 12, 4)));
   out->compress = static_cast<uint8_t>(head[16]);
-  std::string raw(n, '\0');
-  if (n) {
-    st = ReadAll(fd, &raw[0], n, timeout_ms);
-    if (st != RecvStatus::kOk) return st;
-  }
-  if (out->compress == kCompressNone) {
-    out->body.swap(raw);
-  } else if (out->compress == kCompressSnappy) {
-    if (!snappy_codec::Uncompress(raw.data(), raw.size(), &out->body)) return RecvStatus::kBadFrame;
-  } else {
+  if (out->compress != kCompressNone && out->compress != kCompressSnappy) return RecvStatus::kBadFrame;
+  try {
+    // the length comes off the wire: a peer that announces more than this host can hold is a broken peer,
+    // not a reason to die
+    // and the buffer grows with the bytes that really arrive (4 MiB at a time), not with the announcement
+    std::string raw;
+    for (size_t got = 0; got < n;) {
+      const size_t step = std::min<size_t>(n - got, 4u << 20);
+      raw.resize(got + step);
+      st = ReadAll(fd, &raw[got], step, timeout_ms);
+      if (st != RecvStatus::kOk) return st;
+      got += step;
+    }
+    if (out->compress == kCompressNone) {
+      out->body.swap(raw);
+    } else if (!snappy_codec::Uncompress(raw.data(), raw.size(), &out->body)) {
+      return RecvStatus::kBadFrame;
+    }
+  } catch (const std::bad_alloc&) {
+    return RecvStatus::kBadFrame;
+  } catch (const std::length_error&) {
     return RecvStatus::kBadFrame;
   }
   return RecvStatus::kOk;
@@ -244,17 +258,22 @@ void Station::Start() {
       }
       st->conns.insert(c);
       st->threads.emplace_back([st, c] {
-        Frame req;
-        while (RecvFrame(c, -1, &req) == RecvStatus::kOk) {
-          std::pair<int32_t, std::string> reply;
-          try {
-            reply = st->handler(static_cast<uint32_t>(req.code), req.body);
-          } catch (const KrakenError& e) {
-            reply = {e.code, e.what()};
-          } catch (const std::exception& e) {  // a failing handler must not take the server down
-            reply = {err::kUnknown, e.what()};
+        try {
+          Frame req;
+          while (RecvFrame(c, -1, &req) == RecvStatus::kOk) {
+            std::pair<int32_t, std::string> reply;
+            try {
+              reply = st->handler(static_cast<uint32_t>(req.code), req.body);
+            } catch (const KrakenError& e) {
+              reply = {e.code, e.what()};
+            } catch (const std::exception& e) {  // a failing handler must not take the server down
+              reply = {err::kUnknown, e.what()};
+            }
+            if (!SendFrame(c, req.stamp, reply.first, reply.second, reply.first == 0 ? req.compress : kCompressNone))
+              break;
           }
-          if (!SendFrame(c, req.stamp, reply.first, reply.second, reply.first == 0 ? req.compress : kCompressNone)) break;
+        } catch (...) {
+          // nothing may leave a connection's thread: the connection is dropped, the server stays
         }
         std::lock_guard<std::mutex> g2(st->mu);
         if (st->conns.erase(c)) ::close(c);

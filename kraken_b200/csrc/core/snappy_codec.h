@@ -153,6 +153,9 @@ inline bool Uncompress(const char* data, size_t n, std::string* out) {
     if (b < 128) break;
   }
   if (total > (1ull << 32)) return false;
+  // the densest element is a 3-byte copy of 64 bytes: a stream cannot expand by more than ~21.4 x, so a header
+  // that claims more is damaged (and must not make this side allocate gigabytes for a few bytes of input)
+  if (total > 22ull * n + 64) return false;
   const size_t want = static_cast<size_t>(total);
   out->assign(want, '\0');
   char* dst = want ? &(*out)[0] : nullptr;

@@ -157,3 +157,29 @@ def test_message_bodies_pack_and_unpack_with_one_copy_per_tensor():
     for bad in (body[:-1], body[:9], b"\x09\x00\x00\x00{}", body[:len(j) + 8] + b"\xff" * 8):
         with pytest.raises(C.KrakenError):
             rpc.unpack_body(bad)
+
+
+def test_hostile_frames_do_not_take_the_server_down():
+    """A length field that announces gigabytes, a Snappy header that claims an impossible expansion, an unknown
+    compression code: the connection is dropped (or the frame refused), the station keeps serving others."""
+    st, _ = echo_station()
+    try:
+        for bad in (struct.pack("<IQiB", 0xFFFFFFF0, 1, 0, 0) + b"tiny",                       # 4 GiB announced, 4 bytes sent
+                    struct.pack("<IQiB", 6, 2, 0, 1) + b"\xff\xff\xff\xff\x0f\x00",             # Snappy: 4 GiB from 6 bytes
+                    struct.pack("<IQiB", 3, 3, 0, 9) + b"abc"):                                 # compression code 9
+            s = socket.create_connection(("127.0.0.1", st.port))
+            s.sendall(bad)
+            s.shutdown(socket.SHUT_WR)
+            s.settimeout(5)
+            try:
+                assert s.recv(64) == b""        # no reply: the server closed the connection
+            except ConnectionResetError:
+                pass                            # ... with bytes of ours still unread
+            s.close()
+        c = C.NetConnecter("127.0.0.1", st.port, 2000, 1)
+        assert c.call(7, b"still here", 0) == (0, 0, b"ereh llits")
+        c.close()
+    finally:
+        st.stop()
+    with pytest.raises(C.KrakenError):
+        C.snappy_uncompress(b"\xff\xff\xff\xff\x0f\x00")      # claims 4 GiB, holds one byte
