@@ -505,10 +505,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         Reader rr(&one);
         std::vector<int64_t> dims = rr.Vec<int64_t>();
         const DType dt = static_cast<DType>(rr.Pod<uint8_t>());
-        for (int64_t d : dims) KB_CHECK(d >= 0, err::kDeserializeRequest, "negative tensor extent");
+        // the shape comes off the wire: it must describe exactly the bytes that follow BEFORE anything is allocated
+        const uint64_t payload = len - 1 - one.offset();
+        uint64_t bytes = DTypeBytes(dt);
+        KB_CHECK(bytes > 0, err::kDeserializeRequest, "tensor of a type without a size");
+        for (int64_t d : dims) {
+          KB_CHECK(d >= 0, err::kDeserializeRequest, "negative tensor extent");
+          KB_CHECK(d == 0 || bytes <= payload / static_cast<uint64_t>(d), err::kDeserializeRequest,
+                   "tensor payload does not match its shape");
+          bytes *= static_cast<uint64_t>(d);
+        }
+        KB_CHECK(bytes == payload, err::kDeserializeRequest, "tensor payload does not match its shape");
         torch::Tensor t = torch::empty(dims, torch::TensorOptions().dtype(scalar_of(dt)));
-        KB_CHECK(1 + one.offset() + static_cast<size_t>(t.nbytes()) == len, err::kDeserializeRequest,
-                 "tensor payload does not match its shape");
         if (t.nbytes()) std::memcpy(t.data_ptr(), q + 1 + one.offset(), static_cast<size_t>(t.nbytes()));
         tensors.append(t);
       } else {

@@ -154,7 +154,11 @@ def test_message_bodies_pack_and_unpack_with_one_copy_per_tensor():
     for a, b in zip(ts, got):
         assert a.dtype == b.dtype and torch.equal(a, b)
     assert rpc.unpack_body(rpc.pack_body({}, [])) == ({}, [])
-    for bad in (body[:-1], body[:9], b"\x09\x00\x00\x00{}", body[:len(j) + 8] + b"\xff" * 8):
+    # a tensor header that claims 2^40 x 2^20 floats in front of 8 bytes of payload must be refused before anything
+    # of that size is allocated
+    hdr = struct.pack("<BQqqB", 0, 2, 1 << 40, 1 << 20, 11)
+    bomb = struct.pack("<I", 2) + b"{}" + struct.pack("<IQ", 1, len(hdr) + 8) + hdr + b"\0" * 8
+    for bad in (body[:-1], body[:9], b"\x09\x00\x00\x00{}", body[:len(j) + 8] + b"\xff" * 8, bomb):
         with pytest.raises(C.KrakenError):
             rpc.unpack_body(bad)
 
