@@ -10,7 +10,7 @@ from .initializer import (ConstantInitializer, NormalInitializer, UniformInitial
                           XavierUniformInitializer)
 from .jagged_embedding import CombineJaggedEmbedding, JaggedEmbedding
 from .jagged_tensor import JaggedTensor
-from .lr import LR, ConstantLR, StepLR
+from .lr import LR, ConstantLR, ExponentialLR, LambdaLR, StepLR, WarmupCosineLR
 from .optim import SGD, Adagrad, Adam, RMSprop
 from .optimizer import Optimizer
 from .sparse_table import CombineSparseTable, SparseTable

@@ -1,69 +1,63 @@
-"""Row initializer descriptors: (type, string conf) pairs that travel to the
-shards and into checkpoints (same classes and conf keys as
-kraken/pytorch/initializer.py:16-78)."""
+"""Row initializer descriptors: a kind and string-valued options that travel to the shards and into
+checkpoints.  Same class names, constructor arguments and option keys as the reference's
+kraken/pytorch/initializer.py:16-78, so model code written for it constructs them unchanged."""
 from typing import Dict
 
 from .native import InitializerType
 
 
-class Initializer(object):
+class Initializer:
+    """A kind plus named options; subclasses only name their options and defaults."""
+
+    KIND = None
+
+    def __init__(self, **options: float) -> None:
+        self._options = dict(options)
+
     def type(self):
-        raise NotImplementedError
+        if self.KIND is None:
+            raise NotImplementedError("Initializer is abstract: use one of its subclasses")
+        return self.KIND
 
     def conf(self) -> Dict[str, str]:
-        raise NotImplementedError
+        """Options as strings, the form in which the shards and the checkpoint files keep them."""
+        return {name: str(value) for name, value in self._options.items()}
+
+    def __repr__(self) -> str:
+        inner = ", ".join(f"{k}={v}" for k, v in self._options.items())
+        return f"{type(self).__name__}({inner})"
 
 
 class ConstantInitializer(Initializer):
-    def __init__(self, value: float = 0.0):
-        self._value = value
+    KIND = InitializerType.kConstant
 
-    def type(self):
-        return InitializerType.kConstant
-
-    def conf(self):
-        return {"value": str(self._value)}
+    def __init__(self, value: float = 0.0) -> None:
+        super().__init__(value=value)
 
 
 class UniformInitializer(Initializer):
-    def __init__(self, lower: float = 0.0, upper: float = 1.0):
-        self._lower, self._upper = lower, upper
+    KIND = InitializerType.kUniform
 
-    def type(self):
-        return InitializerType.kUniform
-
-    def conf(self):
-        return {"lower": str(self._lower), "upper": str(self._upper)}
+    def __init__(self, lower: float = 0.0, upper: float = 1.0) -> None:
+        super().__init__(lower=lower, upper=upper)
 
 
 class NormalInitializer(Initializer):
-    def __init__(self, mean: float = 0.0, stddev: float = 1.0):
-        self._mean, self._stddev = mean, stddev
+    KIND = InitializerType.kNormal
 
-    def type(self):
-        return InitializerType.kNormal
-
-    def conf(self):
-        return {"mean": str(self._mean), "stddev": str(self._stddev)}
+    def __init__(self, mean: float = 0.0, stddev: float = 1.0) -> None:
+        super().__init__(mean=mean, stddev=stddev)
 
 
 class XavierUniformInitializer(Initializer):
-    def __init__(self, gain: float = 1.0):
-        self._gain = gain
+    KIND = InitializerType.kXavierUniform
 
-    def type(self):
-        return InitializerType.kXavierUniform
-
-    def conf(self):
-        return {"gain": str(self._gain)}
+    def __init__(self, gain: float = 1.0) -> None:
+        super().__init__(gain=gain)
 
 
 class XavierNormalInitializer(Initializer):
-    def __init__(self, gain: float = 1.0):
-        self._gain = gain
+    KIND = InitializerType.kXavierNormal
 
-    def type(self):
-        return InitializerType.kXavierNormal
-
-    def conf(self):
-        return {"gain": str(self._gain)}
+    def __init__(self, gain: float = 1.0) -> None:
+        super().__init__(gain=gain)

@@ -286,3 +286,30 @@ def test_corrupted_or_missing_checkpoint_is_reported(tmp_path):
     assert kk.try_load_model_blocked(d)
     assert kk.native.engine().shard.sparse_size(0) == 500
     kk.stop()
+
+
+def test_learning_rate_schedules_reach_the_servers():
+    """A schedule is stepped once per optimizer step and its rate travels with the next push (the reference's
+    Optimizer does lr.step() + update_lr in step(), kraken/pytorch/optimizer.py:151-173; it ships ConstantLR only)."""
+    import math
+    assert [round(kk.StepLR(1.0, 2, 0.5).rate_at(n), 4) for n in range(5)] == [1.0, 1.0, 0.5, 0.5, 0.25]
+    assert [round(kk.ExponentialLR(2.0, 0.5).rate_at(n), 4) for n in range(3)] == [2.0, 1.0, 0.5]
+    wc = kk.WarmupCosineLR(1.0, warmup=4, total=12, floor=0.1)
+    assert [round(wc.rate_at(n), 3) for n in (0, 3, 4, 8, 12, 20)] == [0.25, 1.0, 1.0, 0.55, 0.1, 0.1]
+    assert kk.LambdaLR(0.5, lambda n: 1.0 / (1 + n)).rate_at(3) == 0.125
+
+    kk.initialize("cpu", seed=0)
+    try:
+        emb = kk.Embedding(2, initializer=kk.ConstantInitializer(1.0), name="sched")
+        opt = kk.Optimizer("sched", emb.named_parameters(), kk.StepLR(0.5, step_size=2, gamma=0.1), kk.SGD())
+        ids = torch.tensor([7])
+        seen = []
+        for _ in range(5):
+            before = emb(ids).detach().clone()
+            emb(ids).sum().backward()            # gradient 1 per element: the row moves by exactly the rate in force
+            opt.step()
+            seen.append(round(float((before - emb(ids).detach())[0, 0]), 6))
+        assert seen == [0.5, 0.5, 0.05, 0.05, 0.005]
+        assert math.isclose(kk.native.engine().lr, 0.005, rel_tol=1e-6)
+    finally:
+        kk.stop()
