@@ -14,6 +14,7 @@ job: NCCL for the GPU engine, gloo for the CPU engine.
 from __future__ import annotations
 
 import os
+import re
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -66,6 +67,8 @@ def initialize(s_addr: str = "auto", emitter_type=EmitterType.kDefault, life_spa
     if backend is None:
         head = (s_addr or "auto").split("://")[0].lower()
         backend = head if head in ("cpu", "gpu") else ("remote" if head == "tcp" else "auto")
+        if backend == "auto" and re.fullmatch(r"[^:/\s]+:\d{1,5}", s_addr or ""):
+            backend = "remote"     # "host:port", the reference's form of a scheduler address
     if backend == "auto":
         backend = "gpu" if torch.cuda.is_available() else "cpu"
     cfg = EngineConfig(backend=backend, emitter_type=emitter_type, life_span=int(life_span), eta=float(eta))

@@ -313,3 +313,25 @@ def test_learning_rate_schedules_reach_the_servers():
         assert math.isclose(kk.native.engine().lr, 0.005, rel_tol=1e-6)
     finally:
         kk.stop()
+
+
+def test_alias_resolves_every_module_path_of_the_reference_layout():
+    """``install_alias()``: ``kraken.pytorch`` and each module the reference has under it
+    (kraken/pytorch/*.py), plus ``kraken_native``, resolve to THE modules of this package, not to second copies
+    (a second copy of a submodule would load the native library twice); unknown names still fail."""
+    import importlib
+    import sys
+
+    import kraken_b200
+    kraken_b200.install_alias()
+    for name in ("embedding", "combine_embedding", "jagged_embedding", "combine_jagged_embedding", "jagged_tensor",
+                 "jagged_embedding_funcs", "sparse_table", "combine_sparse_table", "optim", "optimizer", "initializer", "lr"):
+        aliased = importlib.import_module("kraken.pytorch." + name)
+        assert aliased is importlib.import_module("kraken_b200.pytorch." + name), name
+    from kraken.pytorch.combine_jagged_embedding import CombineJaggedEmbedding
+    from kraken.pytorch.combine_sparse_table import CombineSparseTable
+    assert CombineJaggedEmbedding.__module__.startswith("kraken_b200.") and CombineSparseTable is not None
+    import kraken_native
+    assert kraken_native is sys.modules["kraken_b200.pytorch.native"] and hasattr(kraken_native, "jagged_mean_backward")
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("kraken.pytorch.no_such_module")

@@ -74,7 +74,7 @@ def test_worker_against_scheduler_and_two_servers(tmp_path):
 def test_stale_ring_is_refetched_once(tmp_path):
     sched, servers = boot(tmp_path, n_ps=1)
     try:
-        kk.initialize(f"tcp://127.0.0.1:{sched.port}")
+        kk.initialize(f"127.0.0.1:{sched.port}")     # a bare "host:port", as the reference's scheduler address
         kk.init_model("m", kk.OptimType.kSGD, {})
         kk.update_lr(1.0)
         ts = kk.register_sparse_table("e", 2, torch.float32, kk.InitializerType.kConstant, {"value": "0"})
