@@ -225,3 +225,51 @@ def test_the_same_script_trains_the_same_under_both_packages(tmp_path):
     assert np.allclose(ours["losses"], ref["losses"], rtol=1e-4, atol=1e-5), (ours["losses"], ref["losses"])
     for k in range(6):
         assert np.allclose(ours[f"param_{k}"], ref[f"param_{k}"], rtol=1e-3, atol=1e-5), k
+
+
+def test_the_references_own_example_model_runs_unmodified_under_the_alias():
+    """examples/DeepFM/model/DeepFM.py of the reference - 39 + 39 ``kk.Embedding`` tables, ``kk.Optimizer`` with
+    ``kk.Adam()``, its own ``fit`` loop - is imported from the reference checkout as it is and trained on the CPU
+    engine behind ``install_alias()``.  (Its ``main.py`` cannot run anywhere: the data file it reads,
+    ``feature_sizes.txt``, is empty in the checkout.)"""
+    import importlib.util
+    src = os.path.join(os.environ.get("KRAKEN_REFERENCE_SRC", "/root/reference"), "examples", "DeepFM", "model", "DeepFM.py")
+    if not os.path.exists(src):
+        pytest.skip("no checkout of the reference here")
+    import kraken_b200
+    kraken_b200.install_alias()
+    import kraken.pytorch as kk
+    spec = importlib.util.spec_from_file_location("reference_example_deepfm", src)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(5)
+    fields, n = 39, 64
+    batches = []
+    for _ in range(6):
+        xi = torch.randint(0, 50, (n, fields, 1), generator=g)
+        xv = torch.ones(n, fields)
+        y = ((xi[:, 0, 0] % 2) == 0).float()            # learnable from the first field
+        batches.append((xi, xv, y))
+
+    class Loader(list):
+        class dataset:
+            train = True
+
+    kk.initialize("cpu", seed=0)
+    try:
+        model = mod.DeepFM([50] * fields, use_cuda=False)
+        optimizer = kk.Optimizer(model_name="DeepFM", named_parameters=model.named_parameters(), optim=kk.Adam(), lr=1e-2)
+        assert len(kk.native.engine().tables) >= 2 * fields          # every Embedding became a sparse table
+        crit = torch.nn.functional.binary_cross_entropy_with_logits
+        model.eval()
+        with torch.no_grad():
+            before = float(sum(crit(model(xi, xv.float()), y) for xi, xv, y in batches)) / len(batches)
+        model.fit(Loader(batches), Loader(batches), optimizer, epochs=15, verbose=False)
+        model.eval()
+        with torch.no_grad():
+            after = float(sum(crit(model(xi, xv.float()), y) for xi, xv, y in batches)) / len(batches)
+        assert after < 0.7 * before, (before, after)
+    finally:
+        kk.stop()
