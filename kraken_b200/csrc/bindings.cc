@@ -529,6 +529,66 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return py::make_tuple(json, tensors);
   });
 
+  // ---------------- the reference's own message bodies (ZeroMQ front end): a vector<Tensor> of n rows of one width,
+  // as its servers answer a sparse pull and its workers send sparse gradients (kraken/common/serialize.h:156-217:
+  // u64 count, then per tensor u8 layout = 0, Shape = u64 rank + i64 dims, u8 dtype, raw data)
+  m.def("wire_rows_to_tensor_list", [](const torch::Tensor& rows_in) {
+    torch::Tensor rows = rows_in.detach().contiguous();
+    need_cpu(rows, "rows", torch::kFloat32);
+    TORCH_CHECK(rows.dim() == 2, "rows must be [n, dim]");
+    const uint64_t n = static_cast<uint64_t>(rows.size(0));
+    const int64_t dim = rows.size(1);
+    const size_t per = 1 + 8 + 8 + 1 + static_cast<size_t>(dim) * 4;
+    py::bytes out = py::reinterpret_steal<py::bytes>(PyBytes_FromStringAndSize(nullptr, static_cast<Py_ssize_t>(8 + n * per)));
+    KB_CHECK(out.ptr() != nullptr, err::kSerializeReply, "cannot allocate the reply");
+    char* p = PyBytes_AS_STRING(out.ptr());
+    std::memcpy(p, &n, 8);
+    p += 8;
+    const uint64_t rank = 1;
+    const uint8_t f32 = static_cast<uint8_t>(DType::kFloat32);
+    const float* src = rows.data_ptr<float>();
+    for (uint64_t i = 0; i < n; ++i) {
+      *p++ = 0;
+      std::memcpy(p, &rank, 8);
+      std::memcpy(p + 8, &dim, 8);
+      p[16] = static_cast<char>(f32);
+      std::memcpy(p + 17, src + i * dim, static_cast<size_t>(dim) * 4);
+      p += 17 + static_cast<size_t>(dim) * 4;
+    }
+    return out;
+  });
+  m.def("wire_tensor_list_to_rows", [](const std::string& b, uint64_t offset) {
+    // (rows [n, dim] float32, offset behind the list); every tensor must be a dense float32 vector of one width
+    auto fail = [] { throw KrakenError(err::kDeserializeRequest, "malformed list of row tensors"); };
+    size_t pos = static_cast<size_t>(offset);
+    if (pos + 8 > b.size()) fail();
+    uint64_t n;
+    std::memcpy(&n, b.data() + pos, 8);
+    pos += 8;
+    int64_t dim = 0;
+    torch::Tensor rows;
+    for (uint64_t i = 0; i < n; ++i) {
+      if (pos + 18 > b.size()) fail();
+      uint64_t rank;
+      int64_t d;
+      std::memcpy(&rank, b.data() + pos + 1, 8);
+      if (b[pos] != 0 || rank != 1) fail();
+      if (pos + 18 > b.size()) fail();
+      std::memcpy(&d, b.data() + pos + 9, 8);
+      if (static_cast<uint8_t>(b[pos + 17]) != static_cast<uint8_t>(DType::kFloat32) || d < 0) fail();
+      if (i == 0) {
+        dim = d;
+        if (n > (b.size() - pos) / (18 + static_cast<size_t>(dim) * 4 == 0 ? 1 : 18 + static_cast<size_t>(dim) * 4)) fail();
+        rows = torch::empty({static_cast<int64_t>(n), dim}, torch::kFloat32);
+      }
+      if (d != dim || pos + 18 + static_cast<size_t>(dim) * 4 > b.size()) fail();
+      std::memcpy(rows.data_ptr<float>() + i * dim, b.data() + pos + 18, static_cast<size_t>(dim) * 4);
+      pos += 18 + static_cast<size_t>(dim) * 4;
+    }
+    if (n == 0) rows = torch::empty({0, 0}, torch::kFloat32);
+    return py::make_tuple(rows, static_cast<uint64_t>(pos));
+  });
+
   // ---------------- serializer (tests, socket transport)
   m.def("serialize_tensor", [](const torch::Tensor& t) {
     MemSink s;
