@@ -66,7 +66,7 @@ def initialize(s_addr: str = "auto", emitter_type=EmitterType.kDefault, life_spa
     backend = options.pop("backend", None)
     if backend is None:
         head = (s_addr or "auto").split("://")[0].lower()
-        backend = head if head in ("cpu", "gpu") else ("remote" if head == "tcp" else "auto")
+        backend = head if head in ("cpu", "gpu", "zmq") else ("remote" if head == "tcp" else "auto")
         if backend == "auto" and re.fullmatch(r"[^:/\s]+:\d{1,5}", s_addr or ""):
             backend = "remote"     # "host:port", the reference's form of a scheduler address
     if backend == "auto":
@@ -78,6 +78,11 @@ def initialize(s_addr: str = "auto", emitter_type=EmitterType.kDefault, life_spa
             raise KrakenError(f"unknown initialize option {k!r}")
         setattr(cfg, k, v)
 
+    if backend == "zmq":
+        # this framework's worker on a cluster of the REFERENCE's scheduler and servers (its ZeroMQ wire protocol)
+        from ..runtime.zmq_client import ZmqRemoteEngine
+        _engine = ZmqRemoteEngine(cfg, s_addr.split("://", 1)[-1])
+        return
     if backend == "remote":
         # multi-process CPU deployment: s_addr = "tcp://host:port" of a running scheduler_server
         from ..runtime.remote import RemoteEngine

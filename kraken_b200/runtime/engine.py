@@ -26,7 +26,7 @@ from .._native import C
 
 @dataclass
 class EngineConfig:
-    backend: str = "auto"            # "cpu" | "gpu" | "auto"
+    backend: str = "auto"            # "cpu" | "gpu" | "auto" ("remote" / "zmq" are chosen by the address given to initialize)
     emitter_type: object = None      # C.EmitterType
     life_span: int = 1000
     eta: float = 0.75

@@ -690,10 +690,12 @@ def _model_meta(meta: dict):
 class RemoteEngine(Engine):
     """Worker-side engine of the multi-process deployment (``initialize("host:port")``)."""
 
+    connecter_cls = Connecter    # how this worker reaches a scheduler or a server (a subclass may speak another wire)
+
     def __init__(self, cfg: EngineConfig, s_addr: str) -> None:
         super().__init__(cfg, 0, 1)
         self.device = torch.device("cpu")
-        self.scheduler = Connecter(s_addr)   # control messages travel uncompressed, as in the reference
+        self.scheduler = self.connecter_cls(s_addr)   # control messages travel uncompressed, as in the reference
         self.compress = 1 if (cfg.compress is not None and int(getattr(cfg.compress, "value", cfg.compress)) != 0) else 0
         self.ps: Dict[int, Connecter] = {}
         self.dct_states: Dict[int, object] = {}
@@ -716,7 +718,7 @@ class RemoteEngine(Engine):
             router = _router_from_hex(meta["router"])
             for nid, addr in meta["nodes"].items():
                 if int(nid) not in self.ps:
-                    self.ps[int(nid)] = Connecter(addr, compress=self.compress)
+                    self.ps[int(nid)] = self.connecter_cls(addr, compress=self.compress)
             vn = router.vnodes()
             vhash = np.array([v[0] for v in vn], dtype=np.uint64)
             vnode = np.array([v[1] for v in vn], dtype=np.int64)

@@ -1,6 +1,8 @@
-"""Workers of the UNMODIFIED reference train against servers of this framework through the ZeroMQ front end
+"""Interoperation with the reference over ITS wire protocol, both ways.  Workers of the UNMODIFIED reference train against servers of this framework through the ZeroMQ front end
 (kraken_b200/runtime/zmq_frontend.py): its worker library, its wire format, this package's scheduler_server and
-ps_server behind it.  Needs the offline reference build and pyzmq; skipped where either is absent."""
+ps_server behind it; and this framework's worker (``initialize("zmq://...")``, kraken_b200/runtime/zmq_client.py)
+trains on the reference's own scheduler_server and ps_server processes.  Needs the offline reference build and
+pyzmq; skipped where either is absent."""
 import os
 import subprocess
 import sys
@@ -142,3 +144,74 @@ def test_reference_dct_emitter_pushes_through_the_front_end(tmp_path):
             assert np.allclose(kk.pull_dense_table(ts).numpy(), got[f"small_{k}"], atol=1e-6), k
     finally:
         kk.stop()
+
+
+def test_this_frameworks_worker_trains_on_the_references_servers(tmp_path):
+    """The other direction: ``kk.initialize("zmq://...")`` puts this framework's worker (its deduplication, ring
+    routing, retries) on a cluster of the reference's own scheduler_server and two ps_server processes.  The same
+    training script gives the losses the reference's own worker gets on a cluster of the same kind."""
+    from test_reference_checkpoint_compat import ReferenceCluster
+    script = os.path.join(ROOT, "baseline", "dropin_train.py")
+    outs = {}
+    for impl in ("reference", "ours"):
+        cluster = ReferenceCluster(str(tmp_path / f"scratch_{impl}"), n_ps=2)
+        try:
+            outs[impl] = str(tmp_path / f"{impl}.npz")
+            if impl == "reference":
+                cmd = [sys.executable, script, "--impl", "reference", "--ref-path", REF, "--s-addr", cluster.s_addr, "--out", outs[impl]]
+                env = cluster.env
+            else:
+                cmd = [sys.executable, script, "--impl", "ours", "--s-addr", "zmq://" + cluster.s_addr, "--out", outs[impl]]
+                env = dict(os.environ, KRAKEN_B200_NO_BUILD="1", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+            run = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+            assert run.returncode == 0, (impl, (run.stdout + run.stderr)[-3000:])
+        finally:
+            cluster.stop()
+    a, b = dict(np.load(outs["reference"])), dict(np.load(outs["ours"]))
+    assert np.allclose(a["losses"], b["losses"], rtol=1e-4, atol=1e-5), (a["losses"], b["losses"])
+    for k in range(6):
+        assert np.allclose(a[f"param_{k}"], b[f"param_{k}"], rtol=1e-3, atol=1e-5), k
+
+
+def test_this_frameworks_api_on_the_references_servers(tmp_path):
+    """Table by table through the public API against the reference's servers: dense and sparse pull / push, the
+    combined calls, a DCT-compressed dense push, a checkpoint the reference writes."""
+    import kraken_b200.pytorch as kk
+    from test_reference_checkpoint_compat import ReferenceCluster
+    saved = tmp_path / "ref_saved"
+    saved.mkdir()
+    cluster = ReferenceCluster(str(saved), n_ps=2)
+    try:
+        kk.initialize("zmq://" + cluster.s_addr, kk.EmitterType.kDCT, 2, 0.75)
+        kk.init_model("api", kk.OptimType.kSGD, {})
+        kk.update_lr(0.5)
+        a = torch.randn(3, 4)
+        td = kk.register_dense_table("w", a)
+        tb = kk.register_dense_table("big", torch.zeros(20, 20))          # 400 elements: DCT compresses its gradient
+        ts = kk.register_sparse_table("e", 3, torch.float32, kk.InitializerType.kConstant, {"value": "1.0"})
+        t2 = kk.register_sparse_table("f", 2, torch.float32, kk.InitializerType.kConstant, {"value": "-1.0"})
+        assert kk.register_dense_table("w", a) == td
+        assert torch.equal(kk.pull_dense_table(td), a)
+        g = torch.randn(3, 4)
+        kk.push_dense_table(td, g)
+        assert torch.allclose(kk.pull_dense_table(td), a - 0.5 * g)
+        ids = torch.arange(40).view(4, 10)
+        assert torch.equal(kk.pull_sparse_table(ts, ids), torch.ones(4, 10, 3))
+        kk.push_sparse_table(ts, torch.tensor([3, 3, 7]), torch.ones(3, 3))
+        assert torch.allclose(kk.pull_sparse_table(ts, torch.tensor([3, 7, 8])), torch.tensor([[0.0] * 3, [0.5] * 3, [1.0] * 3]))
+        r1, r2 = kk.combine_pull_sparse_table([ts, t2], [torch.tensor([3, 100]), torch.tensor([5, 6, 5])])
+        assert torch.allclose(r1, torch.tensor([[0.0] * 3, [1.0] * 3])) and torch.equal(r2, -torch.ones(3, 2))
+        kk.combine_push_sparse_table([ts, t2], [torch.tensor([100]), torch.tensor([5, 5])], [torch.ones(1, 3), torch.ones(2, 2)])
+        assert torch.allclose(kk.pull_sparse_table(t2, torch.tensor([5, 6])), torch.tensor([[-2.0, -2.0], [-1.0, -1.0]]))
+        d1, d2 = kk.combine_pull_dense_table([td, tb])
+        assert torch.allclose(d1, a - 0.5 * g) and torch.equal(d2, torch.zeros(20, 20))
+        gb = torch.randn(20, 20)
+        kk.push_dense_table(tb, gb)                                         # travels as a COO gradient: top 25 % by magnitude
+        moved = kk.pull_dense_table(tb)
+        kept = moved != 0
+        assert 0.2 < kept.float().mean() < 0.3 and torch.allclose(moved[kept], (-0.5 * gb)[kept])
+        assert kk.try_save_model()
+        assert sorted(d for d in os.listdir(saved) if d.startswith("shard_")) == ["shard_0", "shard_1"]
+    finally:
+        kk.stop()
+        cluster.stop()
