@@ -1,6 +1,8 @@
-"""Interoperation with the reference over ITS wire protocol, both ways.  Workers of the UNMODIFIED reference train against servers of this framework through the ZeroMQ front end
+"""Interoperation with the reference over ITS wire protocol, both ways.
+
+Workers of the UNMODIFIED reference train against servers of this framework through the ZeroMQ front end
 (kraken_b200/runtime/zmq_frontend.py): its worker library, its wire format, this package's scheduler_server and
-ps_server behind it; and this framework's worker (``initialize("zmq://...")``, kraken_b200/runtime/zmq_client.py)
+ps_server behind it.  And this framework's worker (``initialize("zmq://...")``, kraken_b200/runtime/zmq_client.py)
 trains on the reference's own scheduler_server and ps_server processes.  Needs the offline reference build and
 pyzmq; skipped where either is absent."""
 import os
