@@ -54,6 +54,28 @@ class ReferenceCluster:
                 stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL))
             time.sleep(2.0)   # the reference's scheduler takes one join at a time
         assert all(p.poll() is None for p in self.procs), "a reference server exited at start-up"
+        self._wait_for_servers(n_ps)
+
+    def _wait_for_servers(self, n_ps: int, timeout_s: float = 90.0) -> None:
+        """Asks the reference's scheduler for its ring (over its own protocol) until every server has joined; on a
+        busy machine a join can take longer than the pauses above."""
+        try:
+            from kraken_b200.runtime.rpc import Rpc, RpcError
+            from kraken_b200.runtime.zmq_client import ZmqConnecter
+        except ImportError:           # no pyzmq: the pauses above have to do
+            return
+        t0 = time.monotonic()
+        while time.monotonic() - t0 < timeout_s:
+            c = ZmqConnecter(self.s_addr, timeout_ms=2000)
+            try:
+                if len(c.call(Rpc.FETCH_ROUTER)[0]["nodes"]) >= n_ps:
+                    return
+            except RpcError:
+                pass
+            finally:
+                c.close()
+            time.sleep(0.5)
+        raise AssertionError(f"the reference's scheduler did not see {n_ps} servers within {timeout_s} s")
 
     def worker(self, mode: str, out: str, load_dir: str = "") -> dict:
         run = subprocess.run([sys.executable, WORKER, "--ref-path", REF, "--s-addr", self.s_addr, "--mode", mode, "--dir",
