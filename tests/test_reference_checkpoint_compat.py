@@ -93,6 +93,37 @@ class ReferenceCluster:
                 p.kill()
 
 
+def wait_for_checkpoint(saved_dir, n_shards: int, table_files=("e.sparse",), timeout_s: float = 60.0) -> None:
+    """The reference answers TrySaveModel once its servers have QUEUED the save (kraken/ps/ps.cc:487-520: the work
+    runs on the server's task thread); the files appear a moment later.  Returns when every shard directory holds a
+    complete set of files whose sizes have stopped changing."""
+    def snapshot():
+        sizes = {}
+        shards = sorted(d for d in os.listdir(saved_dir) if d.startswith("shard_"))
+        if len(shards) < n_shards:
+            return None
+        for d in shards:
+            stamps = sorted(os.listdir(os.path.join(saved_dir, d)))
+            if not stamps:
+                return None
+            last = os.path.join(saved_dir, d, stamps[-1])
+            names = os.listdir(last)
+            if not all(f in names for f in ("model.binary", "router.binary") + tuple(table_files)):
+                return None
+            for f in names:
+                sizes[os.path.join(last, f)] = os.path.getsize(os.path.join(last, f))
+        return sizes
+
+    t0, before = time.monotonic(), None
+    while time.monotonic() - t0 < timeout_s:
+        now = snapshot()
+        if now is not None and now == before:
+            return
+        before = now
+        time.sleep(0.4)
+    raise AssertionError(f"no complete checkpoint of {n_shards} shards under {saved_dir} within {timeout_s} s")
+
+
 def worker_inputs():
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     try:
@@ -109,6 +140,7 @@ def test_a_checkpoint_written_by_the_reference_loads_here(tmp_path):
     cluster = ReferenceCluster(str(ref_dir))
     try:
         want = cluster.worker("save", str(tmp_path / "ref_save.npz"))
+        wait_for_checkpoint(str(ref_dir), 2)          # before the servers are stopped under it
     finally:
         cluster.stop()
     assert sorted(d for d in os.listdir(ref_dir) if d.startswith("shard_")) == ["shard_0", "shard_1"]

@@ -213,6 +213,8 @@ def test_this_frameworks_api_on_the_references_servers(tmp_path):
         kept = moved != 0
         assert 0.2 < kept.float().mean() < 0.3 and torch.allclose(moved[kept], (-0.5 * gb)[kept])
         assert kk.try_save_model()
+        from test_reference_checkpoint_compat import wait_for_checkpoint
+        wait_for_checkpoint(str(saved), 2, table_files=("e.sparse", "f.sparse"))   # its servers write after they answer
         assert sorted(d for d in os.listdir(saved) if d.startswith("shard_")) == ["shard_0", "shard_1"]
     finally:
         kk.stop()
