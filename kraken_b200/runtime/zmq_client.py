@@ -25,7 +25,7 @@ from .._native import C
 from .engine import EngineConfig
 from .remote import RemoteEngine
 from .rpc import COMPRESS_NONE, Rpc, RpcError
-from .zmq_frontend import _In, _tensor_bytes
+from .ref_wire import WireReader, tensor_bytes
 
 _F32 = 11   # DType code of float32 (kraken/t/element_type.h:23-37)
 
@@ -50,7 +50,7 @@ def _u64s(v: Sequence[int]) -> bytes:
 
 def _coo(idx: torch.Tensor, val: torch.Tensor, numel: int) -> bytes:
     """A flat COO gradient as the reference's DCT emitter sends it: indices [1, nnz], values [nnz], shape [numel]."""
-    return (struct.pack("<B", 1) + _tensor_bytes(idx.to(torch.int64).reshape(1, -1)) + _tensor_bytes(val.to(torch.float32).reshape(-1))
+    return (struct.pack("<B", 1) + tensor_bytes(idx.to(torch.int64).reshape(1, -1)) + tensor_bytes(val.to(torch.float32).reshape(-1))
             + struct.pack("<Qq", 1, numel))
 
 
@@ -75,7 +75,7 @@ class ZmqConnecter:
         if rpc == Rpc.INIT_MODEL:
             return _str(meta["name"]) + struct.pack("<B", int(meta["optim_type"])) + _conf(meta["optim_conf"])
         if rpc == Rpc.REGISTER_DENSE:
-            return _str(meta["name"]) + _tensor_bytes(ts[0])
+            return _str(meta["name"]) + tensor_bytes(ts[0])
         if rpc == Rpc.REGISTER_SPARSE:
             return (_str(meta["name"]) + struct.pack("<qBB", int(meta["dimension"]), _F32, int(meta["init_type"]))
                     + _conf(meta["init_conf"]))
@@ -89,7 +89,7 @@ class ZmqConnecter:
             return v + _u64s(meta["table_ids"])
         if rpc == Rpc.PUSH_DENSE:
             tid = int(meta["table_id"])
-            grad = _coo(ts[0], ts[1], self.numel.get(tid, 0)) if meta.get("coo") else _tensor_bytes(ts[0].to(torch.float32))
+            grad = _coo(ts[0], ts[1], self.numel.get(tid, 0)) if meta.get("coo") else tensor_bytes(ts[0].to(torch.float32))
             return v + struct.pack("<Q", tid) + grad + struct.pack("<f", float(meta["lr"]))
         if rpc == Rpc.PULL_SPARSE:
             return v + struct.pack("<Q", int(meta["table_id"])) + _ids(ts[0])
@@ -107,7 +107,7 @@ class ZmqConnecter:
         raise RpcError(1, f"type {rpc} has no counterpart in the reference's worker protocol")
 
     def _reply(self, rpc: int, meta: dict, body: bytes) -> Tuple[dict, List[torch.Tensor]]:
-        r = _In(body)
+        r = WireReader(body)
         if rpc in (Rpc.REGISTER_DENSE, Rpc.REGISTER_SPARSE):
             return {"table_id": r.u64()}, []
         if rpc == Rpc.FETCH_ROUTER:
