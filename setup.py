@@ -4,6 +4,7 @@ commands with the names and flags of the reference's executables:
 
     scheduler_server --port 50000
     ps_server --port 50001 --addr 127.0.0.1:50001 --s_addr 127.0.0.1:50000 [--saved_dir DIR --max_save_count 3]
+    kraken_zmq_frontend --s_addr 127.0.0.1:50000 --port 60000      (workers of the reference use these servers)
 
 Working from the source tree needs none of this: ``python __graft_entry__.py`` builds in place.
 """
@@ -37,5 +38,6 @@ setup(
     install_requires=["torch", "numpy"],
     cmdclass={"build_py": BuildWithNative},
     entry_points={"console_scripts": ["ps_server = kraken_b200.launch.ps_server:main",
-                                      "scheduler_server = kraken_b200.launch.scheduler_server:main"]},
+                                      "scheduler_server = kraken_b200.launch.scheduler_server:main",
+                                      "kraken_zmq_frontend = kraken_b200.runtime.zmq_frontend:main"]},
 )
