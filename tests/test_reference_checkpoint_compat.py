@@ -45,24 +45,25 @@ class ReferenceCluster:
         self.s_addr = f"127.0.0.1:{ports[0]}"
         self.procs = [subprocess.Popen([os.path.join(REF, "bin", "scheduler_server"), f"--port={ports[0]}"], env=self.env,
                                        stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)]
-        time.sleep(1.0)
-        for p in ports[1:]:
+        time.sleep(0.5)
+        for k, p in enumerate(ports[1:]):
             # one request thread: a pull must not overtake the push in front of it
             self.procs.append(subprocess.Popen(
                 [os.path.join(REF, "bin", "ps_server"), f"--port={p}", "--thread_nums=1", f"--addr=127.0.0.1:{p}",
                  f"--s_addr={self.s_addr}", f"--saved_dir={saved_dir}"], env=self.env,
                 stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL))
-            time.sleep(2.0)   # the reference's scheduler takes one join at a time
+            # the reference's scheduler takes one join at a time (a server that finds another join in flight backs
+            # off for 10 s): the next server starts once this one is in the ring
+            self._wait_for_servers(k + 1)
         assert all(p.poll() is None for p in self.procs), "a reference server exited at start-up"
-        self._wait_for_servers(n_ps)
 
     def _wait_for_servers(self, n_ps: int, timeout_s: float = 90.0) -> None:
-        """Asks the reference's scheduler for its ring (over its own protocol) until every server has joined; on a
-        busy machine a join can take longer than the pauses above."""
+        """Asks the reference's scheduler for its ring (over its own protocol) until ``n_ps`` servers have joined."""
         try:
             from kraken_b200.runtime.rpc import Rpc, RpcError
             from kraken_b200.runtime.zmq_client import ZmqConnecter
-        except ImportError:           # no pyzmq: the pauses above have to do
+        except ImportError:           # no pyzmq: a fixed pause has to do
+            time.sleep(2.0)
             return
         t0 = time.monotonic()
         while time.monotonic() - t0 < timeout_s:
