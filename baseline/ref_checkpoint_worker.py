@@ -35,6 +35,39 @@ def settle():
     time.sleep(0.5)
 
 
+def wait_until_written(saved_dir: str, shards: int, timeout_s: float = 60.0) -> bool:
+    """The reference answers TrySaveModel when its servers have QUEUED the save (kraken/ps/ps.cc:487-520); a push
+    sent right behind it can land in some rows before they are written.  Returns once every shard directory holds
+    router, model and table files whose sizes have stopped changing."""
+    import os
+
+    def snapshot():
+        dirs = sorted(d for d in os.listdir(saved_dir) if d.startswith("shard_"))
+        if len(dirs) < shards:
+            return None
+        sizes = {}
+        for d in dirs:
+            stamps = sorted(os.listdir(os.path.join(saved_dir, d)))
+            if not stamps:
+                return None
+            last = os.path.join(saved_dir, d, stamps[-1])
+            names = os.listdir(last)
+            if not all(f in names for f in ("model.binary", "router.binary", "e.sparse")):
+                return None
+            for f in names:
+                sizes[os.path.join(last, f)] = os.path.getsize(os.path.join(last, f))
+        return sizes
+
+    t0, before = time.time(), None
+    while time.time() - t0 < timeout_s:
+        now = snapshot()
+        if now is not None and now == before:
+            return True
+        before = now
+        time.sleep(0.3)
+    return False
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-path", required=True)
@@ -42,6 +75,8 @@ def main() -> int:
     ap.add_argument("--mode", choices=("save", "load"), required=True)
     ap.add_argument("--dir", default="", help="checkpoint directory to load (mode load)")
     ap.add_argument("--out", required=True, help=".npz file for the numbers")
+    ap.add_argument("--saved-dir", default="", help="mode save: the servers' --saved_dir, watched until the files are complete")
+    ap.add_argument("--shards", type=int, default=1, help="mode save: how many servers write")
     a = ap.parse_args()
     sys.path.insert(0, a.ref_path)
     import kraken.pytorch as kk  # the reference's package
@@ -64,6 +99,9 @@ def main() -> int:
         out["dense_at_save"] = kk.pull_dense_table(td).numpy()
         if not kk.try_save_model():
             print("the reference refused to save", file=sys.stderr)
+            return 2
+        if a.saved_dir and not wait_until_written(a.saved_dir, a.shards):
+            print("the checkpoint files did not appear under " + a.saved_dir, file=sys.stderr)
             return 2
     else:
         if not kk.try_load_model_blocked(a.dir):

@@ -78,9 +78,10 @@ class ReferenceCluster:
             time.sleep(0.5)
         raise AssertionError(f"the reference's scheduler did not see {n_ps} servers within {timeout_s} s")
 
-    def worker(self, mode: str, out: str, load_dir: str = "") -> dict:
+    def worker(self, mode: str, out: str, load_dir: str = "", saved_dir: str = "", shards: int = 1) -> dict:
         run = subprocess.run([sys.executable, WORKER, "--ref-path", REF, "--s-addr", self.s_addr, "--mode", mode, "--dir",
-                              load_dir, "--out", out], env=self.env, capture_output=True, text=True, timeout=300)
+                              load_dir, "--out", out, "--saved-dir", saved_dir, "--shards", str(shards)],
+                             env=self.env, capture_output=True, text=True, timeout=300)
         assert run.returncode == 0, (run.stdout + run.stderr)[-2000:]
         return dict(np.load(out))
 
@@ -140,8 +141,10 @@ def test_a_checkpoint_written_by_the_reference_loads_here(tmp_path):
     ref_dir.mkdir()
     cluster = ReferenceCluster(str(ref_dir))
     try:
-        want = cluster.worker("save", str(tmp_path / "ref_save.npz"))
-        wait_for_checkpoint(str(ref_dir), 2)          # before the servers are stopped under it
+        # the worker waits for the files before it pushes again: the reference writes a checkpoint AFTER it has
+        # answered, and a push right behind the request could reach rows that are not written yet
+        want = cluster.worker("save", str(tmp_path / "ref_save.npz"), saved_dir=str(ref_dir), shards=2)
+        wait_for_checkpoint(str(ref_dir), 2)          # and before the servers are stopped under it
     finally:
         cluster.stop()
     assert sorted(d for d in os.listdir(ref_dir) if d.startswith("shard_")) == ["shard_0", "shard_1"]
