@@ -371,3 +371,44 @@ def test_async_push_returns_at_once_and_is_applied_in_order(tmp_path):
         sched.stop()
         for s in servers:
             s.stop()
+
+
+def test_several_workers_share_the_servers(tmp_path):
+    """Four worker PROCESSES train against two servers at once, on overlapping rows and one dense table
+    (the reference's data parallelism: independent workers, every push its own update,
+    kraken/worker/emitter.cc:417-447,491-550).  With SGD the order of the updates does not matter, so the
+    final tables are known exactly: a lost or doubled update under concurrency would show."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sched, servers = boot(tmp_path)
+    workers, steps = 4, 12
+    try:
+        env = dict(os.environ, KRAKEN_B200_NO_BUILD="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        procs = [subprocess.Popen([sys.executable, os.path.join(root, "tests", "mp_tcp_worker.py"),
+                                   f"tcp://127.0.0.1:{sched.port}", str(k), str(workers), str(steps)], env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for k in range(workers)]
+        outs = [p.communicate(timeout=300)[0] for p in procs]
+        for k, (p, out) in enumerate(zip(procs, outs)):
+            assert p.returncode == 0 and f"TCP_WORKER {k} ok" in out, out[-2000:]
+        # what the tables must hold: every occurrence of an id moves its row by lr * (worker index + 1)
+        want = torch.zeros(300, 4)
+        for k in range(workers):
+            g = torch.Generator().manual_seed(100 + k)
+            for _ in range(steps):
+                ids = torch.randint(0, 300, (200,), generator=g)
+                want.index_add_(0, ids, torch.full((200, 4), -0.5 * (k + 1)))
+        kk.initialize(f"tcp://127.0.0.1:{sched.port}")
+        ts = kk.register_sparse_table("e", 4, torch.float32, kk.InitializerType.kConstant, {"value": "0.0"})
+        td = kk.register_dense_table("w", torch.zeros(6, 5))
+        seen = want.abs().sum(1) > 0
+        got = kk.pull_sparse_table(ts, torch.arange(300)[seen])
+        assert torch.allclose(got, want[seen], atol=1e-4)
+        assert torch.allclose(kk.pull_dense_table(td), torch.full((6, 5), -0.5 * steps * sum(range(1, workers + 1))), atol=1e-4)
+        assert sum(s.shard.sparse_size(ts) for s in servers) == int(seen.sum())
+    finally:
+        kk.stop()
+        sched.stop()
+        for s in servers:
+            s.stop()
