@@ -931,12 +931,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("pull_dense",
            [](CpuShard& s, uint64_t id) {
              torch::Tensor out = torch::empty({s.DenseNumel(id)}, torch::kFloat32);
-             s.PullDense(id, out.data_ptr<float>());
+             {
+               py::gil_scoped_release nogil;   // the shard locks per table: other connections' handlers run meanwhile
+               s.PullDense(id, out.data_ptr<float>());
+             }
              return out;
            })
       .def("push_dense",
            [](CpuShard& s, uint64_t id, const torch::Tensor& grad, float lr) {
              torch::Tensor g = grad.detach().cpu().contiguous().to(torch::kFloat32);
+             py::gil_scoped_release nogil;
              s.PushDense(id, g.data_ptr<float>(), g.numel(), lr);
            })
       .def("push_dense_coo",
@@ -944,6 +948,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              torch::Tensor i = idx.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
              torch::Tensor v = vals.detach().cpu().contiguous().to(torch::kFloat32).reshape({-1});
              TORCH_CHECK(i.numel() == v.numel(), "COO indices and values differ in length");
+             py::gil_scoped_release nogil;
              s.PushDenseCoo(id, i.data_ptr<int64_t>(), v.data_ptr<float>(), i.numel(), lr);
            })
       .def("sparse_dim", &CpuShard::SparseDim)
@@ -952,7 +957,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            [](CpuShard& s, uint64_t id, const torch::Tensor& ids) {
              torch::Tensor i = ids.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
              torch::Tensor out = torch::empty({i.numel(), s.SparseDim(id)}, torch::kFloat32);
-             s.PullSparse(id, reinterpret_cast<const uint64_t*>(i.data_ptr<int64_t>()), i.numel(), out.data_ptr<float>());
+             {
+               py::gil_scoped_release nogil;
+               s.PullSparse(id, reinterpret_cast<const uint64_t*>(i.data_ptr<int64_t>()), i.numel(), out.data_ptr<float>());
+             }
              return out;
            })
       .def("push_sparse",
@@ -960,6 +968,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              torch::Tensor i = ids.detach().cpu().contiguous().to(torch::kInt64).reshape({-1});
              torch::Tensor g = grads.detach().cpu().contiguous().to(torch::kFloat32);
              TORCH_CHECK(g.numel() == i.numel() * s.SparseDim(id), "grads must be [n, dim]");
+             py::gil_scoped_release nogil;
              return s.PushSparse(id, reinterpret_cast<const uint64_t*>(i.data_ptr<int64_t>()), i.numel(),
                                  g.data_ptr<float>(), lr);
            })
