@@ -53,9 +53,9 @@ class ZmqFrontend:
         self.ps_native: Dict[int, Connecter] = {}
         self.shapes: Dict[int, List[int]] = {}       # dense table id -> shape (replies carry it)
         self.stopping = False
-        self.thread: Optional[threading.Thread] = None
-        self.wake = self.ctx.socket(zmq.PAIR)
-        self.wake.bind("inproc://kraken-b200-frontend-wake")
+        self.started = False
+        self.threads: List[threading.Thread] = []     # one per ROUTER socket: requests to different servers run side by side
+        self.lock = threading.Lock()
         self._discover()
 
     def _bind(self, sock, port: int) -> int:
@@ -67,13 +67,16 @@ class ZmqFrontend:
     def _discover(self) -> dict:
         """A ROUTER socket and a native connection for every server of the deployment (new ones as they join)."""
         meta, _ = self.native_sched.call(Rpc.FETCH_ROUTER)
-        for nid, addr in meta["nodes"].items():
-            nid = int(nid)
-            if nid not in self.ps_socks:
-                sock = self.ctx.socket(self.zmq.ROUTER)
-                self.ps_addr[nid] = f"{self.host}:{self._bind(sock, 0)}"
-                self.ps_socks[nid] = sock
-                self.ps_native[nid] = Connecter(addr, timeout_ms=60_000, compress=1)
+        with self.lock:
+            for nid, addr in meta["nodes"].items():
+                nid = int(nid)
+                if nid not in self.ps_socks:
+                    sock = self.ctx.socket(self.zmq.ROUTER)
+                    self.ps_addr[nid] = f"{self.host}:{self._bind(sock, 0)}"
+                    self.ps_native[nid] = Connecter(addr, timeout_ms=60_000, compress=1)
+                    self.ps_socks[nid] = sock
+                    if self.started:
+                        self._serve(sock, nid)
         return meta
 
     # ------------------------------------------------------------------ scheduler messages
@@ -175,42 +178,35 @@ class ZmqFrontend:
             code, body = 4, b""               # kDeserializeRequestError
         sock.send_multipart([ident, struct.pack("<QiB", stamp, code, comp if code == 0 and body else 0) + body])
 
-    def _run(self) -> None:
-        zmq = self.zmq
-        wake = self.ctx.socket(zmq.PAIR)
-        wake.connect("inproc://kraken-b200-frontend-wake")
-        known: Dict[object, Optional[int]] = {}
-        poller = zmq.Poller()
-        poller.register(wake, zmq.POLLIN)
-        while not self.stopping:
-            for nid, s in list(self.ps_socks.items()):
-                if s not in known:
-                    known[s] = nid
-                    poller.register(s, zmq.POLLIN)
-            if self.sched_sock not in known:
-                known[self.sched_sock] = None
-                poller.register(self.sched_sock, zmq.POLLIN)
-            for sock, _ in poller.poll(200):
-                if sock is wake:
-                    wake.recv()
-                    continue
-                self._answer(sock, known[sock])
-        wake.close()
+    def _serve(self, sock, node: Optional[int]) -> None:
+        """A thread that owns ``sock`` from here on: requests of one socket are answered in order (a worker's pull
+        behind its push sees the push), different sockets do not wait for one another."""
+        def loop():
+            poller = self.zmq.Poller()
+            poller.register(sock, self.zmq.POLLIN)
+            while not self.stopping:
+                if poller.poll(200):
+                    self._answer(sock, node)
+            sock.close(linger=0)
+
+        t = threading.Thread(target=loop, name=f"kraken-zmq-frontend-{'scheduler' if node is None else node}", daemon=True)
+        t.start()
+        self.threads.append(t)
 
     def start(self) -> None:
-        self.thread = threading.Thread(target=self._run, name="kraken-zmq-frontend", daemon=True)
-        self.thread.start()
+        with self.lock:
+            self.started = True
+            self._serve(self.sched_sock, None)
+            for nid, sock in self.ps_socks.items():
+                self._serve(sock, nid)
 
     def stop(self) -> None:
         self.stopping = True
-        try:
-            self.wake.send(b"x")
-        except Exception:
-            pass
-        if self.thread is not None:
-            self.thread.join(timeout=10)
-        for s in [self.sched_sock, self.wake] + list(self.ps_socks.values()):
-            s.close(linger=0)
+        for t in self.threads:
+            t.join(timeout=10)
+        if not self.started:
+            for s in [self.sched_sock] + list(self.ps_socks.values()):
+                s.close(linger=0)
         self.ctx.term()
         for c in [self.native_sched] + list(self.ps_native.values()):
             c.close()

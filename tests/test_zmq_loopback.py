@@ -104,3 +104,39 @@ def test_a_checkpoint_loads_through_the_front_end(tmp_path):
         sched.stop()
         for s in servers:
             s.stop()
+
+
+def test_several_workers_through_the_front_end_at_once(tmp_path):
+    """Three worker processes speak the reference's protocol to the front end at the same time, on overlapping rows
+    of two servers (every front-end socket has its own thread).  SGD: the final tables are known exactly."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sched, servers, front = boot(tmp_path)
+    workers, steps = 3, 10
+    try:
+        env = dict(os.environ, KRAKEN_B200_NO_BUILD="1", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        procs = [subprocess.Popen([sys.executable, os.path.join(root, "tests", "mp_tcp_worker.py"),
+                                   f"zmq://127.0.0.1:{front.port}", str(k), str(workers), str(steps)], env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for k in range(workers)]
+        outs = [p.communicate(timeout=300)[0] for p in procs]
+        for k, (p, out) in enumerate(zip(procs, outs)):
+            assert p.returncode == 0 and f"TCP_WORKER {k} ok" in out, out[-2000:]
+        want = torch.zeros(300, 4)
+        for k in range(workers):
+            g = torch.Generator().manual_seed(100 + k)
+            for _ in range(steps):
+                ids = torch.randint(0, 300, (200,), generator=g)
+                want.index_add_(0, ids, torch.full((200, 4), -0.5 * (k + 1)))
+        kk.initialize(f"zmq://127.0.0.1:{front.port}")
+        ts = kk.register_sparse_table("e", 4, torch.float32, kk.InitializerType.kConstant, {"value": "0.0"})
+        td = kk.register_dense_table("w", torch.zeros(6, 5))
+        seen = want.abs().sum(1) > 0
+        assert torch.allclose(kk.pull_sparse_table(ts, torch.arange(300)[seen]), want[seen], atol=1e-4)
+        assert torch.allclose(kk.pull_dense_table(td), torch.full((6, 5), -0.5 * steps * sum(range(1, workers + 1))), atol=1e-4)
+    finally:
+        kk.stop()
+        front.stop()
+        sched.stop()
+        for s in servers:
+            s.stop()
